@@ -1,0 +1,99 @@
+# Build of libdccl.so, the command-line tools and the examples.
+#
+#   make                 library + tools for B200 (sm_100a), CUDA enabled
+#   make CUDA=0          host-only library (no nvcc needed; device calls are refused)
+#   make SANITIZE=address|thread|undefined   instrument the host code (host-only build)
+#   make DEBUG_BOUNDS=1  device kernels check every access against its buffer and
+#                        report through the status word instead of touching memory
+#
+# Everything lands in build/; the shared library is also copied into the Python
+# package (dccl_b200/lib/) so that it is found next to the bindings.
+
+CUDA ?= 1
+CUDA_HOME ?= /usr/local/cuda
+NVCC ?= $(CUDA_HOME)/bin/nvcc
+CXX ?= g++
+BUILD ?= build
+CACHELINE := $(shell getconf LEVEL1_DCACHE_LINESIZE 2>/dev/null || echo 64)
+ifeq ($(CACHELINE),0)
+CACHELINE := 64
+endif
+ifeq ($(CACHELINE),)
+CACHELINE := 64
+endif
+
+CXXFLAGS := -std=c++17 -O3 -fPIC -Wall -Wextra -Wno-unused-parameter -Iinclude -DCACHELINE_SIZE=$(CACHELINE) -DENABLE_EVALUATION=1 -pthread
+LDFLAGS := -pthread -lrt -ldl
+NVCCFLAGS := -std=c++17 -O3 -lineinfo -gencode arch=compute_100a,code=sm_100a -Xcompiler -fPIC -Iinclude \
+             -DCACHELINE_SIZE=$(CACHELINE) -DENABLE_EVALUATION=1 -DDCCL_WITH_CUDA_RUNTIME
+ifdef PTXAS_V
+NVCCFLAGS += -Xptxas -v
+endif
+ifdef DEBUG_BOUNDS
+NVCCFLAGS += -DDCCL_DEBUG_BOUNDS=1
+endif
+ifdef SANITIZE
+CUDA := 0
+CXXFLAGS += -fsanitize=$(SANITIZE) -fno-omit-frame-pointer -g
+LDFLAGS += -fsanitize=$(SANITIZE)
+BUILD := build-$(SANITIZE)
+endif
+
+HOST_SRCS := csrc/core/config.cpp csrc/core/log.cpp csrc/core/timestamp.cpp \
+             csrc/bootstrap/bootstrap.cpp csrc/cpu/cpu_backend.cpp \
+             csrc/api/dccl_api.cpp csrc/api/c_api.cpp csrc/api/names.cpp csrc/tuner/tuner.cpp
+ifeq ($(CUDA),1)
+CU_SRCS := $(wildcard csrc/gpu/*.cu) $(wildcard csrc/kernels/*.cu)
+CXXFLAGS += -DDCCL_WITH_CUDA -DDCCL_WITH_CUDA_RUNTIME -I$(CUDA_HOME)/include
+CUDA_LIBS := -L$(CUDA_HOME)/lib64 -lcudart_static
+TOOL_DEFS := -DDCCL_WITH_CUDA
+else
+HOST_SRCS += csrc/gpu/gpu_stub.cpp
+CU_SRCS :=
+CUDA_LIBS :=
+TOOL_DEFS :=
+endif
+
+HOST_OBJS := $(patsubst %.cpp,$(BUILD)/obj/%.o,$(HOST_SRCS))
+CU_OBJS := $(patsubst %.cu,$(BUILD)/obj/%.cu.o,$(CU_SRCS))
+LIB := $(BUILD)/libdccl.so
+TOOLS := $(BUILD)/dccl_cli $(BUILD)/p2p_perf $(BUILD)/helloworld
+ifeq ($(CUDA),1)
+TOOLS += $(BUILD)/nccl_cli
+endif
+
+.PHONY: all lib tools clean
+all: lib tools
+lib: $(LIB) dccl_b200/lib/libdccl.so
+tools: $(TOOLS)
+
+$(BUILD)/obj/%.o: %.cpp $(wildcard include/dccl/*.hpp) $(wildcard csrc/*/*.hpp)
+	@mkdir -p $(dir $@)
+	$(CXX) $(CXXFLAGS) -c $< -o $@
+
+$(BUILD)/obj/%.cu.o: %.cu $(wildcard include/dccl/*.hpp) $(wildcard csrc/*/*.hpp) $(wildcard csrc/*/*.cuh)
+	@mkdir -p $(dir $@)
+	$(NVCC) $(NVCCFLAGS) -c $< -o $@
+
+$(LIB): $(HOST_OBJS) $(CU_OBJS)
+	$(CXX) -shared -o $@ $^ $(CUDA_LIBS) $(LDFLAGS)
+
+dccl_b200/lib/libdccl.so: $(LIB)
+	@mkdir -p dccl_b200/lib
+	cp $(LIB) $@
+
+$(BUILD)/dccl_cli: tools/dccl_cli.cpp tools/tool_common.hpp $(LIB)
+	$(CXX) $(CXXFLAGS) $(TOOL_DEFS) $< -o $@ -L$(BUILD) -ldccl -Wl,-rpath,'$$ORIGIN' $(CUDA_LIBS) $(LDFLAGS)
+
+$(BUILD)/p2p_perf: tools/p2p_perf.cpp tools/tool_common.hpp $(LIB)
+	$(CXX) $(CXXFLAGS) $(TOOL_DEFS) $< -o $@ -L$(BUILD) -ldccl -Wl,-rpath,'$$ORIGIN' $(CUDA_LIBS) $(LDFLAGS)
+
+$(BUILD)/helloworld: examples/helloworld/main.cpp $(LIB)
+	$(CXX) $(CXXFLAGS) $< -o $@ -L$(BUILD) -ldccl -Wl,-rpath,'$$ORIGIN' $(LDFLAGS)
+
+# comparator: the same workload through stock NCCL (found at run time with dlopen)
+$(BUILD)/nccl_cli: tools/nccl_cli.cpp tools/tool_common.hpp $(LIB)
+	$(CXX) $(CXXFLAGS) $(TOOL_DEFS) $< -o $@ -L$(BUILD) -ldccl -Wl,-rpath,'$$ORIGIN' $(CUDA_LIBS) $(LDFLAGS)
+
+clean:
+	rm -rf build build-address build-thread build-undefined dccl_b200/lib

@@ -1,0 +1,114 @@
+/**
+ * Flat C symbols over the C++ API, for ctypes / dlopen callers (the Python
+ * package binds these). Every function returns the ncclResult_t value as int;
+ * C++ exceptions (a null communicator) become ncclInvalidArgument.
+ */
+#include <dccl/dccl.hpp>
+#include "../core/config.hpp"
+#include "../core/types.hpp"
+#include "../gpu/gpu_comm.hpp"
+#include "comm.hpp"
+#include <cstring>
+
+using namespace dccl;
+
+#define GUARD(expr) try { return (int)(expr); } catch (const std::exception&) { return (int)ncclInvalidArgument; }
+
+extern "C" {
+
+int dccl_comm_init(void** comm) { GUARD(ncclCommInit((ncclComm_t*)comm)); }
+int dccl_get_unique_id(void* id128) { GUARD(dcclGetUniqueId((dcclUniqueId*)id128)); }
+int dccl_comm_init_rank(void** comm, int nranks, const void* id128, int rank) {
+    dcclUniqueId id;
+    memcpy(&id, id128, sizeof(id));
+    GUARD(dcclCommInitRank((ncclComm_t*)comm, nranks, id, rank));
+}
+int dccl_comm_finalize(void* comm) { GUARD(ncclCommFinalize((ncclComm_t)comm)); }
+int dccl_comm_abort(void* comm) { GUARD(dcclCommAbort((ncclComm_t)comm)); }
+int dccl_world_size(void* comm) { try { return (int)dcclGetWorldSize((ncclComm_t)comm); } catch (...) { return -1; } }
+int dccl_rank(void* comm) { try { return (int)dcclGetMyRank((ncclComm_t)comm); } catch (...) { return -1; } }
+int dccl_last_error(void* comm, int* code, char* msg, size_t len) {
+    ncclResult_t r = ncclSuccess;
+    try { dcclGetLastError((ncclComm_t)comm, &r, msg, len); } catch (...) { return (int)ncclInvalidArgument; }
+    if (code) *code = (int)r;
+    return 0;
+}
+const char* dccl_error_string(int r) { return dcclGetErrorString((ncclResult_t)r); }
+
+/** Bind this rank to a CUDA device now (collective): the device side is otherwise set up on the first device call. */
+int dccl_comm_bind_device(void* comm, int device) {
+    dcclComm* c = (dcclComm*)comm;
+    if (!c) return (int)ncclInvalidArgument;
+    if (c->gpu) return c->gpu->device() == device ? 0 : (int)ncclInvalidUsage;
+    std::string err;
+    c->gpu = GpuComm::create(&c->bs, device, &err);
+    if (!c->gpu) { c->gpu_failed = true; return (int)ncclUnhandledCudaError; }
+    return 0;
+}
+int dccl_has_multicast(void* comm) { dcclComm* c = (dcclComm*)comm; return c && c->gpu && c->gpu->has_multicast() ? 1 : 0; }
+unsigned long long dccl_launch_count(void* comm) { dcclComm* c = (dcclComm*)comm; return c && c->gpu ? c->gpu->launches() : 0ull; }
+int dccl_cuda_device_count() { return cuda_device_count(); }
+
+int dccl_register(void* comm, void* buf, size_t size) { GUARD(dcclRegisterCacheMemory((ncclComm_t)comm, buf, size)); }
+int dccl_deregister(void* comm, void* buf) { GUARD(dcclDeregisterCacheMemory((ncclComm_t)comm, buf)); }
+int dccl_mem_alloc(void* comm, void** ptr, size_t size) { GUARD(dcclMemAlloc((ncclComm_t)comm, ptr, size)); }
+int dccl_mem_free(void* comm, void* ptr) { GUARD(dcclMemFree((ncclComm_t)comm, ptr)); }
+
+int dccl_all_reduce(const void* s, void* r, size_t count, int dt, int op, void* comm, void* stream) {
+    GUARD(ncclAllReduce(s, r, count, (ncclDataType_t)dt, (ncclRedOp_t)op, (ncclComm_t)comm, (cudaStream_t)stream));
+}
+int dccl_reduce_scatter(const void* s, void* r, size_t recvcount, int dt, int op, void* comm, void* stream) {
+    GUARD(ncclReduceScatter(s, r, recvcount, (ncclDataType_t)dt, (ncclRedOp_t)op, (ncclComm_t)comm, (cudaStream_t)stream));
+}
+int dccl_all_gather(const void* s, void* r, size_t sendcount, int dt, void* comm, void* stream) {
+    GUARD(ncclAllGather(s, r, sendcount, (ncclDataType_t)dt, (ncclComm_t)comm, (cudaStream_t)stream));
+}
+int dccl_broadcast(const void* s, void* r, size_t count, int dt, int root, void* comm, void* stream) {
+    GUARD(ncclBroadcast(s, r, count, (ncclDataType_t)dt, root, (ncclComm_t)comm, (cudaStream_t)stream));
+}
+int dccl_reduce(const void* s, void* r, size_t count, int dt, int op, int root, void* comm, void* stream) {
+    GUARD(ncclReduce(s, r, count, (ncclDataType_t)dt, (ncclRedOp_t)op, root, (ncclComm_t)comm, (cudaStream_t)stream));
+}
+int dccl_send(const void* s, size_t count, int dt, int peer, void* comm, void* stream) {
+    GUARD(ncclSend(s, count, (ncclDataType_t)dt, peer, (ncclComm_t)comm, (cudaStream_t)stream));
+}
+int dccl_recv(void* r, size_t count, int dt, int peer, void* comm, void* stream) {
+    GUARD(ncclRecv(r, count, (ncclDataType_t)dt, peer, (ncclComm_t)comm, (cudaStream_t)stream));
+}
+int dccl_group_start() { return (int)dcclGroupStart(); }
+int dccl_group_end() { return (int)dcclGroupEnd(); }
+int dccl_set_algorithm(void* comm, const char* coll, const char* name) { GUARD(dcclSetAlgorithm((ncclComm_t)comm, coll, name)); }
+const char* dccl_last_algorithm(void* comm, const char* coll) {
+    try { return dcclGetLastAlgorithm((ncclComm_t)comm, coll); } catch (...) { return ""; }
+}
+
+/* timestamps */
+void dccl_timestamp_log(unsigned long long tag, unsigned long long rank, unsigned long long extra) { Timestamp::log(tag, rank, extra); }
+void dccl_timestamp_flush(const char* filename, int clear) { Timestamp::flush(filename, clear != 0); }
+void dccl_timestamp_clear() { Timestamp::clear(); }
+unsigned long long dccl_timestamp_size() { return Timestamp::size(); }
+
+/* configuration, for tests */
+void dccl_config_reload() { Config::global().reload(); }
+void dccl_config_set(const char* key, const char* value) { Config::global().set(key, value); }
+int dccl_config_get(const char* key, char* out, size_t len) {
+    std::string v;
+    if (!Config::global().get(key, &v)) return 0;
+    snprintf(out, len, "%s", v.c_str());
+    return 1;
+}
+int dccl_config_parse_world(const char* json) { return Config::world_size_from_layout(json); }
+
+/* index arithmetic, exported so unit tests can check it without a communicator */
+void dccl_slot_range(size_t count, unsigned n, unsigned i, size_t align, size_t* lo, size_t* hi) { slot_range(count, n, i, align, lo, hi); }
+unsigned dccl_reverse_bits(unsigned x, unsigned bits) { return reverse_bits(x, bits); }
+unsigned dccl_log_two(unsigned x) { return log_two(x); }
+size_t dccl_size_of_type(int dt) { return size_of_type((ncclDataType_t)dt); }
+int dccl_parse_type(const char* s) { return (int)parse_type_name(s); }
+int dccl_parse_op(const char* s) { return (int)parse_op_name(s); }
+float dccl_half_to_float(unsigned short h) { return half_to_float(h); }
+unsigned short dccl_float_to_half(float f) { return float_to_half(f); }
+float dccl_bf16_to_float(unsigned short h) { return bf16_to_float(h); }
+unsigned short dccl_float_to_bf16(float f) { return float_to_bf16(f); }
+
+} // extern "C"

@@ -1,0 +1,139 @@
+/**
+ * Single-box bootstrap: the replacement for the Derecho group join of the
+ * original (reference src/core/dccl.cpp:287-332).
+ *
+ *  - control plane: rank 0 runs a small TCP server thread; every rank (rank 0
+ *    included) is a client. The only primitive is an all-gather of equal-size
+ *    blobs (barrier = all-gather of nothing), executed in lock step.
+ *  - handle plane: one abstract unix datagram socket per rank, used to pass
+ *    file descriptors (cuMem shareable handles) with SCM_RIGHTS.
+ *  - liveness: a POSIX shared-memory control segment with one heartbeat word
+ *    and pid per rank plus a group-wide abort word; a watchdog thread per rank
+ *    bumps its own heartbeat every heartbeat_ms (100 ms, like the original's
+ *    failure detector, reference cfg/n0/derecho.cfg:20-25) and flips `abort`
+ *    when a peer process has exited or has not been heard from for too long.
+ *  - data plane for host buffers: a second shared-memory segment with one
+ *    byte FIFO per ordered rank pair.
+ *
+ * Fault injection for tests, all on the host: DCCL_FAULT is a comma separated
+ * list of  drop_hello@<rank>  (that rank never says hello: peers time out),
+ * delay_ms=<n>@<rank>  (that rank sleeps before every control message) and
+ * exit_at_barrier=<k>@<rank>  (that rank _exit()s when it reaches its k-th
+ * control operation).
+ */
+#pragma once
+#include <dccl/dccl.hpp>
+#include <atomic>
+#include <cstdint>
+#include <deque>
+#include <functional>
+#include <string>
+#include <thread>
+#include <vector>
+
+namespace dccl {
+
+static const int kMaxRanks = 64;       // host backend limit
+static const int kMaxGpuRanks = 8;     // one NVSwitch box
+
+struct UniqueIdData {
+    uint32_t magic;
+    uint32_t port;
+    uint64_t token;
+    char addr[64];
+};
+static_assert(sizeof(UniqueIdData) <= sizeof(dcclUniqueId), "unique id too large");
+
+/** Layout of the shared control segment. */
+struct CtlRank {
+    std::atomic<uint64_t> heartbeat;
+    std::atomic<int32_t> pid;
+    std::atomic<int32_t> state;   // 0 = not joined, 1 = alive, 2 = left cleanly
+    char pad[48];
+};
+struct CtlSegment {
+    std::atomic<uint32_t> abort;       // non-zero: somebody failed; value = 1 + failed rank
+    std::atomic<uint32_t> abort_code;  // ncclResult_t
+    char pad[56];
+    CtlRank ranks[kMaxRanks];
+};
+
+/** One direction of a rank pair: single-producer single-consumer byte FIFO. */
+struct ShmChannel {
+    std::atomic<uint64_t> head;   // bytes written by the sender
+    char pad0[56];
+    std::atomic<uint64_t> tail;   // bytes consumed by the receiver
+    char pad1[56];
+    // data follows
+};
+
+class Bootstrap {
+public:
+    Bootstrap();
+    ~Bootstrap();
+
+    /** Bind + listen on rank 0. port 0 picks a free one. Fills id. */
+    static bool create_listener(const std::string& addr, int port, UniqueIdData* id, std::string* err);
+
+    /** Join. Blocks until all `world` ranks said hello or timeout_ms passed. */
+    bool init(const UniqueIdData& id, int rank, int world, int timeout_ms, std::string* err);
+    void shutdown();
+
+    int rank() const { return rank_; }
+    int world() const { return world_; }
+    uint64_t token() const { return token_; }
+
+    /** out must hold world*bytes. Returns false on peer failure / timeout. */
+    bool allgather(const void* in, size_t bytes, void* out);
+    bool barrier();
+    bool broadcast(void* buf, size_t bytes, int root);
+
+    bool send_fd(int peer, int fd, uint32_t tag);
+    bool recv_fd(int peer, uint32_t tag, int* fd, int timeout_ms);
+
+    /* liveness */
+    CtlSegment* ctl() { return ctl_; }
+    bool aborted() const { return ctl_ && ctl_->abort.load(std::memory_order_acquire) != 0; }
+    void set_abort(int failed_rank, ncclResult_t code);
+    int failed_rank() const { return ctl_ ? (int)ctl_->abort.load() - 1 : -1; }
+    /** Called by the watchdog when it flips abort (lets the GPU side mirror the flag). */
+    void on_abort(std::function<void(int)> cb) { abort_cb_ = cb; }
+    int heartbeat_ms() const { return heartbeat_ms_; }
+
+    /* host data plane */
+    ShmChannel* channel(int src, int dst);
+    size_t channel_bytes() const { return chan_bytes_; }
+
+    const std::string& last_error() const { return err_; }
+
+private:
+    bool client_roundtrip(uint32_t op, const void* in, size_t bytes, void* out, size_t out_bytes);
+    void server_loop();
+    void watchdog_loop();
+    bool map_segments(std::string* err);
+    void fault_hook(const char* where);
+
+    int rank_ = -1, world_ = 0;
+    uint64_t token_ = 0;
+    int sock_ = -1;                 // client connection to the server
+    int usock_ = -1;                // unix datagram socket for fds
+    int listen_fd_ = -1;            // rank 0 only
+    std::thread server_, watchdog_;
+    std::atomic<bool> stop_{false};
+    std::atomic<int64_t> server_deadline_{0};
+    CtlSegment* ctl_ = nullptr;
+    char* data_ = nullptr;
+    size_t data_bytes_ = 0, chan_bytes_ = 0, chan_stride_ = 0;
+    int heartbeat_ms_ = 100, hb_timeout_ms_ = 10000, op_timeout_ms_ = 60000;
+    uint64_t ops_ = 0;
+    std::string err_;
+    std::function<void(int)> abort_cb_;
+    struct PendingFd { int src; uint32_t tag; int fd; };
+    std::deque<PendingFd> pending_fds_;
+    // fault injection
+    int fault_delay_ms_ = 0;
+    long fault_exit_at_ = -1;
+    bool fault_drop_hello_ = false;
+};
+
+} // namespace dccl

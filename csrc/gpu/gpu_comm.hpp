@@ -1,0 +1,70 @@
+/**
+ * Device side of a communicator: symmetric memory, peer mappings, multicast
+ * objects and the launchers of the collective kernels.
+ *
+ * Where the original registers memory with the NIC and posts one RDMA
+ * send/recv pair per algorithm step from the host (reference
+ * src/core/internal_common.hpp:713-792, dccl.cpp:503-542), this class maps
+ * every peer's pool into the local address space once, and each collective is
+ * then ONE kernel launch on the caller's stream: all steps, the reduction, the
+ * dtype handling and the 1/world scale run inside it, synchronised by flag
+ * words in peer memory with bounded waits.
+ */
+#pragma once
+#include <dccl/dccl.hpp>
+#include "../bootstrap/bootstrap.hpp"
+#include <string>
+
+namespace dccl {
+
+enum Collective { COLL_ALLREDUCE = 0, COLL_REDUCESCATTER, COLL_ALLGATHER, COLL_BROADCAST, COLL_REDUCE, COLL_SENDRECV, COLL_COUNT };
+
+enum GpuAlgo { ALGO_AUTO = 0, ALGO_RING, ALGO_RABENSEIFNER, ALGO_ONESHOT, ALGO_TWOSHOT, ALGO_NVLS, ALGO_LOCAL, ALGO_COUNT };
+
+const char* algo_name(GpuAlgo a);
+/** Returns ALGO_COUNT for an unknown name. */
+GpuAlgo parse_algo_name(const char* s);
+int parse_collective_name(const char* s);
+
+/** True when p is device memory of some CUDA device (false when CUDA is not usable at all). */
+bool is_device_pointer(const void* p, int* device);
+/** Number of usable CUDA devices; 0 on a machine without a driver. */
+int cuda_device_count();
+
+class GpuComm {
+public:
+    /** Collective over all ranks of bs: every rank calls it, each with its own device. */
+    static GpuComm* create(Bootstrap* bs, int device, std::string* err);
+    virtual ~GpuComm() {}
+
+    virtual ncclResult_t all_reduce(const void* send, void* recv, size_t count, ncclDataType_t dt, ncclRedOp_t op,
+                                    GpuAlgo algo, cudaStream_t stream) = 0;
+    virtual ncclResult_t reduce_scatter(const void* send, void* recv, size_t recvcount, ncclDataType_t dt, ncclRedOp_t op,
+                                        GpuAlgo algo, cudaStream_t stream) = 0;
+    virtual ncclResult_t all_gather(const void* send, void* recv, size_t sendcount, ncclDataType_t dt,
+                                    GpuAlgo algo, cudaStream_t stream) = 0;
+    virtual ncclResult_t broadcast(const void* send, void* recv, size_t count, ncclDataType_t dt, int root,
+                                   GpuAlgo algo, cudaStream_t stream) = 0;
+    virtual ncclResult_t reduce(const void* send, void* recv, size_t count, ncclDataType_t dt, ncclRedOp_t op, int root,
+                                GpuAlgo algo, cudaStream_t stream) = 0;
+    virtual ncclResult_t send(const void* buf, size_t bytes, int peer, cudaStream_t stream) = 0;
+    virtual ncclResult_t recv(void* buf, size_t bytes, int peer, cudaStream_t stream) = 0;
+    virtual void group_start() = 0;
+    virtual ncclResult_t group_end() = 0;
+
+    virtual ncclResult_t mem_alloc(void** ptr, size_t size) = 0;
+    virtual ncclResult_t mem_free(void* ptr) = 0;
+    virtual ncclResult_t register_buffer(void* buf, size_t size) = 0;
+    virtual ncclResult_t deregister_buffer(void* buf) = 0;
+
+    /** ncclSuccess, or the error a kernel recorded (timeout on a peer, abort). */
+    virtual ncclResult_t async_error(char* msg, size_t msg_len) = 0;
+    virtual void abort(int failed_rank) = 0;
+    virtual GpuAlgo last_algo(int coll) const = 0;
+    virtual int device() const = 0;
+    virtual bool has_multicast() const = 0;
+    /** Kernels launched by this communicator so far. */
+    virtual uint64_t launches() const = 0;
+};
+
+} // namespace dccl

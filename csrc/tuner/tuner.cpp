@@ -1,0 +1,124 @@
+#include "tuner.hpp"
+#include "../core/config.hpp"
+#include "../core/log.hpp"
+#include <algorithm>
+#include <cstdlib>
+#include <fstream>
+#include <sstream>
+
+namespace dccl {
+
+static const size_t kInf = ~(size_t)0;
+
+/* Built-in table. Message bytes are the per-rank buffer for all-reduce /
+ * broadcast / reduce and the full gathered vector for reduce-scatter /
+ * all-gather. */
+static const TuneRule kBuiltin[] = {
+    // all-reduce: flag-in-data one-shot while latency bound, two-shot through staging in the
+    // middle, in-switch reduction once the message is large enough to amortise two barriers
+    {COLL_ALLREDUCE, 0, 64u << 10, ALGO_ONESHOT, 8},
+    {COLL_ALLREDUCE, 0, 512u << 10, ALGO_TWOSHOT, 32},
+    {COLL_ALLREDUCE, 0, kInf, ALGO_NVLS, 64},
+    {COLL_REDUCESCATTER, 0, 1u << 20, ALGO_TWOSHOT, 32},
+    {COLL_REDUCESCATTER, 0, kInf, ALGO_NVLS, 64},
+    {COLL_ALLGATHER, 0, 1u << 20, ALGO_TWOSHOT, 32},
+    {COLL_ALLGATHER, 0, kInf, ALGO_TWOSHOT, 64},
+    {COLL_BROADCAST, 0, 1u << 20, ALGO_ONESHOT, 16},
+    {COLL_BROADCAST, 0, kInf, ALGO_NVLS, 64},
+    {COLL_REDUCE, 0, 1u << 20, ALGO_TWOSHOT, 32},
+    {COLL_REDUCE, 0, kInf, ALGO_NVLS, 64},
+};
+
+Tuner::Tuner() {
+    for (const auto& r : kBuiltin) add(r);
+    std::string path = Config::global().get_str("DCCL/tune_file", "");
+    if (!path.empty()) {
+        std::string err;
+        if (!load_file(path, &err)) dccl_warn("tuning file %s: %s", path.c_str(), err.c_str());
+    }
+}
+
+void Tuner::add(const TuneRule& r) {
+    for (auto& x : rules_)
+        if (x.coll == r.coll && x.nranks == r.nranks && x.max_bytes == r.max_bytes) { x = r; return; }
+    rules_.push_back(r);
+    std::stable_sort(rules_.begin(), rules_.end(), [](const TuneRule& a, const TuneRule& b) {
+        if (a.coll != b.coll) return a.coll < b.coll;
+        if (a.nranks != b.nranks) return a.nranks > b.nranks;   // exact world sizes before the wildcard
+        return a.max_bytes < b.max_bytes;
+    });
+}
+
+static bool parse_bytes(const std::string& s, size_t* out) {
+    if (s == "inf" || s == "*") { *out = kInf; return true; }
+    char* end = nullptr;
+    unsigned long long v = strtoull(s.c_str(), &end, 0);
+    if (end == s.c_str()) return false;
+    if (*end == 'k' || *end == 'K') v <<= 10;
+    else if (*end == 'm' || *end == 'M') v <<= 20;
+    else if (*end == 'g' || *end == 'G') v <<= 30;
+    else if (*end) return false;
+    *out = (size_t)v;
+    return true;
+}
+
+int Tuner::load_text(const std::string& text, std::string* err) {
+    std::istringstream in(text);
+    std::string line;
+    int ok = 0, lineno = 0;
+    bool cleared[COLL_COUNT] = {false};
+    while (std::getline(in, line)) {
+        lineno++;
+        size_t h = line.find('#');
+        if (h != std::string::npos) line = line.substr(0, h);
+        std::istringstream ls(line);
+        std::string coll, nr, mb, algo;
+        int ctas = 0;
+        if (!(ls >> coll)) continue;
+        if (!(ls >> nr >> mb >> algo >> ctas)) { if (err) *err += "line " + std::to_string(lineno) + ": expected 5 fields; "; continue; }
+        TuneRule r;
+        r.coll = parse_collective_name(coll.c_str());
+        r.nranks = nr == "*" ? 0 : atoi(nr.c_str());
+        r.algo = parse_algo_name(algo.c_str());
+        r.ctas = ctas;
+        if (r.coll < 0 || r.algo == ALGO_COUNT || !parse_bytes(mb, &r.max_bytes) || ctas < 1 || ctas > 256) {
+            if (err) *err += "line " + std::to_string(lineno) + ": bad value; ";
+            continue;
+        }
+        // a file that mentions a collective replaces the built-in rows of that collective
+        if (!cleared[r.coll]) {
+            cleared[r.coll] = true;
+            rules_.erase(std::remove_if(rules_.begin(), rules_.end(), [&](const TuneRule& x) { return x.coll == r.coll; }), rules_.end());
+        }
+        add(r);
+        ok++;
+    }
+    return ok;
+}
+
+bool Tuner::load_file(const std::string& path, std::string* err) {
+    std::ifstream f(path);
+    if (!f) { if (err) *err = "cannot open"; return false; }
+    std::stringstream ss;
+    ss << f.rdbuf();
+    std::string e;
+    int n = load_text(ss.str(), &e);
+    if (err) *err = e;
+    return n > 0;
+}
+
+TuneChoice Tuner::choose(int coll, int nranks, size_t bytes, bool nvls_ok) const {
+    TuneChoice fallback = {ALGO_TWOSHOT, 32};
+    for (int pass = 0; pass < 2; pass++) {
+        for (const auto& r : rules_) {
+            if (r.coll != coll) continue;
+            if (pass == 0 ? r.nranks != nranks : r.nranks != 0) continue;
+            if (bytes > r.max_bytes) continue;
+            if (r.algo == ALGO_NVLS && !nvls_ok) { fallback.ctas = r.ctas; continue; }
+            return TuneChoice{r.algo, r.ctas};
+        }
+    }
+    return fallback;
+}
+
+} // namespace dccl

@@ -1,0 +1,53 @@
+/**
+ * Variant selection: which kernel variant and how many CTAs serve a call.
+ *
+ * The original picks between ring and Rabenseifner from one configuration key
+ * (reference src/core/dccl.cpp:412-413,454). Here the choice is made per
+ * (collective, world size, message bytes) from a table of measured bus
+ * bandwidths: the built-in table below was filled from sweeps on 8xB200, and a
+ * file named by DCCL_TUNE_FILE (or DCCL/tune_file) replaces rows of it. File
+ * format, one rule per line, '#' comments:
+ *
+ *     <collective> <nranks|*> <max_bytes> <algorithm> <ctas>
+ *
+ * Rules of one (collective, nranks) are tried in ascending max_bytes; the
+ * first whose max_bytes >= message bytes wins (max_bytes accepts k/m/g
+ * suffixes and "inf").
+ */
+#pragma once
+#include "../gpu/gpu_comm.hpp"
+#include <cstddef>
+#include <string>
+#include <vector>
+
+namespace dccl {
+
+struct TuneRule {
+    int coll;
+    int nranks;          // 0 = any
+    size_t max_bytes;    // inclusive upper bound
+    GpuAlgo algo;
+    int ctas;
+};
+
+struct TuneChoice {
+    GpuAlgo algo;
+    int ctas;
+};
+
+class Tuner {
+public:
+    Tuner();
+    /** Replace / add rules from text in the file format. Returns rules accepted; bad lines go to *err. */
+    int load_text(const std::string& text, std::string* err);
+    bool load_file(const std::string& path, std::string* err);
+    /** nvls_ok: the variant can serve this (dtype, op, buffers) on this communicator. */
+    TuneChoice choose(int coll, int nranks, size_t bytes, bool nvls_ok) const;
+    const std::vector<TuneRule>& rules() const { return rules_; }
+
+private:
+    void add(const TuneRule& r);
+    std::vector<TuneRule> rules_;
+};
+
+} // namespace dccl
