@@ -128,6 +128,7 @@ ncclResult_t ncclCommFinalize(ncclComm_t comm) {
         if (comm->calls[i]) dccl_info("%s: %llu calls, %llu bytes", names[i], (unsigned long long)comm->calls[i], (unsigned long long)comm->bytes[i]);
     if (comm->gpu) dccl_info("device kernels launched: %llu", (unsigned long long)comm->gpu->launches());
     // everybody arrives here before anybody unmaps peer memory; a failed group skips the wait
+    if (comm->gpu) comm->gpu->quiesce();
     if (!comm->bs.aborted()) comm->bs.barrier();
     delete comm->gpu; comm->gpu = nullptr;
     delete comm->cpu; comm->cpu = nullptr;

@@ -1,0 +1,283 @@
+/**
+ * Single-GPU emulation of a multi-rank communicator, for tests.
+ *
+ * The collective kernels take their rank from the CTA index when an array of
+ * per-rank views is passed, so ONE cooperative launch of ranks x ctas CTAs
+ * plays every rank on one GPU: each virtual rank gets its own pool and its own
+ * user buffers in ordinary device memory, "peer" pointers simply point at the
+ * other virtual ranks' pools. The code path inside the kernels (flags,
+ * barriers, staging halves, packets, reduction) is exactly the multi-GPU one;
+ * only the multimem (NVSwitch) variants cannot be played this way. Ranks that
+ * wait on each other never run as separate launches here: the cooperative
+ * launch guarantees all CTAs are resident.
+ */
+#include "../kernels/kernels.hpp"
+#include "../core/types.hpp"
+#include "gpu_comm.hpp"
+#include <cstdio>
+#include <cstring>
+#include <string>
+#include <vector>
+
+using namespace dccl;
+
+namespace {
+
+struct EmuWorld {
+    int n = 0;
+    size_t stage_bytes = 0, pool_bytes = 0;
+    std::vector<char*> pools;
+    uint32_t* status = nullptr;      // device memory: ST_WORDS + abort word
+    DevComm* d_comms = nullptr;
+    std::vector<DevComm> comms;
+    ~EmuWorld() {
+        for (char* p : pools) if (p) cudaFree(p);
+        if (status) cudaFree(status);
+        if (d_comms) cudaFree(d_comms);
+    }
+    bool create(int nranks, size_t stage, unsigned long long timeout_ms) {
+        n = nranks;
+        stage_bytes = stage;
+        pool_bytes = kStageOff + 2 * stage;
+        pools.assign(n, nullptr);
+        for (int r = 0; r < n; r++) {
+            if (cudaMalloc((void**)&pools[r], pool_bytes) != cudaSuccess) return false;
+            if (cudaMemset(pools[r], 0, kStageOff) != cudaSuccess) return false;
+        }
+        if (cudaMalloc((void**)&status, (ST_WORDS + 8) * sizeof(uint32_t)) != cudaSuccess) return false;
+        cudaMemset(status, 0, (ST_WORDS + 8) * sizeof(uint32_t));
+        comms.resize(n);
+        for (int r = 0; r < n; r++) {
+            DevComm& c = comms[r];
+            memset(&c, 0, sizeof(c));
+            c.rank = r;
+            c.nranks = n;
+            for (int p = 0; p < n; p++) c.pool[p] = pools[p];
+            c.mc_pool = nullptr;
+            c.status = status;
+            c.abort_word = status + ST_WORDS;
+            c.timeout_ns = timeout_ms * 1000000ull;
+            c.stage_bytes = stage;
+        }
+        if (cudaMalloc((void**)&d_comms, n * sizeof(DevComm)) != cudaSuccess) return false;
+        return cudaMemcpy(d_comms, comms.data(), n * sizeof(DevComm), cudaMemcpyHostToDevice) == cudaSuccess;
+    }
+};
+
+int fail(const char* what) {
+    cudaError_t e = cudaGetLastError();
+    fprintf(stderr, "dccl emulation: %s (%s)\n", what, cudaGetErrorString(e));
+    return -1;
+}
+
+} // namespace
+
+extern "C" {
+
+/**
+ * Run `iters` back-to-back calls of one collective among `nranks` virtual ranks on the current
+ * device and return every rank's output of the last call.
+ *   kind: allreduce | reducescatter | allgather | broadcast | reduce
+ *   algo: oneshot | twoshot | ring | rabenseifner
+ *   count: all-reduce / broadcast / reduce: elements per rank; reduce-scatter: recvcount; all-gather: sendcount
+ *   host_in:  nranks consecutive inputs;  host_out: nranks consecutive outputs
+ *   misalign: bytes added to every user pointer (exercises the unaligned paths)
+ * Returns 0, a negative value on a CUDA / argument error, or 100 + device status code when a kernel
+ * reported a failure.
+ */
+int dccl_emu_collective(const char* kind_s, const char* algo_s, int nranks, int dtype, int op, size_t count, int root, int ctas,
+                        int in_place, size_t misalign, int iters, size_t stage_bytes, const void* host_in, void* host_out) {
+    const int coll = parse_collective_name(kind_s);
+    const GpuAlgo algo = parse_algo_name(algo_s);
+    if (coll < 0 || algo == ALGO_COUNT || nranks < 1 || nranks > kMaxPeers || ctas < 1) return -2;
+    const ncclDataType_t dt = (ncclDataType_t)dtype;
+    const size_t es = size_of_type(dt);
+    if (!es) return -2;
+    const size_t n = (size_t)nranks;
+    size_t in_elems = count, out_elems = count;
+    if (coll == COLL_REDUCESCATTER) in_elems = count * n;
+    if (coll == COLL_ALLGATHER) out_elems = count * n;
+    if (stage_bytes == 0) stage_bytes = 8u << 20;
+    stage_bytes = (stage_bytes + 4095) / 4096 * 4096;
+
+    EmuWorld w;
+    if (!w.create(nranks, stage_bytes, 2000)) return fail("cannot create the virtual ranks");
+
+    // user buffers
+    std::vector<char*> sendb(n, nullptr), recvb(n, nullptr);
+    std::vector<RankIO> ios(n);
+    const size_t buf_elems = in_elems > out_elems ? in_elems : out_elems;
+    for (size_t r = 0; r < n; r++) {
+        if (cudaMalloc((void**)&sendb[r], buf_elems * es + misalign + 64) != cudaSuccess) return fail("cudaMalloc");
+        if (cudaMalloc((void**)&recvb[r], buf_elems * es + misalign + 64) != cudaSuccess) return fail("cudaMalloc");
+        cudaMemset(recvb[r], 0xEE, buf_elems * es + misalign + 64);
+        memset(&ios[r], 0, sizeof(RankIO));
+        char* s = sendb[r] + misalign;
+        char* d = in_place ? s : recvb[r] + misalign;
+        if (in_place && coll == COLL_REDUCESCATTER) d = s + r * count * es;       // output is the rank's slot of the input
+        if (in_place && coll == COLL_ALLGATHER) { d = s; s = s + r * count * es; } // input is the rank's slot of the output
+        ios[r].send = s;
+        ios[r].recv = d;
+    }
+    RankIO* d_ios = nullptr;
+    if (cudaMalloc((void**)&d_ios, n * sizeof(RankIO)) != cudaSuccess) return fail("cudaMalloc");
+    cudaMemcpy(d_ios, ios.data(), n * sizeof(RankIO), cudaMemcpyHostToDevice);
+
+    LaunchCfg cfg;
+    cfg.ctas = ctas;
+    cfg.ranks_in_launch = nranks;
+    int rc = 0;
+    for (int it = 0; it < iters && rc == 0; it++) {
+        // fresh inputs every call (in-place runs overwrite them)
+        for (size_t r = 0; r < n; r++) {
+            const char* src = (const char*)host_in + r * in_elems * es;
+            if (in_place && coll == COLL_ALLGATHER) cudaMemcpy((char*)ios[r].send, src, in_elems * es, cudaMemcpyHostToDevice);
+            else cudaMemcpy((char*)ios[r].send, src, in_elems * es, cudaMemcpyHostToDevice);
+        }
+        CollArgs a;
+        memset(&a, 0, sizeof(a));
+        a.emu = w.d_comms;
+        a.emu_io = d_ios;
+        a.count = count;
+        a.stride = count;
+        a.seq = (uint32_t)(it + 1);
+        a.parity = (int)(a.seq & 1u);
+        a.op = op;
+        a.root = root;
+        cudaError_t e = cudaErrorInvalidValue;
+        size_t cap = 0;
+        if (coll == COLL_ALLREDUCE) {
+            if (algo == ALGO_ONESHOT) { cap = oneshot_ll_capacity_bytes() / es; if (count <= cap) e = launch_oneshot_ll(a, dt, cfg); }
+            else if (algo == ALGO_RING) { a.mode = RING_ALLREDUCE; cap = ring_capacity(a.mode, nranks, es, stage_bytes); if (count <= cap) e = launch_ring(a, dt, cfg); }
+            else if (algo == ALGO_RABENSEIFNER) { cap = hd_capacity(nranks, es, stage_bytes); if (count <= cap && is_power_of_two((uint32_t)nranks)) e = launch_hd(a, dt, cfg); }
+            else { a.mode = TS_ALLREDUCE; cap = twoshot_capacity(a.mode, nranks, es, stage_bytes); if (count <= cap) e = launch_twoshot(a, dt, cfg); }
+        } else if (coll == COLL_REDUCESCATTER) {
+            if (algo == ALGO_RING) { a.mode = RING_REDUCESCATTER; cap = ring_capacity(a.mode, nranks, es, stage_bytes); if (count <= cap) e = launch_ring(a, dt, cfg); }
+            else { a.mode = TS_REDUCESCATTER; cap = twoshot_capacity(a.mode, nranks, es, stage_bytes); if (count <= cap) e = launch_twoshot(a, dt, cfg); }
+        } else if (coll == COLL_ALLGATHER) {
+            if (algo == ALGO_RING) { a.mode = RING_ALLGATHER; cap = ring_capacity(a.mode, nranks, es, stage_bytes); if (count <= cap) e = launch_ring(a, dt, cfg); }
+            else { a.mode = TS_ALLGATHER; cap = twoshot_capacity(a.mode, nranks, es, stage_bytes); if (count <= cap) e = launch_twoshot(a, dt, cfg); }
+        } else if (coll == COLL_BROADCAST) {
+            a.mode = algo == ALGO_ONESHOT ? TS_BROADCAST_DIRECT : TS_BROADCAST;
+            cap = twoshot_capacity(a.mode, nranks, es, stage_bytes);
+            if (count <= cap) e = launch_twoshot(a, dt, cfg);
+        } else if (coll == COLL_REDUCE) {
+            a.mode = TS_REDUCE;
+            cap = twoshot_capacity(a.mode, nranks, es, stage_bytes);
+            if (count <= cap) e = launch_twoshot(a, dt, cfg);
+        }
+        if (e != cudaSuccess) { fprintf(stderr, "dccl emulation: launch failed or count %zu above capacity %zu: %s\n", count, cap, cudaGetErrorString(e)); rc = -3; break; }
+        if (cudaDeviceSynchronize() != cudaSuccess) { rc = fail("kernel"); break; }
+        uint32_t st[ST_WORDS];
+        cudaMemcpy(st, w.status, sizeof(st), cudaMemcpyDeviceToHost);
+        if (st[ST_CODE] != DEV_OK) {
+            fprintf(stderr, "dccl emulation: kernel reported code %u peer %u site %u seq %u\n", st[ST_CODE], st[ST_PEER], st[ST_SITE], st[ST_SEQ]);
+            rc = 100 + (int)st[ST_CODE];
+        }
+    }
+    if (rc == 0)
+        for (size_t r = 0; r < n; r++)
+            cudaMemcpy((char*)host_out + r * out_elems * es, ios[r].recv, out_elems * es, cudaMemcpyDeviceToHost);
+    for (size_t r = 0; r < n; r++) { cudaFree(sendb[r]); cudaFree(recvb[r]); }
+    cudaFree(d_ios);
+    if (rc == 0 && cudaGetLastError() != cudaSuccess) rc = -4;
+    return rc;
+}
+
+/**
+ * Ring of send/recv pairs among virtual ranks: rank r sends `bytes` to r+1 and receives from r-1,
+ * `iters` times, all in one launch per iteration (the grouped form). host_in: nranks messages;
+ * host_out: what each rank received last.
+ */
+int dccl_emu_sendrecv_ring(int nranks, size_t bytes, int ctas_per_op, int iters, const void* host_in, void* host_out) {
+    if (nranks < 2 || nranks > kMaxPeers || ctas_per_op < 1 || ctas_per_op > kP2pCtas) return -2;
+    EmuWorld w;
+    if (!w.create(nranks, 1u << 20, 2000)) return fail("cannot create the virtual ranks");
+    const size_t n = (size_t)nranks;
+    std::vector<char*> sb(n), rb(n);
+    for (size_t r = 0; r < n; r++) {
+        if (cudaMalloc((void**)&sb[r], bytes + 16) != cudaSuccess || cudaMalloc((void**)&rb[r], bytes + 16) != cudaSuccess) return fail("cudaMalloc");
+        cudaMemcpy(sb[r], (const char*)host_in + r * bytes, bytes, cudaMemcpyHostToDevice);
+        cudaMemset(rb[r], 0xEE, bytes);
+    }
+    P2pOp* d_ops = nullptr;
+    int* d_nops = nullptr;
+    cudaMalloc((void**)&d_ops, n * kMaxP2pOps * sizeof(P2pOp));
+    cudaMalloc((void**)&d_nops, n * sizeof(int));
+    std::vector<int> nops(n, 2);
+    cudaMemcpy(d_nops, nops.data(), n * sizeof(int), cudaMemcpyHostToDevice);
+    int rc = 0;
+    unsigned long long chunk_base = 0;
+    for (int it = 0; it < iters && rc == 0; it++) {
+        std::vector<P2pOp> ops(n * kMaxP2pOps);
+        for (size_t r = 0; r < n; r++) {
+            P2pOp& s = ops[r * kMaxP2pOps];
+            P2pOp& d = ops[r * kMaxP2pOps + 1];
+            s.is_send = 1; s.peer = (int)((r + 1) % n); s.buf = sb[r]; s.bytes = bytes; s.chunk_base = chunk_base;
+            d.is_send = 0; d.peer = (int)((r + n - 1) % n); d.buf = rb[r]; d.bytes = bytes; d.chunk_base = chunk_base;
+        }
+        chunk_base += p2p_chunks(bytes);
+        cudaMemcpy(d_ops, ops.data(), ops.size() * sizeof(P2pOp), cudaMemcpyHostToDevice);
+        P2pArgs a;
+        memset(&a, 0, sizeof(a));
+        a.emu = w.d_comms;
+        a.emu_ops = d_ops;
+        a.emu_nops = d_nops;
+        a.ctas_per_op = ctas_per_op;
+        a.ctas_per_rank = 2 * ctas_per_op;
+        LaunchCfg cfg;
+        cfg.ctas = a.ctas_per_rank;
+        cfg.ranks_in_launch = nranks;
+        if (launch_p2p(a, cfg) != cudaSuccess || cudaDeviceSynchronize() != cudaSuccess) { rc = fail("send/recv kernel"); break; }
+        uint32_t st[ST_WORDS];
+        cudaMemcpy(st, w.status, sizeof(st), cudaMemcpyDeviceToHost);
+        if (st[ST_CODE] != DEV_OK) rc = 100 + (int)st[ST_CODE];
+    }
+    if (rc == 0) for (size_t r = 0; r < n; r++) cudaMemcpy((char*)host_out + r * bytes, rb[r], bytes, cudaMemcpyDeviceToHost);
+    for (size_t r = 0; r < n; r++) { cudaFree(sb[r]); cudaFree(rb[r]); }
+    cudaFree(d_ops);
+    cudaFree(d_nops);
+    return rc;
+}
+
+/**
+ * Bounded-wait check: one thread waits, with a `timeout_ms` budget, for a flag that nothing sets.
+ * Returns the status code the kernel recorded (DEV_TIMEOUT = 1 is the expected answer) and the time
+ * the kernel took in milliseconds through *elapsed_ms. The context stays usable afterwards.
+ */
+int dccl_emu_wait_probe(unsigned timeout_ms, float* elapsed_ms) {
+    EmuWorld w;
+    if (!w.create(1, 4096, timeout_ms)) return fail("cannot create the virtual rank");
+    cudaEvent_t t0, t1;
+    cudaEventCreate(&t0);
+    cudaEventCreate(&t1);
+    cudaEventRecord(t0);
+    if (launch_wait_probe(w.comms[0], nullptr) != cudaSuccess) return fail("launch");
+    cudaEventRecord(t1);
+    if (cudaDeviceSynchronize() != cudaSuccess) return fail("probe kernel");
+    float ms = 0;
+    cudaEventElapsedTime(&ms, t0, t1);
+    if (elapsed_ms) *elapsed_ms = ms;
+    cudaEventDestroy(t0);
+    cudaEventDestroy(t1);
+    uint32_t st[ST_WORDS];
+    cudaMemcpy(st, w.status, sizeof(st), cudaMemcpyDeviceToHost);
+    return (int)st[ST_CODE];
+}
+
+/** Pairwise reduce and copy kernels, for single-GPU numerics tests: acc = op(acc, in). */
+int dccl_local_reduce(void* host_acc, const void* host_in, size_t count, int dtype, int op) {
+    const size_t es = size_of_type((ncclDataType_t)dtype);
+    char *a = nullptr, *b = nullptr;
+    if (cudaMalloc((void**)&a, count * es + 16) != cudaSuccess || cudaMalloc((void**)&b, count * es + 16) != cudaSuccess) return fail("cudaMalloc");
+    cudaMemcpy(a, host_acc, count * es, cudaMemcpyHostToDevice);
+    cudaMemcpy(b, host_in, count * es, cudaMemcpyHostToDevice);
+    cudaError_t e = launch_local_reduce(a, b, count, (ncclDataType_t)dtype, (ncclRedOp_t)op, nullptr);
+    if (e == cudaSuccess) e = cudaDeviceSynchronize();
+    if (e == cudaSuccess) cudaMemcpy(host_acc, a, count * es, cudaMemcpyDeviceToHost);
+    cudaFree(a);
+    cudaFree(b);
+    return e == cudaSuccess ? 0 : fail("local reduce");
+}
+
+} // extern "C"

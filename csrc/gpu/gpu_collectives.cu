@@ -1,0 +1,391 @@
+/**
+ * Device collectives: choose the variant for a call, cut messages larger than
+ * the staging capacity into several launches, fill the kernel arguments and
+ * launch on the caller's stream. Counterpart of the algorithm switch in the
+ * original (reference src/core/dccl.cpp:412-496), with the choice coming from
+ * the tuner table unless the caller forces a variant.
+ *
+ * Every launch takes the next sequence number; its parity selects the staging
+ * half and the packet generation. All ranks issue the same calls in the same
+ * order, so they agree on sequence numbers without talking to each other.
+ */
+#include "gpu_impl.hpp"
+#include "../core/config.hpp"
+#include "../core/log.hpp"
+#include "../core/types.hpp"
+
+namespace dccl {
+
+int GpuCommImpl::ctas_for(int tuned) const {
+    int c = ctas_override_ > 0 ? ctas_override_ : tuned;
+    if (c < 1) c = 1;
+    if (c > kMaxCtas) c = kMaxCtas;
+    return c;
+}
+
+CollArgs GpuCommImpl::base_args(const void* send, void* recv, ncclRedOp_t op, int root) {
+    CollArgs a;
+    memset(&a, 0, sizeof(a));
+    a.comm = dc_;
+    a.io.send = send;
+    a.io.recv = recv;
+    a.op = (int)op;
+    a.root = root;
+    return a;
+}
+
+#define NEXT_SEQ(a)                                   \
+    do {                                              \
+        if (++seq_ == 0) ++seq_;                      \
+        (a).seq = seq_;                               \
+        (a).parity = (int)(seq_ & 1u);                \
+    } while (0)
+
+ncclResult_t GpuCommImpl::all_reduce(const void* send, void* recv, size_t count, ncclDataType_t dt, ncclRedOp_t op,
+                                     GpuAlgo algo, cudaStream_t stream) {
+    DeviceGuard g(dev_);
+    const size_t es = size_of_type(dt), bytes = count * es;
+    if (n_ == 1) {
+        last_[COLL_ALLREDUCE] = ALGO_LOCAL;
+        if (send != recv && bytes) { launches_++; return cuda_result(launch_local_copy(recv, send, bytes, stream), "local copy"); }
+        return ncclSuccess;
+    }
+    ncclResult_t pre = precheck();
+    if (pre != ncclSuccess) return pre;
+    if (!count) return ncclSuccess;
+
+    const bool nvls_ok = pool_.mc_base != nullptr && nvls_supports(dt, op);
+    TuneChoice ch = tuner_.choose(COLL_ALLREDUCE, n_, bytes, nvls_ok);
+    if (algo != ALGO_AUTO) ch.algo = algo;
+    // a forced variant that cannot serve this call falls back to the closest one that can
+    if (ch.algo == ALGO_NVLS && !nvls_ok) ch.algo = ALGO_TWOSHOT;
+    if (ch.algo == ALGO_ONESHOT && bytes > oneshot_ll_capacity_bytes()) ch.algo = ALGO_TWOSHOT;
+    if (ch.algo == ALGO_RABENSEIFNER && !is_power_of_two((uint32_t)n_)) ch.algo = ALGO_TWOSHOT;
+    if (ch.algo == ALGO_LOCAL || ch.algo == ALGO_AUTO) ch.algo = ALGO_TWOSHOT;
+    last_[COLL_ALLREDUCE] = ch.algo;
+
+    LaunchCfg cfg;
+    cfg.ctas = ctas_for(ch.ctas);
+    cfg.stream = stream;
+    CollArgs a = base_args(send, recv, op, 0);
+
+    if (ch.algo == ALGO_ONESHOT) {
+        a.count = count;
+        NEXT_SEQ(a);
+        launches_++;
+        return cuda_result(launch_oneshot_ll(a, dt, cfg), "one-shot all-reduce");
+    }
+
+    // zero-copy switch reduction when both buffers sit in multicast-bound symmetric memory
+    if (ch.algo == ALGO_NVLS) {
+        const char* sp[kMaxPeers];
+        const char* rp[kMaxPeers];
+        const char *smc = nullptr, *rmc = nullptr;
+        if (bytes % 16 == 0 && sym_view(send, bytes, sp, &smc) && sym_view(recv, bytes, rp, &rmc) && smc && rmc &&
+            ((uintptr_t)smc % 16 == 0) && ((uintptr_t)rmc % 16 == 0)) {
+            a.symmetric = 1;
+            a.io.send_mc = smc;
+            a.io.recv_mc = (char*)rmc;
+            a.mode = NV_ALLREDUCE;
+            a.count = count;
+            NEXT_SEQ(a);
+            launches_++;
+            return cuda_result(launch_nvls(a, dt, cfg), "nvls all-reduce (symmetric)");
+        }
+    }
+
+    size_t cap;
+    switch (ch.algo) {
+    case ALGO_NVLS: cap = nvls_capacity(NV_ALLREDUCE, n_, es, stage_bytes_); break;
+    case ALGO_RING: cap = ring_capacity(RING_ALLREDUCE, n_, es, stage_bytes_); break;
+    case ALGO_RABENSEIFNER: cap = hd_capacity(n_, es, stage_bytes_); break;
+    default: cap = twoshot_capacity(TS_ALLREDUCE, n_, es, stage_bytes_); break;
+    }
+    for (size_t off = 0; off < count; off += cap) {
+        const size_t c = count - off < cap ? count - off : cap;
+        a.io.send = (const char*)send + off * es;
+        a.io.recv = (char*)recv + off * es;
+        a.count = c;
+        NEXT_SEQ(a);
+        cudaError_t e;
+        switch (ch.algo) {
+        case ALGO_NVLS: a.mode = NV_ALLREDUCE; e = launch_nvls(a, dt, cfg); break;
+        case ALGO_RING: a.mode = RING_ALLREDUCE; e = launch_ring(a, dt, cfg); break;
+        case ALGO_RABENSEIFNER: e = launch_hd(a, dt, cfg); break;
+        default: a.mode = TS_ALLREDUCE; e = launch_twoshot(a, dt, cfg); break;
+        }
+        launches_++;
+        if (e != cudaSuccess) return cuda_result(e, "all-reduce launch");
+    }
+    return ncclSuccess;
+}
+
+ncclResult_t GpuCommImpl::reduce_scatter(const void* send, void* recv, size_t recvcount, ncclDataType_t dt, ncclRedOp_t op,
+                                         GpuAlgo algo, cudaStream_t stream) {
+    DeviceGuard g(dev_);
+    const size_t es = size_of_type(dt);
+    if (n_ == 1) {
+        last_[COLL_REDUCESCATTER] = ALGO_LOCAL;
+        if (send != recv && recvcount) { launches_++; return cuda_result(launch_local_copy(recv, send, recvcount * es, stream), "local copy"); }
+        return ncclSuccess;
+    }
+    ncclResult_t pre = precheck();
+    if (pre != ncclSuccess) return pre;
+    if (!recvcount) return ncclSuccess;
+    const size_t bytes = recvcount * es * (size_t)n_;
+    const bool nvls_ok = pool_.mc_base != nullptr && nvls_supports(dt, op);
+    TuneChoice ch = tuner_.choose(COLL_REDUCESCATTER, n_, bytes, nvls_ok);
+    if (algo != ALGO_AUTO) ch.algo = algo;
+    if (ch.algo == ALGO_NVLS && !nvls_ok) ch.algo = ALGO_TWOSHOT;
+    if (ch.algo != ALGO_NVLS && ch.algo != ALGO_RING) ch.algo = ALGO_TWOSHOT;
+    last_[COLL_REDUCESCATTER] = ch.algo;
+
+    LaunchCfg cfg;
+    cfg.ctas = ctas_for(ch.ctas);
+    cfg.stream = stream;
+    CollArgs a = base_args(send, recv, op, 0);
+    a.stride = recvcount;
+
+    if (ch.algo == ALGO_NVLS) {
+        const char* sp[kMaxPeers];
+        const char* smc = nullptr;
+        if ((recvcount * es) % 16 == 0 && sym_view(send, bytes, sp, &smc) && smc && (uintptr_t)smc % 16 == 0) {
+            a.symmetric = 1;
+            a.io.send_mc = smc;
+            a.mode = NV_REDUCESCATTER;
+            a.count = recvcount;
+            NEXT_SEQ(a);
+            launches_++;
+            return cuda_result(launch_nvls(a, dt, cfg), "nvls reduce-scatter (symmetric)");
+        }
+    }
+    size_t cap = ch.algo == ALGO_NVLS ? nvls_capacity(NV_REDUCESCATTER, n_, es, stage_bytes_)
+                 : ch.algo == ALGO_RING ? ring_capacity(RING_REDUCESCATTER, n_, es, stage_bytes_)
+                                        : twoshot_capacity(TS_REDUCESCATTER, n_, es, stage_bytes_);
+    for (size_t off = 0; off < recvcount; off += cap) {
+        const size_t c = recvcount - off < cap ? recvcount - off : cap;
+        a.io.send = (const char*)send + off * es;   // slot j of this piece starts at send + j*stride + off
+        a.io.recv = (char*)recv + off * es;
+        a.count = c;
+        NEXT_SEQ(a);
+        cudaError_t e;
+        if (ch.algo == ALGO_NVLS) { a.mode = NV_REDUCESCATTER; e = launch_nvls(a, dt, cfg); }
+        else if (ch.algo == ALGO_RING) { a.mode = RING_REDUCESCATTER; e = launch_ring(a, dt, cfg); }
+        else { a.mode = TS_REDUCESCATTER; e = launch_twoshot(a, dt, cfg); }
+        launches_++;
+        if (e != cudaSuccess) return cuda_result(e, "reduce-scatter launch");
+    }
+    return ncclSuccess;
+}
+
+ncclResult_t GpuCommImpl::all_gather(const void* send, void* recv, size_t sendcount, ncclDataType_t dt,
+                                     GpuAlgo algo, cudaStream_t stream) {
+    DeviceGuard g(dev_);
+    const size_t es = size_of_type(dt);
+    if (n_ == 1) {
+        last_[COLL_ALLGATHER] = ALGO_LOCAL;
+        if (send != recv && sendcount) { launches_++; return cuda_result(launch_local_copy(recv, send, sendcount * es, stream), "local copy"); }
+        return ncclSuccess;
+    }
+    ncclResult_t pre = precheck();
+    if (pre != ncclSuccess) return pre;
+    if (!sendcount) return ncclSuccess;
+    const size_t bytes = sendcount * es * (size_t)n_;
+    const bool nvls_ok = pool_.mc_base != nullptr;
+    TuneChoice ch = tuner_.choose(COLL_ALLGATHER, n_, bytes, nvls_ok);
+    if (algo != ALGO_AUTO) ch.algo = algo;
+    if (ch.algo == ALGO_NVLS && !nvls_ok) ch.algo = ALGO_TWOSHOT;
+    if (ch.algo != ALGO_NVLS && ch.algo != ALGO_RING) ch.algo = ALGO_TWOSHOT;
+    last_[COLL_ALLGATHER] = ch.algo;
+
+    LaunchCfg cfg;
+    cfg.ctas = ctas_for(ch.ctas);
+    cfg.stream = stream;
+    CollArgs a = base_args(send, recv, ncclSum, 0);
+    a.stride = sendcount;
+
+    if (ch.algo == ALGO_NVLS) {
+        const char* rp[kMaxPeers];
+        const char* rmc = nullptr;
+        if ((sendcount * es) % 16 == 0 && (uintptr_t)send % 16 == 0 && sym_view(recv, bytes, rp, &rmc) && rmc && (uintptr_t)rmc % 16 == 0) {
+            a.symmetric = 1;
+            a.io.recv_mc = (char*)rmc;
+            a.mode = NV_ALLGATHER;
+            a.count = sendcount;
+            NEXT_SEQ(a);
+            launches_++;
+            return cuda_result(launch_nvls(a, dt, cfg), "nvls all-gather (symmetric)");
+        }
+    }
+    size_t cap = ch.algo == ALGO_NVLS ? nvls_capacity(NV_ALLGATHER, n_, es, stage_bytes_)
+                 : ch.algo == ALGO_RING ? ring_capacity(RING_ALLGATHER, n_, es, stage_bytes_)
+                                        : twoshot_capacity(TS_ALLGATHER, n_, es, stage_bytes_);
+    for (size_t off = 0; off < sendcount; off += cap) {
+        const size_t c = sendcount - off < cap ? sendcount - off : cap;
+        a.io.send = (const char*)send + off * es;
+        a.io.recv = (char*)recv + off * es;
+        a.count = c;
+        NEXT_SEQ(a);
+        cudaError_t e;
+        if (ch.algo == ALGO_NVLS) { a.mode = NV_ALLGATHER; e = launch_nvls(a, dt, cfg); }
+        else if (ch.algo == ALGO_RING) { a.mode = RING_ALLGATHER; e = launch_ring(a, dt, cfg); }
+        else { a.mode = TS_ALLGATHER; e = launch_twoshot(a, dt, cfg); }
+        launches_++;
+        if (e != cudaSuccess) return cuda_result(e, "all-gather launch");
+    }
+    return ncclSuccess;
+}
+
+ncclResult_t GpuCommImpl::broadcast(const void* send, void* recv, size_t count, ncclDataType_t dt, int root,
+                                    GpuAlgo algo, cudaStream_t stream) {
+    DeviceGuard g(dev_);
+    const size_t es = size_of_type(dt), bytes = count * es;
+    if (n_ == 1) {
+        last_[COLL_BROADCAST] = ALGO_LOCAL;
+        if (send != recv && bytes) { launches_++; return cuda_result(launch_local_copy(recv, send, bytes, stream), "local copy"); }
+        return ncclSuccess;
+    }
+    ncclResult_t pre = precheck();
+    if (pre != ncclSuccess) return pre;
+    if (!count) return ncclSuccess;
+    const bool nvls_ok = pool_.mc_base != nullptr;
+    TuneChoice ch = tuner_.choose(COLL_BROADCAST, n_, bytes, nvls_ok);
+    if (algo != ALGO_AUTO) ch.algo = algo;
+    if (ch.algo == ALGO_NVLS && !nvls_ok) ch.algo = ALGO_TWOSHOT;
+    if (ch.algo != ALGO_NVLS && ch.algo != ALGO_ONESHOT) ch.algo = ALGO_TWOSHOT;
+    last_[COLL_BROADCAST] = ch.algo;
+
+    LaunchCfg cfg;
+    cfg.ctas = ctas_for(ch.ctas);
+    cfg.stream = stream;
+    if (rank_ != root) send = recv;   // only the root's source is read
+    CollArgs a = base_args(send, recv, ncclSum, root);
+
+    if (ch.algo == ALGO_NVLS) {
+        const char* rp[kMaxPeers];
+        const char* rmc = nullptr;
+        // every rank must take the same branch, so only properties that all ranks share may decide
+        if (bytes % 16 == 0 && sym_view(recv, bytes, rp, &rmc) && rmc && (uintptr_t)rmc % 16 == 0 &&
+            Config::global().get_bool("DCCL/symmetric_broadcast", false)) {
+            a.symmetric = 1;
+            a.io.recv_mc = (char*)rmc;
+            a.mode = NV_BROADCAST;
+            a.count = count;
+            NEXT_SEQ(a);
+            launches_++;
+            return cuda_result(launch_nvls(a, dt, cfg), "nvls broadcast (symmetric)");
+        }
+    }
+    const int ts_mode = ch.algo == ALGO_ONESHOT ? TS_BROADCAST_DIRECT : TS_BROADCAST;
+    size_t cap = ch.algo == ALGO_NVLS ? nvls_capacity(NV_BROADCAST, n_, es, stage_bytes_) : twoshot_capacity(ts_mode, n_, es, stage_bytes_);
+    for (size_t off = 0; off < count; off += cap) {
+        const size_t c = count - off < cap ? count - off : cap;
+        a.io.send = (const char*)send + off * es;
+        a.io.recv = (char*)recv + off * es;
+        a.count = c;
+        NEXT_SEQ(a);
+        cudaError_t e;
+        if (ch.algo == ALGO_NVLS) { a.mode = NV_BROADCAST; e = launch_nvls(a, dt, cfg); }
+        else { a.mode = ts_mode; e = launch_twoshot(a, dt, cfg); }
+        launches_++;
+        if (e != cudaSuccess) return cuda_result(e, "broadcast launch");
+    }
+    return ncclSuccess;
+}
+
+ncclResult_t GpuCommImpl::reduce(const void* send, void* recv, size_t count, ncclDataType_t dt, ncclRedOp_t op, int root,
+                                 GpuAlgo algo, cudaStream_t stream) {
+    DeviceGuard g(dev_);
+    const size_t es = size_of_type(dt), bytes = count * es;
+    if (n_ == 1) {
+        last_[COLL_REDUCE] = ALGO_LOCAL;
+        if (send != recv && bytes) { launches_++; return cuda_result(launch_local_copy(recv, send, bytes, stream), "local copy"); }
+        return ncclSuccess;
+    }
+    ncclResult_t pre = precheck();
+    if (pre != ncclSuccess) return pre;
+    if (!count) return ncclSuccess;
+    const bool nvls_ok = pool_.mc_base != nullptr && nvls_supports(dt, op);
+    TuneChoice ch = tuner_.choose(COLL_REDUCE, n_, bytes, nvls_ok);
+    if (algo != ALGO_AUTO) ch.algo = algo;
+    if (ch.algo == ALGO_NVLS && !nvls_ok) ch.algo = ALGO_TWOSHOT;
+    if (ch.algo != ALGO_NVLS) ch.algo = ALGO_TWOSHOT;
+    last_[COLL_REDUCE] = ch.algo;
+
+    LaunchCfg cfg;
+    cfg.ctas = ctas_for(ch.ctas);
+    cfg.stream = stream;
+    CollArgs a = base_args(send, recv, op, root);
+    size_t cap = ch.algo == ALGO_NVLS ? nvls_capacity(NV_REDUCE, n_, es, stage_bytes_) : twoshot_capacity(TS_REDUCE, n_, es, stage_bytes_);
+    for (size_t off = 0; off < count; off += cap) {
+        const size_t c = count - off < cap ? count - off : cap;
+        a.io.send = (const char*)send + off * es;
+        a.io.recv = recv ? (char*)recv + off * es : nullptr;
+        a.count = c;
+        NEXT_SEQ(a);
+        cudaError_t e;
+        if (ch.algo == ALGO_NVLS) { a.mode = NV_REDUCE; e = launch_nvls(a, dt, cfg); }
+        else { a.mode = TS_REDUCE; e = launch_twoshot(a, dt, cfg); }
+        launches_++;
+        if (e != cudaSuccess) return cuda_result(e, "reduce launch");
+    }
+    return ncclSuccess;
+}
+
+/* ---------------- point to point ---------------- */
+
+ncclResult_t GpuCommImpl::p2p_launch(std::vector<P2pOp>& ops, cudaStream_t stream) {
+    DeviceGuard g(dev_);
+    for (size_t first = 0; first < ops.size(); first += kMaxP2pOps) {
+        P2pArgs a;
+        memset(&a, 0, sizeof(a));
+        a.comm = dc_;
+        a.ctas_per_op = p2p_ctas_;
+        a.nops = (int)(ops.size() - first < (size_t)kMaxP2pOps ? ops.size() - first : (size_t)kMaxP2pOps);
+        for (int i = 0; i < a.nops; i++) a.ops[i] = ops[first + i];
+        LaunchCfg cfg;
+        cfg.ctas = a.nops * p2p_ctas_;
+        cfg.stream = stream;
+        a.ctas_per_rank = cfg.ctas;
+        launches_++;
+        cudaError_t e = launch_p2p(a, cfg);
+        if (e != cudaSuccess) return cuda_result(e, "send/recv launch");
+    }
+    return ncclSuccess;
+}
+
+ncclResult_t GpuCommImpl::send(const void* buf, size_t bytes, int peer, cudaStream_t stream) {
+    ncclResult_t pre = precheck();
+    if (pre != ncclSuccess) return pre;
+    last_[COLL_SENDRECV] = ALGO_ONESHOT;
+    if (!bytes) return ncclSuccess;
+    P2pOp op;
+    op.is_send = 1; op.peer = peer; op.buf = (char*)buf; op.bytes = bytes; op.chunk_base = sent_chunks_[peer];
+    sent_chunks_[peer] += p2p_chunks(bytes);
+    if (in_group_) { if (group_ops_.empty()) group_stream_ = stream; group_ops_.push_back(op); return ncclSuccess; }
+    std::vector<P2pOp> ops{op};
+    return p2p_launch(ops, stream);
+}
+
+ncclResult_t GpuCommImpl::recv(void* buf, size_t bytes, int peer, cudaStream_t stream) {
+    ncclResult_t pre = precheck();
+    if (pre != ncclSuccess) return pre;
+    last_[COLL_SENDRECV] = ALGO_ONESHOT;
+    if (!bytes) return ncclSuccess;
+    P2pOp op;
+    op.is_send = 0; op.peer = peer; op.buf = (char*)buf; op.bytes = bytes; op.chunk_base = recv_chunks_[peer];
+    recv_chunks_[peer] += p2p_chunks(bytes);
+    if (in_group_) { if (group_ops_.empty()) group_stream_ = stream; group_ops_.push_back(op); return ncclSuccess; }
+    std::vector<P2pOp> ops{op};
+    return p2p_launch(ops, stream);
+}
+
+ncclResult_t GpuCommImpl::group_end() {
+    in_group_ = false;
+    if (group_ops_.empty()) return ncclSuccess;
+    std::vector<P2pOp> ops;
+    ops.swap(group_ops_);
+    return p2p_launch(ops, group_stream_);
+}
+
+} // namespace dccl

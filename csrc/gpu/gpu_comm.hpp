@@ -60,6 +60,8 @@ public:
     /** ncclSuccess, or the error a kernel recorded (timeout on a peer, abort). */
     virtual ncclResult_t async_error(char* msg, size_t msg_len) = 0;
     virtual void abort(int failed_rank) = 0;
+    /** Wait until every kernel this rank launched has finished (called before peers unmap memory). */
+    virtual void quiesce() = 0;
     virtual GpuAlgo last_algo(int coll) const = 0;
     virtual int device() const = 0;
     virtual bool has_multicast() const = 0;

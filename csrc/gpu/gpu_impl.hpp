@@ -1,0 +1,88 @@
+/** Implementation class behind GpuComm; split over gpu_comm.cu (life cycle, memory) and
+ *  gpu_collectives.cu (variant choice, chunking, launches). */
+#pragma once
+#include "gpu_comm.hpp"
+#include "symmem.hpp"
+#include "../kernels/kernels.hpp"
+#include "../tuner/tuner.hpp"
+#include <atomic>
+#include <map>
+#include <vector>
+
+namespace dccl {
+
+struct RegisteredBuffer {
+    char* base = nullptr;             // as given by the user
+    size_t size = 0;
+    char* peer[kMaxPeers] = {nullptr};   // the same buffer of every rank, mapped here
+    void* opened[kMaxPeers] = {nullptr}; // what cudaIpcOpenMemHandle returned (to close it)
+};
+
+class GpuCommImpl : public GpuComm {
+public:
+    GpuCommImpl(Bootstrap* bs, int device);
+    ~GpuCommImpl() override;
+    bool init(std::string* err);
+
+    ncclResult_t all_reduce(const void* send, void* recv, size_t count, ncclDataType_t dt, ncclRedOp_t op, GpuAlgo algo, cudaStream_t stream) override;
+    ncclResult_t reduce_scatter(const void* send, void* recv, size_t recvcount, ncclDataType_t dt, ncclRedOp_t op, GpuAlgo algo, cudaStream_t stream) override;
+    ncclResult_t all_gather(const void* send, void* recv, size_t sendcount, ncclDataType_t dt, GpuAlgo algo, cudaStream_t stream) override;
+    ncclResult_t broadcast(const void* send, void* recv, size_t count, ncclDataType_t dt, int root, GpuAlgo algo, cudaStream_t stream) override;
+    ncclResult_t reduce(const void* send, void* recv, size_t count, ncclDataType_t dt, ncclRedOp_t op, int root, GpuAlgo algo, cudaStream_t stream) override;
+    ncclResult_t send(const void* buf, size_t bytes, int peer, cudaStream_t stream) override;
+    ncclResult_t recv(void* buf, size_t bytes, int peer, cudaStream_t stream) override;
+    void group_start() override { in_group_ = true; }
+    ncclResult_t group_end() override;
+
+    ncclResult_t mem_alloc(void** ptr, size_t size) override;
+    ncclResult_t mem_free(void* ptr) override;
+    ncclResult_t register_buffer(void* buf, size_t size) override;
+    ncclResult_t deregister_buffer(void* buf) override;
+
+    ncclResult_t async_error(char* msg, size_t msg_len) override;
+    void abort(int failed_rank) override;
+    void quiesce() override { DeviceGuard g(dev_); cudaDeviceSynchronize(); cudaGetLastError(); }
+    GpuAlgo last_algo(int coll) const override { return last_[coll]; }
+    int device() const override { return dev_; }
+    bool has_multicast() const override { return pool_.mc_base != nullptr; }
+    uint64_t launches() const override { return launches_; }
+
+private:
+    struct DeviceGuard {
+        int prev = -1;
+        explicit DeviceGuard(int dev) { cudaGetDevice(&prev); if (prev != dev) cudaSetDevice(dev); else prev = -1; }
+        ~DeviceGuard() { if (prev >= 0) cudaSetDevice(prev); }
+    };
+    ncclResult_t precheck();
+    ncclResult_t cuda_result(cudaError_t e, const char* what);
+    CollArgs base_args(const void* send, void* recv, ncclRedOp_t op, int root);
+    /** Fill the symmetric views of a user buffer; false when it is not inside a dcclMemAlloc segment. */
+    bool sym_view(const void* p, size_t bytes, const char** peers, const char** mc) const;
+    int ctas_for(int tuned) const;
+    ncclResult_t p2p_launch(std::vector<P2pOp>& ops, cudaStream_t stream);
+
+    Bootstrap* bs_;
+    int dev_, rank_, n_;
+    SymAllocator* sym_ = nullptr;
+    SymSegment pool_;
+    DevComm dc_;
+    uint32_t* status_host_ = nullptr;   // ST_WORDS status words, then the abort word
+    uint32_t* status_dev_ = nullptr;
+    size_t stage_bytes_ = 0;
+    uint32_t seq_ = 0;
+    Tuner tuner_;
+    GpuAlgo last_[COLL_COUNT];
+    uint64_t launches_ = 0;
+    int ctas_override_ = 0;
+    int p2p_ctas_ = 16;
+    bool sticky_error_ = false;
+    std::vector<SymSegment> user_segs_;
+    std::vector<RegisteredBuffer> regs_;
+    std::map<std::string, void*> ipc_opened_;   // handle bytes -> mapping, one open per allocation
+    unsigned long long sent_chunks_[kMaxPeers], recv_chunks_[kMaxPeers];
+    bool in_group_ = false;
+    std::vector<P2pOp> group_ops_;
+    cudaStream_t group_stream_ = nullptr;
+};
+
+} // namespace dccl

@@ -1,0 +1,113 @@
+/**
+ * Rabenseifner all-reduce (recursive halving reduce-scatter + recursive doubling
+ * all-gather) as one kernel, for power-of-two world sizes.
+ *
+ * Same exchange pattern as the original (reference
+ * src/core/reduce_scatter_recursive_halving.cpp:66-111 and
+ * all_gather_recursive_doubling.cpp:48-74): step k pairs rank r with r XOR 2^k,
+ * the active region halves every step, and the gather walks back with the held
+ * region doubling every step (the doubling the shipped original leaves commented
+ * out). log2(n) exchanges each way instead of n-1. Halves are pushed into the
+ * partner's staging at their absolute position, one area per halving step and
+ * one for the gather. Work is dealt
+ * to CTAs by absolute position (block-cyclic), so a CTA only ever reads
+ * partial sums that it produced itself in the previous step and the only
+ * synchronisation is the flag between CTA b and CTA b of the partner.
+ */
+#include "kernels.hpp"
+#include "../device/reduce_ops.cuh"
+#include "../device/geometry.cuh"
+
+namespace dccl {
+
+constexpr size_t kHdChunkBytes = 16u << 10;   // dealing unit
+
+/** Calls f(lo, n) for every piece of [lo,hi) (elements) that belongs to CTA bid. */
+template <typename T, typename F>
+__device__ __forceinline__ void for_my_pieces(size_t lo, size_t hi, int bid, int nb, F f) {
+    constexpr size_t CE = kHdChunkBytes / sizeof(T);
+    for (size_t ch = lo / CE; ch * CE < hi; ch++) {
+        if ((int)(ch % (size_t)nb) != bid) continue;
+        size_t a = ch * CE, b = a + CE;
+        if (a < lo) a = lo;
+        if (b > hi) b = hi;
+        if (b > a) f(a, b - a);
+    }
+}
+
+template <typename T, int OP>
+__global__ void __launch_bounds__(512) k_hd(const __grid_constant__ CollArgs a) {
+    constexpr size_t VE = 16 / sizeof(T);
+    const Ctx x = make_ctx(a);
+    const DevComm& c = *x.c;
+    const int n = c.nranks, r = c.rank;
+    const T* send = reinterpret_cast<const T*>(x.io->send);
+    T* recv = reinterpret_cast<T*>(x.io->recv);
+    const size_t count = a.count;
+    const size_t area = (count + VE - 1) / VE * VE;          // elements per staging area
+    const bool avg = a.op == (int)ncclAvg;
+    int steps = 0;
+    while ((1 << steps) < n) steps++;
+    // one receive area per halving step (the regions received in successive steps are nested, so
+    // they must not share memory), then one for the gather (those regions are disjoint)
+    T* my_stage = stage_ptr<T>(c, r, a.parity);
+    T* my_ag = my_stage + (size_t)steps * area;
+
+    size_t los[4], his[4];
+    size_t lo = 0, hi = count;
+    const T* cur = send;                                     // where my current partial sums live
+    for (int k = 0; k < steps; k++) {
+        const int peer = r ^ (1 << k);
+        los[k] = lo; his[k] = hi;
+        size_t mid = lo + ((hi - lo) / 2 + VE - 1) / VE * VE;
+        if (mid > hi) mid = hi;
+        size_t klo, khi, slo, shi;
+        if (!((r >> k) & 1)) { klo = lo; khi = mid; slo = mid; shi = hi; }
+        else { klo = mid; khi = hi; slo = lo; shi = mid; }
+        T* peer_rs = stage_ptr<T>(c, peer, a.parity) + (size_t)k * area;
+        const T* my_rs = my_stage + (size_t)k * area;
+        for_my_pieces<T>(slo, shi, x.bid, x.nb, [&](size_t p, size_t len) { copy_range<T>(peer_rs + p, cur + p, len); });
+        cta_signal_peer(c, peer, x.bid, a.seq, k);
+        if (!cta_wait_peer(c, peer, x.bid, a.seq, k, 700 + k)) return;
+        const bool last = k == steps - 1;
+        for_my_pieces<T>(klo, khi, x.bid, x.nb, [&](size_t p, size_t len) {
+            const T* ins[1] = {my_rs + p};
+            reduce_range<T, OP>(recv + p, nullptr, cur + p, ins, 1, len, last && avg, n);
+        });
+        __syncthreads();
+        cur = recv;
+        lo = klo; hi = khi;
+    }
+    if (steps == 0 && send != recv) for_my_pieces<T>(0, count, x.bid, x.nb, [&](size_t p, size_t len) { copy_range<T>(recv + p, send + p, len); });
+
+    for (int k = steps - 1; k >= 0; k--) {
+        const int peer = r ^ (1 << k);
+        const size_t plo = los[k], phi = his[k];
+        size_t olo, ohi;
+        if (lo == plo) { olo = hi; ohi = phi; } else { olo = plo; ohi = lo; }
+        T* peer_ag = stage_ptr<T>(c, peer, a.parity) + (size_t)steps * area;
+        for_my_pieces<T>(lo, hi, x.bid, x.nb, [&](size_t p, size_t len) { copy_range<T>(peer_ag + p, recv + p, len); });
+        const int idx = steps + (steps - 1 - k);
+        cta_signal_peer(c, peer, x.bid, a.seq, idx);
+        if (!cta_wait_peer(c, peer, x.bid, a.seq, idx, 750 + k)) return;
+        for_my_pieces<T>(olo, ohi, x.bid, x.nb, [&](size_t p, size_t len) { copy_range<T>(recv + p, my_ag + p, len); });
+        __syncthreads();
+        lo = plo; hi = phi;
+    }
+}
+
+size_t hd_capacity(int nranks, size_t es, size_t stage_bytes) {
+    int steps = 0;
+    while ((1 << steps) < nranks) steps++;
+    const size_t ve = 16 / es;
+    return stage_bytes / es / (size_t)(steps + 1) / ve * ve;
+}
+
+cudaError_t launch_hd(const CollArgs& a, ncclDataType_t dt, const LaunchCfg& cfg) {
+#define CALL(T, OP) return launch_coll(k_hd<T, OP>, a, cfg)
+    DCCL_DISPATCH_TYPE_OP((int)dt, a.op, CALL)
+#undef CALL
+    return cudaErrorInvalidValue;
+}
+
+} // namespace dccl

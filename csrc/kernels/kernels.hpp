@@ -1,0 +1,87 @@
+/**
+ * Host-callable launchers of the collective kernels. One launch = one whole
+ * collective (all algorithm steps of reference src/core/algorithms.hpp run
+ * inside the kernel). `ranks_in_launch` > 1 means single-GPU emulation: the
+ * grid is ranks x ctas and is launched cooperatively so every CTA is resident.
+ */
+#pragma once
+#include "../device/prims.cuh"
+#include <dccl/dccl.hpp>
+
+namespace dccl {
+
+struct LaunchCfg {
+    int ctas = 32;               // CTAs per rank
+    int threads = 512;
+    cudaStream_t stream = nullptr;
+    int ranks_in_launch = 1;     // > 1: emulation, cooperative launch
+};
+
+/* twoshot.cu: staging-based peer-to-peer variants */
+enum { TS_ALLREDUCE = 0, TS_REDUCESCATTER, TS_ALLGATHER, TS_BROADCAST, TS_BROADCAST_DIRECT, TS_REDUCE };
+/** Elements one launch can take for `mode` with n ranks and the given staging half. */
+size_t twoshot_capacity(int mode, int nranks, size_t elem_size, size_t stage_bytes);
+cudaError_t launch_twoshot(const CollArgs& a, ncclDataType_t dt, const LaunchCfg& cfg);
+
+/* oneshot_ll.cu: flag-in-data all-reduce for small messages */
+size_t oneshot_ll_capacity_bytes();
+cudaError_t launch_oneshot_ll(const CollArgs& a, ncclDataType_t dt, const LaunchCfg& cfg);
+
+/* nvls.cu: in-switch reduction / multicast variants */
+enum { NV_ALLREDUCE = 0, NV_REDUCESCATTER, NV_ALLGATHER, NV_BROADCAST, NV_REDUCE };
+bool nvls_supports(ncclDataType_t dt, ncclRedOp_t op);
+size_t nvls_capacity(int mode, int nranks, size_t elem_size, size_t stage_bytes);
+cudaError_t launch_nvls(const CollArgs& a, ncclDataType_t dt, const LaunchCfg& cfg);
+
+/* ring.cu / hd.cu: the two algorithms of the original as single kernels */
+enum { RING_ALLREDUCE = 0, RING_REDUCESCATTER, RING_ALLGATHER };
+size_t ring_capacity(int mode, int nranks, size_t elem_size, size_t stage_bytes);
+cudaError_t launch_ring(const CollArgs& a, ncclDataType_t dt, const LaunchCfg& cfg);
+size_t hd_capacity(int nranks, size_t elem_size, size_t stage_bytes);
+cudaError_t launch_hd(const CollArgs& a, ncclDataType_t dt, const LaunchCfg& cfg);
+
+/* local.cu: one-rank paths (copy, scale) and a pairwise reduce */
+cudaError_t launch_local_copy(void* dst, const void* src, size_t bytes, cudaStream_t stream);
+cudaError_t launch_local_reduce(void* acc, const void* in, size_t count, ncclDataType_t dt, ncclRedOp_t op, cudaStream_t stream);
+
+/* p2p.cu: send / recv through the per-pair FIFOs */
+struct P2pOp {
+    int is_send;
+    int peer;
+    char* buf;
+    size_t bytes;
+    unsigned long long chunk_base;   // chunks already moved on this (peer, direction) before this op
+};
+constexpr int kMaxP2pOps = 16;
+struct P2pArgs {
+    DevComm comm;
+    const DevComm* emu;              // emulation: array of per-rank DevComm
+    const P2pOp* emu_ops;            // emulation: [ranks][kMaxP2pOps]
+    const int* emu_nops;
+    int ctas_per_op;
+    int ctas_per_rank;
+    int nops;
+    P2pOp ops[kMaxP2pOps];
+};
+cudaError_t launch_p2p(const P2pArgs& a, const LaunchCfg& cfg);
+inline size_t p2p_chunks(size_t bytes) { return (bytes + kP2pChunk - 1) / kP2pChunk; }
+
+/* bounded-wait self test: waits on a flag nobody sets, must come back with a timeout status */
+cudaError_t launch_wait_probe(const DevComm& c, cudaStream_t stream);
+
+template <typename K>
+inline cudaError_t launch_kernel(K kernel, const void* args_struct, const LaunchCfg& cfg) {
+    void* params[] = {const_cast<void*>(args_struct)};
+    dim3 grid((unsigned)(cfg.ctas * cfg.ranks_in_launch)), block((unsigned)cfg.threads);
+    if (cfg.ranks_in_launch > 1) return cudaLaunchCooperativeKernel((const void*)kernel, grid, block, params, 0, cfg.stream);
+    return cudaLaunchKernel((const void*)kernel, grid, block, params, 0, cfg.stream);
+}
+
+/** Launch a collective kernel; fixes up the CTA count per rank that the kernel derives its ranges from. */
+template <typename K>
+inline cudaError_t launch_coll(K kernel, CollArgs a, const LaunchCfg& cfg) {
+    a.ctas_per_rank = cfg.ctas;
+    return launch_kernel(kernel, &a, cfg);
+}
+
+} // namespace dccl
