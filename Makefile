@@ -76,7 +76,7 @@ $(BUILD)/obj/%.cu.o: %.cu $(wildcard include/dccl/*.hpp) $(wildcard csrc/*/*.hpp
 	$(NVCC) $(NVCCFLAGS) -c $< -o $@
 
 $(LIB): $(HOST_OBJS) $(CU_OBJS)
-	$(CXX) -shared -o $@ $^ $(CUDA_LIBS) $(LDFLAGS)
+	$(CXX) -shared -o $@ $^ $(CUDA_LIBS) $(LDFLAGS) -Wl,--exclude-libs,ALL -Wl,-Bsymbolic
 
 dccl_b200/lib/libdccl.so: $(LIB)
 	@mkdir -p dccl_b200/lib

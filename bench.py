@@ -1,0 +1,389 @@
+#!/usr/bin/env python
+"""Headline benchmark: all-reduce bus bandwidth (nccl-tests convention) on N GPUs of one node.
+
+    python bench.py --gpus 1 --steps 20 --warmup 5
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 \
+           --master-port 29500 bench.py --gpus 8 --steps 20 --warmup 5
+
+One step = one ncclAllReduce (sum, bf16) of --bytes per rank through the library's public Python
+API. The device-timed number uses a buffer that already lives on the GPU (symmetric memory when
+there is more than one rank, so the NVSwitch reduces it in place); the end-to-end number adds, in
+every step, the copy of that step's input from pinned host memory and the read-back of the result.
+Times are CUDA-event times, maximum over ranks. busBW = S/t * 2(n-1)/n; with one GPU the factor is
+undefined and the value is algBW = S/t of the out-of-place local path.
+
+--impl nccl runs the same measurement through stock NCCL (torch.distributed), --impl reference
+reports that the original (a C++/Derecho/RDMA library) cannot be installed here, --sweep adds a
+size sweep of all-reduce / reduce-scatter / all-gather for every variant.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "allreduce_busbw"
+UNAVAILABLE = ("the reference is a C++17/CMake library on top of Derecho, mutils, libfabric and spdlog; "
+               "'pip install /root/reference' fails (no setup.py / pyproject.toml) and its dependencies are not installable offline")
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index = index
+        self.samples = []
+        self.proc = None
+        self.thread = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.FIELDS, "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+            return
+        self.thread = threading.Thread(target=self._read, daemon=True)
+        self.thread.start()
+
+    def _read(self):
+        for line in self.proc.stdout:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) >= 7:
+                self.samples.append(parts)
+
+    def stop(self):
+        if self.proc:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+        if self.thread:
+            self.thread.join(timeout=2)
+
+    def summary(self):
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        sm = [float(s[0]) for s in self.samples if s[0].replace(".", "").isdigit()]
+        mx = [float(s[1]) for s in self.samples if s[1].replace(".", "").isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(s[3 + i].lower() == "active" for s in self.samples)]
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None, "reasons": reasons, "samples": len(self.samples)}
+
+
+def env_rank_world():
+    return int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("LOCAL_RANK", "0"))
+
+
+def bus_factor(coll, n):
+    if n <= 1:
+        return 1.0
+    return {"allreduce": 2.0 * (n - 1) / n, "reducescatter": (n - 1) / n, "allgather": (n - 1) / n}.get(coll, 1.0)
+
+
+class Ours:
+    name = "dccl_b200"
+
+    def __init__(self, rank, world, local):
+        import torch
+        from dccl_b200 import Communicator
+        self.torch = torch
+        self.comm = Communicator(device=local)   # rank / world / rendezvous from the launcher's environment
+        self.dev = torch.device("cuda", local)
+        self.local = local
+        self.world = world
+
+    def alloc(self, numel, dtype, symmetric=True):
+        if symmetric and self.world > 1:
+            return self.comm.symmetric_empty(numel, dtype, self.local)
+        return self.torch.empty(numel, dtype=dtype, device=self.dev)
+
+    def free(self, t):
+        if hasattr(t, "_dccl_ptr"):
+            self.comm.free_symmetric(t)
+
+    def all_reduce(self, s, r):
+        self.comm.all_reduce(s, r, op="sum")
+        return r
+
+    def reduce_scatter(self, s, r):
+        self.comm.reduce_scatter(s, r, op="sum")
+
+    def all_gather(self, s, r):
+        self.comm.all_gather(s, r)
+
+    def set_algo(self, coll, algo):
+        self.comm.set_algorithm(coll, algo)
+
+    def launches(self):
+        return self.comm.launches
+
+    def host_max(self, x):
+        import numpy as np
+        a = np.array([x], dtype=np.float64)
+        self.comm.all_reduce(a, op="max")
+        return float(a[0])
+
+    def barrier(self):
+        import numpy as np
+        a = np.zeros(1, dtype=np.int32)
+        self.comm.all_reduce(a)
+
+    def close(self):
+        self.comm.finalize()
+
+
+class StockNccl:
+    name = "nccl"
+
+    def __init__(self, rank, world, local):
+        import torch
+        import torch.distributed as dist
+        self.torch, self.dist = torch, dist
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29531")
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", local))
+        self.dev = torch.device("cuda", local)
+        self.world = world
+        self._launch = 0
+
+    def alloc(self, numel, dtype, symmetric=True):
+        return self.torch.empty(numel, dtype=dtype, device=self.dev)
+
+    def free(self, t):
+        pass
+
+    def all_reduce(self, s, r):
+        # torch's NCCL binding reduces in place; the second buffer is not used (values may overflow
+        # to inf over many steps, which does not change the time)
+        self.dist.all_reduce(s)
+        self._launch += 1
+        return s
+
+    def reduce_scatter(self, s, r):
+        self.dist.reduce_scatter_tensor(r, s)
+        self._launch += 1
+
+    def all_gather(self, s, r):
+        self.dist.all_gather_into_tensor(r, s)
+        self._launch += 1
+
+    def set_algo(self, coll, algo):
+        pass
+
+    def launches(self):
+        return self._launch
+
+    def host_max(self, x):
+        t = self.torch.tensor([x], dtype=self.torch.float64, device=self.dev)
+        self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def barrier(self):
+        self.dist.barrier()
+
+    def close(self):
+        self.dist.destroy_process_group()
+
+
+def timed(backend, fn, steps, warmup):
+    """ms per step: W warm-up calls, then K calls between two events, barrier + synchronize on both sides, max over ranks."""
+    torch = backend.torch
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    backend.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    backend.barrier()
+    torch.cuda.synchronize()
+    return backend.host_max(e0.elapsed_time(e1) / steps)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "nccl", "reference"])
+    ap.add_argument("--bytes", type=int, default=1 << 30, help="message bytes per rank for the headline all-reduce")
+    ap.add_argument("--dtype", default="bf16", choices=["bf16", "fp32"])
+    ap.add_argument("--algo", default="auto")
+    ap.add_argument("--sweep", action="store_true", help="also sweep sizes and variants; table goes to --out")
+    ap.add_argument("--out", default=os.path.join(ROOT, "gpurun_out", "sweep.json"))
+    ap.add_argument("--e2e-steps", type=int, default=5)
+    args = ap.parse_args()
+    if args.warmup < 3:
+        args.warmup = 3
+
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable": UNAVAILABLE}))
+        return 0
+
+    import torch
+    rank, world, local = env_rank_world()
+    if world != args.gpus and rank == 0:
+        print("note: --gpus %d but WORLD_SIZE is %d; using the launcher's value" % (args.gpus, world), file=sys.stderr)
+    torch.cuda.set_device(local)
+    backend = (Ours if args.impl == "ours" else StockNccl)(rank, world, local)
+    dtype = torch.bfloat16 if args.dtype == "bf16" else torch.float32
+    es = 2 if args.dtype == "bf16" else 4
+    numel = args.bytes // es
+    nbytes = numel * es
+
+    # ---- device-timed headline ----
+    if args.algo != "auto":
+        backend.set_algo("allreduce", args.algo)
+    buf = backend.alloc(numel, dtype, symmetric=True)
+    buf.fill_(1.0 / 1024)
+    out = backend.alloc(numel, dtype, symmetric=True)   # out of place: the input keeps its values over all steps
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.3)
+
+    def step():
+        backend.all_reduce(buf, out)
+
+    l0 = backend.launches()
+    ms = timed(backend, step, args.steps, args.warmup)
+    launches = (backend.launches() - l0) * args.steps // (args.steps + args.warmup)
+    algo_used = backend.comm.last_algorithm("allreduce") if args.impl == "ours" else "nccl"
+    algbw = nbytes / (ms * 1e-3) / 1e9
+    value = algbw * bus_factor("allreduce", world)
+
+    # same measurement on an ordinary (non-symmetric) tensor, for the record
+    plain_ms = None
+    if world > 1:
+        pbuf = backend.alloc(numel, dtype, symmetric=False)
+        pbuf.fill_(1.0 / 1024)
+        plain_ms = timed(backend, lambda: backend.all_reduce(pbuf, pbuf), max(3, args.steps // 2), 3)
+        del pbuf
+
+    # ---- end to end: pinned host input -> device -> all-reduce -> host, every step ----
+    host_in = torch.empty(numel, dtype=dtype).pin_memory()
+    host_in.fill_(1.0 / 1024)
+    host_out = torch.empty(numel, dtype=dtype).pin_memory()
+
+    def e2e_step():
+        buf.copy_(host_in, non_blocking=True)
+        res = backend.all_reduce(buf, out)
+        host_out.copy_(res, non_blocking=True)
+
+    e2e_ms = timed(backend, e2e_step, args.e2e_steps, 3)
+    e2e_value = nbytes / (e2e_ms * 1e-3) / 1e9 * bus_factor("allreduce", world)
+    ok = bool(torch.isfinite(host_out[:1024].float()).all())
+
+    clocks = None
+    if rank == 0:
+        sampler.stop()
+        clocks = sampler.summary()
+
+    sweep = None
+    if args.sweep:
+        sweep = run_sweep(backend, args, rank, world, dtype, es)
+
+    backend.free(buf)
+    backend.free(out)
+    if rank == 0:
+        peaks = {}
+        try:
+            peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+        except Exception:
+            pass
+        link_gbs = 900.0
+        roofline_ms = (2.0 * nbytes / (peaks.get("hbm_gbs", 6650.0) * 1e9) if world == 1
+                       else 2.0 * nbytes * (world - 1) / world / (link_gbs * 1e9)) * 1e3
+        line = {
+            "metric": METRIC, "value": round(value, 3), "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": round(ms, 5), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": args.dtype, "data": "synthetic", "impl": backend.name,
+            "config": {"model": "ncclAllReduce sum", "message_bytes_per_rank": nbytes, "global_batch": None, "seq_len": None,
+                       "parallelism": "%d ranks, one per GPU" % world, "algorithm": algo_used,
+                       "buffers": "symmetric (dcclMemAlloc), out of place" if world > 1 and args.impl == "ours" else "ordinary device memory",
+                       "l2": "message (%d MiB) larger than the 126 MB L2" % (nbytes >> 20) if nbytes > (126 << 20) else "message fits L2: not flushed",
+                       "value_is": "busBW = algBW*2(n-1)/n" if world > 1 else "algBW (one rank: out-of-place local path)"},
+            "algbw_gbs": round(algbw, 3),
+            "roofline": {"ms": round(roofline_ms, 5), "fraction": round(roofline_ms / ms, 4),
+                         "of": "measured HBM copy" if world == 1 else "2S(n-1)/n over 900 GB/s per direction (P2P bound)"},
+            "plain_buffer": None if plain_ms is None else {"ms_per_step": round(plain_ms, 5), "busbw_gbs": round(nbytes / (plain_ms * 1e-3) / 1e9 * bus_factor("allreduce", world), 3)},
+            "e2e": {"value": round(e2e_value, 3), "unit": "GB/s", "ms_per_step": round(e2e_ms, 4), "h2d_bytes_per_step": nbytes,
+                    "d2h_bytes_per_step": nbytes, "steps": args.e2e_steps, "result_finite": ok},
+            "gpu_launches": int(launches) if args.impl == "ours" else 0,
+            "clocks": clocks,
+        }
+        if sweep is not None:
+            os.makedirs(os.path.dirname(args.out), exist_ok=True)
+            with open(args.out, "w") as f:
+                json.dump({"n_gpus": world, "impl": backend.name, "rows": sweep}, f, indent=1)
+            line["sweep_file"] = os.path.relpath(args.out, ROOT)
+        print(json.dumps(line))
+    backend.close()
+    return 0
+
+
+def run_sweep(backend, args, rank, world, dtype, es):
+    """busBW per (collective, variant, size); sizes are powers of two from 1 KB to the headline size."""
+    torch = backend.torch
+    rows = []
+    sizes = []
+    s = 1024
+    while s <= args.bytes:
+        sizes.append(s)
+        s *= 4 if s >= (1 << 20) else 2
+    if sizes[-1] != args.bytes:
+        sizes.append(args.bytes)
+    variants = {"allreduce": ["auto", "oneshot", "twoshot", "ring", "rabenseifner", "nvls"],
+                "reducescatter": ["auto", "twoshot", "ring", "nvls"], "allgather": ["auto", "twoshot", "ring", "nvls"]}
+    if args.impl != "ours" or world == 1:
+        variants = {k: ["auto"] for k in variants}
+    maxel = args.bytes // es
+    src = backend.alloc(maxel, dtype, symmetric=False)
+    dst = backend.alloc(maxel, dtype, symmetric=False)
+    src.fill_(1.0 / 1024)
+    for coll, algos in variants.items():
+        for algo in algos:
+            backend.set_algo(coll, algo)
+            for size in sizes:
+                if algo == "oneshot" and size > (128 << 10):
+                    continue
+                if algo in ("ring", "rabenseifner") and size < (64 << 10) and world > 1 and False:
+                    continue
+                n_el = max(size // es, world)
+                per = n_el // world
+                if coll == "allreduce":
+                    fn = lambda: backend.all_reduce(src[:n_el], dst[:n_el])   # noqa: E731
+                    total = n_el * es
+                elif coll == "reducescatter":
+                    fn = lambda: backend.reduce_scatter(src[:per * world], dst[:per])   # noqa: E731
+                    total = per * world * es
+                else:
+                    fn = lambda: backend.all_gather(src[:per], dst[:per * world])   # noqa: E731
+                    total = per * world * es
+                steps = 200 if size <= (1 << 20) else 20 if size <= (64 << 20) else 8
+                ms = timed(backend, fn, steps, 5)
+                algbw = total / (ms * 1e-3) / 1e9
+                used = backend.comm.last_algorithm(coll) if args.impl == "ours" else "nccl"
+                rows.append({"coll": coll, "algo": algo, "ran": used, "bytes": total, "us": round(ms * 1e3, 3),
+                             "algbw_gbs": round(algbw, 3), "busbw_gbs": round(algbw * bus_factor(coll, world), 3)})
+            backend.set_algo(coll, "auto")
+    return rows
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -8,6 +8,7 @@
 #include "../core/types.hpp"
 #include "../gpu/gpu_comm.hpp"
 #include "comm.hpp"
+#include "../tuner/tuner.hpp"
 #include <cstring>
 
 using namespace dccl;
@@ -98,6 +99,18 @@ int dccl_config_get(const char* key, char* out, size_t len) {
     return 1;
 }
 int dccl_config_parse_world(const char* json) { return Config::world_size_from_layout(json); }
+
+/* variant table, for tests and tools: a process-wide table separate from any communicator */
+static Tuner& test_tuner() { static Tuner t; return t; }
+int dccl_tuner_load_text(const char* text) { std::string err; return test_tuner().load_text(text, &err); }
+int dccl_tuner_choose(const char* coll, int nranks, size_t bytes, int nvls_ok, char* algo_out, size_t len, int* ctas) {
+    int c = parse_collective_name(coll);
+    if (c < 0) return -1;
+    TuneChoice ch = test_tuner().choose(c, nranks, bytes, nvls_ok != 0);
+    if (algo_out && len) snprintf(algo_out, len, "%s", algo_name(ch.algo));
+    if (ctas) *ctas = ch.ctas;
+    return 0;
+}
 
 /* index arithmetic, exported so unit tests can check it without a communicator */
 void dccl_slot_range(size_t count, unsigned n, unsigned i, size_t align, size_t* lo, size_t* hi) { slot_range(count, n, i, align, lo, hi); }

@@ -1,0 +1,232 @@
+"""Python face of the communicator: a thin object over the C API.
+
+Buffers are passed as raw addresses, so the same calls serve numpy arrays
+(host collectives over shared memory) and torch CUDA tensors (device kernels).
+Counterpart of the C++ API in ``include/dccl/dccl.hpp`` (which follows
+reference include/dccl/dccl.hpp:143-474).
+"""
+import ctypes
+import os
+
+import numpy as np
+
+from ._lib import lib
+
+# ncclDataType_t / ncclRedOp_t values
+INT8, UINT8, INT32, UINT32, INT64, UINT64, FLOAT16, FLOAT32, FLOAT64, BFLOAT16 = range(10)
+SUM, PROD, MAX, MIN, AVG = range(5)
+OPS = {"sum": SUM, "prod": PROD, "max": MAX, "min": MIN, "avg": AVG}
+DTYPE_NAMES = ["int8", "uint8", "int32", "uint32", "int64", "uint64", "float16", "float32", "float64", "bfloat16"]
+DTYPE_SIZES = [1, 1, 4, 4, 8, 8, 2, 4, 8, 2]
+
+_NP_TO_DCCL = {
+    np.dtype(np.int8): INT8, np.dtype(np.uint8): UINT8, np.dtype(np.int32): INT32, np.dtype(np.uint32): UINT32,
+    np.dtype(np.int64): INT64, np.dtype(np.uint64): UINT64, np.dtype(np.float16): FLOAT16,
+    np.dtype(np.float32): FLOAT32, np.dtype(np.float64): FLOAT64,
+}
+
+
+class DcclError(RuntimeError):
+    def __init__(self, code, what):
+        self.code = code
+        msg = lib().dccl_error_string(code).decode()
+        super().__init__("%s failed: %s (ncclResult_t %d)" % (what, msg, code))
+
+
+def _check(code, what):
+    if code != 0:
+        raise DcclError(code, what)
+
+
+def _torch():
+    import torch
+    return torch
+
+
+def dtype_of(x):
+    """ncclDataType_t value of a numpy array or torch tensor."""
+    if isinstance(x, np.ndarray):
+        return _NP_TO_DCCL[x.dtype]
+    torch = _torch()
+    table = {torch.int8: INT8, torch.uint8: UINT8, torch.int32: INT32, torch.int64: INT64, torch.float16: FLOAT16,
+             torch.float32: FLOAT32, torch.float64: FLOAT64, torch.bfloat16: BFLOAT16}
+    if hasattr(torch, "uint32"):
+        table[torch.uint32] = UINT32
+        table[torch.uint64] = UINT64
+    return table[x.dtype]
+
+
+def _addr(x):
+    if x is None:
+        return None
+    if isinstance(x, np.ndarray):
+        if not x.flags["C_CONTIGUOUS"]:
+            raise ValueError("buffers must be contiguous")
+        return x.ctypes.data
+    if not x.is_contiguous():
+        raise ValueError("buffers must be contiguous")
+    return x.data_ptr()
+
+
+def _numel(x):
+    return x.size if isinstance(x, np.ndarray) else x.numel()
+
+
+def _stream_of(x, stream):
+    if stream is not None:
+        return stream if isinstance(stream, int) else stream.cuda_stream
+    if isinstance(x, np.ndarray):
+        return None
+    if x.is_cuda:
+        return _torch().cuda.current_stream(x.device).cuda_stream
+    return None
+
+
+def get_unique_id():
+    """128-byte rendezvous token; the calling process becomes the rendezvous server (rank 0)."""
+    buf = ctypes.create_string_buffer(128)
+    _check(lib().dccl_get_unique_id(buf), "dcclGetUniqueId")
+    return buf.raw
+
+
+class Communicator:
+    """One rank's handle on a group of processes.
+
+    ``Communicator()`` reads rank / world / rendezvous address from the
+    environment or a configuration directory (see ``ncclCommInit``);
+    ``Communicator(rank=, world=, unique_id=)`` takes them explicitly.
+    ``device`` binds a CUDA device right away (a collective step: every rank
+    passes its own device); without it the device side is set up by the first
+    call that is given device memory.
+    """
+
+    def __init__(self, rank=None, world=None, unique_id=None, device=None):
+        self._h = ctypes.c_void_p()
+        if unique_id is not None:
+            buf = ctypes.create_string_buffer(bytes(unique_id), 128)
+            _check(lib().dccl_comm_init_rank(ctypes.byref(self._h), int(world), buf, int(rank)), "dcclCommInitRank")
+        else:
+            if rank is not None:
+                os.environ["DCCL_RANK"] = str(rank)
+                os.environ["DCCL_WORLD_SIZE"] = str(world)
+            _check(lib().dccl_comm_init(ctypes.byref(self._h)), "ncclCommInit")
+        self.rank = lib().dccl_rank(self._h)
+        self.world = lib().dccl_world_size(self._h)
+        if device is not None:
+            _check(lib().dccl_comm_bind_device(self._h, int(device)), "device setup")
+
+    # -- life cycle ---------------------------------------------------
+    def finalize(self):
+        if self._h:
+            h, self._h = self._h, ctypes.c_void_p()
+            _check(lib().dccl_comm_finalize(h), "ncclCommFinalize")
+
+    def abort(self):
+        _check(lib().dccl_comm_abort(self._h), "dcclCommAbort")
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        self.finalize()
+
+    def last_error(self):
+        """(code, message) of the asynchronous state; code 0 means healthy."""
+        code = ctypes.c_int(0)
+        msg = ctypes.create_string_buffer(256)
+        lib().dccl_last_error(self._h, ctypes.byref(code), msg, 256)
+        return code.value, msg.value.decode()
+
+    def check(self):
+        code, msg = self.last_error()
+        if code:
+            raise DcclError(code, "communicator (" + msg + ")")
+
+    @property
+    def has_multicast(self):
+        return bool(lib().dccl_has_multicast(self._h))
+
+    @property
+    def launches(self):
+        return int(lib().dccl_launch_count(self._h))
+
+    def set_algorithm(self, collective, name):
+        _check(lib().dccl_set_algorithm(self._h, collective.encode(), name.encode()), "dcclSetAlgorithm")
+
+    def last_algorithm(self, collective):
+        return lib().dccl_last_algorithm(self._h, collective.encode()).decode()
+
+    # -- memory -------------------------------------------------------
+    def register(self, x):
+        nbytes = _numel(x) * DTYPE_SIZES[dtype_of(x)]
+        _check(lib().dccl_register(self._h, _addr(x), nbytes), "dcclRegisterCacheMemory")
+
+    def deregister(self, x):
+        _check(lib().dccl_deregister(self._h, _addr(x)), "dcclDeregisterCacheMemory")
+
+    def mem_alloc(self, nbytes):
+        p = ctypes.c_void_p()
+        _check(lib().dccl_mem_alloc(self._h, ctypes.byref(p), int(nbytes)), "dcclMemAlloc")
+        return p.value
+
+    def mem_free(self, ptr):
+        _check(lib().dccl_mem_free(self._h, ctypes.c_void_p(ptr)), "dcclMemFree")
+
+    def symmetric_empty(self, numel, dtype, device=None):
+        """A torch tensor in symmetric (peer-mapped, multicast-bound) device memory. Collective.
+        Free it with ``free_symmetric`` before the communicator is finalized."""
+        from .utils.memory import tensor_from_pointer
+        torch = _torch()
+        itemsize = torch.empty((), dtype=dtype).element_size()
+        ptr = self.mem_alloc(numel * itemsize)
+        t = tensor_from_pointer(ptr, numel, dtype, device if device is not None else torch.cuda.current_device())
+        t._dccl_ptr = ptr
+        return t
+
+    def free_symmetric(self, t):
+        self.mem_free(t._dccl_ptr)
+
+    # -- collectives --------------------------------------------------
+    def all_reduce(self, send, recv=None, op="sum", stream=None):
+        recv = send if recv is None else recv
+        _check(lib().dccl_all_reduce(_addr(send), _addr(recv), _numel(send), dtype_of(send), OPS[op], self._h,
+                                     _stream_of(send, stream)), "ncclAllReduce")
+        return recv
+
+    def reduce_scatter(self, send, recv, op="sum", stream=None):
+        _check(lib().dccl_reduce_scatter(_addr(send), _addr(recv), _numel(recv), dtype_of(send), OPS[op], self._h,
+                                         _stream_of(send, stream)), "ncclReduceScatter")
+        return recv
+
+    def all_gather(self, send, recv, stream=None):
+        _check(lib().dccl_all_gather(_addr(send), _addr(recv), _numel(send), dtype_of(send), self._h,
+                                     _stream_of(send, stream)), "ncclAllGather")
+        return recv
+
+    def broadcast(self, send, recv=None, root=0, stream=None):
+        recv = send if recv is None else recv
+        _check(lib().dccl_broadcast(_addr(send), _addr(recv), _numel(recv), dtype_of(recv), root, self._h,
+                                    _stream_of(recv, stream)), "ncclBroadcast")
+        return recv
+
+    def reduce(self, send, recv=None, op="sum", root=0, stream=None):
+        if recv is None and self.rank == root:
+            recv = send
+        _check(lib().dccl_reduce(_addr(send), _addr(recv), _numel(send), dtype_of(send), OPS[op], root, self._h,
+                                 _stream_of(send, stream)), "ncclReduce")
+        return recv
+
+    def send(self, x, peer, stream=None):
+        _check(lib().dccl_send(_addr(x), _numel(x), dtype_of(x), peer, self._h, _stream_of(x, stream)), "ncclSend")
+
+    def recv(self, x, peer, stream=None):
+        _check(lib().dccl_recv(_addr(x), _numel(x), dtype_of(x), peer, self._h, _stream_of(x, stream)), "ncclRecv")
+        return x
+
+
+def group_start():
+    _check(lib().dccl_group_start(), "dcclGroupStart")
+
+
+def group_end():
+    _check(lib().dccl_group_end(), "dcclGroupEnd")

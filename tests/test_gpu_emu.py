@@ -1,0 +1,181 @@
+"""Device kernels against the serial fold, all ranks emulated on ONE GPU.
+
+One cooperative launch plays every rank (see csrc/gpu/emu.cu), so the flag protocol, staging halves,
+packet generations and the reductions are the code that runs on a multi-GPU box. Each case runs
+three calls back to back, which exercises the reuse of both staging halves / packet generations.
+"""
+import ctypes
+
+import numpy as np
+import pytest
+
+from dccl_b200.comm import DTYPE_NAMES, OPS
+from dccl_b200.utils import oracle
+
+pytestmark = pytest.mark.gpu
+
+FLOATS = ["float16", "float32", "float64", "bfloat16"]
+
+
+def np_dtype(name):
+    return np.uint16 if name == "bfloat16" else np.dtype(name)
+
+
+def inputs_for(name, op, count, n, seed):
+    ins = [oracle.make_input(name, count, seed=seed * 100 + r) for r in range(n)]
+    if op == "prod" and name in FLOATS:   # keep products in range
+        if name == "bfloat16":
+            ins = [oracle.f32_to_bf16(np.where(np.abs(oracle.bf16_to_f32(x)) < 0.5, 1.0, 1.25).astype(np.float32)) for x in ins]
+        else:
+            ins = [np.where(np.abs(x) < 0.5, 1.0, 1.25).astype(name) for x in ins]
+    return ins
+
+
+def close(got, want, name, world):
+    rtol, atol = oracle.tolerances(name, world)
+    if rtol == 0.0:
+        return np.array_equal(got, want)
+    if name == "bfloat16":
+        got, want = oracle.bf16_to_f32(got), oracle.bf16_to_f32(want)
+    return np.allclose(got.astype(np.float64), want.astype(np.float64), rtol=rtol, atol=atol)
+
+
+def emu(lib, kind, algo, n, name, op, count, ins, root=0, ctas=3, in_place=0, misalign=0, iters=3, stage=0):
+    dt = DTYPE_NAMES.index(name)
+    es = np_dtype(name).itemsize if name != "bfloat16" else 2
+    in_elems = count * n if kind == "reducescatter" else count
+    out_elems = count * n if kind == "allgather" else count
+    hin = np.concatenate(ins).astype(np_dtype(name), copy=False)
+    assert hin.size == in_elems * n
+    hout = np.zeros(out_elems * n, dtype=np_dtype(name))
+    rc = lib.dccl_emu_collective(kind.encode(), algo.encode(), n, dt, OPS[op], count, root, ctas, in_place, misalign, iters,
+                                 stage, hin.ctypes.data, hout.ctypes.data)
+    assert rc == 0, "emulation returned %d" % rc
+    assert es * out_elems * n == hout.nbytes
+    return hout.reshape(n, out_elems)
+
+
+@pytest.mark.parametrize("algo", ["oneshot", "twoshot", "ring", "rabenseifner"])
+@pytest.mark.parametrize("n", [2, 4, 8])
+def test_allreduce_fp32_bf16_sizes(dccl_lib, algo, n):
+    for name in ["float32", "bfloat16"]:
+        for count in [1, 3, 257, 4096, 10007, 65536 + 5]:
+            if algo == "oneshot" and count * (4 if name == "float32" else 2) > 128 * 1024:
+                continue
+            for op in ["sum", "avg"]:
+                ins = inputs_for(name, op, count, n, seed=count % 89)
+                want = oracle.fold(ins, op, bf16=name == "bfloat16")
+                out = emu(dccl_lib, "allreduce", algo, n, name, op, count, ins)
+                for r in range(n):
+                    assert close(out[r], want, name, n), (algo, n, name, op, count, r)
+                # all ranks must hold the same bits
+                for r in range(1, n):
+                    assert np.array_equal(out[r], out[0]), (algo, n, name, op, count, "ranks differ")
+
+
+@pytest.mark.parametrize("algo", ["oneshot", "twoshot", "ring", "rabenseifner"])
+def test_allreduce_every_dtype_and_operator(dccl_lib, algo):
+    n, count = 4, 1031
+    for name in DTYPE_NAMES:
+        for op in ["sum", "prod", "max", "min", "avg"]:
+            ins = inputs_for(name, op, count, n, seed=7)
+            want = oracle.fold(ins, op, bf16=name == "bfloat16")
+            out = emu(dccl_lib, "allreduce", algo, n, name, op, count, ins)
+            for r in range(n):
+                assert close(out[r], want, name, n), (algo, name, op, r)
+
+
+@pytest.mark.parametrize("algo", ["oneshot", "twoshot", "ring", "rabenseifner"])
+def test_allreduce_in_place_and_unaligned(dccl_lib, algo):
+    n = 4
+    for name, misalign in [("float32", 4), ("bfloat16", 2), ("float32", 0), ("int8", 1), ("float64", 8)]:
+        for in_place in [0, 1]:
+            count = 5003
+            ins = inputs_for(name, "sum", count, n, seed=3)
+            want = oracle.fold(ins, "sum", bf16=name == "bfloat16")
+            out = emu(dccl_lib, "allreduce", algo, n, name, "sum", count, ins, in_place=in_place, misalign=misalign)
+            for r in range(n):
+                assert close(out[r], want, name, n), (algo, name, misalign, in_place, r)
+
+
+@pytest.mark.parametrize("algo", ["twoshot", "ring"])
+@pytest.mark.parametrize("n", [2, 3, 8])
+def test_reduce_scatter_and_all_gather(dccl_lib, algo, n):
+    for name in ["float32", "bfloat16", "int32", "float16"]:
+        for count in [1, 256, 1000, 4097]:
+            for op in ["sum", "max", "min", "avg"]:
+                ins = inputs_for(name, op, count * n, n, seed=11)
+                want = oracle.fold(ins, op, bf16=name == "bfloat16")
+                for in_place in [0, 1]:
+                    out = emu(dccl_lib, "reducescatter", algo, n, name, op, count, ins, in_place=in_place)
+                    for r in range(n):
+                        assert close(out[r], want[r * count:(r + 1) * count], name, n), ("rs", algo, n, name, op, count, r, in_place)
+            ins = inputs_for(name, "sum", count, n, seed=13)
+            for in_place in [0, 1]:
+                out = emu(dccl_lib, "allgather", algo, n, name, "sum", count, ins, in_place=in_place)
+                for r in range(n):
+                    assert np.array_equal(out[r], np.concatenate(ins)), ("ag", algo, n, name, count, r, in_place)
+
+
+@pytest.mark.parametrize("n", [2, 5, 8])
+def test_broadcast_and_reduce_roots(dccl_lib, n):
+    for root in {0, n - 1}:
+        for count in [1, 4, 1000, 70001]:
+            ins = inputs_for("float32", "sum", count, n, seed=17)
+            for algo in ["oneshot", "twoshot"]:
+                out = emu(dccl_lib, "broadcast", algo, n, "float32", "sum", count, ins, root=root, in_place=1)
+                for r in range(n):
+                    assert np.array_equal(out[r], ins[root]), ("bcast", algo, n, root, count, r)
+            for op in ["sum", "avg", "max"]:
+                want = oracle.fold(ins, op)
+                out = emu(dccl_lib, "reduce", "twoshot", n, "float32", op, count, ins, root=root)
+                assert close(out[root], want, "float32", n), ("reduce", n, root, count, op)
+
+
+def test_many_ctas_and_small_staging(dccl_lib):
+    """More CTAs than vectors, and a staging half barely larger than the message."""
+    n = 8
+    for ctas in [1, 7, 16]:
+        for count in [5, 20000]:
+            ins = inputs_for("float32", "sum", count, n, seed=ctas)
+            want = oracle.fold(ins, "sum")
+            for algo in ["twoshot", "ring", "rabenseifner"]:
+                out = emu(dccl_lib, "allreduce", algo, n, "float32", "sum", count, ins, ctas=ctas, stage=1 << 20)
+                for r in range(n):
+                    assert close(out[r], want, "float32", n), (algo, ctas, count, r)
+
+
+def test_send_recv_ring(dccl_lib):
+    for n in [2, 8]:
+        for nbytes in [4, 1000, (1 << 20) + 24, 5 * (1 << 20) + 8]:   # the last one is longer than the FIFO: needs flow control
+            rng = np.random.default_rng(nbytes)
+            hin = rng.integers(0, 256, n * nbytes, dtype=np.uint8)
+            hout = np.zeros_like(hin)
+            rc = dccl_lib.dccl_emu_sendrecv_ring(n, nbytes, 4, 3, hin.ctypes.data, hout.ctypes.data)
+            assert rc == 0
+            hin, hout = hin.reshape(n, nbytes), hout.reshape(n, nbytes)
+            for r in range(n):
+                assert np.array_equal(hout[r], hin[(r - 1) % n]), (n, nbytes, r)
+
+
+def test_local_reduce_every_dtype_and_operator(dccl_lib):
+    count = 100003
+    for name in DTYPE_NAMES:
+        for op in ["sum", "prod", "max", "min"]:
+            a, b = inputs_for(name, op, count, 2, seed=23)
+            want = oracle.fold([a, b], op, bf16=name == "bfloat16")
+            acc = a.copy()
+            rc = dccl_lib.dccl_local_reduce(acc.ctypes.data, b.ctypes.data, count, DTYPE_NAMES.index(name), OPS[op])
+            assert rc == 0 and close(acc, want, name, 2), (name, op)
+
+
+def test_bounded_wait_returns_a_status(dccl_lib):
+    """A wait on a flag that nothing sets ends by itself with a timeout status; the context stays usable."""
+    ms = ctypes.c_float()
+    code = dccl_lib.dccl_emu_wait_probe(50, ctypes.byref(ms))
+    assert code == 1, "expected the timeout status, got %d" % code
+    assert 40.0 <= ms.value < 2000.0
+    # the device still works
+    a = np.ones(1000, dtype=np.float32)
+    b = np.ones(1000, dtype=np.float32)
+    assert dccl_lib.dccl_local_reduce(a.ctypes.data, b.ctypes.data, 1000, 7, 0) == 0 and np.all(a == 2.0)

@@ -1,0 +1,37 @@
+"""Device collectives among real processes, one per GPU (needs at least two GPUs)."""
+import os
+
+import pytest
+
+from conftest import gpu_count
+from dccl_b200.utils.launch import python_ranks
+
+pytestmark = pytest.mark.gpu
+HERE = os.path.dirname(os.path.abspath(__file__))
+WORKER = os.path.join(HERE, "workers", "gpu_worker.py")
+
+
+def run(world, args, env=None, timeout=600):
+    res = python_ranks(WORKER, args, world, env_extra=env, timeout=timeout, gpus=True)
+    for r, p in enumerate(res):
+        assert p.returncode == 0, "rank %d:\n%s\n%s" % (r, p.stdout[-3000:], p.stderr[-3000:])
+        assert p.stdout.strip().splitlines()[-1].startswith("OK"), p.stdout
+    return res
+
+
+@pytest.mark.skipif(gpu_count() < 2, reason="needs two GPUs")
+def test_every_variant_on_all_gpus():
+    world = min(gpu_count(), 8)
+    run(world, ["--suite", "basic"])
+
+
+@pytest.mark.skipif(gpu_count() < 2, reason="needs two GPUs")
+def test_messages_larger_than_staging_are_chunked():
+    world = min(gpu_count(), 8)
+    run(world, ["--suite", "chunk"], env={"DCCL_STAGING_BYTES": str(4 << 20)})
+
+
+@pytest.mark.skipif(gpu_count() < 2, reason="needs two GPUs")
+def test_peer_handles_fallback_without_multicast():
+    """cudaIpc handles instead of cuMem descriptors: no multicast, peer loads / stores only."""
+    run(2, ["--suite", "chunk"], env={"DCCL_POOL_MODE": "ipc", "DCCL_STAGING_BYTES": str(16 << 20)})

@@ -1,0 +1,146 @@
+"""Host-side unit tests: index arithmetic, conversions, configuration, timestamps, variant table."""
+import ctypes
+import os
+
+import numpy as np
+import pytest
+from hypothesis import given, settings, strategies as st
+
+from dccl_b200.utils import oracle, tt
+
+
+def test_slot_range_covers_everything(dccl_lib):
+    lo, hi = ctypes.c_size_t(), ctypes.c_size_t()
+    for count in [0, 1, 7, 8, 1000, 1023, 1024, 1025, 99999]:
+        for n in range(1, 9):
+            for align in [1, 4, 8]:
+                covered = 0
+                prev_hi = 0
+                for i in range(n):
+                    dccl_lib.dccl_slot_range(count, n, i, align, ctypes.byref(lo), ctypes.byref(hi))
+                    assert lo.value == prev_hi and hi.value >= lo.value
+                    if lo.value < count:
+                        assert lo.value % align == 0
+                    covered += hi.value - lo.value
+                    prev_hi = hi.value
+                assert covered == count and prev_hi == count
+
+
+@given(st.integers(0, 255), st.integers(1, 8))
+@settings(max_examples=200, deadline=None)
+def test_reverse_bits_is_an_involution(dccl_lib, x, bits):
+    x &= (1 << bits) - 1
+    r = dccl_lib.dccl_reverse_bits(x, bits)
+    assert dccl_lib.dccl_reverse_bits(r, bits) == x
+    assert bin(r).count("1") == bin(x).count("1")
+
+
+def test_log_two(dccl_lib):
+    for x in range(1, 300):
+        assert dccl_lib.dccl_log_two(x) == x.bit_length() - 1
+
+
+def test_type_and_op_names(dccl_lib):
+    names = ["int8", "uint8", "int32", "uint32", "int64", "uint64", "float16", "float32", "float64", "bfloat16"]
+    sizes = [1, 1, 4, 4, 8, 8, 2, 4, 8, 2]
+    for i, (nm, sz) in enumerate(zip(names, sizes)):
+        assert dccl_lib.dccl_parse_type(nm.encode()) == i
+        assert dccl_lib.dccl_size_of_type(i) == sz
+    # every operator name maps to its own value (the original's parser mixed them up)
+    for i, nm in enumerate(["sum", "prod", "max", "min", "avg"]):
+        assert dccl_lib.dccl_parse_op(nm.encode()) == i
+    assert dccl_lib.dccl_parse_op(b"nonsense") == 5
+    assert dccl_lib.dccl_parse_type(b"nonsense") == 10
+
+
+def test_half_conversion_matches_numpy(dccl_lib):
+    bits = np.arange(0, 65536, 7, dtype=np.uint16)
+    for b in bits:
+        f = np.array([b], dtype=np.uint16).view(np.float16)[0]
+        got = dccl_lib.dccl_half_to_float(int(b))
+        if np.isnan(f):
+            assert np.isnan(got)
+        else:
+            assert got == float(f)
+    rng = np.random.default_rng(0)
+    vals = np.concatenate([rng.normal(0, 1, 2000), rng.normal(0, 1e-6, 500), rng.normal(0, 3e4, 500), [0.0, -0.0, 65504.0, 1e6, -1e6, 6e-8]]).astype(np.float32)
+    for v in vals:
+        want = np.array([v], dtype=np.float32).astype(np.float16).view(np.uint16)[0]
+        assert dccl_lib.dccl_float_to_half(float(v)) == int(want), v
+
+
+def test_bf16_conversion_round_to_nearest_even(dccl_lib):
+    rng = np.random.default_rng(1)
+    vals = rng.normal(0, 10, 3000).astype(np.float32)
+    want = oracle.f32_to_bf16(vals)
+    for v, w in zip(vals, want):
+        assert dccl_lib.dccl_float_to_bf16(float(v)) == int(w)
+        assert dccl_lib.dccl_bf16_to_float(int(w)) == float(oracle.bf16_to_f32(np.array([w]))[0])
+
+
+def test_config_file_env_and_layout(dccl_lib, tmp_path, monkeypatch):
+    cfg = tmp_path / "derecho.cfg"
+    cfg.write_text("# comment\n[DERECHO]\nlocal_id = 3\ncontact_ip = 127.0.0.1\ncontact_port = 23580 # trailing\n"
+                   "[DCCL]\nallreduce_algorithm = rabenseifner\n[LOGGER]\ndefault_log_level = info\n")
+    (tmp_path / "layout.json").write_text('[{"layout":[{"min_nodes_by_shard": ["8"], "max_nodes_by_shard": ["8"]}]}]')
+    monkeypatch.chdir(tmp_path)
+    monkeypatch.delenv("DCCL_ALLREDUCE_ALGORITHM", raising=False)
+    dccl_lib.dccl_config_reload()
+    out = ctypes.create_string_buffer(64)
+    assert dccl_lib.dccl_config_get(b"DCCL/allreduce_algorithm", out, 64) == 1 and out.value == b"rabenseifner"
+    assert dccl_lib.dccl_config_get(b"DERECHO/contact_port", out, 64) == 1 and out.value == b"23580"
+    assert dccl_lib.dccl_config_get(b"DERECHO/nothing", out, 64) == 0
+    # environment beats the file
+    monkeypatch.setenv("DCCL_ALLREDUCE_ALGORITHM", "ring")
+    assert dccl_lib.dccl_config_get(b"DCCL/allreduce_algorithm", out, 64) == 1 and out.value == b"ring"
+    assert dccl_lib.dccl_config_parse_world((tmp_path / "layout.json").read_text().encode()) == 8
+    assert dccl_lib.dccl_config_parse_world(b"{}") == 0
+    monkeypatch.chdir(os.path.dirname(__file__))
+    dccl_lib.dccl_config_reload()
+
+
+def test_timestamp_file_format(dccl_lib, tmp_path):
+    dccl_lib.dccl_timestamp_clear()
+    for i in range(5000):   # more than the first buffer: exercises growth
+        dccl_lib.dccl_timestamp_log(1001001 + (i % 2) * 99, 3, i)
+    assert dccl_lib.dccl_timestamp_size() == 5000
+    path = tmp_path / "x.tt"
+    dccl_lib.dccl_timestamp_flush(str(path).encode(), 1)
+    assert dccl_lib.dccl_timestamp_size() == 0
+    lines = path.read_text().splitlines()
+    assert lines[0] == "# number of entries:5000"
+    assert lines[1] == "# tag rank extra tsns"
+    declared, rows = tt.read_tt(str(path))
+    assert declared == 5000 and len(rows) == 5000
+    assert rows[0][:3] == (1001001, 3, 0) and rows[1][:3] == (1001100, 3, 1)
+    ts = [r[3] for r in rows]
+    assert all(b >= a for a, b in zip(ts, ts[1:]))
+    assert len(tt.durations(rows, 1001001, 1001100)) == 2500
+
+
+def test_tuner_table_and_file_override(dccl_lib):
+    algo = ctypes.create_string_buffer(32)
+    ctas = ctypes.c_int()
+
+    def choose(coll, n, nbytes, nvls=1):
+        assert dccl_lib.dccl_tuner_choose(coll.encode(), n, nbytes, nvls, algo, 32, ctypes.byref(ctas)) == 0
+        return algo.value.decode(), ctas.value
+
+    assert choose("allreduce", 8, 1024)[0] == "oneshot"
+    assert choose("allreduce", 8, 1 << 30)[0] == "nvls"
+    assert choose("allreduce", 8, 1 << 30, nvls=0)[0] == "twoshot"     # no multicast: peer-to-peer variant
+    assert dccl_lib.dccl_tuner_choose(b"bogus", 8, 1, 1, algo, 32, ctypes.byref(ctas)) == -1
+    text = b"# my table\nallreduce 8 4k ring 4\nallreduce * inf rabenseifner 12\nnot a rule\nallreduce 8 1m twoshot 999\n"
+    assert dccl_lib.dccl_tuner_load_text(text) == 2
+    assert choose("allreduce", 8, 1000) == ("ring", 4)
+    assert choose("allreduce", 8, 100000) == ("rabenseifner", 12)
+    assert choose("allreduce", 4, 10) == ("rabenseifner", 12)
+    assert choose("reducescatter", 8, 10)[0] == "twoshot"              # untouched collective keeps the built-in rows
+
+
+def test_oracle_integer_semantics():
+    a = np.array([100, -100, 7], dtype=np.int8)
+    b = np.array([100, -100, -2], dtype=np.int8)
+    assert list(oracle.fold([a, b], "sum")) == [-56, 56, 5]            # wraps like the kernels
+    assert list(oracle.fold([a, b], "prod")) == [16, 16, -14]
+    assert list(oracle.fold([np.array([-7], np.int32), np.array([2], np.int32)], "avg")) == [-2]   # truncates toward zero

@@ -1,0 +1,163 @@
+"""One rank of a multi-GPU test: device collectives on torch tensors, every variant, checked against
+a fold computed on the CPU from the seeds of all ranks. Prints 'OK <cases>' or the failures."""
+import argparse
+import os
+import sys
+
+import numpy as np
+import torch
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))))
+from dccl_b200 import Communicator, group_end, group_start  # noqa: E402
+from dccl_b200.utils import oracle  # noqa: E402
+
+TORCH = {"float32": torch.float32, "bfloat16": torch.bfloat16, "float16": torch.float16, "float64": torch.float64,
+         "int32": torch.int32, "int64": torch.int64, "int8": torch.int8, "uint8": torch.uint8}
+
+
+def to_torch(arr, name, dev):
+    if name == "bfloat16":
+        return torch.from_numpy(arr.view(np.int16).copy()).view(torch.bfloat16).to(dev)
+    return torch.from_numpy(arr.copy()).to(dev)
+
+
+def to_numpy(t, name):
+    if name == "bfloat16":
+        return t.cpu().view(torch.int16).numpy().view(np.uint16)
+    return t.cpu().numpy()
+
+
+def close(got, want, name, world):
+    rtol, atol = oracle.tolerances(name, world)
+    if rtol == 0.0:
+        return np.array_equal(got, want)
+    if name == "bfloat16":
+        got, want = oracle.bf16_to_f32(got), oracle.bf16_to_f32(want)
+    return np.allclose(got.astype(np.float64), want.astype(np.float64), rtol=rtol, atol=atol)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--suite", default="basic")
+    args = ap.parse_args()
+    local = int(os.environ.get("DCCL_LOCAL_DEVICE", os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    comm = Communicator(device=local)
+    rank, world = comm.rank, comm.world
+    failures, cases = [], 0
+
+    def check(ok, what):
+        nonlocal cases
+        cases += 1
+        if not ok:
+            failures.append(what)
+
+    algos = ["oneshot", "twoshot", "ring", "rabenseifner"] + (["nvls"] if comm.has_multicast else [])
+    if args.suite == "basic":
+        names, counts = ["float32", "bfloat16", "int32", "float16"], [1, 1000, 16384, 300001, 4 << 20]
+    else:   # chunking: staging is made small through DCCL_STAGING_BYTES by the caller
+        names, counts = ["float32", "bfloat16"], [3 << 20, (8 << 20) + 12345]
+    for name in names:
+        for count in counts:
+            ins = [oracle.make_input(name, count, seed=31 * r + count % 101) for r in range(world)]
+            bf = name == "bfloat16"
+            for op in (["sum", "avg", "max"] if args.suite == "basic" else ["sum"]):
+                want = oracle.fold(ins, op, bf16=bf)
+                for algo in algos:
+                    comm.set_algorithm("allreduce", algo)
+                    s = to_torch(ins[rank], name, dev)
+                    r = torch.zeros_like(s)
+                    for _ in range(3):
+                        comm.all_reduce(s, r, op=op)
+                    torch.cuda.synchronize()
+                    used = comm.last_algorithm("allreduce")
+                    check(close(to_numpy(r, name), want, name, world), "all_reduce %s %s %s n=%d (ran %s)" % (algo, name, op, count, used))
+                    comm.all_reduce(s, op=op)   # in place
+                    torch.cuda.synchronize()
+                    check(close(to_numpy(s, name), want, name, world), "all_reduce in place %s %s %s n=%d" % (algo, name, op, count))
+                comm.set_algorithm("allreduce", "auto")
+                # reduce to both ends
+                for root in {0, world - 1}:
+                    for algo in ["twoshot"] + (["nvls"] if comm.has_multicast else []):
+                        comm.set_algorithm("reduce", algo)
+                        s = to_torch(ins[rank], name, dev)
+                        r = torch.zeros_like(s)
+                        comm.reduce(s, r, op=op, root=root)
+                        torch.cuda.synchronize()
+                        check(rank != root or close(to_numpy(r, name), want, name, world), "reduce %s %s %s n=%d root=%d" % (algo, name, op, count, root))
+                # reduce-scatter (count must split)
+                per = count // world
+                if per:
+                    wantrs = want[rank * per:(rank + 1) * per]
+                    for algo in ["twoshot", "ring"] + (["nvls"] if comm.has_multicast else []):
+                        comm.set_algorithm("reducescatter", algo)
+                        s = to_torch(ins[rank][:per * world], name, dev)
+                        r = torch.zeros(per, dtype=s.dtype, device=dev)
+                        comm.reduce_scatter(s, r, op=op)
+                        torch.cuda.synchronize()
+                        check(close(to_numpy(r, name), wantrs, name, world), "reduce_scatter %s %s %s n=%d" % (algo, name, op, per))
+            per = max(1, count // world)
+            full = np.concatenate([x[:per] for x in ins])
+            for algo in ["twoshot", "ring"] + (["nvls"] if comm.has_multicast else []):
+                comm.set_algorithm("allgather", algo)
+                s = to_torch(ins[rank][:per], name, dev)
+                r = torch.zeros(per * world, dtype=s.dtype, device=dev)
+                comm.all_gather(s, r)
+                torch.cuda.synchronize()
+                check(np.array_equal(to_numpy(r, name), full), "all_gather %s %s n=%d" % (algo, name, per))
+            for root in {0, world - 1}:
+                for algo in ["oneshot", "twoshot"] + (["nvls"] if comm.has_multicast else []):
+                    comm.set_algorithm("broadcast", algo)
+                    b = to_torch(ins[rank], name, dev)
+                    comm.broadcast(b, root=root)
+                    torch.cuda.synchronize()
+                    check(np.array_equal(to_numpy(b, name), ins[root]), "broadcast %s %s n=%d root=%d" % (algo, name, count, root))
+
+    # symmetric memory: zero-copy switch reduction
+    if comm.has_multicast and args.suite == "basic":
+        for name in ["float32", "bfloat16"]:
+            count = 1 << 20
+            ins = [oracle.make_input(name, count, seed=900 + r) for r in range(world)]
+            want = oracle.fold(ins, "avg", bf16=name == "bfloat16")
+            t = comm.symmetric_empty(count, TORCH[name], local)
+            t.copy_(to_torch(ins[rank], name, dev))
+            torch.cuda.synchronize()
+            comm.set_algorithm("allreduce", "nvls")
+            comm.all_reduce(t, op="avg")
+            torch.cuda.synchronize()
+            check(close(to_numpy(t, name), want, name, world), "symmetric all_reduce %s" % name)
+            comm.free_symmetric(t)
+        comm.set_algorithm("allreduce", "auto")
+
+    # send / recv: grouped ring with 8 MB messages (longer than the FIFO), then a plain pair
+    msg = torch.full((2 << 20,), float(rank), dtype=torch.float32, device=dev)
+    got = torch.zeros_like(msg)
+    for _ in range(2):
+        group_start()
+        comm.send(msg, (rank + 1) % world)
+        comm.recv(got, (rank - 1) % world)
+        group_end()
+    torch.cuda.synchronize()
+    check(bool((got == float((rank - 1) % world)).all()), "grouped ring send/recv")
+    small = torch.full((1000,), float(rank + 10), dtype=torch.float32, device=dev)
+    if rank == 0:
+        comm.send(small, 1)
+    elif rank == 1:
+        comm.recv(small, 0)
+        torch.cuda.synchronize()
+        check(bool((small == 10.0).all()), "plain send/recv")
+    torch.cuda.synchronize()
+    code, emsg = comm.last_error()
+    check(code == 0, "async error: " + emsg)
+    mc = comm.has_multicast
+    launches = comm.launches
+    comm.finalize()
+    if failures:
+        print("FAILED %d of %d on rank %d: %s" % (len(failures), cases, rank, "; ".join(failures[:10])))
+        sys.exit(1)
+    print("OK %d multicast=%d launches=%d" % (cases, int(mc), launches))
+
+
+if __name__ == "__main__":
+    main()
