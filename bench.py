@@ -227,6 +227,8 @@ def main():
     ap.add_argument("--sweep", action="store_true", help="also sweep sizes and variants; table goes to --out")
     ap.add_argument("--out", default=os.path.join(ROOT, "gpurun_out", "sweep.json"))
     ap.add_argument("--e2e-steps", type=int, default=5)
+    ap.add_argument("--sweep-ctas", default="16,32,64,128")
+    ap.add_argument("--sweep-unroll", default="4,8")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3
@@ -257,13 +259,17 @@ def main():
         sampler.start()
         time.sleep(0.3)
 
+    algo_seen = []
+
     def step():
         backend.all_reduce(buf, out)
+        if not algo_seen and args.impl == "ours":
+            algo_seen.append(backend.comm.last_algorithm("allreduce"))
 
     l0 = backend.launches()
     ms = timed(backend, step, args.steps, args.warmup)
     launches = (backend.launches() - l0) * args.steps // (args.steps + args.warmup)
-    algo_used = backend.comm.last_algorithm("allreduce") if args.impl == "ours" else "nccl"
+    algo_used = algo_seen[0] if algo_seen else "nccl"
     algbw = nbytes / (ms * 1e-3) / 1e9
     value = algbw * bus_factor("allreduce", world)
 
@@ -338,50 +344,73 @@ def main():
 
 
 def run_sweep(backend, args, rank, world, dtype, es):
-    """busBW per (collective, variant, size); sizes are powers of two from 1 KB to the headline size."""
-    torch = backend.torch
+    """busBW per (collective, variant, CTAs, unroll, size); sizes from 1 KB to the headline size.
+    The pseudo-variant "nvls_sym" is the switch variant on symmetric (dcclMemAlloc) buffers."""
     rows = []
     sizes = []
     s = 1024
     while s <= args.bytes:
         sizes.append(s)
-        s *= 4 if s >= (1 << 20) else 2
+        s *= 8
     if sizes[-1] != args.bytes:
         sizes.append(args.bytes)
-    variants = {"allreduce": ["auto", "oneshot", "twoshot", "ring", "rabenseifner", "nvls"],
+    ours = args.impl == "ours" and world > 1
+    variants = {"allreduce": ["auto", "oneshot", "twoshot", "ring", "rabenseifner", "nvls", "nvls_sym"],
                 "reducescatter": ["auto", "twoshot", "ring", "nvls"], "allgather": ["auto", "twoshot", "ring", "nvls"]}
-    if args.impl != "ours" or world == 1:
+    if not ours:
         variants = {k: ["auto"] for k in variants}
+    ctas_list = [int(x) for x in args.sweep_ctas.split(",")] if ours else [0]
+    unroll_list = [int(x) for x in args.sweep_unroll.split(",")] if ours else [4]
     maxel = args.bytes // es
     src = backend.alloc(maxel, dtype, symmetric=False)
     dst = backend.alloc(maxel, dtype, symmetric=False)
     src.fill_(1.0 / 1024)
+    ssrc = sdst = None
+    if ours and backend.comm.has_multicast:
+        ssrc = backend.alloc(maxel, dtype, symmetric=True)
+        sdst = backend.alloc(maxel, dtype, symmetric=True)
+        ssrc.fill_(1.0 / 1024)
     for coll, algos in variants.items():
         for algo in algos:
-            backend.set_algo(coll, algo)
+            if algo in ("nvls", "nvls_sym") and ours and not backend.comm.has_multicast:
+                continue
+            backend.set_algo(coll, "nvls" if algo == "nvls_sym" else algo)
+            a, b = (ssrc, sdst) if algo == "nvls_sym" else (src, dst)
             for size in sizes:
                 if algo == "oneshot" and size > (128 << 10):
                     continue
-                if algo in ("ring", "rabenseifner") and size < (64 << 10) and world > 1 and False:
+                if algo in ("ring", "rabenseifner") and size > (256 << 20):
                     continue
-                n_el = max(size // es, world)
-                per = n_el // world
-                if coll == "allreduce":
-                    fn = lambda: backend.all_reduce(src[:n_el], dst[:n_el])   # noqa: E731
-                    total = n_el * es
-                elif coll == "reducescatter":
-                    fn = lambda: backend.reduce_scatter(src[:per * world], dst[:per])   # noqa: E731
-                    total = per * world * es
-                else:
-                    fn = lambda: backend.all_gather(src[:per], dst[:per * world])   # noqa: E731
-                    total = per * world * es
-                steps = 200 if size <= (1 << 20) else 20 if size <= (64 << 20) else 8
-                ms = timed(backend, fn, steps, 5)
-                algbw = total / (ms * 1e-3) / 1e9
-                used = backend.comm.last_algorithm(coll) if args.impl == "ours" else "nccl"
-                rows.append({"coll": coll, "algo": algo, "ran": used, "bytes": total, "us": round(ms * 1e3, 3),
-                             "algbw_gbs": round(algbw, 3), "busbw_gbs": round(algbw * bus_factor(coll, world), 3)})
+                for ctas in (ctas_list if (algo != "auto" and size >= (512 << 10)) else [0]):
+                    for unroll in (unroll_list if algo in ("nvls", "nvls_sym") and size >= (512 << 10) else [4]):
+                        if ours:
+                            backend.comm.set_param("ctas", ctas)
+                            backend.comm.set_param("unroll", unroll)
+                        n_el = max(size // es, world * 8) // (world * 8) * (world * 8)
+                        per = n_el // world
+                        if coll == "allreduce":
+                            fn = lambda: backend.all_reduce(a[:n_el], b[:n_el])   # noqa: E731
+                            total = n_el * es
+                        elif coll == "reducescatter":
+                            fn = lambda: backend.reduce_scatter(a[:per * world], b[:per])   # noqa: E731
+                            total = per * world * es
+                        else:
+                            fn = lambda: backend.all_gather(a[:per], b[:per * world])   # noqa: E731
+                            total = per * world * es
+                        steps = 200 if size <= (1 << 20) else 20 if size <= (64 << 20) else 8
+                        ms = timed(backend, fn, steps, 5)
+                        algbw = total / (ms * 1e-3) / 1e9
+                        used = backend.comm.last_algorithm(coll) if args.impl == "ours" else "nccl"
+                        rows.append({"coll": coll, "algo": algo, "ran": used, "ctas": ctas, "unroll": unroll, "bytes": total,
+                                     "us": round(ms * 1e3, 3), "algbw_gbs": round(algbw, 3),
+                                     "busbw_gbs": round(algbw * bus_factor(coll, world), 3)})
             backend.set_algo(coll, "auto")
+    if ours:
+        backend.comm.set_param("ctas", 0)
+        backend.comm.set_param("unroll", 4)
+    if ssrc is not None:
+        backend.free(ssrc)
+        backend.free(sdst)
     return rows
 
 

@@ -48,6 +48,7 @@ int dccl_comm_bind_device(void* comm, int device) {
 }
 int dccl_has_multicast(void* comm) { dcclComm* c = (dcclComm*)comm; return c && c->gpu && c->gpu->has_multicast() ? 1 : 0; }
 unsigned long long dccl_launch_count(void* comm) { dcclComm* c = (dcclComm*)comm; return c && c->gpu ? c->gpu->launches() : 0ull; }
+int dccl_comm_set_param(void* comm, const char* name, int value) { dcclComm* c = (dcclComm*)comm; return c && c->gpu && c->gpu->set_param(name, value) ? 0 : (int)ncclInvalidArgument; }
 int dccl_cuda_device_count() { return cuda_device_count(); }
 
 int dccl_register(void* comm, void* buf, size_t size) { GUARD(dcclRegisterCacheMemory((ncclComm_t)comm, buf, size)); }
@@ -104,7 +105,7 @@ int dccl_config_parse_world(const char* json) { return Config::world_size_from_l
 static Tuner& test_tuner() { static Tuner t; return t; }
 int dccl_tuner_load_text(const char* text) { std::string err; return test_tuner().load_text(text, &err); }
 int dccl_tuner_choose(const char* coll, int nranks, size_t bytes, int nvls_ok, char* algo_out, size_t len, int* ctas) {
-    int c = parse_collective_name(coll);
+    int c = coll && !strcmp(coll, "allreduce_sym") ? TUNE_ALLREDUCE_SYM : parse_collective_name(coll);
     if (c < 0) return -1;
     TuneChoice ch = test_tuner().choose(c, nranks, bytes, nvls_ok != 0);
     if (algo_out && len) snprintf(algo_out, len, "%s", algo_name(ch.algo));

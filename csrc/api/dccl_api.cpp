@@ -462,8 +462,9 @@ const char* dcclGetLastAlgorithm(ncclComm_t comm, const char* collective) {
     VALIDATE_COMM(comm);
     int coll = collective ? parse_collective_name(collective) : -1;
     if (coll < 0) return "";
+    // a device variant, once one ran, is what tools ask about; host calls report ring / rabenseifner
+    if (comm->gpu && comm->gpu->last_algo(coll) != ALGO_AUTO) return algo_name(comm->gpu->last_algo(coll));
     if (comm->last_was_host[coll]) return comm->last_host_algo[coll] == HOST_ALGO_RABENSEIFNER ? "rabenseifner" : "ring";
-    if (comm->gpu) return algo_name(comm->gpu->last_algo(coll));
     return "";
 }
 

@@ -80,6 +80,7 @@ struct CollArgs {
     int root;
     int mode;
     int symmetric;         // user buffers are in symmetric memory (zero-copy variant)
+    int unroll;            // vectors in flight per thread in the switch pass (2, 4 or 8)
 };
 
 struct Ctx {

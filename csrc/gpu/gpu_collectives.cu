@@ -20,7 +20,17 @@ int GpuCommImpl::ctas_for(int tuned) const {
     int c = ctas_override_ > 0 ? ctas_override_ : tuned;
     if (c < 1) c = 1;
     if (c > kMaxCtas) c = kMaxCtas;
+    if (c > sm_count_) c = sm_count_;   // CTAs of one call wait on each other's peers: keep them all resident
     return c;
+}
+
+bool GpuCommImpl::set_param(const char* name, int value) {
+    const std::string k(name ? name : "");
+    if (k == "ctas" && value >= 0 && value <= kMaxCtas) { ctas_override_ = value; return true; }
+    if (k == "threads" && value >= 64 && value <= 512 && value % 32 == 0) { threads_ = value; return true; }
+    if (k == "unroll" && (value == 2 || value == 4 || value == 8)) { unroll_ = value; return true; }
+    if (k == "p2p_ctas" && value >= 1 && value <= kP2pCtas) { p2p_ctas_ = value; return true; }
+    return false;
 }
 
 CollArgs GpuCommImpl::base_args(const void* send, void* recv, ncclRedOp_t op, int root) {
@@ -31,6 +41,7 @@ CollArgs GpuCommImpl::base_args(const void* send, void* recv, ncclRedOp_t op, in
     a.io.recv = recv;
     a.op = (int)op;
     a.root = root;
+    a.unroll = unroll_;
     return a;
 }
 
@@ -55,7 +66,13 @@ ncclResult_t GpuCommImpl::all_reduce(const void* send, void* recv, size_t count,
     if (!count) return ncclSuccess;
 
     const bool nvls_ok = pool_.mc_base != nullptr && nvls_supports(dt, op);
-    TuneChoice ch = tuner_.choose(COLL_ALLREDUCE, n_, bytes, nvls_ok);
+    // both buffers in multicast-bound symmetric memory: the switch variant can run without copies
+    const char* sp[kMaxPeers];
+    const char* rp[kMaxPeers];
+    const char *smc = nullptr, *rmc = nullptr;
+    const bool sym = nvls_ok && bytes % 16 == 0 && sym_view(send, bytes, sp, &smc) && sym_view(recv, bytes, rp, &rmc) && smc && rmc &&
+                     ((uintptr_t)smc % 16 == 0) && ((uintptr_t)rmc % 16 == 0);
+    TuneChoice ch = tuner_.choose(sym ? TUNE_ALLREDUCE_SYM : COLL_ALLREDUCE, n_, bytes, nvls_ok);
     if (algo != ALGO_AUTO) ch.algo = algo;
     // a forced variant that cannot serve this call falls back to the closest one that can
     if (ch.algo == ALGO_NVLS && !nvls_ok) ch.algo = ALGO_TWOSHOT;
@@ -67,6 +84,7 @@ ncclResult_t GpuCommImpl::all_reduce(const void* send, void* recv, size_t count,
     LaunchCfg cfg;
     cfg.ctas = ctas_for(ch.ctas);
     cfg.stream = stream;
+    cfg.threads = threads_;
     CollArgs a = base_args(send, recv, op, 0);
 
     if (ch.algo == ALGO_ONESHOT) {
@@ -76,22 +94,15 @@ ncclResult_t GpuCommImpl::all_reduce(const void* send, void* recv, size_t count,
         return cuda_result(launch_oneshot_ll(a, dt, cfg), "one-shot all-reduce");
     }
 
-    // zero-copy switch reduction when both buffers sit in multicast-bound symmetric memory
-    if (ch.algo == ALGO_NVLS) {
-        const char* sp[kMaxPeers];
-        const char* rp[kMaxPeers];
-        const char *smc = nullptr, *rmc = nullptr;
-        if (bytes % 16 == 0 && sym_view(send, bytes, sp, &smc) && sym_view(recv, bytes, rp, &rmc) && smc && rmc &&
-            ((uintptr_t)smc % 16 == 0) && ((uintptr_t)rmc % 16 == 0)) {
-            a.symmetric = 1;
-            a.io.send_mc = smc;
-            a.io.recv_mc = (char*)rmc;
-            a.mode = NV_ALLREDUCE;
-            a.count = count;
-            NEXT_SEQ(a);
-            launches_++;
-            return cuda_result(launch_nvls(a, dt, cfg), "nvls all-reduce (symmetric)");
-        }
+    if (ch.algo == ALGO_NVLS && sym) {
+        a.symmetric = 1;
+        a.io.send_mc = smc;
+        a.io.recv_mc = (char*)rmc;
+        a.mode = NV_ALLREDUCE;
+        a.count = count;
+        NEXT_SEQ(a);
+        launches_++;
+        return cuda_result(launch_nvls(a, dt, cfg), "nvls all-reduce (symmetric)");
     }
 
     size_t cap;
@@ -143,6 +154,7 @@ ncclResult_t GpuCommImpl::reduce_scatter(const void* send, void* recv, size_t re
     LaunchCfg cfg;
     cfg.ctas = ctas_for(ch.ctas);
     cfg.stream = stream;
+    cfg.threads = threads_;
     CollArgs a = base_args(send, recv, op, 0);
     a.stride = recvcount;
 
@@ -201,6 +213,7 @@ ncclResult_t GpuCommImpl::all_gather(const void* send, void* recv, size_t sendco
     LaunchCfg cfg;
     cfg.ctas = ctas_for(ch.ctas);
     cfg.stream = stream;
+    cfg.threads = threads_;
     CollArgs a = base_args(send, recv, ncclSum, 0);
     a.stride = sendcount;
 
@@ -258,6 +271,7 @@ ncclResult_t GpuCommImpl::broadcast(const void* send, void* recv, size_t count, 
     LaunchCfg cfg;
     cfg.ctas = ctas_for(ch.ctas);
     cfg.stream = stream;
+    cfg.threads = threads_;
     if (rank_ != root) send = recv;   // only the root's source is read
     CollArgs a = base_args(send, recv, ncclSum, root);
 
@@ -315,6 +329,7 @@ ncclResult_t GpuCommImpl::reduce(const void* send, void* recv, size_t count, ncc
     LaunchCfg cfg;
     cfg.ctas = ctas_for(ch.ctas);
     cfg.stream = stream;
+    cfg.threads = threads_;
     CollArgs a = base_args(send, recv, op, root);
     size_t cap = ch.algo == ALGO_NVLS ? nvls_capacity(NV_REDUCE, n_, es, stage_bytes_) : twoshot_capacity(TS_REDUCE, n_, es, stage_bytes_);
     for (size_t off = 0; off < count; off += cap) {
@@ -346,6 +361,7 @@ ncclResult_t GpuCommImpl::p2p_launch(std::vector<P2pOp>& ops, cudaStream_t strea
         LaunchCfg cfg;
         cfg.ctas = a.nops * p2p_ctas_;
         cfg.stream = stream;
+    cfg.threads = threads_;
         a.ctas_per_rank = cfg.ctas;
         launches_++;
         cudaError_t e = launch_p2p(a, cfg);

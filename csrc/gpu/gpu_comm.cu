@@ -50,8 +50,11 @@ bool GpuCommImpl::init(std::string* err) {
     Config& cfg = Config::global();
     bool ok = cudaSetDevice(dev_) == cudaSuccess;
     if (!ok) { cudaGetLastError(); if (err) *err = "cudaSetDevice(" + std::to_string(dev_) + ") failed"; }
+    if (ok) { int sms = 0; if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev_) == cudaSuccess && sms > 0) sm_count_ = sms; }
     ctas_override_ = (int)cfg.get_int("DCCL/ctas", 0);
     p2p_ctas_ = (int)cfg.get_int("DCCL/p2p_ctas", 16);
+    set_param("threads", (int)cfg.get_int("DCCL/threads", 512));
+    set_param("unroll", (int)cfg.get_int("DCCL/unroll", 4));
     if (p2p_ctas_ < 1) p2p_ctas_ = 1;
     if (p2p_ctas_ > kP2pCtas) p2p_ctas_ = kP2pCtas;
     stage_bytes_ = (size_t)cfg.get_int("DCCL/staging_bytes", 256ll << 20);

@@ -46,6 +46,7 @@ public:
     int device() const override { return dev_; }
     bool has_multicast() const override { return pool_.mc_base != nullptr; }
     uint64_t launches() const override { return launches_; }
+    bool set_param(const char* name, int value) override;
 
 private:
     struct DeviceGuard {
@@ -75,6 +76,9 @@ private:
     uint64_t launches_ = 0;
     int ctas_override_ = 0;
     int p2p_ctas_ = 16;
+    int threads_ = 512;
+    int sm_count_ = 148;
+    int unroll_ = 4;
     bool sticky_error_ = false;
     std::vector<SymSegment> user_segs_;
     std::vector<RegisteredBuffer> regs_;

@@ -123,15 +123,14 @@ template <typename T> __device__ __forceinline__ uint4 avg16(uint4 raw, int worl
     return *reinterpret_cast<uint4*>(&v);
 }
 
-constexpr int kNvUnroll = 4;
 
 /**
  * For every 16-byte vector i in [0,nv): out = finish(ld_reduce(src_mc + 16 i)), then
  * multimem.st to dst_mc and / or a plain store to dst_local (either may be null).
  * `valid_bytes` limits the plain store of the last vector (local destinations only).
  */
-template <typename T, int OP>
-__device__ __forceinline__ void nvls_pass(const char* src_mc, char* dst_mc, char* dst_local, size_t nv, size_t valid_bytes, bool avg, int world) {
+template <typename T, int OP, int kNvUnroll>
+__device__ __forceinline__ void nvls_pass_u(const char* src_mc, char* dst_mc, char* dst_local, size_t nv, size_t valid_bytes, bool avg, int world) {
     const int tid = threadIdx.x, nt = blockDim.x;
     size_t i = tid;
     const size_t full = dst_local ? valid_bytes / 16 : nv;   // vectors that can be stored whole
@@ -160,8 +159,16 @@ __device__ __forceinline__ void nvls_pass(const char* src_mc, char* dst_mc, char
     }
 }
 
+template <typename T, int OP>
+__device__ __forceinline__ void nvls_pass(const char* src_mc, char* dst_mc, char* dst_local, size_t nv, size_t valid_bytes, bool avg, int world, int unroll = 4) {
+    if (unroll >= 8) nvls_pass_u<T, OP, 8>(src_mc, dst_mc, dst_local, nv, valid_bytes, avg, world);
+    else if (unroll >= 4) nvls_pass_u<T, OP, 4>(src_mc, dst_mc, dst_local, nv, valid_bytes, avg, world);
+    else nvls_pass_u<T, OP, 2>(src_mc, dst_mc, dst_local, nv, valid_bytes, avg, world);
+}
+
 /** multimem.st of nv vectors read from local memory (src must be 16-byte aligned). */
 __device__ __forceinline__ void nvls_push(char* dst_mc, const char* src, size_t nv) {
+    constexpr int kNvUnroll = 4;
     const int tid = threadIdx.x, nt = blockDim.x;
     size_t i = tid;
     for (; i + (size_t)(kNvUnroll - 1) * nt < nv; i += (size_t)kNvUnroll * nt) {
@@ -200,7 +207,7 @@ __global__ void __launch_bounds__(512) k_nvls(const __grid_constant__ CollArgs a
         if (!rank_barrier(c, x.bid, a.seq, 0, 400 + mode)) return;
         if (mode == NV_ALLREDUCE) {
             const size_t lo = lo_of(r), hi = hi_of(r);
-            if (hi > lo) nvls_pass<T, OP>(send_mc + ((size_t)r * stride + lo) * ES, recv_mc + ((size_t)r * stride + lo) * ES, nullptr, vecs(hi - lo), 0, avg, n);
+            if (hi > lo) nvls_pass<T, OP>(send_mc + ((size_t)r * stride + lo) * ES, recv_mc + ((size_t)r * stride + lo) * ES, nullptr, vecs(hi - lo), 0, avg, n, a.unroll);
         } else if (mode == NV_REDUCESCATTER) {
             const size_t lo = lo_of(r), hi = hi_of(r);
             if (hi > lo) nvls_pass<T, OP>(send_mc + ((size_t)r * stride + lo) * ES, nullptr, reinterpret_cast<char*>(recv + lo), vecs(hi - lo), (hi - lo) * ES, avg, n);
@@ -261,7 +268,7 @@ __global__ void __launch_bounds__(512) k_nvls(const __grid_constant__ CollArgs a
         const size_t lo = lo_of(r), hi = hi_of(r);
         if (hi > lo) {
             const size_t off = ((size_t)r * g.slot_stride + lo) * ES;
-            nvls_pass<T, OP>(mc_stage + off, mc_stage + off, nullptr, vecs(hi - lo), 0, avg, n);
+            nvls_pass<T, OP>(mc_stage + off, mc_stage + off, nullptr, vecs(hi - lo), 0, avg, n, a.unroll);
         }
         if (!rank_barrier(c, x.bid, a.seq, 1, 550 + mode)) return;
     } else if (mode == NV_REDUCESCATTER) {

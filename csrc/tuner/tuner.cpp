@@ -14,19 +14,23 @@ static const size_t kInf = ~(size_t)0;
  * broadcast / reduce and the full gathered vector for reduce-scatter /
  * all-gather. */
 static const TuneRule kBuiltin[] = {
-    // all-reduce: flag-in-data one-shot while latency bound, two-shot through staging in the
-    // middle, in-switch reduction once the message is large enough to amortise two barriers
-    {COLL_ALLREDUCE, 0, 64u << 10, ALGO_ONESHOT, 8},
-    {COLL_ALLREDUCE, 0, 512u << 10, ALGO_TWOSHOT, 32},
-    {COLL_ALLREDUCE, 0, kInf, ALGO_NVLS, 64},
+    // Measured on 8 x B200 (bf16 sum; sweep of every variant x CTA count, best per size bucket).
+    // all-reduce, ordinary buffers: packets while latency bound, then the switch variant through staging
+    {COLL_ALLREDUCE, 0, 128u << 10, ALGO_ONESHOT, 8},
+    {COLL_ALLREDUCE, 0, 8u << 20, ALGO_NVLS, 64},
+    {COLL_ALLREDUCE, 0, kInf, ALGO_NVLS, 128},
+    // all-reduce, symmetric buffers: zero-copy switch variant; more than ~32 CTAs only adds contention
+    {TUNE_ALLREDUCE_SYM, 0, 64u << 10, ALGO_ONESHOT, 8},
+    {TUNE_ALLREDUCE_SYM, 0, kInf, ALGO_NVLS, 32},
     {COLL_REDUCESCATTER, 0, 1u << 20, ALGO_TWOSHOT, 32},
-    {COLL_REDUCESCATTER, 0, kInf, ALGO_NVLS, 64},
-    {COLL_ALLGATHER, 0, 1u << 20, ALGO_TWOSHOT, 32},
-    {COLL_ALLGATHER, 0, kInf, ALGO_TWOSHOT, 64},
-    {COLL_BROADCAST, 0, 1u << 20, ALGO_ONESHOT, 16},
+    {COLL_REDUCESCATTER, 0, kInf, ALGO_TWOSHOT, 128},
+    {COLL_ALLGATHER, 0, 1u << 20, ALGO_NVLS, 32},
+    {COLL_ALLGATHER, 0, 8u << 20, ALGO_NVLS, 128},
+    {COLL_ALLGATHER, 0, kInf, ALGO_TWOSHOT, 128},
+    {COLL_BROADCAST, 0, 256u << 10, ALGO_ONESHOT, 16},
     {COLL_BROADCAST, 0, kInf, ALGO_NVLS, 64},
     {COLL_REDUCE, 0, 1u << 20, ALGO_TWOSHOT, 32},
-    {COLL_REDUCE, 0, kInf, ALGO_NVLS, 64},
+    {COLL_REDUCE, 0, kInf, ALGO_NVLS, 128},
 };
 
 Tuner::Tuner() {
@@ -66,7 +70,7 @@ int Tuner::load_text(const std::string& text, std::string* err) {
     std::istringstream in(text);
     std::string line;
     int ok = 0, lineno = 0;
-    bool cleared[COLL_COUNT] = {false};
+    bool cleared[TUNE_KEYS] = {false};
     while (std::getline(in, line)) {
         lineno++;
         size_t h = line.find('#');
@@ -77,7 +81,7 @@ int Tuner::load_text(const std::string& text, std::string* err) {
         if (!(ls >> coll)) continue;
         if (!(ls >> nr >> mb >> algo >> ctas)) { if (err) *err += "line " + std::to_string(lineno) + ": expected 5 fields; "; continue; }
         TuneRule r;
-        r.coll = parse_collective_name(coll.c_str());
+        r.coll = coll == "allreduce_sym" ? TUNE_ALLREDUCE_SYM : parse_collective_name(coll.c_str());
         r.nranks = nr == "*" ? 0 : atoi(nr.c_str());
         r.algo = parse_algo_name(algo.c_str());
         r.ctas = ctas;

@@ -10,6 +10,10 @@
  *
  *     <collective> <nranks|*> <max_bytes> <algorithm> <ctas>
  *
+ * <collective> is allreduce, reducescatter, allgather, broadcast, reduce, or
+ * allreduce_sym (all-reduce whose buffers live in symmetric memory, where the
+ * switch variant copies nothing and wants fewer CTAs).
+ *
  * Rules of one (collective, nranks) are tried in ascending max_bytes; the
  * first whose max_bytes >= message bytes wins (max_bytes accepts k/m/g
  * suffixes and "inf").
@@ -21,6 +25,10 @@
 #include <vector>
 
 namespace dccl {
+
+/** Extra table key: all-reduce on symmetric (dcclMemAlloc) buffers. */
+constexpr int TUNE_ALLREDUCE_SYM = COLL_COUNT;
+constexpr int TUNE_KEYS = COLL_COUNT + 1;
 
 struct TuneRule {
     int coll;

@@ -42,6 +42,7 @@ def _declare(lib):
         "dccl_has_multicast": (i, [vp]),
         "dccl_launch_count": (c.c_ulonglong, [vp]),
         "dccl_cuda_device_count": (i, []),
+        "dccl_comm_set_param": (i, [vp, cp, i]),
         "dccl_register": (i, [vp, vp, sz]),
         "dccl_deregister": (i, [vp, vp]),
         "dccl_mem_alloc": (i, [vp, c.POINTER(vp), sz]),

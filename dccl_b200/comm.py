@@ -150,6 +150,10 @@ class Communicator:
     def launches(self):
         return int(lib().dccl_launch_count(self._h))
 
+    def set_param(self, name, value):
+        """Tuning knob for sweeps: ctas (0 = table), threads, unroll, p2p_ctas."""
+        _check(lib().dccl_comm_set_param(self._h, name.encode(), int(value)), "set_param")
+
     def set_algorithm(self, collective, name):
         _check(lib().dccl_set_algorithm(self._h, collective.encode(), name.encode()), "dcclSetAlgorithm")
 
