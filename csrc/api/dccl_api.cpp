@@ -151,7 +151,10 @@ ncclResult_t dcclGetLastError(ncclComm_t comm, ncclResult_t* async_error, char* 
     if (comm->gpu) r = comm->gpu->async_error(msg, msg_len);
     if (r == ncclSuccess && comm->host_error != ncclSuccess) {
         r = comm->host_error;
-        if (msg && msg_len) snprintf(msg, msg_len, "%s", comm->host_error_msg.c_str());
+        if (msg && msg_len) {
+            if (comm->bs.aborted()) snprintf(msg, msg_len, "%s (rank %d failed or aborted)", comm->host_error_msg.c_str(), comm->bs.failed_rank());
+            else snprintf(msg, msg_len, "%s", comm->host_error_msg.c_str());
+        }
     }
     if (r == ncclSuccess && comm->bs.aborted()) {
         r = ncclRemoteError;
@@ -189,6 +192,9 @@ static ncclResult_t ensure_gpu(dcclComm* c, int device) {
 static HostAlgo host_algo_for(dcclComm* c, int coll) {
     return c->algo[coll] == ALGO_RABENSEIFNER ? HOST_ALGO_RABENSEIFNER : HOST_ALGO_RING;
 }
+
+/** A group that lost a rank or was aborted takes no more work. */
+#define HOST_CALL(c, expr) ((c)->bs.aborted() ? ncclRemoteError : (expr))
 
 static ncclResult_t note_host(dcclComm* c, int coll, ncclResult_t r, const char* what) {
     c->last_was_host[coll] = true;
@@ -261,7 +267,7 @@ ncclResult_t ncclAllReduce(const void* sendbuff, void* recvbuff, size_t count, n
     if (w == ON_HOST) {
         HostAlgo ha = host_algo_for(comm, COLL_ALLREDUCE);
         comm->last_host_algo[COLL_ALLREDUCE] = ha;
-        r = note_host(comm, COLL_ALLREDUCE, comm->cpu->all_reduce(sendbuff, recvbuff, count, dt, op, ha), "ncclAllReduce");
+        r = note_host(comm, COLL_ALLREDUCE, HOST_CALL(comm, comm->cpu->all_reduce(sendbuff, recvbuff, count, dt, op, ha)), "ncclAllReduce");
     } else {
         if ((r = ensure_gpu(comm, dev)) != ncclSuccess) return r;
         comm->last_was_host[COLL_ALLREDUCE] = false;
@@ -286,7 +292,7 @@ ncclResult_t ncclReduceScatter(const void* sendbuff, void* recvbuff, size_t recv
     if (w == ON_HOST) {
         HostAlgo ha = host_algo_for(comm, COLL_REDUCESCATTER);
         comm->last_host_algo[COLL_REDUCESCATTER] = ha;
-        r = note_host(comm, COLL_REDUCESCATTER, comm->cpu->reduce_scatter(sendbuff, recvbuff, recvcount, dt, op, ha), "ncclReduceScatter");
+        r = note_host(comm, COLL_REDUCESCATTER, HOST_CALL(comm, comm->cpu->reduce_scatter(sendbuff, recvbuff, recvcount, dt, op, ha)), "ncclReduceScatter");
     } else {
         if ((r = ensure_gpu(comm, dev)) != ncclSuccess) return r;
         comm->last_was_host[COLL_REDUCESCATTER] = false;
@@ -311,7 +317,7 @@ ncclResult_t ncclAllGather(const void* sendbuff, void* recvbuff, size_t sendcoun
     if (w == ON_HOST) {
         HostAlgo ha = host_algo_for(comm, COLL_ALLGATHER);
         comm->last_host_algo[COLL_ALLGATHER] = ha;
-        r = note_host(comm, COLL_ALLGATHER, comm->cpu->all_gather(sendbuff, recvbuff, sendcount, dt, ha), "ncclAllGather");
+        r = note_host(comm, COLL_ALLGATHER, HOST_CALL(comm, comm->cpu->all_gather(sendbuff, recvbuff, sendcount, dt, ha)), "ncclAllGather");
     } else {
         if ((r = ensure_gpu(comm, dev)) != ncclSuccess) return r;
         comm->last_was_host[COLL_ALLGATHER] = false;
@@ -336,7 +342,7 @@ ncclResult_t ncclBroadcast(const void* sendbuff, void* recvbuff, size_t count, n
     comm->bytes[COLL_BROADCAST] += count * size_of_type(dt);
     ncclResult_t r;
     if (w == ON_HOST) {
-        r = note_host(comm, COLL_BROADCAST, comm->cpu->broadcast(sendbuff, recvbuff, count, dt, root), "ncclBroadcast");
+        r = note_host(comm, COLL_BROADCAST, HOST_CALL(comm, comm->cpu->broadcast(sendbuff, recvbuff, count, dt, root)), "ncclBroadcast");
     } else {
         if ((r = ensure_gpu(comm, dev)) != ncclSuccess) return r;
         comm->last_was_host[COLL_BROADCAST] = false;
@@ -364,7 +370,7 @@ ncclResult_t ncclReduce(const void* sendbuff, void* recvbuff, size_t count, nccl
     comm->bytes[COLL_REDUCE] += count * size_of_type(dt);
     ncclResult_t r;
     if (w == ON_HOST) {
-        r = note_host(comm, COLL_REDUCE, comm->cpu->reduce(sendbuff, recvbuff, count, dt, op, root), "ncclReduce");
+        r = note_host(comm, COLL_REDUCE, HOST_CALL(comm, comm->cpu->reduce(sendbuff, recvbuff, count, dt, op, root)), "ncclReduce");
     } else {
         if ((r = ensure_gpu(comm, dev)) != ncclSuccess) return r;
         comm->last_was_host[COLL_REDUCE] = false;
@@ -413,7 +419,7 @@ ncclResult_t ncclSend(const void* sendbuff, size_t count, ncclDataType_t dt, int
     ncclResult_t r;
     if (!is_device_pointer(sendbuff, &dev)) {
         if (t_group_depth > 0) group_touch(comm);
-        r = note_host(comm, COLL_SENDRECV, comm->cpu->send(sendbuff, bytes, peer), "ncclSend");
+        r = note_host(comm, COLL_SENDRECV, HOST_CALL(comm, comm->cpu->send(sendbuff, bytes, peer)), "ncclSend");
     } else {
         if ((r = ensure_gpu(comm, dev)) != ncclSuccess) return r;
         if (t_group_depth > 0) { group_touch(comm); comm->gpu->group_start(); }
@@ -436,7 +442,7 @@ ncclResult_t ncclRecv(void* recvbuff, size_t count, ncclDataType_t dt, int peer,
     ncclResult_t r;
     if (!is_device_pointer(recvbuff, &dev)) {
         if (t_group_depth > 0) group_touch(comm);
-        r = note_host(comm, COLL_SENDRECV, comm->cpu->recv(recvbuff, bytes, peer), "ncclRecv");
+        r = note_host(comm, COLL_SENDRECV, HOST_CALL(comm, comm->cpu->recv(recvbuff, bytes, peer)), "ncclRecv");
     } else {
         if ((r = ensure_gpu(comm, dev)) != ncclSuccess) return r;
         if (t_group_depth > 0) { group_touch(comm); comm->gpu->group_start(); }

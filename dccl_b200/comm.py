@@ -115,8 +115,24 @@ class Communicator:
         if device is not None:
             _check(lib().dccl_comm_bind_device(self._h, int(device)), "device setup")
 
+    @classmethod
+    def from_handle(cls, handle):
+        """Wrap a native communicator that something else owns (the PyTorch backend); finalize() is then a no-op."""
+        self = cls.__new__(cls)
+        self._h = ctypes.c_void_p(handle)
+        self._borrowed = True
+        self.rank = lib().dccl_rank(self._h)
+        self.world = lib().dccl_world_size(self._h)
+        return self
+
+    def bind_device(self, device):
+        """Set up the device side now (collective: every rank calls it with its own device)."""
+        _check(lib().dccl_comm_bind_device(self._h, int(device)), "device setup")
+
     # -- life cycle ---------------------------------------------------
     def finalize(self):
+        if getattr(self, "_borrowed", False):
+            return
         if self._h:
             h, self._h = self._h, ctypes.c_void_p()
             _check(lib().dccl_comm_finalize(h), "ncclCommFinalize")

@@ -1,0 +1,114 @@
+"""One rank of the process-group test: torch.distributed collectives through backend "dccl" on CPU
+tensors (and on CUDA tensors when --cuda), checked against values computed from the ranks' seeds."""
+import argparse
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))))
+import dccl_b200.parallel.process_group  # noqa: E402,F401  (registers the backend)
+
+
+def tensor_for(rank, n, dtype, dev):
+    g = torch.Generator().manual_seed(1234 + rank)
+    if dtype in (torch.int32, torch.int64):
+        return torch.randint(-1000, 1000, (n,), generator=g, dtype=dtype).to(dev)
+    return (torch.rand(n, generator=g) * 2 - 1).to(dtype).to(dev)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--cuda", action="store_true")
+    ap.add_argument("--ddp", action="store_true")
+    args = ap.parse_args()
+    rank, world = int(os.environ["DCCL_RANK"]), int(os.environ["DCCL_WORLD_SIZE"])
+    port = int(os.environ["DCCL_MASTER_PORT"]) + 1
+    if args.cuda:
+        torch.cuda.set_device(int(os.environ.get("DCCL_LOCAL_DEVICE", "0")))
+    dev = torch.device("cuda", torch.cuda.current_device()) if args.cuda else torch.device("cpu")
+    dist.init_process_group("dccl", init_method="tcp://127.0.0.1:%d" % port, rank=rank, world_size=world)
+    fails = []
+
+    def check(ok, what):
+        if not ok:
+            fails.append(what)
+
+    for dtype in (torch.float32, torch.bfloat16, torch.int64, torch.float64):
+        for n in (1, 1000, 70001):
+            ins = [tensor_for(r, n, dtype, dev) for r in range(world)]
+            tol = dict(rtol=2e-2, atol=2e-2 * world) if dtype == torch.bfloat16 else dict(rtol=1e-5, atol=1e-5)
+            want = torch.stack([x.double() for x in ins]).sum(0)
+            t = ins[rank].clone()
+            dist.all_reduce(t)
+            check(torch.allclose(t.double(), want, **tol), "all_reduce %s %d" % (dtype, n))
+            t = ins[rank].clone()
+            w = dist.all_reduce(t, op=dist.ReduceOp.MAX, async_op=True)
+            w.wait()
+            check(torch.equal(t, torch.stack(ins).max(0).values), "all_reduce max async %s %d" % (dtype, n))
+            if dtype.is_floating_point:
+                t = ins[rank].clone()
+                dist.all_reduce(t, op=dist.ReduceOp.AVG)
+                check(torch.allclose(t.double(), want / world, **tol), "all_reduce avg %s %d" % (dtype, n))
+            for root in {0, world - 1}:
+                t = ins[rank].clone()
+                dist.broadcast(t, src=root)
+                check(torch.equal(t, ins[root]), "broadcast %s %d root %d" % (dtype, n, root))
+                t = ins[rank].clone()
+                dist.reduce(t, dst=root)
+                check(rank != root or torch.allclose(t.double(), want, **tol), "reduce %s %d root %d" % (dtype, n, root))
+            out = torch.empty(n * world, dtype=dtype, device=dev)
+            dist.all_gather_into_tensor(out, ins[rank])
+            check(torch.equal(out, torch.cat(ins)), "all_gather_into_tensor %s %d" % (dtype, n))
+            lst = [torch.empty(n, dtype=dtype, device=dev) for _ in range(world)]
+            dist.all_gather(lst, ins[rank])
+            check(all(torch.equal(a, b) for a, b in zip(lst, ins)), "all_gather %s %d" % (dtype, n))
+            big = [tensor_for(100 + r, n * world, dtype, dev) for r in range(world)]
+            wantrs = torch.stack([x.double() for x in big]).sum(0)[rank * n:(rank + 1) * n]
+            out = torch.empty(n, dtype=dtype, device=dev)
+            dist.reduce_scatter_tensor(out, big[rank])
+            check(torch.allclose(out.double(), wantrs, **tol), "reduce_scatter_tensor %s %d" % (dtype, n))
+    # point to point: even ranks send to the next odd rank
+    if world >= 2:
+        msg = torch.full((5000,), float(rank), device=dev)
+        if rank % 2 == 0 and rank + 1 < world:
+            dist.send(msg, rank + 1)
+        elif rank % 2 == 1:
+            dist.recv(msg, rank - 1)
+            check(bool((msg == float(rank - 1)).all()), "send/recv")
+    dist.barrier()
+
+    if args.ddp:
+        # DistributedDataParallel over the backend: gradients must equal the average of the per-rank gradients
+        torch.manual_seed(0)
+        model = torch.nn.Sequential(torch.nn.Linear(32, 64), torch.nn.ReLU(), torch.nn.Linear(64, 8)).to(dev)
+        ref = [p.detach().clone() for p in model.parameters()]
+        ddp = torch.nn.parallel.DistributedDataParallel(model, device_ids=[dev.index] if args.cuda else None, bucket_cap_mb=1)
+        xs = [torch.randn(16, 32, generator=torch.Generator().manual_seed(50 + r)) for r in range(world)]
+        ddp(xs[rank].to(dev)).pow(2).mean().backward()
+        if args.cuda:
+            torch.cuda.synchronize()
+        grads = [p.grad.detach().cpu().double() for p in model.parameters()]
+        # serial reference on the CPU
+        want = None
+        for r in range(world):
+            m = torch.nn.Sequential(torch.nn.Linear(32, 64), torch.nn.ReLU(), torch.nn.Linear(64, 8))
+            with torch.no_grad():
+                for p, q in zip(m.parameters(), ref):
+                    p.copy_(q.cpu())
+            m(xs[r]).pow(2).mean().backward()
+            g = [p.grad.double() for p in m.parameters()]
+            want = g if want is None else [a + b for a, b in zip(want, g)]
+        want = [w / world for w in want]
+        check(all(torch.allclose(a, b, rtol=1e-4, atol=1e-6) for a, b in zip(grads, want)), "DDP gradients")
+
+    dist.destroy_process_group()
+    if fails:
+        print("FAILED on rank %d: %s" % (rank, "; ".join(fails[:10])))
+        sys.exit(1)
+    print("OK")
+
+
+if __name__ == "__main__":
+    main()
