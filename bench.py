@@ -226,6 +226,7 @@ def main():
     ap.add_argument("--algo", default="auto")
     ap.add_argument("--sweep", action="store_true", help="also sweep sizes and variants; table goes to --out")
     ap.add_argument("--out", default=os.path.join(ROOT, "gpurun_out", "sweep.json"))
+    ap.add_argument("--sweep-extra", action="store_true", help="broadcast / reduce / send-recv ring / dtype x operator rows")
     ap.add_argument("--e2e-steps", type=int, default=5)
     ap.add_argument("--sweep-ctas", default="16,32,64,128")
     ap.add_argument("--sweep-unroll", default="4,8")
@@ -303,6 +304,8 @@ def main():
     sweep = None
     if args.sweep:
         sweep = run_sweep(backend, args, rank, world, dtype, es)
+    if args.sweep_extra:
+        sweep = (sweep or []) + run_extra(backend, args, rank, world)
 
     backend.free(buf)
     backend.free(out)
@@ -355,7 +358,7 @@ def run_sweep(backend, args, rank, world, dtype, es):
     if sizes[-1] != args.bytes:
         sizes.append(args.bytes)
     ours = args.impl == "ours" and world > 1
-    variants = {"allreduce": ["auto", "oneshot", "twoshot", "ring", "rabenseifner", "nvls", "nvls_sym"],
+    variants = {"allreduce": ["auto", "oneshot", "twoshot", "ring", "rabenseifner", "nvls", "nvls_staged", "nvls_sym"],
                 "reducescatter": ["auto", "twoshot", "ring", "nvls"], "allgather": ["auto", "twoshot", "ring", "nvls"]}
     if not ours:
         variants = {k: ["auto"] for k in variants}
@@ -372,17 +375,21 @@ def run_sweep(backend, args, rank, world, dtype, es):
         ssrc.fill_(1.0 / 1024)
     for coll, algos in variants.items():
         for algo in algos:
-            if algo in ("nvls", "nvls_sym") and ours and not backend.comm.has_multicast:
+            if algo in ("nvls", "nvls_sym", "nvls_staged") and ours and not backend.comm.has_multicast:
                 continue
-            backend.set_algo(coll, "nvls" if algo == "nvls_sym" else algo)
+            backend.set_algo(coll, "nvls" if algo in ("nvls_sym", "nvls_staged") else algo)
+            if ours:
+                backend.comm.set_param("pipe_min_mb", 0 if algo == "nvls_staged" else 16)
             a, b = (ssrc, sdst) if algo == "nvls_sym" else (src, dst)
             for size in sizes:
                 if algo == "oneshot" and size > (128 << 10):
                     continue
                 if algo in ("ring", "rabenseifner") and size > (256 << 20):
                     continue
+                if algo == "nvls_staged" and size < (16 << 20):
+                    continue
                 for ctas in (ctas_list if (algo != "auto" and size >= (512 << 10)) else [0]):
-                    for unroll in (unroll_list if algo in ("nvls", "nvls_sym") and size >= (512 << 10) else [4]):
+                    for unroll in (unroll_list if algo in ("nvls", "nvls_sym", "nvls_staged") and size >= (512 << 10) else [4]):
                         if ours:
                             backend.comm.set_param("ctas", ctas)
                             backend.comm.set_param("unroll", unroll)
@@ -411,6 +418,83 @@ def run_sweep(backend, args, rank, world, dtype, es):
     if ssrc is not None:
         backend.free(ssrc)
         backend.free(sdst)
+    return rows
+
+
+def run_extra(backend, args, rank, world, es_unused=None):
+    """Rows for the other entry points: broadcast / reduce from both end ranks (fp32, 4 B - 256 MB), a ring of
+    send/recv pairs (bf16, 64 MB), reduce-scatter / all-gather over dtypes and operators."""
+    torch = backend.torch
+    rows = []
+    ours = args.impl == "ours"
+    dev = backend.dev
+    dist = getattr(backend, "dist", None)
+
+    def record(coll, detail, nbytes, ms, factor=1.0):
+        algbw = nbytes / (ms * 1e-3) / 1e9
+        rows.append({"coll": coll, "detail": detail, "bytes": nbytes, "us": round(ms * 1e3, 3), "algbw_gbs": round(algbw, 3),
+                     "busbw_gbs": round(algbw * factor, 3)})
+
+    maxel = (256 << 20) // 4
+    buf = torch.empty(maxel, dtype=torch.float32, device=dev)
+    out = torch.empty(maxel, dtype=torch.float32, device=dev)
+    buf.fill_(1.0)
+    sizes = [4, 64, 1024, 16 << 10, 256 << 10, 4 << 20, 64 << 20, 256 << 20]
+    for root in sorted({0, world - 1}):
+        for size in sizes:
+            n_el = max(1, size // 4)
+            steps = 200 if size <= (1 << 20) else 20
+            if ours:
+                fb = lambda: backend.comm.broadcast(buf[:n_el], root=root)                    # noqa: E731
+                fr = lambda: backend.comm.reduce(buf[:n_el], out[:n_el], op="sum", root=root)   # noqa: E731
+            else:
+                fb = lambda: dist.broadcast(buf[:n_el], src=root)       # noqa: E731
+                fr = lambda: dist.reduce(out[:n_el], dst=root)          # noqa: E731
+            record("broadcast", "root %d fp32" % root, n_el * 4, timed(backend, fb, steps, 5))
+            record("reduce", "root %d fp32 sum" % root, n_el * 4, timed(backend, fr, steps, 5))
+    # ring of send / recv pairs, 64 MB bf16: every rank sends to rank+1 and receives from rank-1
+    if world > 1:
+        n_el = (64 << 20) // 2
+        sb = torch.ones(n_el, dtype=torch.bfloat16, device=dev)
+        rb = torch.empty(n_el, dtype=torch.bfloat16, device=dev)
+        nxt, prv = (rank + 1) % world, (rank - 1) % world
+        if ours:
+            from dccl_b200 import group_end, group_start
+
+            def ring():
+                group_start()
+                backend.comm.send(sb, nxt)
+                backend.comm.recv(rb, prv)
+                group_end()
+        else:
+            def ring():
+                ops = [dist.P2POp(dist.isend, sb, nxt), dist.P2POp(dist.irecv, rb, prv)]
+                for w in dist.batch_isend_irecv(ops):
+                    w.wait()
+        record("sendrecv_ring", "64 MB bf16 per pair", n_el * 2, timed(backend, ring, 20, 5))
+    # reduce-scatter / all-gather over dtypes and operators (per-rank counts 256 ... 16 M elements)
+    tmap = {"fp16": torch.float16, "bf16": torch.bfloat16, "fp32": torch.float32, "int32": torch.int32}
+    for tname, dt in tmap.items():
+        esz = torch.empty((), dtype=dt).element_size()
+        for per in [256, 64 << 10, 16 << 20]:
+            src = torch.ones(per * world, dtype=dt, device=dev)
+            dst = torch.empty(per * world, dtype=dt, device=dev)
+            steps = 200 if per * esz <= (1 << 20) else 10
+            for op in ["sum", "max", "min", "avg"]:
+                if op == "avg" and not dt.is_floating_point and not ours:
+                    continue
+                if ours:
+                    f = lambda: backend.comm.reduce_scatter(src, dst[:per], op=op)   # noqa: E731
+                else:
+                    rop = {"sum": dist.ReduceOp.SUM, "max": dist.ReduceOp.MAX, "min": dist.ReduceOp.MIN, "avg": dist.ReduceOp.AVG}[op]
+                    f = lambda: dist.reduce_scatter_tensor(dst[:per], src, op=rop)   # noqa: E731
+                record("reducescatter", "%s %s" % (tname, op), per * world * esz, timed(backend, f, steps, 5), bus_factor("reducescatter", world))
+            if ours:
+                f = lambda: backend.comm.all_gather(src[:per], dst)   # noqa: E731
+            else:
+                f = lambda: dist.all_gather_into_tensor(dst, src[:per])   # noqa: E731
+            record("allgather", tname, per * world * esz, timed(backend, f, steps, 5), bus_factor("allgather", world))
+            del src, dst
     return rows
 
 

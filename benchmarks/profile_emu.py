@@ -1,0 +1,44 @@
+#!/usr/bin/env python
+"""Runs ONE collective kernel on one GPU with all ranks emulated (cooperative launch), sized for an
+ncu capture: inputs larger than L2, a few GB on the device at most, two launches.
+
+    python benchmarks/profile_emu.py --kind allreduce --algo twoshot --ranks 8 --mb 64 --ctas 16
+    ncu --set full --clock-control none -k regex:k_twoshot -c 1 -o gpurun_out/prof_twoshot \\
+        python benchmarks/profile_emu.py --kind allreduce --algo twoshot --ranks 8 --mb 64 --ctas 16
+"""
+import argparse
+import os
+import sys
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+from dccl_b200._lib import lib  # noqa: E402
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--kind", default="allreduce")
+    ap.add_argument("--algo", default="twoshot")
+    ap.add_argument("--ranks", type=int, default=8)
+    ap.add_argument("--mb", type=float, default=64.0, help="message MB per rank (fp32)")
+    ap.add_argument("--ctas", type=int, default=16)
+    ap.add_argument("--iters", type=int, default=2)
+    args = ap.parse_args()
+    L = lib()
+    n = args.ranks
+    count = int(args.mb * (1 << 20)) // 4
+    in_elems = count * n if args.kind == "reducescatter" else count
+    out_elems = count * n if args.kind == "allgather" else count
+    hin = np.ones(in_elems * n, dtype=np.float32)
+    hout = np.zeros(out_elems * n, dtype=np.float32)
+    stage = int(max(in_elems, out_elems) * 4 * 2.5) + (1 << 20)
+    rc = L.dccl_emu_collective(args.kind.encode(), args.algo.encode(), n, 7, 0, count, 0, args.ctas, 0, 0, args.iters, stage,
+                               hin.ctypes.data, hout.ctypes.data)
+    print("rc", rc, "sample", hout[:2])
+    sys.exit(0 if rc == 0 else 1)
+
+
+if __name__ == "__main__":
+    main()

@@ -30,6 +30,8 @@ bool GpuCommImpl::set_param(const char* name, int value) {
     if (k == "threads" && value >= 64 && value <= 512 && value % 32 == 0) { threads_ = value; return true; }
     if (k == "unroll" && (value == 2 || value == 4 || value == 8)) { unroll_ = value; return true; }
     if (k == "p2p_ctas" && value >= 1 && value <= kP2pCtas) { p2p_ctas_ = value; return true; }
+    if (k == "pipe_min_mb" && value >= 0) { pipe_min_bytes_ = (size_t)value << 20; return true; }
+    if (k == "pipe_ctas" && value >= 3 && value <= kMaxCtas) { pipe_ctas_ = value; return true; }
     return false;
 }
 
@@ -105,9 +107,15 @@ ncclResult_t GpuCommImpl::all_reduce(const void* send, void* recv, size_t count,
         return cuda_result(launch_nvls(a, dt, cfg), "nvls all-reduce (symmetric)");
     }
 
+    // large ordinary buffers through the switch: copy-in, switch pass and copy-out overlap chunk by chunk
+    const bool pipe = ch.algo == ALGO_NVLS && pipe_min_bytes_ > 0 && bytes >= pipe_min_bytes_;
+    if (pipe) {
+        cfg.ctas = pipe_ctas_ < sm_count_ ? pipe_ctas_ : sm_count_;
+        if (ctas_override_ >= 3) cfg.ctas = ctas_override_ < sm_count_ ? ctas_override_ : sm_count_;
+    }
     size_t cap;
     switch (ch.algo) {
-    case ALGO_NVLS: cap = nvls_capacity(NV_ALLREDUCE, n_, es, stage_bytes_); break;
+    case ALGO_NVLS: cap = pipe ? nvls_pipe_capacity(es, stage_bytes_) : nvls_capacity(NV_ALLREDUCE, n_, es, stage_bytes_); break;
     case ALGO_RING: cap = ring_capacity(RING_ALLREDUCE, n_, es, stage_bytes_); break;
     case ALGO_RABENSEIFNER: cap = hd_capacity(n_, es, stage_bytes_); break;
     default: cap = twoshot_capacity(TS_ALLREDUCE, n_, es, stage_bytes_); break;
@@ -120,7 +128,10 @@ ncclResult_t GpuCommImpl::all_reduce(const void* send, void* recv, size_t count,
         NEXT_SEQ(a);
         cudaError_t e;
         switch (ch.algo) {
-        case ALGO_NVLS: a.mode = NV_ALLREDUCE; e = launch_nvls(a, dt, cfg); break;
+        case ALGO_NVLS:
+            if (pipe) e = launch_nvls_pipe(a, dt, cfg);
+            else { a.mode = NV_ALLREDUCE; e = launch_nvls(a, dt, cfg); }
+            break;
         case ALGO_RING: a.mode = RING_ALLREDUCE; e = launch_ring(a, dt, cfg); break;
         case ALGO_RABENSEIFNER: e = launch_hd(a, dt, cfg); break;
         default: a.mode = TS_ALLREDUCE; e = launch_twoshot(a, dt, cfg); break;

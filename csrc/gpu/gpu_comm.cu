@@ -55,6 +55,8 @@ bool GpuCommImpl::init(std::string* err) {
     p2p_ctas_ = (int)cfg.get_int("DCCL/p2p_ctas", 16);
     set_param("threads", (int)cfg.get_int("DCCL/threads", 512));
     set_param("unroll", (int)cfg.get_int("DCCL/unroll", 4));
+    pipe_min_bytes_ = (size_t)cfg.get_int("DCCL/nvls_pipe_min_bytes", 16ll << 20);
+    pipe_ctas_ = (int)cfg.get_int("DCCL/nvls_pipe_ctas", 144);
     if (p2p_ctas_ < 1) p2p_ctas_ = 1;
     if (p2p_ctas_ > kP2pCtas) p2p_ctas_ = kP2pCtas;
     stage_bytes_ = (size_t)cfg.get_int("DCCL/staging_bytes", 256ll << 20);

@@ -78,6 +78,8 @@ private:
     int p2p_ctas_ = 16;
     int threads_ = 512;
     int sm_count_ = 148;
+    size_t pipe_min_bytes_ = 16u << 20;   // ordinary-buffer switch all-reduce is pipelined from this size on (0 = never)
+    int pipe_ctas_ = 144;
     int unroll_ = 4;
     bool sticky_error_ = false;
     std::vector<SymSegment> user_segs_;

@@ -33,6 +33,10 @@ bool nvls_supports(ncclDataType_t dt, ncclRedOp_t op);
 size_t nvls_capacity(int mode, int nranks, size_t elem_size, size_t stage_bytes);
 cudaError_t launch_nvls(const CollArgs& a, ncclDataType_t dt, const LaunchCfg& cfg);
 
+/* nvls_pipe.cu: all-reduce of ordinary buffers with copy-in / switch pass / copy-out overlapped chunk by chunk */
+size_t nvls_pipe_capacity(size_t elem_size, size_t stage_bytes);
+cudaError_t launch_nvls_pipe(const CollArgs& a, ncclDataType_t dt, const LaunchCfg& cfg);
+
 /* ring.cu / hd.cu: the two algorithms of the original as single kernels */
 enum { RING_ALLREDUCE = 0, RING_REDUCESCATTER, RING_ALLGATHER };
 size_t ring_capacity(int mode, int nranks, size_t elem_size, size_t stage_bytes);

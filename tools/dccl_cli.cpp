@@ -33,7 +33,7 @@ static const char* help_string =
     "\t             - only the root (rank 0 unless --root) will 'broadcast', all other node will receive. \n"
     "\t             - 'reduce' will reduce to the root (rank 0 unless --root).\n"
 #ifdef DCCL_WITH_CUDA
-    "\t--gpu,-g     gpu device to use. If not specified, CPU is used.\n"
+    "\t--gpu,-g     gpu device to use (or 'auto': the launcher's local device / the rank). If not specified, CPU is used.\n"
 #endif
     "\t--warmup,-w  number of operations for warmup, defaulted to 0.\n"
     "\t--repeat,-r  number of operations for evaluation, defaulted to 1000.\n"
@@ -90,7 +90,7 @@ int main(int argc, char** argv) {
         if (c == -1) break;
         switch (c) {
         case 'a': api = optarg; break;
-        case 'g': gpu = std::stoi(optarg); break;
+        case 'g': gpu = !strcmp(optarg, "auto") ? -2 : std::stoi(optarg); break;
         case 'w': warmup_count = std::stoul(optarg); break;
         case 'r': repeat_count = std::stoul(optarg); break;
         case 't':
@@ -138,6 +138,11 @@ int main(int argc, char** argv) {
     ncclResult_t ret = ncclCommInit(&comm);
     if (ret != ncclSuccess) { std::cerr << "failed to initialize the dccl communicator." << std::endl; return 1; }
     const uint32_t my_rank = dcclGetMyRank(comm), world_size = dcclGetWorldSize(comm);
+    if (gpu == -2) {   // --gpu auto: the launcher's local device, else the rank
+        const char* e = getenv("DCCL_LOCAL_DEVICE");
+        if (!e || !*e) e = getenv("LOCAL_RANK");
+        gpu = e && *e ? atoi(e) : (int)my_rank;
+    }
     if (!algo.empty()) {
         const char* colls[] = {"allreduce", "reducescatter", "allgather", "broadcast", "reduce"};
         for (const char* c : colls)

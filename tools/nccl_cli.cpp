@@ -54,7 +54,7 @@ int main(int argc, char** argv) {
         if (c == -1) break;
         switch (c) {
         case 'a': api = optarg; break;
-        case 'g': gpu = std::stoi(optarg); break;
+        case 'g': gpu = !strcmp(optarg, "auto") ? -2 : std::stoi(optarg); break;
         case 'w': warmup = std::stoul(optarg); break;
         case 'r': repeat = std::stoul(optarg); break;
         case 't': dt = parse_type_name(optarg); break;
@@ -66,7 +66,7 @@ int main(int argc, char** argv) {
         default: std::cout << "options: --api --gpu --warmup --repeat --type --op --count --verify --init --seed" << std::endl; return 0;
         }
     }
-    if (api.empty() || gpu < 0 || dt == dccl::ncclNumTypes || op == dccl::ncclNumOps) {
+    if (api.empty() || (gpu < 0 && gpu != -2) || dt == dccl::ncclNumTypes || op == dccl::ncclNumOps) {
         std::cerr << "nccl_cli needs --api, --gpu and valid --type / --op" << std::endl;
         return -1;
     }
@@ -88,6 +88,11 @@ int main(int argc, char** argv) {
     dccl::ncclComm_t boot;
     if (dccl::ncclCommInit(&boot) != dccl::ncclSuccess) { std::cerr << "failed to initialize the bootstrap communicator." << std::endl; return 1; }
     const int rank = (int)dccl::dcclGetMyRank(boot), world = (int)dccl::dcclGetWorldSize(boot);
+    if (gpu == -2) {
+        const char* e = getenv("DCCL_LOCAL_DEVICE");
+        if (!e || !*e) e = getenv("LOCAL_RANK");
+        gpu = e && *e ? atoi(e) : rank;
+    }
     if (cudaSetDevice(gpu) != cudaSuccess) { std::cerr << "cudaSetDevice failed" << std::endl; return 4; }
     stock::uid_t id;
     memset(&id, 0, sizeof(id));
