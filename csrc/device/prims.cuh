@@ -195,7 +195,8 @@ __device__ __forceinline__ uint32_t flag_value(uint32_t seq, int idx) { return s
 /** Tell `peer` that CTA `bid` of this rank has reached point `idx` of call `seq`.
  *  Call from ONE thread after a __syncthreads() that follows the CTA's data writes. */
 __device__ __forceinline__ void signal_peer(const DevComm& c, int peer, int bid, uint32_t seq, int idx) {
-    __threadfence_system();
+    // the release store orders everything that happened before it, including the other threads' writes
+    // that the preceding CTA barrier made visible to this thread; no separate fence is needed
     st_release_sys(flag_slot(c.pool[peer], bid, c.rank), flag_value(seq, idx));
 }
 

@@ -151,6 +151,10 @@ int dccl_emu_collective(const char* kind_s, const char* algo_s, int nranks, int 
             else if (algo == ALGO_RING) { a.mode = RING_ALLREDUCE; cap = ring_capacity(a.mode, nranks, es, stage_bytes); if (count <= cap) e = launch_ring(a, dt, cfg); }
             else if (algo == ALGO_RABENSEIFNER) { cap = hd_capacity(nranks, es, stage_bytes); if (count <= cap && is_power_of_two((uint32_t)nranks)) e = launch_hd(a, dt, cfg); }
             else { a.mode = TS_ALLREDUCE; cap = twoshot_capacity(a.mode, nranks, es, stage_bytes); if (count <= cap) e = launch_twoshot(a, dt, cfg); }
+        } else if (coll != COLL_ALLREDUCE && algo == ALGO_ONESHOT && count * es <= oneshot_ll_capacity_bytes()) {
+            a.mode = coll == COLL_REDUCESCATTER ? LL_REDUCESCATTER : coll == COLL_ALLGATHER ? LL_ALLGATHER : coll == COLL_BROADCAST ? LL_BROADCAST : LL_REDUCE;
+            cap = oneshot_ll_capacity_bytes() / es;
+            e = launch_ll_collective(a, dt, cfg);
         } else if (coll == COLL_REDUCESCATTER) {
             if (algo == ALGO_RING) { a.mode = RING_REDUCESCATTER; cap = ring_capacity(a.mode, nranks, es, stage_bytes); if (count <= cap) e = launch_ring(a, dt, cfg); }
             else { a.mode = TS_REDUCESCATTER; cap = twoshot_capacity(a.mode, nranks, es, stage_bytes); if (count <= cap) e = launch_twoshot(a, dt, cfg); }

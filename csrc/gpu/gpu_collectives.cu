@@ -159,7 +159,8 @@ ncclResult_t GpuCommImpl::reduce_scatter(const void* send, void* recv, size_t re
     TuneChoice ch = tuner_.choose(COLL_REDUCESCATTER, n_, bytes, nvls_ok);
     if (algo != ALGO_AUTO) ch.algo = algo;
     if (ch.algo == ALGO_NVLS && !nvls_ok) ch.algo = ALGO_TWOSHOT;
-    if (ch.algo != ALGO_NVLS && ch.algo != ALGO_RING) ch.algo = ALGO_TWOSHOT;
+    if (ch.algo == ALGO_ONESHOT && recvcount * es > oneshot_ll_capacity_bytes()) ch.algo = ALGO_TWOSHOT;
+    if (ch.algo != ALGO_NVLS && ch.algo != ALGO_RING && ch.algo != ALGO_ONESHOT) ch.algo = ALGO_TWOSHOT;
     last_[COLL_REDUCESCATTER] = ch.algo;
 
     LaunchCfg cfg;
@@ -169,6 +170,13 @@ ncclResult_t GpuCommImpl::reduce_scatter(const void* send, void* recv, size_t re
     CollArgs a = base_args(send, recv, op, 0);
     a.stride = recvcount;
 
+    if (ch.algo == ALGO_ONESHOT) {
+        a.mode = LL_REDUCESCATTER;
+        a.count = recvcount;
+        NEXT_SEQ(a);
+        launches_++;
+        return cuda_result(launch_ll_collective(a, dt, cfg), "packet reduce-scatter");
+    }
     if (ch.algo == ALGO_NVLS) {
         const char* sp[kMaxPeers];
         const char* smc = nullptr;
@@ -218,7 +226,8 @@ ncclResult_t GpuCommImpl::all_gather(const void* send, void* recv, size_t sendco
     TuneChoice ch = tuner_.choose(COLL_ALLGATHER, n_, bytes, nvls_ok);
     if (algo != ALGO_AUTO) ch.algo = algo;
     if (ch.algo == ALGO_NVLS && !nvls_ok) ch.algo = ALGO_TWOSHOT;
-    if (ch.algo != ALGO_NVLS && ch.algo != ALGO_RING) ch.algo = ALGO_TWOSHOT;
+    if (ch.algo == ALGO_ONESHOT && sendcount * es > oneshot_ll_capacity_bytes()) ch.algo = ALGO_TWOSHOT;
+    if (ch.algo != ALGO_NVLS && ch.algo != ALGO_RING && ch.algo != ALGO_ONESHOT) ch.algo = ALGO_TWOSHOT;
     last_[COLL_ALLGATHER] = ch.algo;
 
     LaunchCfg cfg;
@@ -228,6 +237,13 @@ ncclResult_t GpuCommImpl::all_gather(const void* send, void* recv, size_t sendco
     CollArgs a = base_args(send, recv, ncclSum, 0);
     a.stride = sendcount;
 
+    if (ch.algo == ALGO_ONESHOT) {
+        a.mode = LL_ALLGATHER;
+        a.count = sendcount;
+        NEXT_SEQ(a);
+        launches_++;
+        return cuda_result(launch_ll_collective(a, dt, cfg), "packet all-gather");
+    }
     if (ch.algo == ALGO_NVLS) {
         const char* rp[kMaxPeers];
         const char* rmc = nullptr;
@@ -286,6 +302,13 @@ ncclResult_t GpuCommImpl::broadcast(const void* send, void* recv, size_t count, 
     if (rank_ != root) send = recv;   // only the root's source is read
     CollArgs a = base_args(send, recv, ncclSum, root);
 
+    if (ch.algo == ALGO_ONESHOT && bytes <= oneshot_ll_capacity_bytes()) {
+        a.mode = LL_BROADCAST;
+        a.count = count;
+        NEXT_SEQ(a);
+        launches_++;
+        return cuda_result(launch_ll_collective(a, dt, cfg), "packet broadcast");
+    }
     if (ch.algo == ALGO_NVLS) {
         const char* rp[kMaxPeers];
         const char* rmc = nullptr;
@@ -334,7 +357,8 @@ ncclResult_t GpuCommImpl::reduce(const void* send, void* recv, size_t count, ncc
     TuneChoice ch = tuner_.choose(COLL_REDUCE, n_, bytes, nvls_ok);
     if (algo != ALGO_AUTO) ch.algo = algo;
     if (ch.algo == ALGO_NVLS && !nvls_ok) ch.algo = ALGO_TWOSHOT;
-    if (ch.algo != ALGO_NVLS) ch.algo = ALGO_TWOSHOT;
+    if (ch.algo == ALGO_ONESHOT && bytes > oneshot_ll_capacity_bytes()) ch.algo = ALGO_TWOSHOT;
+    if (ch.algo != ALGO_NVLS && ch.algo != ALGO_ONESHOT) ch.algo = ALGO_TWOSHOT;
     last_[COLL_REDUCE] = ch.algo;
 
     LaunchCfg cfg;
@@ -342,6 +366,13 @@ ncclResult_t GpuCommImpl::reduce(const void* send, void* recv, size_t count, ncc
     cfg.stream = stream;
     cfg.threads = threads_;
     CollArgs a = base_args(send, recv, op, root);
+    if (ch.algo == ALGO_ONESHOT) {
+        a.mode = LL_REDUCE;
+        a.count = count;
+        NEXT_SEQ(a);
+        launches_++;
+        return cuda_result(launch_ll_collective(a, dt, cfg), "packet reduce");
+    }
     size_t cap = ch.algo == ALGO_NVLS ? nvls_capacity(NV_REDUCE, n_, es, stage_bytes_) : twoshot_capacity(TS_REDUCE, n_, es, stage_bytes_);
     for (size_t off = 0; off < count; off += cap) {
         const size_t c = count - off < cap ? count - off : cap;

@@ -27,6 +27,11 @@ cudaError_t launch_twoshot(const CollArgs& a, ncclDataType_t dt, const LaunchCfg
 size_t oneshot_ll_capacity_bytes();
 cudaError_t launch_oneshot_ll(const CollArgs& a, ncclDataType_t dt, const LaunchCfg& cfg);
 
+/* ll_collectives.cu: flag-in-data reduce-scatter / all-gather / broadcast / reduce for small messages;
+ * count = per-rank elements, at most oneshot_ll_capacity_bytes() per rank */
+enum { LL_REDUCESCATTER = 0, LL_ALLGATHER, LL_BROADCAST, LL_REDUCE };
+cudaError_t launch_ll_collective(const CollArgs& a, ncclDataType_t dt, const LaunchCfg& cfg);
+
 /* nvls.cu: in-switch reduction / multicast variants */
 enum { NV_ALLREDUCE = 0, NV_REDUCESCATTER, NV_ALLGATHER, NV_BROADCAST, NV_REDUCE };
 bool nvls_supports(ncclDataType_t dt, ncclRedOp_t op);

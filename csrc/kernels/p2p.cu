@@ -72,7 +72,6 @@ __global__ void __launch_bounds__(512) k_p2p(const __grid_constant__ P2pArgs a) 
             if (hi > lo) copy_bytes(p2p_fifo(c.pool[peer], r, G) + lo, op.buf + coff + lo, hi - lo);
             __syncthreads();
             if (threadIdx.x == 0) {
-                __threadfence_system();
                 st_release_sys64(p2p_head(c.pool[peer], r, b), G + 1);
             }
         } else {
@@ -82,7 +81,6 @@ __global__ void __launch_bounds__(512) k_p2p(const __grid_constant__ P2pArgs a) 
             if (hi > lo) copy_bytes(op.buf + coff + lo, p2p_fifo(c.pool[r], peer, G) + lo, hi - lo);
             __syncthreads();
             if (threadIdx.x == 0) {
-                __threadfence_system();
                 st_release_sys64(p2p_tail(c.pool[peer], r, b), G + 1);
             }
         }

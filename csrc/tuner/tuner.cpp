@@ -22,13 +22,16 @@ static const TuneRule kBuiltin[] = {
     // all-reduce, symmetric buffers: zero-copy switch variant; more than ~32 CTAs only adds contention
     {TUNE_ALLREDUCE_SYM, 0, 64u << 10, ALGO_ONESHOT, 8},
     {TUNE_ALLREDUCE_SYM, 0, kInf, ALGO_NVLS, 32},
+    {COLL_REDUCESCATTER, 0, 256u << 10, ALGO_ONESHOT, 8},
     {COLL_REDUCESCATTER, 0, 1u << 20, ALGO_TWOSHOT, 32},
     {COLL_REDUCESCATTER, 0, kInf, ALGO_TWOSHOT, 128},
+    {COLL_ALLGATHER, 0, 256u << 10, ALGO_ONESHOT, 8},
     {COLL_ALLGATHER, 0, 1u << 20, ALGO_NVLS, 32},
     {COLL_ALLGATHER, 0, 8u << 20, ALGO_NVLS, 128},
     {COLL_ALLGATHER, 0, kInf, ALGO_TWOSHOT, 128},
     {COLL_BROADCAST, 0, 256u << 10, ALGO_ONESHOT, 16},
     {COLL_BROADCAST, 0, kInf, ALGO_NVLS, 64},
+    {COLL_REDUCE, 0, 64u << 10, ALGO_ONESHOT, 8},
     {COLL_REDUCE, 0, 1u << 20, ALGO_TWOSHOT, 32},
     {COLL_REDUCE, 0, kInf, ALGO_NVLS, 128},
 };

@@ -98,7 +98,7 @@ def test_allreduce_in_place_and_unaligned(dccl_lib, algo):
                 assert close(out[r], want, name, n), (algo, name, misalign, in_place, r)
 
 
-@pytest.mark.parametrize("algo", ["twoshot", "ring"])
+@pytest.mark.parametrize("algo", ["twoshot", "ring", "oneshot"])
 @pytest.mark.parametrize("n", [2, 3, 8])
 def test_reduce_scatter_and_all_gather(dccl_lib, algo, n):
     for name in ["float32", "bfloat16", "int32", "float16"]:
@@ -128,8 +128,9 @@ def test_broadcast_and_reduce_roots(dccl_lib, n):
                     assert np.array_equal(out[r], ins[root]), ("bcast", algo, n, root, count, r)
             for op in ["sum", "avg", "max"]:
                 want = oracle.fold(ins, op)
-                out = emu(dccl_lib, "reduce", "twoshot", n, "float32", op, count, ins, root=root)
-                assert close(out[root], want, "float32", n), ("reduce", n, root, count, op)
+                for algo in ["twoshot", "oneshot"]:     # oneshot: packets up to 128 KB, else the staged variant
+                    out = emu(dccl_lib, "reduce", algo if count * 4 <= 128 * 1024 else "twoshot", n, "float32", op, count, ins, root=root)
+                    assert close(out[root], want, "float32", n), ("reduce", algo, n, root, count, op)
 
 
 def test_many_ctas_and_small_staging(dccl_lib):

@@ -136,7 +136,7 @@ def test_tuner_table_and_file_override(dccl_lib):
     assert choose("allreduce", 8, 1000) == ("ring", 4)
     assert choose("allreduce", 8, 100000) == ("rabenseifner", 12)
     assert choose("allreduce", 4, 10) == ("rabenseifner", 12)
-    assert choose("reducescatter", 8, 10)[0] == "twoshot"              # untouched collective keeps the built-in rows
+    assert choose("reducescatter", 8, 10)[0] == "oneshot"              # untouched collective keeps the built-in rows
 
 
 def test_oracle_integer_semantics():

@@ -79,7 +79,7 @@ def main():
                 comm.set_algorithm("allreduce", "auto")
                 # reduce to both ends
                 for root in {0, world - 1}:
-                    for algo in ["twoshot"] + (["nvls"] if comm.has_multicast else []):
+                    for algo in ["twoshot", "oneshot"] + (["nvls"] if comm.has_multicast else []):
                         comm.set_algorithm("reduce", algo)
                         s = to_torch(ins[rank], name, dev)
                         r = torch.zeros_like(s)
@@ -90,7 +90,7 @@ def main():
                 per = count // world
                 if per:
                     wantrs = want[rank * per:(rank + 1) * per]
-                    for algo in ["twoshot", "ring"] + (["nvls"] if comm.has_multicast else []):
+                    for algo in ["twoshot", "ring", "oneshot"] + (["nvls"] if comm.has_multicast else []):
                         comm.set_algorithm("reducescatter", algo)
                         s = to_torch(ins[rank][:per * world], name, dev)
                         r = torch.zeros(per, dtype=s.dtype, device=dev)
@@ -99,7 +99,7 @@ def main():
                         check(close(to_numpy(r, name), wantrs, name, world), "reduce_scatter %s %s %s n=%d" % (algo, name, op, per))
             per = max(1, count // world)
             full = np.concatenate([x[:per] for x in ins])
-            for algo in ["twoshot", "ring"] + (["nvls"] if comm.has_multicast else []):
+            for algo in ["twoshot", "ring", "oneshot"] + (["nvls"] if comm.has_multicast else []):
                 comm.set_algorithm("allgather", algo)
                 s = to_torch(ins[rank][:per], name, dev)
                 r = torch.zeros(per * world, dtype=s.dtype, device=dev)
