@@ -59,7 +59,7 @@ CU_OBJS := $(patsubst %.cu,$(BUILD)/obj/%.cu.o,$(CU_SRCS))
 LIB := $(BUILD)/libdccl.so
 TOOLS := $(BUILD)/dccl_cli $(BUILD)/p2p_perf $(BUILD)/helloworld
 ifeq ($(CUDA),1)
-TOOLS += $(BUILD)/nccl_cli
+TOOLS += $(BUILD)/nccl_cli $(BUILD)/dccl_sweep
 endif
 
 .PHONY: all lib tools clean
@@ -93,6 +93,9 @@ $(BUILD)/helloworld: examples/helloworld/main.cpp $(LIB)
 
 # comparator: the same workload through stock NCCL (found at run time with dlopen)
 $(BUILD)/nccl_cli: tools/nccl_cli.cpp tools/tool_common.hpp $(LIB)
+	$(CXX) $(CXXFLAGS) $(TOOL_DEFS) $< -o $@ -L$(BUILD) -ldccl -Wl,-rpath,'$$ORIGIN' $(CUDA_LIBS) $(LDFLAGS)
+
+$(BUILD)/dccl_sweep: tools/dccl_sweep.cpp tools/tool_common.hpp $(LIB)
 	$(CXX) $(CXXFLAGS) $(TOOL_DEFS) $< -o $@ -L$(BUILD) -ldccl -Wl,-rpath,'$$ORIGIN' $(CUDA_LIBS) $(LDFLAGS)
 
 clean:

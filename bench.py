@@ -229,6 +229,7 @@ def main():
     ap.add_argument("--sweep-extra", action="store_true", help="broadcast / reduce / send-recv ring / dtype x operator rows")
     ap.add_argument("--e2e-steps", type=int, default=5)
     ap.add_argument("--sweep-ctas", default="16,32,64,128")
+    ap.add_argument("--sweep-min", type=int, default=1024, help="smallest message of the sweep")
     ap.add_argument("--sweep-unroll", default="4,8")
     args = ap.parse_args()
     if args.warmup < 3:
@@ -351,7 +352,7 @@ def run_sweep(backend, args, rank, world, dtype, es):
     The pseudo-variant "nvls_sym" is the switch variant on symmetric (dcclMemAlloc) buffers."""
     rows = []
     sizes = []
-    s = 1024
+    s = args.sweep_min
     while s <= args.bytes:
         sizes.append(s)
         s *= 8
