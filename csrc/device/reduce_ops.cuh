@@ -60,7 +60,7 @@ template <typename T> __device__ __forceinline__ void st_vec(void* p, const Vec1
 
 __device__ __forceinline__ bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
-constexpr int kUnroll = 4;
+constexpr int kUnroll = 8;   // 16-byte vectors in flight per thread in the copy loops
 
 /**
  * dst[0..bytes) = src[0..bytes), all threads of the CTA cooperate. When source and

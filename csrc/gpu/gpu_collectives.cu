@@ -111,11 +111,11 @@ ncclResult_t GpuCommImpl::all_reduce(const void* send, void* recv, size_t count,
     const bool pipe = ch.algo == ALGO_NVLS && pipe_min_bytes_ > 0 && bytes >= pipe_min_bytes_;
     if (pipe) {
         cfg.ctas = pipe_ctas_ < sm_count_ ? pipe_ctas_ : sm_count_;
-        if (ctas_override_ >= 3) cfg.ctas = ctas_override_ < sm_count_ ? ctas_override_ : sm_count_;
+        if (ctas_override_ >= 9) cfg.ctas = ctas_override_ < sm_count_ ? ctas_override_ : sm_count_;
     }
     size_t cap;
     switch (ch.algo) {
-    case ALGO_NVLS: cap = pipe ? nvls_pipe_capacity(es, stage_bytes_) : nvls_capacity(NV_ALLREDUCE, n_, es, stage_bytes_); break;
+    case ALGO_NVLS: cap = pipe ? nvls_pipe_capacity(es, stage_bytes_, n_, false) : nvls_capacity(NV_ALLREDUCE, n_, es, stage_bytes_); break;
     case ALGO_RING: cap = ring_capacity(RING_ALLREDUCE, n_, es, stage_bytes_); break;
     case ALGO_RABENSEIFNER: cap = hd_capacity(n_, es, stage_bytes_); break;
     default: cap = twoshot_capacity(TS_ALLREDUCE, n_, es, stage_bytes_); break;
@@ -129,7 +129,7 @@ ncclResult_t GpuCommImpl::all_reduce(const void* send, void* recv, size_t count,
         cudaError_t e;
         switch (ch.algo) {
         case ALGO_NVLS:
-            if (pipe) e = launch_nvls_pipe(a, dt, cfg);
+            if (pipe) e = launch_nvls_pipe(a, dt, cfg, false);
             else { a.mode = NV_ALLREDUCE; e = launch_nvls(a, dt, cfg); }
             break;
         case ALGO_RING: a.mode = RING_ALLREDUCE; e = launch_ring(a, dt, cfg); break;
@@ -190,7 +190,14 @@ ncclResult_t GpuCommImpl::reduce_scatter(const void* send, void* recv, size_t re
             return cuda_result(launch_nvls(a, dt, cfg), "nvls reduce-scatter (symmetric)");
         }
     }
-    size_t cap = ch.algo == ALGO_NVLS ? nvls_capacity(NV_REDUCESCATTER, n_, es, stage_bytes_)
+    // large ordinary buffers through the switch: copy-in and switch pass overlap chunk by chunk
+    const bool pipe = ch.algo == ALGO_NVLS && pipe_min_bytes_ > 0 && bytes >= pipe_min_bytes_ && (uintptr_t)recv % 16 == 0 && (recvcount * es) % 16 == 0;
+    if (pipe) {
+        cfg.ctas = pipe_ctas_ < sm_count_ ? pipe_ctas_ : sm_count_;
+        if (ctas_override_ >= 5) cfg.ctas = ctas_override_ < sm_count_ ? ctas_override_ : sm_count_;
+    }
+    size_t cap = pipe ? nvls_pipe_capacity(es, stage_bytes_, n_, true)
+                 : ch.algo == ALGO_NVLS ? nvls_capacity(NV_REDUCESCATTER, n_, es, stage_bytes_)
                  : ch.algo == ALGO_RING ? ring_capacity(RING_REDUCESCATTER, n_, es, stage_bytes_)
                                         : twoshot_capacity(TS_REDUCESCATTER, n_, es, stage_bytes_);
     for (size_t off = 0; off < recvcount; off += cap) {
@@ -200,7 +207,8 @@ ncclResult_t GpuCommImpl::reduce_scatter(const void* send, void* recv, size_t re
         a.count = c;
         NEXT_SEQ(a);
         cudaError_t e;
-        if (ch.algo == ALGO_NVLS) { a.mode = NV_REDUCESCATTER; e = launch_nvls(a, dt, cfg); }
+        if (pipe) e = launch_nvls_pipe(a, dt, cfg, true);
+        else if (ch.algo == ALGO_NVLS) { a.mode = NV_REDUCESCATTER; e = launch_nvls(a, dt, cfg); }
         else if (ch.algo == ALGO_RING) { a.mode = RING_REDUCESCATTER; e = launch_ring(a, dt, cfg); }
         else { a.mode = TS_REDUCESCATTER; e = launch_twoshot(a, dt, cfg); }
         launches_++;

@@ -38,9 +38,10 @@ bool nvls_supports(ncclDataType_t dt, ncclRedOp_t op);
 size_t nvls_capacity(int mode, int nranks, size_t elem_size, size_t stage_bytes);
 cudaError_t launch_nvls(const CollArgs& a, ncclDataType_t dt, const LaunchCfg& cfg);
 
-/* nvls_pipe.cu: all-reduce of ordinary buffers with copy-in / switch pass / copy-out overlapped chunk by chunk */
-size_t nvls_pipe_capacity(size_t elem_size, size_t stage_bytes);
-cudaError_t launch_nvls_pipe(const CollArgs& a, ncclDataType_t dt, const LaunchCfg& cfg);
+/* nvls_pipe.cu: all-reduce / reduce-scatter of ordinary buffers with copy-in, switch pass and copy-out overlapped
+ * chunk by chunk (reduce-scatter: count = per-rank elements, stride = slot distance in the send buffer) */
+size_t nvls_pipe_capacity(size_t elem_size, size_t stage_bytes, int nranks, bool reduce_scatter);
+cudaError_t launch_nvls_pipe(const CollArgs& a, ncclDataType_t dt, const LaunchCfg& cfg, bool reduce_scatter);
 
 /* ring.cu / hd.cu: the two algorithms of the original as single kernels */
 enum { RING_ALLREDUCE = 0, RING_REDUCESCATTER, RING_ALLGATHER };

@@ -26,6 +26,13 @@ def test_every_variant_on_all_gpus():
 
 
 @pytest.mark.skipif(gpu_count() < 2, reason="needs two GPUs")
+def test_pipelined_switch_variant_on_small_and_odd_sizes():
+    """The copy-in / switch / copy-out pipeline normally starts at 16 MB; here it serves everything above 256 KB."""
+    world = min(gpu_count(), 8)
+    run(world, ["--suite", "basic"], env={"DCCL_NVLS_PIPE_MIN_BYTES": str(256 << 10)})
+
+
+@pytest.mark.skipif(gpu_count() < 2, reason="needs two GPUs")
 def test_messages_larger_than_staging_are_chunked():
     world = min(gpu_count(), 8)
     run(world, ["--suite", "chunk"], env={"DCCL_STAGING_BYTES": str(4 << 20)})
