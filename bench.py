@@ -415,7 +415,7 @@ def run_sweep(backend, args, rank, world, dtype, es):
             backend.set_algo(coll, "auto")
     if ours:
         backend.comm.set_param("ctas", 0)
-        backend.comm.set_param("unroll", 4)
+        backend.comm.set_param("unroll", 8)
     if ssrc is not None:
         backend.free(ssrc)
         backend.free(sdst)

@@ -54,7 +54,7 @@ bool GpuCommImpl::init(std::string* err) {
     ctas_override_ = (int)cfg.get_int("DCCL/ctas", 0);
     p2p_ctas_ = (int)cfg.get_int("DCCL/p2p_ctas", 16);
     set_param("threads", (int)cfg.get_int("DCCL/threads", 512));
-    set_param("unroll", (int)cfg.get_int("DCCL/unroll", 4));
+    set_param("unroll", (int)cfg.get_int("DCCL/unroll", 8));
     pipe_min_bytes_ = (size_t)cfg.get_int("DCCL/nvls_pipe_min_bytes", 16ll << 20);
     pipe_ctas_ = (int)cfg.get_int("DCCL/nvls_pipe_ctas", 144);
     if (p2p_ctas_ < 1) p2p_ctas_ = 1;

@@ -80,7 +80,7 @@ private:
     int sm_count_ = 148;
     size_t pipe_min_bytes_ = 16u << 20;   // ordinary-buffer switch all-reduce is pipelined from this size on (0 = never)
     int pipe_ctas_ = 144;
-    int unroll_ = 4;
+    int unroll_ = 8;
     bool sticky_error_ = false;
     std::vector<SymSegment> user_segs_;
     std::vector<RegisteredBuffer> regs_;

@@ -15,10 +15,10 @@
  *        all-reduce only)
  *
  * so that the copies of chunks k+1 and k-1 run while the switch works on chunk
- * k. The switch pass saturates with few CTAs (more only add contention), the
- * copies want many, so every NV CTA g is fed by kPipeFan IN CTAs and drained by
- * kPipeFan OUT CTAs that split its sub-range. Hand-over: IN CTA (g,m) of every
- * rank signals flag row g*fan+m of every rank; NV_g waits for all fan x n of
+ * k. Every NV CTA g is fed by kPipeFan IN CTAs and drained by kPipeFan OUT CTAs
+ * that split its sub-range (equal thirds, kPipeFan = 1, measured best on 8 x B200).
+ * Hand-over: IN CTA (g,m) of every rank signals flag row g*fan+m of every rank;
+ * NV_g waits for all fan x n of
  * them, then signals row B_g of every rank, which the OUT CTAs (g, *) wait on.
  * The whole message sits in one staging half, so no staging byte is reused
  * within a launch and the hand-over needs no back pressure.
@@ -30,7 +30,7 @@
 namespace dccl {
 
 constexpr int kPipeMaxChunks = 24;    // flag values per call are limited (kFlagVals)
-constexpr int kPipeFan = 4;           // copy CTAs per switch CTA, on each side
+constexpr int kPipeFan = 1;           // copy CTAs per switch CTA, on each side (measured on 8 x B200: 1 beats 4)
 static_assert(kPipeMaxChunks < kFlagVals, "chunk numbers must fit the per-call flag values");
 
 /** wait until point idx was signalled on flag rows [row0, row0 + rows) by EVERY rank */

@@ -19,9 +19,9 @@ static const TuneRule kBuiltin[] = {
     {COLL_ALLREDUCE, 0, 128u << 10, ALGO_ONESHOT, 8},
     {COLL_ALLREDUCE, 0, 8u << 20, ALGO_NVLS, 64},
     {COLL_ALLREDUCE, 0, kInf, ALGO_NVLS, 128},
-    // all-reduce, symmetric buffers: zero-copy switch variant; more than ~32 CTAs only adds contention
+    // all-reduce, symmetric buffers: zero-copy switch variant; 8-32 CTAs saturate it, more only add contention
     {TUNE_ALLREDUCE_SYM, 0, 64u << 10, ALGO_ONESHOT, 8},
-    {TUNE_ALLREDUCE_SYM, 0, kInf, ALGO_NVLS, 32},
+    {TUNE_ALLREDUCE_SYM, 0, kInf, ALGO_NVLS, 16},
     {COLL_REDUCESCATTER, 0, 256u << 10, ALGO_ONESHOT, 8},
     {COLL_REDUCESCATTER, 0, 1u << 20, ALGO_TWOSHOT, 32},
     {COLL_REDUCESCATTER, 0, kInf, ALGO_TWOSHOT, 128},
