@@ -247,7 +247,7 @@ bool Bootstrap::init(const UniqueIdData& id, int rank, int world, int timeout_ms
         return false;
     }
     if (rh.aux != ST_OK) { if (err) *err = "rank 0 refused the join (world size or rank mismatch)"; return false; }
-    token_ = tok;
+    if (rank != 0) token_ = tok;   // rank 0 made the token; its server thread reads it concurrently
     if (rank != 0 && !map_segments(err)) return false;
 
     // unix datagram socket for file-descriptor passing
