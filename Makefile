@@ -3,8 +3,7 @@
 #   make                 library + tools for B200 (sm_100a), CUDA enabled
 #   make CUDA=0          host-only library (no nvcc needed; device calls are refused)
 #   make SANITIZE=address|thread|undefined   instrument the host code (host-only build)
-#   make DEBUG_BOUNDS=1  device kernels check every access against its buffer and
-#                        report through the status word instead of touching memory
+#   make install PREFIX=/opt/dccl         headers, library, tools, CMake package file
 #
 # Everything lands in build/; the shared library is also copied into the Python
 # package (dccl_b200/lib/) so that it is found next to the bindings.
@@ -28,9 +27,6 @@ NVCCFLAGS := -std=c++17 -O3 -lineinfo -gencode arch=compute_100a,code=sm_100a -X
              -DCACHELINE_SIZE=$(CACHELINE) -DENABLE_EVALUATION=1 -DDCCL_WITH_CUDA_RUNTIME
 ifdef PTXAS_V
 NVCCFLAGS += -Xptxas -v
-endif
-ifdef DEBUG_BOUNDS
-NVCCFLAGS += -DDCCL_DEBUG_BOUNDS=1
 endif
 ifdef SANITIZE
 CUDA := 0
@@ -62,7 +58,8 @@ ifeq ($(CUDA),1)
 TOOLS += $(BUILD)/nccl_cli $(BUILD)/dccl_sweep
 endif
 
-.PHONY: all lib tools clean
+.PHONY: all lib tools clean install
+PREFIX ?= /usr/local
 all: lib tools
 lib: $(LIB) dccl_b200/lib/libdccl.so
 tools: $(TOOLS)
@@ -97,6 +94,14 @@ $(BUILD)/nccl_cli: tools/nccl_cli.cpp tools/tool_common.hpp $(LIB)
 
 $(BUILD)/dccl_sweep: tools/dccl_sweep.cpp tools/tool_common.hpp $(LIB)
 	$(CXX) $(CXXFLAGS) $(TOOL_DEFS) $< -o $@ -L$(BUILD) -ldccl -Wl,-rpath,'$$ORIGIN' $(CUDA_LIBS) $(LDFLAGS)
+
+# headers, library, tools and a CMake package file (find_package(dccl))
+install: all
+	install -d $(PREFIX)/include/dccl $(PREFIX)/lib $(PREFIX)/bin $(PREFIX)/lib/cmake/dccl
+	install -m 644 include/dccl/dccl.hpp $(PREFIX)/include/dccl/
+	install -m 755 $(LIB) $(PREFIX)/lib/
+	install -m 755 $(TOOLS) $(PREFIX)/bin/
+	sed 's/@CACHELINE@/$(CACHELINE)/' dcclConfig.cmake.in > $(PREFIX)/lib/cmake/dccl/dcclConfig.cmake
 
 clean:
 	rm -rf build build-address build-thread build-undefined dccl_b200/lib

@@ -13,6 +13,7 @@
 #include "../core/config.hpp"
 #include "../core/log.hpp"
 #include "../core/types.hpp"
+#include <nvtx3/nvToolsExt.h>
 
 namespace dccl {
 
@@ -47,6 +48,13 @@ CollArgs GpuCommImpl::base_args(const void* send, void* recv, ncclRedOp_t op, in
     return a;
 }
 
+/** Stamps the device time line around one API call when DCCL/device_stamps is on, and opens an NVTX range. */
+struct CallScope {
+    GpuCommImpl* g; cudaStream_t s; uint64_t coll;
+    CallScope(GpuCommImpl* g_, cudaStream_t s_, uint64_t coll_, const char* name) : g(g_), s(s_), coll(coll_) { nvtxRangePushA(name); g->stamp_begin(s, coll); }
+    ~CallScope() { g->stamp_end(s, coll); nvtxRangePop(); }
+};
+
 #define NEXT_SEQ(a)                                   \
     do {                                              \
         if (++seq_ == 0) ++seq_;                      \
@@ -66,6 +74,7 @@ ncclResult_t GpuCommImpl::all_reduce(const void* send, void* recv, size_t count,
     ncclResult_t pre = precheck();
     if (pre != ncclSuccess) return pre;
     if (!count) return ncclSuccess;
+    CallScope scope(this, stream, COLL_ALLREDUCE, "dccl:allreduce");
 
     const bool nvls_ok = pool_.mc_base != nullptr && nvls_supports(dt, op);
     // both buffers in multicast-bound symmetric memory: the switch variant can run without copies
@@ -154,6 +163,7 @@ ncclResult_t GpuCommImpl::reduce_scatter(const void* send, void* recv, size_t re
     ncclResult_t pre = precheck();
     if (pre != ncclSuccess) return pre;
     if (!recvcount) return ncclSuccess;
+    CallScope scope(this, stream, COLL_REDUCESCATTER, "dccl:reducescatter");
     const size_t bytes = recvcount * es * (size_t)n_;
     const bool nvls_ok = pool_.mc_base != nullptr && nvls_supports(dt, op);
     TuneChoice ch = tuner_.choose(COLL_REDUCESCATTER, n_, bytes, nvls_ok);
@@ -229,6 +239,7 @@ ncclResult_t GpuCommImpl::all_gather(const void* send, void* recv, size_t sendco
     ncclResult_t pre = precheck();
     if (pre != ncclSuccess) return pre;
     if (!sendcount) return ncclSuccess;
+    CallScope scope(this, stream, COLL_ALLGATHER, "dccl:allgather");
     const size_t bytes = sendcount * es * (size_t)n_;
     const bool nvls_ok = pool_.mc_base != nullptr;
     TuneChoice ch = tuner_.choose(COLL_ALLGATHER, n_, bytes, nvls_ok);
@@ -296,6 +307,7 @@ ncclResult_t GpuCommImpl::broadcast(const void* send, void* recv, size_t count, 
     ncclResult_t pre = precheck();
     if (pre != ncclSuccess) return pre;
     if (!count) return ncclSuccess;
+    CallScope scope(this, stream, COLL_BROADCAST, "dccl:broadcast");
     const bool nvls_ok = pool_.mc_base != nullptr;
     TuneChoice ch = tuner_.choose(COLL_BROADCAST, n_, bytes, nvls_ok);
     if (algo != ALGO_AUTO) ch.algo = algo;
@@ -361,6 +373,7 @@ ncclResult_t GpuCommImpl::reduce(const void* send, void* recv, size_t count, ncc
     ncclResult_t pre = precheck();
     if (pre != ncclSuccess) return pre;
     if (!count) return ncclSuccess;
+    CallScope scope(this, stream, COLL_REDUCE, "dccl:reduce");
     const bool nvls_ok = pool_.mc_base != nullptr && nvls_supports(dt, op);
     TuneChoice ch = tuner_.choose(COLL_REDUCE, n_, bytes, nvls_ok);
     if (algo != ALGO_AUTO) ch.algo = algo;

@@ -57,6 +57,7 @@ bool GpuCommImpl::init(std::string* err) {
     set_param("unroll", (int)cfg.get_int("DCCL/unroll", 8));
     pipe_min_bytes_ = (size_t)cfg.get_int("DCCL/nvls_pipe_min_bytes", 16ll << 20);
     pipe_ctas_ = (int)cfg.get_int("DCCL/nvls_pipe_ctas", 144);
+    device_stamps_ = cfg.get_bool("DCCL/device_stamps", false);
     if (p2p_ctas_ < 1) p2p_ctas_ = 1;
     if (p2p_ctas_ > kP2pCtas) p2p_ctas_ = kP2pCtas;
     stage_bytes_ = (size_t)cfg.get_int("DCCL/staging_bytes", 256ll << 20);
@@ -127,6 +128,24 @@ GpuCommImpl::~GpuCommImpl() {
     }
     if (status_host_) cudaFreeHost(status_host_);
     cudaGetLastError();
+}
+
+/* ---------------- stream-time stamps ---------------- */
+
+struct StampMsg { uint64_t tag, rank, extra; };
+
+static void CUDART_CB stamp_callback(void* p) {
+    StampMsg* m = (StampMsg*)p;
+    Timestamp::log(m->tag, m->rank, m->extra);
+    delete m;
+}
+
+void GpuCommImpl::stamp(cudaStream_t stream, uint64_t tag, uint64_t extra) {
+    if (!device_stamps_) return;
+    // a host function in the stream runs when the work before it has finished: TT_DEVICE_KERNEL_BEGIN right
+    // before the collective's kernel may start, TT_DEVICE_KERNEL_END right after it has completed
+    StampMsg* m = new StampMsg{tag, (uint64_t)rank_, extra};
+    if (cudaLaunchHostFunc(stream, stamp_callback, m) != cudaSuccess) { cudaGetLastError(); delete m; }
 }
 
 /* ---------------- errors ---------------- */

@@ -61,6 +61,12 @@ private:
     bool sym_view(const void* p, size_t bytes, const char** peers, const char** mc) const;
     int ctas_for(int tuned) const;
     ncclResult_t p2p_launch(std::vector<P2pOp>& ops, cudaStream_t stream);
+    /** With DCCL/device_stamps on: log a timestamp when `stream` reaches this point (kernel begin / end on the device time line). */
+    void stamp(cudaStream_t stream, uint64_t tag, uint64_t extra);
+public:
+    void stamp_begin(cudaStream_t s, uint64_t coll) { stamp(s, TT_DEVICE_KERNEL_BEGIN, coll); }
+    void stamp_end(cudaStream_t s, uint64_t coll) { stamp(s, TT_DEVICE_KERNEL_END, coll); }
+private:
 
     Bootstrap* bs_;
     int dev_, rank_, n_;
@@ -82,6 +88,7 @@ private:
     int pipe_ctas_ = 144;
     int unroll_ = 8;
     bool sticky_error_ = false;
+    bool device_stamps_ = false;
     std::vector<SymSegment> user_segs_;
     std::vector<RegisteredBuffer> regs_;
     std::map<std::string, void*> ipc_opened_;   // handle bytes -> mapping, one open per allocation

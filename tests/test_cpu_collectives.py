@@ -113,3 +113,32 @@ def test_cfg_directory_recipe(build_dir, tmp_path):
     outs = [p.communicate(timeout=60)[0] for p in procs]
     for r, o in enumerate(outs):
         assert "world size = 3, my rank = %d" % r in o
+
+
+def test_p2p_perf_host_mode(build_dir, tmp_path):
+    """Windowed send/recv throughput tool between rank 0 and 1 over the host path; writes oob.dat."""
+    tool = os.path.join(build_dir, "p2p_perf")
+    dirs = []
+    for r in range(2):
+        d = tmp_path / ("r%d" % r)
+        d.mkdir()
+        dirs.append(d)
+    import subprocess
+    from dccl_b200.utils.launch import free_port
+    port = free_port()
+    procs = []
+    for r in range(2):
+        env = dict(os.environ, DCCL_RANK=str(r), DCCL_WORLD_SIZE="2", DCCL_MASTER_PORT=str(port), DCCL_MASTER_ADDR="127.0.0.1")
+        procs.append(subprocess.Popen([tool, "-t", "p2p", "-s", "65536", "-d", "4", "-w", "0.2", "-D", "0.5"], cwd=str(dirs[r]), env=env,
+                                      stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True))
+    outs = [p.communicate(timeout=60) for p in procs]
+    assert all(p.returncode == 0 for p in procs), outs
+    assert "Evaluating transport performance with the following configuration:" in outs[0][0]
+    assert "GB/s" in outs[0][0] and "received" in outs[1][0]
+    from dccl_b200.utils import tt
+    declared, rows = tt.read_tt(str(dirs[0] / "oob.dat"))
+    tags = [x[0] for x in rows]
+    assert declared == len(rows) and tags[0] == 2000001 and 2000004 in tags and tags.count(2001001) >= 8
+    # missing --transport: exit 1 with the help text
+    p = subprocess.run([tool], capture_output=True, text=True)
+    assert p.returncode == 1 and "--transport" in p.stdout + p.stderr
