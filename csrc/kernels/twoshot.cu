@@ -47,6 +47,55 @@ __global__ void __launch_bounds__(512) k_twoshot(const __grid_constant__ CollArg
     auto lo_of = [&](int j) { size_t l = g.len(j); return g.blo < l ? g.blo : l; };
     auto hi_of = [&](int j) { size_t l = g.len(j); return g.bhi < l ? g.bhi : l; };
 
+    /* ---- large reduce-scatter: push and reduce overlap ---- */
+    // The CTA's range is cut into K pieces. Piece k+1 is pushed to the peers (posted remote stores) before
+    // piece k, which every peer has signalled by then, is folded from staging: the NVLink writes of one
+    // piece are in flight while the HBM reads of the previous one run. All ranks derive the same K.
+    if (mode == TS_REDUCESCATTER) {
+        constexpr size_t VE = Geometry<T>::VE;
+        const size_t lo0 = lo_of(0), hi0 = hi_of(0);          // all shards have the same length here
+        const size_t span = g.bhi - g.blo;                     // derived from geometry only: equal on all ranks
+        int K = (int)(span * sizeof(T) / (256u << 10));
+        if (K > 12) K = 12;
+        if (K >= 2) {
+            const size_t piece = ((span + K - 1) / K + VE - 1) / VE * VE;
+            auto piece_lo = [&](int k) { size_t v = g.blo + piece * (size_t)k; return v < hi0 ? (v > lo0 ? v : lo0) : hi0; };
+            auto push = [&](int k) {
+                const size_t lo = piece_lo(k), hi = piece_lo(k + 1);
+                if (hi > lo)
+                    for (int q = 1; q < n; q++) {
+                        const int p = (r + q) % n;
+                        copy_range<T>(stage_ptr<T>(c, p, a.parity) + (size_t)r * g.slot_stride + lo, send + (size_t)p * stride + lo, hi - lo);
+                    }
+                __syncthreads();
+                if ((int)threadIdx.x < n) signal_peer(c, (int)threadIdx.x, x.bid, a.seq, k);
+            };
+            auto fold = [&](int k) -> bool {
+                __shared__ int s_fail;
+                if (threadIdx.x == 0) s_fail = 0;
+                __syncthreads();
+                if ((int)threadIdx.x < n && !wait_peer(c, (int)threadIdx.x, x.bid, a.seq, k, 150)) s_fail = 1;
+                __syncthreads();
+                if (s_fail) return false;
+                const size_t lo = piece_lo(k), hi = piece_lo(k + 1);
+                if (hi > lo) {
+                    const T* ins[kMaxPeers];
+                    int cnt = 0;
+                    for (int p = 0; p < n; p++) if (p != r) ins[cnt++] = my_stage + (size_t)p * g.slot_stride + lo;
+                    reduce_range<T, OP>(recv + lo, nullptr, send + (size_t)r * stride + lo, ins, cnt, hi - lo, avg, n);
+                }
+                return true;
+            };
+            push(0);
+            for (int k = 1; k < K; k++) {
+                push(k);
+                if (!fold(k - 1)) return;
+            }
+            fold(K - 1);
+            return;
+        }
+    }
+
     /* ---- phase 0 ---- */
     if (mode == TS_ALLREDUCE || mode == TS_REDUCESCATTER || mode == TS_REDUCE) {
         for (int k = 1; k < n; k++) {

@@ -180,3 +180,15 @@ def test_bounded_wait_returns_a_status(dccl_lib):
     a = np.ones(1000, dtype=np.float32)
     b = np.ones(1000, dtype=np.float32)
     assert dccl_lib.dccl_local_reduce(a.ctypes.data, b.ctypes.data, 1000, 7, 0) == 0 and np.all(a == 2.0)
+
+
+def test_large_reduce_scatter_overlaps_push_and_reduce(dccl_lib):
+    """Ranges above 512 KB per CTA take the pipelined path (pieces pushed ahead of the fold)."""
+    for n, count, ctas in [(4, (1 << 20) + 7, 3), (8, 300000, 1), (2, (2 << 20) + 3, 2)]:
+        for name, op in [("float32", "sum"), ("bfloat16", "avg"), ("int32", "max")]:
+            ins = inputs_for(name, op, count * n, n, seed=29)
+            want = oracle.fold(ins, op, bf16=name == "bfloat16")
+            for in_place in [0, 1]:
+                out = emu(dccl_lib, "reducescatter", "twoshot", n, name, op, count, ins, ctas=ctas, in_place=in_place, stage=96 << 20)
+                for r in range(n):
+                    assert close(out[r], want[r * count:(r + 1) * count], name, n), (n, count, name, op, r, in_place)
