@@ -15,9 +15,9 @@ def free_port():
         return s.getsockname()[1]
 
 
-def spawn_ranks(argv, world, env_extra=None, per_rank_env=None, timeout=300, cwd=None, gpus=False):
-    """Run ``argv`` once per rank; returns a list of CompletedProcess (stdout/stderr captured).
-    A rank that outlives ``timeout`` is killed (only the processes started here)."""
+def spawn_ranks(argv, world, env_extra=None, per_rank_env=None, timeout=300, cwd=None, gpus=False, per_rank_argv=None):
+    """Run ``argv`` (or ``per_rank_argv[rank]`` where given) once per rank; returns a list of CompletedProcess
+    (stdout/stderr captured). A rank that outlives ``timeout`` is killed (only the processes started here)."""
     port = free_port()
     procs = []
     for r in range(world):
@@ -32,7 +32,8 @@ def spawn_ranks(argv, world, env_extra=None, per_rank_env=None, timeout=300, cwd
             env.update(env_extra)
         if per_rank_env and r in per_rank_env:
             env.update(per_rank_env[r])
-        procs.append(subprocess.Popen(argv, env=env, cwd=cwd, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True))
+        cmd = per_rank_argv[r] if per_rank_argv and r in per_rank_argv else argv
+        procs.append(subprocess.Popen(cmd, env=env, cwd=cwd, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True))
     results = []
     for p in procs:
         try:
