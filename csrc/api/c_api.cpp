@@ -105,7 +105,7 @@ int dccl_config_parse_world(const char* json) { return Config::world_size_from_l
 static Tuner& test_tuner() { static Tuner t; return t; }
 int dccl_tuner_load_text(const char* text) { std::string err; return test_tuner().load_text(text, &err); }
 int dccl_tuner_choose(const char* coll, int nranks, size_t bytes, int nvls_ok, char* algo_out, size_t len, int* ctas) {
-    int c = coll && !strcmp(coll, "allreduce_sym") ? TUNE_ALLREDUCE_SYM : parse_collective_name(coll);
+    int c = coll && !strcmp(coll, "allreduce_sym") ? TUNE_ALLREDUCE_SYM : coll && !strcmp(coll, "reducescatter_sym") ? TUNE_REDUCESCATTER_SYM : parse_collective_name(coll);
     if (c < 0) return -1;
     TuneChoice ch = test_tuner().choose(c, nranks, bytes, nvls_ok != 0);
     if (algo_out && len) snprintf(algo_out, len, "%s", algo_name(ch.algo));

@@ -166,7 +166,11 @@ ncclResult_t GpuCommImpl::reduce_scatter(const void* send, void* recv, size_t re
     CallScope scope(this, stream, COLL_REDUCESCATTER, "dccl:reducescatter");
     const size_t bytes = recvcount * es * (size_t)n_;
     const bool nvls_ok = pool_.mc_base != nullptr && nvls_supports(dt, op);
-    TuneChoice ch = tuner_.choose(COLL_REDUCESCATTER, n_, bytes, nvls_ok);
+    // a send buffer in multicast-bound symmetric memory can be reduced by the switch where it lies
+    const char* sym_peers[kMaxPeers];
+    const char* sym_mc = nullptr;
+    const bool sym = nvls_ok && (recvcount * es) % 16 == 0 && sym_view(send, bytes, sym_peers, &sym_mc) && sym_mc && (uintptr_t)sym_mc % 16 == 0;
+    TuneChoice ch = tuner_.choose(sym ? TUNE_REDUCESCATTER_SYM : COLL_REDUCESCATTER, n_, bytes, nvls_ok);
     if (algo != ALGO_AUTO) ch.algo = algo;
     if (ch.algo == ALGO_NVLS && !nvls_ok) ch.algo = ALGO_TWOSHOT;
     if (ch.algo == ALGO_ONESHOT && recvcount * es > oneshot_ll_capacity_bytes()) ch.algo = ALGO_TWOSHOT;
@@ -188,11 +192,9 @@ ncclResult_t GpuCommImpl::reduce_scatter(const void* send, void* recv, size_t re
         return cuda_result(launch_ll_collective(a, dt, cfg), "packet reduce-scatter");
     }
     if (ch.algo == ALGO_NVLS) {
-        const char* sp[kMaxPeers];
-        const char* smc = nullptr;
-        if ((recvcount * es) % 16 == 0 && sym_view(send, bytes, sp, &smc) && smc && (uintptr_t)smc % 16 == 0) {
+        if (sym) {
             a.symmetric = 1;
-            a.io.send_mc = smc;
+            a.io.send_mc = sym_mc;
             a.mode = NV_REDUCESCATTER;
             a.count = recvcount;
             NEXT_SEQ(a);

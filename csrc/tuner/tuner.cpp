@@ -22,6 +22,11 @@ static const TuneRule kBuiltin[] = {
     // all-reduce, symmetric buffers: zero-copy switch variant; 8-32 CTAs saturate it, more only add contention
     {TUNE_ALLREDUCE_SYM, 0, 64u << 10, ALGO_ONESHOT, 8},
     {TUNE_ALLREDUCE_SYM, 0, kInf, ALGO_NVLS, 16},
+    // reduce-scatter from a symmetric send buffer: in-switch reduction straight out of the user's memory wins from 64 MB on
+    {TUNE_REDUCESCATTER_SYM, 0, 256u << 10, ALGO_ONESHOT, 8},
+    {TUNE_REDUCESCATTER_SYM, 0, 1u << 20, ALGO_TWOSHOT, 32},
+    {TUNE_REDUCESCATTER_SYM, 0, 48u << 20, ALGO_TWOSHOT, 128},
+    {TUNE_REDUCESCATTER_SYM, 0, kInf, ALGO_NVLS, 64},
     {COLL_REDUCESCATTER, 0, 256u << 10, ALGO_ONESHOT, 8},
     {COLL_REDUCESCATTER, 0, 1u << 20, ALGO_TWOSHOT, 32},
     {COLL_REDUCESCATTER, 0, kInf, ALGO_TWOSHOT, 128},
@@ -84,7 +89,7 @@ int Tuner::load_text(const std::string& text, std::string* err) {
         if (!(ls >> coll)) continue;
         if (!(ls >> nr >> mb >> algo >> ctas)) { if (err) *err += "line " + std::to_string(lineno) + ": expected 5 fields; "; continue; }
         TuneRule r;
-        r.coll = coll == "allreduce_sym" ? TUNE_ALLREDUCE_SYM : parse_collective_name(coll.c_str());
+        r.coll = coll == "allreduce_sym" ? TUNE_ALLREDUCE_SYM : coll == "reducescatter_sym" ? TUNE_REDUCESCATTER_SYM : parse_collective_name(coll.c_str());
         r.nranks = nr == "*" ? 0 : atoi(nr.c_str());
         r.algo = parse_algo_name(algo.c_str());
         r.ctas = ctas;

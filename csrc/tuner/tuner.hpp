@@ -12,7 +12,8 @@
  *
  * <collective> is allreduce, reducescatter, allgather, broadcast, reduce, or
  * allreduce_sym (all-reduce whose buffers live in symmetric memory, where the
- * switch variant copies nothing and wants fewer CTAs).
+ * switch variant copies nothing and wants fewer CTAs), or reducescatter_sym
+ * (reduce-scatter whose send buffer is symmetric memory).
  *
  * Rules of one (collective, nranks) are tried in ascending max_bytes; the
  * first whose max_bytes >= message bytes wins (max_bytes accepts k/m/g
@@ -28,7 +29,9 @@ namespace dccl {
 
 /** Extra table key: all-reduce on symmetric (dcclMemAlloc) buffers. */
 constexpr int TUNE_ALLREDUCE_SYM = COLL_COUNT;
-constexpr int TUNE_KEYS = COLL_COUNT + 1;
+/** Extra table key: reduce-scatter whose send buffer is symmetric memory (the switch can read it in place). */
+constexpr int TUNE_REDUCESCATTER_SYM = COLL_COUNT + 1;
+constexpr int TUNE_KEYS = COLL_COUNT + 2;
 
 struct TuneRule {
     int coll;

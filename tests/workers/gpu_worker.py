@@ -127,6 +127,23 @@ def main():
             comm.all_reduce(t, op="avg")
             torch.cuda.synchronize()
             check(close(to_numpy(t, name), want, name, world), "symmetric all_reduce %s" % name)
+            # reduce-scatter straight out of the symmetric buffer, all-gather straight into one
+            per = count // world
+            t.copy_(to_torch(ins[rank], name, dev))
+            torch.cuda.synchronize()
+            comm.set_algorithm("reducescatter", "nvls")
+            out = torch.zeros(per, dtype=TORCH[name], device=dev)
+            comm.reduce_scatter(t, out, op="sum")
+            torch.cuda.synchronize()
+            wsum = oracle.fold(ins, "sum", bf16=name == "bfloat16")
+            check(close(to_numpy(out, name), wsum[rank * per:(rank + 1) * per], name, world), "symmetric reduce_scatter %s (ran %s)" % (name, comm.last_algorithm("reducescatter")))
+            comm.set_algorithm("allgather", "nvls")
+            mine = to_torch(ins[rank][:per], name, dev)
+            comm.all_gather(mine, t)
+            torch.cuda.synchronize()
+            check(np.array_equal(to_numpy(t, name), np.concatenate([x[:per] for x in ins])), "symmetric all_gather %s" % name)
+            comm.set_algorithm("reducescatter", "auto")
+            comm.set_algorithm("allgather", "auto")
             comm.free_symmetric(t)
         comm.set_algorithm("allreduce", "auto")
 
