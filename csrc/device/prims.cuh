@@ -23,7 +23,7 @@ constexpr int kFlagVals = 32;           // flag values reserved per collective c
 
 /* ---- symmetric pool layout (byte offsets from the pool base) ---- */
 constexpr size_t kFlagOff = 0;                          // uint32 flags[kMaxCtas][kMaxPeers]
-constexpr size_t kP2pFlagOff = 16u << 10;               // uint64 head[kMaxPeers][kP2pCtas], tail[kMaxPeers][kP2pCtas]
+constexpr size_t kP2pFlagOff = 16u << 10;               // uint64 head[kMaxPeers][kP2pDepth][kP2pCtas], then tail[...] likewise
 constexpr int kP2pCtas = 32;                            // CTAs that can serve one direction of a pair
 constexpr size_t kLLOff = 64u << 10;                    // flag-in-data packets
 constexpr size_t kLLSlotBytes = 256u << 10;             // packets per source rank (half of it is payload)
@@ -35,6 +35,7 @@ constexpr int kP2pDepth = 4;
 constexpr size_t kP2pBytesPerSrc = kP2pChunk * kP2pDepth;
 constexpr size_t kStageOff = 64u << 20;                 // two staging halves follow
 static_assert(kLLOff + kLLBytes <= kP2pOff, "LL region overlaps the p2p FIFOs");
+static_assert(kP2pFlagOff + 2 * kMaxPeers * 4 * kP2pCtas * 8 <= kLLOff, "p2p flag words overlap the packet region");
 static_assert(kP2pOff + kMaxPeers * kP2pBytesPerSrc <= kStageOff, "p2p FIFOs overlap the staging area");
 
 /* ---- status block (pinned host memory, or device memory in single-GPU emulation) ---- */

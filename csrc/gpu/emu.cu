@@ -189,38 +189,39 @@ int dccl_emu_collective(const char* kind_s, const char* algo_s, int nranks, int 
 }
 
 /**
- * Ring of send/recv pairs among virtual ranks: rank r sends `bytes` to r+1 and receives from r-1,
- * `iters` times, all in one launch per iteration (the grouped form). host_in: nranks messages;
- * host_out: what each rank received last.
+ * Ring of send/recv pairs among virtual ranks: rank r sends `window` messages of `bytes` to r+1 and receives
+ * `window` messages from r-1, `iters` times, all in one launch per iteration (the grouped form; several
+ * operations address the same peer). host_in: nranks x window messages; host_out: what each rank received last.
  */
-int dccl_emu_sendrecv_ring(int nranks, size_t bytes, int ctas_per_op, int iters, const void* host_in, void* host_out) {
-    if (nranks < 2 || nranks > kMaxPeers || ctas_per_op < 1 || ctas_per_op > kP2pCtas) return -2;
+int dccl_emu_sendrecv_ring(int nranks, size_t bytes, int window, int ctas_per_op, int iters, const void* host_in, void* host_out) {
+    if (nranks < 2 || nranks > kMaxPeers || ctas_per_op < 1 || ctas_per_op > kP2pCtas || window < 1 || 2 * window > kMaxP2pOps) return -2;
     EmuWorld w;
     if (!w.create(nranks, 1u << 20, 2000)) return fail("cannot create the virtual ranks");
-    const size_t n = (size_t)nranks;
+    const size_t n = (size_t)nranks, W = (size_t)window;
     std::vector<char*> sb(n), rb(n);
     for (size_t r = 0; r < n; r++) {
-        if (cudaMalloc((void**)&sb[r], bytes + 16) != cudaSuccess || cudaMalloc((void**)&rb[r], bytes + 16) != cudaSuccess) return fail("cudaMalloc");
-        cudaMemcpy(sb[r], (const char*)host_in + r * bytes, bytes, cudaMemcpyHostToDevice);
-        cudaMemset(rb[r], 0xEE, bytes);
+        if (cudaMalloc((void**)&sb[r], W * bytes + 16) != cudaSuccess || cudaMalloc((void**)&rb[r], W * bytes + 16) != cudaSuccess) return fail("cudaMalloc");
+        cudaMemcpy(sb[r], (const char*)host_in + r * W * bytes, W * bytes, cudaMemcpyHostToDevice);
+        cudaMemset(rb[r], 0xEE, W * bytes);
     }
     P2pOp* d_ops = nullptr;
     int* d_nops = nullptr;
     cudaMalloc((void**)&d_ops, n * kMaxP2pOps * sizeof(P2pOp));
     cudaMalloc((void**)&d_nops, n * sizeof(int));
-    std::vector<int> nops(n, 2);
+    std::vector<int> nops(n, 2 * window);
     cudaMemcpy(d_nops, nops.data(), n * sizeof(int), cudaMemcpyHostToDevice);
     int rc = 0;
     unsigned long long chunk_base = 0;
     for (int it = 0; it < iters && rc == 0; it++) {
         std::vector<P2pOp> ops(n * kMaxP2pOps);
-        for (size_t r = 0; r < n; r++) {
-            P2pOp& s = ops[r * kMaxP2pOps];
-            P2pOp& d = ops[r * kMaxP2pOps + 1];
-            s.is_send = 1; s.peer = (int)((r + 1) % n); s.buf = sb[r]; s.bytes = bytes; s.chunk_base = chunk_base;
-            d.is_send = 0; d.peer = (int)((r + n - 1) % n); d.buf = rb[r]; d.bytes = bytes; d.chunk_base = chunk_base;
-        }
-        chunk_base += p2p_chunks(bytes);
+        for (size_t r = 0; r < n; r++)
+            for (size_t k = 0; k < W; k++) {
+                P2pOp& s = ops[r * kMaxP2pOps + 2 * k];
+                P2pOp& d = ops[r * kMaxP2pOps + 2 * k + 1];
+                s.is_send = 1; s.peer = (int)((r + 1) % n); s.buf = sb[r] + k * bytes; s.bytes = bytes; s.chunk_base = chunk_base + k * p2p_chunks(bytes);
+                d.is_send = 0; d.peer = (int)((r + n - 1) % n); d.buf = rb[r] + k * bytes; d.bytes = bytes; d.chunk_base = chunk_base + k * p2p_chunks(bytes);
+            }
+        chunk_base += W * p2p_chunks(bytes);
         cudaMemcpy(d_ops, ops.data(), ops.size() * sizeof(P2pOp), cudaMemcpyHostToDevice);
         P2pArgs a;
         memset(&a, 0, sizeof(a));
@@ -228,7 +229,7 @@ int dccl_emu_sendrecv_ring(int nranks, size_t bytes, int ctas_per_op, int iters,
         a.emu_ops = d_ops;
         a.emu_nops = d_nops;
         a.ctas_per_op = ctas_per_op;
-        a.ctas_per_rank = 2 * ctas_per_op;
+        a.ctas_per_rank = 2 * window * ctas_per_op;
         LaunchCfg cfg;
         cfg.ctas = a.ctas_per_rank;
         cfg.ranks_in_launch = nranks;
@@ -237,7 +238,7 @@ int dccl_emu_sendrecv_ring(int nranks, size_t bytes, int ctas_per_op, int iters,
         cudaMemcpy(st, w.status, sizeof(st), cudaMemcpyDeviceToHost);
         if (st[ST_CODE] != DEV_OK) rc = 100 + (int)st[ST_CODE];
     }
-    if (rc == 0) for (size_t r = 0; r < n; r++) cudaMemcpy((char*)host_out + r * bytes, rb[r], bytes, cudaMemcpyDeviceToHost);
+    if (rc == 0) for (size_t r = 0; r < n; r++) cudaMemcpy((char*)host_out + r * W * bytes, rb[r], W * bytes, cudaMemcpyDeviceToHost);
     for (size_t r = 0; r < n; r++) { cudaFree(sb[r]); cudaFree(rb[r]); }
     cudaFree(d_ops);
     cudaFree(d_nops);

@@ -8,7 +8,7 @@
  * FIFO over NVLink and bumps a head counter there; the receiver's kernel
  * copies chunks out as they arrive and returns credit through a tail counter
  * in the sender's pool. Matching is FIFO per peer, like the original; the
- * counters are cumulative chunk numbers, so nothing is ever reset. A send of
+ * counters are cumulative chunk numbers, one pair per FIFO slot, so nothing is ever reset. A send of
  * up to kP2pDepth chunks completes without the receiver having started.
  * Several sends and receives recorded between dcclGroupStart/End run in ONE
  * launch with a group of CTAs per operation, so a ring in which every rank
@@ -19,11 +19,13 @@
 
 namespace dccl {
 
-__device__ __forceinline__ unsigned long long* p2p_head(char* pool, int src, int cta) {
-    return reinterpret_cast<unsigned long long*>(pool + kP2pFlagOff) + (src * kP2pCtas + cta);
+// One head and one tail word per (peer, FIFO slot, CTA): several operations of one launch may address the
+// same peer (a window of sends), each works on its own slot and must not see another slot's progress.
+__device__ __forceinline__ unsigned long long* p2p_head(char* pool, int src, unsigned long long chunk, int cta) {
+    return reinterpret_cast<unsigned long long*>(pool + kP2pFlagOff) + ((src * kP2pDepth + (int)(chunk % kP2pDepth)) * kP2pCtas + cta);
 }
-__device__ __forceinline__ unsigned long long* p2p_tail(char* pool, int dst, int cta) {
-    return reinterpret_cast<unsigned long long*>(pool + kP2pFlagOff) + (kMaxPeers * kP2pCtas + dst * kP2pCtas + cta);
+__device__ __forceinline__ unsigned long long* p2p_tail(char* pool, int dst, unsigned long long chunk, int cta) {
+    return reinterpret_cast<unsigned long long*>(pool + kP2pFlagOff) + (kMaxPeers * kP2pDepth * kP2pCtas + (dst * kP2pDepth + (int)(chunk % kP2pDepth)) * kP2pCtas + cta);
 }
 __device__ __forceinline__ char* p2p_fifo(char* pool, int src, unsigned long long chunk) {
     return pool + kP2pOff + (size_t)src * kP2pBytesPerSrc + (size_t)(chunk % kP2pDepth) * kP2pChunk;
@@ -65,23 +67,23 @@ __global__ void __launch_bounds__(512) k_p2p(const __grid_constant__ P2pArgs a) 
             if (threadIdx.x == 0) {
                 s_ok = 1;
                 if (G >= (unsigned long long)kP2pDepth)   // wait until the slot's previous tenant was consumed
-                    s_ok = wait_flag64_ge(c, p2p_tail(c.pool[r], peer, b), G - kP2pDepth + 1, peer, 800, 0) ? 1 : 0;
+                    s_ok = wait_flag64_ge(c, p2p_tail(c.pool[r], peer, G, b), G - kP2pDepth + 1, peer, 800, 0) ? 1 : 0;
             }
             __syncthreads();
             if (!s_ok) return;
             if (hi > lo) copy_bytes(p2p_fifo(c.pool[peer], r, G) + lo, op.buf + coff + lo, hi - lo);
             __syncthreads();
             if (threadIdx.x == 0) {
-                st_release_sys64(p2p_head(c.pool[peer], r, b), G + 1);
+                st_release_sys64(p2p_head(c.pool[peer], r, G, b), G + 1);
             }
         } else {
-            if (threadIdx.x == 0) s_ok = wait_flag64_ge(c, p2p_head(c.pool[r], peer, b), G + 1, peer, 810, 0) ? 1 : 0;
+            if (threadIdx.x == 0) s_ok = wait_flag64_ge(c, p2p_head(c.pool[r], peer, G, b), G + 1, peer, 810, 0) ? 1 : 0;
             __syncthreads();
             if (!s_ok) return;
             if (hi > lo) copy_bytes(op.buf + coff + lo, p2p_fifo(c.pool[r], peer, G) + lo, hi - lo);
             __syncthreads();
             if (threadIdx.x == 0) {
-                st_release_sys64(p2p_tail(c.pool[peer], r, b), G + 1);
+                st_release_sys64(p2p_tail(c.pool[peer], r, G, b), G + 1);
             }
         }
     }

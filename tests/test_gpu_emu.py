@@ -147,16 +147,19 @@ def test_many_ctas_and_small_staging(dccl_lib):
 
 
 def test_send_recv_ring(dccl_lib):
-    for n in [2, 8]:
+    for n, window in [(2, 1), (8, 1), (2, 4), (4, 3)]:
+        # window > 1: several operations of one launch address the same peer (each works on its own FIFO slot)
         for nbytes in [4, 1000, (1 << 20) + 24, 5 * (1 << 20) + 8]:   # the last one is longer than the FIFO: needs flow control
+            if window > 1 and nbytes > (2 << 20):
+                continue
             rng = np.random.default_rng(nbytes)
-            hin = rng.integers(0, 256, n * nbytes, dtype=np.uint8)
+            hin = rng.integers(0, 256, n * window * nbytes, dtype=np.uint8)
             hout = np.zeros_like(hin)
-            rc = dccl_lib.dccl_emu_sendrecv_ring(n, nbytes, 4, 3, hin.ctypes.data, hout.ctypes.data)
+            rc = dccl_lib.dccl_emu_sendrecv_ring(n, nbytes, window, 4, 3, hin.ctypes.data, hout.ctypes.data)
             assert rc == 0
-            hin, hout = hin.reshape(n, nbytes), hout.reshape(n, nbytes)
+            hin, hout = hin.reshape(n, window * nbytes), hout.reshape(n, window * nbytes)
             for r in range(n):
-                assert np.array_equal(hout[r], hin[(r - 1) % n]), (n, nbytes, r)
+                assert np.array_equal(hout[r], hin[(r - 1) % n]), (n, window, nbytes, r)
 
 
 def test_local_reduce_every_dtype_and_operator(dccl_lib):
