@@ -30,7 +30,7 @@ sys.path.insert(0, ROOT)
 
 METRIC = "allreduce_busbw"
 UNAVAILABLE = ("the reference is a C++17/CMake library on top of Derecho, mutils, libfabric and spdlog; "
-               "'pip install /root/reference' fails (no setup.py / pyproject.toml) and its dependencies are not installable offline")
+               "'pip install' of the reference tree fails (no setup.py / pyproject.toml) and its dependencies are not installable offline")
 
 
 class ClockSampler:
@@ -225,7 +225,7 @@ def main():
     ap.add_argument("--dtype", default="bf16", choices=["bf16", "fp32"])
     ap.add_argument("--algo", default="auto")
     ap.add_argument("--sweep", action="store_true", help="also sweep sizes and variants; table goes to --out")
-    ap.add_argument("--out", default=os.path.join(ROOT, "gpurun_out", "sweep.json"))
+    ap.add_argument("--out", default=os.path.join(ROOT, "results", "sweep.json"))
     ap.add_argument("--sweep-extra", action="store_true", help="broadcast / reduce / send-recv ring / dtype x operator rows")
     ap.add_argument("--e2e-steps", type=int, default=5)
     ap.add_argument("--sweep-ctas", default="16,32,64,128")

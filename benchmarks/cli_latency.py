@@ -2,7 +2,7 @@
 """Small-message latency through the C tools (no Python in the loop): runs dccl_cli and its stock-NCCL
 twin nccl_cli on every visible GPU for a few sizes and prints their 'avg latency' lines as JSON.
 
-    python benchmarks/cli_latency.py --gpus 8 --out gpurun_out/cli_latency.json
+    python benchmarks/cli_latency.py --gpus 8 --out results/cli_latency.json
 """
 import argparse
 import glob
@@ -19,7 +19,7 @@ from dccl_b200.utils.launch import spawn_ranks  # noqa: E402
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=2)
-    ap.add_argument("--out", default=os.path.join(ROOT, "gpurun_out", "cli_latency.json"))
+    ap.add_argument("--out", default=os.path.join(ROOT, "results", "cli_latency.json"))
     args = ap.parse_args()
     env = {}
     cands = glob.glob(os.path.join(sys.prefix, "lib", "python*", "site-packages", "nvidia", "nccl", "lib", "libnccl.so.2"))

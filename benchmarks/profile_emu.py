@@ -3,7 +3,7 @@
 ncu capture: inputs larger than L2, a few GB on the device at most, two launches.
 
     python benchmarks/profile_emu.py --kind allreduce --algo twoshot --ranks 8 --mb 64 --ctas 16
-    ncu --set full --clock-control none -k regex:k_twoshot -c 1 -o gpurun_out/prof_twoshot \\
+    ncu --set full --clock-control none -k regex:k_twoshot -c 1 -o prof_twoshot \\
         python benchmarks/profile_emu.py --kind allreduce --algo twoshot --ranks 8 --mb 64 --ctas 16
 """
 import argparse

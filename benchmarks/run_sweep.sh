@@ -1,6 +1,6 @@
 #!/bin/bash
 # Bus-bandwidth sweep of this library against stock NCCL on N GPUs of this machine, one process per GPU.
-#   benchmarks/run_sweep.sh 8 [extra dccl_sweep options]     e.g.  --symmetric --out gpurun_out/sweep.json
+#   benchmarks/run_sweep.sh 8 [extra dccl_sweep options]     e.g.  --symmetric --out results/sweep.json
 # The single-box counterpart of the original's cluster run scripts (reference scripts/run_ompi_cli_4.1.5.sh,
 # scripts/azure/run_dccl.sh): same tool on every rank, results collected by rank 0.
 set -e
