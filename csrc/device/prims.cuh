@@ -52,6 +52,11 @@ struct DevComm {
     const uint32_t* abort_word;   // non-zero: stop waiting
     unsigned long long timeout_ns;
     size_t stage_bytes;           // bytes of one staging half
+    // Sequence number kept on the device (nullptr: the host counts and passes it with every launch).
+    // seq_word holds the number of the NEXT call; the last CTA of a call to finish advances it, so a
+    // captured launch can be replayed without the host knowing how often it ran.
+    uint32_t* seq_word;
+    uint32_t* done_word;          // CTAs of the running call that have finished
 };
 
 /** User buffers of one (virtual) rank. */
@@ -89,6 +94,8 @@ struct Ctx {
     const RankIO* io;
     int bid;               // CTA index within the rank
     int nb;                // CTAs per rank
+    uint32_t seq;          // sequence number of this call (from the host, or read from the device counter)
+    int parity;            // staging half / LL generation of this call
 };
 
 __device__ __forceinline__ Ctx make_ctx(const CollArgs& a) {
@@ -105,7 +112,32 @@ __device__ __forceinline__ Ctx make_ctx(const CollArgs& a) {
         x.bid = blockIdx.x;
         x.nb = gridDim.x;
     }
+    x.seq = a.seq;
+    x.parity = a.parity;
+    if (x.c->seq_word != nullptr) {
+        // every CTA of the call reads the same value: the counter only moves after all of them have finished
+        asm volatile("ld.volatile.global.u32 %0, [%1];" : "=r"(x.seq) : "l"(x.c->seq_word) : "memory");
+        x.parity = (int)(x.seq & 1u);
+    }
     return x;
+}
+
+/** Sequence number after `seq`; 0 is never used (a zeroed packet slot must not look like a valid tag). */
+__host__ __device__ __forceinline__ uint32_t next_seq(uint32_t seq) { return seq + 1u ? seq + 1u : 1u; }
+
+/** Last statement of every collective kernel. With a device-side sequence counter, the CTA that finishes
+ *  last advances it for the next call on the stream; with a host-side counter there is nothing to do. */
+__device__ __forceinline__ void finish_call(const Ctx& x) {
+    const DevComm& c = *x.c;
+    if (c.seq_word == nullptr) return;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence();
+        if (atomicAdd(c.done_word, 1u) == (uint32_t)(x.nb - 1)) {
+            *reinterpret_cast<volatile uint32_t*>(c.done_word) = 0u;
+            *reinterpret_cast<volatile uint32_t*>(c.seq_word) = next_seq(x.seq);
+        }
+    }
 }
 
 /* ---- system-scope memory operations ---- */

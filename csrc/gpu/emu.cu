@@ -23,14 +23,19 @@ using namespace dccl;
 
 namespace {
 
+// set by dccl_emu_set_device_seq: the virtual ranks keep their sequence numbers in device counters
+int g_device_seq = 0;
+
 struct EmuWorld {
     int n = 0;
     size_t stage_bytes = 0, pool_bytes = 0;
     std::vector<char*> pools;
     uint32_t* status = nullptr;      // device memory: ST_WORDS + abort word
     DevComm* d_comms = nullptr;
+    uint32_t* seq_words = nullptr;   // per virtual rank: {next sequence number, CTAs done}, 64 bytes apart
     std::vector<DevComm> comms;
     ~EmuWorld() {
+        if (seq_words) cudaFree(seq_words);
         for (char* p : pools) if (p) cudaFree(p);
         if (status) cudaFree(status);
         if (d_comms) cudaFree(d_comms);
@@ -46,10 +51,17 @@ struct EmuWorld {
         }
         if (cudaMalloc((void**)&status, (ST_WORDS + 8) * sizeof(uint32_t)) != cudaSuccess) return false;
         cudaMemset(status, 0, (ST_WORDS + 8) * sizeof(uint32_t));
+        if (g_device_seq) {
+            std::vector<uint32_t> init((size_t)n * 16, 0u);
+            for (int r = 0; r < n; r++) init[(size_t)r * 16] = 1u;   // the first call has number 1
+            if (cudaMalloc((void**)&seq_words, init.size() * sizeof(uint32_t)) != cudaSuccess) return false;
+            if (cudaMemcpy(seq_words, init.data(), init.size() * sizeof(uint32_t), cudaMemcpyHostToDevice) != cudaSuccess) return false;
+        }
         comms.resize(n);
         for (int r = 0; r < n; r++) {
             DevComm& c = comms[r];
             memset(&c, 0, sizeof(c));
+            if (seq_words) { c.seq_word = seq_words + (size_t)r * 16; c.done_word = c.seq_word + 1; }
             c.rank = r;
             c.nranks = n;
             for (int p = 0; p < n; p++) c.pool[p] = pools[p];
@@ -73,6 +85,10 @@ int fail(const char* what) {
 } // namespace
 
 extern "C" {
+
+/** 1: the emulated ranks count their calls in device memory (the mode that makes launches replayable
+ *  from a CUDA graph); the launch arguments then carry a wrong sequence number on purpose. 0: host counts. */
+void dccl_emu_set_device_seq(int on) { g_device_seq = on ? 1 : 0; }
 
 /**
  * Run `iters` back-to-back calls of one collective among `nranks` virtual ranks on the current
@@ -142,6 +158,7 @@ int dccl_emu_collective(const char* kind_s, const char* algo_s, int nranks, int 
         a.stride = count;
         a.seq = (uint32_t)(it + 1);
         a.parity = (int)(a.seq & 1u);
+        if (g_device_seq) { a.seq = 0x5eed0000u; a.parity = 0; }   // what a replayed launch carries: the kernels must not use it
         a.op = op;
         a.root = root;
         cudaError_t e = cudaErrorInvalidValue;

@@ -33,6 +33,7 @@ bool GpuCommImpl::set_param(const char* name, int value) {
     if (k == "p2p_ctas" && value >= 1 && value <= kP2pCtas) { p2p_ctas_ = value; return true; }
     if (k == "pipe_min_mb" && value >= 0) { pipe_min_bytes_ = (size_t)value << 20; return true; }
     if (k == "pipe_ctas" && value >= 3 && value <= kMaxCtas) { pipe_ctas_ = value; return true; }
+    if (k == "device_seq" && (value == 0 || value == 1)) return set_device_seq(value == 1);
     return false;
 }
 
@@ -57,7 +58,7 @@ struct CallScope {
 
 #define NEXT_SEQ(a)                                   \
     do {                                              \
-        if (++seq_ == 0) ++seq_;                      \
+        seq_ = next_seq(seq_);                        \
         (a).seq = seq_;                               \
         (a).parity = (int)(seq_ & 1u);                \
     } while (0)
@@ -72,6 +73,7 @@ ncclResult_t GpuCommImpl::all_reduce(const void* send, void* recv, size_t count,
         return ncclSuccess;
     }
     ncclResult_t pre = precheck();
+    if (pre == ncclSuccess) pre = capture_check(stream, false);
     if (pre != ncclSuccess) return pre;
     if (!count) return ncclSuccess;
     CallScope scope(this, stream, COLL_ALLREDUCE, "dccl:allreduce");
@@ -161,6 +163,7 @@ ncclResult_t GpuCommImpl::reduce_scatter(const void* send, void* recv, size_t re
         return ncclSuccess;
     }
     ncclResult_t pre = precheck();
+    if (pre == ncclSuccess) pre = capture_check(stream, false);
     if (pre != ncclSuccess) return pre;
     if (!recvcount) return ncclSuccess;
     CallScope scope(this, stream, COLL_REDUCESCATTER, "dccl:reducescatter");
@@ -239,6 +242,7 @@ ncclResult_t GpuCommImpl::all_gather(const void* send, void* recv, size_t sendco
         return ncclSuccess;
     }
     ncclResult_t pre = precheck();
+    if (pre == ncclSuccess) pre = capture_check(stream, false);
     if (pre != ncclSuccess) return pre;
     if (!sendcount) return ncclSuccess;
     CallScope scope(this, stream, COLL_ALLGATHER, "dccl:allgather");
@@ -307,6 +311,7 @@ ncclResult_t GpuCommImpl::broadcast(const void* send, void* recv, size_t count, 
         return ncclSuccess;
     }
     ncclResult_t pre = precheck();
+    if (pre == ncclSuccess) pre = capture_check(stream, false);
     if (pre != ncclSuccess) return pre;
     if (!count) return ncclSuccess;
     CallScope scope(this, stream, COLL_BROADCAST, "dccl:broadcast");
@@ -373,6 +378,7 @@ ncclResult_t GpuCommImpl::reduce(const void* send, void* recv, size_t count, ncc
         return ncclSuccess;
     }
     ncclResult_t pre = precheck();
+    if (pre == ncclSuccess) pre = capture_check(stream, false);
     if (pre != ncclSuccess) return pre;
     if (!count) return ncclSuccess;
     CallScope scope(this, stream, COLL_REDUCE, "dccl:reduce");
@@ -437,6 +443,7 @@ ncclResult_t GpuCommImpl::p2p_launch(std::vector<P2pOp>& ops, cudaStream_t strea
 
 ncclResult_t GpuCommImpl::send(const void* buf, size_t bytes, int peer, cudaStream_t stream) {
     ncclResult_t pre = precheck();
+    if (pre == ncclSuccess) pre = capture_check(stream, true);
     if (pre != ncclSuccess) return pre;
     last_[COLL_SENDRECV] = ALGO_ONESHOT;
     if (!bytes) return ncclSuccess;
@@ -450,6 +457,7 @@ ncclResult_t GpuCommImpl::send(const void* buf, size_t bytes, int peer, cudaStre
 
 ncclResult_t GpuCommImpl::recv(void* buf, size_t bytes, int peer, cudaStream_t stream) {
     ncclResult_t pre = precheck();
+    if (pre == ncclSuccess) pre = capture_check(stream, true);
     if (pre != ncclSuccess) return pre;
     last_[COLL_SENDRECV] = ALGO_ONESHOT;
     if (!bytes) return ncclSuccess;

@@ -85,6 +85,14 @@ bool GpuCommImpl::init(std::string* err) {
 
     if (n_ == 1) return ok;   // a world of one needs no pool: every collective is a local copy
 
+    // sequence counter on the device (used when DCCL/device_seq is on): {next sequence number, CTAs done}
+    if (ok) {
+        void* d = nullptr;
+        ok = cudaMalloc(&d, 256) == cudaSuccess && cudaMemset(d, 0, 256) == cudaSuccess;
+        seq_dev_ = (uint32_t*)d;
+        if (!ok) { cudaGetLastError(); if (err) *err = "cannot allocate the sequence counter"; }
+    }
+
     // every rank reports whether it got this far, so nobody blocks in the exchange below
     {
         std::vector<unsigned char> all(n_);
@@ -105,6 +113,7 @@ bool GpuCommImpl::init(std::string* err) {
     // nobody signals into a pool that is not cleared yet
     if (!bs_->barrier()) { if (err) *err = "control plane failed: " + bs_->last_error(); return false; }
     if (!zero_ok) { if (err) *err = "clearing the pool failed"; return false; }
+    if (cfg.get_bool("DCCL/device_seq", false) && !set_device_seq(true)) { if (err) *err = "cannot switch to the device-side sequence counter"; return false; }
     dccl_info("device %d: pool of %zu MB per rank (%s), multicast %s", dev_, pool_.size >> 20,
               pool_.vmm ? "cuMem" : "cudaIpc", pool_.mc_base ? "bound" : "off");
     return true;
@@ -127,7 +136,49 @@ GpuCommImpl::~GpuCommImpl() {
         sym_ = nullptr;
     }
     if (status_host_) cudaFreeHost(status_host_);
+    if (seq_dev_) cudaFree(seq_dev_);
     cudaGetLastError();
+}
+
+/* ---------------- where the sequence number lives ---------------- */
+
+bool GpuCommImpl::set_device_seq(bool on) {
+    if (on == device_seq_) return true;
+    if (n_ == 1) { device_seq_ = on; return true; }
+    if (!seq_dev_) return false;
+    DeviceGuard g(dev_);
+    // calls in flight still count with the old owner of the number
+    if (cudaDeviceSynchronize() != cudaSuccess) { cudaGetLastError(); return false; }
+    if (on) {
+        const uint32_t words[2] = {next_seq(seq_), 0u};
+        if (cudaMemcpy(seq_dev_, words, sizeof(words), cudaMemcpyHostToDevice) != cudaSuccess) { cudaGetLastError(); return false; }
+        dc_.seq_word = seq_dev_;
+        dc_.done_word = seq_dev_ + 1;
+    } else {
+        uint32_t next = 0;
+        if (cudaMemcpy(&next, seq_dev_, sizeof(next), cudaMemcpyDeviceToHost) != cudaSuccess) { cudaGetLastError(); return false; }
+        seq_ = next - 1u;   // next_seq(seq_) is `next` again, also across the wrap
+        dc_.seq_word = nullptr;
+        dc_.done_word = nullptr;
+    }
+    device_seq_ = on;
+    return true;
+}
+
+ncclResult_t GpuCommImpl::capture_check(cudaStream_t stream, bool p2p) {
+    cudaStreamCaptureStatus st = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(stream, &st) != cudaSuccess) { cudaGetLastError(); return ncclSuccess; }
+    if (st == cudaStreamCaptureStatusNone) return ncclSuccess;
+    if (p2p) {
+        dccl_error("send / recv cannot be captured into a CUDA graph: their chunk numbers are counted on the host");
+        return ncclInvalidUsage;
+    }
+    if (!device_seq_ && n_ > 1) {
+        dccl_error("a collective on a capturing stream needs the device-side sequence counter: set DCCL_DEVICE_SEQ=1 "
+                   "(or the parameter device_seq) on every rank before capturing");
+        return ncclInvalidUsage;
+    }
+    return ncclSuccess;
 }
 
 /* ---------------- stream-time stamps ---------------- */

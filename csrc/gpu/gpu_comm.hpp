@@ -65,7 +65,9 @@ public:
     virtual GpuAlgo last_algo(int coll) const = 0;
     virtual int device() const = 0;
     virtual bool has_multicast() const = 0;
-    /** Tuning knobs for sweeps: "ctas" (0 = table value), "threads" (128..512), "unroll" (2, 4, 8). */
+    /** Tuning knobs for sweeps: "ctas" (0 = table value), "threads" (128..512), "unroll" (2, 4, 8), ...;
+     *  "device_seq" (0 / 1) moves the call sequence number between the host and a device counter, which is
+     *  what makes captured launches replayable (collective: every rank switches at the same point). */
     virtual bool set_param(const char* name, int value) = 0;
     /** Kernels launched by this communicator so far. */
     virtual uint64_t launches() const = 0;

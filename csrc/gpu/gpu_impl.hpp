@@ -60,6 +60,11 @@ private:
     /** Fill the symmetric views of a user buffer; false when it is not inside a dcclMemAlloc segment. */
     bool sym_view(const void* p, size_t bytes, const char** peers, const char** mc) const;
     int ctas_for(int tuned) const;
+    /** Move the sequence number to the device counter (calls become replayable from a CUDA graph) or back to
+     *  the host. Every rank must switch at the same point of its call order. Waits for the device to go idle. */
+    bool set_device_seq(bool on);
+    /** Refuse what a capturing stream cannot replay correctly. */
+    ncclResult_t capture_check(cudaStream_t stream, bool p2p);
     ncclResult_t p2p_launch(std::vector<P2pOp>& ops, cudaStream_t stream);
     /** With DCCL/device_stamps on: log a timestamp when `stream` reaches this point (kernel begin / end on the device time line). */
     void stamp(cudaStream_t stream, uint64_t tag, uint64_t extra);
@@ -76,7 +81,9 @@ private:
     uint32_t* status_host_ = nullptr;   // ST_WORDS status words, then the abort word
     uint32_t* status_dev_ = nullptr;
     size_t stage_bytes_ = 0;
-    uint32_t seq_ = 0;
+    uint32_t seq_ = 0;                  // last sequence number given out by the host
+    uint32_t* seq_dev_ = nullptr;       // device counter: {next sequence number, CTAs done}
+    bool device_seq_ = false;
     Tuner tuner_;
     GpuAlgo last_[COLL_COUNT];
     uint64_t launches_ = 0;

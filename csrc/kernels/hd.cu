@@ -36,9 +36,8 @@ __device__ __forceinline__ void for_my_pieces(size_t lo, size_t hi, int bid, int
 }
 
 template <typename T, int OP>
-__global__ void __launch_bounds__(512) k_hd(const __grid_constant__ CollArgs a) {
+__device__ __forceinline__ void hd_body(const CollArgs& a, const Ctx& x) {
     constexpr size_t VE = 16 / sizeof(T);
-    const Ctx x = make_ctx(a);
     const DevComm& c = *x.c;
     const int n = c.nranks, r = c.rank;
     const T* send = reinterpret_cast<const T*>(x.io->send);
@@ -50,7 +49,7 @@ __global__ void __launch_bounds__(512) k_hd(const __grid_constant__ CollArgs a) 
     while ((1 << steps) < n) steps++;
     // one receive area per halving step (the regions received in successive steps are nested, so
     // they must not share memory), then one for the gather (those regions are disjoint)
-    T* my_stage = stage_ptr<T>(c, r, a.parity);
+    T* my_stage = stage_ptr<T>(c, r, x.parity);
     T* my_ag = my_stage + (size_t)steps * area;
 
     size_t los[4], his[4];
@@ -64,11 +63,11 @@ __global__ void __launch_bounds__(512) k_hd(const __grid_constant__ CollArgs a) 
         size_t klo, khi, slo, shi;
         if (!((r >> k) & 1)) { klo = lo; khi = mid; slo = mid; shi = hi; }
         else { klo = mid; khi = hi; slo = lo; shi = mid; }
-        T* peer_rs = stage_ptr<T>(c, peer, a.parity) + (size_t)k * area;
+        T* peer_rs = stage_ptr<T>(c, peer, x.parity) + (size_t)k * area;
         const T* my_rs = my_stage + (size_t)k * area;
         for_my_pieces<T>(slo, shi, x.bid, x.nb, [&](size_t p, size_t len) { copy_range<T>(peer_rs + p, cur + p, len); });
-        cta_signal_peer(c, peer, x.bid, a.seq, k);
-        if (!cta_wait_peer(c, peer, x.bid, a.seq, k, 700 + k)) return;
+        cta_signal_peer(c, peer, x.bid, x.seq, k);
+        if (!cta_wait_peer(c, peer, x.bid, x.seq, k, 700 + k)) return;
         const bool last = k == steps - 1;
         for_my_pieces<T>(klo, khi, x.bid, x.nb, [&](size_t p, size_t len) {
             const T* ins[1] = {my_rs + p};
@@ -85,15 +84,22 @@ __global__ void __launch_bounds__(512) k_hd(const __grid_constant__ CollArgs a) 
         const size_t plo = los[k], phi = his[k];
         size_t olo, ohi;
         if (lo == plo) { olo = hi; ohi = phi; } else { olo = plo; ohi = lo; }
-        T* peer_ag = stage_ptr<T>(c, peer, a.parity) + (size_t)steps * area;
+        T* peer_ag = stage_ptr<T>(c, peer, x.parity) + (size_t)steps * area;
         for_my_pieces<T>(lo, hi, x.bid, x.nb, [&](size_t p, size_t len) { copy_range<T>(peer_ag + p, recv + p, len); });
         const int idx = steps + (steps - 1 - k);
-        cta_signal_peer(c, peer, x.bid, a.seq, idx);
-        if (!cta_wait_peer(c, peer, x.bid, a.seq, idx, 750 + k)) return;
+        cta_signal_peer(c, peer, x.bid, x.seq, idx);
+        if (!cta_wait_peer(c, peer, x.bid, x.seq, idx, 750 + k)) return;
         for_my_pieces<T>(olo, ohi, x.bid, x.nb, [&](size_t p, size_t len) { copy_range<T>(recv + p, my_ag + p, len); });
         __syncthreads();
         lo = plo; hi = phi;
     }
+}
+
+template <typename T, int OP>
+__global__ void __launch_bounds__(512) k_hd(const __grid_constant__ CollArgs a) {
+    const Ctx x = make_ctx(a);
+    hd_body<T, OP>(a, x);
+    finish_call(x);
 }
 
 size_t hd_capacity(int nranks, size_t es, size_t stage_bytes) {

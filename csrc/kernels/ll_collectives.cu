@@ -61,10 +61,9 @@ __device__ __forceinline__ bool poll_packet(const DevComm& c, const char* slot, 
 }
 
 template <typename T, int OP>
-__global__ void __launch_bounds__(512) k_ll_collective(const __grid_constant__ CollArgs a) {
+__device__ __forceinline__ void ll_collective_body(const CollArgs& a, const Ctx& x) {
     using A = typename Traits<T>::Acc;
     constexpr int N = 8 / (int)sizeof(T);
-    const Ctx x = make_ctx(a);
     const DevComm& c = *x.c;
     const int n = c.nranks, r = c.rank, mode = a.mode, root = a.root;
     const char* send = reinterpret_cast<const char*>(x.io->send);
@@ -72,7 +71,7 @@ __global__ void __launch_bounds__(512) k_ll_collective(const __grid_constant__ C
     const size_t nbytes = a.count * sizeof(T);            // per-rank payload
     const size_t sbytes = a.stride * sizeof(T);           // distance between slots in the user buffer (RS / AG)
     const size_t npk = (nbytes + 7) / 8;
-    const uint32_t tag = a.seq;
+    const uint32_t tag = x.seq;
     const bool avg = a.op == (int)ncclAvg;
     const bool fin = (reinterpret_cast<uintptr_t>(send) & 7u) == 0 && (sbytes & 7u) == 0;
     const bool fout = (reinterpret_cast<uintptr_t>(recv) & 7u) == 0 && (sbytes & 7u) == 0;
@@ -88,11 +87,11 @@ __global__ void __launch_bounds__(512) k_ll_collective(const __grid_constant__ C
                 for (int k = 1; k < n; k++) {
                     const int p = (r + k) % n;
                     const uint2 d = load8(send + (size_t)p * sbytes + off, valid, fin);
-                    st_volatile_v4(ll_slot2(c, p, a.parity, r) + i * 16, make_uint4(d.x, tag, d.y, tag));
+                    st_volatile_v4(ll_slot2(c, p, x.parity, r) + i * 16, make_uint4(d.x, tag, d.y, tag));
                 }
             } else if (r != root) {
                 const uint2 d = load8(send + off, valid, fin);
-                st_volatile_v4(ll_slot2(c, root, a.parity, r) + i * 16, make_uint4(d.x, tag, d.y, tag));
+                st_volatile_v4(ll_slot2(c, root, x.parity, r) + i * 16, make_uint4(d.x, tag, d.y, tag));
             }
             if (reducer) {
                 const size_t own_off = mode == LL_REDUCESCATTER ? (size_t)r * sbytes + off : off;
@@ -100,7 +99,7 @@ __global__ void __launch_bounds__(512) k_ll_collective(const __grid_constant__ C
                 for (int p = 0; p < n && ok; p++) {
                     union { uint2 u; T e[N]; } v;
                     if (p == r) v.u = load8(send + own_off, valid, fin);
-                    else ok = poll_packet(c, ll_slot2(c, r, a.parity, p) + i * 16, tag, p, a.seq, &v.u);
+                    else ok = poll_packet(c, ll_slot2(c, r, x.parity, p) + i * 16, tag, p, x.seq, &v.u);
                     if (!ok) break;
                     if (p == 0) {
 #pragma unroll
@@ -120,23 +119,23 @@ __global__ void __launch_bounds__(512) k_ll_collective(const __grid_constant__ C
         } else if (mode == LL_ALLGATHER) {
             const uint2 d = load8(send + off, valid, fin);
             const uint4 pkt = make_uint4(d.x, tag, d.y, tag);
-            for (int k = 1; k < n; k++) st_volatile_v4(ll_slot2(c, (r + k) % n, a.parity, r) + i * 16, pkt);
+            for (int k = 1; k < n; k++) st_volatile_v4(ll_slot2(c, (r + k) % n, x.parity, r) + i * 16, pkt);
             if (recv + (size_t)r * sbytes != send) store8(recv + (size_t)r * sbytes + off, d, valid, fout);
             for (int k = 1; k < n && ok; k++) {
                 const int p = (r + k) % n;
                 uint2 v;
-                ok = poll_packet(c, ll_slot2(c, r, a.parity, p) + i * 16, tag, p, a.seq, &v);
+                ok = poll_packet(c, ll_slot2(c, r, x.parity, p) + i * 16, tag, p, x.seq, &v);
                 if (ok) store8(recv + (size_t)p * sbytes + off, v, valid, fout);
             }
         } else {  // LL_BROADCAST
             if (r == root) {
                 const uint2 d = load8(send + off, valid, fin);
                 const uint4 pkt = make_uint4(d.x, tag, d.y, tag);
-                for (int k = 1; k < n; k++) st_volatile_v4(ll_slot2(c, (r + k) % n, a.parity, r) + i * 16, pkt);
+                for (int k = 1; k < n; k++) st_volatile_v4(ll_slot2(c, (r + k) % n, x.parity, r) + i * 16, pkt);
                 if (recv != send) store8(recv + off, d, valid, fout);
             } else {
                 uint2 v;
-                ok = poll_packet(c, ll_slot2(c, r, a.parity, root) + i * 16, tag, root, a.seq, &v);
+                ok = poll_packet(c, ll_slot2(c, r, x.parity, root) + i * 16, tag, root, x.seq, &v);
                 if (ok) store8(recv + off, v, valid, fout);
             }
         }
@@ -153,13 +152,20 @@ __global__ void __launch_bounds__(512) k_ll_collective(const __grid_constant__ C
         const bool consumer = mode == LL_BROADCAST ? r != root : r == root;   // who read packets
         if (consumer) {
             // I am done reading: tell the producer(s)
-            if (mode == LL_BROADCAST) { if (threadIdx.x == 0) signal_peer(c, root, x.bid, a.seq, 0); }
-            else if ((int)threadIdx.x < n && (int)threadIdx.x != r) signal_peer(c, (int)threadIdx.x, x.bid, a.seq, 0);
+            if (mode == LL_BROADCAST) { if (threadIdx.x == 0) signal_peer(c, root, x.bid, x.seq, 0); }
+            else if ((int)threadIdx.x < n && (int)threadIdx.x != r) signal_peer(c, (int)threadIdx.x, x.bid, x.seq, 0);
         } else {
-            if (mode == LL_BROADCAST) { if ((int)threadIdx.x < n && (int)threadIdx.x != r) wait_peer(c, (int)threadIdx.x, x.bid, a.seq, 0, 320); }
-            else if (threadIdx.x == 0) wait_peer(c, root, x.bid, a.seq, 0, 321);
+            if (mode == LL_BROADCAST) { if ((int)threadIdx.x < n && (int)threadIdx.x != r) wait_peer(c, (int)threadIdx.x, x.bid, x.seq, 0, 320); }
+            else if (threadIdx.x == 0) wait_peer(c, root, x.bid, x.seq, 0, 321);
         }
     }
+}
+
+template <typename T, int OP>
+__global__ void __launch_bounds__(512) k_ll_collective(const __grid_constant__ CollArgs a) {
+    const Ctx x = make_ctx(a);
+    ll_collective_body<T, OP>(a, x);
+    finish_call(x);
 }
 
 cudaError_t launch_ll_collective(const CollArgs& a, ncclDataType_t dt, const LaunchCfg& cfg_in) {

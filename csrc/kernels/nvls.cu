@@ -36,9 +36,8 @@
 namespace dccl {
 
 template <typename T, int OP>
-__global__ void __launch_bounds__(512) k_nvls(const __grid_constant__ CollArgs a) {
+__device__ __forceinline__ void nvls_body(const CollArgs& a, const Ctx& x) {
     constexpr size_t ES = sizeof(T);
-    const Ctx x = make_ctx(a);
     const DevComm& c = *x.c;
     const int n = c.nranks, r = c.rank, mode = a.mode;
     const T* send = reinterpret_cast<const T*>(x.io->send);
@@ -47,7 +46,7 @@ __global__ void __launch_bounds__(512) k_nvls(const __grid_constant__ CollArgs a
     const Geometry<T> g(slots ? GEO_SLOTS : GEO_SPLIT, a.count, n, x.bid, x.nb);
     const size_t stride = slots ? a.stride : g.per;
     const bool avg = a.op == (int)ncclAvg;
-    const size_t stage_off = kStageOff + (size_t)a.parity * c.stage_bytes;
+    const size_t stage_off = kStageOff + (size_t)x.parity * c.stage_bytes;
     T* my_stage = reinterpret_cast<T*>(c.pool[r] + stage_off);
     char* mc_stage = c.mc_pool + stage_off;
     auto lo_of = [&](int j) { size_t l = g.len(j); return g.blo < l ? g.blo : l; };
@@ -58,7 +57,7 @@ __global__ void __launch_bounds__(512) k_nvls(const __grid_constant__ CollArgs a
         /* ---- user buffers are multicast-bound: no copies ---- */
         const char* send_mc = x.io->send_mc;
         char* recv_mc = x.io->recv_mc;
-        if (!rank_barrier(c, x.bid, a.seq, 0, 400 + mode)) return;
+        if (!rank_barrier(c, x.bid, x.seq, 0, 400 + mode)) return;
         if (mode == NV_ALLREDUCE) {
             const size_t lo = lo_of(r), hi = hi_of(r);
             if (hi > lo) nvls_pass<T, OP>(send_mc + ((size_t)r * stride + lo) * ES, recv_mc + ((size_t)r * stride + lo) * ES, nullptr, vecs(hi - lo), 0, avg, n, a.unroll);
@@ -81,7 +80,7 @@ __global__ void __launch_bounds__(512) k_nvls(const __grid_constant__ CollArgs a
                     if (hi > lo) nvls_pass<T, OP>(send_mc + ((size_t)j * stride + lo) * ES, nullptr, reinterpret_cast<char*>(recv + (size_t)j * stride + lo), vecs(hi - lo), (hi - lo) * ES, avg, n);
                 }
         }
-        rank_barrier(c, x.bid, a.seq, 1, 450 + mode);
+        rank_barrier(c, x.bid, x.seq, 1, 450 + mode);
         return;
     }
 
@@ -116,7 +115,7 @@ __global__ void __launch_bounds__(512) k_nvls(const __grid_constant__ CollArgs a
                 }
             }
     }
-    if (!rank_barrier(c, x.bid, a.seq, 0, 500 + mode)) return;
+    if (!rank_barrier(c, x.bid, x.seq, 0, 500 + mode)) return;
 
     if (mode == NV_ALLREDUCE) {
         const size_t lo = lo_of(r), hi = hi_of(r);
@@ -124,7 +123,7 @@ __global__ void __launch_bounds__(512) k_nvls(const __grid_constant__ CollArgs a
             const size_t off = ((size_t)r * g.slot_stride + lo) * ES;
             nvls_pass<T, OP>(mc_stage + off, mc_stage + off, nullptr, vecs(hi - lo), 0, avg, n, a.unroll);
         }
-        if (!rank_barrier(c, x.bid, a.seq, 1, 550 + mode)) return;
+        if (!rank_barrier(c, x.bid, x.seq, 1, 550 + mode)) return;
     } else if (mode == NV_REDUCESCATTER) {
         const size_t lo = lo_of(r), hi = hi_of(r);
         if (hi > lo) {
@@ -179,6 +178,13 @@ __global__ void __launch_bounds__(512) k_nvls(const __grid_constant__ CollArgs a
         }
         copy_range<T>(recv + (size_t)j * stride + lo, my_stage + (size_t)j * g.slot_stride + lo, hi - lo);
     }
+}
+
+template <typename T, int OP>
+__global__ void __launch_bounds__(512) k_nvls(const __grid_constant__ CollArgs a) {
+    const Ctx x = make_ctx(a);
+    nvls_body<T, OP>(a, x);
+    finish_call(x);
 }
 
 bool nvls_supports(ncclDataType_t dt, ncclRedOp_t op) {

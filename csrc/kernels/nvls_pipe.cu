@@ -64,10 +64,9 @@ __device__ __forceinline__ void split_range(size_t lo, size_t hi, int m, int par
 }
 
 template <typename T, int OP>
-__global__ void __launch_bounds__(512) k_nvls_pipe(const __grid_constant__ CollArgs a) {
+__device__ __forceinline__ void nvls_pipe_body(const CollArgs& a, const Ctx& x) {
     constexpr size_t ES = sizeof(T);
     constexpr size_t VE = 16 / ES;
-    const Ctx x = make_ctx(a);
     const DevComm& c = *x.c;
     const int n = c.nranks, r = c.rank;
     const bool rs = a.root != 0;                   // reduce-scatter (count = per-rank elements) instead of all-reduce
@@ -82,7 +81,7 @@ __global__ void __launch_bounds__(512) k_nvls_pipe(const __grid_constant__ CollA
     const T* send = reinterpret_cast<const T*>(x.io->send);
     T* recv = reinterpret_cast<T*>(x.io->recv);
     const bool avg = a.op == (int)ncclAvg;
-    const size_t stage_off = kStageOff + (size_t)a.parity * c.stage_bytes;
+    const size_t stage_off = kStageOff + (size_t)x.parity * c.stage_bytes;
     T* my_stage = reinterpret_cast<T*>(c.pool[r] + stage_off);
     char* mc_stage = c.mc_pool + stage_off;
     const int nchunks = a.mode;                    // chosen by the host, 1..kPipeMaxChunks
@@ -108,9 +107,9 @@ __global__ void __launch_bounds__(512) k_nvls_pipe(const __grid_constant__ CollA
                 if (rs) copy_range<T>(my_stage + (size_t)j * slot + base + lo, send + (size_t)j * a.stride + base + lo, hi - lo);
                 else { const size_t off = base + (size_t)j * geo.per + lo; copy_range<T>(my_stage + off, send + off, hi - lo); }
             }
-            signal_all_ranks(c, row_a0 + m, a.seq, k);
+            signal_all_ranks(c, row_a0 + m, x.seq, k);
         } else if (role == 1) {
-            if (!wait_rows_all_ranks(c, row_a0, kPipeFan, a.seq, k, 560)) return;
+            if (!wait_rows_all_ranks(c, row_a0, kPipeFan, x.seq, k, 560)) return;
             const size_t lo = lo_of(r), hi = hi_of(r);
             if (hi > lo) {
                 if (rs) {
@@ -121,9 +120,9 @@ __global__ void __launch_bounds__(512) k_nvls_pipe(const __grid_constant__ CollA
                     nvls_pass<T, OP>(mc_stage + off, mc_stage + off, nullptr, ((hi - lo) * ES + 15) / 16, 0, avg, n, a.unroll);
                 }
             }
-            if (!rs) signal_all_ranks(c, row_b, a.seq, k);
+            if (!rs) signal_all_ranks(c, row_b, x.seq, k);
         } else {
-            if (!wait_rows_all_ranks(c, row_b, 1, a.seq, k, 570)) return;
+            if (!wait_rows_all_ranks(c, row_b, 1, x.seq, k, 570)) return;
             for (int j = 0; j < n && cnt; j++) {
                 size_t lo, hi;
                 split_range(lo_of(j), hi_of(j), m, kPipeFan, VE, &lo, &hi);
@@ -133,6 +132,13 @@ __global__ void __launch_bounds__(512) k_nvls_pipe(const __grid_constant__ CollA
             }
         }
     }
+}
+
+template <typename T, int OP>
+__global__ void __launch_bounds__(512) k_nvls_pipe(const __grid_constant__ CollArgs a) {
+    const Ctx x = make_ctx(a);
+    nvls_pipe_body<T, OP>(a, x);
+    finish_call(x);
 }
 
 size_t nvls_pipe_capacity(size_t es, size_t stage_bytes, int nranks, bool reduce_scatter) {

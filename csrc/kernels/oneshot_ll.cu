@@ -26,17 +26,16 @@ __device__ __forceinline__ char* ll_slot(const DevComm& c, int owner, int parity
 }
 
 template <typename T, int OP>
-__global__ void __launch_bounds__(512) k_oneshot_ll(const __grid_constant__ CollArgs a) {
+__device__ __forceinline__ void oneshot_ll_body(const CollArgs& a, const Ctx& x) {
     using A = typename Traits<T>::Acc;
     constexpr int N = 8 / (int)sizeof(T);
-    const Ctx x = make_ctx(a);
     const DevComm& c = *x.c;
     const int n = c.nranks, r = c.rank;
     const char* send = reinterpret_cast<const char*>(x.io->send);
     char* recv = reinterpret_cast<char*>(x.io->recv);
     const size_t nbytes = a.count * sizeof(T);
     const size_t npk = (nbytes + 7) / 8;
-    const uint32_t tag = a.seq;
+    const uint32_t tag = x.seq;
     const bool avg = a.op == (int)ncclAvg;
     const bool fast_in = (reinterpret_cast<uintptr_t>(send) & 7u) == 0, fast_out = (reinterpret_cast<uintptr_t>(recv) & 7u) == 0;
 
@@ -51,7 +50,7 @@ __global__ void __launch_bounds__(512) k_oneshot_ll(const __grid_constant__ Coll
         const uint4 pkt = make_uint4(mine.u.x, tag, mine.u.y, tag);
         for (int k = 1; k < n; k++) {
             const int p = (r + k) % n;
-            st_volatile_v4(ll_slot(c, p, a.parity, r) + i * 16, pkt);
+            st_volatile_v4(ll_slot(c, p, x.parity, r) + i * 16, pkt);
         }
 
         A acc[N];
@@ -60,7 +59,7 @@ __global__ void __launch_bounds__(512) k_oneshot_ll(const __grid_constant__ Coll
             union { uint2 u; T e[N]; } theirs;
             if (p == r) theirs.u = mine.u;
             else {
-                const char* slot = ll_slot(c, r, a.parity, p) + i * 16;
+                const char* slot = ll_slot(c, r, x.parity, p) + i * 16;
                 uint4 v = ld_volatile_v4(slot);
                 uint32_t spins = 0;
                 unsigned long long t0 = 0;
@@ -68,8 +67,8 @@ __global__ void __launch_bounds__(512) k_oneshot_ll(const __grid_constant__ Coll
                     if ((++spins & 0xffu) == 0) {
                         unsigned long long now = global_timer_ns();
                         if (t0 == 0) t0 = now;
-                        else if (now - t0 > c.timeout_ns) { report_failure(c, DEV_TIMEOUT, p, 300, a.seq); ok = false; break; }
-                        if ((spins & 0xfffu) == 0 && ld_volatile_u32(c.abort_word) != 0) { report_failure(c, DEV_ABORTED, p, 300, a.seq); ok = false; break; }
+                        else if (now - t0 > c.timeout_ns) { report_failure(c, DEV_TIMEOUT, p, 300, x.seq); ok = false; break; }
+                        if ((spins & 0xfffu) == 0 && ld_volatile_u32(c.abort_word) != 0) { report_failure(c, DEV_ABORTED, p, 300, x.seq); ok = false; break; }
                     }
                     v = ld_volatile_v4(slot);
                 }
@@ -91,6 +90,13 @@ __global__ void __launch_bounds__(512) k_oneshot_ll(const __grid_constant__ Coll
         if (fast_out && valid == 8) *reinterpret_cast<uint2*>(recv + off) = out.u;
         else for (int k = 0; k < valid; k++) recv[off + k] = (char)out.b[k];
     }
+}
+
+template <typename T, int OP>
+__global__ void __launch_bounds__(512) k_oneshot_ll(const __grid_constant__ CollArgs a) {
+    const Ctx x = make_ctx(a);
+    oneshot_ll_body<T, OP>(a, x);
+    finish_call(x);
 }
 
 cudaError_t launch_oneshot_ll(const CollArgs& a, ncclDataType_t dt, const LaunchCfg& cfg_in) {

@@ -18,8 +18,7 @@
 namespace dccl {
 
 template <typename T, int OP>
-__global__ void __launch_bounds__(512) k_ring(const __grid_constant__ CollArgs a) {
-    const Ctx x = make_ctx(a);
+__device__ __forceinline__ void ring_body(const CollArgs& a, const Ctx& x) {
     const DevComm& c = *x.c;
     const int n = c.nranks, r = c.rank, mode = a.mode;
     const T* send = reinterpret_cast<const T*>(x.io->send);
@@ -29,8 +28,8 @@ __global__ void __launch_bounds__(512) k_ring(const __grid_constant__ CollArgs a
     const size_t stride = slots ? a.stride : g.per;
     const int next = (r + 1) % n, prev = (r + n - 1) % n;
     const bool avg = a.op == (int)ncclAvg;
-    T* my_stage = stage_ptr<T>(c, r, a.parity);
-    T* next_stage = stage_ptr<T>(c, next, a.parity);
+    T* my_stage = stage_ptr<T>(c, r, x.parity);
+    T* next_stage = stage_ptr<T>(c, next, x.parity);
     auto lo_of = [&](int j) { size_t l = g.len(j); return g.blo < l ? g.blo : l; };
     auto hi_of = [&](int j) { size_t l = g.len(j); return g.bhi < l ? g.bhi : l; };
     auto md = [&](int v) { int m = v % n; return m < 0 ? m + n : m; };
@@ -45,10 +44,10 @@ __global__ void __launch_bounds__(512) k_ring(const __grid_constant__ CollArgs a
             const int j = md(r + sh);
             const size_t lo = lo_of(j), hi = hi_of(j);
             if (hi > lo) copy_range<T>(area(next_stage, 0) + lo, send + (size_t)j * stride + lo, hi - lo);
-            cta_signal_peer(c, next, x.bid, a.seq, 0);
+            cta_signal_peer(c, next, x.bid, x.seq, 0);
         }
         for (int s = 0; s < n - 1; s++) {
-            if (!cta_wait_peer(c, prev, x.bid, a.seq, s, 600 + s)) return;
+            if (!cta_wait_peer(c, prev, x.bid, x.seq, s, 600 + s)) return;
             const int j = md(r - s - 1 + sh);
             const size_t lo = lo_of(j), hi = hi_of(j);
             const bool last = s == n - 2;
@@ -59,8 +58,8 @@ __global__ void __launch_bounds__(512) k_ring(const __grid_constant__ CollArgs a
                 else if (mode == RING_REDUCESCATTER) reduce_range<T, OP>(recv + lo, nullptr, mine, ins, 1, hi - lo, avg, n);
                 else reduce_range<T, OP>(recv + (size_t)j * stride + lo, area(next_stage, n - 1) + lo, mine, ins, 1, hi - lo, avg, n);
             }
-            if (!last) cta_signal_peer(c, next, x.bid, a.seq, s + 1);
-            else if (mode == RING_ALLREDUCE) cta_signal_peer(c, next, x.bid, a.seq, n - 1);
+            if (!last) cta_signal_peer(c, next, x.bid, x.seq, s + 1);
+            else if (mode == RING_ALLREDUCE) cta_signal_peer(c, next, x.bid, x.seq, n - 1);
         }
         if (mode == RING_REDUCESCATTER) return;
     } else {
@@ -70,12 +69,12 @@ __global__ void __launch_bounds__(512) k_ring(const __grid_constant__ CollArgs a
             copy_range<T>(area(next_stage, n - 1) + lo, send + lo, hi - lo);
             if (recv + (size_t)r * stride != send) copy_range<T>(recv + (size_t)r * stride + lo, send + lo, hi - lo);
         }
-        cta_signal_peer(c, next, x.bid, a.seq, n - 1);
+        cta_signal_peer(c, next, x.bid, x.seq, n - 1);
     }
 
     /* gather: at step t shard (own - t - 1) arrives; keep it and pass it on */
     for (int t = 0; t < n - 1; t++) {
-        if (!cta_wait_peer(c, prev, x.bid, a.seq, n - 1 + t, 650 + t)) return;
+        if (!cta_wait_peer(c, prev, x.bid, x.seq, n - 1 + t, 650 + t)) return;
         const int j = md(own - t - 1);
         const size_t lo = lo_of(j), hi = hi_of(j);
         if (hi > lo) {
@@ -83,8 +82,15 @@ __global__ void __launch_bounds__(512) k_ring(const __grid_constant__ CollArgs a
             if (t < n - 2) copy_range<T>(area(next_stage, n + t) + lo, src, hi - lo);
             copy_range<T>(recv + (size_t)j * stride + lo, src, hi - lo);
         }
-        if (t < n - 2) cta_signal_peer(c, next, x.bid, a.seq, n + t);
+        if (t < n - 2) cta_signal_peer(c, next, x.bid, x.seq, n + t);
     }
+}
+
+template <typename T, int OP>
+__global__ void __launch_bounds__(512) k_ring(const __grid_constant__ CollArgs a) {
+    const Ctx x = make_ctx(a);
+    ring_body<T, OP>(a, x);
+    finish_call(x);
 }
 
 size_t ring_capacity(int mode, int nranks, size_t es, size_t stage_bytes) {

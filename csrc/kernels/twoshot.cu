@@ -32,8 +32,7 @@
 namespace dccl {
 
 template <typename T, int OP>
-__global__ void __launch_bounds__(512) k_twoshot(const __grid_constant__ CollArgs a) {
-    const Ctx x = make_ctx(a);
+__device__ __forceinline__ void twoshot_body(const CollArgs& a, const Ctx& x) {
     const DevComm& c = *x.c;
     const int n = c.nranks, r = c.rank, mode = a.mode;
     const T* send = reinterpret_cast<const T*>(x.io->send);
@@ -42,7 +41,7 @@ __global__ void __launch_bounds__(512) k_twoshot(const __grid_constant__ CollArg
                   a.count, n, x.bid, x.nb);
     if (mode == TS_ALLREDUCE || mode == TS_REDUCESCATTER || mode == TS_REDUCE) g.res_off = g.slot_stride * (size_t)n;
     const size_t stride = (mode == TS_REDUCESCATTER || mode == TS_ALLGATHER) ? a.stride : g.per;
-    T* my_stage = stage_ptr<T>(c, r, a.parity);
+    T* my_stage = stage_ptr<T>(c, r, x.parity);
     const bool avg = a.op == (int)ncclAvg;
     auto lo_of = [&](int j) { size_t l = g.len(j); return g.blo < l ? g.blo : l; };
     auto hi_of = [&](int j) { size_t l = g.len(j); return g.bhi < l ? g.bhi : l; };
@@ -65,16 +64,16 @@ __global__ void __launch_bounds__(512) k_twoshot(const __grid_constant__ CollArg
                 if (hi > lo)
                     for (int q = 1; q < n; q++) {
                         const int p = (r + q) % n;
-                        copy_range<T>(stage_ptr<T>(c, p, a.parity) + (size_t)r * g.slot_stride + lo, send + (size_t)p * stride + lo, hi - lo);
+                        copy_range<T>(stage_ptr<T>(c, p, x.parity) + (size_t)r * g.slot_stride + lo, send + (size_t)p * stride + lo, hi - lo);
                     }
                 __syncthreads();
-                if ((int)threadIdx.x < n) signal_peer(c, (int)threadIdx.x, x.bid, a.seq, k);
+                if ((int)threadIdx.x < n) signal_peer(c, (int)threadIdx.x, x.bid, x.seq, k);
             };
             auto fold = [&](int k) -> bool {
                 __shared__ int s_fail;
                 if (threadIdx.x == 0) s_fail = 0;
                 __syncthreads();
-                if ((int)threadIdx.x < n && !wait_peer(c, (int)threadIdx.x, x.bid, a.seq, k, 150)) s_fail = 1;
+                if ((int)threadIdx.x < n && !wait_peer(c, (int)threadIdx.x, x.bid, x.seq, k, 150)) s_fail = 1;
                 __syncthreads();
                 if (s_fail) return false;
                 const size_t lo = piece_lo(k), hi = piece_lo(k + 1);
@@ -101,7 +100,7 @@ __global__ void __launch_bounds__(512) k_twoshot(const __grid_constant__ CollArg
         for (int k = 1; k < n; k++) {
             const int p = (r + k) % n;
             const size_t lo = lo_of(p), hi = hi_of(p);
-            if (hi > lo) copy_range<T>(stage_ptr<T>(c, p, a.parity) + (size_t)r * g.slot_stride + lo, send + (size_t)p * stride + lo, hi - lo);
+            if (hi > lo) copy_range<T>(stage_ptr<T>(c, p, x.parity) + (size_t)r * g.slot_stride + lo, send + (size_t)p * stride + lo, hi - lo);
         }
     } else if (mode == TS_ALLGATHER) {
         const size_t lo = lo_of(0), hi = hi_of(0);   // every shard has the same length here
@@ -111,7 +110,7 @@ __global__ void __launch_bounds__(512) k_twoshot(const __grid_constant__ CollArg
             for (int k = 0; k < n; k++) {
                 const int p = (r + k) % n;
                 const size_t lo = lo_of(p), hi = hi_of(p);
-                if (hi > lo) copy_range<T>(stage_ptr<T>(c, p, a.parity) + g.res_off + lo, send + (size_t)p * stride + lo, hi - lo);
+                if (hi > lo) copy_range<T>(stage_ptr<T>(c, p, x.parity) + g.res_off + lo, send + (size_t)p * stride + lo, hi - lo);
             }
         }
     } else {  // TS_BROADCAST_DIRECT
@@ -120,7 +119,7 @@ __global__ void __launch_bounds__(512) k_twoshot(const __grid_constant__ CollArg
             if (hi > lo) copy_range<T>(my_stage + lo, send + lo, hi - lo);
         }
     }
-    if (!rank_barrier(c, x.bid, a.seq, 0, 100 + mode)) return;
+    if (!rank_barrier(c, x.bid, x.seq, 0, 100 + mode)) return;
 
     /* ---- phase 1: reduce my shard ---- */
     if (mode == TS_ALLREDUCE || mode == TS_REDUCESCATTER || mode == TS_REDUCE) {
@@ -139,7 +138,7 @@ __global__ void __launch_bounds__(512) k_twoshot(const __grid_constant__ CollArg
             reduce_range<T, OP>(out0, out1, own, ins, k, hi - lo, avg, n);
         }
         if (mode == TS_REDUCESCATTER) return;
-        if (!rank_barrier(c, x.bid, a.seq, 1, 200 + mode)) return;
+        if (!rank_barrier(c, x.bid, x.seq, 1, 200 + mode)) return;
     }
 
     /* ---- phase 2: collect ---- */
@@ -147,7 +146,7 @@ __global__ void __launch_bounds__(512) k_twoshot(const __grid_constant__ CollArg
         for (int k = 1; k < n; k++) {
             const int p = (r + k) % n;
             const size_t lo = lo_of(p), hi = hi_of(p);
-            if (hi > lo) copy_range<T>(recv + (size_t)p * stride + lo, stage_ptr<T>(c, p, a.parity) + g.res_off + lo, hi - lo);
+            if (hi > lo) copy_range<T>(recv + (size_t)p * stride + lo, stage_ptr<T>(c, p, x.parity) + g.res_off + lo, hi - lo);
         }
         const size_t lo = lo_of(r), hi = hi_of(r);
         if (mode == TS_ALLGATHER) {
@@ -164,10 +163,17 @@ __global__ void __launch_bounds__(512) k_twoshot(const __grid_constant__ CollArg
     } else if (mode == TS_BROADCAST_DIRECT) {
         const size_t lo = lo_of(0), hi = hi_of(0);
         if (hi > lo) {
-            if (r != a.root) copy_range<T>(recv + lo, stage_ptr<T>(c, a.root, a.parity) + lo, hi - lo);
+            if (r != a.root) copy_range<T>(recv + lo, stage_ptr<T>(c, a.root, x.parity) + lo, hi - lo);
             else if (recv != send) copy_range<T>(recv + lo, send + lo, hi - lo);
         }
     }
+}
+
+template <typename T, int OP>
+__global__ void __launch_bounds__(512) k_twoshot(const __grid_constant__ CollArgs a) {
+    const Ctx x = make_ctx(a);
+    twoshot_body<T, OP>(a, x);
+    finish_call(x);
 }
 
 size_t twoshot_capacity(int mode, int nranks, size_t es, size_t stage_bytes) {

@@ -195,3 +195,38 @@ def test_large_reduce_scatter_overlaps_push_and_reduce(dccl_lib):
                 out = emu(dccl_lib, "reducescatter", "twoshot", n, name, op, count, ins, ctas=ctas, in_place=in_place, stage=96 << 20)
                 for r in range(n):
                     assert close(out[r], want[r * count:(r + 1) * count], name, n), (n, count, name, op, r, in_place)
+
+
+def test_sequence_number_kept_on_the_device(dccl_lib):
+    """With the device-side counter, a launch carries no usable sequence number (as when a CUDA graph
+    replays it); every variant must still run call after call, alternating staging halves."""
+    dccl_lib.dccl_emu_set_device_seq(1)
+    try:
+        for n in [2, 8]:
+            for count in [5, 4099, 70001]:
+                ins = inputs_for("bfloat16", "avg", count, n, seed=31)
+                want = oracle.fold(ins, "avg", bf16=True)
+                for algo in ["oneshot", "twoshot", "ring", "rabenseifner"]:
+                    if algo == "oneshot" and count * 2 > 128 * 1024:
+                        continue
+                    out = emu(dccl_lib, "allreduce", algo, n, "bfloat16", "avg", count, ins, iters=5, ctas=4)
+                    for r in range(n):
+                        assert close(out[r], want, "bfloat16", n), ("allreduce", algo, n, count, r)
+                ins = inputs_for("float32", "sum", count * n, n, seed=37)
+                want = oracle.fold(ins, "sum")
+                for algo in ["oneshot", "twoshot", "ring"]:
+                    if algo == "oneshot" and count * 4 > 128 * 1024:
+                        continue
+                    out = emu(dccl_lib, "reducescatter", algo, n, "float32", "sum", count, ins, iters=4)
+                    for r in range(n):
+                        assert close(out[r], want[r * count:(r + 1) * count], "float32", n), ("rs", algo, n, count, r)
+                ins = inputs_for("float32", "sum", count, n, seed=41)
+                for algo in ["oneshot", "twoshot"]:
+                    out = emu(dccl_lib, "allgather", algo if count * 4 <= 128 * 1024 else "twoshot", n, "float32", "sum", count, ins, iters=4)
+                    for r in range(n):
+                        assert np.array_equal(out[r], np.concatenate(ins)), ("ag", algo, n, count, r)
+                    out = emu(dccl_lib, "broadcast", algo, n, "float32", "sum", count, ins, root=n - 1, in_place=1, iters=4)
+                    for r in range(n):
+                        assert np.array_equal(out[r], ins[n - 1]), ("bcast", algo, n, count, r)
+    finally:
+        dccl_lib.dccl_emu_set_device_seq(0)

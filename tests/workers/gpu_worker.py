@@ -165,6 +165,66 @@ def main():
         torch.cuda.synchronize()
         check(bool((small == 10.0).all()), "plain send/recv")
     torch.cuda.synchronize()
+
+    # CUDA graph replay: refused while the host counts sequence numbers, correct with the device-side counter
+    if args.suite == "basic":
+        from dccl_b200.comm import DcclError
+        n_small, n_big = 1000, 1 << 20
+        xs = torch.zeros(n_small, dtype=torch.float32, device=dev)
+        ys = torch.zeros_like(xs)
+        xb = torch.zeros(n_big, dtype=torch.bfloat16, device=dev)
+        yb = torch.zeros_like(xb)
+        zb = torch.zeros_like(xb)
+        rs_out = torch.zeros(n_big // world, dtype=torch.bfloat16, device=dev)
+        ag_out = torch.zeros(n_small * world, dtype=torch.float32, device=dev)
+        side = torch.cuda.Stream(device=dev)
+        refused = False
+        g0 = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g0, stream=side):
+            ys.add_(0)   # something to capture, so that the graph is not empty
+            try:
+                comm.all_reduce(xs, ys, op="sum")
+            except DcclError:
+                refused = True
+        check(refused, "capture with host-side sequence numbers must be refused")
+        torch.cuda.synchronize()
+        comm.set_param("device_seq", 1)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=side):
+            comm.all_reduce(xs, ys, op="sum")            # packets
+            comm.all_reduce(xb, yb, op="avg")            # staging half A
+            comm.all_reduce(yb, zb, op="sum")            # staging half B
+            comm.reduce_scatter(xb, rs_out, op="sum")
+            comm.all_gather(xs, ag_out)
+        for it in range(4):
+            ins_s = [oracle.make_input("float32", n_small, seed=2000 + 10 * it + r) for r in range(world)]
+            ins_b = [oracle.make_input("bfloat16", n_big, seed=3000 + 10 * it + r) for r in range(world)]
+            xs.copy_(to_torch(ins_s[rank], "float32", dev))
+            xb.copy_(to_torch(ins_b[rank], "bfloat16", dev))
+            torch.cuda.synchronize()
+            g.replay()
+            if it == 1:
+                g.replay()   # twice in a row without the host in between
+            torch.cuda.synchronize()
+            check(close(to_numpy(ys, "float32"), oracle.fold(ins_s, "sum"), "float32", world), "graph replay %d: small all_reduce" % it)
+            avg = oracle.fold(ins_b, "avg", bf16=True)
+            check(close(to_numpy(yb, "bfloat16"), avg, "bfloat16", world), "graph replay %d: all_reduce avg" % it)
+            want_z = oracle.fold([to_numpy(yb, "bfloat16")] * world, "sum", bf16=True)
+            check(close(to_numpy(zb, "bfloat16"), want_z, "bfloat16", world), "graph replay %d: chained all_reduce" % it)
+            per = n_big // world
+            wsum = oracle.fold(ins_b, "sum", bf16=True)
+            check(close(to_numpy(rs_out, "bfloat16"), wsum[rank * per:(rank + 1) * per], "bfloat16", world), "graph replay %d: reduce_scatter" % it)
+            check(np.array_equal(to_numpy(ag_out, "float32"), np.concatenate(ins_s)), "graph replay %d: all_gather" % it)
+        # eager calls interleave with replays in this mode, and the number goes back to the host afterwards
+        comm.all_reduce(xs, ys, op="max")
+        g.replay()
+        torch.cuda.synchronize()
+        comm.set_param("device_seq", 0)
+        comm.all_reduce(xs, ys, op="max")
+        torch.cuda.synchronize()
+        check(close(to_numpy(ys, "float32"), oracle.fold(ins_s, "max"), "float32", world), "all_reduce after leaving the device-counter mode")
+        del g, g0
+
     code, emsg = comm.last_error()
     check(code == 0, "async error: " + emsg)
     mc = comm.has_multicast
