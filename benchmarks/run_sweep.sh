@@ -9,4 +9,4 @@ ROOT=$(cd "$(dirname "$0")/.." && pwd)
 NCCL_LIB=$(python -c "import glob,sys,os; c=glob.glob(os.path.join(sys.prefix,'lib','python*','site-packages','nvidia','nccl','lib','libnccl.so.2')); print(c[0] if c else '')")
 export DCCL_NCCL_LIB=${DCCL_NCCL_LIB:-$NCCL_LIB}
 exec python -m torch.distributed.run --no-python --nnodes=1 --nproc-per-node "$N" --master-addr 127.0.0.1 --master-port ${MASTER_PORT:-29541} \
-     "$ROOT/build/dccl_sweep" --gpu auto "$@"
+     -- "$ROOT/build/dccl_sweep" --gpu auto "$@"

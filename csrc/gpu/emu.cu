@@ -25,6 +25,9 @@ namespace {
 
 // set by dccl_emu_set_device_seq: the virtual ranks keep their sequence numbers in device counters
 int g_device_seq = 0;
+// set by dccl_emu_set_peer_buffers: the user buffers count as addressable by every rank (symmetric / registered
+// memory), so that the two-shot all-reduce takes its zero-copy form
+int g_peer_buffers = 0;
 
 struct EmuWorld {
     int n = 0;
@@ -90,6 +93,9 @@ extern "C" {
  *  from a CUDA graph); the launch arguments then carry a wrong sequence number on purpose. 0: host counts. */
 void dccl_emu_set_device_seq(int on) { g_device_seq = on ? 1 : 0; }
 
+/** 1: all-reduce with the two-shot variant runs its zero-copy form on the emulated ranks' user buffers. */
+void dccl_emu_set_peer_buffers(int on) { g_peer_buffers = on ? 1 : 0; }
+
 /**
  * Run `iters` back-to-back calls of one collective among `nranks` virtual ranks on the current
  * device and return every rank's output of the last call.
@@ -135,6 +141,12 @@ int dccl_emu_collective(const char* kind_s, const char* algo_s, int nranks, int 
         ios[r].send = s;
         ios[r].recv = d;
     }
+    for (size_t r = 0; r < n; r++)
+        for (size_t p = 0; p < n; p++) {
+            ios[r].send_peer[p] = (const char*)ios[p].send;
+            ios[r].recv_peer[p] = (char*)ios[p].recv;
+        }
+    const bool direct = g_peer_buffers && coll == COLL_ALLREDUCE && algo == ALGO_TWOSHOT && misalign % 16 == 0;
     RankIO* d_ios = nullptr;
     if (cudaMalloc((void**)&d_ios, n * sizeof(RankIO)) != cudaSuccess) return fail("cudaMalloc");
     cudaMemcpy(d_ios, ios.data(), n * sizeof(RankIO), cudaMemcpyHostToDevice);
@@ -167,6 +179,7 @@ int dccl_emu_collective(const char* kind_s, const char* algo_s, int nranks, int 
             if (algo == ALGO_ONESHOT) { cap = oneshot_ll_capacity_bytes() / es; if (count <= cap) e = launch_oneshot_ll(a, dt, cfg); }
             else if (algo == ALGO_RING) { a.mode = RING_ALLREDUCE; cap = ring_capacity(a.mode, nranks, es, stage_bytes); if (count <= cap) e = launch_ring(a, dt, cfg); }
             else if (algo == ALGO_RABENSEIFNER) { cap = hd_capacity(nranks, es, stage_bytes); if (count <= cap && is_power_of_two((uint32_t)nranks)) e = launch_hd(a, dt, cfg); }
+            else if (direct) { a.symmetric = 1; cap = count; e = launch_direct(a, dt, cfg); }
             else { a.mode = TS_ALLREDUCE; cap = twoshot_capacity(a.mode, nranks, es, stage_bytes); if (count <= cap) e = launch_twoshot(a, dt, cfg); }
         } else if (coll != COLL_ALLREDUCE && algo == ALGO_ONESHOT && count * es <= oneshot_ll_capacity_bytes()) {
             a.mode = coll == COLL_REDUCESCATTER ? LL_REDUCESCATTER : coll == COLL_ALLGATHER ? LL_ALLGATHER : coll == COLL_BROADCAST ? LL_BROADCAST : LL_REDUCE;

@@ -83,8 +83,11 @@ ncclResult_t GpuCommImpl::all_reduce(const void* send, void* recv, size_t count,
     const char* sp[kMaxPeers];
     const char* rp[kMaxPeers];
     const char *smc = nullptr, *rmc = nullptr;
-    const bool sym = nvls_ok && bytes % 16 == 0 && sym_view(send, bytes, sp, &smc) && sym_view(recv, bytes, rp, &rmc) && smc && rmc &&
-                     ((uintptr_t)smc % 16 == 0) && ((uintptr_t)rmc % 16 == 0);
+    // every rank can address both buffers of every rank (symmetric memory, or registered buffers)
+    bool peer_addr = sym_view(send, bytes, sp, &smc) && sym_view(recv, bytes, rp, &rmc);
+    // all ranks must come to the same answer: look at every rank's alignment, not only the local one
+    for (int p = 0; peer_addr && p < n_; p++) peer_addr = (uintptr_t)sp[p] % 16 == 0 && (uintptr_t)rp[p] % 16 == 0;
+    const bool sym = peer_addr && nvls_ok && bytes % 16 == 0 && smc && rmc && ((uintptr_t)smc % 16 == 0) && ((uintptr_t)rmc % 16 == 0);
     TuneChoice ch = tuner_.choose(sym ? TUNE_ALLREDUCE_SYM : COLL_ALLREDUCE, n_, bytes, nvls_ok);
     if (algo != ALGO_AUTO) ch.algo = algo;
     // a forced variant that cannot serve this call falls back to the closest one that can
@@ -105,6 +108,17 @@ ncclResult_t GpuCommImpl::all_reduce(const void* send, void* recv, size_t count,
         NEXT_SEQ(a);
         launches_++;
         return cuda_result(launch_oneshot_ll(a, dt, cfg), "one-shot all-reduce");
+    }
+
+    // two-shot on buffers the peers can address: fold straight out of / into the user buffers, no staging
+    if (ch.algo == ALGO_TWOSHOT && peer_addr) {
+        a.symmetric = 1;
+        for (int p = 0; p < n_; p++) { a.io.send_peer[p] = sp[p]; a.io.recv_peer[p] = (char*)rp[p]; }
+        a.count = count;
+        if (ch.ctas < 64 && ctas_override_ == 0) cfg.ctas = ctas_for(64);   // a row meant for the switch variant
+        NEXT_SEQ(a);
+        launches_++;
+        return cuda_result(launch_direct(a, dt, cfg), "zero-copy two-shot all-reduce");
     }
 
     if (ch.algo == ALGO_NVLS && sym) {

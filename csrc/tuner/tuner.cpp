@@ -19,6 +19,13 @@ static const TuneRule kBuiltin[] = {
     {COLL_ALLREDUCE, 0, 128u << 10, ALGO_ONESHOT, 8},
     {COLL_ALLREDUCE, 0, 8u << 20, ALGO_NVLS, 64},
     {COLL_ALLREDUCE, 0, kInf, ALGO_NVLS, 128},
+    // two ranks (measured on 2 x B200): the switch fetches the local copy over NVLink as well, so the peer-to-peer
+    // two-shot variant wins for large messages, with or without symmetric buffers
+    // (zero-copy on buffers the peers can address: 682 GB/s at 1 GB against 410 through the switch)
+    {COLL_ALLREDUCE, 2, 128u << 10, ALGO_ONESHOT, 8},
+    {COLL_ALLREDUCE, 2, kInf, ALGO_TWOSHOT, 128},
+    {TUNE_ALLREDUCE_SYM, 2, 128u << 10, ALGO_ONESHOT, 8},
+    {TUNE_ALLREDUCE_SYM, 2, kInf, ALGO_TWOSHOT, 128},
     // all-reduce, symmetric buffers: zero-copy switch variant; 8-32 CTAs saturate it, more only add contention
     {TUNE_ALLREDUCE_SYM, 0, 64u << 10, ALGO_ONESHOT, 8},
     {TUNE_ALLREDUCE_SYM, 0, kInf, ALGO_NVLS, 16},

@@ -142,7 +142,10 @@ uint32_t dcclGetMyRank(ncclComm_t comm);
  * multiples of CACHELINE_SIZE, otherwise ncclInvalidArgument. Host memory needs
  * no mapping and is only checked. Device memory is exported to every peer
  * process so the kernels can read it in place; this variant is COLLECTIVE for
- * device memory: every rank must call it in the same order.
+ * device memory: every rank must call it in the same order. An all-reduce whose
+ * send and receive buffers both lie inside registered (or dcclMemAlloc) memory
+ * may run without staging, peers folding the buffers directly; such a call must
+ * use the same offset into the registered buffer on every rank.
  */
 ncclResult_t  dcclRegisterCacheMemory(ncclComm_t comm, void* buffer, size_t size);
 ncclResult_t  dcclDeregisterCacheMemory(ncclComm_t comm, void* buffer, size_t size = 0UL);

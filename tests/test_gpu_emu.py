@@ -230,3 +230,23 @@ def test_sequence_number_kept_on_the_device(dccl_lib):
                         assert np.array_equal(out[r], ins[n - 1]), ("bcast", algo, n, count, r)
     finally:
         dccl_lib.dccl_emu_set_device_seq(0)
+
+
+def test_zero_copy_two_shot_on_peer_addressable_buffers(dccl_lib):
+    """Buffers that every rank can address are folded straight out of / into the user memory."""
+    dccl_lib.dccl_emu_set_peer_buffers(1)
+    try:
+        for n in [2, 3, 4, 8]:
+            for name in ["bfloat16", "float32", "int32", "float64", "uint8"]:
+                for count in [1, 7, 4096, 100003, (1 << 20) + 24]:
+                    for op in ["sum", "avg", "min"]:
+                        ins = inputs_for(name, op, count, n, seed=43)
+                        want = oracle.fold(ins, op, bf16=name == "bfloat16")
+                        for in_place in [0, 1]:
+                            out = emu(dccl_lib, "allreduce", "twoshot", n, name, op, count, ins, in_place=in_place, ctas=5)
+                            for r in range(n):
+                                assert close(out[r], want, name, n), (n, name, count, op, r, in_place)
+                            for r in range(1, n):
+                                assert np.array_equal(out[r], out[0]), (n, name, count, op, "ranks differ")
+    finally:
+        dccl_lib.dccl_emu_set_peer_buffers(0)

@@ -147,6 +147,46 @@ def main():
             comm.free_symmetric(t)
         comm.set_algorithm("allreduce", "auto")
 
+    # buffers every rank can address (symmetric, or registered): the two-shot variant folds them without staging
+    if args.suite == "basic":
+        for name, count in [("bfloat16", (1 << 20) + 8), ("float32", 300001), ("int32", 4099)]:
+            ins = [oracle.make_input(name, count, seed=1200 + r) for r in range(world)]
+            for op in ["sum", "avg", "max"]:
+                want = oracle.fold(ins, op, bf16=name == "bfloat16")
+                src = comm.symmetric_empty(count, TORCH[name], local)
+                dst = comm.symmetric_empty(count, TORCH[name], local)
+                src.copy_(to_torch(ins[rank], name, dev))
+                torch.cuda.synchronize()
+                comm.set_algorithm("allreduce", "twoshot")
+                before = comm.launches
+                for _ in range(3):
+                    comm.all_reduce(src, dst, op=op)
+                torch.cuda.synchronize()
+                check(comm.launches - before == 3, "zero-copy two-shot: one launch per call")
+                check(close(to_numpy(dst, name), want, name, world), "zero-copy two-shot all_reduce %s %s" % (name, op))
+                comm.all_reduce(src, op=op)   # in place
+                torch.cuda.synchronize()
+                check(close(to_numpy(src, name), want, name, world), "zero-copy two-shot all_reduce in place %s %s" % (name, op))
+                comm.free_symmetric(src)
+                comm.free_symmetric(dst)
+            # ordinary allocations, registered with every rank
+            # (registration wants whole cache lines: pad the allocation, use its front part)
+            padded = (count + 63) // 64 * 64
+            abuf = torch.zeros(padded, dtype=TORCH[name], device=dev)
+            bbuf = torch.zeros(padded, dtype=TORCH[name], device=dev)
+            a, b = abuf[:count], bbuf[:count]
+            a.copy_(to_torch(ins[rank], name, dev))
+            comm.register(abuf)
+            comm.register(bbuf)
+            before = comm.launches
+            comm.all_reduce(a, b, op="sum")
+            torch.cuda.synchronize()
+            check(comm.launches - before == 1, "registered buffers: one launch")
+            check(close(to_numpy(b, name), oracle.fold(ins, "sum", bf16=name == "bfloat16"), name, world), "registered buffers all_reduce %s" % name)
+            comm.deregister(abuf)
+            comm.deregister(bbuf)
+        comm.set_algorithm("allreduce", "auto")
+
     # send / recv: grouped ring with 8 MB messages (longer than the FIFO), then a plain pair
     msg = torch.full((2 << 20,), float(rank), dtype=torch.float32, device=dev)
     got = torch.zeros_like(msg)

@@ -177,7 +177,7 @@ int main(int argc, char** argv) {
             if (phase == 1 && rc == 0) {
                 const double bytes = (double)windows * (double)depth * (double)size_byte;
                 printf("sent %zu messages of %zu bytes in %.3f s: %.3f GB/s, %.2f us per message\n", windows * depth, size_byte, dt,
-                       bytes / dt / 1e9, dt / (double)(windows * depth ? windows * depth : 1) * 1e6);
+                       bytes / dt / 1e9, dt / (double)(windows * depth > 0 ? windows * depth : 1) * 1e6);
             }
         }
         // the terminating window
