@@ -146,7 +146,8 @@ int dccl_emu_collective(const char* kind_s, const char* algo_s, int nranks, int 
             ios[r].send_peer[p] = (const char*)ios[p].send;
             ios[r].recv_peer[p] = (char*)ios[p].recv;
         }
-    const bool direct = g_peer_buffers && coll == COLL_ALLREDUCE && algo == ALGO_TWOSHOT && misalign % 16 == 0;
+    const bool direct = g_peer_buffers && algo == ALGO_TWOSHOT && misalign % 16 == 0 &&
+                        (coll == COLL_ALLREDUCE || (coll == COLL_REDUCESCATTER && (count * es) % 16 == 0));
     RankIO* d_ios = nullptr;
     if (cudaMalloc((void**)&d_ios, n * sizeof(RankIO)) != cudaSuccess) return fail("cudaMalloc");
     cudaMemcpy(d_ios, ios.data(), n * sizeof(RankIO), cudaMemcpyHostToDevice);
@@ -179,7 +180,7 @@ int dccl_emu_collective(const char* kind_s, const char* algo_s, int nranks, int 
             if (algo == ALGO_ONESHOT) { cap = oneshot_ll_capacity_bytes() / es; if (count <= cap) e = launch_oneshot_ll(a, dt, cfg); }
             else if (algo == ALGO_RING) { a.mode = RING_ALLREDUCE; cap = ring_capacity(a.mode, nranks, es, stage_bytes); if (count <= cap) e = launch_ring(a, dt, cfg); }
             else if (algo == ALGO_RABENSEIFNER) { cap = hd_capacity(nranks, es, stage_bytes); if (count <= cap && is_power_of_two((uint32_t)nranks)) e = launch_hd(a, dt, cfg); }
-            else if (direct) { a.symmetric = 1; cap = count; e = launch_direct(a, dt, cfg); }
+            else if (direct) { a.symmetric = 1; a.mode = DIRECT_ALLREDUCE; cap = count; e = launch_direct(a, dt, cfg); }
             else { a.mode = TS_ALLREDUCE; cap = twoshot_capacity(a.mode, nranks, es, stage_bytes); if (count <= cap) e = launch_twoshot(a, dt, cfg); }
         } else if (coll != COLL_ALLREDUCE && algo == ALGO_ONESHOT && count * es <= oneshot_ll_capacity_bytes()) {
             a.mode = coll == COLL_REDUCESCATTER ? LL_REDUCESCATTER : coll == COLL_ALLGATHER ? LL_ALLGATHER : coll == COLL_BROADCAST ? LL_BROADCAST : LL_REDUCE;
@@ -187,6 +188,7 @@ int dccl_emu_collective(const char* kind_s, const char* algo_s, int nranks, int 
             e = launch_ll_collective(a, dt, cfg);
         } else if (coll == COLL_REDUCESCATTER) {
             if (algo == ALGO_RING) { a.mode = RING_REDUCESCATTER; cap = ring_capacity(a.mode, nranks, es, stage_bytes); if (count <= cap) e = launch_ring(a, dt, cfg); }
+            else if (direct) { a.symmetric = 1; a.mode = DIRECT_REDUCESCATTER; cap = count; e = launch_direct(a, dt, cfg); }
             else { a.mode = TS_REDUCESCATTER; cap = twoshot_capacity(a.mode, nranks, es, stage_bytes); if (count <= cap) e = launch_twoshot(a, dt, cfg); }
         } else if (coll == COLL_ALLGATHER) {
             if (algo == ALGO_RING) { a.mode = RING_ALLGATHER; cap = ring_capacity(a.mode, nranks, es, stage_bytes); if (count <= cap) e = launch_ring(a, dt, cfg); }

@@ -17,6 +17,10 @@
  * choice where the switch cannot reduce (no multicast binding) and at world
  * size two, where multimem fetches the local copy through the switch as well.
  * Every rank stores identical bits: a shard is folded by exactly one rank.
+ *
+ * Reduce-scatter has the same form with one destination: rank r folds slot r of
+ * every rank's send buffer into its own receive buffer (only the send buffers
+ * have to be addressable by the peers).
  */
 #include "kernels.hpp"
 #include "../device/geometry.cuh"
@@ -25,12 +29,12 @@
 namespace dccl {
 
 /**
- * Fold `nvec` 16-byte vectors starting `byte_off` into every rank's receive buffer.
- * NR > 0: world size known at compile time, U vectors per source in flight per thread
- * (NR x U = 8 loads outstanding); NR == 0: any world size, one vector per source.
+ * out = fold over `n` sources of `nvec` 16-byte vectors, stored to `ndst` destinations.
+ * NR > 0: number of sources known at compile time, U vectors per source in flight per thread
+ * (NR x U = 8 loads outstanding); NR == 0: any number, one vector per source.
  */
 template <typename T, int OP, int NR>
-__device__ __forceinline__ void direct_pass(const RankIO& io, int n, int r, size_t byte_off, size_t nvec, bool avg) {
+__device__ __forceinline__ void direct_pass(const char* const* srcs, char* const* dsts, int n, int ndst, size_t nvec, bool avg) {
     using A = typename Traits<T>::Acc;
     constexpr int N = Vec16<T>::N;
     constexpr int U = NR == 0 ? 1 : 8 / NR;
@@ -40,9 +44,8 @@ __device__ __forceinline__ void direct_pass(const RankIO& io, int n, int r, size
     char* dst[S];
 #pragma unroll
     for (int s = 0; s < S; s++) {
-        const int p = s < n ? (r + s) % n : r;      // own copy first
-        src[s] = io.send_peer[p] + byte_off;
-        dst[s] = io.recv_peer[p] + byte_off;
+        src[s] = srcs[s < n ? s : 0];
+        dst[s] = dsts[s < ndst ? s : 0];
     }
     for (size_t i0 = tid; i0 < nvec; i0 += (size_t)U * nt) {
         Vec16<T> v[S][U];
@@ -75,7 +78,7 @@ __device__ __forceinline__ void direct_pass(const RankIO& io, int n, int r, size
             for (int e = 0; e < N; e++) out.e[e] = Traits<T>::down(avg ? avg_finish<A>(acc[e], n) : acc[e]);
 #pragma unroll
             for (int s = 0; s < S; s++)
-                if (s < n) st_vec<T>(dst[s] + i * 16, out);
+                if (s < ndst) st_vec<T>(dst[s] + i * 16, out);
         }
     }
 }
@@ -87,27 +90,35 @@ __device__ __forceinline__ void direct_body(const CollArgs& a, const Ctx& x) {
     const RankIO& io = *x.io;
     const int n = c.nranks, r = c.rank;
     const bool avg = a.op == (int)ncclAvg;
-    const Geometry<T> g(GEO_SPLIT, a.count, n, x.bid, x.nb);
+    const bool rs = a.mode == DIRECT_REDUCESCATTER;
+    // all-reduce: this rank folds shard r of one vector; reduce-scatter: slot r (count elements) of every send buffer
+    const Geometry<T> g(rs ? GEO_WHOLE : GEO_SPLIT, a.count, rs ? 1 : n, x.bid, x.nb);
 
     if (!rank_barrier(c, x.bid, x.seq, 0, 900)) return;
 
-    const size_t len = g.len(r);
+    const size_t len = rs ? a.count : g.len(r);
     const size_t lo = g.blo < len ? g.blo : len, hi = g.bhi < len ? g.bhi : len;
     if (hi > lo) {
         // shard and CTA boundaries are multiples of one vector; only the very end of the message can be ragged
-        const size_t first = (size_t)r * g.per + lo, cnt = hi - lo;
+        const size_t first = (rs ? (size_t)r * a.stride : (size_t)r * g.per) + lo, cnt = hi - lo;
         const size_t nvec = cnt / Vec16<T>::N;
-        const size_t byte_off = first * sizeof(T);
-        if (n == 2) direct_pass<T, OP, 2>(io, n, r, byte_off, nvec, avg);
-        else if (n == 4) direct_pass<T, OP, 4>(io, n, r, byte_off, nvec, avg);
-        else if (n == 8) direct_pass<T, OP, 8>(io, n, r, byte_off, nvec, avg);
-        else direct_pass<T, OP, 0>(io, n, r, byte_off, nvec, avg);
+        const char* srcs[kMaxPeers];
+        char* dsts[kMaxPeers];
+        for (int s = 0; s < n; s++) {
+            const int p = (r + s) % n;      // own copy first
+            srcs[s] = io.send_peer[p] + first * sizeof(T);
+            dsts[s] = rs ? reinterpret_cast<char*>(io.recv) + lo * sizeof(T) : io.recv_peer[p] + first * sizeof(T);
+        }
+        const int ndst = rs ? 1 : n;
+        if (n == 2) direct_pass<T, OP, 2>(srcs, dsts, n, ndst, nvec, avg);
+        else if (n == 4) direct_pass<T, OP, 4>(srcs, dsts, n, ndst, nvec, avg);
+        else if (n == 8) direct_pass<T, OP, 8>(srcs, dsts, n, ndst, nvec, avg);
+        else direct_pass<T, OP, 0>(srcs, dsts, n, ndst, nvec, avg);
         for (size_t j = nvec * Vec16<T>::N + threadIdx.x; j < cnt; j += blockDim.x) {
-            const size_t e = first + j;
-            A acc = Traits<T>::up(reinterpret_cast<const T*>(io.send_peer[r])[e]);
-            for (int s = 1; s < n; s++) acc = op_apply<OP, A>(acc, Traits<T>::up(reinterpret_cast<const T*>(io.send_peer[(r + s) % n])[e]));
+            A acc = Traits<T>::up(reinterpret_cast<const T*>(srcs[0])[j]);
+            for (int s = 1; s < n; s++) acc = op_apply<OP, A>(acc, Traits<T>::up(reinterpret_cast<const T*>(srcs[s])[j]));
             const T out = Traits<T>::down(avg ? avg_finish<A>(acc, n) : acc);
-            for (int s = 0; s < n; s++) reinterpret_cast<T*>(io.recv_peer[s])[e] = out;
+            for (int s = 0; s < ndst; s++) reinterpret_cast<T*>(dsts[s])[j] = out;
         }
     }
     rank_barrier(c, x.bid, x.seq, 1, 950);

@@ -23,7 +23,9 @@ enum { TS_ALLREDUCE = 0, TS_REDUCESCATTER, TS_ALLGATHER, TS_BROADCAST, TS_BROADC
 size_t twoshot_capacity(int mode, int nranks, size_t elem_size, size_t stage_bytes);
 cudaError_t launch_twoshot(const CollArgs& a, ncclDataType_t dt, const LaunchCfg& cfg);
 
-/* direct.cu: zero-copy peer all-reduce; io.send_peer / io.recv_peer must hold every rank's buffers (16-byte aligned) */
+/* direct.cu: zero-copy peer all-reduce (io.send_peer / io.recv_peer hold every rank's buffers, 16-byte aligned) and
+ * reduce-scatter (io.send_peer, io.recv; count = per-rank elements, stride = slot distance, slots 16-byte aligned) */
+enum { DIRECT_ALLREDUCE = 0, DIRECT_REDUCESCATTER };
 cudaError_t launch_direct(const CollArgs& a, ncclDataType_t dt, const LaunchCfg& cfg);
 
 /* oneshot_ll.cu: flag-in-data all-reduce for small messages */

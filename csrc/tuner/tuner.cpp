@@ -26,6 +26,8 @@ static const TuneRule kBuiltin[] = {
     {COLL_ALLREDUCE, 2, kInf, ALGO_TWOSHOT, 128},
     {TUNE_ALLREDUCE_SYM, 2, 128u << 10, ALGO_ONESHOT, 8},
     {TUNE_ALLREDUCE_SYM, 2, kInf, ALGO_TWOSHOT, 128},
+    {TUNE_REDUCESCATTER_SYM, 2, 256u << 10, ALGO_ONESHOT, 8},
+    {TUNE_REDUCESCATTER_SYM, 2, kInf, ALGO_TWOSHOT, 128},
     // all-reduce, symmetric buffers: zero-copy switch variant; 8-32 CTAs saturate it, more only add contention
     {TUNE_ALLREDUCE_SYM, 0, 64u << 10, ALGO_ONESHOT, 8},
     {TUNE_ALLREDUCE_SYM, 0, kInf, ALGO_NVLS, 16},

@@ -248,5 +248,15 @@ def test_zero_copy_two_shot_on_peer_addressable_buffers(dccl_lib):
                                 assert close(out[r], want, name, n), (n, name, count, op, r, in_place)
                             for r in range(1, n):
                                 assert np.array_equal(out[r], out[0]), (n, name, count, op, "ranks differ")
+            # reduce-scatter: slot r of every send buffer folded into rank r's receive buffer (whole vectors per slot)
+            for name in ["bfloat16", "float32", "int64"]:
+                for count in [16, 4096, 100000, (1 << 19) + 64]:
+                    for op in ["sum", "avg", "max"]:
+                        ins = inputs_for(name, op, count * n, n, seed=47)
+                        want = oracle.fold(ins, op, bf16=name == "bfloat16")
+                        for in_place in [0, 1]:
+                            out = emu(dccl_lib, "reducescatter", "twoshot", n, name, op, count, ins, in_place=in_place, ctas=5)
+                            for r in range(n):
+                                assert close(out[r], want[r * count:(r + 1) * count], name, n), ("rs", n, name, count, op, r, in_place)
     finally:
         dccl_lib.dccl_emu_set_peer_buffers(0)

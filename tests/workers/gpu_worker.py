@@ -149,7 +149,7 @@ def main():
 
     # buffers every rank can address (symmetric, or registered): the two-shot variant folds them without staging
     if args.suite == "basic":
-        for name, count in [("bfloat16", (1 << 20) + 8), ("float32", 300001), ("int32", 4099)]:
+        for name, count in [("bfloat16", (1 << 20) + 64), ("float32", 300001), ("int32", 4099)]:
             ins = [oracle.make_input(name, count, seed=1200 + r) for r in range(world)]
             for op in ["sum", "avg", "max"]:
                 want = oracle.fold(ins, op, bf16=name == "bfloat16")
@@ -167,6 +167,15 @@ def main():
                 comm.all_reduce(src, op=op)   # in place
                 torch.cuda.synchronize()
                 check(close(to_numpy(src, name), want, name, world), "zero-copy two-shot all_reduce in place %s %s" % (name, op))
+                if count % (8 * world) == 0:
+                    per = count // world
+                    src.copy_(to_torch(ins[rank], name, dev))
+                    torch.cuda.synchronize()
+                    comm.set_algorithm("reducescatter", "twoshot")
+                    comm.reduce_scatter(src, dst[:per], op=op)
+                    torch.cuda.synchronize()
+                    check(close(to_numpy(dst[:per], name), want[rank * per:(rank + 1) * per], name, world), "zero-copy two-shot reduce_scatter %s %s" % (name, op))
+                    comm.set_algorithm("reducescatter", "auto")
                 comm.free_symmetric(src)
                 comm.free_symmetric(dst)
             # ordinary allocations, registered with every rank
