@@ -3,6 +3,11 @@
 ncu capture: inputs larger than L2, a few GB on the device at most, two launches.
 
     python benchmarks/profile_emu.py --kind allreduce --algo twoshot --ranks 8 --mb 64 --ctas 16
+    python benchmarks/profile_emu.py --kind allreduce --algo twoshot --peer-buffers --ranks 8 --mb 64   (zero-copy form, k_direct)
+    python benchmarks/profile_emu.py --kind allreduce --algo rabenseifner --ranks 8 --mb 64               (k_hd)
+    python benchmarks/profile_emu.py --kind reducescatter --algo oneshot --ranks 8 --mb 0.0625           (k_ll_collective)
+    python benchmarks/profile_emu.py --kind sendrecv --ranks 8 --mb 64 --ctas 16                          (k_p2p, ring of pairs)
+    python benchmarks/profile_emu.py --kind switch --mb 256 --ctas 16     (k_nvls on a one-member multicast object, where the driver allows one)
     ncu --set full --clock-control none -k regex:k_twoshot -c 1 -o prof_twoshot \\
         python benchmarks/profile_emu.py --kind allreduce --algo twoshot --ranks 8 --mb 64 --ctas 16
 """
@@ -25,9 +30,27 @@ def main():
     ap.add_argument("--mb", type=float, default=64.0, help="message MB per rank (fp32)")
     ap.add_argument("--ctas", type=int, default=16)
     ap.add_argument("--iters", type=int, default=2)
+    ap.add_argument("--peer-buffers", action="store_true", help="user buffers count as addressable by every rank (zero-copy two-shot)")
+    ap.add_argument("--device-seq", action="store_true", help="sequence numbers counted on the device (the CUDA-graph mode)")
     args = ap.parse_args()
     L = lib()
     n = args.ranks
+    L.dccl_emu_set_peer_buffers(1 if args.peer_buffers else 0)
+    L.dccl_emu_set_device_seq(1 if args.device_seq else 0)
+    if args.kind == "switch":
+        count = int(args.mb * (1 << 20)) // 4
+        hin = np.arange(count, dtype=np.float32)
+        hout = np.zeros(count, dtype=np.float32)
+        rc = L.dccl_emu_switch_single(7, 0, count, args.ctas, args.iters, hin.ctypes.data, hout.ctypes.data)
+        print("rc", rc, "(-10: no multicast here, -11: set-up refused)", "match", bool(rc == 0 and np.array_equal(hin, hout)))
+        sys.exit(0 if rc == 0 and np.array_equal(hin, hout) else 1)
+    if args.kind == "sendrecv":
+        nbytes = int(args.mb * (1 << 20))
+        hin = np.ones(n * nbytes, dtype=np.uint8)
+        hout = np.zeros(n * nbytes, dtype=np.uint8)
+        rc = L.dccl_emu_sendrecv_ring(n, nbytes, 1, args.ctas, args.iters, hin.ctypes.data, hout.ctypes.data)
+        print("rc", rc, "sample", hout[:2])
+        sys.exit(0 if rc == 0 else 1)
     count = int(args.mb * (1 << 20)) // 4
     in_elems = count * n if args.kind == "reducescatter" else count
     out_elems = count * n if args.kind == "allgather" else count

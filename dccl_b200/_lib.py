@@ -85,6 +85,7 @@ def _declare(lib):
         "dccl_emu_wait_probe": (i, [c.c_uint, c.POINTER(c.c_float)]),
         "dccl_emu_set_device_seq": (None, [i]),
         "dccl_emu_set_peer_buffers": (None, [i]),
+        "dccl_emu_switch_single": (i, [i, i, sz, i, i, vp, vp]),
         "dccl_local_reduce": (i, [vp, vp, sz, i, i]),
     }
     for name, (res, args) in sigs.items():
