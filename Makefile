@@ -37,7 +37,7 @@ endif
 
 HOST_SRCS := csrc/core/config.cpp csrc/core/log.cpp csrc/core/timestamp.cpp \
              csrc/bootstrap/bootstrap.cpp csrc/cpu/cpu_backend.cpp \
-             csrc/api/dccl_api.cpp csrc/api/c_api.cpp csrc/api/names.cpp csrc/tuner/tuner.cpp
+             csrc/api/dccl_api.cpp csrc/api/composed.cpp csrc/api/c_api.cpp csrc/api/names.cpp csrc/tuner/tuner.cpp
 ifeq ($(CUDA),1)
 CU_SRCS := $(wildcard csrc/gpu/*.cu) $(wildcard csrc/kernels/*.cu)
 CXXFLAGS += -DDCCL_WITH_CUDA -DDCCL_WITH_CUDA_RUNTIME -I$(CUDA_HOME)/include

@@ -77,6 +77,19 @@ int dccl_send(const void* s, size_t count, int dt, int peer, void* comm, void* s
 int dccl_recv(void* r, size_t count, int dt, int peer, void* comm, void* stream) {
     GUARD(ncclRecv(r, count, (ncclDataType_t)dt, peer, (ncclComm_t)comm, (cudaStream_t)stream));
 }
+int dccl_all_to_all(const void* s, void* r, size_t count, int dt, void* comm, void* stream) {
+    GUARD(dcclAllToAll(s, r, count, (ncclDataType_t)dt, (ncclComm_t)comm, (cudaStream_t)stream));
+}
+int dccl_all_to_allv(const void* s, const size_t* scounts, const size_t* sdispls, void* r, const size_t* rcounts, const size_t* rdispls,
+                     int dt, void* comm, void* stream) {
+    GUARD(dcclAllToAllv(s, scounts, sdispls, r, rcounts, rdispls, (ncclDataType_t)dt, (ncclComm_t)comm, (cudaStream_t)stream));
+}
+int dccl_gather(const void* s, void* r, size_t count, int dt, int root, void* comm, void* stream) {
+    GUARD(dcclGather(s, r, count, (ncclDataType_t)dt, root, (ncclComm_t)comm, (cudaStream_t)stream));
+}
+int dccl_scatter(const void* s, void* r, size_t count, int dt, int root, void* comm, void* stream) {
+    GUARD(dcclScatter(s, r, count, (ncclDataType_t)dt, root, (ncclComm_t)comm, (cudaStream_t)stream));
+}
 int dccl_group_start() { return (int)dcclGroupStart(); }
 int dccl_group_end() { return (int)dcclGroupEnd(); }
 int dccl_set_algorithm(void* comm, const char* coll, const char* name) { GUARD(dcclSetAlgorithm((ncclComm_t)comm, coll, name)); }

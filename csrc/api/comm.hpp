@@ -26,4 +26,7 @@ struct dcclComm {
     uint64_t bytes[COLL_COUNT] = {0, 0, 0, 0, 0, 0};
 };
 
+/** Bind the device side of the communicator on first use (collective: every rank gets here with its first device call). */
+ncclResult_t ensure_gpu(dcclComm* c, int device);
+
 } // namespace dccl

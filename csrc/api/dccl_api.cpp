@@ -178,7 +178,7 @@ static Where classify(const void* a, const void* b, int* device) {
     return ON_HOST;
 }
 
-static ncclResult_t ensure_gpu(dcclComm* c, int device) {
+ncclResult_t ensure_gpu(dcclComm* c, int device) {
     if (c->gpu) return ncclSuccess;
     if (c->gpu_failed) return ncclUnhandledCudaError;
     std::lock_guard<std::mutex> g(c->mu);

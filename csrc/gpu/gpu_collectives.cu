@@ -14,6 +14,7 @@
 #include "../core/log.hpp"
 #include "../core/types.hpp"
 #include <nvtx3/nvToolsExt.h>
+#include <algorithm>
 
 namespace dccl {
 
@@ -456,6 +457,9 @@ ncclResult_t GpuCommImpl::reduce(const void* send, void* recv, size_t count, ncc
 
 ncclResult_t GpuCommImpl::p2p_launch(std::vector<P2pOp>& ops, cudaStream_t stream) {
     DeviceGuard g(dev_);
+    // Receivers get the lower block numbers: they never wait for anything but data, so once they are resident
+    // every sender that waits for FIFO credit is waiting for a CTA that runs, however many CTAs the launch has.
+    std::stable_partition(ops.begin(), ops.end(), [](const P2pOp& o) { return o.is_send == 0; });
     for (size_t first = 0; first < ops.size(); first += kMaxP2pOps) {
         P2pArgs a;
         memset(&a, 0, sizeof(a));
@@ -466,7 +470,7 @@ ncclResult_t GpuCommImpl::p2p_launch(std::vector<P2pOp>& ops, cudaStream_t strea
         LaunchCfg cfg;
         cfg.ctas = a.nops * p2p_ctas_;
         cfg.stream = stream;
-    cfg.threads = threads_;
+        cfg.threads = threads_;
         a.ctas_per_rank = cfg.ctas;
         launches_++;
         cudaError_t e = launch_p2p(a, cfg);

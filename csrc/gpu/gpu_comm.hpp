@@ -51,6 +51,8 @@ public:
     virtual ncclResult_t recv(void* buf, size_t bytes, int peer, cudaStream_t stream) = 0;
     virtual void group_start() = 0;
     virtual ncclResult_t group_end() = 0;
+    /** dst = src on this device, stream ordered (the own block of all-to-all / gather / scatter). */
+    virtual ncclResult_t local_copy(void* dst, const void* src, size_t bytes, cudaStream_t stream) = 0;
 
     virtual ncclResult_t mem_alloc(void** ptr, size_t size) = 0;
     virtual ncclResult_t mem_free(void* ptr) = 0;

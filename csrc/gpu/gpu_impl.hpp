@@ -33,6 +33,11 @@ public:
     ncclResult_t recv(void* buf, size_t bytes, int peer, cudaStream_t stream) override;
     void group_start() override { in_group_ = true; }
     ncclResult_t group_end() override;
+    ncclResult_t local_copy(void* dst, const void* src, size_t bytes, cudaStream_t stream) override {
+        DeviceGuard g(dev_);
+        launches_++;
+        return cuda_result(launch_local_copy(dst, src, bytes, stream), "local copy");
+    }
 
     ncclResult_t mem_alloc(void** ptr, size_t size) override;
     ncclResult_t mem_free(void* ptr) override;

@@ -229,6 +229,100 @@ public:
             return dccl::ncclRecv(t.data_ptr(), (size_t)t.numel(), to_dtype(t.scalar_type()), src, comm_, s);
         });
     }
+    c10::intrusive_ptr<Work> alltoall_base(at::Tensor& out, at::Tensor& in, std::vector<int64_t>& out_splits, std::vector<int64_t>& in_splits,
+                                           const c10d::AllToAllOptions&) override {
+        TORCH_CHECK(out.is_contiguous() && in.is_contiguous(), "dccl backend: tensors must be contiguous");
+        TORCH_CHECK(out.scalar_type() == in.scalar_type(), "dccl backend: all_to_all tensors must have one dtype");
+        const int n = getSize();
+        // splits count rows of dimension 0; a row is numel / size(0) elements
+        const size_t in_row = in.dim() > 0 && in.size(0) > 0 ? (size_t)(in.numel() / in.size(0)) : 1;
+        const size_t out_row = out.dim() > 0 && out.size(0) > 0 ? (size_t)(out.numel() / out.size(0)) : 1;
+        std::vector<size_t> sc((size_t)n), sd((size_t)n), rc((size_t)n), rd((size_t)n);
+        if (in_splits.empty()) {
+            TORCH_CHECK(in.numel() % n == 0, "dccl backend: all_to_all input must divide by the world size");
+            for (int p = 0; p < n; p++) sc[(size_t)p] = (size_t)in.numel() / (size_t)n;
+        } else {
+            TORCH_CHECK((int)in_splits.size() == n, "dccl backend: one input split per rank");
+            for (int p = 0; p < n; p++) sc[(size_t)p] = (size_t)in_splits[(size_t)p] * in_row;
+        }
+        if (out_splits.empty()) {
+            TORCH_CHECK(out.numel() % n == 0, "dccl backend: all_to_all output must divide by the world size");
+            for (int p = 0; p < n; p++) rc[(size_t)p] = (size_t)out.numel() / (size_t)n;
+        } else {
+            TORCH_CHECK((int)out_splits.size() == n, "dccl backend: one output split per rank");
+            for (int p = 0; p < n; p++) rc[(size_t)p] = (size_t)out_splits[(size_t)p] * out_row;
+        }
+        size_t so = 0, ro = 0;
+        for (int p = 0; p < n; p++) { sd[(size_t)p] = so; so += sc[(size_t)p]; rd[(size_t)p] = ro; ro += rc[(size_t)p]; }
+        TORCH_CHECK(so <= (size_t)in.numel() && ro <= (size_t)out.numel(), "dccl backend: splits exceed the tensors");
+        return run(c10d::OpType::ALLTOALL_BASE, {out}, out, [&](cudaStream_t s) {
+            return dccl::dcclAllToAllv(in.data_ptr(), sc.data(), sd.data(), out.data_ptr(), rc.data(), rd.data(), to_dtype(in.scalar_type()), comm_, s);
+        });
+    }
+    c10::intrusive_ptr<Work> alltoall(std::vector<at::Tensor>& outs, std::vector<at::Tensor>& ins, const c10d::AllToAllOptions&) override {
+        const int n = getSize(), me = getRank();
+        TORCH_CHECK((int)outs.size() == n && (int)ins.size() == n, "dccl backend: all_to_all expects world_size tensors on both sides");
+        for (int p = 0; p < n; p++) TORCH_CHECK(outs[(size_t)p].is_contiguous() && ins[(size_t)p].is_contiguous(), "dccl backend: tensors must be contiguous");
+        return run(c10d::OpType::ALLTOALL, outs, outs[0], [&](cudaStream_t s) {
+            dccl::ncclResult_t res = dccl::ncclSuccess;
+            dccl::dcclGroupStart();
+            for (int k = 1; k < n && res == dccl::ncclSuccess; k++) {
+                at::Tensor& t = outs[(size_t)((me - k + n) % n)];
+                if (t.numel()) res = dccl::ncclRecv(t.data_ptr(), (size_t)t.numel(), to_dtype(t.scalar_type()), (me - k + n) % n, comm_, s);
+            }
+            for (int k = 1; k < n && res == dccl::ncclSuccess; k++) {
+                at::Tensor& t = ins[(size_t)((me + k) % n)];
+                if (t.numel()) res = dccl::ncclSend(t.data_ptr(), (size_t)t.numel(), to_dtype(t.scalar_type()), (me + k) % n, comm_, s);
+            }
+            dccl::ncclResult_t e = dccl::dcclGroupEnd();
+            if (res == dccl::ncclSuccess) res = e;
+            if (res == dccl::ncclSuccess) outs[(size_t)me].copy_(ins[(size_t)me], true);
+            return res;
+        }, /*torch_ops=*/true);
+    }
+    c10::intrusive_ptr<Work> gather(std::vector<std::vector<at::Tensor>>& outs, std::vector<at::Tensor>& ins, const c10d::GatherOptions& opts) override {
+        const int n = getSize(), me = getRank(), root = (int)opts.rootRank;
+        at::Tensor& in = one(ins);
+        if (me == root) TORCH_CHECK(outs.size() == 1 && (int)outs[0].size() == n, "dccl backend: the root of gather needs world_size outputs");
+        if (me == root)
+            for (auto& t : outs[0]) TORCH_CHECK(t.is_contiguous() && t.numel() == in.numel(), "dccl backend: gather outputs must be contiguous and of the input's size");
+        std::vector<at::Tensor> results = me == root ? outs[0] : std::vector<at::Tensor>{};
+        return run(c10d::OpType::GATHER, results, in, [&](cudaStream_t s) {
+            if (me != root) return dccl::ncclSend(in.data_ptr(), (size_t)in.numel(), to_dtype(in.scalar_type()), root, comm_, s);
+            dccl::ncclResult_t res = dccl::ncclSuccess;
+            dccl::dcclGroupStart();
+            for (int p = 0; p < n && res == dccl::ncclSuccess; p++) {
+                if (p == root) continue;
+                at::Tensor& t = outs[0][(size_t)p];
+                res = dccl::ncclRecv(t.data_ptr(), (size_t)t.numel(), to_dtype(t.scalar_type()), p, comm_, s);
+            }
+            dccl::ncclResult_t e = dccl::dcclGroupEnd();
+            if (res == dccl::ncclSuccess) res = e;
+            if (res == dccl::ncclSuccess) outs[0][(size_t)root].copy_(in, true);
+            return res;
+        }, /*torch_ops=*/true);
+    }
+    c10::intrusive_ptr<Work> scatter(std::vector<at::Tensor>& outs, std::vector<std::vector<at::Tensor>>& ins, const c10d::ScatterOptions& opts) override {
+        const int n = getSize(), me = getRank(), root = (int)opts.rootRank;
+        at::Tensor& out = one(outs);
+        if (me == root) TORCH_CHECK(ins.size() == 1 && (int)ins[0].size() == n, "dccl backend: the root of scatter needs world_size inputs");
+        if (me == root)
+            for (auto& t : ins[0]) TORCH_CHECK(t.is_contiguous() && t.numel() == out.numel(), "dccl backend: scatter inputs must be contiguous and of the output's size");
+        return run(c10d::OpType::SCATTER, {out}, out, [&](cudaStream_t s) {
+            if (me != root) return dccl::ncclRecv(out.data_ptr(), (size_t)out.numel(), to_dtype(out.scalar_type()), root, comm_, s);
+            dccl::ncclResult_t res = dccl::ncclSuccess;
+            dccl::dcclGroupStart();
+            for (int p = 0; p < n && res == dccl::ncclSuccess; p++) {
+                if (p == root) continue;
+                at::Tensor& t = ins[0][(size_t)p];
+                res = dccl::ncclSend(t.data_ptr(), (size_t)t.numel(), to_dtype(t.scalar_type()), p, comm_, s);
+            }
+            dccl::ncclResult_t e = dccl::dcclGroupEnd();
+            if (res == dccl::ncclSuccess) res = e;
+            if (res == dccl::ncclSuccess) out.copy_(ins[0][(size_t)root], true);
+            return res;
+        }, /*torch_ops=*/true);
+    }
     c10::intrusive_ptr<Work> barrier(const c10d::BarrierOptions&) override {
         // a host all-reduce of one word: returns when every rank has arrived
         int32_t word = 0;

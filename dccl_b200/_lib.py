@@ -54,6 +54,10 @@ def _declare(lib):
         "dccl_reduce": (i, [vp, vp, sz, i, i, i, vp, vp]),
         "dccl_send": (i, [vp, sz, i, i, vp, vp]),
         "dccl_recv": (i, [vp, sz, i, i, vp, vp]),
+        "dccl_all_to_all": (i, [vp, vp, sz, i, vp, vp]),
+        "dccl_all_to_allv": (i, [vp, c.POINTER(sz), c.POINTER(sz), vp, c.POINTER(sz), c.POINTER(sz), i, vp, vp]),
+        "dccl_gather": (i, [vp, vp, sz, i, i, vp, vp]),
+        "dccl_scatter": (i, [vp, vp, sz, i, i, vp, vp]),
         "dccl_group_start": (i, []),
         "dccl_group_end": (i, []),
         "dccl_set_algorithm": (i, [vp, cp, cp]),

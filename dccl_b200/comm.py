@@ -236,6 +236,34 @@ class Communicator:
                                  _stream_of(send, stream)), "ncclReduce")
         return recv
 
+    def all_to_all(self, send, recv, send_counts=None, recv_counts=None, stream=None):
+        """Block p of `send` goes to rank p, block p of `recv` comes from rank p. Equal blocks unless
+        per-peer element counts are given (blocks are then packed back to back)."""
+        if send_counts is None and recv_counts is None:
+            _check(lib().dccl_all_to_all(_addr(send), _addr(recv), _numel(send) // self.world, dtype_of(send), self._h,
+                                         _stream_of(send, stream)), "dcclAllToAll")
+            return recv
+        arr = ctypes.c_size_t * self.world
+        sc = list(send_counts if send_counts is not None else [_numel(send) // self.world] * self.world)
+        rc = list(recv_counts if recv_counts is not None else [_numel(recv) // self.world] * self.world)
+        sd = [sum(sc[:p]) for p in range(self.world)]
+        rd = [sum(rc[:p]) for p in range(self.world)]
+        _check(lib().dccl_all_to_allv(_addr(send), arr(*sc), arr(*sd), _addr(recv), arr(*rc), arr(*rd), dtype_of(send), self._h,
+                                      _stream_of(send, stream)), "dcclAllToAllv")
+        return recv
+
+    def gather(self, send, recv=None, root=0, stream=None):
+        """The root receives every rank's `send` into block <rank> of `recv`."""
+        _check(lib().dccl_gather(_addr(send), _addr(recv) if recv is not None else None, _numel(send), dtype_of(send), root, self._h,
+                                 _stream_of(send, stream)), "dcclGather")
+        return recv
+
+    def scatter(self, send, recv, root=0, stream=None):
+        """Rank p receives block p of the root's `send` into `recv`."""
+        _check(lib().dccl_scatter(_addr(send) if send is not None else None, _addr(recv), _numel(recv), dtype_of(recv), root, self._h,
+                                  _stream_of(recv, stream)), "dcclScatter")
+        return recv
+
     def send(self, x, peer, stream=None):
         _check(lib().dccl_send(_addr(x), _numel(x), dtype_of(x), peer, self._h, _stream_of(x, stream)), "ncclSend")
 

@@ -196,6 +196,27 @@ ncclResult_t  dcclGroupStart();
 ncclResult_t  dcclGroupEnd();
 
 /**
+ * Collectives composed of grouped send / recv (no counterpart in the original,
+ * whose API stops at ncclSend / ncclRecv). Buffers are all on the host or all
+ * on the device; device calls are ONE launch on `stream` plus a local copy of
+ * the rank's own block.
+ *   dcclAllToAll   block p (count elements) of sendbuff goes to rank p, block p of recvbuff comes from rank p
+ *   dcclAllToAllv  the same with per-peer counts and displacements (in elements; arrays of world size)
+ *   dcclGather     root receives count elements from every rank into block <rank> of recvbuff
+ *   dcclScatter    root sends block p of sendbuff (count elements) to rank p's recvbuff
+ * recvbuff (gather) and sendbuff (scatter) are only read on the root.
+ */
+ncclResult_t  dcclAllToAll(const void* sendbuff, void* recvbuff, size_t count, ncclDataType_t datatype,
+    ncclComm_t comm, cudaStream_t stream);
+ncclResult_t  dcclAllToAllv(const void* sendbuff, const size_t* sendcounts, const size_t* sdispls,
+    void* recvbuff, const size_t* recvcounts, const size_t* rdispls, ncclDataType_t datatype,
+    ncclComm_t comm, cudaStream_t stream);
+ncclResult_t  dcclGather(const void* sendbuff, void* recvbuff, size_t count, ncclDataType_t datatype, int root,
+    ncclComm_t comm, cudaStream_t stream);
+ncclResult_t  dcclScatter(const void* sendbuff, void* recvbuff, size_t count, ncclDataType_t datatype, int root,
+    ncclComm_t comm, cudaStream_t stream);
+
+/**
  * Force an algorithm for one collective ("allreduce", "reducescatter",
  * "allgather", "broadcast", "reduce") on this communicator. name is one of
  * auto, ring, rabenseifner, oneshot, twoshot, nvls. Unknown names give

@@ -154,6 +154,25 @@ def main():
             else:
                 comm.recv(got, 0)
                 check(np.all(got == 0), "blocking send/recv")
+    # all-to-all (equal and uneven blocks), gather, scatter
+    for n in [1, 1000, 400001]:
+        src = [np.arange(n * world, dtype=np.float64) + 1e6 * r for r in range(world)]
+        out = np.zeros(n * world, dtype=np.float64)
+        comm.all_to_all(src[rank], out)
+        check(np.array_equal(out, np.concatenate([src[p][rank * n:(rank + 1) * n] for p in range(world)])), "all_to_all n=%d" % n)
+        for root in {0, world - 1}:
+            got = np.zeros(n * world, dtype=np.float64) if rank == root else None
+            comm.gather(src[rank][:n], got, root=root)
+            check(rank != root or np.array_equal(got, np.concatenate([src[p][:n] for p in range(world)])), "gather n=%d root=%d" % (n, root))
+            piece = np.zeros(n, dtype=np.float64)
+            comm.scatter(src[root] if rank == root else None, piece, root=root)
+            check(np.array_equal(piece, src[root][rank * n:(rank + 1) * n]), "scatter n=%d root=%d" % (n, root))
+    sc = [(p + rank) % 3 * 5 for p in range(world)]              # what I send to p (some blocks are empty)
+    rc = [(rank + p) % 3 * 5 for p in range(world)]              # what p sends to me
+    sbuf = np.concatenate([np.full(sc[p], 100 * rank + p, dtype=np.int32) for p in range(world)] + [np.zeros(0, np.int32)])
+    rbuf = np.zeros(sum(rc), dtype=np.int32)
+    comm.all_to_all(sbuf, rbuf, send_counts=sc, recv_counts=rc)
+    check(np.array_equal(rbuf, np.concatenate([np.full(rc[p], 100 * p + rank, dtype=np.int32) for p in range(world)] + [np.zeros(0, np.int32)])), "all_to_all with uneven blocks")
     code, msg_ = comm.last_error()
     check(code == 0, "async error " + msg_)
     algo = comm.last_algorithm("allreduce")

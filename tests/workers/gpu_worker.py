@@ -215,6 +215,25 @@ def main():
         check(bool((small == 10.0).all()), "plain send/recv")
     torch.cuda.synchronize()
 
+    # all-to-all, gather, scatter on device buffers: one launch of grouped sends / receives plus the own block
+    if args.suite == "basic":
+        for n_el in [1, 1000, (3 << 20) + 5]:      # the largest is longer than the 4 x 1 MB FIFO of a pair
+            src = [torch.arange(n_el * world, dtype=torch.float32) + 1e6 * r for r in range(world)]
+            mine = src[rank].to(dev)
+            out = torch.zeros(n_el * world, dtype=torch.float32, device=dev)
+            comm.all_to_all(mine, out)
+            torch.cuda.synchronize()
+            want = torch.cat([src[p][rank * n_el:(rank + 1) * n_el] for p in range(world)])
+            check(torch.equal(out.cpu(), want), "all_to_all n=%d" % n_el)
+            for root in sorted({0, world - 1}):
+                got = torch.zeros(n_el * world, dtype=torch.float32, device=dev) if rank == root else None
+                comm.gather(mine[:n_el], got, root=root)
+                piece = torch.zeros(n_el, dtype=torch.float32, device=dev)
+                comm.scatter(mine if rank == root else None, piece, root=root)
+                torch.cuda.synchronize()
+                check(rank != root or torch.equal(got.cpu(), torch.cat([src[p][:n_el] for p in range(world)])), "gather n=%d root=%d" % (n_el, root))
+                check(torch.equal(piece.cpu(), src[root][rank * n_el:(rank + 1) * n_el]), "scatter n=%d root=%d" % (n_el, root))
+
     # CUDA graph replay: refused while the host counts sequence numbers, correct with the device-side counter
     if args.suite == "basic":
         from dccl_b200.comm import DcclError

@@ -69,6 +69,32 @@ def main():
             out = torch.empty(n, dtype=dtype, device=dev)
             dist.reduce_scatter_tensor(out, big[rank])
             check(torch.allclose(out.double(), wantrs, **tol), "reduce_scatter_tensor %s %d" % (dtype, n))
+    # all-to-all, gather, scatter (grouped send / recv underneath)
+    for dtype in (torch.float32, torch.int64):
+        for n in (1, 257, 300001):
+            ins = [tensor_for(200 + r, n * world, dtype, dev) for r in range(world)]
+            out = torch.empty(n * world, dtype=dtype, device=dev)
+            dist.all_to_all_single(out, ins[rank])
+            want = torch.cat([ins[p][rank * n:(rank + 1) * n] for p in range(world)])
+            check(torch.equal(out, want), "all_to_all_single %s %d" % (dtype, n))
+            outs = [torch.empty(n, dtype=dtype, device=dev) for _ in range(world)]
+            dist.all_to_all(outs, list(ins[rank].split(n)))
+            check(torch.equal(torch.cat(outs), want), "all_to_all %s %d" % (dtype, n))
+            for root in {0, world - 1}:
+                lst = [torch.empty(n, dtype=dtype, device=dev) for _ in range(world)] if rank == root else None
+                dist.gather(ins[rank][:n], lst, dst=root)
+                check(rank != root or all(torch.equal(lst[p], ins[p][:n]) for p in range(world)), "gather %s %d root %d" % (dtype, n, root))
+                got = torch.empty(n, dtype=dtype, device=dev)
+                dist.scatter(got, list(ins[root].split(n)) if rank == root else None, src=root)
+                check(torch.equal(got, ins[root][rank * n:(rank + 1) * n]), "scatter %s %d root %d" % (dtype, n, root))
+    # uneven splits: rank r sends (p + 1) rows of 3 to rank p and receives (r + 1) rows from everybody
+    rows_in = sum(p + 1 for p in range(world))
+    src = (torch.arange(rows_in * 3, dtype=torch.float32) + 1000 * rank).reshape(rows_in, 3).to(dev)
+    dst = torch.empty(((rank + 1) * world, 3), dtype=torch.float32, device=dev)
+    dist.all_to_all_single(dst, src, output_split_sizes=[rank + 1] * world, input_split_sizes=[p + 1 for p in range(world)])
+    off = sum(p + 1 for p in range(rank)) * 3
+    want = torch.cat([(torch.arange(off, off + (rank + 1) * 3, dtype=torch.float32) + 1000 * p).reshape(rank + 1, 3) for p in range(world)]).to(dev)
+    check(torch.equal(dst, want), "all_to_all_single with uneven splits")
     # point to point: even ranks send to the next odd rank
     if world >= 2:
         msg = torch.full((5000,), float(rank), device=dev)
