@@ -65,6 +65,18 @@ def test_baseline_config_dccl_cli(build_dir, tmp_path, api):
             assert tags.count(1001001) == 1000 and tags.count(1001100) == 1000
 
 
+@pytest.mark.parametrize("api", ["all_to_all", "gather", "scatter"])
+def test_dccl_cli_composed_collectives(build_dir, tmp_path, api):
+    """The entry points composed of grouped send / recv, 3 host processes, messages longer than a FIFO."""
+    cli = os.path.join(build_dir, "dccl_cli")
+    res = spawn_ranks([cli, "-a", api, "-t", "int64", "-c", str(3 * 200001), "-r", "5", "-w", "1", "-i", "uniform", "--verify", "--root", "2"],
+                      3, cwd=str(tmp_path), timeout=240)
+    for r, p in enumerate(res):
+        assert p.returncode == 0, "rank %d: %s\n%s" % (r, p.stdout[-1500:], p.stderr[-1500:])
+        if api != "gather" or r == 2:
+            assert "verify: ok" in p.stdout, (api, r, p.stdout[-500:])
+
+
 def test_cli_defaults_match_the_original(build_dir, tmp_path):
     cli = os.path.join(build_dir, "dccl_cli")
     p = spawn_ranks([cli, "-a", "all_reduce", "-r", "3"], 1, cwd=str(tmp_path))[0]

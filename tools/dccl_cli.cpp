@@ -28,6 +28,7 @@ using namespace dccl_tools;
 static const char* help_string =
     "\t--api,-a     name of the DCCL api to be tested. This option is mandatory. Full api list:\n"
     "\t             broadcast,send,recv,reduce,all_reduce,reduce_scatter,all_gather\n"
+    "\t             (and, beyond the original: all_to_all,gather,scatter)\n"
     "\t             Please note that\n"
     "\t             - 'send' and 'recv' only work between rank 0 and 1. \n"
     "\t             - only the root (rank 0 unless --root) will 'broadcast', all other node will receive. \n"
@@ -148,7 +149,8 @@ int main(int argc, char** argv) {
         for (const char* c : colls)
             if (dcclSetAlgorithm(comm, c, algo.c_str()) != ncclSuccess) { std::cerr << "unknown algorithm:" << algo << std::endl; ncclCommFinalize(comm); return 1; }
     }
-    if ((api == "reduce_scatter" || api == "all_gather") && data_count % world_size) {
+    const bool composed = api == "all_to_all" || api == "gather" || api == "scatter";
+    if ((api == "reduce_scatter" || api == "all_gather" || composed) && data_count % world_size) {
         std::cerr << "count must be a multiple of the world size (" << world_size << ") for " << api << std::endl;
         ncclCommFinalize(comm);
         return 1;
@@ -190,7 +192,7 @@ int main(int argc, char** argv) {
         std::cerr << "Failed to register sendbuf@" << sendbuf << "to dccl." << std::endl;
         return 1;
     }
-    if (api == "broadcast" || verify) {
+    if (api == "broadcast" || verify || composed) {
         if (dcclRegisterCacheMemory(comm, recvbuf, reg_bytes) != ncclSuccess) {
             std::cerr << "Failed to register recvbuf@" << recvbuf << "to dccl." << std::endl;
             return 1;
@@ -207,6 +209,9 @@ int main(int argc, char** argv) {
             return ncclAllGather(at(sendbuf, my_rank * slot_bytes), verify ? recvbuf : sendbuf, slot_count, data_type, comm, stream);
         if (api == "reduce") return ncclReduce(sendbuf, verify ? recvbuf : sendbuf, data_count, data_type, operation, root, comm, stream);
         if (api == "broadcast") return ncclBroadcast(sendbuf, recvbuf, data_count, data_type, root, comm, stream);
+        if (api == "all_to_all") return dcclAllToAll(sendbuf, recvbuf, slot_count, data_type, comm, stream);
+        if (api == "gather") return dcclGather(at(sendbuf, my_rank * slot_bytes), recvbuf, slot_count, data_type, root, comm, stream);
+        if (api == "scatter") return dcclScatter(sendbuf, recvbuf, slot_count, data_type, root, comm, stream);
         if (api == "send") return my_rank < 2 ? ncclSend(sendbuf, data_count, data_type, 1 - (int)my_rank, comm, stream) : ncclSuccess;
         if (api == "recv") return my_rank < 2 ? ncclRecv(verify ? recvbuf : sendbuf, data_count, data_type, 1 - (int)my_rank, comm, stream) : ncclSuccess;
         return ncclInvalidArgument;
@@ -280,6 +285,9 @@ int main(int argc, char** argv) {
         else if (api == "reduce_scatter") { reference_fold(all, data_count, data_type, operation, want.data()); check_count = slot_count; want_off = my_rank * slot_bytes; }
         else if (api == "all_gather") { for (uint32_t r = 0; r < world_size; r++) memcpy(want.data() + r * slot_bytes, all[r].data() + r * slot_bytes, slot_bytes); check_count = slot_count * world_size; }
         else if (api == "broadcast") { want = all[root]; check_count = data_count; }
+        else if (api == "all_to_all") { for (uint32_t r = 0; r < world_size; r++) memcpy(want.data() + r * slot_bytes, all[r].data() + my_rank * slot_bytes, slot_bytes); check_count = slot_count * world_size; }
+        else if (api == "gather") { for (uint32_t r = 0; r < world_size; r++) memcpy(want.data() + r * slot_bytes, all[r].data() + r * slot_bytes, slot_bytes); check_count = slot_count * world_size; have = (int)my_rank == root; }
+        else if (api == "scatter") { memcpy(want.data(), all[root].data() + my_rank * slot_bytes, slot_bytes); check_count = slot_count; }
         else if (api == "recv") { if (my_rank < 2) want = all[1 - my_rank]; else have = false; check_count = data_count; }
         else have = false;
         if (have) {
@@ -294,7 +302,7 @@ int main(int argc, char** argv) {
     }
 
     if (dcclDeregisterCacheMemory(comm, sendbuf) != ncclSuccess) std::cerr << "Failed to deregister sendbuf@" << sendbuf << "from dccl." << std::endl;
-    if (api == "broadcast" || verify)
+    if (api == "broadcast" || verify || composed)
         if (dcclDeregisterCacheMemory(comm, recvbuf) != ncclSuccess) std::cerr << "Failed to deregister recvbuf@" << recvbuf << "from dccl." << std::endl;
     if (gpu < 0) {
         if (save) { save_mem(recvbuf, bytes, "recvbuf.host.txt"); save_mem(sendbuf, bytes, "sendbuf.host.after.txt"); }
