@@ -61,7 +61,12 @@ endif
 .PHONY: all lib tools clean install
 PREFIX ?= /usr/local
 all: lib tools
+# only the default build directory feeds the Python package: an instrumented library must not replace the real one
+ifeq ($(BUILD),build)
 lib: $(LIB) dccl_b200/lib/libdccl.so
+else
+lib: $(LIB)
+endif
 tools: $(TOOLS)
 
 $(BUILD)/obj/%.o: %.cpp $(wildcard include/dccl/*.hpp) $(wildcard csrc/*/*.hpp)
