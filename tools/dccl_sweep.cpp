@@ -15,6 +15,7 @@
  *   --gpu N|auto  --min BYTES --max BYTES --factor F  --type bfloat16|float32|...
  *   --colls all_reduce,reduce_scatter,all_gather  --impls dccl,nccl
  *   --algo NAME (force a variant of this library)  --symmetric (dcclMemAlloc buffers)
+ *   --register (ordinary cudaMalloc buffers registered with dcclRegisterCacheMemory)
  *   --out FILE (rank 0 writes the rows as JSON)
  */
 #include <dccl/dccl.hpp>
@@ -60,16 +61,16 @@ int main(int argc, char** argv) {
         {"gpu", required_argument, 0, 'g'}, {"min", required_argument, 0, 'm'}, {"max", required_argument, 0, 'M'},
         {"factor", required_argument, 0, 'f'}, {"type", required_argument, 0, 't'}, {"colls", required_argument, 0, 'c'},
         {"impls", required_argument, 0, 'i'}, {"algo", required_argument, 0, 'A'}, {"symmetric", no_argument, 0, 's'},
-        {"out", required_argument, 0, 'o'}, {"op", required_argument, 0, 'O'}, {0, 0, 0, 0}};
+        {"out", required_argument, 0, 'o'}, {"op", required_argument, 0, 'O'}, {"register", no_argument, 0, 'R'}, {0, 0, 0, 0}};
     int gpu = -2;
     size_t minb = 1024, maxb = 1ull << 30, factor = 2;
     dccl::ncclDataType_t dt = dccl::ncclBfloat16;
     dccl::ncclRedOp_t op = dccl::ncclSum;
     std::string colls = "all_reduce,reduce_scatter,all_gather", impls = "dccl,nccl", algo, out;
-    bool symmetric = false;
+    bool symmetric = false, registered = false;
     while (true) {
         int idx = 0;
-        int c = getopt_long(argc, argv, "g:m:M:f:t:c:i:A:so:O:", long_options, &idx);
+        int c = getopt_long(argc, argv, "g:m:M:f:t:c:i:A:so:O:R", long_options, &idx);
         if (c == -1) break;
         switch (c) {
         case 'g': gpu = !strcmp(optarg, "auto") ? -2 : atoi(optarg); break;
@@ -81,6 +82,7 @@ int main(int argc, char** argv) {
         case 'i': impls = optarg; break;
         case 'A': algo = optarg; break;
         case 's': symmetric = true; break;
+        case 'R': registered = true; break;
         case 'o': out = optarg; break;
         case 'O': op = parse_op_name(optarg); break;
         default: break;
@@ -115,6 +117,9 @@ int main(int argc, char** argv) {
         } else {
             symmetric = false;
             if (cudaMalloc((void**)&s_ours, maxb) != cudaSuccess || cudaMalloc((void**)&r_ours, maxb) != cudaSuccess) return 4;
+            // --register: ordinary allocations that every rank maps (cudaIpc), the zero-copy peer variants can use them
+            if (registered && (dccl::dcclRegisterCacheMemory(comm, s_ours, maxb) != dccl::ncclSuccess ||
+                               dccl::dcclRegisterCacheMemory(comm, r_ours, maxb) != dccl::ncclSuccess)) return 2;
         }
         cudaMemset(s_ours, 0, maxb);
         if (!algo.empty())
