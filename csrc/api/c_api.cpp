@@ -26,6 +26,7 @@ int dccl_comm_init_rank(void** comm, int nranks, const void* id128, int rank) {
 }
 int dccl_comm_finalize(void* comm) { GUARD(ncclCommFinalize((ncclComm_t)comm)); }
 int dccl_comm_abort(void* comm) { GUARD(dcclCommAbort((ncclComm_t)comm)); }
+int dccl_comm_shrink(void* comm, void** newcomm) { GUARD(dcclCommShrink((ncclComm_t)comm, (ncclComm_t*)newcomm)); }
 int dccl_world_size(void* comm) { try { return (int)dcclGetWorldSize((ncclComm_t)comm); } catch (...) { return -1; } }
 int dccl_rank(void* comm) { try { return (int)dcclGetMyRank((ncclComm_t)comm); } catch (...) { return -1; } }
 int dccl_last_error(void* comm, int* code, char* msg, size_t len) {

@@ -144,6 +144,23 @@ ncclResult_t dcclCommAbort(ncclComm_t comm) {
     return ncclSuccess;
 }
 
+ncclResult_t dcclCommShrink(ncclComm_t comm, ncclComm_t* newcomm) {
+    VALIDATE_COMM(comm);
+    if (!newcomm) return ncclInvalidArgument;
+    UniqueIdData id;
+    int nr = -1, nw = 0;
+    std::string err;
+    const int timeout = (int)Config::global().get_int("DCCL/init_timeout_ms", 120000);
+    if (!comm->bs.shrink_rendezvous(timeout, &id, &nr, &nw, &err)) {
+        dccl_error("dcclCommShrink: %s", err.c_str());
+        return ncclInvalidUsage;
+    }
+    dccl_info("rank %d of %d continues as rank %d of %d", comm->bs.rank(), comm->bs.world(), nr, nw);
+    dcclComm* c = new (std::nothrow) dcclComm();
+    if (!c) return ncclSystemError;
+    return finish_init(c, id, nr, nw, newcomm);
+}
+
 ncclResult_t dcclGetLastError(ncclComm_t comm, ncclResult_t* async_error, char* msg, size_t msg_len) {
     VALIDATE_COMM(comm);
     ncclResult_t r = ncclSuccess;

@@ -282,6 +282,52 @@ void Bootstrap::set_abort(int failed_rank, ncclResult_t code) {
     if (ctl_->abort.compare_exchange_strong(expect, (uint32_t)(failed_rank + 1))) ctl_->abort_code.store((uint32_t)code);
 }
 
+bool Bootstrap::shrink_rendezvous(int timeout_ms, UniqueIdData* id, int* new_rank, int* new_world, std::string* err) {
+    if (!ctl_ || rank_ < 0) { if (err) *err = "not initialised"; return false; }
+    const int failed = failed_rank();
+    auto member = [&](int r) {
+        if (r == failed) return false;
+        if (ctl_->ranks[r].state.load(std::memory_order_acquire) != 1) return false;
+        const int32_t pid = ctl_->ranks[r].pid.load(std::memory_order_acquire);
+        return pid > 0 && (::kill((pid_t)pid, 0) == 0 || errno == EPERM);
+    };
+    if (!member(rank_)) { if (err) *err = "this rank was reported as failed or has left: it cannot be part of the smaller group"; return false; }
+    int leader = -1;
+    for (int r = 0; r < world_ && leader < 0; r++) if (member(r)) leader = r;
+    CtlShrink& sh = ctl_->shrink;
+    if (leader == rank_) {
+        uint64_t mask = 0;
+        for (int r = 0; r < world_; r++) if (member(r)) mask |= 1ull << r;
+        UniqueIdData nid;
+        std::string e;
+        if (!create_listener("127.0.0.1", 0, &nid, &e)) { if (err) *err = e; return false; }
+        sh.alive_mask = mask;
+        sh.id = nid;
+        shrink_seen_ = sh.generation.load(std::memory_order_relaxed) + 1;
+        sh.generation.store(shrink_seen_, std::memory_order_release);
+    } else {
+        const int64_t deadline = now_ms() + timeout_ms;
+        while (sh.generation.load(std::memory_order_acquire) == shrink_seen_) {
+            if (now_ms() > deadline) { if (err) *err = "rank " + std::to_string(leader) + " did not open the smaller group in time"; return false; }
+            if (!member(leader)) { if (err) *err = "rank " + std::to_string(leader) + " went away while the smaller group was being formed; call again"; return false; }
+            usleep(200);
+        }
+        shrink_seen_ = sh.generation.load(std::memory_order_acquire);
+    }
+    const uint64_t mask = sh.alive_mask;
+    if (!(mask >> rank_ & 1ull)) { if (err) *err = "the leader does not count this rank among the survivors"; return false; }
+    *id = sh.id;
+    int nr = 0, nw = 0;
+    for (int r = 0; r < world_; r++) {
+        if (!(mask >> r & 1ull)) continue;
+        if (r < rank_) nr++;
+        nw++;
+    }
+    *new_rank = nr;
+    *new_world = nw;
+    return true;
+}
+
 void Bootstrap::watchdog_loop() {
     std::vector<uint64_t> last(world_, 0);
     std::vector<int64_t> seen(world_, now_ms());

@@ -51,11 +51,19 @@ struct CtlRank {
     std::atomic<int32_t> state;   // 0 = not joined, 1 = alive, 2 = left cleanly
     char pad[48];
 };
+/** Rendezvous of the group that the survivors of a failure form (dcclCommShrink). */
+struct CtlShrink {
+    std::atomic<uint32_t> generation;  // bumped by the leader after it filled in the fields below
+    uint32_t pad;
+    uint64_t alive_mask;               // ranks of this group that are members of the next one
+    UniqueIdData id;                   // where the next group meets
+};
 struct CtlSegment {
     std::atomic<uint32_t> abort;       // non-zero: somebody failed; value = 1 + failed rank
     std::atomic<uint32_t> abort_code;  // ncclResult_t
     char pad[56];
     CtlRank ranks[kMaxRanks];
+    CtlShrink shrink;
 };
 
 /** One direction of a rank pair: single-producer single-consumer byte FIFO. */
@@ -99,6 +107,13 @@ public:
     /** Called by the watchdog when it flips abort (lets the GPU side mirror the flag). */
     void on_abort(std::function<void(int)> cb) { abort_cb_ = cb; }
     int heartbeat_ms() const { return heartbeat_ms_; }
+    /**
+     * The ranks that are still there agree on a smaller group: the lowest surviving rank opens a new
+     * rendezvous and publishes it, with the list of members, in the control segment; the others read it.
+     * Members are the ranks whose process exists, that joined and did not leave, and that were not the
+     * rank reported as failed. Every member must call this; a rank that is not a member gets false.
+     */
+    bool shrink_rendezvous(int timeout_ms, UniqueIdData* id, int* new_rank, int* new_world, std::string* err);
 
     /* host data plane */
     ShmChannel* channel(int src, int dst);
@@ -126,6 +141,7 @@ private:
     size_t data_bytes_ = 0, chan_bytes_ = 0, chan_stride_ = 0;
     int heartbeat_ms_ = 100, hb_timeout_ms_ = 10000, op_timeout_ms_ = 60000;
     uint64_t ops_ = 0;
+    uint32_t shrink_seen_ = 0;      // generation of the last shrink this rank took part in
     std::string err_;
     std::function<void(int)> abort_cb_;
     struct PendingFd { int src; uint32_t tag; int fd; };

@@ -140,6 +140,18 @@ class Communicator:
     def abort(self):
         _check(lib().dccl_comm_abort(self._h), "dcclCommAbort")
 
+    def shrink(self, device=None):
+        """After a failure: a new communicator over the ranks that are still there (every survivor calls it).
+        This communicator stays usable for last_error() and should still be finalized."""
+        new = Communicator.__new__(Communicator)
+        new._h = ctypes.c_void_p()
+        _check(lib().dccl_comm_shrink(self._h, ctypes.byref(new._h)), "dcclCommShrink")
+        new.rank = lib().dccl_rank(new._h)
+        new.world = lib().dccl_world_size(new._h)
+        if device is not None:
+            new.bind_device(device)
+        return new
+
     def __enter__(self):
         return self
 

@@ -124,6 +124,16 @@ ncclResult_t  ncclCommFinalize(ncclComm_t comm);
 ncclResult_t  dcclCommAbort(ncclComm_t comm);
 
 /**
+ * Continue without the ranks that are gone (no counterpart in the original, which
+ * leaves a failed group to time out). After a communicator has failed, every
+ * surviving rank calls this; it returns a new communicator over the survivors,
+ * ranks renumbered densely in the old order. Members are the ranks whose process
+ * still exists and that were not the rank reported as failed. The old communicator
+ * stays valid for dcclGetLastError and must still be finalized (that does not block).
+ */
+ncclResult_t  dcclCommShrink(ncclComm_t comm, ncclComm_t* newcomm);
+
+/**
  * Report the asynchronous state of the communicator: ncclSuccess, or the error
  * that a kernel or the watchdog recorded (a peer that stopped answering is
  * ncclRemoteError). msg, when not null, receives a one-line description.

@@ -70,3 +70,15 @@ def test_local_abort_unblocks_everybody():
     res = python_ranks(WORKER, ["--mode", "abort_local", "--victim", "0"], 3, timeout=60, env_extra={"DCCL_TIMEOUT_MS": "20000"})
     r = results(res)
     assert all(x.startswith("RESULT error") for x in r), r
+
+
+def test_survivors_shrink_the_group_and_carry_on():
+    """Rank 1 of 4 dies; ranks 0, 2, 3 become ranks 0, 1, 2 of a new group and reduce again. With rank 0 as the
+    victim the lowest survivor leads the new rendezvous instead."""
+    for victim in (1, 0):
+        res = python_ranks(WORKER, ["--mode", "exit_then_shrink", "--victim", str(victim)], 4, timeout=90, env_extra={"DCCL_TIMEOUT_MS": "20000"})
+        r = results(res)
+        assert res[victim].returncode == 9
+        for i in range(4):
+            if i != victim:
+                assert r[i].startswith("RESULT shrunk ok=1 world=3"), (victim, i, r[i], res[i].stderr[-800:])

@@ -26,7 +26,7 @@ def main():
     x = np.ones(1 << 16, dtype=np.float32)
     try:
         for it in range(200):
-            if args.mode == "exit_mid_run" and rank == args.victim and it == 50:
+            if args.mode in ("exit_mid_run", "exit_then_shrink") and rank == args.victim and it == 50:
                 os._exit(9)             # dies without leaving the group
             if args.mode == "abort_local" and rank == args.victim and it == 50:
                 comm.abort()
@@ -38,6 +38,20 @@ def main():
         comm.finalize()
     except DcclError as e:
         code, msg = comm.last_error()
+        if args.mode == "exit_then_shrink":
+            # the survivors go on as a smaller group: dense ranks in the old order, collectives work again
+            new = comm.shrink()
+            y = np.full(1000, float(rank), dtype=np.float64)
+            new.all_reduce(y)
+            alive = [r for r in range(world) if r != args.victim]
+            ok = new.world == world - 1 and new.rank == alive.index(rank) and bool(np.all(y == float(sum(alive))))
+            lst = np.zeros(new.world, dtype=np.int32)
+            new.all_gather(np.array([rank], dtype=np.int32), lst)
+            ok = ok and list(lst) == alive
+            print("RESULT shrunk ok=%d world=%d rank=%d first_error=%d" % (int(ok), new.world, new.rank, e.code))
+            new.finalize()
+            comm.finalize()
+            return
         print("RESULT error code=%d async=%d after=%.1f msg=%s" % (e.code, code, time.time() - t0, msg))
         # a failed group is not finalized collectively; just leave
 
