@@ -149,3 +149,40 @@ def test_oracle_integer_semantics():
     assert list(oracle.fold([a, b], "sum")) == [-56, 56, 5]            # wraps like the kernels
     assert list(oracle.fold([a, b], "prod")) == [16, 16, -14]
     assert list(oracle.fold([np.array([-7], np.int32), np.array([2], np.int32)], "avg")) == [-2]   # truncates toward zero
+
+
+def test_tuning_table_from_measured_sweeps(dccl_lib, tmp_path):
+    """benchmarks/make_tune_table.py: the fastest variant per size becomes a rule the native tuner accepts."""
+    import json
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    rows = []
+    for nbytes, times in [(1024, {"oneshot": 5.0, "twoshot": 12.0}), (65536, {"oneshot": 8.0, "twoshot": 13.0}),
+                          (1 << 20, {"twoshot": 20.0, "nvls": 18.0}), (1 << 26, {"twoshot": 300.0, "nvls": 150.0, "ring": 500.0})]:
+        for algo, us in times.items():
+            for ctas in (16, 64):
+                rows.append({"coll": "allreduce", "algo": algo, "ran": algo, "ctas": ctas, "unroll": 4, "bytes": nbytes,
+                             "us": us + (0.5 if ctas == 16 else 0.0)})
+    rows.append({"coll": "allreduce", "algo": "auto", "ran": "nvls", "ctas": 0, "bytes": 1 << 26, "us": 1.0})        # ignored
+    rows.append({"coll": "allreduce", "algo": "rabenseifner", "ran": "twoshot", "ctas": 64, "bytes": 1024, "us": 1.0})  # fell back: ignored
+    rows.append({"coll": "allreduce", "algo": "nvls_sym", "ran": "nvls", "ctas": 16, "bytes": 1 << 26, "us": 100.0})
+    f1 = tmp_path / "sweep.json"
+    f1.write_text(json.dumps({"n_gpus": 8, "impl": "ours", "rows": rows}))
+    f2 = tmp_path / "ctool.json"
+    f2.write_text(json.dumps({"n_gpus": 8, "symmetric": False, "rows": [
+        {"coll": "reduce_scatter", "impl": "dccl", "bytes": 1 << 20, "us": 30.0, "variant": "twoshot"},
+        {"coll": "reduce_scatter", "impl": "nccl", "bytes": 1 << 20, "us": 1.0, "variant": "nccl"}]}))
+    out = tmp_path / "tune.txt"
+    subprocess.run([sys.executable, os.path.join(root, "benchmarks", "make_tune_table.py"), "--in", str(f1), "--in", str(f2) + ":128",
+                    "--out", str(out)], check=True)
+    text = out.read_text()
+    assert "allreduce 8 65536 oneshot 64" in text and "allreduce 8 inf nvls 64" in text
+    assert "allreduce_sym 8 inf nvls 16" in text and "reducescatter 8 inf twoshot 128" in text
+    assert dccl_lib.dccl_tuner_load_text(text.encode()) == 4
+    algo = ctypes.create_string_buffer(32)
+    ctas = ctypes.c_int()
+    for nbytes, want in [(512, b"oneshot"), (65536, b"oneshot"), (65537, b"nvls"), (1 << 30, b"nvls")]:
+        assert dccl_lib.dccl_tuner_choose(b"allreduce", 8, nbytes, 1, algo, 32, ctypes.byref(ctas)) == 0
+        assert algo.value == want, (nbytes, algo.value)
+    assert dccl_lib.dccl_tuner_choose(b"reducescatter", 8, 1 << 28, 1, algo, 32, ctypes.byref(ctas)) == 0 and (algo.value, ctas.value) == (b"twoshot", 128)
