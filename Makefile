@@ -53,7 +53,7 @@ endif
 HOST_OBJS := $(patsubst %.cpp,$(BUILD)/obj/%.o,$(HOST_SRCS))
 CU_OBJS := $(patsubst %.cu,$(BUILD)/obj/%.cu.o,$(CU_SRCS))
 LIB := $(BUILD)/libdccl.so
-TOOLS := $(BUILD)/dccl_cli $(BUILD)/p2p_perf $(BUILD)/helloworld
+TOOLS := $(BUILD)/dccl_cli $(BUILD)/p2p_perf $(BUILD)/helloworld $(BUILD)/nccl_names
 ifeq ($(CUDA),1)
 TOOLS += $(BUILD)/nccl_cli $(BUILD)/dccl_sweep
 endif
@@ -91,6 +91,9 @@ $(BUILD)/p2p_perf: tools/p2p_perf.cpp tools/tool_common.hpp $(LIB)
 	$(CXX) $(CXXFLAGS) $(TOOL_DEFS) $< -o $@ -L$(BUILD) -ldccl -Wl,-rpath,'$$ORIGIN' $(CUDA_LIBS) $(LDFLAGS)
 
 $(BUILD)/helloworld: examples/helloworld/main.cpp $(LIB)
+	$(CXX) $(CXXFLAGS) $< -o $@ -L$(BUILD) -ldccl -Wl,-rpath,'$$ORIGIN' $(LDFLAGS)
+
+$(BUILD)/nccl_names: examples/nccl_names/main.cpp $(LIB)
 	$(CXX) $(CXXFLAGS) $< -o $@ -L$(BUILD) -ldccl -Wl,-rpath,'$$ORIGIN' $(LDFLAGS)
 
 # comparator: the same workload through stock NCCL (found at run time with dlopen)

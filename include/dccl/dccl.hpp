@@ -240,6 +240,23 @@ const char*   dcclGetLastAlgorithm(ncclComm_t comm, const char* collective);
 
 const char*   dcclGetErrorString(ncclResult_t r);
 
+/* ------------------------------------------------------------------ *
+ * NCCL spellings of the calls above, for code written against NCCL
+ * (the original stops at the names it implements; these are thin inline
+ * aliases and add no behaviour).
+ * ------------------------------------------------------------------ */
+typedef dcclUniqueId ncclUniqueId;
+inline ncclResult_t ncclGetUniqueId(ncclUniqueId* id) { return dcclGetUniqueId(id); }
+inline ncclResult_t ncclCommInitRank(ncclComm_t* comm, int nranks, ncclUniqueId id, int rank) { return dcclCommInitRank(comm, nranks, id, rank); }
+inline ncclResult_t ncclCommDestroy(ncclComm_t comm) { return ncclCommFinalize(comm); }
+inline ncclResult_t ncclCommAbort(ncclComm_t comm) { return dcclCommAbort(comm); }
+inline ncclResult_t ncclCommCount(const ncclComm_t comm, int* count) { if (!count) return ncclInvalidArgument; *count = (int)dcclGetWorldSize(comm); return ncclSuccess; }
+inline ncclResult_t ncclCommUserRank(const ncclComm_t comm, int* rank) { if (!rank) return ncclInvalidArgument; *rank = (int)dcclGetMyRank(comm); return ncclSuccess; }
+inline ncclResult_t ncclCommGetAsyncError(ncclComm_t comm, ncclResult_t* async_error) { return dcclGetLastError(comm, async_error, nullptr, 0); }
+inline const char*  ncclGetErrorString(ncclResult_t r) { return dcclGetErrorString(r); }
+inline ncclResult_t ncclGroupStart() { return dcclGroupStart(); }
+inline ncclResult_t ncclGroupEnd() { return dcclGroupEnd(); }
+
 #define CACHELINE_OFFSET(addr)          ( ((uint64_t)(addr))%CACHELINE_SIZE)
 #define CUDA_L1_CACHELINE_OFFSET(addr)  ( ((uint64_t)(addr))%CUDA_L1_CACHELINE_SIZE)
 #define CUDA_L2_CACHELINE_OFFSET(addr)  ( ((uint64_t)(addr))%CUDA_L2_CACHELINE_SIZE)

@@ -6,6 +6,7 @@ same shapes for reduce-scatter and all-gather) plus every dtype x operator, worl
 powers of two, counts that the world size does not divide, unaligned buffers, both algorithms.
 """
 import os
+import subprocess
 import sys
 
 import pytest
@@ -75,6 +76,12 @@ def test_dccl_cli_composed_collectives(build_dir, tmp_path, api):
         assert p.returncode == 0, "rank %d: %s\n%s" % (r, p.stdout[-1500:], p.stderr[-1500:])
         if api != "gather" or r == 2:
             assert "verify: ok" in p.stdout, (api, r, p.stdout[-500:])
+
+
+def test_nccl_spellings_compile_and_run(build_dir, tmp_path):
+    """examples/nccl_names: the inline NCCL-style aliases of the header (built by make)."""
+    p = subprocess.run([os.path.join(build_dir, "nccl_names")], cwd=str(tmp_path), capture_output=True, text=True, timeout=60)
+    assert p.returncode == 0 and p.stdout.strip() == "1 0 no error 2.0", (p.stdout, p.stderr)
 
 
 def test_cli_defaults_match_the_original(build_dir, tmp_path):
