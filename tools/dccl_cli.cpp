@@ -221,9 +221,16 @@ int main(int argc, char** argv) {
         if (gpu >= 0) cudaStreamSynchronize(stream);
 #endif
     };
+    // per-call wall time (meaningful for host buffers, where a call returns when the data is there;
+    // for device buffers it is the launch cost and the summary line reports the stream time instead)
+    double call_min_us = 1e300, call_max_us = 0.0;
 #define RUN_WITH_COUNTER(cnt) \
     for (size_t i_ = 0; i_ < (cnt); i_++) { \
+        auto c0_ = std::chrono::steady_clock::now(); \
         ret = run_once(); \
+        double d_ = std::chrono::duration<double, std::micro>(std::chrono::steady_clock::now() - c0_).count(); \
+        if (d_ < call_min_us) call_min_us = d_; \
+        if (d_ > call_max_us) call_max_us = d_; \
         if (ret != ncclSuccess) { \
             std::cerr << "API:" << api << " failed with error:" << ret << std::endl; \
             ncclCommFinalize(comm); \
@@ -241,6 +248,7 @@ int main(int argc, char** argv) {
 
     // step 4 - run test
     std::cout << "run test..." << std::endl;
+    call_min_us = 1e300; call_max_us = 0.0;   // forget the warm-up calls
     auto t0 = std::chrono::steady_clock::now();
     TIMESTAMP(TT_TEST_START, my_rank, 0);
     RUN_WITH_COUNTER(repeat_count);
@@ -259,6 +267,8 @@ int main(int argc, char** argv) {
                  dcclGetLastAlgorithm(comm, api == "all_reduce" ? "allreduce" : api == "reduce_scatter" ? "reducescatter"
                                           : api == "all_gather" ? "allgather" : api == "broadcast" ? "broadcast"
                                           : api == "reduce" ? "reduce" : "sendrecv"));
+        std::cout << line << std::endl;
+        snprintf(line, sizeof(line), "%s per call: min %.2f us   max %.2f us", gpu < 0 ? "latency" : "launch cost", call_min_us, call_max_us);
         std::cout << line << std::endl;
     }
     {
