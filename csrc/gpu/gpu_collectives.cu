@@ -35,6 +35,7 @@ bool GpuCommImpl::set_param(const char* name, int value) {
     if (k == "pipe_min_mb" && value >= 0) { pipe_min_bytes_ = (size_t)value << 20; return true; }
     if (k == "pipe_ctas" && value >= 3 && value <= kMaxCtas) { pipe_ctas_ = value; return true; }
     if (k == "device_seq" && (value == 0 || value == 1)) return set_device_seq(value == 1);
+    if (k == "rooted_pipe" && (value == 0 || value == 1)) { rooted_pipe_ = value == 1; return true; }
     return false;
 }
 
@@ -387,7 +388,10 @@ ncclResult_t GpuCommImpl::broadcast(const void* send, void* recv, size_t count, 
         }
     }
     const int ts_mode = ch.algo == ALGO_ONESHOT ? TS_BROADCAST_DIRECT : TS_BROADCAST;
-    size_t cap = ch.algo == ALGO_NVLS ? nvls_capacity(NV_BROADCAST, n_, es, stage_bytes_) : twoshot_capacity(ts_mode, n_, es, stage_bytes_);
+    // large messages through the switch: the receivers' copy-out overlaps the root's push chunk by chunk
+    const bool rooted = ch.algo == ALGO_NVLS && rooted_pipe_ && bytes >= rooted_pipe_min_bytes_;
+    size_t cap = rooted ? nvls_pipe_capacity(es, stage_bytes_, n_, false)
+                 : ch.algo == ALGO_NVLS ? nvls_capacity(NV_BROADCAST, n_, es, stage_bytes_) : twoshot_capacity(ts_mode, n_, es, stage_bytes_);
     for (size_t off = 0; off < count; off += cap) {
         const size_t c = count - off < cap ? count - off : cap;
         a.io.send = (const char*)send + off * es;
@@ -395,7 +399,8 @@ ncclResult_t GpuCommImpl::broadcast(const void* send, void* recv, size_t count, 
         a.count = c;
         NEXT_SEQ(a);
         cudaError_t e;
-        if (ch.algo == ALGO_NVLS) { a.mode = NV_BROADCAST; e = launch_nvls(a, dt, cfg); }
+        if (rooted) { a.mode = ROOTED_BROADCAST; e = launch_nvls_rooted(a, dt, cfg); }
+        else if (ch.algo == ALGO_NVLS) { a.mode = NV_BROADCAST; e = launch_nvls(a, dt, cfg); }
         else { a.mode = ts_mode; e = launch_twoshot(a, dt, cfg); }
         launches_++;
         if (e != cudaSuccess) return cuda_result(e, "broadcast launch");
@@ -437,7 +442,10 @@ ncclResult_t GpuCommImpl::reduce(const void* send, void* recv, size_t count, ncc
         launches_++;
         return cuda_result(launch_ll_collective(a, dt, cfg), "packet reduce");
     }
-    size_t cap = ch.algo == ALGO_NVLS ? nvls_capacity(NV_REDUCE, n_, es, stage_bytes_) : twoshot_capacity(TS_REDUCE, n_, es, stage_bytes_);
+    // large messages through the switch: every rank's copy-in overlaps the root's switch pass chunk by chunk
+    const bool rooted = ch.algo == ALGO_NVLS && rooted_pipe_ && bytes >= rooted_pipe_min_bytes_;
+    size_t cap = rooted ? nvls_pipe_capacity(es, stage_bytes_, n_, false)
+                 : ch.algo == ALGO_NVLS ? nvls_capacity(NV_REDUCE, n_, es, stage_bytes_) : twoshot_capacity(TS_REDUCE, n_, es, stage_bytes_);
     for (size_t off = 0; off < count; off += cap) {
         const size_t c = count - off < cap ? count - off : cap;
         a.io.send = (const char*)send + off * es;
@@ -445,7 +453,8 @@ ncclResult_t GpuCommImpl::reduce(const void* send, void* recv, size_t count, ncc
         a.count = c;
         NEXT_SEQ(a);
         cudaError_t e;
-        if (ch.algo == ALGO_NVLS) { a.mode = NV_REDUCE; e = launch_nvls(a, dt, cfg); }
+        if (rooted) { a.mode = ROOTED_REDUCE; e = launch_nvls_rooted(a, dt, cfg); }
+        else if (ch.algo == ALGO_NVLS) { a.mode = NV_REDUCE; e = launch_nvls(a, dt, cfg); }
         else { a.mode = TS_REDUCE; e = launch_twoshot(a, dt, cfg); }
         launches_++;
         if (e != cudaSuccess) return cuda_result(e, "reduce launch");

@@ -58,6 +58,8 @@ bool GpuCommImpl::init(std::string* err) {
     pipe_min_bytes_ = (size_t)cfg.get_int("DCCL/nvls_pipe_min_bytes", 16ll << 20);
     pipe_ctas_ = (int)cfg.get_int("DCCL/nvls_pipe_ctas", 144);
     device_stamps_ = cfg.get_bool("DCCL/device_stamps", false);
+    rooted_pipe_ = cfg.get_bool("DCCL/nvls_rooted_pipe", false);
+    rooted_pipe_min_bytes_ = (size_t)cfg.get_int("DCCL/nvls_rooted_pipe_min_bytes", 16ll << 20);
     if (p2p_ctas_ < 1) p2p_ctas_ = 1;
     if (p2p_ctas_ > kP2pCtas) p2p_ctas_ = kP2pCtas;
     stage_bytes_ = (size_t)cfg.get_int("DCCL/staging_bytes", 256ll << 20);

@@ -99,6 +99,8 @@ private:
     size_t pipe_min_bytes_ = 16u << 20;   // ordinary-buffer switch all-reduce is pipelined from this size on (0 = never)
     int pipe_ctas_ = 144;
     int unroll_ = 8;
+    bool rooted_pipe_ = false;            // broadcast / reduce of large ordinary buffers: pipelined switch form (nvls_rooted.cu)
+    size_t rooted_pipe_min_bytes_ = 16u << 20;
     bool sticky_error_ = false;
     bool device_stamps_ = false;
     std::vector<SymSegment> user_segs_;

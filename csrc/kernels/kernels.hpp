@@ -48,6 +48,11 @@ cudaError_t launch_nvls(const CollArgs& a, ncclDataType_t dt, const LaunchCfg& c
 size_t nvls_pipe_capacity(size_t elem_size, size_t stage_bytes, int nranks, bool reduce_scatter);
 cudaError_t launch_nvls_pipe(const CollArgs& a, ncclDataType_t dt, const LaunchCfg& cfg, bool reduce_scatter);
 
+/* nvls_rooted.cu: broadcast / reduce of large ordinary buffers through the switch with the local copies overlapped
+ * chunk by chunk (count elements, at most nvls_pipe_capacity(..., false); root in a.root) */
+enum { ROOTED_BROADCAST = 0, ROOTED_REDUCE };
+cudaError_t launch_nvls_rooted(const CollArgs& a, ncclDataType_t dt, const LaunchCfg& cfg);
+
 /* ring.cu / hd.cu: the two algorithms of the original as single kernels */
 enum { RING_ALLREDUCE = 0, RING_REDUCESCATTER, RING_ALLGATHER };
 size_t ring_capacity(int mode, int nranks, size_t elem_size, size_t stage_bytes);

@@ -1,0 +1,176 @@
+/**
+ * Pipelined switch (NVLS) broadcast and reduce for large ORDINARY device buffers.
+ *
+ * The staged forms in nvls.cu run their phases one after the other: broadcast
+ * pushes the whole message through the switch into every rank's staging and
+ * then every rank copies it out; reduce copies everything into staging and then
+ * the root pulls the reduction through the switch. Here the message is cut
+ * into chunks and the local copies of one chunk run while the switch works on
+ * the next, in ONE launch:
+ *
+ *   broadcast  root CTA g:   multimem.st chunk k (its sub-range) to all ranks, signal row g of every rank
+ *              other ranks:  CTA g waits for the root's signal k, copies chunk k from staging to the user buffer
+ *   reduce     every rank, CTA g (first half of the grid): copy chunk k into staging, signal row g of the root
+ *              root, CTA G+g (second half):                wait for signal k of every rank,
+ *                                                          multimem.ld_reduce chunk k into the user buffer
+ *
+ * The whole message sits in one staging half, so no byte of it is reused within
+ * a launch and the hand-over needs no back pressure. The side that waits for
+ * nobody during the pipeline (the root of a broadcast, the non-roots of a
+ * reduce) waits at the end for the others, so that a later call cannot reach
+ * the same staging half while it is still being read.
+ *
+ * The original's broadcast is a Derecho multicast into host memory followed by
+ * a memcpy, and its reduce a gather of slots to the root (reference
+ * src/core/dccl.cpp:701-736, 745-846); neither takes device buffers.
+ */
+#include "kernels.hpp"
+#include "../device/geometry.cuh"
+#include "../device/multimem.cuh"
+
+namespace dccl {
+
+constexpr int kRootedMaxChunks = 24;
+constexpr int kRootedDone = 31;        // flag index of the trailing hand-shake
+static_assert(kRootedMaxChunks < kRootedDone && kRootedDone < kFlagVals, "chunk numbers and the trailing index share the per-call flag values");
+
+template <typename T, int OP>
+__device__ __forceinline__ void nvls_rooted_body(const CollArgs& a, const Ctx& x) {
+    constexpr size_t ES = sizeof(T);
+    constexpr size_t VE = 16 / ES;
+    const DevComm& c = *x.c;
+    const int n = c.nranks, r = c.rank, root = a.root;
+    const bool reduce = a.mode == ROOTED_REDUCE;
+    const int nchunks = (int)a.stride;
+    const T* send = reinterpret_cast<const T*>(x.io->send);
+    T* recv = reinterpret_cast<T*>(x.io->recv);
+    const bool avg = a.op == (int)ncclAvg;
+    const size_t stage_off = kStageOff + (size_t)x.parity * c.stage_bytes;
+    T* my_stage = reinterpret_cast<T*>(c.pool[r] + stage_off);
+    char* mc_stage = c.mc_pool + stage_off;
+    const size_t chunk = ((a.count + nchunks - 1) / nchunks + VE - 1) / VE * VE;
+    auto vecs = [&](size_t elems) { return (elems * ES + 15) / 16; };
+    __shared__ int s_fail;
+
+    // reduce: the first half of the grid copies in (every rank), the second half is the root's switch pass
+    const int G = reduce ? x.nb / 2 : x.nb;
+    const bool second = reduce && x.bid >= G;
+    const int g = second ? x.bid - G : x.bid;
+    if (reduce && (x.bid >= 2 * G || (second && r != root))) return;
+
+    for (int k = 0; k < nchunks; k++) {
+        const size_t base = (size_t)k * chunk;
+        const size_t cnt = base >= a.count ? 0 : (a.count - base < chunk ? a.count - base : chunk);
+        const Geometry<T> geo(GEO_WHOLE, cnt, 1, g, G);
+        const size_t lo = geo.blo < cnt ? geo.blo : cnt, hi = geo.bhi < cnt ? geo.bhi : cnt;
+        const size_t off = base + lo;
+        if (!reduce) {
+            if (r == root) {
+                if (hi > lo) {
+                    const T* src = send + off;
+                    if (aligned16(src)) nvls_push(mc_stage + off * ES, reinterpret_cast<const char*>(src), vecs(hi - lo));
+                    else {   // multimem.st wants whole aligned vectors: go through the own staging copy
+                        copy_range<T>(my_stage + off, src, hi - lo);
+                        __syncthreads();
+                        nvls_push(mc_stage + off * ES, reinterpret_cast<const char*>(my_stage + off), vecs(hi - lo));
+                    }
+                    if (recv != send) copy_range<T>(recv + off, src, hi - lo);
+                }
+                __syncthreads();
+                if ((int)threadIdx.x < n) signal_peer(c, (int)threadIdx.x, g, x.seq, k);
+            } else {
+                if (!cta_wait_peer(c, root, g, x.seq, k, 580)) return;
+                if (hi > lo) copy_range<T>(recv + off, my_stage + off, hi - lo);
+            }
+        } else if (!second) {
+            if (hi > lo) copy_range<T>(my_stage + off, send + off, hi - lo);
+            cta_signal_peer(c, root, g, x.seq, k);
+        } else {
+            if (threadIdx.x == 0) s_fail = 0;
+            __syncthreads();
+            if ((int)threadIdx.x < n && !wait_peer(c, (int)threadIdx.x, g, x.seq, k, 590)) s_fail = 1;
+            __syncthreads();
+            if (s_fail) return;
+            if (hi > lo) {
+                char* dst = reinterpret_cast<char*>(recv + off);
+                if (aligned16(dst)) nvls_pass<T, OP>(mc_stage + off * ES, nullptr, dst, vecs(hi - lo), (hi - lo) * ES, avg, n, a.unroll);
+                else {   // unaligned output: reduce into the own staging copy (each vector is read once, then replaced), then copy
+                    nvls_pass<T, OP>(mc_stage + off * ES, nullptr, reinterpret_cast<char*>(my_stage + off), vecs(hi - lo), vecs(hi - lo) * 16, avg, n, a.unroll);
+                    __syncthreads();
+                    copy_range<T>(recv + off, my_stage + off, hi - lo);
+                }
+            }
+            __syncthreads();
+        }
+    }
+
+    // trailing hand-shake: whoever waited for nobody so far waits for the others now
+    if (!reduce) {
+        if (r != root) cta_signal_peer(c, root, g, x.seq, kRootedDone);
+        else if ((int)threadIdx.x < n && (int)threadIdx.x != root) wait_peer(c, (int)threadIdx.x, g, x.seq, kRootedDone, 585);
+    } else if (second) {
+        __syncthreads();
+        if ((int)threadIdx.x < n && (int)threadIdx.x != root) signal_peer(c, (int)threadIdx.x, g, x.seq, kRootedDone);
+    } else if (r != root) {
+        if (threadIdx.x == 0) wait_peer(c, root, g, x.seq, kRootedDone, 595);
+    }
+}
+
+template <typename T, int OP>
+__global__ void __launch_bounds__(512) k_nvls_rooted(const __grid_constant__ CollArgs a) {
+    const Ctx x = make_ctx(a);
+    nvls_rooted_body<T, OP>(a, x);
+    finish_call(x);
+}
+
+int nvls_rooted_chunks(size_t bytes) {
+    size_t k = (bytes + (8u << 20) - 1) / (8u << 20);
+    if (k < 2) k = 2;
+    if (k > (size_t)kRootedMaxChunks) k = kRootedMaxChunks;
+    return (int)k;
+}
+
+cudaError_t launch_nvls_rooted(const CollArgs& a_in, ncclDataType_t dt, const LaunchCfg& cfg_in) {
+    CollArgs a = a_in;
+    LaunchCfg cfg = cfg_in;
+    const size_t es = dt == ncclInt8 || dt == ncclUint8 ? 1 : dt == ncclFloat16 || dt == ncclBfloat16 ? 2
+                      : dt == ncclInt32 || dt == ncclUint32 || dt == ncclFloat32 ? 4 : 8;
+    if (a.mode == ROOTED_REDUCE) {
+        cfg.ctas = cfg.ctas / 2 * 2;                 // copy-in half and switch half
+        if (cfg.ctas < 2) cfg.ctas = 2;
+    }
+    if (a.mode == ROOTED_BROADCAST) {
+        // pure data movement: run on bytes
+        a.count = a.count * es;
+        a.stride = (size_t)nvls_rooted_chunks(a.count);
+        return launch_coll(k_nvls_rooted<uint8_t, OP_SUM>, a, cfg);
+    }
+    a.stride = (size_t)nvls_rooted_chunks(a.count * es);
+    const int op = a.op == (int)ncclAvg ? (int)ncclSum : a.op;
+    switch (dt) {
+#define ROOTED_CASE(DT, T)                                                                    \
+    case DT:                                                                                  \
+        if (op == (int)ncclSum) return launch_coll(k_nvls_rooted<T, OP_SUM>, a, cfg);         \
+        if (op == (int)ncclMax) return launch_coll(k_nvls_rooted<T, OP_MAX>, a, cfg);         \
+        if (op == (int)ncclMin) return launch_coll(k_nvls_rooted<T, OP_MIN>, a, cfg);         \
+        break;
+#define ROOTED_CASE_SUM(DT, T)                                                                \
+    case DT:                                                                                  \
+        if (op == (int)ncclSum) return launch_coll(k_nvls_rooted<T, OP_SUM>, a, cfg);         \
+        break;
+    ROOTED_CASE_SUM(ncclFloat32, float)
+    ROOTED_CASE_SUM(ncclFloat64, double)
+    ROOTED_CASE(ncclFloat16, __half)
+    ROOTED_CASE(ncclBfloat16, __nv_bfloat16)
+    ROOTED_CASE(ncclInt32, int32_t)
+    ROOTED_CASE(ncclUint32, uint32_t)
+    ROOTED_CASE(ncclInt64, long long)
+    ROOTED_CASE(ncclUint64, unsigned long long)
+#undef ROOTED_CASE
+#undef ROOTED_CASE_SUM
+    default: break;
+    }
+    return cudaErrorInvalidValue;
+}
+
+} // namespace dccl

@@ -53,6 +53,45 @@ def main():
         if not ok:
             failures.append(what)
 
+    if args.suite == "rooted":
+        # broadcast / reduce of large ordinary buffers with the pipelined switch form switched on
+        if not comm.has_multicast:
+            comm.finalize()
+            print("OK 0 multicast=0 launches=0")
+            return
+        comm.set_param("rooted_pipe", 1)
+        for name, count in [("float32", (8 << 20) + 3), ("bfloat16", 16 << 20), ("int32", (5 << 20) + 1)]:
+            ins = [oracle.make_input(name, count, seed=500 + r) for r in range(world)]
+            for root in sorted({0, world - 1}):
+                for shift in (0, 1):       # 1: buffers that do not start on a 16-byte boundary
+                    base = torch.zeros(count + 8, dtype=TORCH[name], device=dev)
+                    b = base[shift:shift + count]
+                    for _ in range(3):
+                        b.copy_(to_torch(ins[rank], name, dev))
+                        comm.broadcast(b, root=root)
+                    torch.cuda.synchronize()
+                    check(comm.last_algorithm("broadcast") == "nvls", "broadcast ran %s" % comm.last_algorithm("broadcast"))
+                    check(np.array_equal(to_numpy(b.contiguous(), name), ins[root]), "pipelined broadcast %s root=%d shift=%d" % (name, root, shift))
+                    if shift:
+                        continue
+                    for op in ["sum", "avg", "max"]:
+                        s = to_torch(ins[rank], name, dev)
+                        out = torch.zeros_like(s)
+                        for _ in range(2):
+                            comm.reduce(s, out, op=op, root=root)
+                        torch.cuda.synchronize()
+                        want = oracle.fold(ins, op, bf16=name == "bfloat16")
+                        check(rank != root or close(to_numpy(out, name), want, name, world), "pipelined reduce %s %s root=%d" % (name, op, root))
+        code, emsg = comm.last_error()
+        check(code == 0, "async error: " + emsg)
+        launches = comm.launches
+        comm.finalize()
+        if failures:
+            print("FAILED %d of %d on rank %d: %s" % (len(failures), cases, rank, "; ".join(failures[:10])))
+            sys.exit(1)
+        print("OK %d multicast=1 launches=%d" % (cases, launches))
+        return
+
     algos = ["oneshot", "twoshot", "ring", "rabenseifner"] + (["nvls"] if comm.has_multicast else [])
     if args.suite == "basic":
         names, counts = ["float32", "bfloat16", "int32", "float16"], [1, 1000, 16384, 300001, 4 << 20]
