@@ -53,3 +53,32 @@ def python_ranks(module_or_script, args, world, **kw):
     else:
         argv = [sys.executable, "-m", module_or_script] + list(args)
     return spawn_ranks(argv, world, **kw)
+
+
+def main(argv=None):
+    """``python -m dccl_b200.utils.launch -n 4 [--gpus] program [args...]``: one process per rank on this machine,
+    output of every rank printed in rank order, exit code 0 only if every rank returned 0."""
+    import argparse
+    ap = argparse.ArgumentParser(prog="python -m dccl_b200.utils.launch")
+    ap.add_argument("-n", "--ranks", type=int, default=2)
+    ap.add_argument("--gpus", action="store_true", help="rank r drives GPU r (DCCL_LOCAL_DEVICE)")
+    ap.add_argument("--timeout", type=int, default=600)
+    ap.add_argument("program", nargs=argparse.REMAINDER)
+    args = ap.parse_args(argv)
+    prog = args.program[1:] if args.program[:1] == ["--"] else args.program
+    if not prog:
+        ap.error("no program given")
+    if prog[0].endswith(".py"):
+        prog = [sys.executable] + prog
+    res = spawn_ranks(prog, args.ranks, timeout=args.timeout, gpus=args.gpus)
+    worst = 0
+    for r, p in enumerate(res):
+        sys.stdout.write("".join("[%d] %s\n" % (r, ln) for ln in p.stdout.splitlines()))
+        sys.stderr.write("".join("[%d] %s\n" % (r, ln) for ln in p.stderr.splitlines()))
+        if p.returncode != 0:
+            worst = p.returncode or 1
+    return worst
+
+
+if __name__ == "__main__":
+    sys.exit(main())
