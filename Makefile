@@ -106,7 +106,7 @@ $(BUILD)/dccl_sweep: tools/dccl_sweep.cpp tools/tool_common.hpp $(LIB)
 # headers, library, tools and a CMake package file (find_package(dccl))
 install: all
 	install -d $(PREFIX)/include/dccl $(PREFIX)/lib $(PREFIX)/bin $(PREFIX)/lib/cmake/dccl
-	install -m 644 include/dccl/dccl.hpp $(PREFIX)/include/dccl/
+	install -m 644 include/dccl/dccl.hpp include/dccl/config.h $(PREFIX)/include/dccl/
 	install -m 755 $(LIB) $(PREFIX)/lib/
 	install -m 755 $(TOOLS) $(PREFIX)/bin/
 	sed 's/@CACHELINE@/$(CACHELINE)/' dcclConfig.cmake.in > $(PREFIX)/lib/cmake/dccl/dcclConfig.cmake
