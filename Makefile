@@ -53,7 +53,7 @@ endif
 HOST_OBJS := $(patsubst %.cpp,$(BUILD)/obj/%.o,$(HOST_SRCS))
 CU_OBJS := $(patsubst %.cu,$(BUILD)/obj/%.cu.o,$(CU_SRCS))
 LIB := $(BUILD)/libdccl.so
-TOOLS := $(BUILD)/dccl_cli $(BUILD)/p2p_perf $(BUILD)/helloworld $(BUILD)/nccl_names
+TOOLS := $(BUILD)/dccl_cli $(BUILD)/p2p_perf $(BUILD)/helloworld $(BUILD)/nccl_names $(BUILD)/c_api_example
 ifeq ($(CUDA),1)
 TOOLS += $(BUILD)/nccl_cli $(BUILD)/dccl_sweep
 endif
@@ -96,6 +96,9 @@ $(BUILD)/helloworld: examples/helloworld/main.cpp $(LIB)
 $(BUILD)/nccl_names: examples/nccl_names/main.cpp $(LIB)
 	$(CXX) $(CXXFLAGS) $< -o $@ -L$(BUILD) -ldccl -Wl,-rpath,'$$ORIGIN' $(LDFLAGS)
 
+$(BUILD)/c_api_example: examples/c_api/main.c include/dccl/dccl_c.h $(LIB)
+	$(CC) -O2 -Wall -Iinclude $< -o $@ -L$(BUILD) -ldccl -Wl,-rpath,'$$ORIGIN' $(LDFLAGS)
+
 # comparator: the same workload through stock NCCL (found at run time with dlopen)
 $(BUILD)/nccl_cli: tools/nccl_cli.cpp tools/tool_common.hpp $(LIB)
 	$(CXX) $(CXXFLAGS) $(TOOL_DEFS) $< -o $@ -L$(BUILD) -ldccl -Wl,-rpath,'$$ORIGIN' $(CUDA_LIBS) $(LDFLAGS)
@@ -106,7 +109,7 @@ $(BUILD)/dccl_sweep: tools/dccl_sweep.cpp tools/tool_common.hpp $(LIB)
 # headers, library, tools and a CMake package file (find_package(dccl))
 install: all
 	install -d $(PREFIX)/include/dccl $(PREFIX)/lib $(PREFIX)/bin $(PREFIX)/lib/cmake/dccl
-	install -m 644 include/dccl/dccl.hpp include/dccl/config.h $(PREFIX)/include/dccl/
+	install -m 644 include/dccl/dccl.hpp include/dccl/dccl_c.h include/dccl/config.h $(PREFIX)/include/dccl/
 	install -m 755 $(LIB) $(PREFIX)/lib/
 	install -m 755 $(TOOLS) $(PREFIX)/bin/
 	sed 's/@CACHELINE@/$(CACHELINE)/' dcclConfig.cmake.in > $(PREFIX)/lib/cmake/dccl/dcclConfig.cmake

@@ -84,6 +84,12 @@ def test_nccl_spellings_compile_and_run(build_dir, tmp_path):
     assert p.returncode == 0 and p.stdout.strip() == "1 0 no error 2.0", (p.stdout, p.stderr)
 
 
+def test_flat_c_interface_from_plain_c(build_dir, tmp_path):
+    """examples/c_api/main.c compiled as C against include/dccl/dccl_c.h (built by make)."""
+    p = subprocess.run([os.path.join(build_dir, "c_api_example")], cwd=str(tmp_path), capture_output=True, text=True, timeout=60)
+    assert p.returncode == 0 and p.stdout.strip() == "rank 0 of 1: 1 2 3 4 (no error)", (p.stdout, p.stderr)
+
+
 def test_cli_defaults_match_the_original(build_dir, tmp_path):
     cli = os.path.join(build_dir, "dccl_cli")
     p = spawn_ranks([cli, "-a", "all_reduce", "-r", "3"], 1, cwd=str(tmp_path))[0]
