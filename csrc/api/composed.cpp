@@ -38,8 +38,10 @@ struct GroupScope {
 
 } // namespace
 
-ncclResult_t dcclAllToAllv(const void* sendbuff, const size_t* sendcounts, const size_t* sdispls, void* recvbuff,
-                           const size_t* recvcounts, const size_t* rdispls, ncclDataType_t dt, ncclComm_t comm, cudaStream_t stream) {
+/** `uniform`: every rank is known to record the same operations (equal, non-empty blocks everywhere). */
+static ncclResult_t all_to_all_impl(const void* sendbuff, const size_t* sendcounts, const size_t* sdispls, void* recvbuff,
+                                    const size_t* recvcounts, const size_t* rdispls, ncclDataType_t dt, ncclComm_t comm, cudaStream_t stream,
+                                    bool uniform) {
     if (!comm) return ncclInvalidArgument;
     const int rank = comm->bs.rank(), n = comm->bs.world();
     const size_t es = size_of_type(dt);
@@ -63,6 +65,9 @@ ncclResult_t dcclAllToAllv(const void* sendbuff, const size_t* sendcounts, const
             const int p = (rank + k) % n;
             if (sendcounts[p]) res = ncclSend(s + sdispls[p] * es, sendcounts[p], dt, p, comm, stream);
         }
+        // every rank records the same 2 (n - 1) operations: the launch may shrink its CTA groups so that all of them
+        // are resident together (with per-peer counts a rank cannot know what the others record, so it does not)
+        if (comm->gpu && uniform && n > 1) comm->gpu->group_same_shape(2 * (n - 1));
         ncclResult_t e = g.end();
         if (res == ncclSuccess) res = e;
     }
@@ -70,12 +75,17 @@ ncclResult_t dcclAllToAllv(const void* sendbuff, const size_t* sendcounts, const
     return res;
 }
 
+ncclResult_t dcclAllToAllv(const void* sendbuff, const size_t* sendcounts, const size_t* sdispls, void* recvbuff,
+                           const size_t* recvcounts, const size_t* rdispls, ncclDataType_t dt, ncclComm_t comm, cudaStream_t stream) {
+    return all_to_all_impl(sendbuff, sendcounts, sdispls, recvbuff, recvcounts, rdispls, dt, comm, stream, false);
+}
+
 ncclResult_t dcclAllToAll(const void* sendbuff, void* recvbuff, size_t count, ncclDataType_t dt, ncclComm_t comm, cudaStream_t stream) {
     if (!comm) return ncclInvalidArgument;
     const int n = comm->bs.world();
     std::vector<size_t> counts((size_t)n, count), displs((size_t)n);
     for (int p = 0; p < n; p++) displs[(size_t)p] = (size_t)p * count;
-    return dcclAllToAllv(sendbuff, counts.data(), displs.data(), recvbuff, counts.data(), displs.data(), dt, comm, stream);
+    return all_to_all_impl(sendbuff, counts.data(), displs.data(), recvbuff, counts.data(), displs.data(), dt, comm, stream, count > 0);
 }
 
 ncclResult_t dcclGather(const void* sendbuff, void* recvbuff, size_t count, ncclDataType_t dt, int root, ncclComm_t comm, cudaStream_t stream) {

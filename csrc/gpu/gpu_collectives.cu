@@ -464,7 +464,8 @@ ncclResult_t GpuCommImpl::reduce(const void* send, void* recv, size_t count, ncc
 
 /* ---------------- point to point ---------------- */
 
-ncclResult_t GpuCommImpl::p2p_launch(std::vector<P2pOp>& ops, cudaStream_t stream) {
+ncclResult_t GpuCommImpl::p2p_launch(std::vector<P2pOp>& ops, cudaStream_t stream, int ctas_per_op) {
+    if (ctas_per_op <= 0) ctas_per_op = p2p_ctas_;
     DeviceGuard g(dev_);
     // Receivers get the lower block numbers: they never wait for anything but data, so once they are resident
     // every sender that waits for FIFO credit is waiting for a CTA that runs, however many CTAs the launch has.
@@ -473,11 +474,11 @@ ncclResult_t GpuCommImpl::p2p_launch(std::vector<P2pOp>& ops, cudaStream_t strea
         P2pArgs a;
         memset(&a, 0, sizeof(a));
         a.comm = dc_;
-        a.ctas_per_op = p2p_ctas_;
+        a.ctas_per_op = ctas_per_op;
         a.nops = (int)(ops.size() - first < (size_t)kMaxP2pOps ? ops.size() - first : (size_t)kMaxP2pOps);
         for (int i = 0; i < a.nops; i++) a.ops[i] = ops[first + i];
         LaunchCfg cfg;
-        cfg.ctas = a.nops * p2p_ctas_;
+        cfg.ctas = a.nops * ctas_per_op;
         cfg.stream = stream;
         cfg.threads = threads_;
         a.ctas_per_rank = cfg.ctas;
@@ -518,10 +519,12 @@ ncclResult_t GpuCommImpl::recv(void* buf, size_t bytes, int peer, cudaStream_t s
 
 ncclResult_t GpuCommImpl::group_end() {
     in_group_ = false;
+    const int per_op = group_ctas_;
+    group_ctas_ = 0;
     if (group_ops_.empty()) return ncclSuccess;
     std::vector<P2pOp> ops;
     ops.swap(group_ops_);
-    return p2p_launch(ops, group_stream_);
+    return p2p_launch(ops, group_stream_, per_op);
 }
 
 } // namespace dccl

@@ -51,6 +51,12 @@ public:
     virtual ncclResult_t recv(void* buf, size_t bytes, int peer, cudaStream_t stream) = 0;
     virtual void group_start() = 0;
     virtual ncclResult_t group_end() = 0;
+    /**
+     * The group being recorded has the same `nops` operations on every rank (an all-to-all): its launch may use
+     * fewer CTAs per operation so that all of them fit the GPU at once. Only valid when every rank says the same,
+     * because both ends of a transfer must split it over the same number of CTAs. Forgotten at the next group end.
+     */
+    virtual void group_same_shape(int nops) = 0;
     /** dst = src on this device, stream ordered (the own block of all-to-all / gather / scatter). */
     virtual ncclResult_t local_copy(void* dst, const void* src, size_t bytes, cudaStream_t stream) = 0;
 

@@ -33,6 +33,12 @@ public:
     ncclResult_t recv(void* buf, size_t bytes, int peer, cudaStream_t stream) override;
     void group_start() override { in_group_ = true; }
     ncclResult_t group_end() override;
+    void group_same_shape(int nops) override {
+        int per = nops > 0 ? sm_count_ / nops : p2p_ctas_;
+        if (per > p2p_ctas_) per = p2p_ctas_;
+        if (per < 1) per = 1;
+        group_ctas_ = per;
+    }
     ncclResult_t local_copy(void* dst, const void* src, size_t bytes, cudaStream_t stream) override {
         DeviceGuard g(dev_);
         launches_++;
@@ -70,7 +76,7 @@ private:
     bool set_device_seq(bool on);
     /** Refuse what a capturing stream cannot replay correctly. */
     ncclResult_t capture_check(cudaStream_t stream, bool p2p);
-    ncclResult_t p2p_launch(std::vector<P2pOp>& ops, cudaStream_t stream);
+    ncclResult_t p2p_launch(std::vector<P2pOp>& ops, cudaStream_t stream, int ctas_per_op = 0);
     /** With DCCL/device_stamps on: log a timestamp when `stream` reaches this point (kernel begin / end on the device time line). */
     void stamp(cudaStream_t stream, uint64_t tag, uint64_t extra);
 public:
@@ -110,6 +116,7 @@ private:
     bool in_group_ = false;
     std::vector<P2pOp> group_ops_;
     cudaStream_t group_stream_ = nullptr;
+    int group_ctas_ = 0;               // CTAs per operation of the group being recorded (0: p2p_ctas_)
 };
 
 } // namespace dccl
