@@ -67,6 +67,25 @@ def fold(inputs, op, bf16=False):
     return acc.astype(inputs[0].dtype)
 
 
+def ring_fold_sum(inputs, align=1):
+    """fp32 / fp64 sum in the order the ring algorithm adds: the vector is cut into world slots of ceil(count / world)
+    elements (rounded up to `align` elements: 1 on the host, one 16-byte vector in the device kernels); slot j starts
+    at rank j and picks up ranks j+1, j+2, ... one by one. Bit-exact reference for the ring all-reduce
+    (floating-point addition is commutative but not associative)."""
+    n = len(inputs)
+    count = inputs[0].size
+    per = -(-count // n)
+    per = -(-per // align) * align
+    out = np.empty_like(inputs[0])
+    for j in range(n):
+        lo, hi = min(per * j, count), min(per * (j + 1), count)
+        acc = inputs[j][lo:hi].copy()
+        for k in range(1, n):
+            acc = acc + inputs[(j + k) % n][lo:hi]
+        out[lo:hi] = acc
+    return out
+
+
 def tolerances(dtype_name, world):
     """(rtol, atol) the tests use when comparing a kernel with the fold above."""
     return {

@@ -107,6 +107,9 @@ def main():
                     r = unaligned(np.zeros_like(pins[rank]), 3)
                     rc = raw.all_reduce(s, r, name, op)
                     check(rc == 0 and close(r, want, name, world), "all_reduce %s %s n=%d rc=%d" % (name, op, count, rc))
+                    if args.algo == "ring" and op == "sum" and name in ("float32", "float64"):
+                        # same additions in the same order as the ring: the bits must match, on every rank
+                        check(np.array_equal(r, oracle.ring_fold_sum(pins)), "all_reduce %s ring order n=%d" % (name, count))
                 # in place
                 s = pins[rank].copy()
                 rc = raw.all_reduce(s, s, name, op)
