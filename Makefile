@@ -2,7 +2,8 @@
 #
 #   make                 library + tools for B200 (sm_100a), CUDA enabled
 #   make CUDA=0          host-only library (no nvcc needed; device calls are refused)
-#   make SANITIZE=address|thread|undefined   instrument the host code (host-only build)
+#   make SANITIZE=address|thread|undefined CXX=/usr/bin/g++ CC=/usr/bin/gcc   instrument the host code (host-only build;
+#                        a compiler wrapper that links statically may lack the sanitizer runtimes)
 #   make install PREFIX=/opt/dccl         headers, library, tools, CMake package file
 #
 # Everything lands in build/; the shared library is also copied into the Python
