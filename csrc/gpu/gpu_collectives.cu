@@ -467,15 +467,17 @@ ncclResult_t GpuCommImpl::reduce(const void* send, void* recv, size_t count, ncc
 ncclResult_t GpuCommImpl::p2p_launch(std::vector<P2pOp>& ops, cudaStream_t stream, int ctas_per_op) {
     if (ctas_per_op <= 0) ctas_per_op = p2p_ctas_;
     DeviceGuard g(dev_);
-    // Receivers get the lower block numbers: they never wait for anything but data, so once they are resident
-    // every sender that waits for FIFO credit is waiting for a CTA that runs, however many CTAs the launch has.
-    std::stable_partition(ops.begin(), ops.end(), [](const P2pOp& o) { return o.is_send == 0; });
     for (size_t first = 0; first < ops.size(); first += kMaxP2pOps) {
         P2pArgs a;
         memset(&a, 0, sizeof(a));
         a.comm = dc_;
         a.ctas_per_op = ctas_per_op;
         a.nops = (int)(ops.size() - first < (size_t)kMaxP2pOps ? ops.size() - first : (size_t)kMaxP2pOps);
+        // Within one launch the receivers get the lower block numbers: they never wait for anything but data, so once
+        // they are resident every sender that waits for FIFO credit waits for a CTA that runs, however many CTAs the
+        // launch has. Batches keep the recording order, so that both ends of a transfer land in the same batch when
+        // the ranks record their operations in matching order.
+        std::stable_partition(ops.begin() + (long)first, ops.begin() + (long)first + a.nops, [](const P2pOp& o) { return o.is_send == 0; });
         for (int i = 0; i < a.nops; i++) a.ops[i] = ops[first + i];
         LaunchCfg cfg;
         cfg.ctas = a.nops * ctas_per_op;
