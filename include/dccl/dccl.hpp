@@ -200,7 +200,10 @@ ncclResult_t ncclRecv(void* recvbuff, size_t count, ncclDataType_t datatype, int
 /**
  * Group several ncclSend / ncclRecv calls into one launch. Between Start and
  * End the calls are only recorded; End issues them together, so a ring in
- * which every rank sends before it receives cannot deadlock.
+ * which every rank sends before it receives cannot deadlock. On the device up
+ * to 16 operations share one launch; a longer group runs as consecutive
+ * launches of 16 in recording order, so the two ends of a transfer must fall
+ * into the same batch (they do when all ranks record in matching order).
  */
 ncclResult_t  dcclGroupStart();
 ncclResult_t  dcclGroupEnd();
