@@ -72,7 +72,9 @@ private:
     bool sym_view(const void* p, size_t bytes, const char** peers, const char** mc) const;
     int ctas_for(int tuned) const;
     /** Move the sequence number to the device counter (calls become replayable from a CUDA graph) or back to
-     *  the host. Every rank must switch at the same point of its call order. Waits for the device to go idle. */
+     *  the host. Every rank must switch at the same point of its call order. Waits for the device to go idle.
+     *  Graphs captured in device mode must not be replayed after switching back: they would go on from the device
+     *  word while eager calls have moved the host's number. */
     bool set_device_seq(bool on);
     /** Refuse what a capturing stream cannot replay correctly. */
     ncclResult_t capture_check(cudaStream_t stream, bool p2p);
