@@ -78,6 +78,7 @@ def main():
         # capture both chains
         side = torch.cuda.Stream(device=dev)
         comm.set_param("device_seq", 1)
+        row["ours_eager_devseq_us"] = timed(ours_batch) * 1e3 / args.chain   # what the device-side counter costs per call
         g_ours = torch.cuda.CUDAGraph()
         with torch.cuda.graph(g_ours, stream=side):
             ours_batch()
