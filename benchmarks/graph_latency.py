@@ -80,14 +80,14 @@ def main():
         comm.set_param("device_seq", 1)
         row["ours_eager_devseq_us"] = timed(ours_batch) * 1e3 / args.chain   # what the device-side counter costs per call
         g_ours = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(g_ours, stream=side):
+        with torch.cuda.graph(g_ours, stream=side, capture_error_mode="thread_local"):
             ours_batch()
         row["ours_graph_us"] = timed(g_ours.replay) * 1e3 / args.chain
         del g_ours
         torch.cuda.synchronize()
         comm.set_param("device_seq", 0)
         g_nccl = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(g_nccl, stream=side):
+        with torch.cuda.graph(g_nccl, stream=side, capture_error_mode="thread_local"):
             nccl_batch()
         row["nccl_graph_us"] = timed(g_nccl.replay) * 1e3 / args.chain
         del g_nccl
