@@ -255,7 +255,7 @@ public:
         size_t so = 0, ro = 0;
         for (int p = 0; p < n; p++) { sd[(size_t)p] = so; so += sc[(size_t)p]; rd[(size_t)p] = ro; ro += rc[(size_t)p]; }
         TORCH_CHECK(so <= (size_t)in.numel() && ro <= (size_t)out.numel(), "dccl backend: splits exceed the tensors");
-        if (in_splits.empty() && out_splits.empty() && in.numel() == out.numel())
+        if (in_splits.empty() && out_splits.empty() && in.numel() == out.numel() && in.numel() % n == 0)
             return run(c10d::OpType::ALLTOALL_BASE, {out}, out, [&](cudaStream_t s) {
                 return dccl::dcclAllToAll(in.data_ptr(), out.data_ptr(), (size_t)in.numel() / (size_t)n, to_dtype(in.scalar_type()), comm_, s);
             });
