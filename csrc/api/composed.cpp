@@ -29,6 +29,13 @@ ncclResult_t self_copy(dcclComm* c, void* dst, const void* src, size_t bytes, cu
     return c->gpu->local_copy(dst, src, bytes, stream);
 }
 
+/** Both buffers (where given) on the host, or both on the device: the own block is copied between them. */
+bool same_side(const void* a, const void* b) {
+    if (!a || !b) return true;
+    int da = -1, db = -1;
+    return is_device_pointer(a, &da) == is_device_pointer(b, &db);
+}
+
 struct GroupScope {
     GroupScope() { dcclGroupStart(); }
     ncclResult_t end() { done = true; return dcclGroupEnd(); }
@@ -49,6 +56,7 @@ static ncclResult_t all_to_all_impl(const void* sendbuff, const size_t* sendcoun
     size_t total_s = 0, total_r = 0;
     for (int p = 0; p < n; p++) { total_s += sendcounts[p]; total_r += recvcounts[p]; }
     if ((total_s && !sendbuff) || (total_r && !recvbuff)) return ncclInvalidArgument;
+    if (!same_side(sendbuff, recvbuff)) { dccl_error("dcclAllToAll: sendbuff and recvbuff must both be host or both be device memory"); return ncclInvalidArgument; }
     if (sendcounts[rank] != recvcounts[rank]) { dccl_error("dcclAllToAllv: rank %d sends %zu elements to itself but expects %zu", rank, sendcounts[rank], recvcounts[rank]); return ncclInvalidArgument; }
     const char* s = (const char*)sendbuff;
     char* r = (char*)recvbuff;
@@ -94,6 +102,7 @@ ncclResult_t dcclGather(const void* sendbuff, void* recvbuff, size_t count, nccl
     const size_t es = size_of_type(dt);
     if (!es || root < 0 || root >= n || (count && !sendbuff) || (count && rank == root && !recvbuff)) return ncclInvalidArgument;
     if (!count) return ncclSuccess;
+    if (rank == root && !same_side(sendbuff, recvbuff)) { dccl_error("dcclGather: sendbuff and recvbuff must both be host or both be device memory"); return ncclInvalidArgument; }
     if (rank != root) return ncclSend(sendbuff, count, dt, root, comm, stream);
     char* r = (char*)recvbuff;
     ncclResult_t res = ncclSuccess;
@@ -114,6 +123,7 @@ ncclResult_t dcclScatter(const void* sendbuff, void* recvbuff, size_t count, ncc
     const size_t es = size_of_type(dt);
     if (!es || root < 0 || root >= n || (count && !recvbuff) || (count && rank == root && !sendbuff)) return ncclInvalidArgument;
     if (!count) return ncclSuccess;
+    if (rank == root && !same_side(sendbuff, recvbuff)) { dccl_error("dcclScatter: sendbuff and recvbuff must both be host or both be device memory"); return ncclInvalidArgument; }
     if (rank != root) return ncclRecv(recvbuff, count, dt, root, comm, stream);
     const char* s = (const char*)sendbuff;
     ncclResult_t res = ncclSuccess;
