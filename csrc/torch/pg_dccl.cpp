@@ -176,7 +176,7 @@ public:
         TORCH_CHECK(out.numel() == in.numel() * getSize(), "dccl backend: all_gather output must hold world_size inputs");
         return run(c10d::OpType::_ALLGATHER_BASE, {out}, out, [&](cudaStream_t s) {
             return dccl::ncclAllGather(in.data_ptr(), out.data_ptr(), (size_t)in.numel(), to_dtype(in.scalar_type()), comm_, s);
-        });
+        }, false, nullptr, {in});
     }
     c10::intrusive_ptr<Work> allgather(std::vector<std::vector<at::Tensor>>& outs, std::vector<at::Tensor>& ins, const c10d::AllgatherOptions& opts) override {
         TORCH_CHECK(ins.size() == 1 && outs.size() == 1 && (int)outs[0].size() == getSize(), "dccl backend: all_gather expects one input and world_size outputs");
@@ -200,7 +200,7 @@ public:
         TORCH_CHECK(in.numel() == out.numel() * getSize(), "dccl backend: reduce_scatter input must hold world_size outputs");
         return run(c10d::OpType::_REDUCE_SCATTER_BASE, {out}, out, [&](cudaStream_t s) {
             return dccl::ncclReduceScatter(in.data_ptr(), out.data_ptr(), (size_t)out.numel(), to_dtype(in.scalar_type()), to_op(opts.reduceOp), comm_, s);
-        });
+        }, false, nullptr, {in});
     }
     c10::intrusive_ptr<Work> reduce_scatter(std::vector<at::Tensor>& outs, std::vector<std::vector<at::Tensor>>& ins, const c10d::ReduceScatterOptions& opts) override {
         TORCH_CHECK(outs.size() == 1 && ins.size() == 1 && (int)ins[0].size() == getSize(), "dccl backend: reduce_scatter expects one output and world_size inputs");
@@ -258,10 +258,10 @@ public:
         if (in_splits.empty() && out_splits.empty() && in.numel() == out.numel() && in.numel() % n == 0)
             return run(c10d::OpType::ALLTOALL_BASE, {out}, out, [&](cudaStream_t s) {
                 return dccl::dcclAllToAll(in.data_ptr(), out.data_ptr(), (size_t)in.numel() / (size_t)n, to_dtype(in.scalar_type()), comm_, s);
-            });
+            }, false, nullptr, {in});
         return run(c10d::OpType::ALLTOALL_BASE, {out}, out, [&](cudaStream_t s) {
             return dccl::dcclAllToAllv(in.data_ptr(), sc.data(), sd.data(), out.data_ptr(), rc.data(), rd.data(), to_dtype(in.scalar_type()), comm_, s);
-        });
+        }, false, nullptr, {in});
     }
     c10::intrusive_ptr<Work> alltoall(std::vector<at::Tensor>& outs, std::vector<at::Tensor>& ins, const c10d::AllToAllOptions&) override {
         const int n = getSize(), me = getRank();
@@ -282,7 +282,7 @@ public:
             if (res == dccl::ncclSuccess) res = e;
             if (res == dccl::ncclSuccess) outs[(size_t)me].copy_(ins[(size_t)me], true);
             return res;
-        }, /*torch_ops=*/true);
+        }, /*torch_ops=*/true, nullptr, ins);
     }
     c10::intrusive_ptr<Work> gather(std::vector<std::vector<at::Tensor>>& outs, std::vector<at::Tensor>& ins, const c10d::GatherOptions& opts) override {
         const int n = getSize(), me = getRank(), root = (int)opts.rootRank;
@@ -304,7 +304,7 @@ public:
             if (res == dccl::ncclSuccess) res = e;
             if (res == dccl::ncclSuccess) outs[0][(size_t)root].copy_(in, true);
             return res;
-        }, /*torch_ops=*/true);
+        }, /*torch_ops=*/true, nullptr, {in});
     }
     c10::intrusive_ptr<Work> scatter(std::vector<at::Tensor>& outs, std::vector<std::vector<at::Tensor>>& ins, const c10d::ScatterOptions& opts) override {
         const int n = getSize(), me = getRank(), root = (int)opts.rootRank;
@@ -325,7 +325,7 @@ public:
             if (res == dccl::ncclSuccess) res = e;
             if (res == dccl::ncclSuccess) out.copy_(ins[0][(size_t)root], true);
             return res;
-        }, /*torch_ops=*/true);
+        }, /*torch_ops=*/true, nullptr, me == root ? ins[0] : std::vector<at::Tensor>{});
     }
     c10::intrusive_ptr<Work> barrier(const c10d::BarrierOptions&) override {
         // a host all-reduce of one word: returns when every rank has arrived
@@ -354,9 +354,11 @@ private:
         return *stream_;
     }
 
+    /** `keep`: inputs that the communication stream reads; like the outputs they must not be handed back to the
+     *  allocator while that stream still uses them. */
     template <typename F>
     c10::intrusive_ptr<Work> run(c10d::OpType op, std::vector<at::Tensor> outputs, const at::Tensor& where, F fn, bool torch_ops = false,
-                                 c10::intrusive_ptr<Work> after = nullptr) {
+                                 c10::intrusive_ptr<Work> after = nullptr, const std::vector<at::Tensor>& keep = {}) {
         std::lock_guard<std::mutex> g(mu_);
         TORCH_CHECK(comm_, "dccl backend: the process group was shut down");
         const bool cuda = where.is_cuda();
@@ -380,6 +382,7 @@ private:
         }
         // tensors used on the communication stream must not be freed while it still runs
         for (auto& t : work->result()) c10::cuda::CUDACachingAllocator::recordStream(t.storage().data_ptr(), cs);
+        for (auto& t : keep) if (t.defined() && t.is_cuda()) c10::cuda::CUDACachingAllocator::recordStream(t.storage().data_ptr(), cs);
         work->launched(&cs);
         return work;
     }
