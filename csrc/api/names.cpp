@@ -4,7 +4,7 @@
 
 namespace dccl {
 
-static const char* kAlgoNames[ALGO_COUNT] = {"auto", "ring", "rabenseifner", "oneshot", "twoshot", "nvls", "local"};
+static const char* kAlgoNames[ALGO_COUNT] = {"auto", "ring", "rabenseifner", "oneshot", "twoshot", "nvls", "local", "twoshot_ll"};
 
 const char* algo_name(GpuAlgo a) { return (int)a >= 0 && a < ALGO_COUNT ? kAlgoNames[a] : "?"; }
 

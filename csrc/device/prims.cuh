@@ -33,10 +33,13 @@ constexpr size_t kP2pOff = 8u << 20;                    // send/recv FIFOs, one 
 constexpr size_t kP2pChunk = 1u << 20;
 constexpr int kP2pDepth = 4;
 constexpr size_t kP2pBytesPerSrc = kP2pChunk * kP2pDepth;
+constexpr size_t kLL2Off = 40u << 20;                   // packets of the two-shot packet all-reduce
+constexpr size_t kLL2PhaseBytes = 512u << 10;           // per generation, source rank and phase (half of it is payload)
 constexpr size_t kStageOff = 64u << 20;                 // two staging halves follow
 static_assert(kLLOff + kLLBytes <= kP2pOff, "LL region overlaps the p2p FIFOs");
 static_assert(kP2pFlagOff + 2 * kMaxPeers * 4 * kP2pCtas * 8 <= kLLOff, "p2p flag words overlap the packet region");
-static_assert(kP2pOff + kMaxPeers * kP2pBytesPerSrc <= kStageOff, "p2p FIFOs overlap the staging area");
+static_assert(kP2pOff + kMaxPeers * kP2pBytesPerSrc <= kLL2Off, "p2p FIFOs overlap the second packet region");
+static_assert(kLL2Off + 2 * kMaxPeers * 2 * kLL2PhaseBytes <= kStageOff, "second packet region overlaps the staging area");
 
 /* ---- status block (pinned host memory, or device memory in single-GPU emulation) ---- */
 enum : uint32_t { ST_CODE = 0, ST_PEER = 1, ST_SITE = 2, ST_SEQ = 3, ST_KERNEL = 4, ST_WORDS = 8 };

@@ -100,7 +100,7 @@ void dccl_emu_set_peer_buffers(int on) { g_peer_buffers = on ? 1 : 0; }
  * Run `iters` back-to-back calls of one collective among `nranks` virtual ranks on the current
  * device and return every rank's output of the last call.
  *   kind: allreduce | reducescatter | allgather | broadcast | reduce
- *   algo: oneshot | twoshot | ring | rabenseifner
+ *   algo: oneshot | twoshot | twoshot_ll | ring | rabenseifner
  *   count: all-reduce / broadcast / reduce: elements per rank; reduce-scatter: recvcount; all-gather: sendcount
  *   host_in:  nranks consecutive inputs;  host_out: nranks consecutive outputs
  *   misalign: bytes added to every user pointer (exercises the unaligned paths)
@@ -178,6 +178,7 @@ int dccl_emu_collective(const char* kind_s, const char* algo_s, int nranks, int 
         size_t cap = 0;
         if (coll == COLL_ALLREDUCE) {
             if (algo == ALGO_ONESHOT) { cap = oneshot_ll_capacity_bytes() / es; if (count <= cap) e = launch_oneshot_ll(a, dt, cfg); }
+            else if (algo == ALGO_TWOSHOT_LL) { cap = ll_twoshot_capacity_bytes(nranks) / es; if (count <= cap) e = launch_ll_twoshot(a, dt, cfg); }
             else if (algo == ALGO_RING) { a.mode = RING_ALLREDUCE; cap = ring_capacity(a.mode, nranks, es, stage_bytes); if (count <= cap) e = launch_ring(a, dt, cfg); }
             else if (algo == ALGO_RABENSEIFNER) { cap = hd_capacity(nranks, es, stage_bytes); if (count <= cap && is_power_of_two((uint32_t)nranks)) e = launch_hd(a, dt, cfg); }
             else if (direct) { a.symmetric = 1; a.mode = DIRECT_ALLREDUCE; cap = count; e = launch_direct(a, dt, cfg); }

@@ -95,6 +95,7 @@ ncclResult_t GpuCommImpl::all_reduce(const void* send, void* recv, size_t count,
     // a forced variant that cannot serve this call falls back to the closest one that can
     if (ch.algo == ALGO_NVLS && !nvls_ok) ch.algo = ALGO_TWOSHOT;
     if (ch.algo == ALGO_ONESHOT && bytes > oneshot_ll_capacity_bytes()) ch.algo = ALGO_TWOSHOT;
+    if (ch.algo == ALGO_TWOSHOT_LL && bytes > ll_twoshot_capacity_bytes(n_)) ch.algo = ALGO_TWOSHOT;
     if (ch.algo == ALGO_RABENSEIFNER && !is_power_of_two((uint32_t)n_)) ch.algo = ALGO_TWOSHOT;
     if (ch.algo == ALGO_LOCAL || ch.algo == ALGO_AUTO) ch.algo = ALGO_TWOSHOT;
     last_[COLL_ALLREDUCE] = ch.algo;
@@ -110,6 +111,13 @@ ncclResult_t GpuCommImpl::all_reduce(const void* send, void* recv, size_t count,
         NEXT_SEQ(a);
         launches_++;
         return cuda_result(launch_oneshot_ll(a, dt, cfg), "one-shot all-reduce");
+    }
+
+    if (ch.algo == ALGO_TWOSHOT_LL) {
+        a.count = count;
+        NEXT_SEQ(a);
+        launches_++;
+        return cuda_result(launch_ll_twoshot(a, dt, cfg), "two-shot packet all-reduce");
     }
 
     // two-shot on buffers the peers can address: fold straight out of / into the user buffers, no staging

@@ -19,7 +19,7 @@ namespace dccl {
 
 enum Collective { COLL_ALLREDUCE = 0, COLL_REDUCESCATTER, COLL_ALLGATHER, COLL_BROADCAST, COLL_REDUCE, COLL_SENDRECV, COLL_COUNT };
 
-enum GpuAlgo { ALGO_AUTO = 0, ALGO_RING, ALGO_RABENSEIFNER, ALGO_ONESHOT, ALGO_TWOSHOT, ALGO_NVLS, ALGO_LOCAL, ALGO_COUNT };
+enum GpuAlgo { ALGO_AUTO = 0, ALGO_RING, ALGO_RABENSEIFNER, ALGO_ONESHOT, ALGO_TWOSHOT, ALGO_NVLS, ALGO_LOCAL, ALGO_TWOSHOT_LL, ALGO_COUNT };
 
 const char* algo_name(GpuAlgo a);
 /** Returns ALGO_COUNT for an unknown name. */

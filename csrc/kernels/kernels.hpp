@@ -32,6 +32,10 @@ cudaError_t launch_direct(const CollArgs& a, ncclDataType_t dt, const LaunchCfg&
 size_t oneshot_ll_capacity_bytes();
 cudaError_t launch_oneshot_ll(const CollArgs& a, ncclDataType_t dt, const LaunchCfg& cfg);
 
+/* ll_twoshot.cu: two-shot all-reduce on packets (shard to its owner, folded shard to everybody), no barrier */
+size_t ll_twoshot_capacity_bytes(int nranks);
+cudaError_t launch_ll_twoshot(const CollArgs& a, ncclDataType_t dt, const LaunchCfg& cfg);
+
 /* ll_collectives.cu: flag-in-data reduce-scatter / all-gather / broadcast / reduce for small messages;
  * count = per-rank elements, at most oneshot_ll_capacity_bytes() per rank */
 enum { LL_REDUCESCATTER = 0, LL_ALLGATHER, LL_BROADCAST, LL_REDUCE };

@@ -263,3 +263,19 @@ def test_zero_copy_two_shot_on_peer_addressable_buffers(dccl_lib):
                                 assert close(out[r], want[r * count:(r + 1) * count], name, n), ("rs", n, name, count, op, r, in_place)
     finally:
         dccl_lib.dccl_emu_set_peer_buffers(0)
+
+
+@pytest.mark.parametrize("n", [2, 3, 8])
+def test_two_shot_packet_all_reduce(dccl_lib, n):
+    """Shards to their owners and folded shards to everybody, both as polled packets (no barrier); up to 256 KB per shard."""
+    for name in ["float32", "bfloat16", "int8", "float64"]:
+        for count in [1, 3, 9, 1000, 4099, 65536 + 5, (n * (256 << 10)) // np.dtype(np_dtype(name)).itemsize]:
+            for op in ["sum", "avg", "max"]:
+                ins = inputs_for(name, op, count, n, seed=53)
+                want = oracle.fold(ins, op, bf16=name == "bfloat16")
+                for in_place, misalign in [(0, 0), (1, 0), (0, 4)]:
+                    out = emu(dccl_lib, "allreduce", "twoshot_ll", n, name, op, count, ins, in_place=in_place, misalign=misalign, iters=4, ctas=6)
+                    for r in range(n):
+                        assert close(out[r], want, name, n), (n, name, op, count, r, in_place, misalign)
+                    for r in range(1, n):
+                        assert np.array_equal(out[r], out[0]), (n, name, op, count, "ranks differ")

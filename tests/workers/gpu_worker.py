@@ -92,7 +92,7 @@ def main():
         print("OK %d multicast=1 launches=%d" % (cases, launches))
         return
 
-    algos = ["oneshot", "twoshot", "ring", "rabenseifner"] + (["nvls"] if comm.has_multicast else [])
+    algos = ["oneshot", "twoshot", "twoshot_ll", "ring", "rabenseifner"] + (["nvls"] if comm.has_multicast else [])
     if args.suite == "basic":
         names, counts = ["float32", "bfloat16", "int32", "float16"], [1, 1000, 16384, 300001, 4 << 20]
     else:   # chunking: staging is made small through DCCL_STAGING_BYTES by the caller
