@@ -359,7 +359,7 @@ def run_sweep(backend, args, rank, world, dtype, es):
     if sizes[-1] != args.bytes:
         sizes.append(args.bytes)
     ours = args.impl == "ours" and world > 1
-    variants = {"allreduce": ["auto", "oneshot", "twoshot", "ring", "rabenseifner", "nvls", "nvls_staged", "nvls_sym"],
+    variants = {"allreduce": ["auto", "oneshot", "twoshot_ll", "twoshot", "ring", "rabenseifner", "nvls", "nvls_staged", "nvls_sym"],
                 "reducescatter": ["auto", "twoshot", "ring", "nvls"], "allgather": ["auto", "twoshot", "ring", "nvls"]}
     if not ours:
         variants = {k: ["auto"] for k in variants}
@@ -384,6 +384,8 @@ def run_sweep(backend, args, rank, world, dtype, es):
             a, b = (ssrc, sdst) if algo == "nvls_sym" else (src, dst)
             for size in sizes:
                 if algo == "oneshot" and size > (128 << 10):
+                    continue
+                if algo == "twoshot_ll" and size > world * (256 << 10):
                     continue
                 if algo in ("ring", "rabenseifner") and size > (256 << 20):
                     continue

@@ -232,7 +232,7 @@ ncclResult_t  dcclScatter(const void* sendbuff, void* recvbuff, size_t count, nc
 /**
  * Force an algorithm for one collective ("allreduce", "reducescatter",
  * "allgather", "broadcast", "reduce") on this communicator. name is one of
- * auto, ring, rabenseifner, oneshot, twoshot, nvls. Unknown names give
+ * auto, ring, rabenseifner, oneshot, twoshot, twoshot_ll, nvls. Unknown names give
  * ncclInvalidArgument; a variant that cannot serve a call (for example nvls
  * with ncclProd) falls back to the automatic choice for that call.
  */
