@@ -114,6 +114,7 @@ ncclResult_t GpuCommImpl::all_reduce(const void* send, void* recv, size_t count,
     }
 
     if (ch.algo == ALGO_TWOSHOT_LL) {
+        a.mode = LL2_ALLREDUCE;
         a.count = count;
         NEXT_SEQ(a);
         launches_++;
@@ -435,7 +436,8 @@ ncclResult_t GpuCommImpl::reduce(const void* send, void* recv, size_t count, ncc
     if (algo != ALGO_AUTO) ch.algo = algo;
     if (ch.algo == ALGO_NVLS && !nvls_ok) ch.algo = ALGO_TWOSHOT;
     if (ch.algo == ALGO_ONESHOT && bytes > oneshot_ll_capacity_bytes()) ch.algo = ALGO_TWOSHOT;
-    if (ch.algo != ALGO_NVLS && ch.algo != ALGO_ONESHOT) ch.algo = ALGO_TWOSHOT;
+    if (ch.algo == ALGO_TWOSHOT_LL && bytes > ll_twoshot_capacity_bytes(n_)) ch.algo = ALGO_TWOSHOT;
+    if (ch.algo != ALGO_NVLS && ch.algo != ALGO_ONESHOT && ch.algo != ALGO_TWOSHOT_LL) ch.algo = ALGO_TWOSHOT;
     last_[COLL_REDUCE] = ch.algo;
 
     LaunchCfg cfg;
@@ -449,6 +451,13 @@ ncclResult_t GpuCommImpl::reduce(const void* send, void* recv, size_t count, ncc
         NEXT_SEQ(a);
         launches_++;
         return cuda_result(launch_ll_collective(a, dt, cfg), "packet reduce");
+    }
+    if (ch.algo == ALGO_TWOSHOT_LL) {
+        a.mode = LL2_REDUCE;
+        a.count = count;
+        NEXT_SEQ(a);
+        launches_++;
+        return cuda_result(launch_ll_twoshot(a, dt, cfg), "two-shot packet reduce");
     }
     // large messages through the switch: every rank's copy-in overlaps the root's switch pass chunk by chunk
     const bool rooted = ch.algo == ALGO_NVLS && rooted_pipe_ && bytes >= rooted_pipe_min_bytes_;

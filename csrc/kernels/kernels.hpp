@@ -32,7 +32,9 @@ cudaError_t launch_direct(const CollArgs& a, ncclDataType_t dt, const LaunchCfg&
 size_t oneshot_ll_capacity_bytes();
 cudaError_t launch_oneshot_ll(const CollArgs& a, ncclDataType_t dt, const LaunchCfg& cfg);
 
-/* ll_twoshot.cu: two-shot all-reduce on packets (shard to its owner, folded shard to everybody), no barrier */
+/* ll_twoshot.cu: two-shot all-reduce on packets (shard to its owner, folded shard to everybody), no barrier;
+ * LL2_REDUCE sends the folded shards to a.root only */
+enum { LL2_ALLREDUCE = 0, LL2_REDUCE };
 size_t ll_twoshot_capacity_bytes(int nranks);
 cudaError_t launch_ll_twoshot(const CollArgs& a, ncclDataType_t dt, const LaunchCfg& cfg);
 

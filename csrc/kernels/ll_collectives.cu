@@ -7,15 +7,20 @@
  *   reduce-scatter  push shard p of my input to rank p; fold the n-1 packets that arrive
  *                   with my own shard, in rank order
  *   all-gather      push my slot to everybody; copy the n-1 slots that arrive
- *   broadcast       the root pushes, the others poll; the others then acknowledge with a
- *                   flag word and the root waits for the acknowledgements, so that it can
- *                   never lap a slow receiver and overwrite packets that were not read yet
- *   reduce          everybody pushes to the root, the root folds in rank order and then
- *                   acknowledges; the senders wait for that (same reason)
+ *   broadcast       the root pushes, the others poll
+ *   reduce          everybody pushes to the root, the root folds in rank order
  *
- * Reduce-scatter and all-gather need no acknowledgement: a rank only finishes
- * after it has seen every peer's packets of this call, so every peer has
- * entered this call and is done reading the previous generation.
+ * The two packet generations are safe to alternate as long as a rank that has
+ * left call m knows that every rank has ENTERED call m (and so has left every
+ * earlier call, in stream order): it can then reach the generation of call m-1
+ * again only after everybody is done reading it. Reduce-scatter and all-gather
+ * give that for free, a rank only finishes after it has seen every peer's
+ * packets of this call. In the rooted forms a rank would otherwise hear from
+ * the root only (or, as a sender of a reduce, from nobody), so there every CTA
+ * announces its entry to the same CTA of every peer with a flag when it starts
+ * and checks all peers' announcements before it leaves; by then they have
+ * normally long arrived. This covers the other kernels as well: whatever ran
+ * before or runs after a rooted call sees the same guarantee.
  */
 #include "kernels.hpp"
 #include "../device/reduce_ops.cuh"
@@ -76,6 +81,9 @@ __device__ __forceinline__ void ll_collective_body(const CollArgs& a, const Ctx&
     const bool fin = (reinterpret_cast<uintptr_t>(send) & 7u) == 0 && (sbytes & 7u) == 0;
     const bool fout = (reinterpret_cast<uintptr_t>(recv) & 7u) == 0 && (sbytes & 7u) == 0;
     bool ok = true;
+    const bool rooted = mode == LL_BROADCAST || mode == LL_REDUCE;
+    // entry announcement (see the file comment); nothing has to be ordered before it
+    if (rooted && (int)threadIdx.x < n && (int)threadIdx.x != r) signal_peer(c, (int)threadIdx.x, x.bid, x.seq, 0);
 
     for (size_t i = (size_t)x.bid * blockDim.x + threadIdx.x; i < npk && ok; i += (size_t)x.nb * blockDim.x) {
         const size_t off = i * 8;
@@ -141,24 +149,8 @@ __device__ __forceinline__ void ll_collective_body(const CollArgs& a, const Ctx&
         }
     }
 
-    // acknowledgements for the rooted collectives (see the file comment)
-    if (mode == LL_BROADCAST || mode == LL_REDUCE) {
-        __shared__ int s_ok;
-        if (threadIdx.x == 0) s_ok = 1;
-        __syncthreads();
-        if (!ok) s_ok = 0;
-        __syncthreads();
-        if (!s_ok) return;
-        const bool consumer = mode == LL_BROADCAST ? r != root : r == root;   // who read packets
-        if (consumer) {
-            // I am done reading: tell the producer(s)
-            if (mode == LL_BROADCAST) { if (threadIdx.x == 0) signal_peer(c, root, x.bid, x.seq, 0); }
-            else if ((int)threadIdx.x < n && (int)threadIdx.x != r) signal_peer(c, (int)threadIdx.x, x.bid, x.seq, 0);
-        } else {
-            if (mode == LL_BROADCAST) { if ((int)threadIdx.x < n && (int)threadIdx.x != r) wait_peer(c, (int)threadIdx.x, x.bid, x.seq, 0, 320); }
-            else if (threadIdx.x == 0) wait_peer(c, root, x.bid, x.seq, 0, 321);
-        }
-    }
+    // rooted forms: nobody leaves before everybody has entered
+    if (rooted && ok && (int)threadIdx.x < n && (int)threadIdx.x != r) wait_peer(c, (int)threadIdx.x, x.bid, x.seq, 0, 320);
 }
 
 template <typename T, int OP>

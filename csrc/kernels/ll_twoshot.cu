@@ -24,6 +24,11 @@
  * peer, so every peer has entered the call and is done with the previous
  * generation: no acknowledgement is needed.
  *
+ * Reduce to a root is the same kernel with phase B sent to the root only. Phase
+ * A still makes every rank wait for every other rank (the root owns a shard
+ * and contributes to all shards), which is what keeps a fast rank from
+ * reaching the same packet generation again before the root has read it.
+ *
  * The original has one algorithm per call for all sizes (ring or Rabenseifner,
  * reference src/core/dccl.cpp:412-496), each step a host-driven RDMA transfer.
  */
@@ -89,6 +94,8 @@ __device__ __forceinline__ void ll_twoshot_body(const CollArgs& a, const Ctx& x)
     const size_t per = (npk + (size_t)n - 1) / (size_t)n;   // packets per shard; shard j = packets [j*per, (j+1)*per)
     const uint32_t tag = x.seq;
     const bool avg = a.op == (int)ncclAvg;
+    const bool rooted = a.mode == LL2_REDUCE;             // the folded shards go to a.root only
+    const int root = a.root;
     const bool fast_in = (reinterpret_cast<uintptr_t>(send) & 7u) == 0, fast_out = (reinterpret_cast<uintptr_t>(recv) & 7u) == 0;
     const size_t first = (size_t)x.bid * blockDim.x + threadIdx.x, step = (size_t)x.nb * blockDim.x;
     auto valid_of = [&](size_t gi) { return gi >= npk ? 0 : (nbytes - gi * 8 >= 8 ? 8 : (int)(nbytes - gi * 8)); };
@@ -126,9 +133,13 @@ __device__ __forceinline__ void ll_twoshot_body(const CollArgs& a, const Ctx& x)
 #pragma unroll
         for (int e = 0; e < N; e++) out.e[e] = Traits<T>::down(avg ? avg_finish<A>(acc[e], n) : acc[e]);
         const uint4 pkt = make_uint4(out.u.x, tag, out.u.y, tag);
-        for (int k = 1; k < n; k++) st_volatile_v4(ll2_slot(c, (r + k) % n, x.parity, 1, r) + i * 16, pkt);
-        st8(recv + gi * 8, out.u, valid, fast_out);
+        if (!rooted) {
+            for (int k = 1; k < n; k++) st_volatile_v4(ll2_slot(c, (r + k) % n, x.parity, 1, r) + i * 16, pkt);
+            st8(recv + gi * 8, out.u, valid, fast_out);
+        } else if (r == root) st8(recv + gi * 8, out.u, valid, fast_out);
+        else st_volatile_v4(ll2_slot(c, root, x.parity, 1, r) + i * 16, pkt);
     }
+    if (rooted && r != root) return;
 
     /* the other shards arrive folded */
     for (size_t i = first; i < per; i += step)

@@ -18,7 +18,12 @@
  * a launch and the hand-over needs no back pressure. The side that waits for
  * nobody during the pipeline (the root of a broadcast, the non-roots of a
  * reduce) waits at the end for the others, so that a later call cannot reach
- * the same staging half while it is still being read.
+ * the same staging half while it is still being read. Like every kernel of the
+ * library, a rank also leaves only when it knows that every rank has entered
+ * this call (that is what lets staging halves and packet generations alternate
+ * without trailing barriers): the pipeline alone tells a receiver about the
+ * root only, so every CTA announces its entry to all peers when it starts
+ * (flag index 0; chunk k uses index k+1) and checks the announcements at the end.
  *
  * The original's broadcast is a Derecho multicast into host memory followed by
  * a memcpy, and its reduce a gather of slots to the root (reference
@@ -32,7 +37,7 @@ namespace dccl {
 
 constexpr int kRootedMaxChunks = 24;
 constexpr int kRootedDone = 31;        // flag index of the trailing hand-shake
-static_assert(kRootedMaxChunks < kRootedDone && kRootedDone < kFlagVals, "chunk numbers and the trailing index share the per-call flag values");
+static_assert(kRootedMaxChunks + 1 < kRootedDone && kRootedDone < kFlagVals, "chunk numbers and the trailing index share the per-call flag values");
 
 template <typename T, int OP>
 __device__ __forceinline__ void nvls_rooted_body(const CollArgs& a, const Ctx& x) {
@@ -57,6 +62,8 @@ __device__ __forceinline__ void nvls_rooted_body(const CollArgs& a, const Ctx& x
     const bool second = reduce && x.bid >= G;
     const int g = second ? x.bid - G : x.bid;
     if (reduce && (x.bid >= 2 * G || (second && r != root))) return;
+    // entry announcement; the root's second group shares rows with its first and leaves it to that one
+    if (!second && (int)threadIdx.x < n && (int)threadIdx.x != r) signal_peer(c, (int)threadIdx.x, g, x.seq, 0);
 
     for (int k = 0; k < nchunks; k++) {
         const size_t base = (size_t)k * chunk;
@@ -77,18 +84,18 @@ __device__ __forceinline__ void nvls_rooted_body(const CollArgs& a, const Ctx& x
                     if (recv != send) copy_range<T>(recv + off, src, hi - lo);
                 }
                 __syncthreads();
-                if ((int)threadIdx.x < n) signal_peer(c, (int)threadIdx.x, g, x.seq, k);
+                if ((int)threadIdx.x < n) signal_peer(c, (int)threadIdx.x, g, x.seq, k + 1);
             } else {
-                if (!cta_wait_peer(c, root, g, x.seq, k, 580)) return;
+                if (!cta_wait_peer(c, root, g, x.seq, k + 1, 580)) return;
                 if (hi > lo) copy_range<T>(recv + off, my_stage + off, hi - lo);
             }
         } else if (!second) {
             if (hi > lo) copy_range<T>(my_stage + off, send + off, hi - lo);
-            cta_signal_peer(c, root, g, x.seq, k);
+            cta_signal_peer(c, root, g, x.seq, k + 1);
         } else {
             if (threadIdx.x == 0) s_fail = 0;
             __syncthreads();
-            if ((int)threadIdx.x < n && !wait_peer(c, (int)threadIdx.x, g, x.seq, k, 590)) s_fail = 1;
+            if ((int)threadIdx.x < n && !wait_peer(c, (int)threadIdx.x, g, x.seq, k + 1, 590)) s_fail = 1;
             __syncthreads();
             if (s_fail) return;
             if (hi > lo) {
@@ -114,6 +121,8 @@ __device__ __forceinline__ void nvls_rooted_body(const CollArgs& a, const Ctx& x
     } else if (r != root) {
         if (threadIdx.x == 0) wait_peer(c, root, g, x.seq, kRootedDone, 595);
     }
+    // nobody leaves before everybody has entered (the announcements have normally long arrived)
+    if (!second && (int)threadIdx.x < n && (int)threadIdx.x != r) wait_peer(c, (int)threadIdx.x, g, x.seq, 0, 597);
 }
 
 template <typename T, int OP>
