@@ -99,6 +99,11 @@ __device__ __forceinline__ void ll_twoshot_body(const CollArgs& a, const Ctx& x)
     const bool fast_in = (reinterpret_cast<uintptr_t>(send) & 7u) == 0, fast_out = (reinterpret_cast<uintptr_t>(recv) & 7u) == 0;
     const size_t first = (size_t)x.bid * blockDim.x + threadIdx.x, step = (size_t)x.nb * blockDim.x;
     auto valid_of = [&](size_t gi) { return gi >= npk ? 0 : (nbytes - gi * 8 >= 8 ? 8 : (int)(nbytes - gi * 8)); };
+    // A rank leaves a call only when it knows that every rank has entered it (which is what lets the two packet
+    // generations alternate). Folding a shard means hearing from everybody, but a vector too short to give every
+    // rank a shard leaves some ranks with nothing to fold: then the CTAs announce their entry with a flag instead.
+    const bool announce = (size_t)(n - 1) * per >= npk;
+    if (announce && (int)threadIdx.x < n && (int)threadIdx.x != r) signal_peer(c, (int)threadIdx.x, x.bid, x.seq, 0);
 
     /* A: my part of every other rank's shard goes to its owner */
     for (size_t i = first; i < per; i += step)
@@ -139,6 +144,7 @@ __device__ __forceinline__ void ll_twoshot_body(const CollArgs& a, const Ctx& x)
         } else if (r == root) st8(recv + gi * 8, out.u, valid, fast_out);
         else st_volatile_v4(ll2_slot(c, root, x.parity, 1, r) + i * 16, pkt);
     }
+    if (announce && (int)threadIdx.x < n && (int)threadIdx.x != r && !wait_peer(c, (int)threadIdx.x, x.bid, x.seq, 0, 335)) return;
     if (rooted && r != root) return;
 
     /* the other shards arrive folded */
