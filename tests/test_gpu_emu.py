@@ -279,3 +279,10 @@ def test_two_shot_packet_all_reduce(dccl_lib, n):
                         assert close(out[r], want, name, n), (n, name, op, count, r, in_place, misalign)
                     for r in range(1, n):
                         assert np.array_equal(out[r], out[0]), (n, name, op, count, "ranks differ")
+    # the same kernel as a reduce: folded shards go to the root only
+    for root in {0, n - 1}:
+        for count in [1, 5, 4099, 65536 + 5]:
+            ins = inputs_for("float32", "sum", count, n, seed=59)
+            for op in ["sum", "avg"]:
+                out = emu(dccl_lib, "reduce", "twoshot_ll", n, "float32", op, count, ins, root=root, iters=4, ctas=6)
+                assert close(out[root], oracle.fold(ins, op), "float32", n), ("reduce", n, root, count, op)
