@@ -36,6 +36,7 @@ bool GpuCommImpl::set_param(const char* name, int value) {
     if (k == "pipe_ctas" && value >= 3 && value <= kMaxCtas) { pipe_ctas_ = value; return true; }
     if (k == "device_seq" && (value == 0 || value == 1)) return set_device_seq(value == 1);
     if (k == "rooted_pipe" && (value == 0 || value == 1)) { rooted_pipe_ = value == 1; return true; }
+    if (k == "pipe_chunk_kb" && value >= 256) { nvls_pipe_set_chunk_bytes((size_t)value << 10); return true; }
     return false;
 }
 

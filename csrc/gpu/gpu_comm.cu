@@ -59,6 +59,7 @@ bool GpuCommImpl::init(std::string* err) {
     pipe_ctas_ = (int)cfg.get_int("DCCL/nvls_pipe_ctas", 144);
     device_stamps_ = cfg.get_bool("DCCL/device_stamps", false);
     rooted_pipe_ = cfg.get_bool("DCCL/nvls_rooted_pipe", false);
+    nvls_pipe_set_chunk_bytes((size_t)cfg.get_int("DCCL/nvls_pipe_chunk_bytes", 8ll << 20));
     rooted_pipe_min_bytes_ = (size_t)cfg.get_int("DCCL/nvls_rooted_pipe_min_bytes", 16ll << 20);
     if (p2p_ctas_ < 1) p2p_ctas_ = 1;
     if (p2p_ctas_ > kP2pCtas) p2p_ctas_ = kP2pCtas;

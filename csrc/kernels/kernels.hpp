@@ -53,6 +53,8 @@ cudaError_t launch_nvls(const CollArgs& a, ncclDataType_t dt, const LaunchCfg& c
  * chunk by chunk (reduce-scatter: count = per-rank elements, stride = slot distance in the send buffer) */
 size_t nvls_pipe_capacity(size_t elem_size, size_t stage_bytes, int nranks, bool reduce_scatter);
 cudaError_t launch_nvls_pipe(const CollArgs& a, ncclDataType_t dt, const LaunchCfg& cfg, bool reduce_scatter);
+/** Target chunk size of the pipeline (default 8 MB, at most 24 chunks per launch); a tuning knob, the same on every rank. */
+void nvls_pipe_set_chunk_bytes(size_t bytes);
 
 /* nvls_rooted.cu: broadcast / reduce of large ordinary buffers through the switch with the local copies overlapped
  * chunk by chunk (count elements, at most nvls_pipe_capacity(..., false); root in a.root) */

@@ -147,8 +147,12 @@ size_t nvls_pipe_capacity(size_t es, size_t stage_bytes, int nranks, bool reduce
     return reduce_scatter ? (elems / (size_t)nranks / 64) * 64 : elems;
 }
 
+static size_t g_pipe_chunk_bytes = 8u << 20;   // target chunk size; every rank must use the same value
+
+void nvls_pipe_set_chunk_bytes(size_t bytes) { if (bytes >= (256u << 10)) g_pipe_chunk_bytes = bytes; }
+
 int nvls_pipe_chunks(size_t bytes) {
-    size_t k = (bytes + (8u << 20) - 1) / (8u << 20);
+    size_t k = (bytes + g_pipe_chunk_bytes - 1) / g_pipe_chunk_bytes;
     if (k < 2) k = 2;
     if (k > (size_t)kPipeMaxChunks) k = kPipeMaxChunks;
     return (int)k;
