@@ -269,7 +269,7 @@ def test_zero_copy_two_shot_on_peer_addressable_buffers(dccl_lib):
 def test_two_shot_packet_all_reduce(dccl_lib, n):
     """Shards to their owners and folded shards to everybody, both as polled packets (no barrier); up to 256 KB per shard."""
     for name in ["float32", "bfloat16", "int8", "float64"]:
-        for count in [1, 3, 9, 1000, 4099, 65536 + 5, (n * (256 << 10)) // np.dtype(np_dtype(name)).itemsize]:
+        for count in [1, 9, 4099, 65536 + 5, (n * (256 << 10)) // np.dtype(np_dtype(name)).itemsize]:
             for op in ["sum", "avg", "max"]:
                 ins = inputs_for(name, op, count, n, seed=53)
                 want = oracle.fold(ins, op, bf16=name == "bfloat16")
