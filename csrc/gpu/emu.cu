@@ -29,6 +29,33 @@ int g_device_seq = 0;
 // memory), so that the two-shot all-reduce takes its zero-copy form
 int g_peer_buffers = 0;
 
+// Pools of finished emulation runs, kept for the next run of the same size (the tests make thousands of short
+// runs; allocating and clearing 8 x 80 MB for each would dominate them).
+std::vector<char*> g_spare_pools;
+size_t g_spare_pool_bytes = 0;
+
+char* take_pool(size_t bytes) {
+    if (g_spare_pool_bytes != bytes) {
+        for (char* p : g_spare_pools) cudaFree(p);
+        g_spare_pools.clear();
+        g_spare_pool_bytes = bytes;
+    }
+    if (!g_spare_pools.empty()) { char* p = g_spare_pools.back(); g_spare_pools.pop_back(); return p; }
+    char* p = nullptr;
+    return cudaMalloc((void**)&p, bytes) == cudaSuccess ? p : nullptr;
+}
+
+void give_pool(char* p, size_t bytes) {
+    if (bytes == g_spare_pool_bytes && g_spare_pools.size() < (size_t)kMaxPeers) g_spare_pools.push_back(p);
+    else cudaFree(p);
+}
+
+/** Flags, credit words and packet tags must start from zero; FIFO and staging contents do not matter. */
+bool clear_pool_control(char* pool) {
+    return cudaMemset(pool, 0, kLLOff + kLLBytes) == cudaSuccess &&
+           cudaMemset(pool + kLL2Off, 0, 2 * (size_t)kMaxPeers * 2 * kLL2PhaseBytes) == cudaSuccess;
+}
+
 struct EmuWorld {
     int n = 0;
     size_t stage_bytes = 0, pool_bytes = 0;
@@ -39,7 +66,8 @@ struct EmuWorld {
     std::vector<DevComm> comms;
     ~EmuWorld() {
         if (seq_words) cudaFree(seq_words);
-        for (char* p : pools) if (p) cudaFree(p);
+        cudaDeviceSynchronize();
+        for (char* p : pools) if (p) give_pool(p, pool_bytes);
         if (status) cudaFree(status);
         if (d_comms) cudaFree(d_comms);
     }
@@ -49,8 +77,8 @@ struct EmuWorld {
         pool_bytes = kStageOff + 2 * stage;
         pools.assign(n, nullptr);
         for (int r = 0; r < n; r++) {
-            if (cudaMalloc((void**)&pools[r], pool_bytes) != cudaSuccess) return false;
-            if (cudaMemset(pools[r], 0, kStageOff) != cudaSuccess) return false;
+            if ((pools[r] = take_pool(pool_bytes)) == nullptr) return false;
+            if (!clear_pool_control(pools[r])) return false;
         }
         if (cudaMalloc((void**)&status, (ST_WORDS + 8) * sizeof(uint32_t)) != cudaSuccess) return false;
         cudaMemset(status, 0, (ST_WORDS + 8) * sizeof(uint32_t));
