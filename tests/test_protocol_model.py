@@ -17,7 +17,7 @@ N = 3   # ranks
 
 
 def plan(kind, root, rank):
-    """(peers I write to when I start, peers whose packet I read, do I wait for everybody's entry)."""
+    """(peers whose inbox I write when I start, peers whose packet I read)."""
     others = [p for p in range(N) if p != rank]
     if kind == "allreduce":
         return others, others
