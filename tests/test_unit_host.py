@@ -186,3 +186,17 @@ def test_tuning_table_from_measured_sweeps(dccl_lib, tmp_path):
         assert dccl_lib.dccl_tuner_choose(b"allreduce", 8, nbytes, 1, algo, 32, ctypes.byref(ctas)) == 0
         assert algo.value == want, (nbytes, algo.value)
     assert dccl_lib.dccl_tuner_choose(b"reducescatter", 8, 1 << 28, 1, algo, 32, ctypes.byref(ctas)) == 0 and (algo.value, ctas.value) == (b"twoshot", 128)
+
+
+def test_launcher_command_line():
+    """python -m dccl_b200.utils.launch: one process per rank, rank-tagged output, worst exit code."""
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    p = subprocess.run([sys.executable, "-m", "dccl_b200.utils.launch", "-n", "3", "--", "/bin/sh", "-c", "echo rank $DCCL_RANK of $DCCL_WORLD_SIZE"],
+                       cwd=root, capture_output=True, text=True, timeout=60)
+    assert p.returncode == 0, p.stderr
+    assert sorted(p.stdout.split("\n")[:3]) == ["[0] rank 0 of 3", "[1] rank 1 of 3", "[2] rank 2 of 3"]
+    p = subprocess.run([sys.executable, "-m", "dccl_b200.utils.launch", "-n", "2", "--", "/bin/sh", "-c", "exit $DCCL_RANK"],
+                       cwd=root, capture_output=True, text=True, timeout=60)
+    assert p.returncode == 1
