@@ -122,3 +122,96 @@ def test_acknowledging_the_root_only_is_not_enough():
     assert bad is not None and "overwrites" in bad, bad
     # and the all-to-all kernels alone never needed anything extra
     assert explore([("allreduce", 0)] * 3, announce=False) is None
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+# grouped send / recv: FIFO credits and the batching of long groups
+# ---------------------------------------------------------------------------------------------------------------------
+
+def run_group(ops_per_rank, batch, depth, partition):
+    """Fixpoint simulation of one grouped call (csrc/kernels/p2p.cu, GpuCommImpl::p2p_launch).
+
+    ops_per_rank[r] is the recorded list of ("send" | "recv", peer, chunks). Chunk numbers per ordered pair are given
+    out in recording order. The list is cut into launches of `batch` operations; a rank starts its next launch when
+    all operations of the current one are done; inside a launch all operations progress concurrently. A sender may
+    write chunk G when G < depth or the receiver has consumed chunk G - depth; a receiver may read chunk G once it is
+    written. `partition`: "batch" moves the receives of every launch to its front (what the library does), "global"
+    moves all receives of the whole group to the front before cutting (the mistake this test guards against),
+    "none" keeps the recording order. Returns True when every operation completes, False on deadlock."""
+    n = len(ops_per_rank)
+    next_chunk = {}
+    plans = []
+    for r, ops in enumerate(ops_per_rank):
+        tagged = []
+        for kind, peer, chunks in ops:
+            key = (r, peer) if kind == "send" else (peer, r)
+            first = next_chunk.get((kind, key), 0)
+            next_chunk[(kind, key)] = first + chunks
+            tagged.append([kind, key, first, chunks, 0])            # ..., chunks done
+        if partition == "global":
+            tagged.sort(key=lambda o: o[0] != "recv")
+        launches = [tagged[i:i + batch] for i in range(0, len(tagged), batch)]
+        if partition == "batch":
+            for launch in launches:
+                launch.sort(key=lambda o: o[0] != "recv")
+        plans.append(launches)
+    written, consumed = {}, {}                                       # per ordered pair: chunks written / consumed
+    current = [0] * n
+    while True:
+        progress = False
+        for r in range(n):
+            if current[r] >= len(plans[r]):
+                continue
+            launch = plans[r][current[r]]
+            for op in launch:
+                kind, key, first, chunks, done = op
+                while done < chunks:
+                    g = first + done
+                    if kind == "send":
+                        if g >= depth and consumed.get(key, 0) < g - depth + 1:
+                            break
+                        if written.get(key, 0) != g:                 # chunks of one pair are written in order
+                            break
+                        written[key] = g + 1
+                    else:
+                        if written.get(key, 0) < g + 1 or consumed.get(key, 0) != g:
+                            break
+                        consumed[key] = g + 1
+                    done += 1
+                    progress = True
+                op[4] = done
+            if all(op[4] == op[3] for op in launch):
+                current[r] += 1
+                progress = True
+        if all(current[r] >= len(plans[r]) for r in range(n)):
+            return True
+        if not progress:
+            return False
+
+
+def ring(n, window, chunks):
+    return [[op for _ in range(window) for op in (("send", (r + 1) % n, chunks), ("recv", (r - 1) % n, chunks))] for r in range(n)]
+
+
+def all_to_all(n, chunks):
+    return [[("recv", (r - k) % n, chunks) for k in range(1, n)] + [("send", (r + k) % n, chunks) for k in range(1, n)] for r in range(n)]
+
+
+def test_grouped_send_recv_never_deadlocks_with_receivers_first_per_launch():
+    for n in (2, 3, 8):
+        for chunks in (1, 3, 9):                                     # 9 > FIFO depth: senders need credit
+            assert run_group(all_to_all(n, chunks), batch=16, depth=4, partition="batch")
+            for window in (1, 4, 10):
+                assert run_group(ring(n, window, chunks), batch=16, depth=4, partition="batch"), (n, window, chunks)
+                assert run_group(ring(n, window, chunks), batch=16, depth=4, partition="none"), (n, window, chunks)
+    # gather / scatter: the root groups n-1 operations, everybody else issues a single one
+    n = 8
+    gather = [[("recv", p, 5) for p in range(1, n)]] + [[("send", 0, 5)] for _ in range(1, n)]
+    assert run_group(gather, batch=16, depth=4, partition="batch")
+
+
+def test_moving_all_receives_of_a_long_group_to_the_front_would_deadlock():
+    # 10 sends and 10 receives per rank = 20 operations = two launches: with all receives first, the receives of the
+    # first launch wait for sends that sit in the peers' second launch
+    assert not run_group(ring(4, 10, 1), batch=16, depth=4, partition="global")
+    assert run_group(ring(4, 10, 1), batch=16, depth=4, partition="batch")
