@@ -115,8 +115,12 @@ private:
 class BackendDccl : public c10d::Backend {
 public:
     BackendDccl(const c10::intrusive_ptr<c10d::Store>& store, int rank, int size) : Backend(rank, size) {
-        static std::atomic<int> counter{0};
-        const std::string key = "dccl_unique_id/" + std::to_string(counter++);
+        // The store is private to the process group (c10d prefixes it per group and device), so the key only has to
+        // tell apart several backends made on the same store: every member counts its own creations there, and all
+        // members of a group create the same number. (A counter of the process would run apart between ranks as soon
+        // as subgroups with different members exist.)
+        const int64_t instance = store->add("dccl_instances/" + std::to_string(rank), 1);
+        const std::string key = "dccl_unique_id/" + std::to_string(instance);
         dccl::dcclUniqueId id;
         if (rank == 0) {
             check(dccl::dcclGetUniqueId(&id), "dcclGetUniqueId");

@@ -105,6 +105,23 @@ def main():
             check(bool((msg == float(rank - 1)).all()), "send/recv")
     dist.barrier()
 
+    # subgroups: every rank calls new_group, only the members get a communicator; then a second world-wide group
+    if world >= 3:
+        members = list(range(0, world, 2))
+        evens = dist.new_group(ranks=members)
+        t = torch.full((1000,), float(rank), device=dev)
+        if rank in members:
+            dist.all_reduce(t, group=evens)
+            check(bool((t == float(sum(members))).all()), "all_reduce in a subgroup")
+            out = torch.empty(len(members), device=dev)
+            dist.all_gather_into_tensor(out, torch.tensor([float(rank)], device=dev), group=evens)
+            check(out.tolist() == [float(m) for m in members], "all_gather in a subgroup")
+        again = dist.new_group(ranks=list(range(world)))
+        t = torch.full((10,), 1.0, device=dev)
+        dist.all_reduce(t, group=again)
+        check(bool((t == float(world)).all()), "all_reduce in a second world-wide group")
+        dist.barrier()
+
     if args.ddp:
         # DistributedDataParallel over the backend: gradients must equal the average of the per-rank gradients
         torch.manual_seed(0)
