@@ -105,6 +105,14 @@ def main():
             check(bool((msg == float(rank - 1)).all()), "send/recv")
     dist.barrier()
 
+    # Python objects ride on byte tensors: broadcast_object_list, all_gather_object
+    objs = [{"from": rank, "payload": list(range(rank + 3))}]
+    dist.broadcast_object_list(objs, src=world - 1, device=dev)
+    check(objs[0] == {"from": world - 1, "payload": list(range(world + 2))}, "broadcast_object_list")
+    gathered = [None] * world
+    dist.all_gather_object(gathered, ("rank", rank))
+    check(gathered == [("rank", r) for r in range(world)], "all_gather_object")
+
     # subgroups: every rank calls new_group, only the members get a communicator; then a second world-wide group
     if world >= 3:
         members = list(range(0, world, 2))
