@@ -331,6 +331,30 @@ public:
             return res;
         }, /*torch_ops=*/true, nullptr, me == root ? ins[0] : std::vector<at::Tensor>{});
     }
+    /* ---- coalescing (torch.distributed.batch_isend_irecv): sends and receives issued between start and end are
+     *      recorded and leave as ONE grouped launch, so a ring of isend / irecv cannot deadlock ---- */
+    bool supportsCoalescing() const override { return true; }
+    void startCoalescing() override {
+        std::lock_guard<std::mutex> g(mu_);
+        TORCH_CHECK(!coalescing_, "dccl backend: coalescing is already active");
+        check(dccl::dcclGroupStart(), "dcclGroupStart");
+        coalescing_ = true;
+        coalesced_device_ = -1;
+    }
+    c10::intrusive_ptr<Work> endCoalescing() override {
+        std::lock_guard<std::mutex> g(mu_);
+        TORCH_CHECK(coalescing_, "dccl backend: endCoalescing without startCoalescing");
+        coalescing_ = false;
+        const dccl::ncclResult_t r = dccl::dcclGroupEnd();     // device operations launch on the communication stream here
+        check(r, "dcclGroupEnd");
+        const bool cuda = coalesced_device_ >= 0;
+        auto work = c10::make_intrusive<WorkDccl>(c10d::OpType::COALESCED, std::vector<at::Tensor>{}, cuda);
+        if (cuda) {
+            c10::cuda::CUDAGuard dg((c10::DeviceIndex)coalesced_device_);
+            work->launched(&comm_stream((c10::DeviceIndex)coalesced_device_));
+        } else work->launched(nullptr);
+        return work;
+    }
     c10::intrusive_ptr<Work> barrier(const c10d::BarrierOptions&) override {
         // a host all-reduce of one word: returns when every rank has arrived
         int32_t word = 0;
@@ -373,6 +397,7 @@ private:
             return work;
         }
         (void)after;   // same communication stream: already ordered
+        if (coalescing_) coalesced_device_ = (int)where.device().index();
         c10::cuda::CUDAGuard dg(where.device());
         c10::cuda::CUDAStream& cs = comm_stream(where.device().index());
         at::cuda::CUDAEvent ready(cudaEventDisableTiming);
@@ -394,6 +419,8 @@ private:
     dccl::ncclComm_t comm_ = nullptr;
     std::unique_ptr<c10::cuda::CUDAStream> stream_;
     std::mutex mu_;
+    bool coalescing_ = false;
+    int coalesced_device_ = -1;   // device of the CUDA tensors seen while coalescing, -1: host tensors only
 };
 
 } // namespace

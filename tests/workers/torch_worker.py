@@ -105,6 +105,17 @@ def main():
             check(bool((msg == float(rank - 1)).all()), "send/recv")
     dist.barrier()
 
+    # batch_isend_irecv: a ring in which everybody sends first, with messages longer than a FIFO; one grouped launch
+    if world >= 2:
+        big = torch.full((1 << 20,), float(rank), device=dev)          # 4 MB
+        got = torch.empty_like(big)
+        works = dist.batch_isend_irecv([dist.P2POp(dist.isend, big, (rank + 1) % world), dist.P2POp(dist.irecv, got, (rank - 1) % world)])
+        for w in works:
+            w.wait()
+        if args.cuda:
+            torch.cuda.synchronize()
+        check(bool((got == float((rank - 1) % world)).all()), "batch_isend_irecv ring")
+
     # Python objects ride on byte tensors: broadcast_object_list, all_gather_object
     objs = [{"from": rank, "payload": list(range(rank + 3))}]
     dist.broadcast_object_list(objs, src=world - 1, device=dev)
