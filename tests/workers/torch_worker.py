@@ -105,6 +105,21 @@ def main():
             check(bool((msg == float(rank - 1)).all()), "send/recv")
     dist.barrier()
 
+    # list forms: reduce_scatter from a list of tensors (goes through a temporary), product and min
+    parts = [torch.full((257,), float(rank + 1 + p), device=dev) for p in range(world)]
+    out = torch.empty(257, device=dev)
+    dist.reduce_scatter(out, parts)
+    check(bool((out == float(sum(r + 1 + rank for r in range(world)))).all()), "reduce_scatter (list)")
+    t = torch.full((33,), float(rank + 1), device=dev, dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.PRODUCT)
+    want = 1.0
+    for r in range(world):
+        want *= r + 1
+    check(bool((t == want).all()), "all_reduce product")
+    t = torch.full((33,), rank + 5, device=dev, dtype=torch.int32)
+    dist.all_reduce(t, op=dist.ReduceOp.MIN)
+    check(bool((t == 5).all()), "all_reduce min")
+
     # batch_isend_irecv: a ring in which everybody sends first, with messages longer than a FIFO; one grouped launch
     if world >= 2:
         big = torch.full((1 << 20,), float(rank), device=dev)          # 4 MB
