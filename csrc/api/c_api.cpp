@@ -10,6 +10,9 @@
 #include "comm.hpp"
 #include "../tuner/tuner.hpp"
 #include <cstring>
+#include <cstdlib>
+#include <sys/mman.h>
+#include <unistd.h>
 
 using namespace dccl;
 
@@ -96,6 +99,37 @@ int dccl_group_end() { return (int)dcclGroupEnd(); }
 int dccl_set_algorithm(void* comm, const char* coll, const char* name) { GUARD(dcclSetAlgorithm((ncclComm_t)comm, coll, name)); }
 const char* dccl_last_algorithm(void* comm, const char* coll) {
     try { return dcclGetLastAlgorithm((ncclComm_t)comm, coll); } catch (...) { return ""; }
+}
+
+/**
+ * Self test of the descriptor plane (what carries the cuMem handles between ranks): every rank puts its rank
+ * number into an anonymous memory file, passes the descriptor to every peer and reads what the peers passed.
+ * Returns 0, or 1 + the first peer whose file did not arrive or did not hold that peer's rank.
+ */
+int dccl_selftest_fd_exchange(void* comm) {
+    dcclComm* c = (dcclComm*)comm;
+    if (!c) return -1;
+    Bootstrap& bs = c->bs;
+    const int n = bs.world(), r = bs.rank();
+    if (n == 1) return 0;
+    int fd = memfd_create("dccl-fdtest", 0);
+    if (fd < 0) return -2;
+    int32_t mine = r;
+    if (write(fd, &mine, sizeof(mine)) != (ssize_t)sizeof(mine)) { close(fd); return -2; }
+    const uint32_t tag = 0x7e570000u;
+    int bad = 0;
+    for (int k = 1; k < n && !bad; k++) if (!bs.send_fd((r + k) % n, fd, tag)) bad = 1 + (r + k) % n;
+    for (int k = 1; k < n && !bad; k++) {
+        const int p = (r + n - k) % n;
+        int got = -1;
+        int32_t v = -1;
+        if (!bs.recv_fd(p, tag, &got, 10000) || pread(got, &v, sizeof(v), 0) != (ssize_t)sizeof(v) || v != p) bad = 1 + p;
+        if (got >= 0) close(got);
+    }
+    close(fd);
+    // nobody tears its socket down while a peer still expects a descriptor
+    if (!bs.barrier() && !bad) bad = -3;
+    return bad;
 }
 
 /* timestamps */

@@ -34,6 +34,7 @@ def _declare(lib):
         "dccl_comm_init_rank": (i, [c.POINTER(vp), i, vp, i]),
         "dccl_comm_finalize": (i, [vp]),
         "dccl_comm_abort": (i, [vp]),
+        "dccl_selftest_fd_exchange": (i, [vp]),
         "dccl_comm_shrink": (i, [vp, c.POINTER(vp)]),
         "dccl_world_size": (i, [vp]),
         "dccl_rank": (i, [vp]),

@@ -157,6 +157,10 @@ def main():
             else:
                 comm.recv(got, 0)
                 check(np.all(got == 0), "blocking send/recv")
+    # the descriptor plane (SCM_RIGHTS over the per-rank unix sockets) that carries the GPU memory handles
+    from dccl_b200._lib import lib as _native
+    check(_native().dccl_selftest_fd_exchange(comm._h) == 0, "descriptor exchange between all ranks")
+
     # all-to-all (equal and uneven blocks), gather, scatter
     for n in [1, 1000, 400001]:
         src = [np.arange(n * world, dtype=np.float64) + 1e6 * r for r in range(world)]
