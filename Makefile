@@ -56,7 +56,7 @@ CU_OBJS := $(patsubst %.cu,$(BUILD)/obj/%.cu.o,$(CU_SRCS))
 LIB := $(BUILD)/libdccl.so
 TOOLS := $(BUILD)/dccl_cli $(BUILD)/p2p_perf $(BUILD)/helloworld $(BUILD)/nccl_names $(BUILD)/c_api_example
 ifeq ($(CUDA),1)
-TOOLS += $(BUILD)/nccl_cli $(BUILD)/dccl_sweep
+TOOLS += $(BUILD)/nccl_cli $(BUILD)/dccl_sweep $(BUILD)/dccl_topo
 endif
 
 .PHONY: all lib tools clean install
@@ -102,6 +102,9 @@ $(BUILD)/c_api_example: examples/c_api/main.c include/dccl/dccl_c.h $(LIB)
 
 # comparator: the same workload through stock NCCL (found at run time with dlopen)
 $(BUILD)/nccl_cli: tools/nccl_cli.cpp tools/tool_common.hpp $(LIB)
+	$(CXX) $(CXXFLAGS) $(TOOL_DEFS) $< -o $@ -L$(BUILD) -ldccl -Wl,-rpath,'$$ORIGIN' $(CUDA_LIBS) $(LDFLAGS)
+
+$(BUILD)/dccl_topo: tools/dccl_topo.cpp $(LIB)
 	$(CXX) $(CXXFLAGS) $(TOOL_DEFS) $< -o $@ -L$(BUILD) -ldccl -Wl,-rpath,'$$ORIGIN' $(CUDA_LIBS) $(LDFLAGS)
 
 $(BUILD)/dccl_sweep: tools/dccl_sweep.cpp tools/tool_common.hpp $(LIB)

@@ -7,6 +7,9 @@
 #include "../core/config.hpp"
 #include "../core/types.hpp"
 #include "../gpu/gpu_comm.hpp"
+#ifdef DCCL_WITH_CUDA
+#include "../gpu/topology.hpp"
+#endif
 #include "comm.hpp"
 #include "../tuner/tuner.hpp"
 #include <cstring>
@@ -54,6 +57,16 @@ int dccl_has_multicast(void* comm) { dcclComm* c = (dcclComm*)comm; return c && 
 unsigned long long dccl_launch_count(void* comm) { dcclComm* c = (dcclComm*)comm; return c && c->gpu ? c->gpu->launches() : 0ull; }
 int dccl_comm_set_param(void* comm, const char* name, int value) { dcclComm* c = (dcclComm*)comm; return c && c->gpu && c->gpu->set_param(name, value) ? 0 : (int)ncclInvalidArgument; }
 int dccl_cuda_device_count() { return cuda_device_count(); }
+int dccl_topology_json(void* comm, char* out, size_t len) { GUARD(dcclGetTopology((ncclComm_t)comm, out, len)); }
+#ifdef DCCL_WITH_CUDA
+/** NVLink links per GPU from NVML alone (no CUDA, no communicator): 0 and JSON in `out`, or -1 when NVML cannot be loaded. */
+int dccl_nvml_link_report(const char* lib, char* out, size_t len) {
+    std::string json, err;
+    if (!nvml_link_report(lib, &json, &err)) { if (out && len) snprintf(out, len, "%s", err.c_str()); return -1; }
+    if (out && len) snprintf(out, len, "%s", json.c_str());
+    return 0;
+}
+#endif
 
 int dccl_register(void* comm, void* buf, size_t size) { GUARD(dcclRegisterCacheMemory((ncclComm_t)comm, buf, size)); }
 int dccl_deregister(void* comm, void* buf) { GUARD(dcclDeregisterCacheMemory((ncclComm_t)comm, buf)); }

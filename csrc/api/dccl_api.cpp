@@ -469,6 +469,14 @@ ncclResult_t ncclRecv(void* recvbuff, size_t count, ncclDataType_t dt, int peer,
     return r;
 }
 
+ncclResult_t dcclGetTopology(ncclComm_t comm, char* json, size_t len) {
+    VALIDATE_COMM(comm);
+    if (!json || !len) return ncclInvalidArgument;
+    if (!comm->gpu) { json[0] = 0; return ncclInvalidUsage; }
+    snprintf(json, len, "%s", comm->gpu->topology().c_str());
+    return ncclSuccess;
+}
+
 /* ---------------- algorithm control ---------------- */
 
 ncclResult_t dcclSetAlgorithm(ncclComm_t comm, const char* collective, const char* name) {

@@ -86,6 +86,11 @@ bool GpuCommImpl::init(std::string* err) {
     dc_.timeout_ns = (unsigned long long)cfg.get_int("DCCL/timeout_ms", 5000) * 1000000ull;
     dc_.stage_bytes = stage_bytes_;
 
+    {   // collective: also a rank whose set-up failed above takes part, or its peers would wait for it
+        std::string terr;
+        const bool tok = discover_topology(&terr);
+        if (!tok && ok && n_ > 1) { ok = false; if (err && err->empty()) *err = terr; }   // a world of one can live without it
+    }
     if (n_ == 1) return ok;   // a world of one needs no pool: every collective is a local copy
 
     // sequence counter on the device (used when DCCL/device_seq is on): {next sequence number, CTAs done}
@@ -141,6 +146,40 @@ GpuCommImpl::~GpuCommImpl() {
     if (status_host_) cudaFreeHost(status_host_);
     if (seq_dev_) cudaFree(seq_dev_);
     cudaGetLastError();
+}
+
+/* ---------------- topology ---------------- */
+
+bool GpuCommImpl::discover_topology(std::string* err) {
+    topo_ = Topology();
+    topo_.nranks = n_;
+    GpuInfo mine;
+    const bool have = discover_gpu(dev_, &mine, err);
+    if (n_ == 1) {
+        topo_.gpu[0] = mine;
+        topo_.access[0][0] = 2;
+        topo_.atomics[0][0] = 1;
+        if (have) dccl_info("topology: %s", topology_summary(topo_).c_str());
+        return have;
+    }
+    // the control plane carries both exchanges; a rank whose discovery failed still takes part (with an empty record)
+    if (!bs_->allgather(&mine, sizeof(mine), topo_.gpu)) { if (err) *err = "control plane failed: " + bs_->last_error(); return false; }
+    unsigned char row[2][kMaxPeers];
+    memset(row, 0, sizeof(row));
+    discover_peer_row(dev_, topo_.gpu, n_, row[0], row[1]);
+    unsigned char all[kMaxPeers][2][kMaxPeers];
+    if (!bs_->allgather(row, sizeof(row), all)) { if (err) *err = "control plane failed: " + bs_->last_error(); return false; }
+    bool blocked = false;
+    for (int a = 0; a < n_; a++)
+        for (int b = 0; b < n_; b++) {
+            topo_.access[a][b] = all[a][0][b];
+            topo_.atomics[a][b] = all[a][1][b];
+            if (a != b && all[a][0][b] == 0) blocked = true;
+        }
+    if (rank_ == 0) dccl_info("topology: %s", topology_summary(topo_).c_str());
+    if (blocked) dccl_warn("some GPU pairs report no peer access; mapping the pools will show whether they can be reached");
+    for (int a = 0; a < n_; a++) if (topo_.gpu[a].device < 0) { if (err) *err = "rank " + std::to_string(a) + " could not describe its GPU"; return false; }
+    return true;
 }
 
 /* ---------------- where the sequence number lives ---------------- */

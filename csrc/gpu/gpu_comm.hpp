@@ -72,6 +72,8 @@ public:
     virtual void quiesce() = 0;
     virtual GpuAlgo last_algo(int coll) const = 0;
     virtual int device() const = 0;
+    /** The GPUs of all ranks, the peer-access matrix and the NVLink / multicast facts, as JSON (topology.hpp). */
+    virtual std::string topology() const = 0;
     virtual bool has_multicast() const = 0;
     /** Tuning knobs for sweeps: "ctas" (0 = table value), "threads" (128..512), "unroll" (2, 4, 8), ...;
      *  "device_seq" (0 / 1) moves the call sequence number between the host and a device counter, which is

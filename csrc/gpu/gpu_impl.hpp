@@ -3,6 +3,7 @@
 #pragma once
 #include "gpu_comm.hpp"
 #include "symmem.hpp"
+#include "topology.hpp"
 #include "../kernels/kernels.hpp"
 #include "../tuner/tuner.hpp"
 #include <atomic>
@@ -55,6 +56,7 @@ public:
     void quiesce() override { DeviceGuard g(dev_); cudaDeviceSynchronize(); cudaGetLastError(); }
     GpuAlgo last_algo(int coll) const override { return last_[coll]; }
     int device() const override { return dev_; }
+    std::string topology() const override { return topology_json(topo_); }
     bool has_multicast() const override { return pool_.mc_base != nullptr; }
     uint64_t launches() const override { return launches_; }
     bool set_param(const char* name, int value) override;
@@ -86,6 +88,9 @@ public:
     void stamp_end(cudaStream_t s, uint64_t coll) { stamp(s, TT_DEVICE_KERNEL_END, coll); }
 private:
 
+    /** Every rank describes its GPU and its view of the peers' GPUs; all ranks end with the same table. */
+    bool discover_topology(std::string* err);
+    Topology topo_;
     Bootstrap* bs_;
     int dev_, rank_, n_;
     SymAllocator* sym_ = nullptr;

@@ -34,6 +34,7 @@ def _declare(lib):
         "dccl_comm_init_rank": (i, [c.POINTER(vp), i, vp, i]),
         "dccl_comm_finalize": (i, [vp]),
         "dccl_comm_abort": (i, [vp]),
+        "dccl_topology_json": (i, [vp, cp, sz]),
         "dccl_selftest_fd_exchange": (i, [vp]),
         "dccl_comm_shrink": (i, [vp, c.POINTER(vp)]),
         "dccl_world_size": (i, [vp]),
@@ -89,6 +90,7 @@ def _declare(lib):
         "dccl_emu_collective": (i, [cp, cp, i, i, i, sz, i, i, i, sz, i, sz, vp, vp]),
         "dccl_emu_sendrecv_ring": (i, [i, sz, i, i, i, vp, vp]),
         "dccl_emu_wait_probe": (i, [c.c_uint, c.POINTER(c.c_float)]),
+        "dccl_nvml_link_report": (i, [cp, cp, sz]),
         "dccl_emu_set_device_seq": (None, [i]),
         "dccl_emu_set_peer_buffers": (None, [i]),
         "dccl_emu_switch_single": (i, [i, i, sz, i, i, vp, vp]),

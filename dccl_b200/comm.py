@@ -178,6 +178,13 @@ class Communicator:
     def launches(self):
         return int(lib().dccl_launch_count(self._h))
 
+    def topology(self):
+        """The box as the communicator found it: {"nranks", "gpus": [...], "peer_access": [[...]], "peer_atomics": [[...]]}."""
+        import json
+        buf = ctypes.create_string_buffer(16384)
+        _check(lib().dccl_topology_json(self._h, buf, len(buf)), "dcclGetTopology")
+        return json.loads(buf.value.decode())
+
     def set_param(self, name, value):
         """Tuning knob for sweeps: ctas (0 = table), threads, unroll, p2p_ctas."""
         _check(lib().dccl_comm_set_param(self._h, name.encode(), int(value)), "set_param")

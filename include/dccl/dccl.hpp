@@ -238,6 +238,14 @@ ncclResult_t  dcclScatter(const void* sendbuff, void* recvbuff, size_t count, nc
  */
 ncclResult_t  dcclSetAlgorithm(ncclComm_t comm, const char* collective, const char* name);
 
+/**
+ * The box as the communicator found it, as one JSON object: per rank the GPU (name, PCI address, SMs, memory,
+ * multicast support, NVLink links up and how many of them end in a switch; -1 where NVML was not available),
+ * and the matrices "peer_access" / "peer_atomics" (1 yes, 0 no, 2 same GPU, 255 not visible to that process).
+ * Needs the device side (ncclInvalidUsage before a device was bound). The text is cut to len - 1 characters.
+ */
+ncclResult_t  dcclGetTopology(ncclComm_t comm, char* json, size_t len);
+
 /** Name of the variant the last call of `collective` used (for tools and tests). */
 const char*   dcclGetLastAlgorithm(ncclComm_t comm, const char* collective);
 

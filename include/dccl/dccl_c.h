@@ -36,6 +36,8 @@ int dccl_has_multicast(void* comm);
 unsigned long long dccl_launch_count(void* comm);
 int dccl_comm_set_param(void* comm, const char* name, int value);
 int dccl_cuda_device_count(void);
+int dccl_topology_json(void* comm, char* out, size_t len);         /* GPUs, peer access, NVLink links, multicast */
+int dccl_nvml_link_report(const char* nvml_library, char* out, size_t len);   /* NVML only; CUDA builds */
 
 /* memory */
 int dccl_register(void* comm, void* buf, size_t size);

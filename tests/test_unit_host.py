@@ -200,3 +200,43 @@ def test_launcher_command_line():
     p = subprocess.run([sys.executable, "-m", "dccl_b200.utils.launch", "-n", "2", "--", "/bin/sh", "-c", "exit $DCCL_RANK"],
                        cwd=root, capture_output=True, text=True, timeout=60)
     assert p.returncode == 1
+
+
+def test_nvlink_report_against_a_fake_nvml(dccl_lib, tmp_path):
+    """The NVML side of the topology discovery (read-only queries, library loaded at run time) against tests/fakes/fake_nvml.c."""
+    import json
+    import subprocess
+    if not hasattr(dccl_lib, "dccl_nvml_link_report"):
+        pytest.skip("host-only build")
+    here = os.path.dirname(os.path.abspath(__file__))
+    so = str(tmp_path / "libfake_nvml.so")
+    subprocess.run(["gcc", "-shared", "-fPIC", "-o", so, os.path.join(here, "fakes", "fake_nvml.c")], check=True)
+    buf = ctypes.create_string_buffer(4096)
+    assert dccl_lib.dccl_nvml_link_report(so.encode(), buf, len(buf)) == 0, buf.value
+    rep = json.loads(buf.value.decode())
+    assert [g["nvlinks_active"] for g in rep["gpus"]] == [18, 17]
+    assert [g["nvlinks_to_switch"] for g in rep["gpus"]] == [18, 17]
+    assert rep["gpus"][0]["name"] == "Fake B200 #0" and rep["gpus"][1]["nvlink_version"] == 7
+    # a library that is not there is an answer, not a crash
+    assert dccl_lib.dccl_nvml_link_report(str(tmp_path / "missing.so").encode(), buf, len(buf)) == -1
+    assert b"cannot load" in buf.value
+
+
+def test_topology_tool_without_a_gpu(build_dir, tmp_path):
+    """dccl_topo on a machine without a usable driver: an empty table, and the NVML view through the fake library."""
+    import json
+    import subprocess
+    tool = os.path.join(build_dir, "dccl_topo")
+    if not os.path.exists(tool):
+        pytest.skip("host-only build")
+    from conftest import gpu_count
+    out = json.loads(subprocess.run([tool], capture_output=True, text=True, timeout=60, check=True).stdout)
+    if gpu_count() == 0:
+        assert out["summary"] == "no CUDA devices" and out["topology"]["nranks"] == 0
+    else:
+        assert out["topology"]["nranks"] == min(gpu_count(), 8)
+    here = os.path.dirname(os.path.abspath(__file__))
+    so = str(tmp_path / "libfake_nvml.so")
+    subprocess.run(["gcc", "-shared", "-fPIC", "-o", so, os.path.join(here, "fakes", "fake_nvml.c")], check=True)
+    rep = json.loads(subprocess.run([tool, "--nvml", so], capture_output=True, text=True, timeout=60, check=True).stdout)
+    assert len(rep["gpus"]) == 2 and rep["gpus"][1]["nvlinks_active"] == 17

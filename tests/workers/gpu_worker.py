@@ -92,6 +92,13 @@ def main():
         print("OK %d multicast=1 launches=%d" % (cases, launches))
         return
 
+    # what the communicator found out about the box
+    topo = comm.topology()
+    check(topo["nranks"] == world and len(topo["gpus"]) == world, "topology: one entry per rank")
+    check(all(g["sm_count"] > 0 and g["mem_bytes"] > 0 and g["pci"] for g in topo["gpus"]), "topology: GPU facts")
+    check(all(topo["peer_access"][a][b] in (1, 255) for a in range(world) for b in range(world) if a != b), "topology: peers reachable")
+    check(all(bool(g["multicast"]) == comm.has_multicast for g in topo["gpus"]) or not comm.has_multicast, "topology: multicast flag")
+
     algos = ["oneshot", "twoshot", "twoshot_ll", "ring", "rabenseifner"] + (["nvls"] if comm.has_multicast else [])
     if args.suite == "basic":
         names, counts = ["float32", "bfloat16", "int32", "float16"], [1, 1000, 16384, 300001, 4 << 20]
