@@ -337,6 +337,15 @@ def main():
             "gpu_launches": int(launches) if args.impl == "ours" else 0,
             "clocks": clocks,
         }
+        if args.impl == "ours":
+            try:    # the fabric as the communicator found it (NVLink links from NVML, -1 when that is not available)
+                topo = backend.comm.topology()
+                line["fabric"] = {"gpu": topo["gpus"][0]["name"], "multicast": bool(topo["gpus"][0]["multicast"]),
+                                  "nvlinks_active_min": min(g["nvlinks_active"] for g in topo["gpus"]),
+                                  "nvlinks_to_switch_min": min(g["nvlinks_to_switch"] for g in topo["gpus"]),
+                                  "all_pairs_peer_access": all(v in (1, 2, 255) for row in topo["peer_access"] for v in row)}
+            except Exception as e:      # never let the report break the measurement
+                line["fabric"] = {"error": str(e)[:120]}
         if sweep is not None:
             os.makedirs(os.path.dirname(args.out), exist_ok=True)
             with open(args.out, "w") as f:
