@@ -42,3 +42,22 @@ def test_messages_larger_than_staging_are_chunked():
 def test_peer_handles_fallback_without_multicast():
     """cudaIpc handles instead of cuMem descriptors: no multicast, peer loads / stores only."""
     run(2, ["--suite", "chunk"], env={"DCCL_POOL_MODE": "ipc", "DCCL_STAGING_BYTES": str(16 << 20)})
+
+
+# Paths that exist and are tested on the host or in the single-GPU emulation but have not yet run on several GPUs.
+# They are kept apart, and a failure is reported as an expected one, so that a first run on hardware cannot hide the
+# results of the suites above; the marks go away with the first clean run.
+FIRST_RUN = pytest.mark.xfail(reason="first run of this path on several GPUs", strict=False)
+
+
+@FIRST_RUN
+@pytest.mark.skipif(gpu_count() < 2, reason="needs two GPUs")
+def test_topology_packets_two_shot_and_composed_collectives():
+    """dcclGetTopology, the two-shot packet all-reduce / reduce, all-to-all / gather / scatter on device buffers."""
+    run(min(gpu_count(), 8), ["--suite", "extra"])
+
+
+@FIRST_RUN
+@pytest.mark.skipif(gpu_count() < 2, reason="needs two GPUs")
+def test_pipelined_switch_broadcast_and_reduce():
+    run(min(gpu_count(), 8), ["--suite", "rooted"])

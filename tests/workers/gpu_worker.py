@@ -92,16 +92,19 @@ def main():
         print("OK %d multicast=1 launches=%d" % (cases, launches))
         return
 
-    # what the communicator found out about the box
-    topo = comm.topology()
-    check(topo["nranks"] == world and len(topo["gpus"]) == world, "topology: one entry per rank")
-    check(all(g["sm_count"] > 0 and g["mem_bytes"] > 0 and g["pci"] for g in topo["gpus"]), "topology: GPU facts")
-    check(all(topo["peer_access"][a][b] in (1, 255) for a in range(world) for b in range(world) if a != b), "topology: peers reachable")
-    check(all(bool(g["multicast"]) == comm.has_multicast for g in topo["gpus"]) or not comm.has_multicast, "topology: multicast flag")
+    if args.suite == "extra":
+        # what the communicator found out about the box
+        topo = comm.topology()
+        check(topo["nranks"] == world and len(topo["gpus"]) == world, "topology: one entry per rank")
+        check(all(g["sm_count"] > 0 and g["mem_bytes"] > 0 and g["pci"] for g in topo["gpus"]), "topology: GPU facts")
+        check(all(topo["peer_access"][a][b] in (1, 255) for a in range(world) for b in range(world) if a != b), "topology: peers reachable")
+        check(all(bool(g["multicast"]) == comm.has_multicast for g in topo["gpus"]) or not comm.has_multicast, "topology: multicast flag")
 
-    algos = ["oneshot", "twoshot", "twoshot_ll", "ring", "rabenseifner"] + (["nvls"] if comm.has_multicast else [])
+    algos = ["oneshot", "twoshot", "ring", "rabenseifner"] + (["nvls"] if comm.has_multicast else [])
     if args.suite == "basic":
         names, counts = ["float32", "bfloat16", "int32", "float16"], [1, 1000, 16384, 300001, 4 << 20]
+    elif args.suite == "extra":   # the two-shot packet variant, up to its capacity and beyond (falls back to the staged form)
+        algos, names, counts = ["twoshot_ll"], ["float32", "bfloat16", "int32"], [1, 1000, 16384, 300001, 4 << 20]
     else:   # chunking: staging is made small through DCCL_STAGING_BYTES by the caller
         names, counts = ["float32", "bfloat16"], [3 << 20, (8 << 20) + 12345]
     for name in names:
@@ -125,7 +128,7 @@ def main():
                 comm.set_algorithm("allreduce", "auto")
                 # reduce to both ends
                 for root in {0, world - 1}:
-                    for algo in ["twoshot", "oneshot"] + (["nvls"] if comm.has_multicast else []):
+                    for algo in (["twoshot_ll"] if args.suite == "extra" else ["twoshot", "oneshot"] + (["nvls"] if comm.has_multicast else [])):
                         comm.set_algorithm("reduce", algo)
                         s = to_torch(ins[rank], name, dev)
                         r = torch.zeros_like(s)
@@ -262,7 +265,7 @@ def main():
     torch.cuda.synchronize()
 
     # all-to-all, gather, scatter on device buffers: one launch of grouped sends / receives plus the own block
-    if args.suite == "basic":
+    if args.suite == "extra":
         for n_el in [1, 1000, (3 << 20) + 5]:      # the largest is longer than the 4 x 1 MB FIFO of a pair
             src = [torch.arange(n_el * world, dtype=torch.float32) + 1e6 * r for r in range(world)]
             mine = src[rank].to(dev)

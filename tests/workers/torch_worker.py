@@ -22,6 +22,7 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--cuda", action="store_true")
     ap.add_argument("--ddp", action="store_true")
+    ap.add_argument("--extra", action="store_true", help="all-to-all / gather / scatter, list forms, batch_isend_irecv, objects, subgroups")
     args = ap.parse_args()
     rank, world = int(os.environ["DCCL_RANK"]), int(os.environ["DCCL_WORLD_SIZE"])
     port = int(os.environ["DCCL_MASTER_PORT"]) + 1
@@ -69,32 +70,33 @@ def main():
             out = torch.empty(n, dtype=dtype, device=dev)
             dist.reduce_scatter_tensor(out, big[rank])
             check(torch.allclose(out.double(), wantrs, **tol), "reduce_scatter_tensor %s %d" % (dtype, n))
-    # all-to-all, gather, scatter (grouped send / recv underneath)
-    for dtype in (torch.float32, torch.int64):
-        for n in (1, 257, 300001):
-            ins = [tensor_for(200 + r, n * world, dtype, dev) for r in range(world)]
-            out = torch.empty(n * world, dtype=dtype, device=dev)
-            dist.all_to_all_single(out, ins[rank])
-            want = torch.cat([ins[p][rank * n:(rank + 1) * n] for p in range(world)])
-            check(torch.equal(out, want), "all_to_all_single %s %d" % (dtype, n))
-            outs = [torch.empty(n, dtype=dtype, device=dev) for _ in range(world)]
-            dist.all_to_all(outs, list(ins[rank].split(n)))
-            check(torch.equal(torch.cat(outs), want), "all_to_all %s %d" % (dtype, n))
-            for root in {0, world - 1}:
-                lst = [torch.empty(n, dtype=dtype, device=dev) for _ in range(world)] if rank == root else None
-                dist.gather(ins[rank][:n], lst, dst=root)
-                check(rank != root or all(torch.equal(lst[p], ins[p][:n]) for p in range(world)), "gather %s %d root %d" % (dtype, n, root))
-                got = torch.empty(n, dtype=dtype, device=dev)
-                dist.scatter(got, list(ins[root].split(n)) if rank == root else None, src=root)
-                check(torch.equal(got, ins[root][rank * n:(rank + 1) * n]), "scatter %s %d root %d" % (dtype, n, root))
-    # uneven splits: rank r sends (p + 1) rows of 3 to rank p and receives (r + 1) rows from everybody
-    rows_in = sum(p + 1 for p in range(world))
-    src = (torch.arange(rows_in * 3, dtype=torch.float32) + 1000 * rank).reshape(rows_in, 3).to(dev)
-    dst = torch.empty(((rank + 1) * world, 3), dtype=torch.float32, device=dev)
-    dist.all_to_all_single(dst, src, output_split_sizes=[rank + 1] * world, input_split_sizes=[p + 1 for p in range(world)])
-    off = sum(p + 1 for p in range(rank)) * 3
-    want = torch.cat([(torch.arange(off, off + (rank + 1) * 3, dtype=torch.float32) + 1000 * p).reshape(rank + 1, 3) for p in range(world)]).to(dev)
-    check(torch.equal(dst, want), "all_to_all_single with uneven splits")
+    if args.extra:
+        # all-to-all, gather, scatter (grouped send / recv underneath)
+        for dtype in (torch.float32, torch.int64):
+            for n in (1, 257, 300001):
+                ins = [tensor_for(200 + r, n * world, dtype, dev) for r in range(world)]
+                out = torch.empty(n * world, dtype=dtype, device=dev)
+                dist.all_to_all_single(out, ins[rank])
+                want = torch.cat([ins[p][rank * n:(rank + 1) * n] for p in range(world)])
+                check(torch.equal(out, want), "all_to_all_single %s %d" % (dtype, n))
+                outs = [torch.empty(n, dtype=dtype, device=dev) for _ in range(world)]
+                dist.all_to_all(outs, list(ins[rank].split(n)))
+                check(torch.equal(torch.cat(outs), want), "all_to_all %s %d" % (dtype, n))
+                for root in {0, world - 1}:
+                    lst = [torch.empty(n, dtype=dtype, device=dev) for _ in range(world)] if rank == root else None
+                    dist.gather(ins[rank][:n], lst, dst=root)
+                    check(rank != root or all(torch.equal(lst[p], ins[p][:n]) for p in range(world)), "gather %s %d root %d" % (dtype, n, root))
+                    got = torch.empty(n, dtype=dtype, device=dev)
+                    dist.scatter(got, list(ins[root].split(n)) if rank == root else None, src=root)
+                    check(torch.equal(got, ins[root][rank * n:(rank + 1) * n]), "scatter %s %d root %d" % (dtype, n, root))
+        # uneven splits: rank r sends (p + 1) rows of 3 to rank p and receives (r + 1) rows from everybody
+        rows_in = sum(p + 1 for p in range(world))
+        src = (torch.arange(rows_in * 3, dtype=torch.float32) + 1000 * rank).reshape(rows_in, 3).to(dev)
+        dst = torch.empty(((rank + 1) * world, 3), dtype=torch.float32, device=dev)
+        dist.all_to_all_single(dst, src, output_split_sizes=[rank + 1] * world, input_split_sizes=[p + 1 for p in range(world)])
+        off = sum(p + 1 for p in range(rank)) * 3
+        want = torch.cat([(torch.arange(off, off + (rank + 1) * 3, dtype=torch.float32) + 1000 * p).reshape(rank + 1, 3) for p in range(world)]).to(dev)
+        check(torch.equal(dst, want), "all_to_all_single with uneven splits")
     # point to point: even ranks send to the next odd rank
     if world >= 2:
         msg = torch.full((5000,), float(rank), device=dev)
@@ -105,56 +107,57 @@ def main():
             check(bool((msg == float(rank - 1)).all()), "send/recv")
     dist.barrier()
 
-    # list forms: reduce_scatter from a list of tensors (goes through a temporary), product and min
-    parts = [torch.full((257,), float(rank + 1 + p), device=dev) for p in range(world)]
-    out = torch.empty(257, device=dev)
-    dist.reduce_scatter(out, parts)
-    check(bool((out == float(sum(r + 1 + rank for r in range(world)))).all()), "reduce_scatter (list)")
-    t = torch.full((33,), float(rank + 1), device=dev, dtype=torch.float64)
-    dist.all_reduce(t, op=dist.ReduceOp.PRODUCT)
-    want = 1.0
-    for r in range(world):
-        want *= r + 1
-    check(bool((t == want).all()), "all_reduce product")
-    t = torch.full((33,), rank + 5, device=dev, dtype=torch.int32)
-    dist.all_reduce(t, op=dist.ReduceOp.MIN)
-    check(bool((t == 5).all()), "all_reduce min")
+    if args.extra:
+        # list forms: reduce_scatter from a list of tensors (goes through a temporary), product and min
+        parts = [torch.full((257,), float(rank + 1 + p), device=dev) for p in range(world)]
+        out = torch.empty(257, device=dev)
+        dist.reduce_scatter(out, parts)
+        check(bool((out == float(sum(r + 1 + rank for r in range(world)))).all()), "reduce_scatter (list)")
+        t = torch.full((33,), float(rank + 1), device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.PRODUCT)
+        want = 1.0
+        for r in range(world):
+            want *= r + 1
+        check(bool((t == want).all()), "all_reduce product")
+        t = torch.full((33,), rank + 5, device=dev, dtype=torch.int32)
+        dist.all_reduce(t, op=dist.ReduceOp.MIN)
+        check(bool((t == 5).all()), "all_reduce min")
 
-    # batch_isend_irecv: a ring in which everybody sends first, with messages longer than a FIFO; one grouped launch
-    if world >= 2:
-        big = torch.full((1 << 20,), float(rank), device=dev)          # 4 MB
-        got = torch.empty_like(big)
-        works = dist.batch_isend_irecv([dist.P2POp(dist.isend, big, (rank + 1) % world), dist.P2POp(dist.irecv, got, (rank - 1) % world)])
-        for w in works:
-            w.wait()
-        if args.cuda:
-            torch.cuda.synchronize()
-        check(bool((got == float((rank - 1) % world)).all()), "batch_isend_irecv ring")
+        # batch_isend_irecv: a ring in which everybody sends first, with messages longer than a FIFO; one grouped launch
+        if world >= 2:
+            big = torch.full((1 << 20,), float(rank), device=dev)          # 4 MB
+            got = torch.empty_like(big)
+            works = dist.batch_isend_irecv([dist.P2POp(dist.isend, big, (rank + 1) % world), dist.P2POp(dist.irecv, got, (rank - 1) % world)])
+            for w in works:
+                w.wait()
+            if args.cuda:
+                torch.cuda.synchronize()
+            check(bool((got == float((rank - 1) % world)).all()), "batch_isend_irecv ring")
 
-    # Python objects ride on byte tensors: broadcast_object_list, all_gather_object
-    objs = [{"from": rank, "payload": list(range(rank + 3))}]
-    dist.broadcast_object_list(objs, src=world - 1, device=dev)
-    check(objs[0] == {"from": world - 1, "payload": list(range(world + 2))}, "broadcast_object_list")
-    gathered = [None] * world
-    dist.all_gather_object(gathered, ("rank", rank))
-    check(gathered == [("rank", r) for r in range(world)], "all_gather_object")
+        # Python objects ride on byte tensors: broadcast_object_list, all_gather_object
+        objs = [{"from": rank, "payload": list(range(rank + 3))}]
+        dist.broadcast_object_list(objs, src=world - 1, device=dev)
+        check(objs[0] == {"from": world - 1, "payload": list(range(world + 2))}, "broadcast_object_list")
+        gathered = [None] * world
+        dist.all_gather_object(gathered, ("rank", rank))
+        check(gathered == [("rank", r) for r in range(world)], "all_gather_object")
 
-    # subgroups: every rank calls new_group, only the members get a communicator; then a second world-wide group
-    if world >= 3:
-        members = list(range(0, world, 2))
-        evens = dist.new_group(ranks=members)
-        t = torch.full((1000,), float(rank), device=dev)
-        if rank in members:
-            dist.all_reduce(t, group=evens)
-            check(bool((t == float(sum(members))).all()), "all_reduce in a subgroup")
-            out = torch.empty(len(members), device=dev)
-            dist.all_gather_into_tensor(out, torch.tensor([float(rank)], device=dev), group=evens)
-            check(out.tolist() == [float(m) for m in members], "all_gather in a subgroup")
-        again = dist.new_group(ranks=list(range(world)))
-        t = torch.full((10,), 1.0, device=dev)
-        dist.all_reduce(t, group=again)
-        check(bool((t == float(world)).all()), "all_reduce in a second world-wide group")
-        dist.barrier()
+        # subgroups: every rank calls new_group, only the members get a communicator; then a second world-wide group
+        if world >= 3:
+            members = list(range(0, world, 2))
+            evens = dist.new_group(ranks=members)
+            t = torch.full((1000,), float(rank), device=dev)
+            if rank in members:
+                dist.all_reduce(t, group=evens)
+                check(bool((t == float(sum(members))).all()), "all_reduce in a subgroup")
+                out = torch.empty(len(members), device=dev)
+                dist.all_gather_into_tensor(out, torch.tensor([float(rank)], device=dev), group=evens)
+                check(out.tolist() == [float(m) for m in members], "all_gather in a subgroup")
+            again = dist.new_group(ranks=list(range(world)))
+            t = torch.full((10,), 1.0, device=dev)
+            dist.all_reduce(t, group=again)
+            check(bool((t == float(world)).all()), "all_reduce in a second world-wide group")
+            dist.barrier()
 
     if args.ddp:
         # DistributedDataParallel over the backend: gradients must equal the average of the per-rank gradients
