@@ -86,10 +86,11 @@ bool GpuCommImpl::init(std::string* err) {
     dc_.timeout_ns = (unsigned long long)cfg.get_int("DCCL/timeout_ms", 5000) * 1000000ull;
     dc_.stage_bytes = stage_bytes_;
 
-    {   // collective: also a rank whose set-up failed above takes part, or its peers would wait for it
+    if (cfg.get_bool("DCCL/topology", true)) {
+        // collective (every rank reads the same key): also a rank whose set-up failed above takes part, or its peers
+        // would wait for it. The table is a report; nothing else depends on it, so a failure here is only logged.
         std::string terr;
-        const bool tok = discover_topology(&terr);
-        if (!tok && ok && n_ > 1) { ok = false; if (err && err->empty()) *err = terr; }   // a world of one can live without it
+        if (!discover_topology(&terr)) dccl_warn("topology discovery incomplete: %s", terr.c_str());
     }
     if (n_ == 1) return ok;   // a world of one needs no pool: every collective is a local copy
 
@@ -179,7 +180,7 @@ bool GpuCommImpl::discover_topology(std::string* err) {
     if (rank_ == 0) dccl_info("topology: %s", topology_summary(topo_).c_str());
     if (blocked) dccl_warn("some GPU pairs report no peer access; mapping the pools will show whether they can be reached");
     for (int a = 0; a < n_; a++) if (topo_.gpu[a].device < 0) { if (err) *err = "rank " + std::to_string(a) + " could not describe its GPU"; return false; }
-    return true;
+    return true;   // (the caller only logs a failure: the table is a report)
 }
 
 /* ---------------- where the sequence number lives ---------------- */
