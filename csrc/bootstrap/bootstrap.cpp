@@ -562,20 +562,39 @@ bool Bootstrap::recv_fd(int peer, uint32_t tag, int* fd, int timeout_ms) {
             if (aborted() || now_ms() > deadline) { err_ = "timed out waiting for a handle from rank " + std::to_string(peer); return false; }
             continue;
         }
-        uint32_t body[2] = {0, 0};
-        struct iovec iov = {body, sizeof(body)};
-        char cbuf[CMSG_SPACE(sizeof(int))];
-        struct msghdr msg;
-        memset(&msg, 0, sizeof(msg));
-        msg.msg_iov = &iov; msg.msg_iovlen = 1;
-        msg.msg_control = cbuf; msg.msg_controllen = sizeof(cbuf);
-        ssize_t r = ::recvmsg(usock_, &msg, 0);
-        if (r < (ssize_t)sizeof(body)) continue;
-        struct cmsghdr* cm = CMSG_FIRSTHDR(&msg);
-        if (!cm || cm->cmsg_type != SCM_RIGHTS) continue;
-        int got;
-        memcpy(&got, CMSG_DATA(cm), sizeof(int));
-        pending_fds_.push_back({(int)body[0], body[1], got});
+        pull_fd();
+    }
+}
+
+/** Take one datagram off the descriptor socket and park its descriptor in pending_fds_. */
+void Bootstrap::pull_fd() {
+    uint32_t body[2] = {0, 0};
+    struct iovec iov = {body, sizeof(body)};
+    char cbuf[CMSG_SPACE(sizeof(int))];
+    struct msghdr msg;
+    memset(&msg, 0, sizeof(msg));
+    msg.msg_iov = &iov; msg.msg_iovlen = 1;
+    msg.msg_control = cbuf; msg.msg_controllen = sizeof(cbuf);
+    ssize_t r = ::recvmsg(usock_, &msg, MSG_DONTWAIT);
+    if (r < (ssize_t)sizeof(body)) return;
+    struct cmsghdr* cm = CMSG_FIRSTHDR(&msg);
+    if (!cm || cm->cmsg_type != SCM_RIGHTS) return;
+    int got;
+    memcpy(&got, CMSG_DATA(cm), sizeof(int));
+    pending_fds_.push_back({(int)body[0], body[1], got});
+}
+
+void Bootstrap::discard_fds(uint32_t tag) {
+    while (usock_ >= 0) {   // whatever has arrived by now, without waiting
+        struct pollfd pf = {usock_, POLLIN, 0};
+        if (::poll(&pf, 1, 0) <= 0) break;
+        const size_t before = pending_fds_.size();
+        pull_fd();
+        if (pending_fds_.size() == before) break;
+    }
+    for (auto it = pending_fds_.begin(); it != pending_fds_.end();) {
+        if (it->tag == tag) { ::close(it->fd); it = pending_fds_.erase(it); }
+        else ++it;
     }
 }
 

@@ -98,6 +98,9 @@ public:
 
     bool send_fd(int peer, int fd, uint32_t tag);
     bool recv_fd(int peer, uint32_t tag, int* fd, int timeout_ms);
+    /** Close every descriptor with this tag that has arrived but was not asked for (an exchange that was called off
+     *  after some ranks had already sent). Call it after the ranks have agreed to give up: all sends precede that. */
+    void discard_fds(uint32_t tag);
 
     /* liveness */
     CtlSegment* ctl() { return ctl_; }
@@ -127,6 +130,7 @@ private:
     void watchdog_loop();
     bool map_segments(std::string* err);
     void fault_hook(const char* where);
+    void pull_fd();
 
     int rank_ = -1, world_ = 0;
     uint64_t token_ = 0;

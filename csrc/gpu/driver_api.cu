@@ -19,8 +19,16 @@ static bool resolve(const char* name, F* out) {
     return true;
 }
 
+static const DriverApi* g_override = nullptr;
+
+void set_driver_api_override(const DriverApi* api) {
+    std::lock_guard<std::mutex> g(g_mu);
+    g_override = api;
+}
+
 const DriverApi* driver_api(std::string* err) {
     std::lock_guard<std::mutex> g(g_mu);
+    if (g_override) return g_override;
     if (!g_tried) {
         g_tried = true;
         int n = 0;

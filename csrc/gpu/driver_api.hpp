@@ -37,6 +37,8 @@ struct DriverApi {
 
 /** Resolved once per process; null when the CUDA runtime cannot reach a driver. */
 const DriverApi* driver_api(std::string* err);
+/** Tests only: make driver_api() hand out `api` (a stand-in for the driver) until called again with nullptr. */
+void set_driver_api_override(const DriverApi* api);
 std::string cu_error(const DriverApi* d, CUresult r);
 
 } // namespace dccl

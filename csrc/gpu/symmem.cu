@@ -85,6 +85,7 @@ bool SymAllocator::alloc_vmm(size_t bytes, bool want_mc, SymSegment* seg, std::s
     // hand my descriptor to every peer, then collect theirs
     if (ok) for (int k = 1; k < n_ && ok; k++) if (!bs_->send_fd((rank_ + k) % n_, fd, tag)) { ok = false; why = "send_fd: " + bs_->last_error(); }
     if (!agree(ok)) {   // nobody waits for a descriptor that will not come
+        bs_->discard_fds(tag);   // ... and the descriptors that did come are not left lying around for a later exchange
         if (fd >= 0) ::close(fd);
         if (seg->handles[rank_]) { d_->MemRelease(seg->handles[rank_]); seg->handles[rank_] = 0; }
         if (err) *err = why.empty() ? "a peer could not create or export its segment" : why;
@@ -111,6 +112,7 @@ bool SymAllocator::alloc_vmm(size_t bytes, bool want_mc, SymSegment* seg, std::s
         if ((r = d_->MemSetAccess(va, size, &acc, 1)) != CUDA_SUCCESS) { ok = false; why = "set access (peer " + std::to_string(p) + "): " + cu_error(d_, r); break; }
     }
     if (!agree(ok)) {
+        bs_->discard_fds(tag);
         SymSegment tmp = *seg;
         tmp.mc_handle = 0;
         // local teardown only: free() would run a barrier the failing path must not depend on
@@ -151,6 +153,7 @@ bool SymAllocator::bind_multicast(SymSegment* seg, std::string* err) {
     // learn whether rank 0 managed before anybody blocks on a descriptor
     unsigned char root_ok = ok ? 1 : 0;
     if (!bs_->broadcast(&root_ok, 1, 0) || !root_ok) {
+        bs_->discard_fds(tag);
         if (seg->mc_handle) { d_->MemRelease(seg->mc_handle); seg->mc_handle = 0; }
         if (err) *err = why.empty() ? "rank 0 could not create the multicast object" : why;
         return false;
@@ -166,7 +169,7 @@ bool SymAllocator::bind_multicast(SymSegment* seg, std::string* err) {
     }
     if (ok && (r = d_->MulticastAddDevice(seg->mc_handle, cu)) != CUDA_SUCCESS) { ok = false; why = "cuMulticastAddDevice: " + cu_error(d_, r); }
     // binding blocks until every device was added, so agree first
-    if (!agree(ok)) { drop_multicast(seg); if (err) *err = why.empty() ? "a peer could not join the multicast object" : why; return false; }
+    if (!agree(ok)) { bs_->discard_fds(tag); drop_multicast(seg); if (err) *err = why.empty() ? "a peer could not join the multicast object" : why; return false; }
     if ((r = d_->MulticastBindMem(seg->mc_handle, 0, seg->handles[rank_], 0, seg->size, 0)) != CUDA_SUCCESS) { ok = false; why = "cuMulticastBindMem: " + cu_error(d_, r); }
     else seg->mc_bound = true;
     if (ok) {

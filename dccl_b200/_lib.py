@@ -91,6 +91,7 @@ def _declare(lib):
         "dccl_emu_sendrecv_ring": (i, [i, sz, i, i, i, vp, vp]),
         "dccl_emu_wait_probe": (i, [c.c_uint, c.POINTER(c.c_float)]),
         "dccl_nvml_link_report": (i, [cp, cp, sz]),
+        "dccl_selftest_symmem": (i, [vp, i]),
         "dccl_emu_set_device_seq": (None, [i]),
         "dccl_emu_set_peer_buffers": (None, [i]),
         "dccl_emu_switch_single": (i, [i, i, sz, i, i, vp, vp]),

@@ -161,6 +161,13 @@ def main():
     from dccl_b200._lib import lib as _native
     check(_native().dccl_selftest_fd_exchange(comm._h) == 0, "descriptor exchange between all ranks")
 
+    # the symmetric allocator over a stand-in driver (memfd + mmap): every rank maps every peer's segment and reads it;
+    # then with one rank's allocation failing: everybody must come back with a failure, nobody may hang
+    if hasattr(_native(), "dccl_selftest_symmem") and world <= 8:
+        check(_native().dccl_selftest_symmem(comm._h, -1) == 0, "symmetric allocator: segments of all ranks mapped and readable")
+        check(_native().dccl_selftest_symmem(comm._h, world - 1) == 0, "symmetric allocator: a failing rank fails everybody")
+        check(_native().dccl_selftest_symmem(comm._h, -1) == 0, "symmetric allocator: works again afterwards")
+
     # all-to-all (equal and uneven blocks), gather, scatter
     for n in [1, 1000, 400001]:
         src = [np.arange(n * world, dtype=np.float64) + 1e6 * r for r in range(world)]
