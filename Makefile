@@ -4,6 +4,8 @@
 #   make CUDA=0          host-only library (no nvcc needed; device calls are refused)
 #   make SANITIZE=address|thread|undefined CXX=/usr/bin/g++ CC=/usr/bin/gcc   instrument the host code (host-only build;
 #                        a compiler wrapper that links statically may lack the sanitizer runtimes)
+#   make BOUNDS=1        debug build of the device code in build-bounds/: every kernel checks the pool ranges it is
+#                        about to use and reports DEV_BOUNDS instead of touching memory outside them
 #   make install PREFIX=/opt/dccl         headers, library, tools, CMake package file
 #
 # Everything lands in build/; the shared library is also copied into the Python
@@ -28,6 +30,10 @@ NVCCFLAGS := -std=c++17 -O3 -lineinfo -gencode arch=compute_100a,code=sm_100a -X
              -DCACHELINE_SIZE=$(CACHELINE) -DENABLE_EVALUATION=1 -DDCCL_WITH_CUDA_RUNTIME
 ifdef PTXAS_V
 NVCCFLAGS += -Xptxas -v
+endif
+ifdef BOUNDS
+NVCCFLAGS += -DDCCL_DEBUG_BOUNDS
+BUILD := build-bounds
 endif
 ifdef SANITIZE
 CUDA := 0

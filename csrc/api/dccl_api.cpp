@@ -477,6 +477,19 @@ ncclResult_t dcclGetTopology(ncclComm_t comm, char* json, size_t len) {
     return ncclSuccess;
 }
 
+ncclResult_t dcclDebugCheck(ncclComm_t comm) {
+    VALIDATE_COMM(comm);
+    if (!comm->gpu) return ncclSuccess;
+    char msg[200];
+    const ncclResult_t r = comm->gpu->debug_check(msg, sizeof(msg));
+    if (r != ncclSuccess) {
+        dccl_error("%s", msg);
+        comm->host_error = r;
+        comm->host_error_msg = msg;
+    }
+    return r;
+}
+
 /* ---------------- algorithm control ---------------- */
 
 ncclResult_t dcclSetAlgorithm(ncclComm_t comm, const char* collective, const char* name) {

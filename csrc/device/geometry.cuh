@@ -38,5 +38,11 @@ __device__ __forceinline__ T* stage_ptr(const DevComm& c, int p, int parity) {
     return reinterpret_cast<T*>(c.pool[p] + kStageOff + (size_t)parity * c.stage_bytes);
 }
 
+/** Debug build (DCCL_DEBUG_BOUNDS): the kernel is about to use the first `elems` elements of a staging half.
+ *  The recorded value is the extent in KB. Always true in the normal build. */
+template <typename T>
+__device__ __forceinline__ bool stage_extent_ok(const DevComm& c, size_t elems, int site) {
+    return DCCL_BOUNDS_OK(c, elems * sizeof(T) <= c.stage_bytes, site, (elems * sizeof(T)) >> 10);
+}
 
 } // namespace dccl

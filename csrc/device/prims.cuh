@@ -194,6 +194,23 @@ __device__ __forceinline__ void report_failure(const DevComm& c, uint32_t code, 
     }
 }
 
+/**
+ * Range checks of a debug build (compile with -DDCCL_DEBUG_BOUNDS, `make BOUNDS=1`). Every kernel checks, before its
+ * first access, that the part of the pool it is about to use (staging areas, packet slots, flag rows) lies inside the
+ * region reserved for it; signal / wait check their flag row and index. A failed check records
+ * {DEV_BOUNDS, own rank, site, offending value} in the status block and the kernel returns without touching memory;
+ * nothing traps. In the normal build the macro is the constant `true` and the checks cost nothing.
+ */
+#ifdef DCCL_DEBUG_BOUNDS
+__device__ __forceinline__ bool bounds_ok(const DevComm& c, bool cond, int site, size_t value) {
+    if (!cond) report_failure(c, DEV_BOUNDS, c.rank, site, value > 0xffffffffull ? 0xffffffffu : (uint32_t)value);
+    return cond;
+}
+#define DCCL_BOUNDS_OK(c, cond, site, value) (::dccl::bounds_ok((c), (cond), (site), (size_t)(value)))
+#else
+#define DCCL_BOUNDS_OK(c, cond, site, value) (true)
+#endif
+
 /** Spin until *p has reached `val` (wrap-safe). False after timeout_ns or when the abort word is set. */
 __device__ __forceinline__ bool wait_flag_ge(const DevComm& c, const uint32_t* p, uint32_t val, int peer, int site, uint32_t seq) {
     uint32_t spins = 0;
@@ -233,11 +250,13 @@ __device__ __forceinline__ uint32_t flag_value(uint32_t seq, int idx) { return s
 __device__ __forceinline__ void signal_peer(const DevComm& c, int peer, int bid, uint32_t seq, int idx) {
     // the release store orders everything that happened before it, including the other threads' writes
     // that the preceding CTA barrier made visible to this thread; no separate fence is needed
+    if (!DCCL_BOUNDS_OK(c, bid >= 0 && bid < kMaxCtas && peer >= 0 && peer < c.nranks && idx >= 0 && idx < kFlagVals, 990, bid)) return;
     st_release_sys(flag_slot(c.pool[peer], bid, c.rank), flag_value(seq, idx));
 }
 
 /** Wait until CTA `bid` of rank `src` has signalled point `idx` of call `seq`. One thread. */
 __device__ __forceinline__ bool wait_peer(const DevComm& c, int src, int bid, uint32_t seq, int idx, int site) {
+    if (!DCCL_BOUNDS_OK(c, bid >= 0 && bid < kMaxCtas && src >= 0 && src < c.nranks && idx >= 0 && idx < kFlagVals, 991, bid)) return false;
     return wait_flag_ge(c, flag_slot(c.pool[c.rank], bid, src), flag_value(seq, idx), src, site, seq);
 }
 

@@ -14,6 +14,7 @@
 #include "../kernels/kernels.hpp"
 #include "../core/types.hpp"
 #include "gpu_comm.hpp"
+#include "canary.hpp"
 #include <cstdio>
 #include <cstring>
 #include <string>
@@ -28,6 +29,14 @@ int g_device_seq = 0;
 // set by dccl_emu_set_peer_buffers: the user buffers count as addressable by every rank (symmetric / registered
 // memory), so that the two-shot all-reduce takes its zero-copy form
 int g_peer_buffers = 0;
+// set by dccl_emu_set_guard: guard words in the unused parts of every virtual rank's pool, checked after each run
+int g_guard = 0;
+// set by dccl_emu_declare_stage_bytes (range-checking builds only): the staging size the kernels are TOLD, smaller
+// than what is allocated, so that their range checks can be seen to refuse a call while every address they could
+// compute still lies inside the allocation
+#ifdef DCCL_DEBUG_BOUNDS
+size_t g_declared_stage = 0;
+#endif
 
 // Pools of finished emulation runs, kept for the next run of the same size (the tests make thousands of short
 // runs; allocating and clearing 8 x 80 MB for each would dominate them).
@@ -79,6 +88,7 @@ struct EmuWorld {
         for (int r = 0; r < n; r++) {
             if ((pools[r] = take_pool(pool_bytes)) == nullptr) return false;
             if (!clear_pool_control(pools[r])) return false;
+            if (g_guard && !canary_fill(pools[r], canary_copy_cuda)) return false;
         }
         if (cudaMalloc((void**)&status, (ST_WORDS + 8) * sizeof(uint32_t)) != cudaSuccess) return false;
         cudaMemset(status, 0, (ST_WORDS + 8) * sizeof(uint32_t));
@@ -101,9 +111,25 @@ struct EmuWorld {
             c.abort_word = status + ST_WORDS;
             c.timeout_ns = timeout_ms * 1000000ull;
             c.stage_bytes = stage;
+#ifdef DCCL_DEBUG_BOUNDS
+            if (g_declared_stage && g_declared_stage < stage) c.stage_bytes = g_declared_stage;
+#endif
         }
         if (cudaMalloc((void**)&d_comms, n * sizeof(DevComm)) != cudaSuccess) return false;
         return cudaMemcpy(d_comms, comms.data(), n * sizeof(DevComm), cudaMemcpyHostToDevice) == cudaSuccess;
+    }
+    /** 0, or 200 + number of the damaged gap (1-based) of the first pool whose guard words were overwritten. */
+    int check_guards() const {
+        if (!g_guard) return 0;
+        for (int r = 0; r < n; r++) {
+            size_t bad = 0;
+            const int rc = canary_check(pools[r], canary_copy_cuda, &bad);
+            if (rc != 0) {
+                fprintf(stderr, "dccl emulation: guard words of virtual rank %d damaged (gap %d, pool offset %zu)\n", r, rc, bad);
+                return rc < 0 ? -5 : 200 + rc;
+            }
+        }
+        return 0;
     }
 };
 
@@ -120,6 +146,26 @@ extern "C" {
 /** 1: the emulated ranks count their calls in device memory (the mode that makes launches replayable
  *  from a CUDA graph); the launch arguments then carry a wrong sequence number on purpose. 0: host counts. */
 void dccl_emu_set_device_seq(int on) { g_device_seq = on ? 1 : 0; }
+
+/** 1: every run fills the unused parts of the virtual ranks' pools with guard words and checks them afterwards;
+ *  a run that damaged them returns 200 + the number of the gap (canary.hpp). */
+void dccl_emu_set_guard(int on) { g_guard = on ? 1 : 0; }
+
+/**
+ * Range-checking builds only (make BOUNDS=1; returns -1 otherwise and changes nothing): tell the kernels of the
+ * following runs that a staging half has `bytes` bytes although the usual, larger size is allocated (0: back to the
+ * truth). A run whose message needs more than the declared size must then come back with 100 + DEV_BOUNDS and
+ * untouched outputs: the kernels refuse before their first access.
+ */
+int dccl_emu_declare_stage_bytes(size_t bytes) {
+#ifdef DCCL_DEBUG_BOUNDS
+    g_declared_stage = bytes;
+    return 0;
+#else
+    (void)bytes;
+    return -1;
+#endif
+}
 
 /** 1: all-reduce with the two-shot variant runs its zero-copy form on the emulated ranks' user buffers. */
 void dccl_emu_set_peer_buffers(int on) { g_peer_buffers = on ? 1 : 0; }
@@ -244,6 +290,7 @@ int dccl_emu_collective(const char* kind_s, const char* algo_s, int nranks, int 
             rc = 100 + (int)st[ST_CODE];
         }
     }
+    if (rc == 0) rc = w.check_guards();
     if (rc == 0)
         for (size_t r = 0; r < n; r++)
             cudaMemcpy((char*)host_out + r * out_elems * es, ios[r].recv, out_elems * es, cudaMemcpyDeviceToHost);
@@ -303,6 +350,7 @@ int dccl_emu_sendrecv_ring(int nranks, size_t bytes, int window, int ctas_per_op
         cudaMemcpy(st, w.status, sizeof(st), cudaMemcpyDeviceToHost);
         if (st[ST_CODE] != DEV_OK) rc = 100 + (int)st[ST_CODE];
     }
+    if (rc == 0) rc = w.check_guards();
     if (rc == 0) for (size_t r = 0; r < n; r++) cudaMemcpy((char*)host_out + r * W * bytes, rb[r], W * bytes, cudaMemcpyDeviceToHost);
     for (size_t r = 0; r < n; r++) { cudaFree(sb[r]); cudaFree(rb[r]); }
     cudaFree(d_ops);

@@ -8,6 +8,7 @@
  * once per communicator, so no call allocates or registers anything.
  */
 #include "gpu_impl.hpp"
+#include "canary.hpp"
 #include "../core/config.hpp"
 #include "../core/log.hpp"
 #include <cstring>
@@ -117,6 +118,9 @@ bool GpuCommImpl::init(std::string* err) {
     if (e == cudaSuccess) e = cudaDeviceSynchronize();
     bool zero_ok = e == cudaSuccess;
     if (!zero_ok) cudaGetLastError();
+    // debug aid: guard words in the unused parts of the pool, checked at finalize and by dcclDebugCheck
+    guard_ = cfg.get_bool("DCCL/debug_bounds", false);
+    if (guard_ && zero_ok && !canary_fill(pool_.base[rank_], canary_copy_cuda)) { zero_ok = false; cudaGetLastError(); }
     for (int p = 0; p < n_; p++) dc_.pool[p] = pool_.base[p];
     dc_.mc_pool = pool_.mc_base;
     // nobody signals into a pool that is not cleared yet
@@ -133,6 +137,10 @@ GpuCommImpl::~GpuCommImpl() {
     // kernels of this communicator may still be queued on user streams
     cudaDeviceSynchronize();
     cudaGetLastError();
+    if (guard_) {
+        char msg[160];
+        if (debug_check(msg, sizeof(msg)) != ncclSuccess) dccl_error("%s", msg);
+    }
     for (auto& r : regs_)
         for (int p = 0; p < n_; p++) r.peer[p] = nullptr;
     for (auto& kv : ipc_opened_) cudaIpcCloseMemHandle(kv.second);
@@ -251,13 +259,31 @@ ncclResult_t GpuCommImpl::cuda_result(cudaError_t e, const char* what) {
     return ncclUnhandledCudaError;
 }
 
+ncclResult_t GpuCommImpl::debug_check(char* msg, size_t len) {
+    if (msg && len) msg[0] = 0;
+    if (!guard_ || !pool_.base[rank_]) return ncclSuccess;
+    DeviceGuard g(dev_);
+    size_t bad = 0;
+    const int rc = canary_check(pool_.base[rank_], canary_copy_cuda, &bad);
+    if (rc == 0) return ncclSuccess;
+    if (rc < 0) { cudaGetLastError(); if (msg && len) snprintf(msg, len, "the pool of rank %d could not be read", rank_); return ncclUnhandledCudaError; }
+    const PoolGap* gaps = nullptr;
+    pool_gaps(&gaps);
+    if (msg && len)
+        snprintf(msg, len, "rank %d: the pool was written outside its regions, first at offset %zu (the gap after %s, %zu..%zu)",
+                 rank_, bad, gaps[rc - 1].after, gaps[rc - 1].lo, gaps[rc - 1].hi);
+    return ncclInternalError;
+}
+
 ncclResult_t GpuCommImpl::async_error(char* msg, size_t len) {
     if (!status_host_) return ncclSuccess;
     volatile uint32_t* st = status_host_;
     const uint32_t code = st[ST_CODE];
     if (code == DEV_OK) return ncclSuccess;
     sticky_error_ = true;
-    if (msg && len) {
+    if (msg && len && code == DEV_BOUNDS)
+        snprintf(msg, len, "a range check failed in a kernel of rank %u (site %u, value %u)", st[ST_PEER], st[ST_SITE], st[ST_SEQ]);
+    else if (msg && len) {
         const char* what = code == DEV_TIMEOUT ? "timed out waiting for" : code == DEV_ABORTED ? "gave up (abort) waiting for" : "failed on";
         snprintf(msg, len, "a kernel %s rank %u (site %u, call %u)", what, st[ST_PEER], st[ST_SITE], st[ST_SEQ]);
     }

@@ -67,6 +67,9 @@ public:
 
     /** ncclSuccess, or the error a kernel recorded (timeout on a peer, abort). */
     virtual ncclResult_t async_error(char* msg, size_t msg_len) = 0;
+    /** With `DCCL/debug_bounds = 1`: ncclInternalError (and where) when something wrote into the unused parts of
+     *  this rank's pool; ncclSuccess otherwise and when guarding is off. Reads 32 KB from the device. */
+    virtual ncclResult_t debug_check(char* msg, size_t msg_len) = 0;
     virtual void abort(int failed_rank) = 0;
     /** Wait until every kernel this rank launched has finished (called before peers unmap memory). */
     virtual void quiesce() = 0;

@@ -52,6 +52,7 @@ public:
     ncclResult_t deregister_buffer(void* buf) override;
 
     ncclResult_t async_error(char* msg, size_t msg_len) override;
+    ncclResult_t debug_check(char* msg, size_t msg_len) override;
     void abort(int failed_rank) override;
     void quiesce() override { DeviceGuard g(dev_); cudaDeviceSynchronize(); cudaGetLastError(); }
     GpuAlgo last_algo(int coll) const override { return last_[coll]; }
@@ -115,6 +116,7 @@ private:
     bool rooted_pipe_ = false;            // broadcast / reduce of large ordinary buffers: pipelined switch form (nvls_rooted.cu)
     size_t rooted_pipe_min_bytes_ = 16u << 20;
     bool sticky_error_ = false;
+    bool guard_ = false;                  // guard words in the unused parts of the pool (canary.hpp)
     bool device_stamps_ = false;
     std::vector<SymSegment> user_segs_;
     std::vector<RegisteredBuffer> regs_;

@@ -35,6 +35,7 @@ def _declare(lib):
         "dccl_comm_finalize": (i, [vp]),
         "dccl_comm_abort": (i, [vp]),
         "dccl_topology_json": (i, [vp, cp, sz]),
+        "dccl_debug_check": (i, [vp]),
         "dccl_selftest_fd_exchange": (i, [vp]),
         "dccl_comm_shrink": (i, [vp, c.POINTER(vp)]),
         "dccl_world_size": (i, [vp]),
@@ -96,6 +97,10 @@ def _declare(lib):
         "dccl_emu_set_peer_buffers": (None, [i]),
         "dccl_emu_switch_single": (i, [i, i, sz, i, i, vp, vp]),
         "dccl_local_reduce": (i, [vp, vp, sz, i, i]),
+        "dccl_debug_bounds_build": (i, []),
+        "dccl_selftest_canary": (i, []),
+        "dccl_emu_set_guard": (None, [i]),
+        "dccl_emu_declare_stage_bytes": (i, [sz]),
     }
     for name, (res, args) in sigs.items():
         fn = getattr(lib, name)
@@ -113,7 +118,9 @@ def lib():
     if _lib is None:
         if not os.path.exists(LIB_PATH):
             build()
-        _lib = _declare(ctypes.CDLL(LIB_PATH))
+        # DCCL_LIBRARY: another build of the library, e.g. build-bounds/libdccl.so (make BOUNDS=1)
+        path = os.environ.get("DCCL_LIBRARY") or LIB_PATH
+        _lib = _declare(ctypes.CDLL(path))
     return _lib
 
 

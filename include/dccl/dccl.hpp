@@ -246,6 +246,16 @@ ncclResult_t  dcclSetAlgorithm(ncclComm_t comm, const char* collective, const ch
  */
 ncclResult_t  dcclGetTopology(ncclComm_t comm, char* json, size_t len);
 
+/**
+ * Debug aid. With `DCCL/debug_bounds = 1` (DCCL_DEBUG_BOUNDS=1) the unused bytes between the regions of the
+ * communicator's device pool hold guard words; this call reads them back and returns ncclInternalError when a
+ * kernel wrote there (dcclGetLastError then says where). ncclSuccess when intact, when guarding is off and when
+ * no device is bound. It waits for the device; it is also run at ncclCommFinalize. A library whose kernels were
+ * compiled with -DDCCL_DEBUG_BOUNDS (make BOUNDS=1) additionally checks its pool ranges before it uses them and
+ * reports a violation like a time-out, through dcclGetLastError.
+ */
+ncclResult_t  dcclDebugCheck(ncclComm_t comm);
+
 /** Name of the variant the last call of `collective` used (for tools and tests). */
 const char*   dcclGetLastAlgorithm(ncclComm_t comm, const char* collective);
 

@@ -41,3 +41,70 @@ def test_two_shot_packet_all_reduce(dccl_lib, n):
             for op in ["sum", "avg"]:
                 out = emu(dccl_lib, "reduce", "twoshot_ll", n, "float32", op, count, ins, root=root, iters=4, ctas=6)
                 assert close(out[root], oracle.fold(ins, op), "float32", n), ("reduce", n, root, count, op)
+
+
+def _capacity_fp32(algo, kind, n, stage):
+    """Largest fp32 count the staged variants take with `stage` bytes per staging half (whole 16-byte vectors)."""
+    elems, fl = stage // 4, lambda v: v // 4 * 4
+    if algo == "ring":
+        return n * fl(elems // (2 * n)) if kind == "allreduce" else fl(elems // (2 * n))
+    if algo == "rabenseifner":
+        return fl(elems // (n.bit_length()))                      # log2(n) + 1 areas for a power of two
+    if kind in ("allreduce", "reduce"):
+        return n * fl(elems // (n + 1))
+    if kind == "reducescatter":
+        return fl(elems // (n + 1))
+    return fl(elems) if kind == "allgather" else n * fl(elems)
+
+
+def test_guard_words_between_the_pool_regions_stay_intact(dccl_lib):
+    """Every emulated variant at the largest message its region takes (and at a small one), with guard words in the
+    unused parts of every pool: the harness returns 200 + gap when a run damaged them."""
+    n, stage = 8, 1 << 20
+    ll_cap = (128 << 10) // 4
+    cases = [("allreduce", "oneshot", ll_cap), ("reducescatter", "oneshot", ll_cap), ("allgather", "oneshot", ll_cap),
+             ("broadcast", "oneshot", ll_cap), ("reduce", "oneshot", ll_cap),
+             ("allreduce", "twoshot_ll", n * (256 << 10) // 4), ("reduce", "twoshot_ll", n * (256 << 10) // 4)]
+    for kind in ["allreduce", "reducescatter", "allgather", "broadcast", "reduce"]:
+        for algo in ["twoshot", "ring", "rabenseifner"]:
+            if algo == "rabenseifner" and kind != "allreduce" or algo == "ring" and kind in ("broadcast", "reduce"):
+                continue
+            cases.append((kind, algo, _capacity_fp32(algo, kind, n, stage)))
+    dccl_lib.dccl_emu_set_guard(1)
+    try:
+        for kind, algo, cap in cases:
+            for count in [5, cap]:
+                in_count = count * n if kind == "reducescatter" else count
+                ins = inputs_for("float32", "sum", in_count, n, seed=61)
+                out = emu(dccl_lib, kind, algo, n, "float32", "sum", count, ins, root=n - 1, iters=2, stage=stage)
+                want = oracle.fold(ins, "sum")
+                if kind == "allreduce":
+                    assert close(out[0], want, "float32", n), (kind, algo, count)
+                elif kind == "reduce":
+                    assert close(out[n - 1], want, "float32", n), (kind, algo, count)
+        # grouped send / recv: messages that wrap every FIFO slot
+        W, nbytes = 2, (4 << 20) + 4096
+        hin = np.random.default_rng(5).integers(0, 255, size=n * W * nbytes, dtype=np.uint8)
+        hout = np.zeros_like(hin)
+        rc = dccl_lib.dccl_emu_sendrecv_ring(n, nbytes, W, 4, 2, hin.ctypes.data, hout.ctypes.data)
+        assert rc == 0, rc
+        got, sent = hout.reshape(n, W * nbytes), hin.reshape(n, W * nbytes)
+        for r in range(n):
+            assert np.array_equal(got[r], sent[(r - 1) % n]), r
+    finally:
+        dccl_lib.dccl_emu_set_guard(0)
+
+
+def test_range_checking_build_refuses_before_it_touches_memory():
+    """The library compiled with its range checks (make BOUNDS=1), in a process of its own: normal runs pass, and a
+    run that is told a smaller staging area than its message needs comes back with the bounds code."""
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    path = os.path.join(root, "build-bounds", "libdccl.so")
+    if not os.path.exists(path):
+        pytest.skip("build-bounds/libdccl.so is not built (make BOUNDS=1 lib)")
+    env = dict(os.environ, DCCL_LIBRARY=path)
+    p = subprocess.run([sys.executable, os.path.join(root, "tests", "workers", "bounds_worker.py")], env=env, capture_output=True, text=True, timeout=600)
+    assert p.returncode == 0 and "bounds worker: ok" in p.stdout, p.stdout[-2000:] + p.stderr[-2000:]

@@ -240,3 +240,15 @@ def test_topology_tool_without_a_gpu(build_dir, tmp_path):
     subprocess.run(["gcc", "-shared", "-fPIC", "-o", so, os.path.join(here, "fakes", "fake_nvml.c")], check=True)
     rep = json.loads(subprocess.run([tool, "--nvml", so], capture_output=True, text=True, timeout=60, check=True).stdout)
     assert len(rep["gpus"]) == 2 and rep["gpus"][1]["nvlinks_active"] == 17
+
+
+def test_guard_words_of_the_pool_layout(dccl_lib):
+    """The guard words between the regions of a device pool, exercised on a host buffer with the same layout: intact
+    after filling, a damaged byte right after each region (and right before the staging area) is named with its
+    gap and offset, and writes that stay inside the regions never disturb them."""
+    if not hasattr(dccl_lib, "dccl_selftest_canary"):
+        pytest.skip("host-only build")
+    assert dccl_lib.dccl_selftest_canary() == 0
+    # the library the package ships is the normal build: range checks are compiled out
+    assert dccl_lib.dccl_debug_bounds_build() == 0
+    assert dccl_lib.dccl_emu_declare_stage_bytes(1 << 16) == -1

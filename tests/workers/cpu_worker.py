@@ -160,6 +160,7 @@ def main():
     # the descriptor plane (SCM_RIGHTS over the per-rank unix sockets) that carries the GPU memory handles
     from dccl_b200._lib import lib as _native
     check(_native().dccl_selftest_fd_exchange(comm._h) == 0, "descriptor exchange between all ranks")
+    check(_native().dccl_debug_check(comm._h) == 0, "pool check without a device side is a success")
 
     # the symmetric allocator over a stand-in driver (memfd + mmap): every rank maps every peer's segment and reads it;
     # then with one rank's allocation failing: everybody must come back with a failure, nobody may hang
