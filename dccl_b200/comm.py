@@ -185,6 +185,11 @@ class Communicator:
         _check(lib().dccl_topology_json(self._h, buf, len(buf)), "dcclGetTopology")
         return json.loads(buf.value.decode())
 
+    def debug_check(self):
+        """With DCCL_DEBUG_BOUNDS=1: raise when a kernel wrote into the unused parts of this rank's device pool
+        (the message names the gap and the offset). No-op otherwise."""
+        _check(lib().dccl_debug_check(self._h), "dcclDebugCheck")
+
     def set_param(self, name, value):
         """Tuning knob for sweeps: ctas (0 = table), threads, unroll, p2p_ctas."""
         _check(lib().dccl_comm_set_param(self._h, name.encode(), int(value)), "set_param")

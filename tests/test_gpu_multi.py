@@ -59,5 +59,12 @@ def test_topology_packets_two_shot_and_composed_collectives():
 
 @FIRST_RUN
 @pytest.mark.skipif(gpu_count() < 2, reason="needs two GPUs")
+def test_no_variant_writes_between_the_pool_regions():
+    """The basic suite with guard words in the unused parts of every rank's pool, checked at the end."""
+    run(min(gpu_count(), 8), ["--suite", "basic"], env={"DCCL_DEBUG_BOUNDS": "1"})
+
+
+@FIRST_RUN
+@pytest.mark.skipif(gpu_count() < 2, reason="needs two GPUs")
 def test_pipelined_switch_broadcast_and_reduce():
     run(min(gpu_count(), 8), ["--suite", "rooted"])

@@ -344,6 +344,12 @@ def main():
 
     code, emsg = comm.last_error()
     check(code == 0, "async error: " + emsg)
+    if os.environ.get("DCCL_DEBUG_BOUNDS") == "1":   # guard words between the pool regions: nothing wrote there
+        torch.cuda.synchronize()
+        try:
+            comm.debug_check()
+        except Exception as e:  # noqa: BLE001
+            check(False, "pool guard words: %s (%s)" % (e, comm.last_error()[1]))
     mc = comm.has_multicast
     launches = comm.launches
     comm.finalize()
