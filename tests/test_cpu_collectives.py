@@ -13,6 +13,8 @@ import pytest
 
 from dccl_b200.utils.launch import python_ranks, spawn_ranks
 
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
 HERE = os.path.dirname(os.path.abspath(__file__))
 WORKER = os.path.join(HERE, "workers", "cpu_worker.py")
 
@@ -167,3 +169,28 @@ def test_p2p_perf_host_mode(build_dir, tmp_path):
     # missing --transport: exit 1 with the help text
     p = subprocess.run([tool], capture_output=True, text=True)
     assert p.returncode == 1 and "--transport" in p.stdout + p.stderr
+
+
+def test_cmake_build_install_and_find_package(tmp_path):
+    """The CMake route of the original (cmake .. && make && make install, then find_package(dccl) from another
+    project; reference CMakeLists.txt:108-175, examples/helloworld/CMakeLists.txt): host-only configuration here."""
+    import shutil
+    if shutil.which("cmake") is None:
+        pytest.skip("cmake is not installed")
+    bdir, prefix, hdir = tmp_path / "b", tmp_path / "inst", tmp_path / "hw"
+    bdir.mkdir()
+    hdir.mkdir()
+    def sh(cmd, cwd):
+        p = subprocess.run(cmd, cwd=str(cwd), capture_output=True, text=True, timeout=900)
+        assert p.returncode == 0, " ".join(cmd) + "\n" + p.stdout[-2000:] + p.stderr[-2000:]
+    sh(["cmake", ROOT, "-DDCCL_WITH_CUDA=OFF", "-DCMAKE_INSTALL_PREFIX=" + str(prefix)], bdir)
+    sh(["make", "-j8"], bdir)
+    sh(["make", "install"], bdir)
+    for rel in ["lib/libdccl.so", "include/dccl/dccl.hpp", "include/dccl/dccl_c.h", "include/dccl/config.h", "bin/dccl_cli", "bin/p2p_perf",
+                "lib/cmake/dccl/dcclConfig.cmake"]:
+        assert (prefix / rel).exists(), rel
+    sh(["cmake", os.path.join(ROOT, "examples", "helloworld"), "-Ddccl_DIR=" + str(prefix / "lib" / "cmake" / "dccl")], hdir)
+    sh(["make"], hdir)
+    env = dict(os.environ, DCCL_RANK="0", DCCL_WORLD_SIZE="1")
+    p = subprocess.run([str(hdir / "helloworld")], env=env, capture_output=True, text=True, timeout=60)
+    assert p.returncode == 0 and "world size = 1, my rank = 0" in p.stdout, p.stdout + p.stderr
