@@ -54,9 +54,10 @@ bool load_nvml(const char* lib, Nvml* n, std::string* err) {
     return true;
 }
 
+/** Ends the NVML session. The library itself stays loaded for the life of the process: other parts of the
+ *  process (a framework's memory statistics, say) may hold it too, and unloading a driver library buys nothing. */
 void unload_nvml(Nvml* n) {
     if (n->ok) n->Shutdown();
-    if (n->h) dlclose(n->h);
     n->h = nullptr;
     n->ok = false;
 }
