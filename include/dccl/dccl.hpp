@@ -277,6 +277,23 @@ inline ncclResult_t ncclCommGetAsyncError(ncclComm_t comm, ncclResult_t* async_e
 inline const char*  ncclGetErrorString(ncclResult_t r) { return dcclGetErrorString(r); }
 inline ncclResult_t ncclGroupStart() { return dcclGroupStart(); }
 inline ncclResult_t ncclGroupEnd() { return dcclGroupEnd(); }
+/* the composed collectives under the names NCCL 2.28 gives them */
+inline ncclResult_t ncclAlltoAll(const void* sendbuff, void* recvbuff, size_t count, ncclDataType_t datatype, ncclComm_t comm, cudaStream_t stream) {
+    return dcclAllToAll(sendbuff, recvbuff, count, datatype, comm, stream);
+}
+inline ncclResult_t ncclGather(const void* sendbuff, void* recvbuff, size_t count, ncclDataType_t datatype, int root, ncclComm_t comm, cudaStream_t stream) {
+    return dcclGather(sendbuff, recvbuff, count, datatype, root, comm, stream);
+}
+inline ncclResult_t ncclScatter(const void* sendbuff, void* recvbuff, size_t count, ncclDataType_t datatype, int root, ncclComm_t comm, cudaStream_t stream) {
+    return dcclScatter(sendbuff, recvbuff, count, datatype, root, comm, stream);
+}
+/* registration: NCCL hands out a handle; here the buffer's address is the handle */
+inline ncclResult_t ncclCommRegister(const ncclComm_t comm, void* buff, size_t size, void** handle) {
+    const ncclResult_t r = dcclRegisterCacheMemory(comm, buff, size);
+    if (handle) *handle = r == ncclSuccess ? buff : nullptr;
+    return r;
+}
+inline ncclResult_t ncclCommDeregister(const ncclComm_t comm, void* handle) { return dcclDeregisterCacheMemory(comm, handle, 0); }
 
 #define CACHELINE_OFFSET(addr)          ( ((uint64_t)(addr))%CACHELINE_SIZE)
 #define CUDA_L1_CACHELINE_OFFSET(addr)  ( ((uint64_t)(addr))%CUDA_L1_CACHELINE_SIZE)
