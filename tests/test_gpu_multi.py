@@ -68,3 +68,14 @@ def test_no_variant_writes_between_the_pool_regions():
 @pytest.mark.skipif(gpu_count() < 2, reason="needs two GPUs")
 def test_pipelined_switch_broadcast_and_reduce():
     run(min(gpu_count(), 8), ["--suite", "rooted"])
+
+
+@FIRST_RUN
+@pytest.mark.skipif(gpu_count() < 2, reason="needs two GPUs")
+def test_differentiable_collectives_and_parallel_layers_on_device_tensors():
+    """tests/workers/tp_worker.py with CUDA tensors: forward and adjoint collectives run as device kernels."""
+    world = min(gpu_count(), 4)
+    res = python_ranks(os.path.join(HERE, "workers", "tp_worker.py"), ["--cuda"], world, timeout=600, gpus=True)
+    for r, p in enumerate(res):
+        assert p.returncode == 0, "rank %d:\n%s\n%s" % (r, p.stdout[-3000:], p.stderr[-3000:])
+        assert p.stdout.strip().splitlines()[-1].startswith("OK"), p.stdout

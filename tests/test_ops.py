@@ -1,0 +1,19 @@
+"""Differentiable collectives (dccl_b200.ops) and the tensor / sequence parallel layers built on them, on CPU ranks:
+every forward against the definition, every backward against the adjoint worked out by hand, and a split MLP against
+the unsplit one (outputs, input gradients, weight and bias gradients)."""
+import os
+
+import pytest
+
+from dccl_b200.utils.launch import python_ranks
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+WORKER = os.path.join(HERE, "workers", "tp_worker.py")
+
+
+@pytest.mark.parametrize("world", [1, 2, 3, 4])
+def test_differentiable_collectives_and_parallel_layers(dccl_lib, world):
+    res = python_ranks(WORKER, [], world, timeout=300)
+    for r, p in enumerate(res):
+        assert p.returncode == 0, "rank %d:\n%s\n%s" % (r, p.stdout[-3000:], p.stderr[-3000:])
+        assert p.stdout.strip().splitlines()[-1].startswith("OK"), p.stdout
