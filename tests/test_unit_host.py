@@ -252,3 +252,25 @@ def test_guard_words_of_the_pool_layout(dccl_lib):
     # the library the package ships is the normal build: range checks are compiled out
     assert dccl_lib.dccl_debug_bounds_build() == 0
     assert dccl_lib.dccl_emu_declare_stage_bytes(1 << 16) == -1
+
+
+def test_profile_summary_from_a_raw_page():
+    """benchmarks/ncu_summary.py on a hand-made raw page: metric rows in a fixed order, the three largest stalls."""
+    import importlib.util
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    spec = importlib.util.spec_from_file_location("ncu_summary", os.path.join(root, "benchmarks", "ncu_summary.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    pre = "smsp__average_warps_issue_stalled_"
+    post = "_per_issue_active.ratio"
+    names = ["ID", "Kernel Name", "gpu__time_duration.sum", "dram__bytes_read.sum", "launch__registers_per_thread",
+             pre + "long_scoreboard" + post, pre + "barrier" + post, pre + "wait" + post, pre + "membar" + post, "other__metric"]
+    units = ["", "", "us", "Mbyte", "register/thread", "inst", "inst", "inst", "inst", ""]
+    row = ["0", "k_direct<float, 0>(CollArgs)", "12.5", "64.0", "96", "30.1", "4.5", "1.25", "9.75", "7"]
+    text = "==PROF== banner line\n" + "\n".join(",".join('"%s"' % v for v in r) for r in (names, units, row)) + "\n"
+    launches = mod.parse_csv(text)
+    assert len(launches) == 1 and launches[0][0].startswith("k_direct")
+    lines = mod.summary_lines(launches[0][1])
+    assert [l[0] for l in lines[:3]] == ["gpu__time_duration.sum", "dram__bytes_read.sum", "launch__registers_per_thread"]
+    assert [l[0] for l in lines[3:]] == [pre + s + post for s in ("long_scoreboard", "membar", "barrier")]
+    assert lines[0][1:] == ("12.5", "us")
