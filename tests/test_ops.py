@@ -17,3 +17,13 @@ def test_differentiable_collectives_and_parallel_layers(dccl_lib, world):
     for r, p in enumerate(res):
         assert p.returncode == 0, "rank %d:\n%s\n%s" % (r, p.stdout[-3000:], p.stderr[-3000:])
         assert p.stdout.strip().splitlines()[-1].startswith("OK"), p.stdout
+
+
+@pytest.mark.parametrize("world", [1, 2, 3])
+def test_sharded_optimizer_matches_the_unsplit_one(dccl_lib, world):
+    """dccl_b200.parallel.zero: reduce-scatter of the gradients, AdamW on this rank's slice, all-gather of the result,
+    against plain AdamW on the mean loss; the optimizer state per rank shrinks with the world size."""
+    res = python_ranks(os.path.join(HERE, "workers", "zero_worker.py"), [], world, timeout=300)
+    for r, p in enumerate(res):
+        assert p.returncode == 0, "rank %d:\n%s\n%s" % (r, p.stdout[-3000:], p.stderr[-3000:])
+        assert p.stdout.strip().splitlines()[-1].startswith("OK"), p.stdout
