@@ -15,6 +15,8 @@ and the adjoint collective in backward:
     broadcast              broadcast from ``root``     reduce (sum) to ``root``
     copy_to_region         identity                    all-reduce (sum)
     reduce_from_region     all-reduce (sum)            identity
+    send                   send to ``peer``            receive the gradient from ``peer``
+    recv                   receive from ``peer``       send the gradient to ``peer``
     =====================  ==========================  ==========================
 
 The first five are exact adjoints when every rank goes on to use its output in its own loss term.
@@ -162,6 +164,35 @@ class _ReduceFromRegion(torch.autograd.Function):
         return g, None
 
 
+class _Send(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, comm, peer):
+        ctx.comm, ctx.peer, ctx.like = comm, peer, (x.shape, x.dtype, x.device)
+        x = x.contiguous()
+        comm.send(x, peer)
+        return x.new_zeros(())
+
+    @staticmethod
+    def backward(ctx, g):
+        shape, dtype, device = ctx.like
+        grad = torch.empty(shape, dtype=dtype, device=device)
+        ctx.comm.recv(grad, ctx.peer)
+        return grad, None, None
+
+
+class _Recv(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, like, comm, peer):
+        ctx.comm, ctx.peer = comm, peer
+        out = torch.empty_like(like)
+        return comm.recv(out, peer)
+
+    @staticmethod
+    def backward(ctx, g):
+        ctx.comm.send(g.contiguous(), ctx.peer)
+        return None, None, None
+
+
 def all_reduce(x, op="sum", comm=None):
     if op not in ("sum", "avg"):
         raise ValueError("differentiable all_reduce supports sum and avg")
@@ -188,6 +219,20 @@ def all_to_all(x, comm=None):
 
 def broadcast(x, root=0, comm=None):
     return _Broadcast.apply(x, _comm(comm), root)
+
+
+def send(x, peer, comm=None):
+    """Send `x` to `peer` (the next pipeline stage). Returns a zero scalar that carries the graph: add it to this
+    rank's loss (or call ``.backward()`` on it when the rank has no loss of its own) and backward receives the
+    gradient of `x` from `peer` and continues into the graph that produced `x`."""
+    return _Send.apply(x, _comm(comm), peer)
+
+
+def recv(like, peer, comm=None):
+    """Receive a tensor shaped like `like` from `peer` (the previous pipeline stage); backward sends its gradient
+    back. `like` only gives shape, dtype and device."""
+    like = like.detach().requires_grad_(True)      # the output must be part of a graph for backward to reach us
+    return _Recv.apply(like, _comm(comm), peer)
 
 
 def copy_to_region(x, comm=None):

@@ -1,6 +1,7 @@
 """Differentiable collectives (dccl_b200.ops) and the tensor / sequence parallel layers built on them, on CPU ranks:
-every forward against the definition, every backward against the adjoint worked out by hand, and a split MLP against
-the unsplit one (outputs, input gradients, weight and bias gradients)."""
+every forward against the definition, every backward against the adjoint worked out by hand, a split MLP against
+the unsplit one (outputs, input gradients, weight and bias gradients), and a pipeline of one stage per rank built
+from the differentiable send / recv."""
 import os
 
 import pytest

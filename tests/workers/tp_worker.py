@@ -124,6 +124,27 @@ def main():
     check(close(down.weight.grad, rw2.grad[:, r * per:(r + 1) * per], 1e-4), "sequence parallel row weight gradient")
     check(close(down.bias.grad, rb2.grad, 1e-4), "sequence parallel row bias gradient after sync")
 
+    # pipeline: stage s (one Linear + tanh) lives on rank s; activations go forward with send / recv, gradients come back
+    if n > 1:
+        torch.manual_seed(99)
+        stages = [torch.nn.Linear(d, d).to(dev) for _ in range(n)]
+        px, ptgt = torch.randn(5, d).to(dev), torch.randn(5, d).to(dev)
+        h = px
+        for st in stages:
+            h = torch.tanh(st(h))
+        ((h - ptgt) ** 2).sum().backward()                        # the unsplit reference, on every rank
+        want_w, want_b = stages[r].weight.grad.clone(), stages[r].bias.grad.clone()
+        mine = torch.nn.Linear(d, d).to(dev)
+        mine.load_state_dict(stages[r].state_dict())
+        h_in = px if r == 0 else ops.recv(px, r - 1)
+        h_out = torch.tanh(mine(h_in))
+        if r == n - 1:
+            ((h_out - ptgt) ** 2).sum().backward()
+        else:
+            ops.send(h_out, r + 1).backward()
+        check(close(mine.weight.grad, want_w, 1e-4), "pipeline stage %d weight gradient" % r)
+        check(close(mine.bias.grad, want_b, 1e-4), "pipeline stage %d bias gradient" % r)
+
     if cuda:
         torch.cuda.synchronize()
     comm.finalize()
