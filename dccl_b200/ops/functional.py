@@ -124,6 +124,30 @@ class _AllToAll(torch.autograd.Function):
         return ctx.comm.all_to_all(g, torch.empty_like(g)), None
 
 
+class _AllToAllV(torch.autograd.Function):
+    """Rows of `x` (first dimension) in per-peer runs of send_counts[p] rows; the result has recv_counts[p] rows from
+    rank p, in rank order. Backward is the same exchange with the counts swapped."""
+
+    @staticmethod
+    def forward(ctx, x, comm, send_counts, recv_counts):
+        ctx.comm, ctx.sc, ctx.rc = comm, list(send_counts), list(recv_counts)
+        x = x.contiguous()
+        row = 1
+        for s in x.shape[1:]:
+            row *= int(s)
+        ctx.row = row
+        out = x.new_empty((sum(ctx.rc),) + tuple(x.shape[1:]))
+        comm.all_to_all(x, out, [c * row for c in ctx.sc], [c * row for c in ctx.rc])
+        return out
+
+    @staticmethod
+    def backward(ctx, g):
+        g = g.contiguous()
+        out = g.new_empty((sum(ctx.sc),) + tuple(g.shape[1:]))
+        ctx.comm.all_to_all(g, out, [c * ctx.row for c in ctx.rc], [c * ctx.row for c in ctx.sc])
+        return out, None, None, None
+
+
 class _Broadcast(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, comm, root):
@@ -211,10 +235,16 @@ def reduce_scatter(x, dim=0, op="sum", comm=None):
     return _ReduceScatter.apply(x, _comm(comm), dim % x.dim(), op)
 
 
-def all_to_all(x, comm=None):
+def all_to_all(x, send_counts=None, recv_counts=None, comm=None):
     """Block p of `x` (first dimension cut into world-size equal blocks) goes to rank p; block p of the result comes
-    from rank p."""
-    return _AllToAll.apply(x, _comm(comm))
+    from rank p. With `send_counts` / `recv_counts` (rows per peer, both needed) the blocks have those sizes."""
+    if send_counts is None and recv_counts is None:
+        return _AllToAll.apply(x, _comm(comm))
+    if send_counts is None or recv_counts is None:
+        raise ValueError("all_to_all: give both send_counts and recv_counts")
+    if sum(send_counts) != x.shape[0]:
+        raise ValueError("all_to_all: send_counts add up to %d rows, the tensor has %d" % (sum(send_counts), x.shape[0]))
+    return _AllToAllV.apply(x, _comm(comm), send_counts, recv_counts)
 
 
 def broadcast(x, root=0, comm=None):

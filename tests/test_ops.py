@@ -28,3 +28,13 @@ def test_sharded_optimizer_matches_the_unsplit_one(dccl_lib, world):
     for r, p in enumerate(res):
         assert p.returncode == 0, "rank %d:\n%s\n%s" % (r, p.stdout[-3000:], p.stderr[-3000:])
         assert p.stdout.strip().splitlines()[-1].startswith("OK"), p.stdout
+
+
+@pytest.mark.parametrize("world", [1, 2, 4])
+def test_expert_parallel_layer_matches_all_experts_in_one_process(dccl_lib, world):
+    """dccl_b200.parallel.expert_parallel: dispatch and combine through the differentiable all-to-all with per-peer
+    counts; output, input gradient, expert gradients and the summed router gradient against the unsplit layer."""
+    res = python_ranks(os.path.join(HERE, "workers", "moe_worker.py"), [], world, timeout=300)
+    for r, p in enumerate(res):
+        assert p.returncode == 0, "rank %d:\n%s\n%s" % (r, p.stdout[-3000:], p.stderr[-3000:])
+        assert p.stdout.strip().splitlines()[-1].startswith("OK"), p.stdout
