@@ -17,6 +17,7 @@ and the adjoint collective in backward:
     reduce_from_region     all-reduce (sum)            identity
     send                   send to ``peer``            receive the gradient from ``peer``
     recv                   receive from ``peer``       send the gradient to ``peer``
+    ring_shift             to rank+k, from rank-k      to rank-k, from rank+k
     =====================  ==========================  ==========================
 
 The first five are exact adjoints when every rank goes on to use its output in its own loss term.
@@ -26,6 +27,10 @@ backward of the entry and to the forward of the exit.
 
 CUDA tensors run the device kernels on the current stream, CPU tensors the shared-memory host path,
 so the same model code is tested without a GPU.
+
+A collective in backward is still a collective: every rank has to reach it. An output that a rank does
+not use must stay in that rank's autograd graph all the same (add ``0.0 * y.sum()`` to something that is
+used), or the other ranks wait for an exchange that this rank never starts.
 """
 import torch
 
@@ -217,6 +222,32 @@ class _Recv(torch.autograd.Function):
         return None, None, None
 
 
+def _exchange(comm, x, to, frm):
+    """x goes to rank `to`, the result comes from rank `frm`; one grouped call, so a ring of these cannot deadlock."""
+    from ..comm import group_end, group_start
+    out = torch.empty_like(x)
+    if to == comm.rank and frm == comm.rank:
+        return out.copy_(x)
+    group_start()
+    comm.send(x, to)
+    comm.recv(out, frm)
+    group_end()
+    return out
+
+
+class _RingShift(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, comm, k):
+        ctx.comm, ctx.k = comm, k
+        n, r = comm.world, comm.rank
+        return _exchange(comm, x.contiguous(), (r + k) % n, (r - k) % n)
+
+    @staticmethod
+    def backward(ctx, g):
+        n, r, k = ctx.comm.world, ctx.comm.rank, ctx.k
+        return _exchange(ctx.comm, g.contiguous(), (r - k) % n, (r + k) % n), None, None
+
+
 def all_reduce(x, op="sum", comm=None):
     if op not in ("sum", "avg"):
         raise ValueError("differentiable all_reduce supports sum and avg")
@@ -263,6 +294,11 @@ def recv(like, peer, comm=None):
     back. `like` only gives shape, dtype and device."""
     like = like.detach().requires_grad_(True)      # the output must be part of a graph for backward to reach us
     return _Recv.apply(like, _comm(comm), peer)
+
+
+def ring_shift(x, k=1, comm=None):
+    """Every rank passes `x` to rank + k and gets the tensor of rank - k (same shape on all ranks)."""
+    return _RingShift.apply(x, _comm(comm), k)
 
 
 def copy_to_region(x, comm=None):

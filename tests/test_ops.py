@@ -38,3 +38,13 @@ def test_expert_parallel_layer_matches_all_experts_in_one_process(dccl_lib, worl
     for r, p in enumerate(res):
         assert p.returncode == 0, "rank %d:\n%s\n%s" % (r, p.stdout[-3000:], p.stderr[-3000:])
         assert p.stdout.strip().splitlines()[-1].startswith("OK"), p.stdout
+
+
+@pytest.mark.parametrize("world", [1, 2, 3])
+def test_ring_and_all_to_all_attention_match_attention_over_the_whole_sequence(dccl_lib, world):
+    """dccl_b200.parallel.context_parallel: key / value blocks travelling the ring with a running softmax, and the
+    sequence-to-heads all-to-all form; outputs and dq / dk / dv, with and without the causal mask."""
+    res = python_ranks(os.path.join(HERE, "workers", "cp_worker.py"), [], world, timeout=300)
+    for r, p in enumerate(res):
+        assert p.returncode == 0, "rank %d:\n%s\n%s" % (r, p.stdout[-3000:], p.stderr[-3000:])
+        assert p.stdout.strip().splitlines()[-1].startswith("OK"), p.stdout
