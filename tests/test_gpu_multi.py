@@ -72,10 +72,11 @@ def test_pipelined_switch_broadcast_and_reduce():
 
 @FIRST_RUN
 @pytest.mark.skipif(gpu_count() < 2, reason="needs two GPUs")
-def test_differentiable_collectives_and_parallel_layers_on_device_tensors():
-    """tests/workers/tp_worker.py with CUDA tensors: forward and adjoint collectives run as device kernels."""
+@pytest.mark.parametrize("worker", ["tp_worker.py", "zero_worker.py", "moe_worker.py", "cp_worker.py"])
+def test_differentiable_collectives_and_parallel_layers_on_device_tensors(worker):
+    """The workers of tests/test_ops.py with CUDA tensors: forward and adjoint collectives run as device kernels."""
     world = min(gpu_count(), 4)
-    res = python_ranks(os.path.join(HERE, "workers", "tp_worker.py"), ["--cuda"], world, timeout=600, gpus=True)
+    res = python_ranks(os.path.join(HERE, "workers", worker), ["--cuda"], world, timeout=600, gpus=True)
     for r, p in enumerate(res):
         assert p.returncode == 0, "rank %d:\n%s\n%s" % (r, p.stdout[-3000:], p.stderr[-3000:])
         assert p.stdout.strip().splitlines()[-1].startswith("OK"), p.stdout

@@ -13,12 +13,19 @@ from dccl_b200.parallel.context_parallel import ring_attention, ulysses_attentio
 
 
 def main():
-    comm = Communicator()
+    dev = "cpu"
+    if "--cuda" in sys.argv[1:]:                      # tensors on GPU <DCCL_LOCAL_DEVICE>: the device kernels run
+        local = int(os.environ.get("DCCL_LOCAL_DEVICE", os.environ.get("LOCAL_RANK", "0")))
+        torch.cuda.set_device(local)
+        dev = torch.device("cuda", local)
+        comm = Communicator(device=local)
+    else:
+        comm = Communicator()
     n, r = comm.world, comm.rank
     B, H, S, D = 2, 2 * n, 5, 8
     torch.manual_seed(2468)
-    full = [torch.randn(B, H, S * n, D) for _ in range(3)]
-    w = torch.randn(B, H, S * n, D)
+    full = [torch.randn(B, H, S * n, D).to(dev) for _ in range(3)]
+    w = torch.randn(B, H, S * n, D).to(dev)
     ok = True
     sl = slice(r * S, (r + 1) * S)
     for causal in (False, True):
@@ -34,6 +41,8 @@ def main():
                 if not torch.allclose(got, want.detach(), rtol=1e-4, atol=1e-5):
                     ok = False
                     print("rank %d: %s attention (causal=%s): %s differs by %g" % (r, name, causal, what, (got - want).abs().max().item()))
+    if dev != "cpu":
+        torch.cuda.synchronize()
     comm.finalize()
     if not ok:
         sys.exit(1)

@@ -14,13 +14,20 @@ from dccl_b200.parallel.zero import ShardedOptimizer  # noqa: E402
 
 
 def main():
-    comm = Communicator()
+    dev = "cpu"
+    if "--cuda" in sys.argv[1:]:                      # tensors on GPU <DCCL_LOCAL_DEVICE>: the device kernels run
+        local = int(os.environ.get("DCCL_LOCAL_DEVICE", os.environ.get("LOCAL_RANK", "0")))
+        torch.cuda.set_device(local)
+        dev = torch.device("cuda", local)
+        comm = Communicator(device=local)
+    else:
+        comm = Communicator()
     n, r = comm.world, comm.rank
     torch.manual_seed(7)
-    model = torch.nn.Sequential(torch.nn.Linear(10, 33), torch.nn.Tanh(), torch.nn.Linear(33, 5))   # odd sizes: padding is exercised
+    model = torch.nn.Sequential(torch.nn.Linear(10, 33), torch.nn.Tanh(), torch.nn.Linear(33, 5)).to(dev)   # odd sizes: padding is exercised
     ref = copy.deepcopy(model)
-    xs = [torch.randn(6, 10) for _ in range(n * 3)]
-    ys = [torch.randn(6, 5) for _ in range(n * 3)]
+    xs = [torch.randn(6, 10).to(dev) for _ in range(n * 3)]
+    ys = [torch.randn(6, 5).to(dev) for _ in range(n * 3)]
     kw = dict(lr=1e-2, weight_decay=0.01, betas=(0.9, 0.95))
     opt = ShardedOptimizer(model.parameters(), comm, torch.optim.AdamW, **kw)
     ref_opt = torch.optim.AdamW(ref.parameters(), **kw)
@@ -41,6 +48,8 @@ def main():
     if n > 1 and not mine < full * 0.75:
         ok = False
         print("rank %d: optimizer state %d bytes, unsplit %d" % (r, mine, full))
+    if dev != "cpu":
+        torch.cuda.synchronize()
     comm.finalize()
     if not ok:
         sys.exit(1)
