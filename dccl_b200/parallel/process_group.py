@@ -8,9 +8,7 @@ kernels (see csrc/torch/pg_dccl.cpp). ``communicator(pg)`` returns a
 ``dccl_b200.Communicator`` that shares the process group's native
 communicator, e.g. for symmetric allocations or for choosing a variant.
 """
-import ctypes
 import importlib.util
-import os
 
 import torch
 import torch.distributed as dist

@@ -7,7 +7,6 @@ powers of two, counts that the world size does not divide, unaligned buffers, bo
 """
 import os
 import subprocess
-import sys
 
 import pytest
 
