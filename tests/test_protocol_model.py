@@ -215,3 +215,45 @@ def test_moving_all_receives_of_a_long_group_to_the_front_would_deadlock():
     # first launch wait for sends that sit in the peers' second launch
     assert not run_group(ring(4, 10, 1), batch=16, depth=4, partition="global")
     assert run_group(ring(4, 10, 1), batch=16, depth=4, partition="batch")
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+# pipelined switch broadcast / reduce: chunk and CTA ranges (csrc/kernels/nvls_rooted.cu, csrc/device/geometry.cuh)
+# ---------------------------------------------------------------------------------------------------------------------
+
+def rooted_ranges(count, es, nchunks, G):
+    """[(chunk, cta, first element, one past the last)] as the kernel computes them: the message is cut into nchunks
+    pieces of whole 16-byte vectors, every piece into G CTA ranges of whole vectors."""
+    VE = 16 // es
+    roundup = lambda x, m: (x + m - 1) // m * m
+    chunk = roundup((count + nchunks - 1) // nchunks, VE)
+    out = []
+    for k in range(nchunks):
+        base = k * chunk
+        cnt = 0 if base >= count else min(count - base, chunk)
+        for g in range(G):
+            per = cnt                                            # GEO_WHOLE: one shard holding the chunk
+            epb = roundup((per + G - 1) // G, VE)
+            blo = min(epb * g, per)
+            bhi = min(blo + epb, per)
+            lo, hi = min(blo, cnt), min(bhi, cnt)
+            out.append((k, g, base + lo, base + hi))
+    return out
+
+
+def rooted_chunks(nbytes):
+    return max(2, min(24, (nbytes + (8 << 20) - 1) // (8 << 20)))
+
+
+def test_pipelined_switch_broadcast_ranges_cover_the_message_once():
+    for es in (1, 2, 4, 8):
+        for count in [1, 15, 16, 17, 4099, (1 << 20) + 3, (24 << 20) // es + 5, (200 << 20) // es + 1]:
+            nchunks = rooted_chunks(count * es)
+            for G in (1, 7, 16, 72):
+                ranges = [(lo, hi) for _, _, lo, hi in rooted_ranges(count, es, nchunks, G) if hi > lo]
+                ranges.sort()
+                assert ranges[0][0] == 0 and ranges[-1][1] == count, (es, count, G)
+                for (a, b), (c, d) in zip(ranges, ranges[1:]):
+                    assert b == c, ("gap or overlap", es, count, G, (a, b), (c, d))
+                # every range starts on a 16-byte boundary of the message (what multimem.st needs when the buffer is aligned)
+                assert all((lo * es) % 16 == 0 for lo, _ in ranges), (es, count, G)
