@@ -234,6 +234,7 @@ int main(int argc, char** argv) {
         if (ret != ncclSuccess) { \
             std::cerr << "API:" << api << " failed with error:" << ret << std::endl; \
             ncclCommFinalize(comm); \
+            if (gpu < 0) { free(raw_send); free(raw_recv); } \
             return 2; \
         } \
     }
