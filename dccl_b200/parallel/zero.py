@@ -13,7 +13,9 @@ drop to 1/world per rank.
              all_gather the updated slice (cast back) into the flat parameter buffer
 
 With ``comm.world == 1`` this is the inner optimizer on a flat buffer. CPU tensors use the host path, CUDA
-tensors the device kernels on the current stream.
+tensors the device kernels on the current stream; on GPUs with NVSwitch multicast the flat buffers live in
+symmetric memory (``symmetric=True``), so that both collectives run zero-copy through the switch. Call
+``close()`` before the communicator is finalized to give that memory back.
 """
 import torch
 
@@ -21,8 +23,9 @@ import torch
 class ShardedOptimizer:
     """optimizer_cls(params, **kwargs) is built over ONE tensor per dtype: this rank's fp32 master slice."""
 
-    def __init__(self, params, comm, optimizer_cls=torch.optim.AdamW, **kwargs):
+    def __init__(self, params, comm, optimizer_cls=torch.optim.AdamW, symmetric=True, **kwargs):
         self.comm = comm
+        self._sym = []
         params = [p for p in params if p.requires_grad]
         if not params:
             raise ValueError("no trainable parameters")
@@ -40,8 +43,13 @@ class ShardedOptimizer:
                 offs.append(total)
                 total += -(-p.numel() // align) * align            # every view starts 16-byte aligned
             per = -(-total // (n * align)) * align                  # slice length, a whole number of 16-byte vectors
-            flat = torch.zeros(per * n, dtype=dtype, device=device)
-            grad = torch.zeros(per * n, dtype=dtype, device=device)
+            if symmetric and device.type == "cuda" and n > 1 and comm.has_multicast:
+                flat = comm.symmetric_empty(per * n, dtype, device.index).zero_()
+                grad = comm.symmetric_empty(per * n, dtype, device.index).zero_()
+                self._sym += [flat, grad]
+            else:
+                flat = torch.zeros(per * n, dtype=dtype, device=device)
+                grad = torch.zeros(per * n, dtype=dtype, device=device)
             for p, off in zip(plist, offs):
                 flat[off:off + p.numel()].copy_(p.data.reshape(-1))
                 p.data = flat[off:off + p.numel()].view_as(p)
@@ -73,6 +81,25 @@ class ShardedOptimizer:
                 comm.all_gather(g["out_slice"], g["flat"])
             else:
                 g["flat"].copy_(g["master"].detach())
+
+    def close(self):
+        """Give symmetric buffers back (collective). The parameters keep their values in ordinary memory."""
+        if not self._sym:
+            return
+        torch.cuda.synchronize()
+        for g in self.groups:
+            keep = g["flat"].clone()
+            off = 0
+            for p in g["params"]:
+                # same layout as in __init__: every view starts 16-byte aligned
+                align = 16 // keep.element_size()
+                p.data = keep[off:off + p.numel()].view_as(p)
+                p.grad = None
+                off += -(-p.numel() // align) * align
+            g["flat"], g["grad"] = keep, torch.zeros_like(keep)
+        for t in self._sym:
+            self.comm.free_symmetric(t)
+        self._sym = []
 
     def state_bytes(self):
         """Bytes of optimizer state held by this rank (for reports and tests)."""

@@ -45,6 +45,11 @@ def main():
                 print("rank %d step %d: parameters differ by %g" % (r, step, (p - q).abs().max().item()))
     full = sum(2 * p.numel() * 4 for p in ref.parameters())
     mine = opt.state_bytes()
+    opt.close()
+    for p, q in zip(model.parameters(), ref.parameters()):
+        if not torch.allclose(p, q, rtol=1e-5, atol=1e-6):
+            ok = False
+            print("rank %d: parameters changed by close()" % r)
     if n > 1 and not mine < full * 0.75:
         ok = False
         print("rank %d: optimizer state %d bytes, unsplit %d" % (r, mine, full))
