@@ -18,8 +18,9 @@ def free_port():
 def spawn_ranks(argv, world, env_extra=None, per_rank_env=None, timeout=300, cwd=None, gpus=False, per_rank_argv=None):
     """Run ``argv`` (or ``per_rank_argv[rank]`` where given) once per rank; returns a list of CompletedProcess
     (stdout/stderr captured). A rank that outlives ``timeout`` is killed (only the processes started here)."""
+    import tempfile
     port = free_port()
-    procs = []
+    procs, files = [], []
     for r in range(world):
         env = dict(os.environ)
         env.update({"DCCL_RANK": str(r), "DCCL_WORLD_SIZE": str(world), "DCCL_MASTER_ADDR": "127.0.0.1",
@@ -33,14 +34,28 @@ def spawn_ranks(argv, world, env_extra=None, per_rank_env=None, timeout=300, cwd
         if per_rank_env and r in per_rank_env:
             env.update(per_rank_env[r])
         cmd = per_rank_argv[r] if per_rank_argv and r in per_rank_argv else argv
-        procs.append(subprocess.Popen(cmd, env=env, cwd=cwd, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True))
+        # output goes to files, not pipes: a rank that prints a lot must never block (and with it the ranks that wait
+        # for it in a collective) because nobody reads its pipe yet
+        fo, fe = tempfile.TemporaryFile(mode="w+"), tempfile.TemporaryFile(mode="w+")
+        files.append((fo, fe))
+        procs.append(subprocess.Popen(cmd, env=env, cwd=cwd, stdout=fo, stderr=fe, stdin=subprocess.DEVNULL, text=True))
+    import time
+    deadline = time.monotonic() + timeout
     results = []
-    for p in procs:
+    for p, (fo, fe) in zip(procs, files):
+        killed = False
         try:
-            out, err = p.communicate(timeout=timeout)
+            p.wait(timeout=max(0.0, deadline - time.monotonic()))
         except subprocess.TimeoutExpired:
             p.kill()
-            out, err = p.communicate()
+            p.wait()
+            killed = True
+        fo.seek(0)
+        fe.seek(0)
+        out, err = fo.read(), fe.read()
+        fo.close()
+        fe.close()
+        if killed:
             err += "\n[killed after %d s]" % timeout
         results.append(subprocess.CompletedProcess(p.args, p.returncode, out, err))
     return results

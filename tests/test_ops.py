@@ -12,7 +12,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 WORKER = os.path.join(HERE, "workers", "tp_worker.py")
 
 
-@pytest.mark.parametrize("world", [1, 2, 3, 4])
+@pytest.mark.parametrize("world", [2, 3])
 def test_differentiable_collectives_and_parallel_layers(dccl_lib, world):
     res = python_ranks(WORKER, [], world, timeout=300)
     for r, p in enumerate(res):
@@ -20,7 +20,7 @@ def test_differentiable_collectives_and_parallel_layers(dccl_lib, world):
         assert p.stdout.strip().splitlines()[-1].startswith("OK"), p.stdout
 
 
-@pytest.mark.parametrize("world", [1, 2, 3])
+@pytest.mark.parametrize("world", [1, 3])
 def test_sharded_optimizer_matches_the_unsplit_one(dccl_lib, world):
     """dccl_b200.parallel.zero: reduce-scatter of the gradients, AdamW on this rank's slice, all-gather of the result,
     against plain AdamW on the mean loss; the optimizer state per rank shrinks with the world size."""
@@ -30,7 +30,7 @@ def test_sharded_optimizer_matches_the_unsplit_one(dccl_lib, world):
         assert p.stdout.strip().splitlines()[-1].startswith("OK"), p.stdout
 
 
-@pytest.mark.parametrize("world", [1, 2, 4])
+@pytest.mark.parametrize("world", [1, 4])
 def test_expert_parallel_layer_matches_all_experts_in_one_process(dccl_lib, world):
     """dccl_b200.parallel.expert_parallel: dispatch and combine through the differentiable all-to-all with per-peer
     counts; output, input gradient, expert gradients and the summed router gradient against the unsplit layer."""
@@ -40,7 +40,7 @@ def test_expert_parallel_layer_matches_all_experts_in_one_process(dccl_lib, worl
         assert p.stdout.strip().splitlines()[-1].startswith("OK"), p.stdout
 
 
-@pytest.mark.parametrize("world", [1, 2, 3])
+@pytest.mark.parametrize("world", [2, 3])
 def test_ring_and_all_to_all_attention_match_attention_over_the_whole_sequence(dccl_lib, world):
     """dccl_b200.parallel.context_parallel: key / value blocks travelling the ring with a running softmax, and the
     sequence-to-heads all-to-all form; outputs and dq / dk / dv, with and without the causal mask."""

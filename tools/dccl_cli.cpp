@@ -47,7 +47,7 @@ static const char* help_string =
     "\t--verify,-v  run out of place and check the result against a serial fold; exit 3 on mismatch.\n"
     "\t--init,-i    buffer contents: bytes (memset to the rank, default), uniform, normal.\n"
     "\t--seed,-S    seed base for uniform/normal; rank r uses seed+r. Defaulted to 0.\n"
-    "\t--algo,-A    force an algorithm: auto,ring,rabenseifner,oneshot,twoshot,nvls.\n"
+    "\t--algo,-A    force an algorithm: auto,ring,rabenseifner,oneshot,twoshot,twoshot_ll,nvls.\n"
     "\t--root,-R    root rank for broadcast and reduce, defaulted to 0.\n"
     "\t--tt-per-rank write dccl_cli.<rank>.tt instead of dccl_cli.tt (ranks sharing a directory).\n"
     "\t--help,-h    print this message.\n";
