@@ -1,0 +1,97 @@
+"""Tensor-parallel form of the Llama-style decoder (``dccl_b200.models.llama``).
+
+``shard(model, comm)`` turns an unsplit ``LlamaDecoder`` into one whose attention heads and feed-forward columns
+are dealt out over the ranks of ``comm`` (heads and KV heads must divide by the world size): q / k / v and
+gate / up keep the rows of their own heads / columns, o and down keep the matching input columns, and each
+block needs two all-reduces forward and two backward (``ops.copy_to_region`` at the entry of the attention and of
+the MLP, ``ops.reduce_from_region`` at their exits). Embedding, norms and the output head stay replicated; since
+every rank sees the same tokens their gradients come out identical on all ranks without further communication.
+Every rank starts from the same unsplit weights, so the sharded model computes what the unsplit one does.
+"""
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from ..ops import functional as ops
+from .llama import LlamaDecoder, apply_rope, rope_tables
+
+
+def _rows(linear, lo, hi):
+    out = nn.Linear(linear.in_features, hi - lo, bias=False, device=linear.weight.device, dtype=linear.weight.dtype)
+    out.weight.data.copy_(linear.weight.data[lo:hi])
+    return out
+
+
+def _cols(linear, lo, hi):
+    out = nn.Linear(hi - lo, linear.out_features, bias=False, device=linear.weight.device, dtype=linear.weight.dtype)
+    out.weight.data.copy_(linear.weight.data[:, lo:hi])
+    return out
+
+
+class ShardedAttention(nn.Module):
+    def __init__(self, attn, comm):
+        super().__init__()
+        n, r = comm.world, comm.rank
+        if attn.h % n or attn.kv % n:
+            raise ValueError("heads (%d) and KV heads (%d) must divide by the world size (%d)" % (attn.h, attn.kv, n))
+        self.comm, self.h, self.kv, self.hd = comm, attn.h // n, attn.kv // n, attn.hd
+        qw, kw = self.h * self.hd, self.kv * self.hd
+        self.q = _rows(attn.q, r * qw, (r + 1) * qw)
+        self.k = _rows(attn.k, r * kw, (r + 1) * kw)
+        self.v = _rows(attn.v, r * kw, (r + 1) * kw)
+        self.o = _cols(attn.o, r * qw, (r + 1) * qw)
+
+    def forward(self, x, cos, sin):
+        b, s, _ = x.shape
+        x = ops.copy_to_region(x, self.comm)
+        q = self.q(x).view(b, s, self.h, self.hd).transpose(1, 2)
+        k = self.k(x).view(b, s, self.kv, self.hd).transpose(1, 2)
+        v = self.v(x).view(b, s, self.kv, self.hd).transpose(1, 2)
+        q, k = apply_rope(q, cos, sin), apply_rope(k, cos, sin)
+        out = F.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=self.kv != self.h)
+        return ops.reduce_from_region(self.o(out.transpose(1, 2).reshape(b, s, self.h * self.hd)), self.comm)
+
+
+class ShardedBlock(nn.Module):
+    def __init__(self, blk, comm):
+        super().__init__()
+        n, r = comm.world, comm.rank
+        ffn = blk.gate.out_features
+        if ffn % n:
+            raise ValueError("the feed-forward width (%d) must divide by the world size (%d)" % (ffn, n))
+        per = ffn // n
+        self.comm = comm
+        self.n1, self.n2 = blk.n1, blk.n2
+        self.attn = ShardedAttention(blk.attn, comm)
+        self.gate = _rows(blk.gate, r * per, (r + 1) * per)
+        self.up = _rows(blk.up, r * per, (r + 1) * per)
+        self.down = _cols(blk.down, r * per, (r + 1) * per)
+
+    def forward(self, x, cos, sin):
+        x = x + self.attn(self.n1(x), cos, sin)
+        h = ops.copy_to_region(self.n2(x), self.comm)
+        return x + ops.reduce_from_region(self.down(F.silu(self.gate(h)) * self.up(h)), self.comm)
+
+
+class ShardedLlamaDecoder(nn.Module):
+    def __init__(self, model: LlamaDecoder, comm):
+        super().__init__()
+        self.cfg, self.comm = model.cfg, comm
+        self.embed, self.norm, self.head = model.embed, model.norm, model.head
+        self.blocks = nn.ModuleList([ShardedBlock(b, comm) for b in model.blocks])
+
+    def forward(self, tokens):
+        x = self.embed(tokens)
+        cos, sin = rope_tables(tokens.shape[1], self.cfg.hidden // self.cfg.heads, self.cfg.rope_theta, tokens.device)
+        for blk in self.blocks:
+            x = blk(x, cos, sin)
+        return self.head(self.norm(x))
+
+    def loss(self, tokens):
+        logits = self.forward(tokens[:, :-1])
+        return F.cross_entropy(logits.reshape(-1, logits.shape[-1]).float(), tokens[:, 1:].reshape(-1))
+
+
+def shard(model: LlamaDecoder, comm):
+    """The tensor-parallel form of `model` for this rank (the unsplit blocks are not kept)."""
+    return ShardedLlamaDecoder(model, comm)

@@ -72,7 +72,7 @@ def test_pipelined_switch_broadcast_and_reduce():
 
 @FIRST_RUN
 @pytest.mark.skipif(gpu_count() < 2, reason="needs two GPUs")
-@pytest.mark.parametrize("worker", ["tp_worker.py", "zero_worker.py", "moe_worker.py", "cp_worker.py"])
+@pytest.mark.parametrize("worker", ["tp_worker.py", "zero_worker.py", "moe_worker.py", "cp_worker.py", "llama_tp_worker.py"])
 def test_differentiable_collectives_and_parallel_layers_on_device_tensors(worker):
     """The workers of tests/test_ops.py with CUDA tensors: forward and adjoint collectives run as device kernels."""
     world = min(gpu_count(), 4)

@@ -48,3 +48,13 @@ def test_ring_and_all_to_all_attention_match_attention_over_the_whole_sequence(d
     for r, p in enumerate(res):
         assert p.returncode == 0, "rank %d:\n%s\n%s" % (r, p.stdout[-3000:], p.stderr[-3000:])
         assert p.stdout.strip().splitlines()[-1].startswith("OK"), p.stdout
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_tensor_parallel_decoder_matches_the_unsplit_one(dccl_lib, world):
+    """dccl_b200.models.llama_tp: heads and feed-forward columns dealt out over the ranks; loss, gradients of the
+    replicated parameters and of every rank's slices against the unsplit decoder."""
+    res = python_ranks(os.path.join(HERE, "workers", "llama_tp_worker.py"), [], world, timeout=300)
+    for r, p in enumerate(res):
+        assert p.returncode == 0, "rank %d:\n%s\n%s" % (r, p.stdout[-3000:], p.stderr[-3000:])
+        assert p.stdout.strip().splitlines()[-1].startswith("OK"), p.stdout

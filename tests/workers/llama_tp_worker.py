@@ -1,0 +1,64 @@
+"""One rank of the tensor-parallel decoder test: the sharded model against the unsplit one it was made from (loss,
+gradients of replicated parameters, gradients of each rank's slices)."""
+import copy
+import os
+import sys
+
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+sys.path.insert(0, ROOT)
+
+from dccl_b200 import Communicator  # noqa: E402
+from dccl_b200.models.llama import LlamaConfig, LlamaDecoder  # noqa: E402
+from dccl_b200.models.llama_tp import shard  # noqa: E402
+
+
+def main():
+    dev = "cpu"
+    if "--cuda" in sys.argv[1:]:
+        local = int(os.environ.get("DCCL_LOCAL_DEVICE", os.environ.get("LOCAL_RANK", "0")))
+        torch.cuda.set_device(local)
+        dev = torch.device("cuda", local)
+        comm = Communicator(device=local)
+    else:
+        comm = Communicator()
+    n, r = comm.world, comm.rank
+    torch.manual_seed(11)
+    cfg = LlamaConfig(vocab_size=128, hidden=64, layers=2, heads=4, kv_heads=2 if n <= 2 else 4, ffn=96 if n != 4 else 128, max_seq=32)
+    full = LlamaDecoder(cfg).to(dev)
+    tokens = torch.randint(0, cfg.vocab_size, (2, 17)).to(dev)
+    tp = shard(copy.deepcopy(full), comm)
+    ref_loss = full.loss(tokens)
+    ref_loss.backward()
+    loss = tp.loss(tokens)
+    loss.backward()
+    ok = True
+
+    def check(a, b, what):
+        nonlocal ok
+        if not torch.allclose(a, b, rtol=2e-4, atol=2e-5):
+            ok = False
+            print("rank %d: %s differs by %g" % (r, what, (a - b).abs().max().item()))
+
+    check(loss.detach(), ref_loss.detach(), "loss")
+    check(tp.embed.weight.grad, full.embed.weight.grad, "embedding gradient")
+    check(tp.head.weight.grad, full.head.weight.grad, "head gradient")
+    for i, (tb, fb) in enumerate(zip(tp.blocks, full.blocks)):
+        check(tb.n1.weight.grad, fb.n1.weight.grad, "block %d norm gradient" % i)
+        qw = tb.attn.h * tb.attn.hd
+        per = tb.gate.out_features
+        check(tb.attn.q.weight.grad, fb.attn.q.weight.grad[r * qw:(r + 1) * qw], "block %d q gradient" % i)
+        check(tb.attn.o.weight.grad, fb.attn.o.weight.grad[:, r * qw:(r + 1) * qw], "block %d o gradient" % i)
+        check(tb.gate.weight.grad, fb.gate.weight.grad[r * per:(r + 1) * per], "block %d gate gradient" % i)
+        check(tb.down.weight.grad, fb.down.weight.grad[:, r * per:(r + 1) * per], "block %d down gradient" % i)
+    if dev != "cpu":
+        torch.cuda.synchronize()
+    comm.finalize()
+    if not ok:
+        sys.exit(1)
+    print("OK llama tp worker rank %d" % r)
+
+
+if __name__ == "__main__":
+    main()
