@@ -183,37 +183,40 @@ def main():
         want = [w / world for w in want]
         check(all(torch.allclose(a, b, rtol=1e-4, atol=1e-6) for a, b in zip(grads, want)), "DDP gradients")
 
-    if args.extra and not args.cuda:
-        # differential run against gloo: the same calls through a gloo group over the same ranks
-        gloo = dist.new_group(ranks=list(range(world)), backend="gloo")
+    if args.extra:
+        # differential run: the same calls through a gloo group (CPU tensors) or a stock NCCL group (CUDA tensors)
+        # over the same ranks
+        gloo = dist.new_group(ranks=list(range(world)), backend="nccl" if args.cuda else "gloo")
         for dtype in (torch.float32, torch.int64):
             n = 4099
             mine = tensor_for(300 + rank, n * world, dtype, dev)
             a, b = mine.clone(), mine.clone()
             dist.all_reduce(a)
             dist.all_reduce(b, group=gloo)
-            check(torch.allclose(a.double(), b.double(), rtol=1e-5, atol=1e-5), "all_reduce against gloo %s" % dtype)
+            check(torch.allclose(a.double(), b.double(), rtol=1e-5, atol=1e-5), "all_reduce against the other library %s" % dtype)
             a, b = mine.clone(), mine.clone()
             dist.all_reduce(a, op=dist.ReduceOp.MIN)
             dist.all_reduce(b, op=dist.ReduceOp.MIN, group=gloo)
-            check(torch.equal(a, b), "all_reduce min against gloo %s" % dtype)
+            check(torch.equal(a, b), "all_reduce min against the other library %s" % dtype)
             a, b = mine.clone(), mine.clone()
             dist.broadcast(a, src=world - 1)
             dist.broadcast(b, src=world - 1, group=gloo)
-            check(torch.equal(a, b), "broadcast against gloo %s" % dtype)
+            check(torch.equal(a, b), "broadcast against the other library %s" % dtype)
             a, b = mine.clone(), mine.clone()
             dist.reduce(a, dst=0)
             dist.reduce(b, dst=0, group=gloo)
-            check(rank != 0 or torch.allclose(a.double(), b.double(), rtol=1e-5, atol=1e-5), "reduce against gloo %s" % dtype)
+            check(rank != 0 or torch.allclose(a.double(), b.double(), rtol=1e-5, atol=1e-5), "reduce against the other library %s" % dtype)
             la = [torch.empty_like(mine) for _ in range(world)]
             lb = [torch.empty_like(mine) for _ in range(world)]
             dist.all_gather(la, mine)
             dist.all_gather(lb, mine, group=gloo)
-            check(all(torch.equal(x, y) for x, y in zip(la, lb)), "all_gather against gloo %s" % dtype)
+            check(all(torch.equal(x, y) for x, y in zip(la, lb)), "all_gather against the other library %s" % dtype)
             a, b = torch.empty_like(mine), torch.empty_like(mine)
             dist.all_to_all_single(a, mine)
             dist.all_to_all_single(b, mine, group=gloo)
-            check(torch.equal(a, b), "all_to_all_single against gloo %s" % dtype)
+            check(torch.equal(a, b), "all_to_all_single against the other library %s" % dtype)
+        if args.cuda:
+            torch.cuda.synchronize()
         dist.barrier()
 
     dist.destroy_process_group()
