@@ -250,13 +250,13 @@ __device__ __forceinline__ uint32_t flag_value(uint32_t seq, int idx) { return s
 __device__ __forceinline__ void signal_peer(const DevComm& c, int peer, int bid, uint32_t seq, int idx) {
     // the release store orders everything that happened before it, including the other threads' writes
     // that the preceding CTA barrier made visible to this thread; no separate fence is needed
-    if (!DCCL_BOUNDS_OK(c, bid >= 0 && bid < kMaxCtas && peer >= 0 && peer < c.nranks && idx >= 0 && idx < kFlagVals, 990, bid)) return;
+    if (!DCCL_BOUNDS_OK(c, bid >= 0 && bid < kMaxCtas && peer >= 0 && peer < c.nranks && idx >= 0 && idx < kFlagVals, 1990, bid)) return;
     st_release_sys(flag_slot(c.pool[peer], bid, c.rank), flag_value(seq, idx));
 }
 
 /** Wait until CTA `bid` of rank `src` has signalled point `idx` of call `seq`. One thread. */
 __device__ __forceinline__ bool wait_peer(const DevComm& c, int src, int bid, uint32_t seq, int idx, int site) {
-    if (!DCCL_BOUNDS_OK(c, bid >= 0 && bid < kMaxCtas && src >= 0 && src < c.nranks && idx >= 0 && idx < kFlagVals, 991, bid)) return false;
+    if (!DCCL_BOUNDS_OK(c, bid >= 0 && bid < kMaxCtas && src >= 0 && src < c.nranks && idx >= 0 && idx < kFlagVals, 1991, bid)) return false;
     return wait_flag_ge(c, flag_slot(c.pool[c.rank], bid, src), flag_value(seq, idx), src, site, seq);
 }
 

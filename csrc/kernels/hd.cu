@@ -47,7 +47,7 @@ __device__ __forceinline__ void hd_body(const CollArgs& a, const Ctx& x) {
     const bool avg = a.op == (int)ncclAvg;
     int steps = 0;
     while ((1 << steps) < n) steps++;
-    if (!DCCL_BOUNDS_OK(c, steps <= 4, 902, steps) || !stage_extent_ok<T>(c, (size_t)(steps + 1) * area, 902)) return;
+    if (!DCCL_BOUNDS_OK(c, steps <= 4, 1902, steps) || !stage_extent_ok<T>(c, (size_t)(steps + 1) * area, 1902)) return;
     // one receive area per halving step (the regions received in successive steps are nested, so
     // they must not share memory), then one for the gather (those regions are disjoint)
     T* my_stage = stage_ptr<T>(c, r, x.parity);

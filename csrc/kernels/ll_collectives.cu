@@ -81,7 +81,7 @@ __device__ __forceinline__ void ll_collective_body(const CollArgs& a, const Ctx&
     const bool fin = (reinterpret_cast<uintptr_t>(send) & 7u) == 0 && (sbytes & 7u) == 0;
     const bool fout = (reinterpret_cast<uintptr_t>(recv) & 7u) == 0 && (sbytes & 7u) == 0;
     bool ok = true;
-    if (!DCCL_BOUNDS_OK(c, npk * 16 <= kLLSlotBytes, 904, npk)) return;   // one packet slot per source rank
+    if (!DCCL_BOUNDS_OK(c, npk * 16 <= kLLSlotBytes, 1904, npk)) return;   // one packet slot per source rank
     const bool rooted = mode == LL_BROADCAST || mode == LL_REDUCE;
     // entry announcement (see the file comment); nothing has to be ordered before it
     if (rooted && (int)threadIdx.x < n && (int)threadIdx.x != r) signal_peer(c, (int)threadIdx.x, x.bid, x.seq, 0);

@@ -103,7 +103,7 @@ __device__ __forceinline__ void ll_twoshot_body(const CollArgs& a, const Ctx& x)
     // generations alternate). Folding a shard means hearing from everybody, but a vector too short to give every
     // rank a shard leaves some ranks with nothing to fold: then the CTAs announce their entry with a flag instead.
     const bool announce = (size_t)(n - 1) * per >= npk;
-    if (!DCCL_BOUNDS_OK(c, per * 16 <= kLL2PhaseBytes, 905, per)) return;   // one shard of packets per source rank and phase
+    if (!DCCL_BOUNDS_OK(c, per * 16 <= kLL2PhaseBytes, 1905, per)) return;   // one shard of packets per source rank and phase
     if (announce && (int)threadIdx.x < n && (int)threadIdx.x != r) signal_peer(c, (int)threadIdx.x, x.bid, x.seq, 0);
 
     /* A: my part of every other rank's shard goes to its owner */

@@ -49,7 +49,7 @@ __device__ __forceinline__ void nvls_body(const CollArgs& a, const Ctx& x) {
     const size_t stage_off = kStageOff + (size_t)x.parity * c.stage_bytes;
     T* my_stage = reinterpret_cast<T*>(c.pool[r] + stage_off);
     char* mc_stage = c.mc_pool + stage_off;
-    if (!a.symmetric && !stage_extent_ok<T>(c, (size_t)n * g.slot_stride, 907)) return;   // one slot per rank
+    if (!a.symmetric && !stage_extent_ok<T>(c, (size_t)n * g.slot_stride, 1907)) return;   // one slot per rank
     auto lo_of = [&](int j) { size_t l = g.len(j); return g.blo < l ? g.blo : l; };
     auto hi_of = [&](int j) { size_t l = g.len(j); return g.bhi < l ? g.bhi : l; };
     auto vecs = [&](size_t elems) { return (elems * ES + 15) / 16; };

@@ -92,8 +92,8 @@ __device__ __forceinline__ void nvls_pipe_body(const CollArgs& a, const Ctx& x) 
     size_t chunk = (a.count + nchunks - 1) / nchunks;
     chunk = rs ? (chunk + VE - 1) / VE * VE : (chunk + VE * n - 1) / (VE * n) * (VE * n);
     // the whole message sits in one staging half; chunk numbers are flag values; rows: fan per switch CTA, then one each
-    if (!stage_extent_ok<T>(c, rs ? (size_t)n * slot : slot, 908) ||
-        !DCCL_BOUNDS_OK(c, nchunks >= 1 && nchunks <= kFlagVals && G * (kPipeFan + 1) <= kMaxCtas, 908, nchunks)) return;
+    if (!stage_extent_ok<T>(c, rs ? (size_t)n * slot : slot, 1908) ||
+        !DCCL_BOUNDS_OK(c, nchunks >= 1 && nchunks <= kFlagVals && G * (kPipeFan + 1) <= kMaxCtas, 1908, nchunks)) return;
 
     for (int k = 0; k < nchunks; k++) {
         const size_t base = (size_t)k * chunk;

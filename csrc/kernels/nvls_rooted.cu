@@ -56,8 +56,8 @@ __device__ __forceinline__ void nvls_rooted_body(const CollArgs& a, const Ctx& x
     const size_t chunk = ((a.count + nchunks - 1) / nchunks + VE - 1) / VE * VE;
     auto vecs = [&](size_t elems) { return (elems * ES + 15) / 16; };
     __shared__ int s_fail;
-    if (!stage_extent_ok<T>(c, (a.count + VE - 1) / VE * VE, 909) ||
-        !DCCL_BOUNDS_OK(c, nchunks >= 1 && nchunks <= kRootedMaxChunks, 909, nchunks)) return;
+    if (!stage_extent_ok<T>(c, (a.count + VE - 1) / VE * VE, 1909) ||
+        !DCCL_BOUNDS_OK(c, nchunks >= 1 && nchunks <= kRootedMaxChunks, 1909, nchunks)) return;
 
     // reduce: the first half of the grid copies in (every rank), the second half is the root's switch pass
     const int G = reduce ? x.nb / 2 : x.nb;

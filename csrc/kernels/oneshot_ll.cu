@@ -37,7 +37,7 @@ __device__ __forceinline__ void oneshot_ll_body(const CollArgs& a, const Ctx& x)
     const size_t npk = (nbytes + 7) / 8;
     const uint32_t tag = x.seq;
     const bool avg = a.op == (int)ncclAvg;
-    if (!DCCL_BOUNDS_OK(c, npk * 16 <= kLLSlotBytes, 903, npk)) return;   // one packet slot per source rank
+    if (!DCCL_BOUNDS_OK(c, npk * 16 <= kLLSlotBytes, 1903, npk)) return;   // one packet slot per source rank
     const bool fast_in = (reinterpret_cast<uintptr_t>(send) & 7u) == 0, fast_out = (reinterpret_cast<uintptr_t>(recv) & 7u) == 0;
 
     for (size_t i = (size_t)x.bid * blockDim.x + threadIdx.x; i < npk; i += (size_t)x.nb * blockDim.x) {

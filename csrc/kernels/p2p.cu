@@ -50,7 +50,7 @@ __global__ void __launch_bounds__(512) k_p2p(const __grid_constant__ P2pArgs a) 
     const DevComm& c = *cp;
     const int opi = bid / a.ctas_per_op, b = bid - opi * a.ctas_per_op, B = a.ctas_per_op;
     if (opi >= nops) return;
-    if (!DCCL_BOUNDS_OK(c, B >= 1 && B <= kP2pCtas && nops <= kMaxP2pOps, 906, B)) return;   // head / tail words per pair: one per CTA
+    if (!DCCL_BOUNDS_OK(c, B >= 1 && B <= kP2pCtas && nops <= kMaxP2pOps, 1906, B)) return;   // head / tail words per pair: one per CTA
     const P2pOp op = ops[opi];
     const int r = c.rank, peer = op.peer;
     const size_t nchunks = (op.bytes + kP2pChunk - 1) / kP2pChunk;

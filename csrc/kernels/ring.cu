@@ -28,7 +28,7 @@ __device__ __forceinline__ void ring_body(const CollArgs& a, const Ctx& x) {
     const size_t stride = slots ? a.stride : g.per;
     const int next = (r + 1) % n, prev = (r + n - 1) % n;
     const bool avg = a.op == (int)ncclAvg;
-    if (!stage_extent_ok<T>(c, (size_t)(2 * n - 1) * g.slot_stride, 901)) return;   // areas 0 .. 2n-2
+    if (!stage_extent_ok<T>(c, (size_t)(2 * n - 1) * g.slot_stride, 1901)) return;   // areas 0 .. 2n-2
     T* my_stage = stage_ptr<T>(c, r, x.parity);
     T* next_stage = stage_ptr<T>(c, next, x.parity);
     auto lo_of = [&](int j) { size_t l = g.len(j); return g.blo < l ? g.blo : l; };

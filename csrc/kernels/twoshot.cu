@@ -41,7 +41,7 @@ __device__ __forceinline__ void twoshot_body(const CollArgs& a, const Ctx& x) {
                   a.count, n, x.bid, x.nb);
     if (mode == TS_ALLREDUCE || mode == TS_REDUCESCATTER || mode == TS_REDUCE) g.res_off = g.slot_stride * (size_t)n;
     const size_t stride = (mode == TS_REDUCESCATTER || mode == TS_ALLGATHER) ? a.stride : g.per;
-    if (!stage_extent_ok<T>(c, g.res_off + g.slot_stride, 900)) return;   // n receive slots and the result area
+    if (!stage_extent_ok<T>(c, g.res_off + g.slot_stride, 1900)) return;   // n receive slots and the result area
     T* my_stage = stage_ptr<T>(c, r, x.parity);
     const bool avg = a.op == (int)ncclAvg;
     auto lo_of = [&](int j) { size_t l = g.len(j); return g.blo < l ? g.blo : l; };
