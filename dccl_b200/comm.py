@@ -288,6 +288,13 @@ class Communicator:
                                   _stream_of(recv, stream)), "dcclScatter")
         return recv
 
+    def group_start(self):
+        """Same as the module-level group_start() (groups are per thread, not per communicator)."""
+        group_start()
+
+    def group_end(self):
+        group_end()
+
     def send(self, x, peer, stream=None):
         _check(lib().dccl_send(_addr(x), _numel(x), dtype_of(x), peer, self._h, _stream_of(x, stream)), "ncclSend")
 

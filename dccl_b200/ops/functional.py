@@ -224,14 +224,13 @@ class _Recv(torch.autograd.Function):
 
 def _exchange(comm, x, to, frm):
     """x goes to rank `to`, the result comes from rank `frm`; one grouped call, so a ring of these cannot deadlock."""
-    from ..comm import group_end, group_start
     out = torch.empty_like(x)
     if to == comm.rank and frm == comm.rank:
         return out.copy_(x)
-    group_start()
+    comm.group_start()
     comm.send(x, to)
     comm.recv(out, frm)
-    group_end()
+    comm.group_end()
     return out
 
 

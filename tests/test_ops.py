@@ -58,3 +58,12 @@ def test_tensor_parallel_decoder_matches_the_unsplit_one(dccl_lib, world):
     for r, p in enumerate(res):
         assert p.returncode == 0, "rank %d:\n%s\n%s" % (r, p.stdout[-3000:], p.stderr[-3000:])
         assert p.stdout.strip().splitlines()[-1].startswith("OK"), p.stdout
+
+
+def test_layers_over_torch_distributed_adapter(dccl_lib):
+    """The same worker with the collectives served by torch.distributed (gloo) through
+    dccl_b200.parallel.torch_comm.TorchDistCommunicator: the layers do not depend on which library moves the data."""
+    res = python_ranks(WORKER, ["--gloo"], 2, timeout=300)
+    for r, p in enumerate(res):
+        assert p.returncode == 0, "rank %d:\n%s\n%s" % (r, p.stdout[-3000:], p.stderr[-3000:])
+        assert p.stdout.strip().splitlines()[-1].startswith("OK"), p.stdout

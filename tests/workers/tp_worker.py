@@ -36,6 +36,13 @@ def main():
         comm = Communicator(device=local)
     else:
         comm = Communicator()
+    native = comm
+    if "--gloo" in sys.argv[1:]:      # the same layers over torch.distributed (gloo): a differential run of the layers
+        import torch.distributed as dist
+        from dccl_b200.parallel.torch_comm import TorchDistCommunicator
+        dist.init_process_group("gloo", init_method="tcp://127.0.0.1:%d" % (int(os.environ["DCCL_MASTER_PORT"]) + 1),
+                                rank=comm.rank, world_size=comm.world)
+        comm = TorchDistCommunicator()
     ops.set_default_communicator(comm)
     n, r = comm.world, comm.rank
     torch.manual_seed(1234)                          # the same "global" data on every rank
@@ -147,7 +154,10 @@ def main():
 
     if cuda:
         torch.cuda.synchronize()
-    comm.finalize()
+    if native is not comm:
+        import torch.distributed as dist
+        dist.destroy_process_group()
+    native.finalize()
     if failures:
         print("FAILED on rank %d: %s" % (r, "; ".join(failures)))
         sys.exit(1)
