@@ -5,6 +5,7 @@ the GPUs (``dccl_b200.models.llama_tp``), two activation all-reduces per block f
     python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 --master-port 29500 \
            benchmarks/train_tp.py --backend dccl
     ... benchmarks/train_tp.py --backend nccl        # the same layers, collectives through stock NCCL
+    ... benchmarks/train_tp.py --backend dccl --in-place-reduce   # forward all-reduces zero-copy on symmetric buffers
 
 Where the data-parallel benchmark (train_ddp.py) hides a few large all-reduces behind backward, this one puts
 4 x layers all-reduces of batch x seq x hidden activations (64 MB in bf16 at the default shape) on the critical
@@ -46,6 +47,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--seq", type=int, default=2048)
+    ap.add_argument("--in-place-reduce", action="store_true",
+                    help="block exits write their product into symmetric buffers that the switch reduces in place (dccl only)")
     args = ap.parse_args()
     rank, world, local = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1)), int(os.environ.get("LOCAL_RANK", 0))
     torch.cuda.set_device(local)
@@ -67,7 +70,7 @@ def main():
         comm = TorchDistCommunicator()
 
     torch.manual_seed(0)                                                            # the same unsplit weights on every rank
-    model = shard(LlamaDecoder(cfg).to(dev).to(torch.bfloat16), comm)
+    model = shard(LlamaDecoder(cfg).to(dev).to(torch.bfloat16), comm, in_place_reduce=args.in_place_reduce and args.backend == "dccl")
     params = [p for p in model.parameters()]
     opt = torch.optim.AdamW(params, lr=1e-4, fused=True)
     host_tokens = torch.randint(0, cfg.vocab_size, (args.batch, seq + 1), generator=torch.Generator().manual_seed(1)).pin_memory()
@@ -120,11 +123,12 @@ def main():
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms, 3), "ms_per_step_without_collectives": round(ms_off, 3),
             "comm_ms": round(max(0.0, ms - ms_off), 3), "allreduces_per_step": 4 * cfg.layers, "allreduce_bytes": act_bytes,
             "higher_is_better": True, "scaling": "strong", "dtype": "bf16", "data": "synthetic", "backend": args.backend,
-            "gpu_launches": int(launches),
+            "gpu_launches": int(launches), "in_place_reduce": bool(args.in_place_reduce and args.backend == "dccl"),
             "e2e": {"h2d_bytes_per_step": host_tokens.numel() * 8, "d2h_bytes_per_step": 4, "included": True},
             "config": {"model": "llama-1.1b" if args.model == "1b" else "llama-tiny", "params": cfg.num_params(), "global_batch": args.batch,
                        "seq_len": seq, "parallelism": "tp%d" % world, "kv_heads": cfg.kv_heads, "optimizer": "AdamW fused, bf16 params"},
             "final_loss": round(final_loss, 4)}))
+    model.close()
     dist.destroy_process_group()
     if args.backend == "dccl":
         comm.finalize()

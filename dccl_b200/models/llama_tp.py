@@ -13,6 +13,7 @@ import torch.nn as nn
 import torch.nn.functional as F
 
 from ..ops import functional as ops
+from ..parallel.tensor_parallel import SymmetricPool, row_linear_reduce_in_place
 from .llama import LlamaDecoder, apply_rope, rope_tables
 
 
@@ -29,8 +30,9 @@ def _cols(linear, lo, hi):
 
 
 class ShardedAttention(nn.Module):
-    def __init__(self, attn, comm):
+    def __init__(self, attn, comm, pool=None):
         super().__init__()
+        self.pool = pool
         n, r = comm.world, comm.rank
         if attn.h % n or attn.kv % n:
             raise ValueError("heads (%d) and KV heads (%d) must divide by the world size (%d)" % (attn.h, attn.kv, n))
@@ -49,12 +51,16 @@ class ShardedAttention(nn.Module):
         v = self.v(x).view(b, s, self.kv, self.hd).transpose(1, 2)
         q, k = apply_rope(q, cos, sin), apply_rope(k, cos, sin)
         out = F.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=self.kv != self.h)
-        return ops.reduce_from_region(self.o(out.transpose(1, 2).reshape(b, s, self.h * self.hd)), self.comm)
+        out = out.transpose(1, 2).reshape(b, s, self.h * self.hd)
+        if self.pool is not None:
+            return row_linear_reduce_in_place(out, self.o.weight, self.comm, self.pool)
+        return ops.reduce_from_region(self.o(out), self.comm)
 
 
 class ShardedBlock(nn.Module):
-    def __init__(self, blk, comm):
+    def __init__(self, blk, comm, pool=None):
         super().__init__()
+        self.pool = pool
         n, r = comm.world, comm.rank
         ffn = blk.gate.out_features
         if ffn % n:
@@ -62,7 +68,7 @@ class ShardedBlock(nn.Module):
         per = ffn // n
         self.comm = comm
         self.n1, self.n2 = blk.n1, blk.n2
-        self.attn = ShardedAttention(blk.attn, comm)
+        self.attn = ShardedAttention(blk.attn, comm, pool)
         self.gate = _rows(blk.gate, r * per, (r + 1) * per)
         self.up = _rows(blk.up, r * per, (r + 1) * per)
         self.down = _cols(blk.down, r * per, (r + 1) * per)
@@ -70,15 +76,25 @@ class ShardedBlock(nn.Module):
     def forward(self, x, cos, sin):
         x = x + self.attn(self.n1(x), cos, sin)
         h = ops.copy_to_region(self.n2(x), self.comm)
-        return x + ops.reduce_from_region(self.down(F.silu(self.gate(h)) * self.up(h)), self.comm)
+        h = F.silu(self.gate(h)) * self.up(h)
+        if self.pool is not None:       # the residual add consumes the pool buffer at once
+            return x + row_linear_reduce_in_place(h, self.down.weight, self.comm, self.pool)
+        return x + ops.reduce_from_region(self.down(h), self.comm)
 
 
 class ShardedLlamaDecoder(nn.Module):
-    def __init__(self, model: LlamaDecoder, comm):
+    def __init__(self, model: LlamaDecoder, comm, in_place_reduce=False):
         super().__init__()
         self.cfg, self.comm = model.cfg, comm
         self.embed, self.norm, self.head = model.embed, model.norm, model.head
-        self.blocks = nn.ModuleList([ShardedBlock(b, comm) for b in model.blocks])
+        # one pool for all blocks: both exits of a block feed a residual add, which consumes the buffer at once
+        self.pool = SymmetricPool(comm) if in_place_reduce else None
+        self.blocks = nn.ModuleList([ShardedBlock(b, comm, self.pool) for b in model.blocks])
+
+    def close(self):
+        """Give the symmetric activation buffers back (collective); call before the communicator is finalized."""
+        if self.pool is not None:
+            self.pool.close()
 
     def forward(self, tokens):
         x = self.embed(tokens)
@@ -92,6 +108,8 @@ class ShardedLlamaDecoder(nn.Module):
         return F.cross_entropy(logits.reshape(-1, logits.shape[-1]).float(), tokens[:, 1:].reshape(-1))
 
 
-def shard(model: LlamaDecoder, comm):
-    """The tensor-parallel form of `model` for this rank (the unsplit blocks are not kept)."""
-    return ShardedLlamaDecoder(model, comm)
+def shard(model: LlamaDecoder, comm, in_place_reduce=False):
+    """The tensor-parallel form of `model` for this rank (the unsplit blocks are not kept). in_place_reduce: the
+    products at the exits of attention and MLP are written into symmetric buffers and summed there by the switch
+    (no staging copies); the forward all-reduces then run zero-copy, the backward ones stay as they are."""
+    return ShardedLlamaDecoder(model, comm, in_place_reduce)

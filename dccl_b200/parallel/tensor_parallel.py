@@ -61,11 +61,12 @@ class RowParallelLinear(torch.nn.Module):
     """
 
     def __init__(self, in_features, out_features, comm, bias=True, sequence_parallel=False, seq_dim=0, seed=1,
-                 dtype=torch.float32, device="cpu"):
+                 dtype=torch.float32, device="cpu", pool=None):
         super().__init__()
         if in_features % comm.world:
             raise ValueError("in_features must split evenly over the ranks")
         self.comm, self.sequence_parallel, self.seq_dim = comm, sequence_parallel, seq_dim
+        self.pool = pool          # a SymmetricPool: the product is written into it and reduced in place (not with sequence_parallel)
         per = in_features // comm.world
         w, b = _full_weight(out_features, in_features, seed, dtype, device)
         self.weight = torch.nn.Parameter(w[:, comm.rank * per:(comm.rank + 1) * per].clone())
@@ -74,9 +75,77 @@ class RowParallelLinear(torch.nn.Module):
         self.bias = torch.nn.Parameter(b.clone()) if bias else None
 
     def forward(self, x):
+        if self.pool is not None and not self.sequence_parallel:
+            y = row_linear_reduce_in_place(x, self.weight, self.comm, self.pool)
+            return y + self.bias if self.bias is not None else y.clone()       # a fresh tensor: the pool buffer is reused
         y = torch.nn.functional.linear(x, self.weight)
         y = F.reduce_scatter(y, self.seq_dim, "sum", self.comm) if self.sequence_parallel else F.reduce_from_region(y, self.comm)
         return y + self.bias if self.bias is not None else y
+
+
+class SymmetricPool:
+    """A few reusable output buffers in symmetric memory (``dcclMemAlloc``), handed out round robin.
+
+    A matrix product that writes its result straight into one of them can be all-reduced IN PLACE by the NVSwitch
+    (``multimem.ld_reduce`` / ``multimem.st`` on the buffer itself): no staging copy in, none out. A buffer is
+    reused after ``depth`` further requests, so the result must be consumed before that (a residual add right
+    after the layer does). Without multicast, on CPU tensors or with one rank the buffers are ordinary tensors
+    and only the in-place form remains. ``close()`` gives the memory back (collective).
+    """
+
+    def __init__(self, comm, depth=4):
+        self.comm, self.depth = comm, depth
+        self._bufs, self._next, self._numel, self._dtype = [], 0, 0, None
+
+    def _symmetric(self, device):
+        return device.type == "cuda" and self.comm.world > 1 and getattr(self.comm, "has_multicast", False)
+
+    def take(self, shape, dtype, device):
+        numel = 1
+        for s in shape:
+            numel *= int(s)
+        if numel > self._numel or dtype != self._dtype:          # first use, or a larger request: every rank sees the same shapes
+            self.close()
+            self._numel, self._dtype = numel, dtype
+            for _ in range(self.depth):
+                if self._symmetric(device):
+                    self._bufs.append(self.comm.symmetric_empty(numel, dtype, device.index))
+                else:
+                    self._bufs.append(torch.empty(numel, dtype=dtype, device=device))
+        buf = self._bufs[self._next]
+        self._next = (self._next + 1) % self.depth
+        return buf[:numel].view(shape)
+
+    def close(self):
+        for b in self._bufs:
+            if hasattr(b, "_dccl_ptr"):
+                self.comm.free_symmetric(b)
+        self._bufs, self._next, self._numel = [], 0, 0
+
+
+class _RowLinearReduceInPlace(torch.autograd.Function):
+    """y = all_reduce(x W^T) with the product written into a pool buffer and reduced there."""
+
+    @staticmethod
+    def forward(ctx, x, weight, comm, pool):
+        ctx.save_for_backward(x, weight)
+        out = pool.take(tuple(x.shape[:-1]) + (weight.shape[0],), x.dtype, x.device)
+        torch.matmul(x, weight.t(), out=out)
+        comm.all_reduce(out, op="sum")
+        return out
+
+    @staticmethod
+    def backward(ctx, g):
+        x, weight = ctx.saved_tensors
+        gx = torch.matmul(g, weight) if ctx.needs_input_grad[0] else None
+        gw = torch.matmul(g.reshape(-1, g.shape[-1]).t(), x.reshape(-1, x.shape[-1])) if ctx.needs_input_grad[1] else None
+        return gx, gw, None, None
+
+
+def row_linear_reduce_in_place(x, weight, comm, pool):
+    """Exit of a tensor-parallel block without a staging copy: ``x @ weight.T`` lands in a buffer of `pool` and the
+    ranks' partial products are summed there. The result is only valid until the pool hands the buffer out again."""
+    return _RowLinearReduceInPlace.apply(x, weight, comm, pool)
 
 
 def sync_replicated_grads(params, comm):

@@ -28,11 +28,8 @@ def main():
     cfg = LlamaConfig(vocab_size=128, hidden=64, layers=2, heads=4, kv_heads=2 if n <= 2 else 4, ffn=96 if n != 4 else 128, max_seq=32)
     full = LlamaDecoder(cfg).to(dev)
     tokens = torch.randint(0, cfg.vocab_size, (2, 17)).to(dev)
-    tp = shard(copy.deepcopy(full), comm)
     ref_loss = full.loss(tokens)
     ref_loss.backward()
-    loss = tp.loss(tokens)
-    loss.backward()
     ok = True
 
     def check(a, b, what):
@@ -41,17 +38,28 @@ def main():
             ok = False
             print("rank %d: %s differs by %g" % (r, what, (a - b).abs().max().item()))
 
-    check(loss.detach(), ref_loss.detach(), "loss")
-    check(tp.embed.weight.grad, full.embed.weight.grad, "embedding gradient")
-    check(tp.head.weight.grad, full.head.weight.grad, "head gradient")
-    for i, (tb, fb) in enumerate(zip(tp.blocks, full.blocks)):
-        check(tb.n1.weight.grad, fb.n1.weight.grad, "block %d norm gradient" % i)
-        qw = tb.attn.h * tb.attn.hd
-        per = tb.gate.out_features
-        check(tb.attn.q.weight.grad, fb.attn.q.weight.grad[r * qw:(r + 1) * qw], "block %d q gradient" % i)
-        check(tb.attn.o.weight.grad, fb.attn.o.weight.grad[:, r * qw:(r + 1) * qw], "block %d o gradient" % i)
-        check(tb.gate.weight.grad, fb.gate.weight.grad[r * per:(r + 1) * per], "block %d gate gradient" % i)
-        check(tb.down.weight.grad, fb.down.weight.grad[:, r * per:(r + 1) * per], "block %d down gradient" % i)
+    # plain form, and the form whose block exits write into pool buffers that are reduced in place
+    for in_place in (False, True):
+        tag = "in-place " if in_place else ""
+        clean = copy.deepcopy(full)
+        clean.zero_grad(set_to_none=True)
+        tp = shard(clean, comm, in_place_reduce=in_place)
+        loss = tp.loss(tokens)
+        loss.backward()
+        check(loss.detach(), ref_loss.detach(), tag + "loss")
+        check(tp.embed.weight.grad, full.embed.weight.grad, tag + "embedding gradient")
+        check(tp.head.weight.grad, full.head.weight.grad, tag + "head gradient")
+        for i, (tb, fb) in enumerate(zip(tp.blocks, full.blocks)):
+            check(tb.n1.weight.grad, fb.n1.weight.grad, tag + "block %d norm gradient" % i)
+            qw = tb.attn.h * tb.attn.hd
+            per = tb.gate.out_features
+            check(tb.attn.q.weight.grad, fb.attn.q.weight.grad[r * qw:(r + 1) * qw], tag + "block %d q gradient" % i)
+            check(tb.attn.o.weight.grad, fb.attn.o.weight.grad[:, r * qw:(r + 1) * qw], tag + "block %d o gradient" % i)
+            check(tb.gate.weight.grad, fb.gate.weight.grad[r * per:(r + 1) * per], tag + "block %d gate gradient" % i)
+            check(tb.down.weight.grad, fb.down.weight.grad[:, r * per:(r + 1) * per], tag + "block %d down gradient" % i)
+        if dev != "cpu":
+            torch.cuda.synchronize()
+        tp.close()
     if dev != "cpu":
         torch.cuda.synchronize()
     comm.finalize()
