@@ -13,7 +13,7 @@ import torch.nn as nn
 import torch.nn.functional as F
 
 from ..ops import functional as ops
-from ..parallel.tensor_parallel import SymmetricPool, row_linear_reduce_in_place
+from ..parallel.tensor_parallel import SymmetricPool, column_linears_reduce_grad_in_place, row_linear_reduce_in_place
 from .llama import LlamaDecoder, apply_rope, rope_tables
 
 
@@ -45,10 +45,14 @@ class ShardedAttention(nn.Module):
 
     def forward(self, x, cos, sin):
         b, s, _ = x.shape
-        x = ops.copy_to_region(x, self.comm)
-        q = self.q(x).view(b, s, self.h, self.hd).transpose(1, 2)
-        k = self.k(x).view(b, s, self.kv, self.hd).transpose(1, 2)
-        v = self.v(x).view(b, s, self.kv, self.hd).transpose(1, 2)
+        if self.pool is not None:
+            q, k, v = column_linears_reduce_grad_in_place(x, (self.q.weight, self.k.weight, self.v.weight), self.comm, self.pool)
+        else:
+            x = ops.copy_to_region(x, self.comm)
+            q, k, v = self.q(x), self.k(x), self.v(x)
+        q = q.view(b, s, self.h, self.hd).transpose(1, 2)
+        k = k.view(b, s, self.kv, self.hd).transpose(1, 2)
+        v = v.view(b, s, self.kv, self.hd).transpose(1, 2)
         q, k = apply_rope(q, cos, sin), apply_rope(k, cos, sin)
         out = F.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=self.kv != self.h)
         out = out.transpose(1, 2).reshape(b, s, self.h * self.hd)
@@ -75,11 +79,11 @@ class ShardedBlock(nn.Module):
 
     def forward(self, x, cos, sin):
         x = x + self.attn(self.n1(x), cos, sin)
+        if self.pool is not None:       # the residual add (forward) and the norm's backward consume the pool buffers at once
+            g, u = column_linears_reduce_grad_in_place(self.n2(x), (self.gate.weight, self.up.weight), self.comm, self.pool)
+            return x + row_linear_reduce_in_place(F.silu(g) * u, self.down.weight, self.comm, self.pool)
         h = ops.copy_to_region(self.n2(x), self.comm)
-        h = F.silu(self.gate(h)) * self.up(h)
-        if self.pool is not None:       # the residual add consumes the pool buffer at once
-            return x + row_linear_reduce_in_place(h, self.down.weight, self.comm, self.pool)
-        return x + ops.reduce_from_region(self.down(h), self.comm)
+        return x + ops.reduce_from_region(self.down(F.silu(self.gate(h)) * self.up(h)), self.comm)
 
 
 class ShardedLlamaDecoder(nn.Module):
@@ -110,6 +114,6 @@ class ShardedLlamaDecoder(nn.Module):
 
 def shard(model: LlamaDecoder, comm, in_place_reduce=False):
     """The tensor-parallel form of `model` for this rank (the unsplit blocks are not kept). in_place_reduce: the
-    products at the exits of attention and MLP are written into symmetric buffers and summed there by the switch
-    (no staging copies); the forward all-reduces then run zero-copy, the backward ones stay as they are."""
+    products at the exits of attention and MLP (forward) and the input gradients at their entries (backward) are
+    written into symmetric buffers and summed there by the switch: all four all-reduces of a block run zero-copy."""
     return ShardedLlamaDecoder(model, comm, in_place_reduce)

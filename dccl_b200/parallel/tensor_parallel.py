@@ -148,6 +148,39 @@ def row_linear_reduce_in_place(x, weight, comm, pool):
     return _RowLinearReduceInPlace.apply(x, weight, comm, pool)
 
 
+class _ColumnLinearsReduceGradInPlace(torch.autograd.Function):
+    """(x W_1^T, ..., x W_k^T) for the column-parallel layers that share the input of a tensor-parallel block; in
+    backward the input gradient sum_i g_i W_i is accumulated in a pool buffer and summed over the ranks there."""
+
+    @staticmethod
+    def forward(ctx, x, comm, pool, *weights):
+        ctx.comm, ctx.pool = comm, pool
+        ctx.save_for_backward(x, *weights)
+        return tuple(torch.matmul(x, w.t()) for w in weights)
+
+    @staticmethod
+    def backward(ctx, *gs):
+        x, *weights = ctx.saved_tensors
+        gx = None
+        if ctx.needs_input_grad[0]:
+            gx = ctx.pool.take(tuple(x.shape), x.dtype, x.device)
+            flat = gx.view(-1, x.shape[-1])
+            torch.matmul(gs[0].reshape(-1, gs[0].shape[-1]), weights[0], out=flat)
+            for g, w in zip(gs[1:], weights[1:]):
+                flat.addmm_(g.reshape(-1, g.shape[-1]), w)
+            ctx.comm.all_reduce(gx, op="sum")
+        x2 = x.reshape(-1, x.shape[-1])
+        gws = tuple(torch.matmul(g.reshape(-1, g.shape[-1]).t(), x2) for g in gs)
+        return (gx, None, None) + gws
+
+
+def column_linears_reduce_grad_in_place(x, weights, comm, pool):
+    """Entry of a tensor-parallel block without a staging copy in backward: returns ``x @ W.T`` for every W in
+    `weights` (no bias); the gradient of `x` is built in a buffer of `pool` and summed over the ranks in place. It is
+    only valid until the pool hands the buffer out again (the backward of the preceding norm consumes it at once)."""
+    return _ColumnLinearsReduceGradInPlace.apply(x, comm, pool, *weights)
+
+
 def sync_replicated_grads(params, comm):
     """Sum the gradients of parameters that are replicated over the ranks but saw only a part of the batch or
     sequence (biases and norms under sequence parallelism). One all-reduce over the flattened gradients."""
