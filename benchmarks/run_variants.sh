@@ -3,7 +3,8 @@
 #   benchmarks/run_variants.sh 8 [out_dir=results/variants]
 # Runs: mid-size all-reduce (table / twoshot_ll / NCCL, ordinary and symmetric buffers), large all-reduce and
 # reduce-scatter on peer-addressable buffers (table / zero-copy two-shot, symmetric and registered), broadcast and
-# reduce with and without the pipelined switch form, graph replay latency. The files feed make_tune_table.py.
+# reduce with and without the pipelined switch form, graph replay latency, the tensor-parallel training step over NCCL /
+# this library / this library reducing in place. The sweep files feed make_tune_table.py.
 set -u
 N=${1:-8}; OUT=${2:-results/variants}
 ROOT=$(cd "$(dirname "$0")/.." && pwd)
@@ -33,4 +34,11 @@ DCCL_REDUCE_ALGORITHM=twoshot_ll run extra_reduce_ll $TORCHRUN "$ROOT/bench.py" 
 
 # eager launches against CUDA-graph replay
 run graph_latency $TORCHRUN "$ROOT/benchmarks/graph_latency.py" --out "$OUT/graph_latency.json"
+
+# tensor-parallel training step: stock NCCL, this library on ordinary buffers, this library reducing in place
+for ARM in "nccl" "dccl" "dccl --in-place-reduce"; do
+    NAME=train_tp_$(echo $ARM | tr -d ' -' )
+    run $NAME $TORCHRUN "$ROOT/benchmarks/train_tp.py" --backend $ARM --steps 8 --warmup 3
+    grep -h '"metric"' "$OUT/$NAME.log" | tail -n 1
+done
 ls -la "$OUT"
