@@ -57,6 +57,7 @@ int dccl_has_multicast(void* comm) { dcclComm* c = (dcclComm*)comm; return c && 
 unsigned long long dccl_launch_count(void* comm) { dcclComm* c = (dcclComm*)comm; return c && c->gpu ? c->gpu->launches() : 0ull; }
 int dccl_comm_set_param(void* comm, const char* name, int value) { dcclComm* c = (dcclComm*)comm; return c && c->gpu && c->gpu->set_param(name, value) ? 0 : (int)ncclInvalidArgument; }
 int dccl_cuda_device_count() { return cuda_device_count(); }
+int dccl_barrier(void* comm) { GUARD(dcclBarrier((ncclComm_t)comm)); }
 int dccl_debug_check(void* comm) { GUARD(dcclDebugCheck((ncclComm_t)comm)); }
 int dccl_topology_json(void* comm, char* out, size_t len) { GUARD(dcclGetTopology((ncclComm_t)comm, out, len)); }
 #ifdef DCCL_WITH_CUDA

@@ -477,6 +477,17 @@ ncclResult_t dcclGetTopology(ncclComm_t comm, char* json, size_t len) {
     return ncclSuccess;
 }
 
+ncclResult_t dcclBarrier(ncclComm_t comm) {
+    VALIDATE_COMM(comm);
+    if (comm->bs.world() == 1) return ncclSuccess;
+    if (!comm->bs.barrier()) {
+        comm->host_error = ncclRemoteError;
+        comm->host_error_msg = "barrier failed: " + comm->bs.last_error();
+        return ncclRemoteError;
+    }
+    return ncclSuccess;
+}
+
 ncclResult_t dcclDebugCheck(ncclComm_t comm) {
     VALIDATE_COMM(comm);
     if (!comm->gpu) return ncclSuccess;

@@ -36,6 +36,7 @@ def _declare(lib):
         "dccl_comm_abort": (i, [vp]),
         "dccl_topology_json": (i, [vp, cp, sz]),
         "dccl_debug_check": (i, [vp]),
+        "dccl_barrier": (i, [vp]),
         "dccl_selftest_fd_exchange": (i, [vp]),
         "dccl_comm_shrink": (i, [vp, c.POINTER(vp)]),
         "dccl_world_size": (i, [vp]),

@@ -185,6 +185,10 @@ class Communicator:
         _check(lib().dccl_topology_json(self._h, buf, len(buf)), "dcclGetTopology")
         return json.loads(buf.value.decode())
 
+    def barrier(self):
+        """Host-side barrier over the control plane (does not wait for CUDA streams)."""
+        _check(lib().dccl_barrier(self._h), "dcclBarrier")
+
     def debug_check(self):
         """With DCCL_DEBUG_BOUNDS=1: raise when a kernel wrote into the unused parts of this rank's device pool
         (the message names the gap and the offset). No-op otherwise."""

@@ -247,6 +247,14 @@ ncclResult_t  dcclSetAlgorithm(ncclComm_t comm, const char* collective, const ch
 ncclResult_t  dcclGetTopology(ncclComm_t comm, char* json, size_t len);
 
 /**
+ * Host-side barrier over the control plane: returns when every rank of the communicator has called it (the
+ * counterpart of the group barrier the original's tools take from Derecho, reference
+ * src/application/p2p_perf.cpp:287). It does not wait for work queued on CUDA streams; synchronise the stream first
+ * where that matters. ncclRemoteError when a rank failed or the group was aborted while waiting.
+ */
+ncclResult_t  dcclBarrier(ncclComm_t comm);
+
+/**
  * Debug aid. With `DCCL/debug_bounds = 1` (DCCL_DEBUG_BOUNDS=1) the unused bytes between the regions of the
  * communicator's device pool hold guard words; this call reads them back and returns ncclInternalError when a
  * kernel wrote there (dcclGetLastError then says where). ncclSuccess when intact, when guarding is off and when

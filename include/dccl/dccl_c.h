@@ -36,6 +36,7 @@ int dccl_has_multicast(void* comm);
 unsigned long long dccl_launch_count(void* comm);
 int dccl_comm_set_param(void* comm, const char* name, int value);
 int dccl_cuda_device_count(void);
+int dccl_barrier(void* comm);                                       /* host-side barrier over the control plane */
 int dccl_debug_check(void* comm);                                   /* guard words of the device pool (DCCL_DEBUG_BOUNDS=1) */
 int dccl_topology_json(void* comm, char* out, size_t len);         /* GPUs, peer access, NVLink links, multicast */
 int dccl_nvml_link_report(const char* nvml_library, char* out, size_t len);   /* NVML only; CUDA builds */

@@ -161,6 +161,13 @@ def main():
     from dccl_b200._lib import lib as _native
     check(_native().dccl_selftest_fd_exchange(comm._h) == 0, "descriptor exchange between all ranks")
     check(_native().dccl_debug_check(comm._h) == 0, "pool check without a device side is a success")
+    # barrier: nobody passes before the last rank has arrived (the last rank arrives 0.3 s late)
+    import time
+    t0 = time.monotonic()
+    if rank == world - 1:
+        time.sleep(0.3)
+    comm.barrier()
+    check(world == 1 or rank == world - 1 or time.monotonic() - t0 > 0.25, "barrier waits for the last rank")
 
     # the symmetric allocator over a stand-in driver (memfd + mmap): every rank maps every peer's segment and reads it;
     # then with one rank's allocation failing: everybody must come back with a failure, nobody may hang
