@@ -106,5 +106,9 @@ def test_range_checking_build_refuses_before_it_touches_memory():
     if not os.path.exists(path):
         pytest.skip("build-bounds/libdccl.so is not built (make BOUNDS=1 lib)")
     env = dict(os.environ, DCCL_LIBRARY=path)
+    probe = subprocess.run([sys.executable, "-c", "import sys; sys.path.insert(0, %r); from dccl_b200 import _lib; _lib.lib()" % root],
+                           env=env, capture_output=True, text=True, timeout=300)
+    if probe.returncode != 0:
+        pytest.skip("build-bounds/libdccl.so does not match the bindings (rebuild it: make BOUNDS=1 lib)")
     p = subprocess.run([sys.executable, os.path.join(root, "tests", "workers", "bounds_worker.py")], env=env, capture_output=True, text=True, timeout=600)
     assert p.returncode == 0 and "bounds worker: ok" in p.stdout, p.stdout[-2000:] + p.stderr[-2000:]
