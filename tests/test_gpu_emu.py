@@ -272,6 +272,7 @@ def test_paths_not_yet_run_on_hardware_in_a_child_process():
     import subprocess
     import sys
     here = os.path.dirname(os.path.abspath(__file__))
-    p = subprocess.run([sys.executable, "-m", "pytest", os.path.join(here, "first_run_emu.py"), "-q", "-x", "-p", "no:cacheprovider"],
+    p = subprocess.run([sys.executable, "-m", "pytest", os.path.join(here, "first_run_emu.py"), "-q", "-rA", "-p", "no:cacheprovider"],
                        capture_output=True, text=True, timeout=1200)
-    assert p.returncode == 0, p.stdout[-3000:] + p.stderr[-2000:]
+    print(p.stdout[-6000:])       # which of them passed, for the report (-rA)
+    assert p.returncode == 0, p.stdout[-6000:] + p.stderr[-2000:]
