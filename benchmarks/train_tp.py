@@ -49,6 +49,7 @@ def main():
     ap.add_argument("--seq", type=int, default=2048)
     ap.add_argument("--in-place-reduce", action="store_true",
                     help="block exits write their product into symmetric buffers that the switch reduces in place (dccl only)")
+    ap.add_argument("--vocab-parallel", action="store_true", help="embedding, head and loss split over the vocabulary as well")
     args = ap.parse_args()
     rank, world, local = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1)), int(os.environ.get("LOCAL_RANK", 0))
     torch.cuda.set_device(local)
@@ -70,7 +71,8 @@ def main():
         comm = TorchDistCommunicator()
 
     torch.manual_seed(0)                                                            # the same unsplit weights on every rank
-    model = shard(LlamaDecoder(cfg).to(dev).to(torch.bfloat16), comm, in_place_reduce=args.in_place_reduce and args.backend == "dccl")
+    model = shard(LlamaDecoder(cfg).to(dev).to(torch.bfloat16), comm, in_place_reduce=args.in_place_reduce and args.backend == "dccl",
+                  vocab_parallel=args.vocab_parallel)
     params = [p for p in model.parameters()]
     opt = torch.optim.AdamW(params, lr=1e-4, fused=True)
     host_tokens = torch.randint(0, cfg.vocab_size, (args.batch, seq + 1), generator=torch.Generator().manual_seed(1)).pin_memory()
@@ -126,7 +128,7 @@ def main():
             "gpu_launches": int(launches), "in_place_reduce": bool(args.in_place_reduce and args.backend == "dccl"),
             "e2e": {"h2d_bytes_per_step": host_tokens.numel() * 8, "d2h_bytes_per_step": 4, "included": True},
             "config": {"model": "llama-1.1b" if args.model == "1b" else "llama-tiny", "params": cfg.num_params(), "global_batch": args.batch,
-                       "seq_len": seq, "parallelism": "tp%d" % world, "kv_heads": cfg.kv_heads, "optimizer": "AdamW fused, bf16 params"},
+                       "seq_len": seq, "parallelism": "tp%d" % world, "kv_heads": cfg.kv_heads, "vocab_parallel": bool(args.vocab_parallel), "optimizer": "AdamW fused, bf16 params"},
             "final_loss": round(final_loss, 4)}))
     model.close()
     dist.destroy_process_group()

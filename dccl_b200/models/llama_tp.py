@@ -86,11 +86,53 @@ class ShardedBlock(nn.Module):
         return x + ops.reduce_from_region(self.down(F.silu(self.gate(h)) * self.up(h)), self.comm)
 
 
+class VocabParallelEmbedding(nn.Module):
+    """Rows [rank * V / n, (rank + 1) * V / n) of the embedding table; tokens of other ranks' rows contribute zeros and
+    the partial results are summed (forward all-reduce, identity backward: every rank updates its own rows)."""
+
+    def __init__(self, embed, comm):
+        super().__init__()
+        n, r = comm.world, comm.rank
+        if embed.num_embeddings % n:
+            raise ValueError("the vocabulary (%d) must divide by the world size (%d)" % (embed.num_embeddings, n))
+        self.comm, self.per = comm, embed.num_embeddings // n
+        self.lo = r * self.per
+        self.weight = nn.Parameter(embed.weight.data[self.lo:self.lo + self.per].clone())
+
+    def forward(self, tokens):
+        local = tokens - self.lo
+        mine = (local >= 0) & (local < self.per)
+        out = F.embedding(local.clamp(0, self.per - 1), self.weight) * mine.unsqueeze(-1).to(self.weight.dtype)
+        return ops.reduce_from_region(out, self.comm)
+
+
+def vocab_parallel_cross_entropy(logits_local, targets, lo, comm):
+    """Mean cross entropy over rows of logits whose columns are split over the ranks (this rank holds the classes
+    [lo, lo + logits_local.shape[-1])). Three small all-reduces: the row maximum, the sum of exponentials and the
+    logit of the target class; the full row of logits never exists on one rank."""
+    x = logits_local.float()
+    per = x.shape[-1]
+    m = x.detach().amax(-1)
+    comm.all_reduce(m, op="max")
+    s = ops.reduce_from_region(torch.exp(x - m.unsqueeze(-1)).sum(-1), comm)
+    local = targets - lo
+    mine = (local >= 0) & (local < per)
+    t = x.gather(-1, local.clamp(0, per - 1).unsqueeze(-1)).squeeze(-1) * mine.to(x.dtype)
+    t = ops.reduce_from_region(t, comm)
+    return (torch.log(s) + m - t).mean()
+
+
 class ShardedLlamaDecoder(nn.Module):
-    def __init__(self, model: LlamaDecoder, comm, in_place_reduce=False):
+    def __init__(self, model: LlamaDecoder, comm, in_place_reduce=False, vocab_parallel=False):
         super().__init__()
         self.cfg, self.comm = model.cfg, comm
         self.embed, self.norm, self.head = model.embed, model.norm, model.head
+        self.vocab_parallel = vocab_parallel
+        if vocab_parallel:
+            per = model.cfg.vocab_size // comm.world
+            self.embed = VocabParallelEmbedding(model.embed, comm)
+            self.head = _rows(model.head, comm.rank * per, (comm.rank + 1) * per)
+            self.vocab_lo = comm.rank * per
         # one pool for all blocks: both exits of a block feed a residual add, which consumes the buffer at once
         self.pool = SymmetricPool(comm) if in_place_reduce else None
         self.blocks = nn.ModuleList([ShardedBlock(b, comm, self.pool) for b in model.blocks])
@@ -105,15 +147,22 @@ class ShardedLlamaDecoder(nn.Module):
         cos, sin = rope_tables(tokens.shape[1], self.cfg.hidden // self.cfg.heads, self.cfg.rope_theta, tokens.device)
         for blk in self.blocks:
             x = blk(x, cos, sin)
-        return self.head(self.norm(x))
+        x = self.norm(x)
+        if self.vocab_parallel:        # this rank's slice of the classes
+            return self.head(ops.copy_to_region(x, self.comm))
+        return self.head(x)
 
     def loss(self, tokens):
         logits = self.forward(tokens[:, :-1])
+        if self.vocab_parallel:
+            return vocab_parallel_cross_entropy(logits.reshape(-1, logits.shape[-1]), tokens[:, 1:].reshape(-1), self.vocab_lo, self.comm)
         return F.cross_entropy(logits.reshape(-1, logits.shape[-1]).float(), tokens[:, 1:].reshape(-1))
 
 
-def shard(model: LlamaDecoder, comm, in_place_reduce=False):
+def shard(model: LlamaDecoder, comm, in_place_reduce=False, vocab_parallel=False):
     """The tensor-parallel form of `model` for this rank (the unsplit blocks are not kept). in_place_reduce: the
     products at the exits of attention and MLP (forward) and the input gradients at their entries (backward) are
-    written into symmetric buffers and summed there by the switch: all four all-reduces of a block run zero-copy."""
-    return ShardedLlamaDecoder(model, comm, in_place_reduce)
+    written into symmetric buffers and summed there by the switch: all four all-reduces of a block run zero-copy.
+    vocab_parallel: embedding table and output head are split over the vocabulary as well and the loss is computed from
+    the split logits (`vocab_parallel_cross_entropy`); forward() then returns this rank's slice of the logits."""
+    return ShardedLlamaDecoder(model, comm, in_place_reduce, vocab_parallel)

@@ -39,16 +39,18 @@ def main():
             print("rank %d: %s differs by %g" % (r, what, (a - b).abs().max().item()))
 
     # plain form, and the form whose block exits write into pool buffers that are reduced in place
-    for in_place in (False, True):
-        tag = "in-place " if in_place else ""
+    for in_place, vocab in ((False, False), (True, False), (False, True), (True, True)):
+        tag = ("in-place " if in_place else "") + ("vocab-parallel " if vocab else "")
         clean = copy.deepcopy(full)
         clean.zero_grad(set_to_none=True)
-        tp = shard(clean, comm, in_place_reduce=in_place)
+        tp = shard(clean, comm, in_place_reduce=in_place, vocab_parallel=vocab)
         loss = tp.loss(tokens)
         loss.backward()
         check(loss.detach(), ref_loss.detach(), tag + "loss")
-        check(tp.embed.weight.grad, full.embed.weight.grad, tag + "embedding gradient")
-        check(tp.head.weight.grad, full.head.weight.grad, tag + "head gradient")
+        vs = slice(r * (cfg.vocab_size // n), (r + 1) * (cfg.vocab_size // n)) if vocab else slice(None)
+        check(tp.embed.weight.grad, full.embed.weight.grad[vs], tag + "embedding gradient")
+        check(tp.head.weight.grad, full.head.weight.grad[vs], tag + "head gradient")
+        check(tp.norm.weight.grad, full.norm.weight.grad, tag + "final norm gradient")
         for i, (tb, fb) in enumerate(zip(tp.blocks, full.blocks)):
             check(tb.n1.weight.grad, fb.n1.weight.grad, tag + "block %d norm gradient" % i)
             qw = tb.attn.h * tb.attn.hd
