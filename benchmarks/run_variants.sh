@@ -36,7 +36,7 @@ DCCL_REDUCE_ALGORITHM=twoshot_ll run extra_reduce_ll $TORCHRUN "$ROOT/bench.py" 
 run graph_latency $TORCHRUN "$ROOT/benchmarks/graph_latency.py" --out "$OUT/graph_latency.json"
 
 # tensor-parallel training step: stock NCCL, this library on ordinary buffers, this library reducing in place
-for ARM in "nccl" "dccl" "dccl --in-place-reduce"; do
+for ARM in "nccl" "dccl" "dccl --in-place-reduce" "nccl --sequence-parallel" "dccl --sequence-parallel"; do
     NAME=train_tp_$(echo $ARM | tr -d ' -' )
     run $NAME $TORCHRUN "$ROOT/benchmarks/train_tp.py" --backend $ARM --steps 8 --warmup 3
     grep -h '"metric"' "$OUT/$NAME.log" | tail -n 1

@@ -5,7 +5,8 @@ the GPUs (``dccl_b200.models.llama_tp``), two activation all-reduces per block f
     python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 --master-port 29500 \
            benchmarks/train_tp.py --backend dccl
     ... benchmarks/train_tp.py --backend nccl        # the same layers, collectives through stock NCCL
-    ... benchmarks/train_tp.py --backend dccl --in-place-reduce   # forward all-reduces zero-copy on symmetric buffers
+    ... benchmarks/train_tp.py --backend dccl --in-place-reduce   # all-reduces zero-copy on symmetric buffers
+    ... benchmarks/train_tp.py --backend dccl --sequence-parallel # all-gather + reduce-scatter instead of all-reduce
 
 Where the data-parallel benchmark (train_ddp.py) hides a few large all-reduces behind backward, this one puts
 4 x layers all-reduces of batch x seq x hidden activations (64 MB in bf16 at the default shape) on the critical
@@ -38,6 +39,14 @@ class NoComm:
             recv.copy_(send)
         return recv
 
+    def all_gather(self, send, recv, stream=None):
+        recv.view(self.world, -1).copy_(send.reshape(1, -1).expand(self.world, -1))
+        return recv
+
+    def reduce_scatter(self, send, recv, op="sum", stream=None):
+        recv.view(-1).copy_(send.view(self.world, -1)[self.rank])
+        return recv
+
 
 def main():
     ap = argparse.ArgumentParser()
@@ -50,6 +59,8 @@ def main():
     ap.add_argument("--in-place-reduce", action="store_true",
                     help="block exits write their product into symmetric buffers that the switch reduces in place (dccl only)")
     ap.add_argument("--vocab-parallel", action="store_true", help="embedding, head and loss split over the vocabulary as well")
+    ap.add_argument("--sequence-parallel", action="store_true",
+                    help="activations between the blocks split along the sequence: all-gather + reduce-scatter instead of all-reduce")
     args = ap.parse_args()
     rank, world, local = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1)), int(os.environ.get("LOCAL_RANK", 0))
     torch.cuda.set_device(local)
@@ -72,7 +83,7 @@ def main():
 
     torch.manual_seed(0)                                                            # the same unsplit weights on every rank
     model = shard(LlamaDecoder(cfg).to(dev).to(torch.bfloat16), comm, in_place_reduce=args.in_place_reduce and args.backend == "dccl",
-                  vocab_parallel=args.vocab_parallel)
+                  vocab_parallel=args.vocab_parallel, sequence_parallel=args.sequence_parallel)
     params = [p for p in model.parameters()]
     opt = torch.optim.AdamW(params, lr=1e-4, fused=True)
     host_tokens = torch.randint(0, cfg.vocab_size, (args.batch, seq + 1), generator=torch.Generator().manual_seed(1)).pin_memory()
@@ -89,6 +100,7 @@ def main():
         tokens.copy_(host_tokens, non_blocking=True)
         loss = model.loss(tokens)
         loss.backward()
+        model.sync_replicated_grads()       # sequence parallel only; nothing otherwise
         opt.step()
         opt.zero_grad(set_to_none=False)
         losses.append(loss.item())
@@ -128,8 +140,8 @@ def main():
             "gpu_launches": int(launches), "in_place_reduce": bool(args.in_place_reduce and args.backend == "dccl"),
             "e2e": {"h2d_bytes_per_step": host_tokens.numel() * 8, "d2h_bytes_per_step": 4, "included": True},
             "config": {"model": "llama-1.1b" if args.model == "1b" else "llama-tiny", "params": cfg.num_params(), "global_batch": args.batch,
-                       "seq_len": seq, "parallelism": "tp%d" % world, "kv_heads": cfg.kv_heads, "vocab_parallel": bool(args.vocab_parallel), "optimizer": "AdamW fused, bf16 params"},
-            "final_loss": round(final_loss, 4)}))
+                       "seq_len": seq, "parallelism": "tp%d" % world, "kv_heads": cfg.kv_heads, "vocab_parallel": bool(args.vocab_parallel), "sequence_parallel": bool(args.sequence_parallel), "optimizer": "AdamW fused, bf16 params"},
+            "final_loss": round(final_loss, 4), "final_loss_is_rank0_share": bool(args.sequence_parallel)}))
     model.close()
     dist.destroy_process_group()
     if args.backend == "dccl":

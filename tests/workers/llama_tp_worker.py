@@ -62,6 +62,30 @@ def main():
         if dev != "cpu":
             torch.cuda.synchronize()
         tp.close()
+    # sequence parallel: 16 positions split over the ranks; the ranks' loss shares add up to the loss, the replicated
+    # parameters' gradients are partial sums until they are synchronised
+    clean = copy.deepcopy(full)
+    clean.zero_grad(set_to_none=True)
+    sp = shard(clean, comm, sequence_parallel=True)
+    part = sp.loss(tokens)
+    part.backward()
+    sp.sync_replicated_grads()
+    whole = part.detach().clone()
+    comm.all_reduce(whole, op="sum")
+    check(whole, ref_loss.detach(), "sequence-parallel loss")
+    check(sp.embed.weight.grad, full.embed.weight.grad, "sequence-parallel embedding gradient")
+    check(sp.head.weight.grad, full.head.weight.grad, "sequence-parallel head gradient")
+    check(sp.norm.weight.grad, full.norm.weight.grad, "sequence-parallel final norm gradient")
+    for i, (tb, fb) in enumerate(zip(sp.blocks, full.blocks)):
+        qw = tb.attn.h * tb.attn.hd
+        per = tb.gate.out_features
+        check(tb.n1.weight.grad, fb.n1.weight.grad, "sequence-parallel block %d norm gradient" % i)
+        check(tb.n2.weight.grad, fb.n2.weight.grad, "sequence-parallel block %d second norm gradient" % i)
+        check(tb.attn.q.weight.grad, fb.attn.q.weight.grad[r * qw:(r + 1) * qw], "sequence-parallel block %d q gradient" % i)
+        check(tb.attn.o.weight.grad, fb.attn.o.weight.grad[:, r * qw:(r + 1) * qw], "sequence-parallel block %d o gradient" % i)
+        check(tb.up.weight.grad, fb.up.weight.grad[r * per:(r + 1) * per], "sequence-parallel block %d up gradient" % i)
+        check(tb.down.weight.grad, fb.down.weight.grad[:, r * per:(r + 1) * per], "sequence-parallel block %d down gradient" % i)
+
     if dev != "cpu":
         torch.cuda.synchronize()
     comm.finalize()
