@@ -193,3 +193,11 @@ def test_cmake_build_install_and_find_package(tmp_path):
     env = dict(os.environ, DCCL_RANK="0", DCCL_WORLD_SIZE="1")
     p = subprocess.run([str(hdir / "helloworld")], env=env, capture_output=True, text=True, timeout=60)
     assert p.returncode == 0 and "world size = 1, my rank = 0" in p.stdout, p.stdout + p.stderr
+
+
+def test_python_examples(dccl_lib):
+    """examples/python: all-reduce on host arrays over 4 ranks, a tensor-parallel MLP training for a few steps on 2."""
+    for script, world in (("allreduce.py", 4), ("tensor_parallel_mlp.py", 2)):
+        res = python_ranks(os.path.join(ROOT, "examples", "python", script), [], world, timeout=300)
+        for r, p in enumerate(res):
+            assert p.returncode == 0, "%s rank %d:\n%s\n%s" % (script, r, p.stdout[-2000:], p.stderr[-2000:])
