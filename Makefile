@@ -6,6 +6,9 @@
 #                        a compiler wrapper that links statically may lack the sanitizer runtimes)
 #   make BOUNDS=1        debug build of the device code in build-bounds/: every kernel checks the pool ranges it is
 #                        about to use and reports DEV_BOUNDS instead of touching memory outside them
+#   make SIM=1 lib       host simulation of the non-multimem kernels in build-sim/: the kernel sources compiled as C++,
+#                        every CUDA thread an OS thread; the single-GPU emulation tests then run without a GPU
+#                        (DCCL_LIBRARY=build-sim/libdccl.so, see tests/test_kernel_sim.py)
 #   make install PREFIX=/opt/dccl         headers, library, tools, CMake package file
 #
 # Everything lands in build/; the shared library is also copied into the Python
@@ -35,6 +38,10 @@ ifdef BOUNDS
 NVCCFLAGS += -DDCCL_DEBUG_BOUNDS
 BUILD := build-bounds
 endif
+ifdef SIM
+CUDA := 0
+BUILD := build-sim
+endif
 ifdef SANITIZE
 CUDA := 0
 CXXFLAGS += -fsanitize=$(SANITIZE) -fno-omit-frame-pointer -g
@@ -57,6 +64,17 @@ CUDA_LIBS :=
 TOOL_DEFS :=
 endif
 
+ifdef SIM
+HOST_SRCS += csrc/sim/sim_runtime.cpp
+CU_SRCS := csrc/gpu/emu.cu csrc/gpu/canary.cu csrc/kernels/twoshot.cu csrc/kernels/ring.cu csrc/kernels/hd.cu csrc/kernels/direct.cu \
+           csrc/kernels/oneshot_ll.cu csrc/kernels/ll_collectives.cu csrc/kernels/ll_twoshot.cu csrc/kernels/p2p.cu
+# -O2 and no strict aliasing: the kernels reinterpret 16-byte vectors the way device code does
+SIM_FLAGS := -Icsrc/sim/include -DDCCL_HOST_SIM -fno-strict-aliasing -Wno-attributes -Wno-unknown-pragmas -Wno-maybe-uninitialized
+ifdef BOUNDS
+SIM_FLAGS += -DDCCL_DEBUG_BOUNDS
+BUILD := build-sim-bounds
+endif
+endif
 HOST_OBJS := $(patsubst %.cpp,$(BUILD)/obj/%.o,$(HOST_SRCS))
 CU_OBJS := $(patsubst %.cu,$(BUILD)/obj/%.cu.o,$(CU_SRCS))
 LIB := $(BUILD)/libdccl.so
@@ -78,11 +96,17 @@ tools: $(TOOLS)
 
 $(BUILD)/obj/%.o: %.cpp $(wildcard include/dccl/*.hpp) $(wildcard csrc/*/*.hpp)
 	@mkdir -p $(dir $@)
-	$(CXX) $(CXXFLAGS) -c $< -o $@
+	$(CXX) $(CXXFLAGS) $(SIM_FLAGS) -c $< -o $@
 
+ifdef SIM
+$(BUILD)/obj/%.cu.o: %.cu $(wildcard include/dccl/*.hpp) $(wildcard csrc/*/*.hpp) $(wildcard csrc/*/*.cuh) $(wildcard csrc/sim/include/*.h)
+	@mkdir -p $(dir $@)
+	$(CXX) -x c++ $(filter-out -O3,$(CXXFLAGS)) -O2 $(SIM_FLAGS) -c $< -o $@
+else
 $(BUILD)/obj/%.cu.o: %.cu $(wildcard include/dccl/*.hpp) $(wildcard csrc/*/*.hpp) $(wildcard csrc/*/*.cuh)
 	@mkdir -p $(dir $@)
 	$(NVCC) $(NVCCFLAGS) -c $< -o $@
+endif
 
 $(LIB): $(HOST_OBJS) $(CU_OBJS)
 	$(CXX) -shared -o $@ $^ $(CUDA_LIBS) $(LDFLAGS) -Wl,--exclude-libs,ALL -Wl,-Bsymbolic

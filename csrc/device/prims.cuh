@@ -14,6 +14,9 @@
 #include <cstdint>
 #include <cstddef>
 #include <cuda_runtime.h>
+#ifdef DCCL_HOST_SIM
+#include <time.h>
+#endif
 
 namespace dccl {
 
@@ -119,7 +122,11 @@ __device__ __forceinline__ Ctx make_ctx(const CollArgs& a) {
     x.parity = a.parity;
     if (x.c->seq_word != nullptr) {
         // every CTA of the call reads the same value: the counter only moves after all of them have finished
+#ifdef DCCL_HOST_SIM
+        x.seq = __atomic_load_n(x.c->seq_word, __ATOMIC_ACQUIRE);
+#else
         asm volatile("ld.volatile.global.u32 %0, [%1];" : "=r"(x.seq) : "l"(x.c->seq_word) : "memory");
+#endif
         x.parity = (int)(x.seq & 1u);
     }
     return x;
@@ -145,6 +152,31 @@ __device__ __forceinline__ void finish_call(const Ctx& x) {
 
 /* ---- system-scope memory operations ---- */
 
+#ifdef DCCL_HOST_SIM
+/* Host simulation (make SIM=1): the same operations on host memory. Loads that are polled yield the processor,
+ * a 16-byte packet access is two 8-byte atomic halves {data, tag}, which is what the packet protocol relies on. */
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) { __atomic_store_n(p, v, __ATOMIC_RELEASE); }
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) { ::dccl_sim::pause(); return __atomic_load_n(p, __ATOMIC_ACQUIRE); }
+__device__ __forceinline__ void st_release_sys64(unsigned long long* p, unsigned long long v) { __atomic_store_n(p, v, __ATOMIC_RELEASE); }
+__device__ __forceinline__ unsigned long long ld_acquire_sys64(const unsigned long long* p) { ::dccl_sim::pause(); return __atomic_load_n(p, __ATOMIC_ACQUIRE); }
+__device__ __forceinline__ uint32_t ld_volatile_u32(const uint32_t* p) { return __atomic_load_n(p, __ATOMIC_ACQUIRE); }
+__device__ __forceinline__ uint4 ld_volatile_v4(const void* p) {
+    ::dccl_sim::pause();
+    const unsigned long long* q = static_cast<const unsigned long long*>(p);
+    const unsigned long long a = __atomic_load_n(q, __ATOMIC_ACQUIRE), b = __atomic_load_n(q + 1, __ATOMIC_ACQUIRE);
+    return make_uint4((unsigned)a, (unsigned)(a >> 32), (unsigned)b, (unsigned)(b >> 32));
+}
+__device__ __forceinline__ void st_volatile_v4(void* p, uint4 v) {
+    unsigned long long* q = static_cast<unsigned long long*>(p);
+    __atomic_store_n(q, (unsigned long long)v.x | ((unsigned long long)v.y << 32), __ATOMIC_RELEASE);
+    __atomic_store_n(q + 1, (unsigned long long)v.z | ((unsigned long long)v.w << 32), __ATOMIC_RELEASE);
+}
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+    struct timespec ts;
+    clock_gettime(CLOCK_MONOTONIC, &ts);
+    return (unsigned long long)ts.tv_sec * 1000000000ull + (unsigned long long)ts.tv_nsec;
+}
+#else
 __device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
     asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
@@ -179,6 +211,7 @@ __device__ __forceinline__ unsigned long long global_timer_ns() {
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
     return t;
 }
+#endif
 
 /** Record a failure for the host. The first report is kept (checked without an atomic, because the
  *  block may live in pinned host memory; two reports racing only mix two true failures). */

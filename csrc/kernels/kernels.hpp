@@ -97,6 +97,22 @@ inline size_t p2p_chunks(size_t bytes) { return (bytes + kP2pChunk - 1) / kP2pCh
 /* bounded-wait self test: waits on a flag nobody sets, must come back with a timeout status */
 cudaError_t launch_wait_probe(const DevComm& c, cudaStream_t stream);
 
+#ifdef DCCL_HOST_SIM
+/** Host simulation: the launch runs every CUDA thread as an OS thread and returns when the kernel has finished.
+ *  DCCL_SIM_THREADS (default 8, at least the world size) replaces the block size; the kernels take any. */
+template <typename A>
+inline cudaError_t launch_kernel(void (*kernel)(const A), const void* args_struct, const LaunchCfg& cfg) {
+    struct Call { void (*k)(const A); const A* a; };
+    Call call{kernel, static_cast<const A*>(args_struct)};
+    const char* e = getenv("DCCL_SIM_THREADS");
+    int threads = e ? atoi(e) : 8;
+    if (threads < 8) threads = 8;
+    if (threads > cfg.threads) threads = cfg.threads;
+    ::dccl_sim::launch([](const void* p) { const Call* c = static_cast<const Call*>(p); c->k(*c->a); }, &call,
+                       (unsigned)(cfg.ctas * cfg.ranks_in_launch), (unsigned)threads);
+    return cudaSuccess;
+}
+#else
 template <typename K>
 inline cudaError_t launch_kernel(K kernel, const void* args_struct, const LaunchCfg& cfg) {
     void* params[] = {const_cast<void*>(args_struct)};
@@ -104,6 +120,7 @@ inline cudaError_t launch_kernel(K kernel, const void* args_struct, const Launch
     if (cfg.ranks_in_launch > 1) return cudaLaunchCooperativeKernel((const void*)kernel, grid, block, params, 0, cfg.stream);
     return cudaLaunchKernel((const void*)kernel, grid, block, params, 0, cfg.stream);
 }
+#endif
 
 /** Launch a collective kernel; fixes up the CTA count per rank that the kernel derives its ranges from. */
 template <typename K>

@@ -60,8 +60,12 @@ __global__ void __launch_bounds__(512) k_p2p(const __grid_constant__ P2pArgs a) 
         const unsigned long long G = op.chunk_base + ci;
         const size_t coff = ci * kP2pChunk;
         const size_t clen = op.bytes - coff < kP2pChunk ? op.bytes - coff : kP2pChunk;
-        // this CTA's 16-byte aligned part of the chunk
-        const size_t sub = ((clen + B - 1) / B + 15) / 16 * 16;
+        // This CTA's 16-byte aligned part of the chunk. The cut is that of a FULL chunk whatever the chunk's length, so
+        // that CTA b always owns the same bytes of a FIFO slot: its credit word then covers exactly what it overwrites,
+        // also when the slot's previous tenant was the short last chunk of a message (a cut that followed the chunk's
+        // length would let CTA b overwrite bytes that another receiving CTA has not read yet). Short chunks are
+        // served by the first CTAs only.
+        const size_t sub = ((kP2pChunk + B - 1) / B + 15) / 16 * 16;
         size_t lo = sub * (size_t)b; if (lo > clen) lo = clen;
         size_t hi = lo + sub; if (hi > clen) hi = clen;
         if (op.is_send) {

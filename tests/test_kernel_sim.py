@@ -1,0 +1,54 @@
+"""The collective kernels on a machine without a GPU.
+
+`make SIM=1 lib` compiles the kernel sources (everything except the multimem variants) and the single-GPU emulation
+harness as ordinary C++ against stand-in CUDA headers (csrc/sim/): every CUDA thread becomes an OS thread, flags are
+host atomics, a packet is two 8-byte atomic halves. The tests of tests/test_gpu_emu.py and tests/first_run_emu.py then
+run unchanged against build-sim/libdccl.so (DCCL_LIBRARY), which checks the flag protocol, the packet generations, the
+staging geometry and the reductions of twoshot / oneshot / twoshot_ll / ring / rabenseifner / zero-copy two-shot /
+send-recv. The scheduling of OS threads is far less regular than a GPU's, which is the point: an ordering the protocol
+does not enforce shows up as a wrong result here (it did: the send/recv FIFO used to cut a short last chunk
+differently from a full one, so that a sender could overwrite bytes another receiving CTA had not read yet).
+
+A subset runs here (about a minute); the whole of both files passes as well:
+    make SIM=1 lib && DCCL_LIBRARY=$PWD/build-sim/libdccl.so python -m pytest tests/test_gpu_emu.py tests/first_run_emu.py -m gpu -q
+(deselect the local-reduce, bounded-wait and child-process tests, whose kernels are not part of the simulation).
+"""
+import os
+import subprocess
+import sys
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def build(target_args, out):
+    p = subprocess.run(["make", "-C", ROOT, "-j8", "lib"] + target_args, capture_output=True, text=True, timeout=1200)
+    assert p.returncode == 0 and os.path.exists(out), p.stdout[-2000:] + p.stderr[-2000:]
+    return out
+
+
+@pytest.fixture(scope="module")
+def sim_lib():
+    return build(["SIM=1"], os.path.join(ROOT, "build-sim", "libdccl.so"))
+
+
+def test_emulation_tests_on_the_host_simulation(sim_lib):
+    select = ("fp32_bf16_sizes or (every_dtype and not local_reduce) or in_place_and_unaligned or roots or send_recv_ring or ring_order "
+              "or (two_shot_packet and 2) or guard_words or sequence_number")
+    env = dict(os.environ, DCCL_LIBRARY=sim_lib)
+    p = subprocess.run([sys.executable, "-m", "pytest", os.path.join(ROOT, "tests", "test_gpu_emu.py"),
+                        os.path.join(ROOT, "tests", "first_run_emu.py"), "-q", "-m", "gpu", "-p", "no:cacheprovider", "-k", select],
+                       env=env, capture_output=True, text=True, timeout=1500)
+    assert p.returncode == 0, p.stdout[-4000:] + p.stderr[-2000:]
+    assert " passed" in p.stdout and "failed" not in p.stdout, p.stdout[-2000:]
+
+
+def test_range_checks_on_the_host_simulation():
+    """The kernels compiled with their range checks (SIM=1 BOUNDS=1): normal runs pass with guard words on, and a run that
+    is told a smaller staging area than its message needs is refused with the bounds code before it touches memory."""
+    lib = build(["SIM=1", "BOUNDS=1"], os.path.join(ROOT, "build-sim-bounds", "libdccl.so"))
+    env = dict(os.environ, DCCL_LIBRARY=lib)
+    p = subprocess.run([sys.executable, os.path.join(ROOT, "tests", "workers", "bounds_worker.py")], env=env, capture_output=True, text=True,
+                       timeout=900)
+    assert p.returncode == 0 and "bounds worker: ok" in p.stdout, p.stdout[-2000:] + p.stderr[-2000:]
