@@ -52,3 +52,39 @@ def test_range_checks_on_the_host_simulation():
     p = subprocess.run([sys.executable, os.path.join(ROOT, "tests", "workers", "bounds_worker.py")], env=env, capture_output=True, text=True,
                        timeout=900)
     assert p.returncode == 0 and "bounds worker: ok" in p.stdout, p.stdout[-2000:] + p.stderr[-2000:]
+
+
+def test_thread_sanitizer_finds_no_unordered_access_between_ranks(tmp_path):
+    """The simulation built with -fsanitize=thread: flags are atomics with the kernels' release / acquire order, data
+    moves with plain loads and stores, so every access to staging, packets, FIFOs and user buffers that the protocol
+    does not order is reported. The only reports allowed are on the simulation's stand-in for shared memory (one
+    static per function instead of one per CTA)."""
+    cxx = "/usr/bin/g++" if os.path.exists("/usr/bin/g++") else None
+    if cxx is None:
+        pytest.skip("needs a system g++ with the sanitizer runtimes")
+    flags = ["-std=c++17", "-O1", "-g", "-fsanitize=thread", "-fno-omit-frame-pointer", "-pthread", "-I" + os.path.join(ROOT, "include"),
+             "-I" + os.path.join(ROOT, "csrc", "sim", "include"), "-DDCCL_HOST_SIM", "-DCACHELINE_SIZE=64", "-DENABLE_EVALUATION=1",
+             "-fno-strict-aliasing", "-w"]
+    srcs = ["csrc/core/config.cpp", "csrc/core/log.cpp", "csrc/api/names.cpp", "csrc/sim/sim_runtime.cpp", "csrc/gpu/emu.cu", "csrc/gpu/canary.cu",
+            "csrc/kernels/twoshot.cu", "csrc/kernels/ring.cu", "csrc/kernels/hd.cu", "csrc/kernels/direct.cu", "csrc/kernels/oneshot_ll.cu",
+            "csrc/kernels/ll_collectives.cu", "csrc/kernels/ll_twoshot.cu", "csrc/kernels/p2p.cu", "tests/sim/tsan_driver.cpp"]
+    procs, objs = [], []
+    for s in srcs:
+        o = str(tmp_path / (os.path.basename(s) + ".o"))
+        objs.append(o)
+        procs.append(subprocess.Popen([cxx, "-x", "c++"] + flags + ["-c", os.path.join(ROOT, s), "-o", o], stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True))
+    for p in procs:
+        out, _ = p.communicate(timeout=900)
+        assert p.returncode == 0, out[-3000:]
+    exe = str(tmp_path / "tsan_driver")
+    p = subprocess.run([cxx] + [f for f in flags if f != "-w"] + objs + ["-o", exe, "-ldl", "-lrt"], capture_output=True, text=True, timeout=600)
+    if p.returncode != 0 and "tsan" in (p.stdout + p.stderr).lower():
+        pytest.skip("the sanitizer runtime is not installed")
+    assert p.returncode == 0, p.stdout[-2000:] + p.stderr[-2000:]
+    run = subprocess.run([exe], cwd=str(tmp_path), capture_output=True, text=True, timeout=900, env=dict(os.environ, TSAN_OPTIONS="exitcode=0"))
+    assert run.returncode == 0, run.stdout[-2000:] + run.stderr[-3000:]
+    assert "sendrecv rc=0" in run.stdout
+    locations = [l.strip() for l in run.stderr.splitlines() if l.strip().startswith("Location is")]
+    other = [l for l in locations if not ("::s_ok'" in l or "::s_fail'" in l)]
+    assert not other, "accesses that the protocol does not order:\n" + "\n".join(other[:10]) + "\n" + run.stderr[-4000:]
+    assert run.stderr.count("WARNING: ThreadSanitizer") == len(locations), run.stderr[-4000:]
