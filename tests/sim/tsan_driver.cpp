@@ -10,6 +10,17 @@
 #include <vector>
 extern "C" int dccl_emu_collective(const char*, const char*, int, int, int, size_t, int, int, int, size_t, int, size_t, const void*, void*);
 extern "C" int dccl_emu_sendrecv_ring(int, size_t, int, int, int, const void*, void*);
+extern "C" void dccl_emu_set_peer_buffers(int);
+extern "C" void dccl_emu_set_device_seq(int);
+
+static int run_one(const char* kind, const char* algo, int n, size_t count, int in_place, size_t misalign) {
+    size_t in_e = !strcmp(kind, "reducescatter") ? count * n : count, out_e = !strcmp(kind, "allgather") ? count * n : count;
+    std::vector<float> in(in_e * n), out(out_e * n);
+    for (size_t i = 0; i < in.size(); i++) in[i] = (float)(i % 97) * 0.25f;
+    int rc = dccl_emu_collective(kind, algo, n, 7, 0, count, n - 1, 2, in_place, misalign, 3, 8 << 20, in.data(), out.data());
+    printf("%s %s n=%d count=%zu in_place=%d misalign=%zu rc=%d\n", kind, algo, n, count, in_place, misalign, rc);
+    return rc != 0;
+}
 int main(int argc, char** argv) {
     const char* kinds[] = {"allreduce", "reducescatter", "allgather", "broadcast", "reduce"};
     const char* algos[] = {"twoshot", "oneshot", "ring", "rabenseifner", "twoshot_ll"};
@@ -28,6 +39,25 @@ int main(int argc, char** argv) {
             printf("%s %s rc=%d\n", kind, algo, rc);
             bad += rc != 0;
         }
+    // other world sizes, in place, unaligned; the zero-copy form on buffers every rank can address; the device-side counter
+    for (int n2 : {2, 3, 8})
+        for (const char* algo : algos) {
+            if (!strcmp(algo, "rabenseifner") && n2 == 3) continue;
+            bad += run_one("allreduce", algo, n2, 1031, 0, 0);
+        }
+    bad += run_one("allreduce", "twoshot", 4, 5003, 1, 0);
+    bad += run_one("allreduce", "ring", 4, 5003, 0, 4);
+    bad += run_one("reducescatter", "twoshot", 4, 300000, 1, 0);      // large enough for the pushes and the fold to overlap in pieces
+    dccl_emu_set_peer_buffers(1);
+    bad += run_one("allreduce", "twoshot", 4, 40000, 0, 0);
+    bad += run_one("allreduce", "twoshot", 8, 4099, 1, 0);
+    bad += run_one("reducescatter", "twoshot", 4, 4096, 0, 0);
+    dccl_emu_set_peer_buffers(0);
+    dccl_emu_set_device_seq(1);
+    for (const char* algo : algos) bad += run_one("allreduce", algo, 4, 1031, 0, 0);
+    bad += run_one("broadcast", "oneshot", 4, 1031, 0, 0);
+    bad += run_one("reduce", "oneshot", 4, 1031, 0, 0);
+    dccl_emu_set_device_seq(0);
     size_t nb = (5u << 20) + 4096;
     std::vector<unsigned char> in(n * nb), out(n * nb);
     for (size_t i = 0; i < in.size(); i++) in[i] = (unsigned char)(i * 7);
