@@ -67,7 +67,8 @@ endif
 ifdef SIM
 HOST_SRCS += csrc/sim/sim_runtime.cpp
 CU_SRCS := csrc/gpu/emu.cu csrc/gpu/canary.cu csrc/kernels/twoshot.cu csrc/kernels/ring.cu csrc/kernels/hd.cu csrc/kernels/direct.cu \
-           csrc/kernels/oneshot_ll.cu csrc/kernels/ll_collectives.cu csrc/kernels/ll_twoshot.cu csrc/kernels/p2p.cu
+           csrc/kernels/oneshot_ll.cu csrc/kernels/ll_collectives.cu csrc/kernels/ll_twoshot.cu csrc/kernels/p2p.cu \
+           csrc/kernels/nvls.cu csrc/kernels/nvls_pipe.cu csrc/kernels/nvls_rooted.cu
 # -O2 and no strict aliasing: the kernels reinterpret 16-byte vectors the way device code does
 SIM_FLAGS := -Icsrc/sim/include -DDCCL_HOST_SIM -fno-strict-aliasing -Wno-attributes -Wno-unknown-pragmas -Wno-maybe-uninitialized
 ifdef BOUNDS

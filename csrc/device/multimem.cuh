@@ -13,6 +13,31 @@ namespace dccl {
 
 /* ---- 16-byte multimem accessors ---- */
 
+#ifdef DCCL_HOST_SIM
+/* Host simulation (make SIM=1): a multicast address is an address inside a reserved, inaccessible range that stands for
+ * the same offset in every rank's memory; a reducing load folds the ranks' copies (16-bit floats in fp32 with one
+ * rounding, as the switch does with .acc::f32), a store writes all of them. */
+template <typename T, int OP> __device__ __forceinline__ uint4 mm_ld_reduce16(const char* mc) {
+    using A = typename Traits<T>::Acc;
+    constexpr int N = Vec16<T>::N;
+    const ::dccl_sim::McMap* m = ::dccl_sim::mc_find(mc);
+    const size_t off = (size_t)(mc - m->base);
+    A acc[N];
+    for (int r = 0; r < m->n; r++) {
+        const Vec16<T> v = ld_vec<T>(m->mem[r] + off);
+        for (int e = 0; e < N; e++) acc[e] = r == 0 ? Traits<T>::up(v.e[e]) : op_apply<OP, A>(acc[e], Traits<T>::up(v.e[e]));
+    }
+    Vec16<T> out;
+    for (int e = 0; e < N; e++) out.e[e] = Traits<T>::down(acc[e]);
+    return *reinterpret_cast<uint4*>(&out);
+}
+__device__ __forceinline__ void mm_st16(void* mc, uint4 v) {
+    const ::dccl_sim::McMap* m = ::dccl_sim::mc_find(mc);
+    const size_t off = (size_t)(static_cast<char*>(mc) - m->base);
+    for (int r = 0; r < m->n; r++) *reinterpret_cast<uint4*>(m->mem[r] + off) = v;
+}
+#else
+
 #define MM_LDRED_V4(NAME, INSTR)                                                                             \
     __device__ __forceinline__ uint4 NAME(const void* mc) {                                                  \
         uint4 v;                                                                                             \
@@ -90,6 +115,8 @@ template <typename T, int OP> __device__ __forceinline__ uint4 mm_ld_reduce16(co
         return make_uint4((uint32_t)lo, (uint32_t)(lo >> 32), (uint32_t)hi, (uint32_t)(hi >> 32));
     }
 }
+
+#endif   // DCCL_HOST_SIM
 
 /** Scale a reduced vector by 1/world (ncclAvg). */
 template <typename T> __device__ __forceinline__ uint4 avg16(uint4 raw, int world) {

@@ -37,6 +37,11 @@ int g_guard = 0;
 #ifdef DCCL_DEBUG_BOUNDS
 size_t g_declared_stage = 0;
 #endif
+#ifdef DCCL_HOST_SIM
+// Host simulation only (a single GPU has no NVSwitch to play): which switch kernel serves algorithm "nvls".
+// 0 staged (nvls.cu), 1 pipelined all-reduce (nvls_pipe.cu), 2 pipelined broadcast / reduce (nvls_rooted.cu)
+int g_switch_form = 0;
+#endif
 
 // Pools of finished emulation runs, kept for the next run of the same size (the tests make thousands of short
 // runs; allocating and clearing 8 x 80 MB for each would dominate them).
@@ -73,7 +78,11 @@ struct EmuWorld {
     DevComm* d_comms = nullptr;
     uint32_t* seq_words = nullptr;   // per virtual rank: {next sequence number, CTAs done}, 64 bytes apart
     std::vector<DevComm> comms;
+    char* mc = nullptr;              // host simulation: multicast alias of the pools
     ~EmuWorld() {
+#ifdef DCCL_HOST_SIM
+        if (mc) ::dccl_sim::mc_destroy(mc);
+#endif
         if (seq_words) cudaFree(seq_words);
         cudaDeviceSynchronize();
         for (char* p : pools) if (p) give_pool(p, pool_bytes);
@@ -98,6 +107,9 @@ struct EmuWorld {
             if (cudaMalloc((void**)&seq_words, init.size() * sizeof(uint32_t)) != cudaSuccess) return false;
             if (cudaMemcpy(seq_words, init.data(), init.size() * sizeof(uint32_t), cudaMemcpyHostToDevice) != cudaSuccess) return false;
         }
+#ifdef DCCL_HOST_SIM
+        if ((mc = ::dccl_sim::mc_create(pool_bytes, n, pools.data())) == nullptr) return false;
+#endif
         comms.resize(n);
         for (int r = 0; r < n; r++) {
             DevComm& c = comms[r];
@@ -106,7 +118,7 @@ struct EmuWorld {
             c.rank = r;
             c.nranks = n;
             for (int p = 0; p < n; p++) c.pool[p] = pools[p];
-            c.mc_pool = nullptr;
+            c.mc_pool = mc;           // nullptr on a GPU: the multimem variants are not emulated there
             c.status = status;
             c.abort_word = status + ST_WORDS;
             c.timeout_ns = timeout_ms * 1000000ull;
@@ -166,6 +178,12 @@ int dccl_emu_declare_stage_bytes(size_t bytes) {
     return -1;
 #endif
 }
+
+#ifdef DCCL_HOST_SIM
+/** Host simulation only: the switch kernel behind algorithm "nvls": 0 staged, 1 pipelined all-reduce,
+ *  2 pipelined broadcast / reduce. */
+void dccl_emu_set_switch_form(int form) { g_switch_form = form; }
+#endif
 
 /** 1: all-reduce with the two-shot variant runs its zero-copy form on the emulated ranks' user buffers. */
 void dccl_emu_set_peer_buffers(int on) { g_peer_buffers = on ? 1 : 0; }
@@ -250,6 +268,30 @@ int dccl_emu_collective(const char* kind_s, const char* algo_s, int nranks, int 
         a.root = root;
         cudaError_t e = cudaErrorInvalidValue;
         size_t cap = 0;
+#ifdef DCCL_HOST_SIM
+        if (algo == ALGO_NVLS) {
+            // the switch kernels on ordinary buffers (staged through the pool), played by the simulated multicast mapping
+            const bool reducing = coll == COLL_ALLREDUCE || coll == COLL_REDUCESCATTER || coll == COLL_REDUCE;
+            const bool switch_op = !reducing || (op != (int)ncclProd && !((dt == ncclFloat32 || dt == ncclFloat64) && (op == (int)ncclMax || op == (int)ncclMin)) &&
+                                                 dt != ncclInt8 && dt != ncclUint8);
+            if (!switch_op) e = cudaErrorInvalidValue;
+            else if (coll == COLL_ALLREDUCE && g_switch_form == 1) {
+                cap = nvls_pipe_capacity(es, stage_bytes, nranks, false);
+                LaunchCfg pc = cfg;
+                pc.ctas = cfg.ctas < 3 ? 3 : cfg.ctas;
+                if (count <= cap) e = launch_nvls_pipe(a, dt, pc, false);
+            } else if ((coll == COLL_BROADCAST || coll == COLL_REDUCE) && g_switch_form == 2) {
+                a.mode = coll == COLL_BROADCAST ? ROOTED_BROADCAST : ROOTED_REDUCE;
+                cap = nvls_pipe_capacity(es, stage_bytes, nranks, false);
+                if (count <= cap) e = launch_nvls_rooted(a, dt, cfg);
+            } else {
+                a.mode = coll == COLL_ALLREDUCE ? NV_ALLREDUCE : coll == COLL_REDUCESCATTER ? NV_REDUCESCATTER : coll == COLL_ALLGATHER ? NV_ALLGATHER
+                         : coll == COLL_BROADCAST ? NV_BROADCAST : NV_REDUCE;
+                cap = nvls_capacity(a.mode, nranks, es, stage_bytes);
+                if (count <= cap) e = launch_nvls(a, dt, cfg);
+            }
+        } else
+#endif
         if (coll == COLL_ALLREDUCE) {
             if (algo == ALGO_ONESHOT) { cap = oneshot_ll_capacity_bytes() / es; if (count <= cap) e = launch_oneshot_ll(a, dt, cfg); }
             else if (algo == ALGO_TWOSHOT_LL) { a.mode = LL2_ALLREDUCE; cap = ll_twoshot_capacity_bytes(nranks) / es; if (count <= cap) e = launch_ll_twoshot(a, dt, cfg); }

@@ -68,6 +68,13 @@ void pause();              // called from polling loops: lets the other simulate
 /** Run fn(arg) once per simulated thread of a grid x block launch; returns when all of them have returned. */
 void launch(void (*fn)(const void*), const void* arg, unsigned grid, unsigned block);
 
+/** A simulated multicast mapping: addresses [base, base + size) stand for the same offsets in n memories. */
+struct McMap { char* base; size_t size; int n; char* mem[8]; };
+/** Reserve an inaccessible address range of `size` bytes that stands for mem[0..n) and return its base. */
+char* mc_create(size_t size, int n, char* const* mem);
+void mc_destroy(char* base);
+const McMap* mc_find(const void* p);
+
 } // namespace dccl_sim
 
 #define threadIdx (::dccl_sim::t_ctx.thread_idx)

@@ -8,7 +8,9 @@
 #include "../kernels/kernels.hpp"
 #include <condition_variable>
 #include <mutex>
+#include <cstdio>
 #include <sched.h>
+#include <sys/mman.h>
 #include <thread>
 #include <vector>
 
@@ -43,6 +45,42 @@ struct CtaBarrier {
 void syncthreads() { static_cast<CtaBarrier*>(t_ctx.cta)->wait(); }
 
 void pause() { sched_yield(); }
+
+namespace {
+constexpr int kMaxMaps = 32;
+McMap g_maps[kMaxMaps];
+std::mutex g_maps_mutex;
+}
+
+char* mc_create(size_t size, int n, char* const* mem) {
+    void* p = mmap(nullptr, size, PROT_NONE, MAP_PRIVATE | MAP_ANONYMOUS | MAP_NORESERVE, -1, 0);   // never dereferenced
+    if (p == MAP_FAILED) return nullptr;
+    std::lock_guard<std::mutex> l(g_maps_mutex);
+    for (McMap& m : g_maps)
+        if (!m.base) {
+            m.size = size; m.n = n;
+            for (int r = 0; r < n; r++) m.mem[r] = mem[r];
+            m.base = static_cast<char*>(p);
+            return m.base;
+        }
+    munmap(p, size);
+    return nullptr;
+}
+
+void mc_destroy(char* base) {
+    std::lock_guard<std::mutex> l(g_maps_mutex);
+    for (McMap& m : g_maps)
+        if (m.base == base && base) { munmap(m.base, m.size); m.base = nullptr; }
+}
+
+/** Mappings only change between launches, so the kernels' threads read the table without a lock. */
+const McMap* mc_find(const void* p) {
+    const char* c = static_cast<const char*>(p);
+    for (const McMap& m : g_maps)
+        if (m.base && c >= m.base && c < m.base + m.size) return &m;
+    fprintf(stderr, "dccl simulation: %p is not a multicast address\n", p);
+    abort();
+}
 
 void launch(void (*fn)(const void*), const void* arg, unsigned grid, unsigned block) {
     std::vector<CtaBarrier*> bars(grid);

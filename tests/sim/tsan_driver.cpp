@@ -12,6 +12,7 @@ extern "C" int dccl_emu_collective(const char*, const char*, int, int, int, size
 extern "C" int dccl_emu_sendrecv_ring(int, size_t, int, int, int, const void*, void*);
 extern "C" void dccl_emu_set_peer_buffers(int);
 extern "C" void dccl_emu_set_device_seq(int);
+extern "C" void dccl_emu_set_switch_form(int);
 
 static int run_one(const char* kind, const char* algo, int n, size_t count, int in_place, size_t misalign) {
     size_t in_e = !strcmp(kind, "reducescatter") ? count * n : count, out_e = !strcmp(kind, "allgather") ? count * n : count;
@@ -58,6 +59,16 @@ int main(int argc, char** argv) {
     bad += run_one("broadcast", "oneshot", 4, 1031, 0, 0);
     bad += run_one("reduce", "oneshot", 4, 1031, 0, 0);
     dccl_emu_set_device_seq(0);
+    // the switch kernels over the simulated multicast mapping: staged, pipelined all-reduce, pipelined broadcast / reduce
+    for (int form = 0; form < 3; form++) {
+        dccl_emu_set_switch_form(form);
+        for (int n2 : {2, 4}) {
+            if (form != 2) bad += run_one("allreduce", "nvls", n2, 40003, 0, 0);
+            if (form == 0) { bad += run_one("reducescatter", "nvls", n2, 4099, 0, 0); bad += run_one("allgather", "nvls", n2, 4099, 0, 4); }
+            if (form != 1) { bad += run_one("broadcast", "nvls", n2, 40003, 0, 4); bad += run_one("reduce", "nvls", n2, 40003, 1, 0); }
+        }
+    }
+    dccl_emu_set_switch_form(0);
     size_t nb = (5u << 20) + 4096;
     std::vector<unsigned char> in(n * nb), out(n * nb);
     for (size_t i = 0; i < in.size(); i++) in[i] = (unsigned char)(i * 7);

@@ -1,11 +1,11 @@
 """The collective kernels on a machine without a GPU.
 
-`make SIM=1 lib` compiles the kernel sources (everything except the multimem variants) and the single-GPU emulation
+`make SIM=1 lib` compiles the kernel sources and the single-GPU emulation
 harness as ordinary C++ against stand-in CUDA headers (csrc/sim/): every CUDA thread becomes an OS thread, flags are
 host atomics, a packet is two 8-byte atomic halves. The tests of tests/test_gpu_emu.py and tests/first_run_emu.py then
 run unchanged against build-sim/libdccl.so (DCCL_LIBRARY), which checks the flag protocol, the packet generations, the
 staging geometry and the reductions of twoshot / oneshot / twoshot_ll / ring / rabenseifner / zero-copy two-shot /
-send-recv. The scheduling of OS threads is far less regular than a GPU's, which is the point: an ordering the protocol
+send-recv, and (with a simulated multicast mapping) of the switch kernels. The scheduling of OS threads is far less regular than a GPU's, which is the point: an ordering the protocol
 does not enforce shows up as a wrong result here (it did: the send/recv FIFO used to cut a short last chunk
 differently from a full one, so that a sender could overwrite bytes another receiving CTA had not read yet).
 
@@ -44,6 +44,16 @@ def test_emulation_tests_on_the_host_simulation(sim_lib):
     assert " passed" in p.stdout and "failed" not in p.stdout, p.stdout[-2000:]
 
 
+def test_switch_kernels_on_the_host_simulation(sim_lib):
+    """The multimem kernels with a simulated multicast mapping (a reserved address range that stands for the same
+    offset in every rank's pool): staged forms of all five collectives, the pipelined all-reduce, the pipelined
+    broadcast / reduce; world sizes 2, 3, 8, four dtypes, in place and unaligned, against the serial fold."""
+    env = dict(os.environ, DCCL_LIBRARY=sim_lib)
+    p = subprocess.run([sys.executable, os.path.join(ROOT, "tests", "workers", "sim_switch_worker.py")], env=env, capture_output=True, text=True,
+                       timeout=1500)
+    assert p.returncode == 0 and "sim switch worker: ok" in p.stdout, p.stdout[-2000:] + p.stderr[-3000:]
+
+
 def test_range_checks_on_the_host_simulation():
     """The kernels compiled with their range checks (SIM=1 BOUNDS=1): normal runs pass with guard words on, and a run that
     is told a smaller staging area than its message needs is refused with the bounds code before it touches memory."""
@@ -67,7 +77,8 @@ def test_thread_sanitizer_finds_no_unordered_access_between_ranks(tmp_path):
              "-fno-strict-aliasing", "-w"]
     srcs = ["csrc/core/config.cpp", "csrc/core/log.cpp", "csrc/api/names.cpp", "csrc/sim/sim_runtime.cpp", "csrc/gpu/emu.cu", "csrc/gpu/canary.cu",
             "csrc/kernels/twoshot.cu", "csrc/kernels/ring.cu", "csrc/kernels/hd.cu", "csrc/kernels/direct.cu", "csrc/kernels/oneshot_ll.cu",
-            "csrc/kernels/ll_collectives.cu", "csrc/kernels/ll_twoshot.cu", "csrc/kernels/p2p.cu", "tests/sim/tsan_driver.cpp"]
+            "csrc/kernels/ll_collectives.cu", "csrc/kernels/ll_twoshot.cu", "csrc/kernels/p2p.cu", "csrc/kernels/nvls.cu", "csrc/kernels/nvls_pipe.cu",
+            "csrc/kernels/nvls_rooted.cu", "tests/sim/tsan_driver.cpp"]
     procs, objs = [], []
     for s in srcs:
         o = str(tmp_path / (os.path.basename(s) + ".o"))

@@ -1,0 +1,55 @@
+"""The switch (multimem) kernels on the host simulation (DCCL_LIBRARY = build-sim/libdccl.so): staged forms of every
+collective, the pipelined all-reduce and the pipelined broadcast / reduce, against the serial fold."""
+import os
+import sys
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+sys.path.insert(0, ROOT)
+sys.path.insert(0, os.path.join(ROOT, "tests"))
+
+from dccl_b200 import _lib  # noqa: E402
+from dccl_b200.utils import oracle  # noqa: E402
+from test_gpu_emu import close, emu, inputs_for  # noqa: E402
+
+
+def main():
+    L = _lib.lib()
+    assert hasattr(L, "dccl_emu_set_switch_form"), "not the simulation build"
+    cases = 0
+    for form, kinds in ((0, ["allreduce", "reducescatter", "allgather", "broadcast", "reduce"]), (1, ["allreduce"]), (2, ["broadcast", "reduce"])):
+        L.dccl_emu_set_switch_form(form)
+        for n in (2, 3, 8):
+            for kind in kinds:
+                for name, op in (("float32", "sum"), ("bfloat16", "avg"), ("int32", "max"), ("float16", "sum")):
+                    if kind in ("allgather", "broadcast") and op != "sum":
+                        continue
+                    for count in (1, 1031, 70001):
+                        for in_place, misalign in ((0, 0), (1, 0), (0, 4 if name in ("float32", "int32") else 2)):
+                            root = n - 1
+                            in_count = count * n if kind == "reducescatter" else count
+                            ins = inputs_for(name, op, in_count, n, seed=71)
+                            out = emu(L, kind, "nvls", n, name, op, count, ins, root=root, ctas=6, in_place=in_place, misalign=misalign,
+                                      iters=3, stage=4 << 20)
+                            bf = name == "bfloat16"
+                            if kind == "allreduce":
+                                want = oracle.fold(ins, op, bf16=bf)
+                                ok = all(close(out[r], want, name, n) for r in range(n))
+                            elif kind == "reduce":
+                                ok = close(out[root], oracle.fold(ins, op, bf16=bf), name, n)
+                            elif kind == "reducescatter":
+                                want = oracle.fold(ins, op, bf16=bf)
+                                ok = all(close(out[r], want[r * count:(r + 1) * count], name, n) for r in range(n))
+                            elif kind == "allgather":
+                                ok = all(np.array_equal(out[r], np.concatenate(ins)) for r in range(n))
+                            else:
+                                ok = all(np.array_equal(out[r], ins[root]) for r in range(n))
+                            assert ok, (form, n, kind, name, op, count, in_place, misalign)
+                            cases += 1
+    L.dccl_emu_set_switch_form(0)
+    print("sim switch worker: ok (%d cases)" % cases)
+
+
+if __name__ == "__main__":
+    main()
