@@ -1,5 +1,6 @@
 """The switch (multimem) kernels on the host simulation (DCCL_LIBRARY = build-sim/libdccl.so): staged forms of every
-collective, the pipelined all-reduce and the pipelined broadcast / reduce, against the serial fold."""
+collective, the pipelined all-reduce and the pipelined broadcast / reduce, against the serial fold. --all adds world
+size 2 and one-element messages."""
 import os
 import sys
 
@@ -20,12 +21,12 @@ def main():
     cases = 0
     for form, kinds in ((0, ["allreduce", "reducescatter", "allgather", "broadcast", "reduce"]), (1, ["allreduce"]), (2, ["broadcast", "reduce"])):
         L.dccl_emu_set_switch_form(form)
-        for n in (2, 3, 8):
+        for n in ((2, 3, 8) if "--all" in sys.argv[1:] else (3, 8)):
             for kind in kinds:
                 for name, op in (("float32", "sum"), ("bfloat16", "avg"), ("int32", "max"), ("float16", "sum")):
                     if kind in ("allgather", "broadcast") and op != "sum":
                         continue
-                    for count in (1, 1031, 70001):
+                    for count in ((1, 1031, 70001) if "--all" in sys.argv[1:] else (1031, 70001)):
                         for in_place, misalign in ((0, 0), (1, 0), (0, 4 if name in ("float32", "int32") else 2)):
                             root = n - 1
                             in_count = count * n if kind == "reducescatter" else count
