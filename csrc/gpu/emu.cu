@@ -240,6 +240,18 @@ int dccl_emu_collective(const char* kind_s, const char* algo_s, int nranks, int 
         }
     const bool direct = g_peer_buffers && algo == ALGO_TWOSHOT && misalign % 16 == 0 &&
                         (coll == COLL_ALLREDUCE || (coll == COLL_REDUCESCATTER && (count * es) % 16 == 0));
+#ifdef DCCL_HOST_SIM
+    // with "peer buffers" on, the user buffers also count as multicast-bound (what dcclMemAlloc memory is): the switch
+    // kernels then run their zero-copy forms on them
+    char *send_mc = nullptr, *recv_mc = nullptr;
+    const bool sym_switch = g_peer_buffers && algo == ALGO_NVLS && misalign % 16 == 0 && !in_place;
+    if (sym_switch) {
+        send_mc = ::dccl_sim::mc_create(buf_elems * es + misalign + 64, nranks, sendb.data());
+        recv_mc = ::dccl_sim::mc_create(buf_elems * es + misalign + 64, nranks, recvb.data());
+        if (!send_mc || !recv_mc) return fail("multicast mapping of the user buffers");
+        for (size_t r = 0; r < n; r++) { ios[r].send_mc = send_mc + misalign; ios[r].recv_mc = recv_mc + misalign; }
+    }
+#endif
     RankIO* d_ios = nullptr;
     if (cudaMalloc((void**)&d_ios, n * sizeof(RankIO)) != cudaSuccess) return fail("cudaMalloc");
     cudaMemcpy(d_ios, ios.data(), n * sizeof(RankIO), cudaMemcpyHostToDevice);
@@ -287,7 +299,8 @@ int dccl_emu_collective(const char* kind_s, const char* algo_s, int nranks, int 
             } else {
                 a.mode = coll == COLL_ALLREDUCE ? NV_ALLREDUCE : coll == COLL_REDUCESCATTER ? NV_REDUCESCATTER : coll == COLL_ALLGATHER ? NV_ALLGATHER
                          : coll == COLL_BROADCAST ? NV_BROADCAST : NV_REDUCE;
-                cap = nvls_capacity(a.mode, nranks, es, stage_bytes);
+                a.symmetric = sym_switch && (count * es) % 16 == 0 ? 1 : 0;      // zero-copy: whole 16-byte vectors per slot
+                cap = a.symmetric ? count : nvls_capacity(a.mode, nranks, es, stage_bytes);
                 if (count <= cap) e = launch_nvls(a, dt, cfg);
             }
         } else
@@ -336,6 +349,10 @@ int dccl_emu_collective(const char* kind_s, const char* algo_s, int nranks, int 
     if (rc == 0)
         for (size_t r = 0; r < n; r++)
             cudaMemcpy((char*)host_out + r * out_elems * es, ios[r].recv, out_elems * es, cudaMemcpyDeviceToHost);
+#ifdef DCCL_HOST_SIM
+    if (send_mc) ::dccl_sim::mc_destroy(send_mc);
+    if (recv_mc) ::dccl_sim::mc_destroy(recv_mc);
+#endif
     for (size_t r = 0; r < n; r++) { cudaFree(sendb[r]); cudaFree(recvb[r]); }
     cudaFree(d_ios);
     if (rc == 0 && cudaGetLastError() != cudaSuccess) rc = -4;

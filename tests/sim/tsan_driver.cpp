@@ -69,6 +69,9 @@ int main(int argc, char** argv) {
         }
     }
     dccl_emu_set_switch_form(0);
+    dccl_emu_set_peer_buffers(1);       // zero-copy switch forms on multicast-mapped user buffers
+    for (const char* kind : kinds) bad += run_one(kind, "nvls", 4, 40000, 0, 0);
+    dccl_emu_set_peer_buffers(0);
     size_t nb = (5u << 20) + 4096;
     std::vector<unsigned char> in(n * nb), out(n * nb);
     for (size_t i = 0; i < in.size(); i++) in[i] = (unsigned char)(i * 7);

@@ -48,7 +48,36 @@ def main():
                                 ok = all(np.array_equal(out[r], ins[root]) for r in range(n))
                             assert ok, (form, n, kind, name, op, count, in_place, misalign)
                             cases += 1
+    # zero-copy forms: the user buffers themselves are multicast-mapped (what dcclMemAlloc memory is)
     L.dccl_emu_set_switch_form(0)
+    L.dccl_emu_set_peer_buffers(1)
+    try:
+        for n in (3, 8):
+            for kind in ["allreduce", "reducescatter", "allgather", "broadcast", "reduce"]:
+                for name, op in (("float32", "sum"), ("bfloat16", "avg"), ("int32", "min")):
+                    if kind in ("allgather", "broadcast") and op != "sum":
+                        continue
+                    for count in (1024, 70000):
+                        root = n - 1
+                        in_count = count * n if kind == "reducescatter" else count
+                        ins = inputs_for(name, op, in_count, n, seed=73)
+                        out = emu(L, kind, "nvls", n, name, op, count, ins, root=root, ctas=4, iters=3, stage=4 << 20)
+                        bf = name == "bfloat16"
+                        if kind == "allreduce":
+                            ok = all(close(out[r], oracle.fold(ins, op, bf16=bf), name, n) for r in range(n))
+                        elif kind == "reduce":
+                            ok = close(out[root], oracle.fold(ins, op, bf16=bf), name, n)
+                        elif kind == "reducescatter":
+                            want = oracle.fold(ins, op, bf16=bf)
+                            ok = all(close(out[r], want[r * count:(r + 1) * count], name, n) for r in range(n))
+                        elif kind == "allgather":
+                            ok = all(np.array_equal(out[r], np.concatenate(ins)) for r in range(n))
+                        else:
+                            ok = all(np.array_equal(out[r], ins[root]) for r in range(n))
+                        assert ok, ("zero-copy", n, kind, name, op, count)
+                        cases += 1
+    finally:
+        L.dccl_emu_set_peer_buffers(0)
     print("sim switch worker: ok (%d cases)" % cases)
 
 
