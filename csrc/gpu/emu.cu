@@ -18,6 +18,7 @@
 #include <cstdio>
 #include <cstring>
 #include <string>
+#include <utility>
 #include <vector>
 
 using namespace dccl;
@@ -29,6 +30,8 @@ int g_device_seq = 0;
 // set by dccl_emu_set_peer_buffers: the user buffers count as addressable by every rank (symmetric / registered
 // memory), so that the two-shot all-reduce takes its zero-copy form
 int g_peer_buffers = 0;
+// set by dccl_emu_set_mix: (collective, variant) pairs launched before every call under test
+std::vector<std::pair<int, GpuAlgo>> g_mix;
 // set by dccl_emu_set_guard: guard words in the unused parts of every virtual rank's pool, checked after each run
 int g_guard = 0;
 // set by dccl_emu_declare_stage_bytes (range-checking builds only): the staging size the kernels are TOLD, smaller
@@ -159,6 +162,34 @@ extern "C" {
  *  from a CUDA graph); the launch arguments then carry a wrong sequence number on purpose. 0: host counts. */
 void dccl_emu_set_device_seq(int on) { g_device_seq = on ? 1 : 0; }
 
+/**
+ * Collectives to run before every call of the following dccl_emu_collective runs, in the same virtual world and on
+ * the same buffers, e.g. "allreduce:oneshot,broadcast:oneshot": sequences of different kernels share flags, packet
+ * generations and staging halves, and a kernel must cope with whatever its predecessors left there. Same element
+ * count, type and operator as the call under test (out of place, aligned runs only); their results are not checked.
+ * Empty string or NULL: none. Returns the number of entries, -1 on a name that is not known.
+ */
+int dccl_emu_set_mix(const char* spec) {
+    g_mix.clear();
+    if (!spec) return 0;
+    std::string s(spec);
+    size_t pos = 0;
+    while (pos < s.size()) {
+        size_t comma = s.find(',', pos);
+        if (comma == std::string::npos) comma = s.size();
+        const std::string item = s.substr(pos, comma - pos);
+        pos = comma + 1;
+        if (item.empty()) continue;
+        const size_t colon = item.find(':');
+        if (colon == std::string::npos) { g_mix.clear(); return -1; }
+        const int c = parse_collective_name(item.substr(0, colon).c_str());
+        const GpuAlgo al = parse_algo_name(item.substr(colon + 1).c_str());
+        if (c < 0 || al == ALGO_COUNT) { g_mix.clear(); return -1; }
+        g_mix.emplace_back(c, al);
+    }
+    return (int)g_mix.size();
+}
+
 /** 1: every run fills the unused parts of the virtual ranks' pools with guard words and checks them afterwards;
  *  a run that damaged them returns 200 + the number of the gap (canary.hpp). */
 void dccl_emu_set_guard(int on) { g_guard = on ? 1 : 0; }
@@ -220,7 +251,8 @@ int dccl_emu_collective(const char* kind_s, const char* algo_s, int nranks, int 
     // user buffers
     std::vector<char*> sendb(n, nullptr), recvb(n, nullptr);
     std::vector<RankIO> ios(n);
-    const size_t buf_elems = in_elems > out_elems ? in_elems : out_elems;
+    size_t buf_elems = in_elems > out_elems ? in_elems : out_elems;
+    if (!g_mix.empty()) buf_elems = count * n;      // a reduce-scatter reads, an all-gather writes n slots
     for (size_t r = 0; r < n; r++) {
         if (cudaMalloc((void**)&sendb[r], buf_elems * es + misalign + 64) != cudaSuccess) return fail("cudaMalloc");
         if (cudaMalloc((void**)&recvb[r], buf_elems * es + misalign + 64) != cudaSuccess) return fail("cudaMalloc");
@@ -260,6 +292,7 @@ int dccl_emu_collective(const char* kind_s, const char* algo_s, int nranks, int 
     cfg.ctas = ctas;
     cfg.ranks_in_launch = nranks;
     int rc = 0;
+    uint32_t next_seq_no = 1;
     for (int it = 0; it < iters && rc == 0; it++) {
         // fresh inputs every call (in-place runs overwrite them)
         for (size_t r = 0; r < n; r++) {
@@ -273,69 +306,87 @@ int dccl_emu_collective(const char* kind_s, const char* algo_s, int nranks, int 
         a.emu_io = d_ios;
         a.count = count;
         a.stride = count;
-        a.seq = (uint32_t)(it + 1);
-        a.parity = (int)(a.seq & 1u);
-        if (g_device_seq) { a.seq = 0x5eed0000u; a.parity = 0; }   // what a replayed launch carries: the kernels must not use it
+        // sequence numbers count launches (set below); with the device-side counter the launch carries a wrong one on purpose
         a.op = op;
         a.root = root;
-        cudaError_t e = cudaErrorInvalidValue;
-        size_t cap = 0;
+        // one launch of (collective, variant) on the buffers of this run; the arguments are a copy, the caller's stay as they are
+        auto launch_one = [&](int coll, GpuAlgo algo, CollArgs a, size_t* cap_out) -> cudaError_t {
+            cudaError_t e = cudaErrorInvalidValue;
+            size_t cap = 0;
 #ifdef DCCL_HOST_SIM
-        if (algo == ALGO_NVLS) {
-            // the switch kernels on ordinary buffers (staged through the pool), played by the simulated multicast mapping
-            const bool reducing = coll == COLL_ALLREDUCE || coll == COLL_REDUCESCATTER || coll == COLL_REDUCE;
-            const bool switch_op = !reducing || (op != (int)ncclProd && !((dt == ncclFloat32 || dt == ncclFloat64) && (op == (int)ncclMax || op == (int)ncclMin)) &&
-                                                 dt != ncclInt8 && dt != ncclUint8);
-            if (!switch_op) e = cudaErrorInvalidValue;
-            else if (coll == COLL_ALLREDUCE && g_switch_form == 1) {
-                cap = nvls_pipe_capacity(es, stage_bytes, nranks, false);
-                LaunchCfg pc = cfg;
-                pc.ctas = cfg.ctas < 3 ? 3 : cfg.ctas;
-                if (count <= cap) e = launch_nvls_pipe(a, dt, pc, false);
-            } else if ((coll == COLL_BROADCAST || coll == COLL_REDUCE) && g_switch_form == 2) {
-                a.mode = coll == COLL_BROADCAST ? ROOTED_BROADCAST : ROOTED_REDUCE;
-                cap = nvls_pipe_capacity(es, stage_bytes, nranks, false);
-                if (count <= cap) e = launch_nvls_rooted(a, dt, cfg);
-            } else {
-                a.mode = coll == COLL_ALLREDUCE ? NV_ALLREDUCE : coll == COLL_REDUCESCATTER ? NV_REDUCESCATTER : coll == COLL_ALLGATHER ? NV_ALLGATHER
-                         : coll == COLL_BROADCAST ? NV_BROADCAST : NV_REDUCE;
-                a.symmetric = sym_switch && (count * es) % 16 == 0 ? 1 : 0;      // zero-copy: whole 16-byte vectors per slot
-                cap = a.symmetric ? count : nvls_capacity(a.mode, nranks, es, stage_bytes);
-                if (count <= cap) e = launch_nvls(a, dt, cfg);
-            }
-        } else
+            if (algo == ALGO_NVLS) {
+                // the switch kernels on ordinary buffers (staged through the pool), played by the simulated multicast mapping
+                const bool reducing = coll == COLL_ALLREDUCE || coll == COLL_REDUCESCATTER || coll == COLL_REDUCE;
+                const bool switch_op = !reducing || (op != (int)ncclProd && !((dt == ncclFloat32 || dt == ncclFloat64) && (op == (int)ncclMax || op == (int)ncclMin)) &&
+                                                     dt != ncclInt8 && dt != ncclUint8);
+                if (!switch_op) e = cudaErrorInvalidValue;
+                else if (coll == COLL_ALLREDUCE && g_switch_form == 1) {
+                    cap = nvls_pipe_capacity(es, stage_bytes, nranks, false);
+                    LaunchCfg pc = cfg;
+                    pc.ctas = cfg.ctas < 3 ? 3 : cfg.ctas;
+                    if (count <= cap) e = launch_nvls_pipe(a, dt, pc, false);
+                } else if ((coll == COLL_BROADCAST || coll == COLL_REDUCE) && g_switch_form == 2) {
+                    a.mode = coll == COLL_BROADCAST ? ROOTED_BROADCAST : ROOTED_REDUCE;
+                    cap = nvls_pipe_capacity(es, stage_bytes, nranks, false);
+                    if (count <= cap) e = launch_nvls_rooted(a, dt, cfg);
+                } else {
+                    a.mode = coll == COLL_ALLREDUCE ? NV_ALLREDUCE : coll == COLL_REDUCESCATTER ? NV_REDUCESCATTER : coll == COLL_ALLGATHER ? NV_ALLGATHER
+                             : coll == COLL_BROADCAST ? NV_BROADCAST : NV_REDUCE;
+                    a.symmetric = sym_switch && (count * es) % 16 == 0 ? 1 : 0;      // zero-copy: whole 16-byte vectors per slot
+                    cap = a.symmetric ? count : nvls_capacity(a.mode, nranks, es, stage_bytes);
+                    if (count <= cap) e = launch_nvls(a, dt, cfg);
+                }
+            } else
 #endif
-        if (coll == COLL_ALLREDUCE) {
-            if (algo == ALGO_ONESHOT) { cap = oneshot_ll_capacity_bytes() / es; if (count <= cap) e = launch_oneshot_ll(a, dt, cfg); }
-            else if (algo == ALGO_TWOSHOT_LL) { a.mode = LL2_ALLREDUCE; cap = ll_twoshot_capacity_bytes(nranks) / es; if (count <= cap) e = launch_ll_twoshot(a, dt, cfg); }
-            else if (algo == ALGO_RING) { a.mode = RING_ALLREDUCE; cap = ring_capacity(a.mode, nranks, es, stage_bytes); if (count <= cap) e = launch_ring(a, dt, cfg); }
-            else if (algo == ALGO_RABENSEIFNER) { cap = hd_capacity(nranks, es, stage_bytes); if (count <= cap && is_power_of_two((uint32_t)nranks)) e = launch_hd(a, dt, cfg); }
-            else if (direct) { a.symmetric = 1; a.mode = DIRECT_ALLREDUCE; cap = count; e = launch_direct(a, dt, cfg); }
-            else { a.mode = TS_ALLREDUCE; cap = twoshot_capacity(a.mode, nranks, es, stage_bytes); if (count <= cap) e = launch_twoshot(a, dt, cfg); }
-        } else if (coll == COLL_REDUCE && algo == ALGO_TWOSHOT_LL) {
-            a.mode = LL2_REDUCE;
-            cap = ll_twoshot_capacity_bytes(nranks) / es;
-            if (count <= cap) e = launch_ll_twoshot(a, dt, cfg);
-        } else if (coll != COLL_ALLREDUCE && algo == ALGO_ONESHOT && count * es <= oneshot_ll_capacity_bytes()) {
-            a.mode = coll == COLL_REDUCESCATTER ? LL_REDUCESCATTER : coll == COLL_ALLGATHER ? LL_ALLGATHER : coll == COLL_BROADCAST ? LL_BROADCAST : LL_REDUCE;
-            cap = oneshot_ll_capacity_bytes() / es;
-            e = launch_ll_collective(a, dt, cfg);
-        } else if (coll == COLL_REDUCESCATTER) {
-            if (algo == ALGO_RING) { a.mode = RING_REDUCESCATTER; cap = ring_capacity(a.mode, nranks, es, stage_bytes); if (count <= cap) e = launch_ring(a, dt, cfg); }
-            else if (direct) { a.symmetric = 1; a.mode = DIRECT_REDUCESCATTER; cap = count; e = launch_direct(a, dt, cfg); }
-            else { a.mode = TS_REDUCESCATTER; cap = twoshot_capacity(a.mode, nranks, es, stage_bytes); if (count <= cap) e = launch_twoshot(a, dt, cfg); }
-        } else if (coll == COLL_ALLGATHER) {
-            if (algo == ALGO_RING) { a.mode = RING_ALLGATHER; cap = ring_capacity(a.mode, nranks, es, stage_bytes); if (count <= cap) e = launch_ring(a, dt, cfg); }
-            else { a.mode = TS_ALLGATHER; cap = twoshot_capacity(a.mode, nranks, es, stage_bytes); if (count <= cap) e = launch_twoshot(a, dt, cfg); }
-        } else if (coll == COLL_BROADCAST) {
-            a.mode = algo == ALGO_ONESHOT ? TS_BROADCAST_DIRECT : TS_BROADCAST;
-            cap = twoshot_capacity(a.mode, nranks, es, stage_bytes);
-            if (count <= cap) e = launch_twoshot(a, dt, cfg);
-        } else if (coll == COLL_REDUCE) {
-            a.mode = TS_REDUCE;
-            cap = twoshot_capacity(a.mode, nranks, es, stage_bytes);
-            if (count <= cap) e = launch_twoshot(a, dt, cfg);
+            if (coll == COLL_ALLREDUCE) {
+                if (algo == ALGO_ONESHOT) { cap = oneshot_ll_capacity_bytes() / es; if (count <= cap) e = launch_oneshot_ll(a, dt, cfg); }
+                else if (algo == ALGO_TWOSHOT_LL) { a.mode = LL2_ALLREDUCE; cap = ll_twoshot_capacity_bytes(nranks) / es; if (count <= cap) e = launch_ll_twoshot(a, dt, cfg); }
+                else if (algo == ALGO_RING) { a.mode = RING_ALLREDUCE; cap = ring_capacity(a.mode, nranks, es, stage_bytes); if (count <= cap) e = launch_ring(a, dt, cfg); }
+                else if (algo == ALGO_RABENSEIFNER) { cap = hd_capacity(nranks, es, stage_bytes); if (count <= cap && is_power_of_two((uint32_t)nranks)) e = launch_hd(a, dt, cfg); }
+                else if (direct) { a.symmetric = 1; a.mode = DIRECT_ALLREDUCE; cap = count; e = launch_direct(a, dt, cfg); }
+                else { a.mode = TS_ALLREDUCE; cap = twoshot_capacity(a.mode, nranks, es, stage_bytes); if (count <= cap) e = launch_twoshot(a, dt, cfg); }
+            } else if (coll == COLL_REDUCE && algo == ALGO_TWOSHOT_LL) {
+                a.mode = LL2_REDUCE;
+                cap = ll_twoshot_capacity_bytes(nranks) / es;
+                if (count <= cap) e = launch_ll_twoshot(a, dt, cfg);
+            } else if (coll != COLL_ALLREDUCE && algo == ALGO_ONESHOT && count * es <= oneshot_ll_capacity_bytes()) {
+                a.mode = coll == COLL_REDUCESCATTER ? LL_REDUCESCATTER : coll == COLL_ALLGATHER ? LL_ALLGATHER : coll == COLL_BROADCAST ? LL_BROADCAST : LL_REDUCE;
+                cap = oneshot_ll_capacity_bytes() / es;
+                e = launch_ll_collective(a, dt, cfg);
+            } else if (coll == COLL_REDUCESCATTER) {
+                if (algo == ALGO_RING) { a.mode = RING_REDUCESCATTER; cap = ring_capacity(a.mode, nranks, es, stage_bytes); if (count <= cap) e = launch_ring(a, dt, cfg); }
+                else if (direct) { a.symmetric = 1; a.mode = DIRECT_REDUCESCATTER; cap = count; e = launch_direct(a, dt, cfg); }
+                else { a.mode = TS_REDUCESCATTER; cap = twoshot_capacity(a.mode, nranks, es, stage_bytes); if (count <= cap) e = launch_twoshot(a, dt, cfg); }
+            } else if (coll == COLL_ALLGATHER) {
+                if (algo == ALGO_RING) { a.mode = RING_ALLGATHER; cap = ring_capacity(a.mode, nranks, es, stage_bytes); if (count <= cap) e = launch_ring(a, dt, cfg); }
+                else { a.mode = TS_ALLGATHER; cap = twoshot_capacity(a.mode, nranks, es, stage_bytes); if (count <= cap) e = launch_twoshot(a, dt, cfg); }
+            } else if (coll == COLL_BROADCAST) {
+                a.mode = algo == ALGO_ONESHOT ? TS_BROADCAST_DIRECT : TS_BROADCAST;
+                cap = twoshot_capacity(a.mode, nranks, es, stage_bytes);
+                if (count <= cap) e = launch_twoshot(a, dt, cfg);
+            } else if (coll == COLL_REDUCE) {
+                a.mode = TS_REDUCE;
+                cap = twoshot_capacity(a.mode, nranks, es, stage_bytes);
+                if (count <= cap) e = launch_twoshot(a, dt, cfg);
+            }
+            *cap_out = cap;
+            return e;
+        };
+        size_t cap = 0;
+        cudaError_t e = cudaSuccess;
+        // other collectives first, in the same world and on the same buffers (dccl_emu_set_mix): what they leave behind in
+        // flags, packet generations and staging halves is what the call under test starts from
+        for (size_t k = 0; k < g_mix.size() && e == cudaSuccess; k++) {
+            a.seq = next_seq_no++;
+            a.parity = (int)(a.seq & 1u);
+            if (g_device_seq) { a.seq = 0x5eed0000u; a.parity = 0; }
+            e = launch_one(g_mix[k].first, g_mix[k].second, a, &cap);
+            if (e == cudaSuccess && cudaDeviceSynchronize() != cudaSuccess) e = cudaErrorLaunchFailure;
         }
+        a.seq = next_seq_no++;
+        a.parity = (int)(a.seq & 1u);
+        if (g_device_seq) { a.seq = 0x5eed0000u; a.parity = 0; }
+        if (e == cudaSuccess) e = launch_one(coll, algo, a, &cap);
         if (e != cudaSuccess) { fprintf(stderr, "dccl emulation: launch failed or count %zu above capacity %zu: %s\n", count, cap, cudaGetErrorString(e)); rc = -3; break; }
         if (cudaDeviceSynchronize() != cudaSuccess) { rc = fail("kernel"); break; }
         uint32_t st[ST_WORDS];

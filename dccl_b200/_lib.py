@@ -101,6 +101,7 @@ def _declare(lib):
         "dccl_debug_bounds_build": (i, []),
         "dccl_selftest_canary": (i, []),
         "dccl_emu_set_guard": (None, [i]),
+        "dccl_emu_set_mix": (i, [cp]),
         "dccl_emu_set_switch_form": (None, [i]),
         "dccl_emu_declare_stage_bytes": (i, [sz]),
     }

@@ -113,3 +113,24 @@ def test_range_checking_build_refuses_before_it_touches_memory():
         pytest.skip("build-bounds/libdccl.so does not match the bindings (rebuild it: make BOUNDS=1 lib)")
     p = subprocess.run([sys.executable, os.path.join(root, "tests", "workers", "bounds_worker.py")], env=env, capture_output=True, text=True, timeout=600)
     assert p.returncode == 0 and "bounds worker: ok" in p.stdout, p.stdout[-2000:] + p.stderr[-2000:]
+
+
+def test_all_reduce_after_other_kernels_in_the_same_world(dccl_lib):
+    """Two other collectives run before every call under test, in the same virtual world and on the same buffers
+    (dccl_emu_set_mix): rooted packet kernels between all-reduces, staged forms between packet forms. What they leave in
+    flags, packet generations and staging halves is what the next kernel starts from."""
+    import itertools
+    pre = ["allreduce:oneshot", "broadcast:oneshot", "reduce:oneshot", "reducescatter:oneshot", "allgather:oneshot", "allreduce:twoshot_ll",
+           "reduce:twoshot_ll", "allreduce:twoshot", "broadcast:twoshot", "reduce:twoshot", "allreduce:ring", "allreduce:rabenseifner"]
+    n, count = 4, 1031
+    try:
+        for a, b in itertools.product(pre, pre):
+            assert dccl_lib.dccl_emu_set_mix((a + "," + b).encode()) == 2
+            for algo in ["oneshot", "twoshot_ll", "twoshot"]:
+                ins = inputs_for("float32", "sum", count, n, seed=5)
+                out = emu(dccl_lib, "allreduce", algo, n, "float32", "sum", count, ins, root=1, iters=3)
+                want = oracle.fold(ins, "sum")
+                for r in range(n):
+                    assert close(out[r], want, "float32", n), ("after", a, b, algo, r)
+    finally:
+        dccl_lib.dccl_emu_set_mix(b"")

@@ -13,6 +13,7 @@ extern "C" int dccl_emu_sendrecv_ring(int, size_t, int, int, int, const void*, v
 extern "C" void dccl_emu_set_peer_buffers(int);
 extern "C" void dccl_emu_set_device_seq(int);
 extern "C" void dccl_emu_set_switch_form(int);
+extern "C" int dccl_emu_set_mix(const char*);
 
 static int run_one(const char* kind, const char* algo, int n, size_t count, int in_place, size_t misalign) {
     size_t in_e = !strcmp(kind, "reducescatter") ? count * n : count, out_e = !strcmp(kind, "allgather") ? count * n : count;
@@ -72,6 +73,13 @@ int main(int argc, char** argv) {
     dccl_emu_set_peer_buffers(1);       // zero-copy switch forms on multicast-mapped user buffers
     for (const char* kind : kinds) bad += run_one(kind, "nvls", 4, 40000, 0, 0);
     dccl_emu_set_peer_buffers(0);
+    // sequences of different kernels in one world: rooted packet kernels between all-reduces, staged forms between packet forms
+    for (const char* mix : {"allreduce:oneshot,broadcast:oneshot", "reduce:oneshot,allreduce:twoshot_ll", "broadcast:twoshot,reduce:twoshot_ll",
+                            "allreduce:nvls,broadcast:nvls", "allreduce:ring,reducescatter:oneshot"}) {
+        dccl_emu_set_mix(mix);
+        for (const char* algo : {"oneshot", "twoshot_ll", "twoshot", "nvls"}) bad += run_one("allreduce", algo, 4, 1031, 0, 0);
+    }
+    dccl_emu_set_mix("");
     size_t nb = (5u << 20) + 4096;
     std::vector<unsigned char> in(n * nb), out(n * nb);
     for (size_t i = 0; i < in.size(); i++) in[i] = (unsigned char)(i * 7);

@@ -1,6 +1,7 @@
 """The switch (multimem) kernels on the host simulation (DCCL_LIBRARY = build-sim/libdccl.so): staged forms of every
-collective, the pipelined all-reduce and the pipelined broadcast / reduce, against the serial fold. --all adds world
-size 2 and one-element messages."""
+collective, the pipelined all-reduce and the pipelined broadcast / reduce, against the serial fold; then all-reduces that
+follow two other collectives in the same world (sequences of different kernels share flags, packet generations and staging
+halves). --all adds world size 2, one-element messages and more sequences."""
 import os
 import sys
 
@@ -78,6 +79,24 @@ def main():
                         cases += 1
     finally:
         L.dccl_emu_set_peer_buffers(0)
+    # sequences: two other collectives before every call under test, in the same world and on the same buffers; what
+    # they leave in flags, packet generations and staging halves is what the next kernel starts from
+    import itertools
+    pre = ["allreduce:oneshot", "broadcast:oneshot", "reduce:oneshot", "reducescatter:oneshot", "allreduce:twoshot_ll", "reduce:twoshot_ll",
+           "allreduce:twoshot", "broadcast:twoshot", "allreduce:ring", "allreduce:nvls", "broadcast:nvls"]
+    if "--all" not in sys.argv[1:]:
+        pre = pre[:3] + pre[4:7] + pre[9:]
+    n, count = 4, 1031
+    try:
+        for a, b in itertools.product(pre, pre):
+            assert L.dccl_emu_set_mix((a + "," + b).encode()) == 2
+            for algo in ["oneshot", "twoshot_ll", "twoshot", "nvls"]:
+                ins = inputs_for("float32", "sum", count, n, seed=5)
+                out = emu(L, "allreduce", algo, n, "float32", "sum", count, ins, root=1, iters=3)
+                assert all(close(out[r], oracle.fold(ins, "sum"), "float32", n) for r in range(n)), ("after", a, b, algo)
+                cases += 1
+    finally:
+        L.dccl_emu_set_mix(b"")
     print("sim switch worker: ok (%d cases)" % cases)
 
 
