@@ -469,6 +469,77 @@ int dccl_emu_sendrecv_ring(int nranks, size_t bytes, int window, int ctas_per_op
 }
 
 /**
+ * All-to-all among virtual ranks as the library composes it from grouped send / recv: every rank records its
+ * receives from rank - k and then its sends to rank + k (k = 1 .. n-1) and launches them together, `iters` times.
+ * Block p of a rank's input (`bytes` each) goes to rank p; the own block is not moved by the kernel and is copied here.
+ * host_in / host_out: nranks x nranks blocks.
+ */
+int dccl_emu_all_to_all(int nranks, size_t bytes, int ctas_per_op, int iters, const void* host_in, void* host_out) {
+    if (nranks < 2 || nranks > kMaxPeers || ctas_per_op < 1 || ctas_per_op > kP2pCtas || 2 * (nranks - 1) > kMaxP2pOps) return -2;
+    EmuWorld w;
+    if (!w.create(nranks, 1u << 20, 2000)) return fail("cannot create the virtual ranks");
+    const size_t n = (size_t)nranks;
+    std::vector<char*> sb(n), rb(n);
+    for (size_t r = 0; r < n; r++) {
+        if (cudaMalloc((void**)&sb[r], n * bytes + 16) != cudaSuccess || cudaMalloc((void**)&rb[r], n * bytes + 16) != cudaSuccess) return fail("cudaMalloc");
+        cudaMemcpy(sb[r], (const char*)host_in + r * n * bytes, n * bytes, cudaMemcpyHostToDevice);
+        cudaMemset(rb[r], 0xEE, n * bytes);
+    }
+    P2pOp* d_ops = nullptr;
+    int* d_nops = nullptr;
+    cudaMalloc((void**)&d_ops, n * kMaxP2pOps * sizeof(P2pOp));
+    cudaMalloc((void**)&d_nops, n * sizeof(int));
+    const int nops = 2 * (nranks - 1);
+    std::vector<int> nops_v(n, nops);
+    cudaMemcpy(d_nops, nops_v.data(), n * sizeof(int), cudaMemcpyHostToDevice);
+    int rc = 0;
+    // chunks moved so far per ordered pair (every pair moves one message per iteration)
+    unsigned long long chunk_base = 0;
+    for (int it = 0; it < iters && rc == 0; it++) {
+        std::vector<P2pOp> ops(n * kMaxP2pOps);
+        for (size_t r = 0; r < n; r++) {
+            int k = 0;
+            for (size_t d = 1; d < n; d++) {        // receivers first: they get the lower block numbers
+                const size_t p = (r + n - d) % n;
+                P2pOp& o = ops[r * kMaxP2pOps + k++];
+                o.is_send = 0; o.peer = (int)p; o.buf = rb[r] + p * bytes; o.bytes = bytes; o.chunk_base = chunk_base;
+            }
+            for (size_t d = 1; d < n; d++) {
+                const size_t p = (r + d) % n;
+                P2pOp& o = ops[r * kMaxP2pOps + k++];
+                o.is_send = 1; o.peer = (int)p; o.buf = sb[r] + p * bytes; o.bytes = bytes; o.chunk_base = chunk_base;
+            }
+        }
+        chunk_base += p2p_chunks(bytes);
+        cudaMemcpy(d_ops, ops.data(), ops.size() * sizeof(P2pOp), cudaMemcpyHostToDevice);
+        P2pArgs a;
+        memset(&a, 0, sizeof(a));
+        a.emu = w.d_comms;
+        a.emu_ops = d_ops;
+        a.emu_nops = d_nops;
+        a.ctas_per_op = ctas_per_op;
+        a.ctas_per_rank = nops * ctas_per_op;
+        LaunchCfg cfg;
+        cfg.ctas = a.ctas_per_rank;
+        cfg.ranks_in_launch = nranks;
+        if (launch_p2p(a, cfg) != cudaSuccess || cudaDeviceSynchronize() != cudaSuccess) { rc = fail("all-to-all kernel"); break; }
+        uint32_t st[ST_WORDS];
+        cudaMemcpy(st, w.status, sizeof(st), cudaMemcpyDeviceToHost);
+        if (st[ST_CODE] != DEV_OK) rc = 100 + (int)st[ST_CODE];
+    }
+    if (rc == 0) rc = w.check_guards();
+    if (rc == 0)
+        for (size_t r = 0; r < n; r++) {
+            cudaMemcpy(rb[r] + r * bytes, sb[r] + r * bytes, bytes, cudaMemcpyDeviceToDevice);    // the own block
+            cudaMemcpy((char*)host_out + r * n * bytes, rb[r], n * bytes, cudaMemcpyDeviceToHost);
+        }
+    for (size_t r = 0; r < n; r++) { cudaFree(sb[r]); cudaFree(rb[r]); }
+    cudaFree(d_ops);
+    cudaFree(d_nops);
+    return rc;
+}
+
+/**
  * Bounded-wait check: one thread waits, with a `timeout_ms` budget, for a flag that nothing sets.
  * Returns the status code the kernel recorded (DEV_TIMEOUT = 1 is the expected answer) and the time
  * the kernel took in milliseconds through *elapsed_ms. The context stays usable afterwards.

@@ -91,6 +91,7 @@ def _declare(lib):
     cuda_only = {
         "dccl_emu_collective": (i, [cp, cp, i, i, i, sz, i, i, i, sz, i, sz, vp, vp]),
         "dccl_emu_sendrecv_ring": (i, [i, sz, i, i, i, vp, vp]),
+        "dccl_emu_all_to_all": (i, [i, sz, i, i, vp, vp]),
         "dccl_emu_wait_probe": (i, [c.c_uint, c.POINTER(c.c_float)]),
         "dccl_nvml_link_report": (i, [cp, cp, sz]),
         "dccl_selftest_symmem": (i, [vp, i]),

@@ -134,3 +134,18 @@ def test_all_reduce_after_other_kernels_in_the_same_world(dccl_lib):
                     assert close(out[r], want, "float32", n), ("after", a, b, algo, r)
     finally:
         dccl_lib.dccl_emu_set_mix(b"")
+
+
+@pytest.mark.parametrize("n,ctas", [(2, 4), (4, 4), (8, 2), (5, 10)])
+def test_all_to_all_as_grouped_send_recv(dccl_lib, n, ctas):
+    """The launch the library composes for an all-to-all: every rank's receives from rank - k, then its sends to rank + k,
+    in one launch, three times in a row; blocks shorter and longer than the FIFO, the last chunk short."""
+    for nbytes in [4, 1000, 65536 + 8, (1 << 20) + 24, (5 << 20) + 8]:
+        hin = np.random.default_rng(nbytes + n).integers(0, 255, size=n * n * nbytes, dtype=np.uint8)
+        hout = np.zeros_like(hin)
+        rc = dccl_lib.dccl_emu_all_to_all(n, nbytes, ctas, 3, hin.ctypes.data, hout.ctypes.data)
+        assert rc == 0, (n, nbytes, rc)
+        src, got = hin.reshape(n, n, nbytes), hout.reshape(n, n, nbytes)
+        for r in range(n):
+            for p in range(n):
+                assert np.array_equal(got[r, p], src[p, r]), (n, nbytes, r, p)

@@ -14,6 +14,7 @@ extern "C" void dccl_emu_set_peer_buffers(int);
 extern "C" void dccl_emu_set_device_seq(int);
 extern "C" void dccl_emu_set_switch_form(int);
 extern "C" int dccl_emu_set_mix(const char*);
+extern "C" int dccl_emu_all_to_all(int, size_t, int, int, const void*, void*);
 
 static int run_one(const char* kind, const char* algo, int n, size_t count, int in_place, size_t misalign) {
     size_t in_e = !strcmp(kind, "reducescatter") ? count * n : count, out_e = !strcmp(kind, "allgather") ? count * n : count;
@@ -85,5 +86,13 @@ int main(int argc, char** argv) {
     for (size_t i = 0; i < in.size(); i++) in[i] = (unsigned char)(i * 7);
     int rc = dccl_emu_sendrecv_ring(n, nb, 1, 4, 2, in.data(), out.data());
     printf("sendrecv rc=%d\n", rc);
+    {   // the all-to-all launch: receives and sends of every rank together, blocks longer than the FIFO
+        const size_t blk = (4u << 20) + 4096;
+        std::vector<unsigned char> ain(n * n * blk), aout(n * n * blk);
+        for (size_t i = 0; i < ain.size(); i++) ain[i] = (unsigned char)(i * 13);
+        const int arc = dccl_emu_all_to_all(n, blk, 2, 2, ain.data(), aout.data());
+        printf("all_to_all rc=%d\n", arc);
+        bad += arc != 0;
+    }
     return bad + (rc != 0);
 }
