@@ -44,33 +44,23 @@ def test_peer_handles_fallback_without_multicast():
     run(2, ["--suite", "chunk"], env={"DCCL_POOL_MODE": "ipc", "DCCL_STAGING_BYTES": str(16 << 20)})
 
 
-# Paths that exist and are tested on the host or in the single-GPU emulation but have not yet run on several GPUs.
-# They are kept apart, and a failure is reported as an expected one, so that a first run on hardware cannot hide the
-# results of the suites above; the marks go away with the first clean run.
-FIRST_RUN = pytest.mark.xfail(reason="first run of this path on several GPUs", strict=False)
-
-
-@FIRST_RUN
 @pytest.mark.skipif(gpu_count() < 2, reason="needs two GPUs")
 def test_topology_packets_two_shot_and_composed_collectives():
     """dcclGetTopology, the two-shot packet all-reduce / reduce, all-to-all / gather / scatter on device buffers."""
     run(min(gpu_count(), 8), ["--suite", "extra"])
 
 
-@FIRST_RUN
 @pytest.mark.skipif(gpu_count() < 2, reason="needs two GPUs")
 def test_no_variant_writes_between_the_pool_regions():
     """The basic suite with guard words in the unused parts of every rank's pool, checked at the end."""
     run(min(gpu_count(), 8), ["--suite", "basic"], env={"DCCL_DEBUG_BOUNDS": "1"})
 
 
-@FIRST_RUN
 @pytest.mark.skipif(gpu_count() < 2, reason="needs two GPUs")
 def test_pipelined_switch_broadcast_and_reduce():
     run(min(gpu_count(), 8), ["--suite", "rooted"])
 
 
-@FIRST_RUN
 @pytest.mark.skipif(gpu_count() < 2, reason="needs two GPUs")
 @pytest.mark.parametrize("worker", ["tp_worker.py", "zero_worker.py", "moe_worker.py", "cp_worker.py", "llama_tp_worker.py"])
 def test_differentiable_collectives_and_parallel_layers_on_device_tensors(worker):

@@ -65,7 +65,6 @@ def test_p2p_perf_and_sweep_tool_on_gpus(build_dir, tmp_path):
     assert len(rows) == 9 and all(r["us"] > 0 for r in rows)
 
 
-@pytest.mark.xfail(reason="first run of this tool on a GPU", strict=False)
 def test_topology_tool_lists_the_visible_gpus(build_dir):
     """dccl_topo: one entry per visible GPU, every pair peer-accessible on an NVSwitch box, a one-line summary."""
     import json

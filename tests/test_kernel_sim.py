@@ -2,16 +2,16 @@
 
 `make SIM=1 lib` compiles the kernel sources and the single-GPU emulation
 harness as ordinary C++ against stand-in CUDA headers (csrc/sim/): every CUDA thread becomes an OS thread, flags are
-host atomics, a packet is two 8-byte atomic halves. The tests of tests/test_gpu_emu.py and tests/first_run_emu.py then
+host atomics, a packet is two 8-byte atomic halves. The tests of tests/test_gpu_emu.py then
 run unchanged against build-sim/libdccl.so (DCCL_LIBRARY), which checks the flag protocol, the packet generations, the
 staging geometry and the reductions of twoshot / oneshot / twoshot_ll / ring / rabenseifner / zero-copy two-shot /
 send-recv, and (with a simulated multicast mapping) of the switch kernels. The scheduling of OS threads is far less regular than a GPU's, which is the point: an ordering the protocol
 does not enforce shows up as a wrong result here (it did: the send/recv FIFO used to cut a short last chunk
 differently from a full one, so that a sender could overwrite bytes another receiving CTA had not read yet).
 
-A subset runs here (about a minute); the whole of both files passes as well:
-    make SIM=1 lib && DCCL_LIBRARY=$PWD/build-sim/libdccl.so python -m pytest tests/test_gpu_emu.py tests/first_run_emu.py -m gpu -q
-(deselect the local-reduce, bounded-wait and child-process tests, whose kernels are not part of the simulation).
+A subset runs here (about a minute); the whole file passes as well:
+    make SIM=1 lib && DCCL_LIBRARY=$PWD/build-sim/libdccl.so python -m pytest tests/test_gpu_emu.py -m gpu -q
+(deselect the local-reduce and bounded-wait tests, whose kernels are not part of the simulation).
 """
 import os
 import subprocess
@@ -35,10 +35,9 @@ def sim_lib():
 
 def test_emulation_tests_on_the_host_simulation(sim_lib):
     select = ("fp32_bf16_sizes or roots or send_recv_ring or ring_order or (two_shot_packet and 2) or guard_words or sequence_number "
-              "or (all_to_all_as and (4-4 or 8-2))")
+              "or (all_to_all_as and (4-4 or 8-1))")
     env = dict(os.environ, DCCL_LIBRARY=sim_lib)
-    p = subprocess.run([sys.executable, "-m", "pytest", os.path.join(ROOT, "tests", "test_gpu_emu.py"),
-                        os.path.join(ROOT, "tests", "first_run_emu.py"), "-q", "-m", "gpu", "-p", "no:cacheprovider", "-k", select],
+    p = subprocess.run([sys.executable, "-m", "pytest", os.path.join(ROOT, "tests", "test_gpu_emu.py"), "-q", "-m", "gpu", "-p", "no:cacheprovider", "-k", select],
                        env=env, capture_output=True, text=True, timeout=1500)
     assert p.returncode == 0, p.stdout[-4000:] + p.stderr[-2000:]
     assert " passed" in p.stdout and "failed" not in p.stdout, p.stdout[-2000:]

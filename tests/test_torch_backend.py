@@ -35,10 +35,7 @@ def test_single_gpu_process_group():
     run(1, ["--cuda", "--ddp"], gpus=True)
 
 
-# These operations are tested on CPU tensors above; on CUDA tensors they have not run yet. A failure is reported as an
-# expected one so that it cannot hide the results of the tests above; the mark goes away with the first clean run.
 @pytest.mark.gpu
-@pytest.mark.xfail(reason="first run of these operations on CUDA tensors", strict=False)
 @pytest.mark.skipif(gpu_count() < 2, reason="needs two GPUs")
 def test_all_to_all_gather_scatter_batches_objects_subgroups_on_cuda_tensors():
     run(min(gpu_count(), 8), ["--cuda", "--extra"], gpus=True)
