@@ -3,6 +3,7 @@
  * package binds these). Every function returns the ncclResult_t value as int;
  * C++ exceptions (a null communicator) become ncclInvalidArgument.
  */
+#include <vector>
 #include <dccl/dccl.hpp>
 #include "../core/config.hpp"
 #include "../core/types.hpp"
@@ -55,6 +56,7 @@ int dccl_comm_bind_device(void* comm, int device) {
 }
 int dccl_has_multicast(void* comm) { dcclComm* c = (dcclComm*)comm; return c && c->gpu && c->gpu->has_multicast() ? 1 : 0; }
 unsigned long long dccl_launch_count(void* comm) { dcclComm* c = (dcclComm*)comm; return c && c->gpu ? c->gpu->launches() : 0ull; }
+unsigned long long dccl_comm_stat(void* comm, const char* name) { dcclComm* c = (dcclComm*)comm; return c && c->gpu ? c->gpu->stat(name) : 0ull; }
 int dccl_comm_set_param(void* comm, const char* name, int value) { dcclComm* c = (dcclComm*)comm; return c && c->gpu && c->gpu->set_param(name, value) ? 0 : (int)ncclInvalidArgument; }
 int dccl_cuda_device_count() { return cuda_device_count(); }
 int dccl_barrier(void* comm) { GUARD(dcclBarrier((ncclComm_t)comm)); }
@@ -114,6 +116,30 @@ int dccl_group_end() { return (int)dcclGroupEnd(); }
 int dccl_set_algorithm(void* comm, const char* coll, const char* name) { GUARD(dcclSetAlgorithm((ncclComm_t)comm, coll, name)); }
 const char* dccl_last_algorithm(void* comm, const char* coll) {
     try { return dcclGetLastAlgorithm((ncclComm_t)comm, coll); } catch (...) { return ""; }
+}
+
+/**
+ * Self test of the exchange board (Bootstrap::fast_allgather): `rounds` all-gathers of a message whose bytes depend on
+ * rank and round; the ranks are skewed on purpose (rank r pauses before round k when k % world == r), so that readers
+ * meet both a writer that is ahead and one that is behind. Returns 0, or 1 + the round that delivered wrong bytes,
+ * or -1 when an exchange failed.
+ */
+int dccl_selftest_board(void* comm, int rounds) {
+    dcclComm* c = (dcclComm*)comm;
+    if (!c) return -1;
+    Bootstrap& bs = c->bs;
+    const int n = bs.world(), r = bs.rank();
+    std::vector<unsigned char> mine(kBoardBytes), all((size_t)n * kBoardBytes);
+    for (int k = 0; k < rounds; k++) {
+        const size_t bytes = 1 + (size_t)(k * 37) % kBoardBytes;
+        for (size_t i = 0; i < bytes; i++) mine[i] = (unsigned char)(r * 31 + k * 7 + (int)i);
+        if (k % n == r) usleep(200);
+        if (!bs.fast_allgather(mine.data(), bytes, all.data())) return -1;
+        for (int p = 0; p < n; p++)
+            for (size_t i = 0; i < bytes; i++)
+                if (all[(size_t)p * bytes + i] != (unsigned char)(p * 31 + k * 7 + (int)i)) return 1 + k;
+    }
+    return 0;
 }
 
 /**

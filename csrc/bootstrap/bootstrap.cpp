@@ -1,4 +1,5 @@
 #include "bootstrap.hpp"
+#include <sched.h>
 #include "../core/config.hpp"
 #include "../core/log.hpp"
 
@@ -159,6 +160,30 @@ bool Bootstrap::map_segments(std::string* err) {
         ::close(fd);
         if (p == MAP_FAILED) { if (err) *err = "mmap data"; return false; }
         data_ = (char*)p;
+    }
+    return true;
+}
+
+bool Bootstrap::fast_allgather(const void* in, size_t bytes, void* out) {
+    if (bytes > kBoardBytes || !ctl_) { err_ = "fast_allgather: message too large"; return false; }
+    if (world_ == 1) { memcpy(out, in, bytes); return true; }
+    const uint64_t seq = ++board_seq_;
+    const int gen = (int)(seq & 1u);
+    CtlBoardSlot& mine = ctl_->board[rank_][gen];
+    memcpy(mine.data, in, bytes);
+    mine.seq.store(seq, std::memory_order_release);
+    const int64_t deadline = now_ms() + op_timeout_ms_;
+    for (int p = 0; p < world_; p++) {
+        CtlBoardSlot& s = ctl_->board[p][gen];
+        uint32_t spins = 0;
+        while (s.seq.load(std::memory_order_acquire) != seq) {
+            if ((++spins & 0x3ffu) == 0) {
+                if (aborted()) { err_ = "fast_allgather: group aborted"; return false; }
+                if (now_ms() > deadline) { err_ = "fast_allgather: timed out waiting for rank " + std::to_string(p); return false; }
+                if (spins > (1u << 16)) sched_yield();
+            }
+        }
+        memcpy((char*)out + (size_t)p * bytes, s.data, bytes);
     }
     return true;
 }

@@ -58,12 +58,21 @@ struct CtlShrink {
     uint64_t alive_mask;               // ranks of this group that are members of the next one
     UniqueIdData id;                   // where the next group meets
 };
+/** One rank's entry of the exchange board: two generations of a small message, each with the number of the
+ *  exchange that wrote it (fast_allgather). */
+static const size_t kBoardBytes = 240;
+struct CtlBoardSlot {
+    std::atomic<uint64_t> seq;
+    char pad[8];
+    char data[kBoardBytes];
+};
 struct CtlSegment {
     std::atomic<uint32_t> abort;       // non-zero: somebody failed; value = 1 + failed rank
     std::atomic<uint32_t> abort_code;  // ncclResult_t
     char pad[56];
     CtlRank ranks[kMaxRanks];
     CtlShrink shrink;
+    CtlBoardSlot board[kMaxRanks][2];
 };
 
 /** One direction of a rank pair: single-producer single-consumer byte FIFO. */
@@ -95,6 +104,14 @@ public:
     bool allgather(const void* in, size_t bytes, void* out);
     bool barrier();
     bool broadcast(void* buf, size_t bytes, int root);
+    /**
+     * All-gather of a small message (at most kBoardBytes) through the shared control segment: no system call, a few
+     * microseconds when the ranks arrive together. Every rank writes its message with the exchange number into its own
+     * board entry and reads the others' once they carry that number. Two generations alternate: a rank can only start
+     * exchange k + 2 after every rank has published k + 1, i.e. has read all of k. For per-call agreement on the host
+     * (lazy buffer registration); all ranks must call it in the same order. False on abort or after the time limit.
+     */
+    bool fast_allgather(const void* in, size_t bytes, void* out);
 
     bool send_fd(int peer, int fd, uint32_t tag);
     bool recv_fd(int peer, uint32_t tag, int* fd, int timeout_ms);
@@ -145,6 +162,7 @@ private:
     size_t data_bytes_ = 0, chan_bytes_ = 0, chan_stride_ = 0;
     int heartbeat_ms_ = 100, hb_timeout_ms_ = 10000, op_timeout_ms_ = 60000;
     uint64_t ops_ = 0;
+    uint64_t board_seq_ = 0;        // exchanges over the board so far
     uint32_t shrink_seen_ = 0;      // generation of the last shrink this rank took part in
     std::string err_;
     std::function<void(int)> abort_cb_;

@@ -93,6 +93,8 @@ struct CollArgs {
     int mode;
     int symmetric;         // user buffers are in symmetric memory (zero-copy variant)
     int unroll;            // vectors in flight per thread in the switch pass (2, 4 or 8)
+    int pipe_nv;           // pipelined switch kernels: CTAs of the switch group ...
+    int pipe_copy;         // ... and of each copy group
 };
 
 struct Ctx {

@@ -51,6 +51,7 @@ const DriverApi* driver_api(std::string* err) {
             vmm &= resolve("cuDeviceGet", &g_api.DeviceGet);
             vmm &= resolve("cuDeviceGetAttribute", &g_api.DeviceGetAttribute);
             resolve("cuGetErrorString", &g_api.GetErrorString);
+            resolve("cuPointerGetAttribute", &g_api.PointerGetAttribute);
             mc &= resolve("cuMulticastCreate", &g_api.MulticastCreate);
             mc &= resolve("cuMulticastAddDevice", &g_api.MulticastAddDevice);
             mc &= resolve("cuMulticastBindMem", &g_api.MulticastBindMem);

@@ -31,6 +31,7 @@ struct DriverApi {
     CUresult (*DeviceGet)(CUdevice*, int);
     CUresult (*DeviceGetAttribute)(int*, CUdevice_attribute, CUdevice);
     CUresult (*GetErrorString)(CUresult, const char**);
+    CUresult (*PointerGetAttribute)(void*, CUpointer_attribute, CUdeviceptr);   // optional (lazy registration)
     bool vmm_ok = false;         // all memory-management entry points resolved
     bool multicast_ok = false;   // all multicast entry points resolved
 };

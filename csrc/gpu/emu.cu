@@ -42,8 +42,9 @@ size_t g_declared_stage = 0;
 #endif
 #ifdef DCCL_HOST_SIM
 // Host simulation only (a single GPU has no NVSwitch to play): which switch kernel serves algorithm "nvls".
-// 0 staged (nvls.cu), 1 pipelined all-reduce (nvls_pipe.cu), 2 pipelined broadcast / reduce (nvls_rooted.cu)
+// 0 staged (nvls.cu), 1 pipelined all-reduce / reduce-scatter (nvls_pipe.cu), 2 pipelined broadcast / reduce (nvls_rooted.cu)
 int g_switch_form = 0;
+int g_pipe_nv = 0;
 #endif
 
 // Pools of finished emulation runs, kept for the next run of the same size (the tests make thousands of short
@@ -214,6 +215,9 @@ int dccl_emu_declare_stage_bytes(size_t bytes) {
 /** Host simulation only: the switch kernel behind algorithm "nvls": 0 staged, 1 pipelined all-reduce,
  *  2 pipelined broadcast / reduce. */
 void dccl_emu_set_switch_form(int form) { g_switch_form = form; }
+/** Host simulation only: target chunk size of the pipelined switch kernels and the size of their switch group
+ *  (0: the default share of the grid). */
+void dccl_emu_set_pipe(size_t chunk_bytes, int nv_ctas) { nvls_pipe_set_chunk_bytes(chunk_bytes); g_pipe_nv = nv_ctas; }
 #endif
 
 /** 1: all-reduce with the two-shot variant runs its zero-copy form on the emulated ranks' user buffers. */
@@ -324,7 +328,12 @@ int dccl_emu_collective(const char* kind_s, const char* algo_s, int nranks, int 
                     cap = nvls_pipe_capacity(es, stage_bytes, nranks, false);
                     LaunchCfg pc = cfg;
                     pc.ctas = cfg.ctas < 3 ? 3 : cfg.ctas;
-                    if (count <= cap) e = launch_nvls_pipe(a, dt, pc, false);
+                    if (count <= cap) e = launch_nvls_pipe(a, dt, pc, false, g_pipe_nv);
+                } else if (coll == COLL_REDUCESCATTER && g_switch_form == 1) {
+                    cap = nvls_pipe_capacity(es, stage_bytes, nranks, true);
+                    LaunchCfg pc = cfg;
+                    pc.ctas = cfg.ctas < 2 ? 2 : cfg.ctas;
+                    if (count <= cap) e = launch_nvls_pipe(a, dt, pc, true, g_pipe_nv);
                 } else if ((coll == COLL_BROADCAST || coll == COLL_REDUCE) && g_switch_form == 2) {
                     a.mode = coll == COLL_BROADCAST ? ROOTED_BROADCAST : ROOTED_REDUCE;
                     cap = nvls_pipe_capacity(es, stage_bytes, nranks, false);

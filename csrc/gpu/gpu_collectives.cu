@@ -34,10 +34,20 @@ bool GpuCommImpl::set_param(const char* name, int value) {
     if (k == "p2p_ctas" && value >= 1 && value <= kP2pCtas) { p2p_ctas_ = value; return true; }
     if (k == "pipe_min_mb" && value >= 0) { pipe_min_bytes_ = (size_t)value << 20; return true; }
     if (k == "pipe_ctas" && value >= 3 && value <= kMaxCtas) { pipe_ctas_ = value; return true; }
+    if (k == "pipe_nv_ctas" && value >= 1 && value <= kMaxCtas / 2) { pipe_nv_ctas_ = value; return true; }
+    if (k == "auto_register_min_kb" && value >= 0) { auto_min_bytes_ = (size_t)value << 10; return true; }
+    if (k == "direct_rs" && (value == 0 || value == 1)) { direct_rs_ = value == 1; return true; }
     if (k == "device_seq" && (value == 0 || value == 1)) return set_device_seq(value == 1);
     if (k == "rooted_pipe" && (value == 0 || value == 1)) { rooted_pipe_ = value == 1; return true; }
     if (k == "pipe_chunk_kb" && value >= 256) { nvls_pipe_set_chunk_bytes((size_t)value << 10); return true; }
     return false;
+}
+
+uint64_t GpuCommImpl::stat(const char* name) const {
+    const std::string k(name ? name : "");
+    if (k == "launches") return launches_;
+    if (k == "zero_copy_calls") return zero_copy_calls_;
+    return 0;
 }
 
 CollArgs GpuCommImpl::base_args(const void* send, void* recv, ncclRedOp_t op, int root) {
@@ -122,8 +132,15 @@ ncclResult_t GpuCommImpl::all_reduce(const void* send, void* recv, size_t count,
         return cuda_result(launch_ll_twoshot(a, dt, cfg), "two-shot packet all-reduce");
     }
 
+    // ordinary buffers that were never registered: the ranks exchange where they lie and map what is new (collective;
+    // entered on facts every rank shares), after which the call runs zero-copy like one on registered buffers
+    if (ch.algo == ALGO_TWOSHOT && !peer_addr && auto_min_bytes_ > 0 && bytes >= auto_min_bytes_ && auto_view(send, recv, sp, rp)) {
+        peer_addr = true;
+        for (int p = 0; peer_addr && p < n_; p++) peer_addr = (uintptr_t)sp[p] % 16 == 0 && (uintptr_t)rp[p] % 16 == 0;
+    }
     // two-shot on buffers the peers can address: fold straight out of / into the user buffers, no staging
     if (ch.algo == ALGO_TWOSHOT && peer_addr) {
+        zero_copy_calls_++;
         a.symmetric = 1;
         for (int p = 0; p < n_; p++) { a.io.send_peer[p] = sp[p]; a.io.recv_peer[p] = (char*)rp[p]; }
         a.mode = DIRECT_ALLREDUCE;
@@ -147,10 +164,7 @@ ncclResult_t GpuCommImpl::all_reduce(const void* send, void* recv, size_t count,
 
     // large ordinary buffers through the switch: copy-in, switch pass and copy-out overlap chunk by chunk
     const bool pipe = ch.algo == ALGO_NVLS && pipe_min_bytes_ > 0 && bytes >= pipe_min_bytes_;
-    if (pipe) {
-        cfg.ctas = pipe_ctas_ < sm_count_ ? pipe_ctas_ : sm_count_;
-        if (ctas_override_ >= 9) cfg.ctas = ctas_override_ < sm_count_ ? ctas_override_ : sm_count_;
-    }
+    if (pipe) cfg.ctas = pipe_ctas_ < sm_count_ ? pipe_ctas_ : sm_count_;
     size_t cap;
     switch (ch.algo) {
     case ALGO_NVLS: cap = pipe ? nvls_pipe_capacity(es, stage_bytes_, n_, false) : nvls_capacity(NV_ALLREDUCE, n_, es, stage_bytes_); break;
@@ -167,7 +181,7 @@ ncclResult_t GpuCommImpl::all_reduce(const void* send, void* recv, size_t count,
         cudaError_t e;
         switch (ch.algo) {
         case ALGO_NVLS:
-            if (pipe) e = launch_nvls_pipe(a, dt, cfg, false);
+            if (pipe) e = launch_nvls_pipe(a, dt, cfg, false, pipe_nv_ctas_);
             else { a.mode = NV_ALLREDUCE; e = launch_nvls(a, dt, cfg); }
             break;
         case ALGO_RING: a.mode = RING_ALLREDUCE; e = launch_ring(a, dt, cfg); break;
@@ -224,13 +238,17 @@ ncclResult_t GpuCommImpl::reduce_scatter(const void* send, void* recv, size_t re
     // two-shot on buffers the peers can address: every rank folds its slot straight out of the peers' send buffers.
     // Chosen by itself only at world size 2, where this form is measured (all-reduce: 1.5 x the staged form);
     // elsewhere the caller asks for it with dcclSetAlgorithm(twoshot).
-    if (ch.algo == ALGO_TWOSHOT && (n_ == 2 || algo == ALGO_TWOSHOT)) {
+    if (ch.algo == ALGO_TWOSHOT && (n_ == 2 || direct_rs_ || algo == ALGO_TWOSHOT) && (recvcount * es) % 16 == 0) {
+        // the kernel moves whole 16-byte vectors, so every rank's send and receive pointer must be aligned; the ranks
+        // know each other's through the symmetric layout or through the exchange
         const char* rp[kMaxPeers];
         const char* rmc = nullptr;
-        bool peer_addr = (recvcount * es) % 16 == 0 && sym_view(send, bytes, sym_peers, &sym_mc) && sym_view(recv, recvcount * es, rp, &rmc);
+        bool peer_addr = sym_view(send, bytes, sym_peers, &sym_mc) && sym_view(recv, recvcount * es, rp, &rmc);
+        if (!peer_addr && auto_min_bytes_ > 0 && bytes >= auto_min_bytes_) peer_addr = auto_view(send, recv, sym_peers, rp);
         // every rank must come to the same answer, so every rank's alignment counts
         for (int p = 0; peer_addr && p < n_; p++) peer_addr = (uintptr_t)sym_peers[p] % 16 == 0 && (uintptr_t)rp[p] % 16 == 0;
         if (peer_addr) {
+            zero_copy_calls_++;
             a.symmetric = 1;
             for (int p = 0; p < n_; p++) a.io.send_peer[p] = sym_peers[p];
             a.mode = DIRECT_REDUCESCATTER;
@@ -252,10 +270,13 @@ ncclResult_t GpuCommImpl::reduce_scatter(const void* send, void* recv, size_t re
         }
     }
     // large ordinary buffers through the switch: copy-in and switch pass overlap chunk by chunk
-    const bool pipe = ch.algo == ALGO_NVLS && pipe_min_bytes_ > 0 && bytes >= pipe_min_bytes_ && (uintptr_t)recv % 16 == 0 && (recvcount * es) % 16 == 0;
+    // (only facts that are the same on every rank may pick the kernel; an unaligned receive buffer is handled inside it)
+    const bool pipe = ch.algo == ALGO_NVLS && pipe_min_bytes_ > 0 && bytes >= pipe_min_bytes_;
     if (pipe) {
-        cfg.ctas = pipe_ctas_ < sm_count_ ? pipe_ctas_ : sm_count_;
-        if (ctas_override_ >= 5) cfg.ctas = ctas_override_ < sm_count_ ? ctas_override_ : sm_count_;
+        // the switch group as in the all-reduce, one copy group instead of two
+        const int total = pipe_ctas_ < sm_count_ ? pipe_ctas_ : sm_count_;
+        const int nv = pipe_nv_ctas_ < total ? pipe_nv_ctas_ : total / 3;
+        cfg.ctas = nv + (total - nv) / 2;
     }
     size_t cap = pipe ? nvls_pipe_capacity(es, stage_bytes_, n_, true)
                  : ch.algo == ALGO_NVLS ? nvls_capacity(NV_REDUCESCATTER, n_, es, stage_bytes_)
@@ -268,7 +289,7 @@ ncclResult_t GpuCommImpl::reduce_scatter(const void* send, void* recv, size_t re
         a.count = c;
         NEXT_SEQ(a);
         cudaError_t e;
-        if (pipe) e = launch_nvls_pipe(a, dt, cfg, true);
+        if (pipe) e = launch_nvls_pipe(a, dt, cfg, true, pipe_nv_ctas_);
         else if (ch.algo == ALGO_NVLS) { a.mode = NV_REDUCESCATTER; e = launch_nvls(a, dt, cfg); }
         else if (ch.algo == ALGO_RING) { a.mode = RING_REDUCESCATTER; e = launch_ring(a, dt, cfg); }
         else { a.mode = TS_REDUCESCATTER; e = launch_twoshot(a, dt, cfg); }
@@ -318,7 +339,8 @@ ncclResult_t GpuCommImpl::all_gather(const void* send, void* recv, size_t sendco
     if (ch.algo == ALGO_NVLS) {
         const char* rp[kMaxPeers];
         const char* rmc = nullptr;
-        if ((sendcount * es) % 16 == 0 && (uintptr_t)send % 16 == 0 && sym_view(recv, bytes, rp, &rmc) && rmc && (uintptr_t)rmc % 16 == 0) {
+        // only facts that every rank shares decide; a source that is not 16-byte aligned is handled inside the kernel
+        if ((sendcount * es) % 16 == 0 && sym_view(recv, bytes, rp, &rmc) && rmc && (uintptr_t)rmc % 16 == 0) {
             a.symmetric = 1;
             a.io.recv_mc = (char*)rmc;
             a.mode = NV_ALLGATHER;

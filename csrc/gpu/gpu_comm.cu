@@ -57,7 +57,10 @@ bool GpuCommImpl::init(std::string* err) {
     set_param("threads", (int)cfg.get_int("DCCL/threads", 512));
     set_param("unroll", (int)cfg.get_int("DCCL/unroll", 8));
     pipe_min_bytes_ = (size_t)cfg.get_int("DCCL/nvls_pipe_min_bytes", 16ll << 20);
-    pipe_ctas_ = (int)cfg.get_int("DCCL/nvls_pipe_ctas", 144);
+    auto_min_bytes_ = (size_t)cfg.get_int("DCCL/auto_register_min_bytes", 4ll << 20);
+    direct_rs_ = cfg.get_bool("DCCL/direct_reduce_scatter", false);
+    pipe_ctas_ = (int)cfg.get_int("DCCL/nvls_pipe_ctas", 80);
+    pipe_nv_ctas_ = (int)cfg.get_int("DCCL/nvls_pipe_nv_ctas", 16);
     device_stamps_ = cfg.get_bool("DCCL/device_stamps", false);
     rooted_pipe_ = cfg.get_bool("DCCL/nvls_rooted_pipe", false);
     nvls_pipe_set_chunk_bytes((size_t)cfg.get_int("DCCL/nvls_pipe_chunk_bytes", 8ll << 20));

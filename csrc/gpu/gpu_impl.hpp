@@ -19,6 +19,21 @@ struct RegisteredBuffer {
     void* opened[kMaxPeers] = {nullptr}; // what cudaIpcOpenMemHandle returned (to close it)
 };
 
+/** Lazy registration (auto_register.cu): an allocation of this rank that the peers have been told about ... */
+struct AutoExport {
+    unsigned long long id = 0;
+    size_t size = 0;
+    cudaIpcMemHandle_t handle;
+    bool announced = false;           // the peers have seen it in an exchange
+    bool refused = false;             // cannot be exported, or a peer could not open it: not offered (again)
+};
+/** ... and a peer's allocation as mapped here. */
+struct AutoImport {
+    unsigned long long id = 0;
+    void* mapped = nullptr;
+    std::string hkey;                 // its entry in the table of opened handles
+};
+
 class GpuCommImpl : public GpuComm {
 public:
     GpuCommImpl(Bootstrap* bs, int device);
@@ -60,6 +75,7 @@ public:
     std::string topology() const override { return topology_json(topo_); }
     bool has_multicast() const override { return pool_.mc_base != nullptr; }
     uint64_t launches() const override { return launches_; }
+    uint64_t stat(const char* name) const override;
     bool set_param(const char* name, int value) override;
 
 private:
@@ -73,6 +89,10 @@ private:
     CollArgs base_args(const void* send, void* recv, ncclRedOp_t op, int root);
     /** Fill the symmetric views of a user buffer; false when it is not inside a dcclMemAlloc segment. */
     bool sym_view(const void* p, size_t bytes, const char** peers, const char** mc) const;
+    /** Lazy registration: the ranks exchange which allocations `send` and `recv` lie in and open what is new. True
+     *  (on every rank alike) when all ranks can address all buffers; fills the peers' views of both. Collective. */
+    bool auto_view(const void* send, const void* recv, const char** send_peers, const char** recv_peers);
+    void close_import(const AutoImport& im);
     int ctas_for(int tuned) const;
     /** Move the sequence number to the device counter (calls become replayable from a CUDA graph) or back to
      *  the host. Every rank must switch at the same point of its call order. Waits for the device to go idle.
@@ -111,7 +131,8 @@ private:
     int threads_ = 512;
     int sm_count_ = 148;
     size_t pipe_min_bytes_ = 16u << 20;   // ordinary-buffer switch all-reduce is pipelined from this size on (0 = never)
-    int pipe_ctas_ = 144;
+    int pipe_ctas_ = 80;                  // grid of the pipelined switch all-reduce: pipe_nv_ctas_ switch CTAs, the rest copy in / out
+    int pipe_nv_ctas_ = 16;
     int unroll_ = 8;
     bool rooted_pipe_ = false;            // broadcast / reduce of large ordinary buffers: pipelined switch form (nvls_rooted.cu)
     size_t rooted_pipe_min_bytes_ = 16u << 20;
@@ -121,6 +142,11 @@ private:
     std::vector<SymSegment> user_segs_;
     std::vector<RegisteredBuffer> regs_;
     std::map<std::string, void*> ipc_opened_;   // handle bytes -> mapping, one open per allocation
+    std::map<unsigned long long, AutoExport> auto_exports_;                  // by base address of the allocation
+    std::map<std::pair<int, unsigned long long>, AutoImport> auto_imports_;  // by (owner, base address at the owner)
+    size_t auto_min_bytes_ = 4u << 20;          // lazy registration serves calls from this size on (0: never)
+    bool direct_rs_ = false;                    // reduce-scatter on addressable buffers: zero-copy pull at every world size
+    uint64_t zero_copy_calls_ = 0;              // calls served straight out of / into user memory by peer kernels
     unsigned long long sent_chunks_[kMaxPeers], recv_chunks_[kMaxPeers];
     bool in_group_ = false;
     std::vector<P2pOp> group_ops_;

@@ -52,7 +52,9 @@ cudaError_t launch_nvls(const CollArgs& a, ncclDataType_t dt, const LaunchCfg& c
 /* nvls_pipe.cu: all-reduce / reduce-scatter of ordinary buffers with copy-in, switch pass and copy-out overlapped
  * chunk by chunk (reduce-scatter: count = per-rank elements, stride = slot distance in the send buffer) */
 size_t nvls_pipe_capacity(size_t elem_size, size_t stage_bytes, int nranks, bool reduce_scatter);
-cudaError_t launch_nvls_pipe(const CollArgs& a, ncclDataType_t dt, const LaunchCfg& cfg, bool reduce_scatter);
+/** cfg.ctas is the whole grid; nv_ctas of it form the switch group (0: a fifth / a third of the grid), the rest is
+ *  split evenly between copy-in and copy-out (all-reduce) or is the copy-in group (reduce-scatter). */
+cudaError_t launch_nvls_pipe(const CollArgs& a, ncclDataType_t dt, const LaunchCfg& cfg, bool reduce_scatter, int nv_ctas = 0);
 /** Target chunk size of the pipeline (default 8 MB, at most 24 chunks per launch); a tuning knob, the same on every rank. */
 void nvls_pipe_set_chunk_bytes(size_t bytes);
 

@@ -67,7 +67,17 @@ __device__ __forceinline__ void nvls_body(const CollArgs& a, const Ctx& x) {
             if (hi > lo) nvls_pass<T, OP>(send_mc + ((size_t)r * stride + lo) * ES, nullptr, reinterpret_cast<char*>(recv + lo), vecs(hi - lo), (hi - lo) * ES, avg, n);
         } else if (mode == NV_ALLGATHER) {
             const size_t lo = lo_of(r), hi = hi_of(r);
-            if (hi > lo) nvls_push(recv_mc + ((size_t)r * stride + lo) * ES, reinterpret_cast<const char*>(send + lo), vecs(hi - lo));
+            if (hi > lo) {
+                if (aligned16(send + lo)) nvls_push(recv_mc + ((size_t)r * stride + lo) * ES, reinterpret_cast<const char*>(send + lo), vecs(hi - lo));
+                else {
+                    // a source that is not 16-byte aligned (only this rank knows): through the own slot of the receive
+                    // buffer, which is, then from there to every rank
+                    T* own = recv + (size_t)r * stride + lo;
+                    copy_range<T>(own, send + lo, hi - lo);
+                    __syncthreads();
+                    nvls_push(recv_mc + ((size_t)r * stride + lo) * ES, reinterpret_cast<const char*>(own), vecs(hi - lo));
+                }
+            }
         } else if (mode == NV_BROADCAST) {
             if (r == a.root)
                 for (int j = 0; j < n; j++) {

@@ -15,13 +15,21 @@
  *        all-reduce only)
  *
  * so that the copies of chunks k+1 and k-1 run while the switch works on chunk
- * k. Every NV CTA g is fed by kPipeFan IN CTAs and drained by kPipeFan OUT CTAs
- * that split its sub-range (equal thirds, kPipeFan = 1, measured best on 8 x B200).
- * Hand-over: IN CTA (g,m) of every rank signals flag row g*fan+m of every rank;
- * NV_g waits for all fan x n of
- * them, then signals row B_g of every rank, which the OUT CTAs (g, *) wait on.
- * The whole message sits in one staging half, so no staging byte is reused
- * within a launch and the hand-over needs no back pressure.
+ * k. The groups have sizes of their own: the switch pass is bound by latency
+ * and saturates with about 16 CTAs, the copies are bound by HBM and want long
+ * contiguous ranges. Each copy CTA therefore moves ONE contiguous slice of a
+ * chunk (a piece of a few tens of KB per source would leave the unrolled copy
+ * loop idle and run at a fraction of HBM speed), and the hand-over is per
+ * chunk, not per range: every CTA signals its own flag row at every rank after
+ * each chunk; an NV CTA waits for the IN rows of all ranks, an OUT CTA for the
+ * NV rows of all ranks. The whole message sits in one staging half, so no
+ * staging byte is reused within a launch and the hand-over needs no back
+ * pressure: IN runs ahead as far as it likes.
+ *
+ * Leaving the call: an all-reduce rank leaves after its OUT group has seen every
+ * rank's NV flags of the last chunk, a reduce-scatter rank after its NV group has
+ * seen every rank's IN flags, so a rank that leaves knows that every rank has
+ * entered the call, which is what the alternation of staging halves needs.
  */
 #include "kernels.hpp"
 #include "../device/geometry.cuh"
@@ -30,7 +38,6 @@
 namespace dccl {
 
 constexpr int kPipeMaxChunks = 24;    // flag values per call are limited (kFlagVals)
-constexpr int kPipeFan = 1;           // copy CTAs per switch CTA, on each side (measured on 8 x B200: 1 beats 4)
 static_assert(kPipeMaxChunks < kFlagVals, "chunk numbers must fit the per-call flag values");
 
 /** wait until point idx was signalled on flag rows [row0, row0 + rows) by EVERY rank */
@@ -38,8 +45,7 @@ __device__ __forceinline__ bool wait_rows_all_ranks(const DevComm& c, int row0, 
     __shared__ int s_fail;
     if (threadIdx.x == 0) s_fail = 0;
     __syncthreads();
-    const int t = (int)threadIdx.x;
-    if (t < c.nranks * rows)
+    for (int t = (int)threadIdx.x; t < c.nranks * rows; t += (int)blockDim.x)
         if (!wait_peer(c, t % c.nranks, row0 + t / c.nranks, seq, idx, site)) s_fail = 1;
     __syncthreads();
     const bool ok = s_fail == 0;
@@ -54,12 +60,11 @@ __device__ __forceinline__ void signal_all_ranks(const DevComm& c, int row, uint
 }
 
 /** sub-range [lo,hi) of [0,len) for part m of `parts`, in whole vectors of VE elements */
-__device__ __forceinline__ void split_range(size_t lo, size_t hi, int m, int parts, size_t ve, size_t* plo, size_t* phi) {
-    const size_t len = hi - lo;
+__device__ __forceinline__ void split_range(size_t len, int m, int parts, size_t ve, size_t* plo, size_t* phi) {
     size_t per = ((len + parts - 1) / parts + ve - 1) / ve * ve;
-    size_t a = lo + per * (size_t)m, b = a + per;
-    if (a > hi) a = hi;
-    if (b > hi) b = hi;
+    size_t a = per * (size_t)m, b = a + per;
+    if (a > len) a = len;
+    if (b > len) b = len;
     *plo = a; *phi = b;
 }
 
@@ -70,13 +75,13 @@ __device__ __forceinline__ void nvls_pipe_body(const CollArgs& a, const Ctx& x) 
     const DevComm& c = *x.c;
     const int n = c.nranks, r = c.rank;
     const bool rs = a.root != 0;                   // reduce-scatter (count = per-rank elements) instead of all-reduce
-    const int nroles = rs ? 1 + kPipeFan : 1 + 2 * kPipeFan;
-    const int G = x.nb / nroles;                   // switch CTAs per rank
-    // CTA order: [IN (G*fan)] [NV (G)] [OUT (G*fan)]
-    int role, g, m = 0;
-    if (x.bid < G * kPipeFan) { role = 0; g = x.bid / kPipeFan; m = x.bid % kPipeFan; }
-    else if (x.bid < G * kPipeFan + G) { role = 1; g = x.bid - G * kPipeFan; }
-    else if (!rs && x.bid < G * (1 + 2 * kPipeFan)) { role = 2; const int o = x.bid - G * (kPipeFan + 1); g = o / kPipeFan; m = o % kPipeFan; }
+    const int Gn = a.pipe_nv, Gc = a.pipe_copy;    // switch CTAs; copy CTAs on each side
+    // CTA order: [NV (Gn)] [IN (Gc)] [OUT (Gc), all-reduce only]; a CTA's flag row is its index
+    enum { ROLE_IN, ROLE_NV, ROLE_OUT };
+    int role, g;
+    if (x.bid < Gn) { role = ROLE_NV; g = x.bid; }
+    else if (x.bid < Gn + Gc) { role = ROLE_IN; g = x.bid - Gn; }
+    else if (!rs && x.bid < Gn + 2 * Gc) { role = ROLE_OUT; g = x.bid - Gn - Gc; }
     else return;                                   // left-over CTAs
     const T* send = reinterpret_cast<const T*>(x.io->send);
     T* recv = reinterpret_cast<T*>(x.io->recv);
@@ -85,54 +90,63 @@ __device__ __forceinline__ void nvls_pipe_body(const CollArgs& a, const Ctx& x) 
     T* my_stage = reinterpret_cast<T*>(c.pool[r] + stage_off);
     char* mc_stage = c.mc_pool + stage_off;
     const int nchunks = a.mode;                    // chosen by the host, 1..kPipeMaxChunks
-    const int row_a0 = g * kPipeFan;               // rows [row_a0, row_a0 + fan): IN (g, m) -> NV g
-    const int row_b = G * kPipeFan + g;            // NV g -> OUT (g, *)
     // reduce-scatter: rank j's slot sits at j * stride in the user buffer and at j * slot in staging
     const size_t slot = (a.count + VE - 1) / VE * VE;
     size_t chunk = (a.count + nchunks - 1) / nchunks;
     chunk = rs ? (chunk + VE - 1) / VE * VE : (chunk + VE * n - 1) / (VE * n) * (VE * n);
-    // the whole message sits in one staging half; chunk numbers are flag values; rows: fan per switch CTA, then one each
+    // the whole message sits in one staging half; chunk numbers are flag values; one flag row per CTA
     if (!stage_extent_ok<T>(c, rs ? (size_t)n * slot : slot, 1908) ||
-        !DCCL_BOUNDS_OK(c, nchunks >= 1 && nchunks <= kFlagVals && G * (kPipeFan + 1) <= kMaxCtas, 1908, nchunks)) return;
+        !DCCL_BOUNDS_OK(c, nchunks >= 1 && nchunks <= kPipeMaxChunks && Gn >= 1 && Gc >= 1 && Gn + 2 * Gc <= kMaxCtas, 1908, nchunks)) return;
+    const int parts = rs ? (Gc + n - 1) / n : 1;   // reduce-scatter copy-in: every slot's chunk is cut into `parts` slices
 
     for (int k = 0; k < nchunks; k++) {
         const size_t base = (size_t)k * chunk;
         const size_t cnt = base >= a.count ? 0 : (a.count - base < chunk ? a.count - base : chunk);
-        // geometry of this chunk: all-reduce splits it into n shards; reduce-scatter has the same chunk in every slot
-        const Geometry<T> geo(rs ? GEO_WHOLE : GEO_SPLIT, cnt, rs ? 1 : n, g, G);
-        auto lo_of = [&](int j) { size_t l = rs ? cnt : geo.len(j); return geo.blo < l ? geo.blo : l; };
-        auto hi_of = [&](int j) { size_t l = rs ? cnt : geo.len(j); return geo.bhi < l ? geo.bhi : l; };
-        if (role == 0) {
-            for (int j = 0; j < n && cnt; j++) {
-                size_t lo, hi;
-                split_range(lo_of(j), hi_of(j), m, kPipeFan, VE, &lo, &hi);
-                if (hi <= lo) continue;
-                if (rs) copy_range<T>(my_stage + (size_t)j * slot + base + lo, send + (size_t)j * a.stride + base + lo, hi - lo);
-                else { const size_t off = base + (size_t)j * geo.per + lo; copy_range<T>(my_stage + off, send + off, hi - lo); }
+        if (role == ROLE_IN) {
+            size_t lo, hi;
+            if (rs) {
+                for (int u = g; u < n * parts && cnt; u += Gc) {      // unit u: slice u / n of slot u % n
+                    const int j = u % n;
+                    split_range(cnt, u / n, parts, VE, &lo, &hi);
+                    if (hi > lo) copy_range<T>(my_stage + (size_t)j * slot + base + lo, send + (size_t)j * a.stride + base + lo, hi - lo);
+                }
+            } else {
+                split_range(cnt, g, Gc, VE, &lo, &hi);
+                if (hi > lo) copy_range<T>(my_stage + base + lo, send + base + lo, hi - lo);
             }
-            signal_all_ranks(c, row_a0 + m, x.seq, k);
-        } else if (role == 1) {
-            if (!wait_rows_all_ranks(c, row_a0, kPipeFan, x.seq, k, 560)) return;
-            const size_t lo = lo_of(r), hi = hi_of(r);
+            signal_all_ranks(c, x.bid, x.seq, k);
+        } else if (role == ROLE_NV) {
+            if (!wait_rows_all_ranks(c, Gn, Gc, x.seq, k, 560)) return;
+            // this rank's shard of the chunk: the whole chunk of its slot (reduce-scatter) or the r-th n-th of it
+            const size_t per = rs ? cnt : ((cnt + n - 1) / n + VE - 1) / VE * VE;
+            const size_t s_lo = rs ? 0 : (per * (size_t)r < cnt ? per * (size_t)r : cnt);
+            const size_t s_len = rs ? cnt : (cnt - s_lo < per ? cnt - s_lo : per);
+            size_t lo, hi;
+            split_range(s_len, g, Gn, VE, &lo, &hi);
             if (hi > lo) {
                 if (rs) {
                     const size_t off = ((size_t)r * slot + base + lo) * ES;
-                    nvls_pass<T, OP>(mc_stage + off, nullptr, reinterpret_cast<char*>(recv + base + lo), ((hi - lo) * ES + 15) / 16, (hi - lo) * ES, avg, n, a.unroll);
+                    char* dst = reinterpret_cast<char*>(recv + base + lo);
+                    if (aligned16(dst)) nvls_pass<T, OP>(mc_stage + off, nullptr, dst, ((hi - lo) * ES + 15) / 16, (hi - lo) * ES, avg, n, a.unroll);
+                    else {
+                        // unaligned output: reduce into the own staging slot (read through the switch by nobody but this
+                        // rank: peers fold THEIR slot of this rank's staging), then copy
+                        char* tmp = reinterpret_cast<char*>(my_stage + (size_t)r * slot + base + lo);
+                        nvls_pass<T, OP>(mc_stage + off, nullptr, tmp, ((hi - lo) * ES + 15) / 16, ((hi - lo) * ES + 15) / 16 * 16, avg, n, a.unroll);
+                        __syncthreads();
+                        copy_range<T>(recv + base + lo, reinterpret_cast<const T*>(tmp), hi - lo);
+                    }
                 } else {
-                    const size_t off = (base + (size_t)r * geo.per + lo) * ES;
+                    const size_t off = (base + s_lo + lo) * ES;
                     nvls_pass<T, OP>(mc_stage + off, mc_stage + off, nullptr, ((hi - lo) * ES + 15) / 16, 0, avg, n, a.unroll);
                 }
             }
-            if (!rs) signal_all_ranks(c, row_b, x.seq, k);
+            if (!rs) signal_all_ranks(c, x.bid, x.seq, k);
         } else {
-            if (!wait_rows_all_ranks(c, row_b, 1, x.seq, k, 570)) return;
-            for (int j = 0; j < n && cnt; j++) {
-                size_t lo, hi;
-                split_range(lo_of(j), hi_of(j), m, kPipeFan, VE, &lo, &hi);
-                if (hi <= lo) continue;
-                const size_t off = base + (size_t)j * geo.per + lo;
-                copy_range<T>(recv + off, my_stage + off, hi - lo);
-            }
+            if (!wait_rows_all_ranks(c, 0, Gn, x.seq, k, 570)) return;
+            size_t lo, hi;
+            split_range(cnt, g, Gc, VE, &lo, &hi);
+            if (hi > lo) copy_range<T>(recv + base + lo, my_stage + base + lo, hi - lo);
         }
     }
 }
@@ -152,7 +166,7 @@ size_t nvls_pipe_capacity(size_t es, size_t stage_bytes, int nranks, bool reduce
 
 static size_t g_pipe_chunk_bytes = 8u << 20;   // target chunk size; every rank must use the same value
 
-void nvls_pipe_set_chunk_bytes(size_t bytes) { if (bytes >= (256u << 10)) g_pipe_chunk_bytes = bytes; }
+void nvls_pipe_set_chunk_bytes(size_t bytes) { if (bytes >= 4096) g_pipe_chunk_bytes = bytes; }
 
 int nvls_pipe_chunks(size_t bytes) {
     size_t k = (bytes + g_pipe_chunk_bytes - 1) / g_pipe_chunk_bytes;
@@ -161,12 +175,23 @@ int nvls_pipe_chunks(size_t bytes) {
     return (int)k;
 }
 
-cudaError_t launch_nvls_pipe(const CollArgs& a_in, ncclDataType_t dt, const LaunchCfg& cfg_in, bool reduce_scatter) {
+void nvls_pipe_split(int ctas, int nv, bool reduce_scatter, int* nv_out, int* copy_out) {
+    const int sides = reduce_scatter ? 1 : 2;
+    if (ctas < 1 + sides) ctas = 1 + sides;
+    if (nv <= 0) nv = ctas / (1 + 2 * sides);       // by default the copy groups are twice the switch group
+    if (nv < 1) nv = 1;
+    if (nv > ctas - sides) nv = ctas - sides;
+    int copy = (ctas - nv) / sides;
+    if (nv + sides * copy > kMaxCtas) copy = (kMaxCtas - nv) / sides;
+    *nv_out = nv;
+    *copy_out = copy;
+}
+
+cudaError_t launch_nvls_pipe(const CollArgs& a_in, ncclDataType_t dt, const LaunchCfg& cfg_in, bool reduce_scatter, int nv_ctas) {
     CollArgs a = a_in;
     LaunchCfg cfg = cfg_in;
-    const int nroles = reduce_scatter ? 1 + kPipeFan : 1 + 2 * kPipeFan;
-    cfg.ctas = cfg.ctas / nroles * nroles;          // whole groups
-    if (cfg.ctas < nroles) cfg.ctas = nroles;
+    nvls_pipe_split(cfg.ctas, nv_ctas, reduce_scatter, &a.pipe_nv, &a.pipe_copy);
+    cfg.ctas = a.pipe_nv + (reduce_scatter ? 1 : 2) * a.pipe_copy;
     const size_t es = dt == ncclFloat64 || dt == ncclInt64 || dt == ncclUint64 ? 8 : dt == ncclFloat16 || dt == ncclBfloat16 ? 2 : 4;
     a.mode = nvls_pipe_chunks(a.count * es * (reduce_scatter ? (size_t)a.comm.nranks : 1));
     a.root = reduce_scatter ? 1 : 0;

@@ -65,6 +65,8 @@ def _declare(lib):
         "dccl_scatter": (i, [vp, vp, sz, i, i, vp, vp]),
         "dccl_group_start": (i, []),
         "dccl_group_end": (i, []),
+        "dccl_comm_stat": (c.c_ulonglong, [vp, cp]),
+        "dccl_selftest_board": (i, [vp, i]),
         "dccl_set_algorithm": (i, [vp, cp, cp]),
         "dccl_last_algorithm": (cp, [vp, cp]),
         "dccl_timestamp_log": (None, [c.c_ulonglong, c.c_ulonglong, c.c_ulonglong]),
@@ -104,6 +106,7 @@ def _declare(lib):
         "dccl_emu_set_guard": (None, [i]),
         "dccl_emu_set_mix": (i, [cp]),
         "dccl_emu_set_switch_form": (None, [i]),
+        "dccl_emu_set_pipe": (None, [sz, i]),
         "dccl_emu_declare_stage_bytes": (i, [sz]),
     }
     for name, (res, args) in sigs.items():

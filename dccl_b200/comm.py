@@ -194,8 +194,14 @@ class Communicator:
         (the message names the gap and the offset). No-op otherwise."""
         _check(lib().dccl_debug_check(self._h), "dcclDebugCheck")
 
+    def stat(self, name):
+        """A counter of the device side: "launches", "zero_copy_calls" (calls that the peer kernels served straight out
+        of / into user memory: symmetric, registered or lazily registered buffers)."""
+        return int(lib().dccl_comm_stat(self._h, name.encode()))
+
     def set_param(self, name, value):
-        """Tuning knob for sweeps: ctas (0 = table), threads, unroll, p2p_ctas."""
+        """Tuning knob for sweeps: ctas (0 = table), threads, unroll, p2p_ctas, pipe_ctas, pipe_nv_ctas, pipe_chunk_kb,
+        auto_register_min_kb (0: no lazy registration), direct_rs."""
         _check(lib().dccl_comm_set_param(self._h, name.encode(), int(value)), "set_param")
 
     def set_algorithm(self, collective, name):

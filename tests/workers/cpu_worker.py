@@ -161,6 +161,8 @@ def main():
     from dccl_b200._lib import lib as _native
     check(_native().dccl_selftest_fd_exchange(comm._h) == 0, "descriptor exchange between all ranks")
     check(_native().dccl_debug_check(comm._h) == 0, "pool check without a device side is a success")
+    # the exchange board in the shared control segment (per-call agreement for lazy registration): 2000 skewed rounds
+    check(_native().dccl_selftest_board(comm._h, 2000) == 0, "small all-gathers over the shared-memory board")
     # barrier: nobody passes before the last rank has arrived (the last rank arrives 0.3 s late)
     import time
     t0 = time.monotonic()

@@ -20,7 +20,7 @@ def main():
     L = _lib.lib()
     assert hasattr(L, "dccl_emu_set_switch_form"), "not the simulation build"
     cases = 0
-    for form, kinds in ((0, ["allreduce", "reducescatter", "allgather", "broadcast", "reduce"]), (1, ["allreduce"]), (2, ["broadcast", "reduce"])):
+    for form, kinds in ((0, ["allreduce", "reducescatter", "allgather", "broadcast", "reduce"]), (1, ["allreduce", "reducescatter"]), (2, ["broadcast", "reduce"])):
         L.dccl_emu_set_switch_form(form)
         for n in ((2, 3, 8) if "--all" in sys.argv[1:] else (3, 8)):
             for kind in kinds:
@@ -49,6 +49,27 @@ def main():
                                 ok = all(np.array_equal(out[r], ins[root]) for r in range(n))
                             assert ok, (form, n, kind, name, op, count, in_place, misalign)
                             cases += 1
+    # the pipelined forms with many chunks (4 KB each: up to 24 per call), other group sizes, in place and unaligned
+    L.dccl_emu_set_switch_form(1)
+    try:
+        for chunk, nv, ctas in ((4096, 2, 7), (16384, 1, 12), (4096, 3, 5)):
+            L.dccl_emu_set_pipe(chunk, nv)
+            for n in (2, 5, 8):
+                for kind in ("allreduce", "reducescatter"):
+                    for name, op in (("float32", "sum"), ("bfloat16", "avg"), ("int64", "min")):
+                        for count in (7, 4099, 50001):
+                            for in_place, misalign in ((0, 0), (1, 0), (0, 8 if name == "int64" else 4 if name == "float32" else 2)):
+                                ins = inputs_for(name, op, count * n if kind == "reducescatter" else count, n, seed=79)
+                                out = emu(L, kind, "nvls", n, name, op, count, ins, ctas=ctas, in_place=in_place, misalign=misalign, iters=3, stage=4 << 20)
+                                want = oracle.fold(ins, op, bf16=name == "bfloat16")
+                                if kind == "allreduce":
+                                    ok = all(close(out[r], want, name, n) for r in range(n))
+                                else:
+                                    ok = all(close(out[r], want[r * count:(r + 1) * count], name, n) for r in range(n))
+                                assert ok, ("pipe", chunk, nv, ctas, n, kind, name, op, count, in_place, misalign)
+                                cases += 1
+    finally:
+        L.dccl_emu_set_pipe(8 << 20, 0)
     # zero-copy forms: the user buffers themselves are multicast-mapped (what dcclMemAlloc memory is)
     L.dccl_emu_set_switch_form(0)
     L.dccl_emu_set_peer_buffers(1)
