@@ -513,6 +513,17 @@ ncclResult_t dcclSetAlgorithm(ncclComm_t comm, const char* collective, const cha
     return ncclSuccess;
 }
 
+ncclResult_t dcclSetParam(ncclComm_t comm, const char* name, int value) {
+    VALIDATE_COMM(comm);
+    if (!comm->gpu) return ncclInvalidUsage;
+    return comm->gpu->set_param(name, value) ? ncclSuccess : ncclInvalidArgument;
+}
+
+unsigned long long dcclGetStat(ncclComm_t comm, const char* name) {
+    VALIDATE_COMM(comm);
+    return comm->gpu ? comm->gpu->stat(name) : 0ull;
+}
+
 const char* dcclGetLastAlgorithm(ncclComm_t comm, const char* collective) {
     VALIDATE_COMM(comm);
     int coll = collective ? parse_collective_name(collective) : -1;

@@ -67,7 +67,7 @@ constexpr int kUnroll = 8;   // 16-byte vectors in flight per thread in the copy
  * destination are misaligned by the same amount the head is peeled and the body moves
  * 16 bytes per access; otherwise 4-byte words or single bytes are used.
  */
-__device__ __forceinline__ void copy_bytes(char* __restrict__ dst, const char* __restrict__ src, size_t bytes) {
+__device__ __forceinline__ void copy_bytes(char* dst, const char* src, size_t bytes) {
     const int tid = threadIdx.x, nt = blockDim.x;
     const uintptr_t d = reinterpret_cast<uintptr_t>(dst), s = reinterpret_cast<uintptr_t>(src);
     if (((d ^ s) & 15u) == 0) {
@@ -99,17 +99,18 @@ __device__ __forceinline__ void copy_bytes(char* __restrict__ dst, const char* _
 }
 
 template <typename T>
-__device__ __forceinline__ void copy_range(T* __restrict__ dst, const T* __restrict__ src, size_t n) {
+__device__ __forceinline__ void copy_range(T* dst, const T* src, size_t n) {
     copy_bytes(reinterpret_cast<char*>(dst), reinterpret_cast<const char*>(src), n * sizeof(T));
 }
 
 /**
  * out[i] = finish(op(own[i], in_0[i], ..., in_{k-1}[i])) for i in [0,n), with up to two
- * destinations. `ins` are k additional sources (staging slots or peer buffers).
+ * destinations. `ins` are k additional sources (staging slots or peer buffers). The pointers carry no
+ * __restrict__: an in-place call passes the same buffer as `own` and as a destination, and every thread reads the
+ * vector it is about to overwrite before it writes it. Buffers that overlap only partly are not supported.
  */
 template <typename T, int OP>
-__device__ __forceinline__ void reduce_range(T* __restrict__ out0, T* __restrict__ out1, const T* __restrict__ own,
-                                             const T* const* ins, int k, size_t n, bool avg, int world) {
+__device__ __forceinline__ void reduce_range(T* out0, T* out1, const T* own, const T* const* ins, int k, size_t n, bool avg, int world) {
     using A = typename Traits<T>::Acc;
     constexpr int N = Vec16<T>::N;
     const int tid = threadIdx.x, nt = blockDim.x;

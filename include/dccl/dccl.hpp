@@ -267,6 +267,19 @@ ncclResult_t  dcclDebugCheck(ncclComm_t comm);
 /** Name of the variant the last call of `collective` used (for tools and tests). */
 const char*   dcclGetLastAlgorithm(ncclComm_t comm, const char* collective);
 
+/**
+ * Tuning knob of the communicator's device side, for sweeps and tools: "ctas" (0: the table's value), "threads",
+ * "unroll", "p2p_ctas", "pipe_ctas", "pipe_nv_ctas", "pipe_chunk_kb", "pipe_min_mb", "rooted_pipe",
+ * "auto_register_min_kb" (0: no lazy registration), "direct_rs", "device_seq". Every rank sets the same value at the
+ * same point of its call order. ncclInvalidArgument for an unknown name or a value out of range, ncclInvalidUsage
+ * before a device was bound.
+ */
+ncclResult_t  dcclSetParam(ncclComm_t comm, const char* name, int value);
+
+/** A counter of the device side: "launches" (kernels launched), "zero_copy_calls" (calls that peer kernels served
+ *  straight out of / into user memory: symmetric, registered or lazily registered buffers). 0 for unknown names. */
+unsigned long long dcclGetStat(ncclComm_t comm, const char* name);
+
 const char*   dcclGetErrorString(ncclResult_t r);
 
 /* ------------------------------------------------------------------ *

@@ -33,6 +33,13 @@ def test_pipelined_switch_variant_on_small_and_odd_sizes():
 
 
 @pytest.mark.skipif(gpu_count() < 2, reason="needs two GPUs")
+def test_unregistered_buffers_are_mapped_on_first_use_and_alignment_is_a_group_decision():
+    """Large calls on ordinary tensors run zero-copy after an exchange of cudaIpc handles inside the call; freed and
+    re-allocated buffers are mapped afresh; one rank with an unaligned pointer changes the path for all ranks alike."""
+    run(min(gpu_count(), 8), ["--suite", "lazy"])
+
+
+@pytest.mark.skipif(gpu_count() < 2, reason="needs two GPUs")
 def test_messages_larger_than_staging_are_chunked():
     world = min(gpu_count(), 8)
     run(world, ["--suite", "chunk"], env={"DCCL_STAGING_BYTES": str(4 << 20)})

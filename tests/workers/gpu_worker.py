@@ -92,6 +92,97 @@ def main():
         print("OK %d multicast=1 launches=%d" % (cases, launches))
         return
 
+    if args.suite == "lazy":
+        # ordinary tensors that nobody registered: a large call on them exchanges the allocations between the ranks,
+        # maps what is new and then runs zero-copy; a freed and re-allocated buffer is mapped afresh; a pointer that is
+        # not 16-byte aligned on ONE rank sends every rank down the staged path
+        comm.set_algorithm("allreduce", "twoshot")
+        comm.set_algorithm("reducescatter", "twoshot")
+        comm.set_param("direct_rs", 1)
+        for rnd in range(3):
+            for name, count in [("bfloat16", (4 << 20) + 64 * world), ("float32", (2 << 20) + 32 * world)]:
+                ins = [oracle.make_input(name, count, seed=7000 + 10 * rnd + r) for r in range(world)]
+                bf = name == "bfloat16"
+                for op in ["sum", "avg"]:
+                    want = oracle.fold(ins, op, bf16=bf)
+                    s = to_torch(ins[rank], name, dev)
+                    out = torch.zeros_like(s)
+                    z0 = comm.stat("zero_copy_calls")
+                    for _ in range(2):
+                        comm.all_reduce(s, out, op=op)
+                    torch.cuda.synchronize()
+                    check(comm.stat("zero_copy_calls") - z0 == 2, "lazy registration: all_reduce %s ran zero-copy (%d)" % (name, comm.stat("zero_copy_calls") - z0))
+                    check(close(to_numpy(out, name), want, name, world), "lazy all_reduce %s %s round %d" % (name, op, rnd))
+                    comm.all_reduce(s, op=op)      # in place
+                    torch.cuda.synchronize()
+                    check(close(to_numpy(s, name), want, name, world), "lazy all_reduce in place %s %s" % (name, op))
+                    # reduce-scatter: the peers read this rank's send buffer
+                    per = count // world
+                    s = to_torch(ins[rank], name, dev)
+                    rs = torch.zeros(per, dtype=s.dtype, device=dev)
+                    z0 = comm.stat("zero_copy_calls")
+                    comm.reduce_scatter(s[:per * world], rs, op=op)
+                    torch.cuda.synchronize()
+                    check(comm.stat("zero_copy_calls") - z0 == 1, "lazy registration: reduce_scatter %s ran zero-copy" % name)
+                    check(close(to_numpy(rs, name), want[rank * per:(rank + 1) * per], name, world), "lazy reduce_scatter %s %s" % (name, op))
+                    # one rank off a 16-byte boundary: staged on every rank, same values
+                    es = s.element_size()
+                    shift = (4 // es) if rank == world - 1 else 0
+                    base_s = torch.zeros(count + 16, dtype=s.dtype, device=dev)
+                    base_o = torch.zeros(count + 16, dtype=s.dtype, device=dev)
+                    v, o = base_s[shift:shift + count], base_o[shift:shift + count]
+                    v.copy_(to_torch(ins[rank], name, dev))
+                    z0 = comm.stat("zero_copy_calls")
+                    comm.all_reduce(v, o, op=op)
+                    torch.cuda.synchronize()
+                    check(comm.stat("zero_copy_calls") == z0, "one unaligned rank: nobody runs zero-copy")
+                    check(close(to_numpy(o.contiguous(), name), want, name, world), "all_reduce with one unaligned rank %s %s" % (name, op))
+                    del s, out, rs, base_s, base_o, v, o
+            # give the memory back to the driver: the next round's tensors are new allocations, often at old addresses
+            torch.cuda.synchronize()
+            comm.barrier()
+            torch.cuda.empty_cache()
+        comm.set_param("direct_rs", 0)
+        comm.set_algorithm("allreduce", "auto")
+        comm.set_algorithm("reducescatter", "auto")
+        # variant choices that only one rank's alignment could have changed: a reduce-scatter into an unaligned receive
+        # buffer (pipelined switch form from 256 KB on) and an all-gather from an unaligned source into symmetric memory
+        if comm.has_multicast:
+            comm.set_param("pipe_min_mb", 1)
+            name, per = "float32", (1 << 20) + 8
+            ins = [oracle.make_input(name, per * world, seed=7500 + r) for r in range(world)]
+            want = oracle.fold(ins, "sum")
+            shift = 1 if rank == world - 1 else 0
+            comm.set_algorithm("reducescatter", "nvls")
+            s = to_torch(ins[rank], name, dev)
+            base_o = torch.zeros(per + 8, dtype=torch.float32, device=dev)
+            o = base_o[shift:shift + per]
+            for _ in range(2):
+                comm.reduce_scatter(s, o, op="sum")
+            torch.cuda.synchronize()
+            check(close(to_numpy(o.contiguous(), name), want[rank * per:(rank + 1) * per], name, world), "switch reduce_scatter, one receive buffer unaligned")
+            comm.set_algorithm("reducescatter", "auto")
+            comm.set_algorithm("allgather", "nvls")
+            g = comm.symmetric_empty(per * world, torch.float32, local)
+            base_s = torch.zeros(per + 8, dtype=torch.float32, device=dev)
+            v = base_s[shift:shift + per]
+            v.copy_(to_torch(ins[rank][:per], name, dev))
+            comm.all_gather(v, g)
+            torch.cuda.synchronize()
+            check(np.array_equal(to_numpy(g, name), np.concatenate([x[:per] for x in ins])), "switch all_gather into symmetric memory, one source unaligned")
+            comm.set_algorithm("allgather", "auto")
+            comm.free_symmetric(g)
+        code, emsg = comm.last_error()
+        check(code == 0, "async error: " + emsg)
+        launches = comm.launches
+        mc = comm.has_multicast
+        comm.finalize()
+        if failures:
+            print("FAILED %d of %d on rank %d: %s" % (len(failures), cases, rank, "; ".join(failures[:10])))
+            sys.exit(1)
+        print("OK %d multicast=%d launches=%d" % (cases, int(mc), launches))
+        return
+
     if args.suite == "extra":
         # what the communicator found out about the box
         topo = comm.topology()

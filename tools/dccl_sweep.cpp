@@ -16,6 +16,10 @@
  *   --colls all_reduce,reduce_scatter,all_gather  --impls dccl,nccl
  *   --algo NAME (force a variant of this library)  --symmetric (dcclMemAlloc buffers)
  *   --register (ordinary cudaMalloc buffers registered with dcclRegisterCacheMemory)
+ *   --param NAME=VALUE (a tuning knob of this library's device side, repeatable: pipe_ctas=96, direct_rs=1, ...)
+ *   --nccl-register (the NCCL arm runs on ncclMemAlloc memory registered with ncclCommRegister: NCCL's own
+ *                    zero-copy path, the like-for-like partner of --symmetric)
+ *   --colls also takes broadcast and reduce (root 0; S = the message)
  *   --out FILE (rank 0 writes the rows as JSON)
  */
 #include <dccl/dccl.hpp>
@@ -37,6 +41,12 @@ typedef int (*CommDestroy_t)(comm_t);
 typedef int (*AllReduce_t)(const void*, void*, size_t, int, int, comm_t, cudaStream_t);
 typedef int (*ReduceScatter_t)(const void*, void*, size_t, int, int, comm_t, cudaStream_t);
 typedef int (*AllGather_t)(const void*, void*, size_t, int, comm_t, cudaStream_t);
+typedef int (*Broadcast_t)(const void*, void*, size_t, int, int, comm_t, cudaStream_t);
+typedef int (*Reduce_t)(const void*, void*, size_t, int, int, int, comm_t, cudaStream_t);
+typedef int (*MemAlloc_t)(void**, size_t);
+typedef int (*MemFree_t)(void*);
+typedef int (*CommRegister_t)(comm_t, void*, size_t, void**);
+typedef int (*CommDeregister_t)(comm_t, void*);
 }
 
 static std::vector<std::string> split(const std::string& s) {
@@ -61,16 +71,18 @@ int main(int argc, char** argv) {
         {"gpu", required_argument, 0, 'g'}, {"min", required_argument, 0, 'm'}, {"max", required_argument, 0, 'M'},
         {"factor", required_argument, 0, 'f'}, {"type", required_argument, 0, 't'}, {"colls", required_argument, 0, 'c'},
         {"impls", required_argument, 0, 'i'}, {"algo", required_argument, 0, 'A'}, {"symmetric", no_argument, 0, 's'},
-        {"out", required_argument, 0, 'o'}, {"op", required_argument, 0, 'O'}, {"register", no_argument, 0, 'R'}, {0, 0, 0, 0}};
+        {"out", required_argument, 0, 'o'}, {"op", required_argument, 0, 'O'}, {"register", no_argument, 0, 'R'},
+        {"param", required_argument, 0, 'p'}, {"nccl-register", no_argument, 0, 'N'}, {0, 0, 0, 0}};
     int gpu = -2;
     size_t minb = 1024, maxb = 1ull << 30, factor = 2;
     dccl::ncclDataType_t dt = dccl::ncclBfloat16;
     dccl::ncclRedOp_t op = dccl::ncclSum;
     std::string colls = "all_reduce,reduce_scatter,all_gather", impls = "dccl,nccl", algo, out;
-    bool symmetric = false, registered = false;
+    bool symmetric = false, registered = false, nccl_registered = false;
+    std::vector<std::pair<std::string, int>> params;
     while (true) {
         int idx = 0;
-        int c = getopt_long(argc, argv, "g:m:M:f:t:c:i:A:so:O:R", long_options, &idx);
+        int c = getopt_long(argc, argv, "g:m:M:f:t:c:i:A:so:O:Rp:N", long_options, &idx);
         if (c == -1) break;
         switch (c) {
         case 'g': gpu = !strcmp(optarg, "auto") ? -2 : atoi(optarg); break;
@@ -83,6 +95,13 @@ int main(int argc, char** argv) {
         case 'A': algo = optarg; break;
         case 's': symmetric = true; break;
         case 'R': registered = true; break;
+        case 'N': nccl_registered = true; break;
+        case 'p': {
+            const char* eq = strchr(optarg, '=');
+            if (!eq) { std::cerr << "--param wants NAME=VALUE" << std::endl; return 1; }
+            params.emplace_back(std::string(optarg, eq - optarg), atoi(eq + 1));
+            break;
+        }
         case 'o': out = optarg; break;
         case 'O': op = parse_op_name(optarg); break;
         default: break;
@@ -122,8 +141,10 @@ int main(int argc, char** argv) {
                                dccl::dcclRegisterCacheMemory(comm, r_ours, maxb) != dccl::ncclSuccess)) return 2;
         }
         cudaMemset(s_ours, 0, maxb);
+        for (const auto& kv : params)
+            if (dccl::dcclSetParam(comm, kv.first.c_str(), kv.second) != dccl::ncclSuccess) { std::cerr << "unknown parameter " << kv.first << std::endl; return 1; }
         if (!algo.empty())
-            for (const char* c : {"allreduce", "reducescatter", "allgather"})
+            for (const char* c : {"allreduce", "reducescatter", "allgather", "broadcast", "reduce"})
                 if (dccl::dcclSetAlgorithm(comm, c, algo.c_str()) != dccl::ncclSuccess) { std::cerr << "unknown algorithm" << std::endl; return 1; }
     }
     stock::comm_t ncomm = nullptr;
@@ -131,6 +152,11 @@ int main(int argc, char** argv) {
     stock::ReduceScatter_t nReduceScatter = nullptr;
     stock::AllGather_t nAllGather = nullptr;
     stock::CommDestroy_t nDestroy = nullptr;
+    stock::Broadcast_t nBroadcast = nullptr;
+    stock::Reduce_t nReduce = nullptr;
+    stock::MemFree_t nMemFree = nullptr;
+    stock::CommDeregister_t nDeregister = nullptr;
+    void *reg_s = nullptr, *reg_r = nullptr;
     if (want_nccl) {
         const char* libname = getenv("DCCL_NCCL_LIB");
         void* h = dlopen(libname && *libname ? libname : "libnccl.so.2", RTLD_NOW | RTLD_LOCAL);
@@ -141,13 +167,23 @@ int main(int argc, char** argv) {
         nAllReduce = (stock::AllReduce_t)dlsym(h, "ncclAllReduce");
         nReduceScatter = (stock::ReduceScatter_t)dlsym(h, "ncclReduceScatter");
         nAllGather = (stock::AllGather_t)dlsym(h, "ncclAllGather");
-        if (!getid || !init || !nDestroy || !nAllReduce || !nReduceScatter || !nAllGather) return 5;
+        nBroadcast = (stock::Broadcast_t)dlsym(h, "ncclBroadcast");
+        nReduce = (stock::Reduce_t)dlsym(h, "ncclReduce");
+        auto nMemAlloc = (stock::MemAlloc_t)dlsym(h, "ncclMemAlloc");
+        auto nRegister = (stock::CommRegister_t)dlsym(h, "ncclCommRegister");
+        nMemFree = (stock::MemFree_t)dlsym(h, "ncclMemFree");
+        nDeregister = (stock::CommDeregister_t)dlsym(h, "ncclCommDeregister");
+        if (!getid || !init || !nDestroy || !nAllReduce || !nReduceScatter || !nAllGather || !nBroadcast || !nReduce) return 5;
+        if (nccl_registered && (!nMemAlloc || !nRegister || !nMemFree || !nDeregister)) { std::cerr << "this libnccl has no ncclMemAlloc / ncclCommRegister" << std::endl; return 5; }
         stock::uid_t id;
         memset(&id, 0, sizeof(id));
         if (rank == 0 && getid(&id) != 0) return 1;
         if (dccl::ncclBroadcast(&id, &id, sizeof(id), dccl::ncclUint8, 0, comm, nullptr) != dccl::ncclSuccess) return 1;
         if (init(&ncomm, world, id, rank) != 0) { std::cerr << "ncclCommInitRank failed" << std::endl; return 1; }
-        if (cudaMalloc((void**)&s_nccl, maxb) != cudaSuccess || cudaMalloc((void**)&r_nccl, maxb) != cudaSuccess) return 4;
+        if (nccl_registered) {
+            if (nMemAlloc((void**)&s_nccl, maxb) != 0 || nMemAlloc((void**)&r_nccl, maxb) != 0) { std::cerr << "ncclMemAlloc failed" << std::endl; return 4; }
+            if (nRegister(ncomm, s_nccl, maxb, &reg_s) != 0 || nRegister(ncomm, r_nccl, maxb, &reg_r) != 0) { std::cerr << "ncclCommRegister failed" << std::endl; return 4; }
+        } else if (cudaMalloc((void**)&s_nccl, maxb) != cudaSuccess || cudaMalloc((void**)&r_nccl, maxb) != cudaSuccess) return 4;
         cudaMemset(s_nccl, 0, maxb);
     }
 
@@ -177,10 +213,13 @@ int main(int argc, char** argv) {
                     if (coll == "all_reduce") return ours ? (int)dccl::ncclAllReduce(sb, rb, elems, dt, op, comm, stream) : nAllReduce(sb, rb, elems, dt, op, ncomm, stream);
                     if (coll == "reduce_scatter") return ours ? (int)dccl::ncclReduceScatter(sb, rb, per, dt, op, comm, stream) : nReduceScatter(sb, rb, per, dt, op, ncomm, stream);
                     if (coll == "all_gather") return ours ? (int)dccl::ncclAllGather(sb, rb, per, dt, comm, stream) : nAllGather(sb, rb, per, dt, ncomm, stream);
+                    if (coll == "broadcast") return ours ? (int)dccl::ncclBroadcast(sb, rb, elems, dt, 0, comm, stream) : nBroadcast(sb, rb, elems, dt, 0, ncomm, stream);
+                    if (coll == "reduce") return ours ? (int)dccl::ncclReduce(sb, rb, elems, dt, op, 0, comm, stream) : nReduce(sb, rb, elems, dt, op, 0, ncomm, stream);
                     return 99;
                 };
                 const int iters = total <= (1u << 20) ? 200 : total <= (64u << 20) ? 40 : 10;
                 int rc = 0;
+                const unsigned long long zc0 = ours ? dccl::dcclGetStat(comm, "zero_copy_calls") : 0ull;
                 for (int i = 0; i < 5 && !rc; i++) rc = call();
                 cudaStreamSynchronize(stream);
                 host_barrier();
@@ -193,13 +232,17 @@ int main(int argc, char** argv) {
                 cudaEventElapsedTime(&ms, e0, e1);
                 const double us = host_max((double)ms * 1e3 / iters);
                 const double n = world, alg = (double)total / (us * 1e-6) / 1e9;
-                const double f = world == 1 ? 1.0 : coll == "all_reduce" ? 2 * (n - 1) / n : (n - 1) / n;
-                const char* variant = ours ? dccl::dcclGetLastAlgorithm(comm, coll == "all_reduce" ? "allreduce" : coll == "reduce_scatter" ? "reducescatter" : "allgather") : "nccl";
+                const double f = world == 1 || coll == "broadcast" || coll == "reduce" ? 1.0 : coll == "all_reduce" ? 2 * (n - 1) / n : (n - 1) / n;
+                const char* variant = ours ? dccl::dcclGetLastAlgorithm(comm, coll == "all_reduce" ? "allreduce" : coll == "reduce_scatter" ? "reducescatter"
+                                                                              : coll == "all_gather" ? "allgather" : coll.c_str())
+                                           : nccl_registered ? "nccl-registered" : "nccl";
+                std::string vname(variant);
+                if (ours && dccl::dcclGetStat(comm, "zero_copy_calls") > zc0) vname += "+zerocopy";   // served out of / into user memory
                 if (rank == 0) {
-                    printf("%-15s %-5s %12zu %10.2f %10.2f %10.2f  %s\n", coll.c_str(), impl.c_str(), total, us, alg, alg * f, variant);
+                    printf("%-15s %-5s %12zu %10.2f %10.2f %10.2f  %s\n", coll.c_str(), impl.c_str(), total, us, alg, alg * f, vname.c_str());
                     fflush(stdout);
                     json << (first ? "" : ",") << "\n {\"coll\": \"" << coll << "\", \"impl\": \"" << impl << "\", \"bytes\": " << total << ", \"us\": " << us
-                         << ", \"algbw_gbs\": " << alg << ", \"busbw_gbs\": " << alg * f << ", \"variant\": \"" << variant << "\"}";
+                         << ", \"algbw_gbs\": " << alg << ", \"busbw_gbs\": " << alg * f << ", \"variant\": \"" << vname << "\"}";
                     first = false;
                 }
             }
@@ -214,6 +257,9 @@ int main(int argc, char** argv) {
     char msg[200];
     dccl::dcclGetLastError(comm, &async, msg, sizeof(msg));
     if (async != dccl::ncclSuccess) std::cerr << "communicator error: " << msg << std::endl;
+    if (reg_s) nDeregister(ncomm, reg_s);
+    if (reg_r) nDeregister(ncomm, reg_r);
+    if (ncomm && nccl_registered) { nMemFree(s_nccl); nMemFree(r_nccl); }
     if (ncomm) nDestroy(ncomm);
     if (symmetric) { dccl::dcclMemFree(comm, s_ours); dccl::dcclMemFree(comm, r_ours); }
     dccl::ncclCommFinalize(comm);
