@@ -16,8 +16,9 @@ namespace dccl {
 
 template <typename T> struct HostSum  { static inline T f(T a, T b) { return (T)(a + b); } };
 template <typename T> struct HostProd { static inline T f(T a, T b) { return (T)(a * b); } };
-template <typename T> struct HostMax  { static inline T f(T a, T b) { return a < b ? b : a; } };
-template <typename T> struct HostMin  { static inline T f(T a, T b) { return b < a ? b : a; } };
+// max / min of floats: the other operand when one is NaN (a != a), like fmax / fmin and the device kernels
+template <typename T> struct HostMax  { static inline T f(T a, T b) { return (a < b || a != a) ? b : a; } };
+template <typename T> struct HostMin  { static inline T f(T a, T b) { return (b < a || a != a) ? b : a; } };
 
 template <typename T, template <typename> class OP>
 static inline void host_reduce_loop(T* __restrict__ acc, const T* __restrict__ in, size_t n) {
@@ -40,8 +41,8 @@ static inline ncclResult_t host_reduce_16(uint16_t* acc, const uint16_t* in, siz
     switch (op) {
     case ncclSum: case ncclAvg: for (size_t i = 0; i < n; i++) acc[i] = FROM(TO(acc[i]) + TO(in[i])); return ncclSuccess;
     case ncclProd: for (size_t i = 0; i < n; i++) acc[i] = FROM(TO(acc[i]) * TO(in[i])); return ncclSuccess;
-    case ncclMax: for (size_t i = 0; i < n; i++) { float a = TO(acc[i]), b = TO(in[i]); acc[i] = FROM(a < b ? b : a); } return ncclSuccess;
-    case ncclMin: for (size_t i = 0; i < n; i++) { float a = TO(acc[i]), b = TO(in[i]); acc[i] = FROM(b < a ? b : a); } return ncclSuccess;
+    case ncclMax: for (size_t i = 0; i < n; i++) { float a = TO(acc[i]), b = TO(in[i]); acc[i] = FROM((a < b || a != a) ? b : a); } return ncclSuccess;
+    case ncclMin: for (size_t i = 0; i < n; i++) { float a = TO(acc[i]), b = TO(in[i]); acc[i] = FROM((b < a || a != a) ? b : a); } return ncclSuccess;
     default: return ncclInvalidArgument;
     }
 }

@@ -31,11 +31,21 @@ template <> struct Traits<__nv_bfloat16> {
     static __device__ __forceinline__ __nv_bfloat16 down(float a) { return __float2bfloat16_rn(a); }
 };
 
+/**
+ * One step of the fold. Floating-point max / min follow IEEE maxNum / minNum, like fmaxf / fminf, NCCL's float kernels
+ * and the switch's multimem.ld_reduce.max/min: when one operand is NaN the other is returned, so the result does not
+ * depend on the order in which the ranks' values meet and is NaN only when every rank's value is.
+ */
 template <int OP, typename A> __device__ __forceinline__ A op_apply(A a, A b) {
     if constexpr (OP == OP_SUM) return a + b;
     else if constexpr (OP == OP_PROD) return a * b;
-    else if constexpr (OP == OP_MAX) return a < b ? b : a;
-    else return b < a ? b : a;
+    else if constexpr (OP == OP_MAX) {
+        if constexpr (std::is_floating_point<A>::value) return (a < b || a != a) ? b : a;
+        else return a < b ? b : a;
+    } else {
+        if constexpr (std::is_floating_point<A>::value) return (b < a || a != a) ? b : a;
+        else return b < a ? b : a;
+    }
 }
 
 /** Final step of ncclAvg on an accumulated sum: floats scale by 1/n, integers divide. */

@@ -588,4 +588,9 @@ int dccl_local_reduce(void* host_acc, const void* host_in, size_t count, int dty
     return e == cudaSuccess ? 0 : fail("local reduce");
 }
 
+/** The same kernel on buffers that already live on the device, on `stream` (no synchronisation): for timing. */
+int dccl_local_reduce_device(void* dev_acc, const void* dev_in, size_t count, int dtype, int op, void* stream) {
+    return launch_local_reduce(dev_acc, dev_in, count, (ncclDataType_t)dtype, (ncclRedOp_t)op, (cudaStream_t)stream) == cudaSuccess ? 0 : fail("local reduce");
+}
+
 } // extern "C"

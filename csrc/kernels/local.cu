@@ -28,15 +28,49 @@ __global__ void __launch_bounds__(512) k_local_copy(char* __restrict__ dst, cons
     copy_bytes(dst + lo, src + lo, n);
 }
 
+/**
+ * acc[i] = op(acc[i], in[i]). Three streams of HBM traffic and nothing else, so what matters is bytes in flight:
+ * every thread keeps kLocalU 16-byte vectors of each operand outstanding (128 KB per SM with two resident CTAs),
+ * each CTA on one contiguous piece.
+ */
+constexpr int kLocalU = 4;
 template <typename T, int OP>
-__global__ void __launch_bounds__(512) k_local_reduce(T* __restrict__ acc, const T* __restrict__ in, size_t count, int avg) {
+__global__ void __launch_bounds__(512) k_local_reduce(T* acc, const T* __restrict__ in, size_t count, int avg) {
+    using A = typename Traits<T>::Acc;
     constexpr size_t VE = 16 / sizeof(T);
+    constexpr int N = Vec16<T>::N;
     const size_t per = ((count + gridDim.x - 1) / gridDim.x + VE - 1) / VE * VE;
     const size_t lo = per * blockIdx.x;
     if (lo >= count) return;
     const size_t n = count - lo < per ? count - lo : per;
-    const T* ins[1] = {in + lo};
-    reduce_range<T, OP>(acc + lo, nullptr, acc + lo, ins, 1, n, avg != 0, 2);
+    T* a = acc + lo;
+    const T* b = in + lo;
+    size_t done = 0;
+    if (aligned16(a) && aligned16(b)) {
+        const size_t nv = n / N, tid = threadIdx.x, nt = blockDim.x;
+        size_t i = tid;
+        for (; i + (size_t)(kLocalU - 1) * nt < nv; i += (size_t)kLocalU * nt) {
+            Vec16<T> x[kLocalU], y[kLocalU];
+#pragma unroll
+            for (int u = 0; u < kLocalU; u++) { x[u] = ld_vec<T>(a + (i + (size_t)u * nt) * N); y[u] = ld_vec<T>(b + (i + (size_t)u * nt) * N); }
+#pragma unroll
+            for (int u = 0; u < kLocalU; u++) {
+#pragma unroll
+                for (int e = 0; e < N; e++) x[u].e[e] = Traits<T>::down(op_apply<OP, A>(Traits<T>::up(x[u].e[e]), Traits<T>::up(y[u].e[e])));
+                st_vec<T>(a + (i + (size_t)u * nt) * N, x[u]);
+            }
+        }
+        for (; i < nv; i += nt) {
+            Vec16<T> x = ld_vec<T>(a + i * N), y = ld_vec<T>(b + i * N);
+#pragma unroll
+            for (int e = 0; e < N; e++) x.e[e] = Traits<T>::down(op_apply<OP, A>(Traits<T>::up(x.e[e]), Traits<T>::up(y.e[e])));
+            st_vec<T>(a + i * N, x);
+        }
+        done = nv * N;
+    }
+    // ragged end, or operands that are not 16-byte aligned
+    const T* ins[1] = {b + done};
+    if (n > done) reduce_range<T, OP>(a + done, nullptr, a + done, ins, 1, n - done, avg != 0, 2);
 }
 
 cudaError_t launch_local_copy(void* dst, const void* src, size_t bytes, cudaStream_t stream) {
@@ -54,7 +88,7 @@ cudaError_t launch_local_reduce(void* acc, const void* in, size_t count, ncclDat
     const size_t es = dt == ncclInt8 || dt == ncclUint8 ? 1 : dt == ncclFloat16 || dt == ncclBfloat16 ? 2
                       : dt == ncclInt32 || dt == ncclUint32 || dt == ncclFloat32 ? 4 : 8;
     size_t want = (count * es + (64u << 10) - 1) / (64u << 10);
-    int grid = (int)(want < (size_t)(2 * sm_count()) ? want : (size_t)(2 * sm_count()));
+    int grid = (int)(want < (size_t)(2 * sm_count()) ? want : (size_t)(2 * sm_count()));   // two resident CTAs per SM: one wave
     if (grid < 1) grid = 1;
     const int avg = 0;   // a pairwise fold has no world size: ncclAvg accumulates like ncclSum here
 #define CALL(T, OP) k_local_reduce<T, OP><<<grid, 512, 0, stream>>>((T*)acc, (const T*)in, count, avg)

@@ -101,6 +101,7 @@ def _declare(lib):
         "dccl_emu_set_peer_buffers": (None, [i]),
         "dccl_emu_switch_single": (i, [i, i, sz, i, i, vp, vp]),
         "dccl_local_reduce": (i, [vp, vp, sz, i, i]),
+        "dccl_local_reduce_device": (i, [vp, vp, sz, i, i, vp]),
         "dccl_debug_bounds_build": (i, []),
         "dccl_selftest_canary": (i, []),
         "dccl_emu_set_guard": (None, [i]),

@@ -56,10 +56,10 @@ def fold(inputs, op, bf16=False):
             acc = acc + v
         elif op == "prod":
             acc = acc * v
-        elif op == "max":
-            acc = np.maximum(acc, v)
+        elif op == "max":      # IEEE maxNum / minNum: a NaN loses against a number (the library's rule, and NCCL's)
+            acc = np.fmax(acc, v)
         elif op == "min":
-            acc = np.minimum(acc, v)
+            acc = np.fmin(acc, v)
     if op == "avg":
         acc = acc / n
     if bf16:

@@ -103,7 +103,7 @@ def test_cli_defaults_match_the_original(build_dir, tmp_path):
     assert (tmp_path / "dccl_cli.tt").exists()
     # no --api: help text, exit status -1
     p = spawn_ranks([cli], 1, cwd=str(tmp_path))[0]
-    assert p.returncode == 255 and "--api,-a" in p.stdout
+    assert p.returncode == 255 and "--api NAME" in p.stdout
     # operators are parsed by name (max is max, not prod)
     p = spawn_ranks([cli, "-a", "all_reduce", "-o", "max", "-r", "1"], 1, cwd=str(tmp_path))[0]
     assert "\top:2" in p.stdout

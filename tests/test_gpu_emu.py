@@ -86,6 +86,29 @@ def test_allreduce_every_dtype_and_operator(dccl_lib, algo):
                 assert close(out[r], want, name, n), (algo, name, op, r)
 
 
+@pytest.mark.parametrize("algo", ["oneshot", "twoshot", "ring", "rabenseifner", "twoshot_ll"])
+def test_min_max_ignore_a_nan_when_a_number_is_there(dccl_lib, algo):
+    """max / min of floats follow IEEE maxNum / minNum (fmax / fmin, as NCCL's kernels do): whichever rank holds the NaN
+    and in whatever order the values meet, the number wins; only an element that is NaN on every rank stays NaN."""
+    n, count = 4, 2053
+    for name in ["float32", "bfloat16", "float16", "float64"]:
+        ins = inputs_for(name, "max", count, n, seed=19)
+        nan = np.uint16(0x7FC0) if name == "bfloat16" else np.nan
+        for r in range(n):
+            ins[r][r::7] = nan                  # a different pattern per rank ...
+        for r in range(n):
+            ins[r][5::101] = nan                # ... and some elements that are NaN everywhere
+        for op in ["max", "min"]:
+            want = oracle.fold(ins, op, bf16=name == "bfloat16")
+            wf = oracle.bf16_to_f32(want) if name == "bfloat16" else want
+            assert np.isnan(wf[5::101]).all() and not np.isnan(np.delete(wf, np.arange(5, count, 101))).any()
+            out = emu(dccl_lib, "allreduce", algo, n, name, op, count, ins)
+            for r in range(n):
+                got = oracle.bf16_to_f32(out[r]) if name == "bfloat16" else out[r]
+                assert np.array_equal(np.isnan(got), np.isnan(wf)), (algo, name, op, r)
+                assert np.array_equal(got[~np.isnan(wf)], wf[~np.isnan(wf)]), (algo, name, op, r)
+
+
 @pytest.mark.parametrize("algo", ["oneshot", "twoshot", "ring", "rabenseifner"])
 def test_allreduce_in_place_and_unaligned(dccl_lib, algo):
     n = 4

@@ -7,7 +7,8 @@ dccl_allreduce_one_device_noalloc, an all-reduce among buffers on one device who
 fixed array inside the library image. This test calls it through its exported C symbol, the way
 such a caller would, twice in a row on the same stream, and compares every rank's output with
 what the allocating entry point (dccl_emu_collective, two-shot variant) returns for the same
-inputs. The buffers the TEST needs are made with torch; the entry point under test gets only
+inputs, and with a fold of the inputs computed on the CPU in fp64 / int64 (the two kernels share
+their reduction code, so agreement between them alone would not show a fault in it). The buffers the TEST needs are made with torch; the entry point under test gets only
 their addresses. The file sorts last so that a run that stops at the first failure has already
 run everything else; it also passes when run alone in a fresh process.
 """
@@ -70,9 +71,11 @@ def _run(lib, torch, n, name, op, count, seed, in_place=False):
     assert rc == 0, "entry point returned %d" % rc
     torch.cuda.synchronize()
     assert int(status.item()) == 0, "a wait inside the kernel gave up"
+    serial = oracle.fold(ins, op, bf16=name == "bfloat16")      # independent of any kernel of the library
     for r in range(n):
         got = d_out[r].cpu().numpy().view(np_dt)
         assert _close(got, want[r], name, n), (n, name, op, count, r)
+        assert _close(got, serial, name, n), ("against the serial fold", n, name, op, count, r)
 
 
 def test_two_calls_in_a_row_match_the_allocating_entry_point(dccl_lib):

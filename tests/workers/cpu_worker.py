@@ -88,6 +88,24 @@ def main():
     else:
         dtypes, ops, counts = ["float32", "bfloat16", "int32"], ["sum", "avg"], [7, 100000, 300001]
 
+    if args.suite == "basic":
+        # max / min of floats: a NaN loses against a number wherever it sits (IEEE maxNum / minNum); NaN on every rank stays
+        for name in ["float32", "float64", "bfloat16", "float16"]:
+            count = 1031
+            ins = [oracle.make_input(name, count, seed=77 + r) for r in range(world)]
+            nan = np.uint16(0x7FC0) if name == "bfloat16" else np.nan
+            for r in range(world):
+                ins[r][r::5] = nan
+                ins[r][3::97] = nan
+            for op in ["max", "min"]:
+                want = oracle.fold(ins, op, bf16=name == "bfloat16")
+                out = np.zeros_like(ins[rank])
+                rc = raw.all_reduce(ins[rank].copy(), out, name, op)
+                gf = oracle.bf16_to_f32(out) if name == "bfloat16" else out.astype(np.float64)
+                wf = oracle.bf16_to_f32(want) if name == "bfloat16" else want.astype(np.float64)
+                check(rc == 0 and np.array_equal(np.isnan(gf), np.isnan(wf)) and np.array_equal(gf[~np.isnan(wf)], wf[~np.isnan(wf)]),
+                      "all_reduce %s %s with NaN inputs" % (name, op))
+
     for name in dtypes:
         for count in counts:
             ins = [oracle.make_input(name, count, seed=1000 * r + count % 97) for r in range(world)]

@@ -26,31 +26,28 @@ using namespace dccl;
 using namespace dccl_tools;
 
 static const char* help_string =
-    "\t--api,-a     name of the DCCL api to be tested. This option is mandatory. Full api list:\n"
-    "\t             broadcast,send,recv,reduce,all_reduce,reduce_scatter,all_gather\n"
-    "\t             (and, beyond the original: all_to_all,gather,scatter)\n"
-    "\t             Please note that\n"
-    "\t             - 'send' and 'recv' only work between rank 0 and 1. \n"
-    "\t             - only the root (rank 0 unless --root) will 'broadcast', all other node will receive. \n"
-    "\t             - 'reduce' will reduce to the root (rank 0 unless --root).\n"
+    "  -a, --api NAME      (required) the call to run: all_reduce, reduce_scatter, all_gather, broadcast, reduce,\n"
+    "                      send, recv; added here: all_to_all, gather, scatter.\n"
+    "                      send / recv run between ranks 0 and 1 only; broadcast sends from, and reduce collects at,\n"
+    "                      the root rank (--root, 0 by default).\n"
 #ifdef DCCL_WITH_CUDA
-    "\t--gpu,-g     gpu device to use (or 'auto': the launcher's local device / the rank). If not specified, CPU is used.\n"
+    "  -g, --gpu DEV       run on device memory of GPU DEV ('auto': the launcher's local device, else the rank);\n"
+    "                      without this option the buffers are host memory.\n"
 #endif
-    "\t--warmup,-w  number of operations for warmup, defaulted to 0.\n"
-    "\t--repeat,-r  number of operations for evaluation, defaulted to 1000.\n"
-    "\t--type,-t    type of the data, defaulted to uint32. Full type list:\n"
-    "\t             int8,uint8,int32,uint32,int64,uint64,float16,float32,float64,bfloat16\n"
-    "\t--op,-o      the operation, defaulted to SUM. Full op list:\n"
-    "\t             sum,prod,max,min,avg\n"
-    "\t--count,-c   number of data entries in the array, defaulted to 1024\n"
-    "\t--save,-s    save data in before.dat and after.dat for validation.\n"
-    "\t--verify,-v  run out of place and check the result against a serial fold; exit 3 on mismatch.\n"
-    "\t--init,-i    buffer contents: bytes (memset to the rank, default), uniform, normal.\n"
-    "\t--seed,-S    seed base for uniform/normal; rank r uses seed+r. Defaulted to 0.\n"
-    "\t--algo,-A    force an algorithm: auto,ring,rabenseifner,oneshot,twoshot,twoshot_ll,nvls.\n"
-    "\t--root,-R    root rank for broadcast and reduce, defaulted to 0.\n"
-    "\t--tt-per-rank write dccl_cli.<rank>.tt instead of dccl_cli.tt (ranks sharing a directory).\n"
-    "\t--help,-h    print this message.\n";
+    "  -w, --warmup N      untimed calls before the measurement (default 0)\n"
+    "  -r, --repeat N      timed calls (default 1000)\n"
+    "  -t, --type T        element type (default uint32): int8 uint8 int32 uint32 int64 uint64 float16 float32\n"
+    "                      float64 bfloat16\n"
+    "  -o, --op OP         reduction (default sum): sum prod max min avg\n"
+    "  -c, --count N       elements per buffer (default 1024)\n"
+    "  -s, --save          dump the buffers before and after the run as hex text files next to the .tt file\n"
+    "  -v, --verify        run out of place and compare with a serial fold; exit code 3 when they differ\n"
+    "  -i, --init KIND     buffer contents: bytes (every byte = rank, the default), uniform, normal\n"
+    "  -S, --seed N        seed of uniform / normal data; rank r draws from seed N + r (default 0)\n"
+    "  -A, --algo NAME     force a variant: auto ring rabenseifner oneshot twoshot twoshot_ll nvls\n"
+    "  -R, --root RANK     root of broadcast / reduce (default 0)\n"
+    "      --tt-per-rank   name the timestamp file dccl_cli.<rank>.tt (for ranks that share a directory)\n"
+    "  -h, --help          show this text\n";
 
 static void print_help(const char* cmd) {
     std::cout << "Usage: " << cmd << " [options]" << std::endl;
@@ -134,7 +131,7 @@ int main(int argc, char** argv) {
     std::cout << "\top:" << operation << std::endl;
     std::cout << "\tcount:" << data_count << std::endl;
 
-    // step 1 - initialize comm
+    // join the group
     ncclComm_t comm;
     ncclResult_t ret = ncclCommInit(&comm);
     if (ret != ncclSuccess) { std::cerr << "failed to initialize the dccl communicator." << std::endl; return 1; }
@@ -156,7 +153,7 @@ int main(int argc, char** argv) {
         return 1;
     }
 
-    // step 2 - buffers
+    // allocate and fill the buffers
     const size_t data_size = size_of_type(data_type), bytes = data_count * data_size;
     void *raw_send = nullptr, *raw_recv = nullptr, *sendbuf = nullptr, *recvbuf = nullptr;
     cudaStream_t stream = nullptr;
@@ -239,7 +236,7 @@ int main(int argc, char** argv) {
         } \
     }
 
-    // step 3 - warmup
+    // untimed calls
     std::cout << "warm up..." << std::endl;
     TIMESTAMP(TT_WARMUP_START, my_rank, 0);
     RUN_WITH_COUNTER(warmup_count);
@@ -247,7 +244,7 @@ int main(int argc, char** argv) {
     TIMESTAMP(TT_WARMUP_END, my_rank, 0);
     std::cout << "done." << std::endl;
 
-    // step 4 - run test
+    // the measurement
     std::cout << "run test..." << std::endl;
     call_min_us = 1e300; call_max_us = 0.0;   // forget the warm-up calls
     auto t0 = std::chrono::steady_clock::now();
@@ -327,12 +324,12 @@ int main(int argc, char** argv) {
     }
 #endif
 
-    // step 5 - flush timestamp
+    // write the timestamp log
     std::cout << "flush timestamp..." << std::endl;
     FLUSH_AND_CLEAR_TIMESTAMP(tt_per_rank ? "dccl_cli." + std::to_string(my_rank) + ".tt" : std::string("dccl_cli.tt"));
     std::cout << "...done" << std::endl;
 
-    // step 6 - finalize comm
+    // leave the group
     ret = ncclCommFinalize(comm);
     if (ret != ncclSuccess) std::cerr << "failed to finalize the dccl communicator." << std::endl;
     return verify_failed ? 3 : 0;

@@ -34,16 +34,16 @@ using namespace dccl;
 #define TT_OOB_ACKD             TT_OOB(1002)
 
 static const char* help_string =
-    "\t--transport,-t       name of the p2p transport driver. This option is mandatory.\n"
-    "\t                     Transport choices: p2p (alias oob)\n"
+    "  -t, --transport NAME  (required) how the messages travel: p2p (the library's send / recv; 'oob' is accepted\n"
+    "                        as another spelling)\n"
 #ifdef DCCL_WITH_CUDA
-    "\t--cuda,-c            using gpu memory on specified cuda device.\n"
+    "  -c, --cuda DEV        keep the message pool in device memory of GPU DEV (default: host memory)\n"
 #endif
-    "\t--size,-s            message size in bytes, default to 1024 bytes.\n"
-    "\t--depth,-d           window deption, default to 16.\n"
-    "\t--warmup,-w          duration of the warming up in seconds, default to one second.\n"
-    "\t--duration,-D        duration for each of the evaluation in seconds, default to five seconds.\n"
-    "\t--help,-h            print this message.\n";
+    "  -s, --size BYTES      bytes per message (default 1024)\n"
+    "  -d, --depth N         messages in flight before the sender waits for the oldest (default 16)\n"
+    "  -w, --warmup SEC      seconds of untimed traffic first (default 1)\n"
+    "  -D, --duration SEC    seconds of measured traffic (default 5)\n"
+    "  -h, --help            show this text\n";
 
 static void print_help(const char* cmd) {
     std::cout << "Usage: " << cmd << " [options]" << std::endl;
