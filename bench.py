@@ -214,6 +214,16 @@ class StockNccl:
         self.dist.barrier()
 
     def close(self):
+        # tensors of the registered pool are gone by now; the pool must go before the communicator it is registered with
+        if self._pool is not None:
+            try:
+                self.torch.cuda.synchronize()
+                self.dist.group.WORLD._get_backend(self.dev).deregister_mem_pool(self._pool)
+            except Exception:       # noqa: BLE001
+                pass
+            self._pool = None
+            import gc
+            gc.collect()
         self.dist.destroy_process_group()
 
 
@@ -486,7 +496,7 @@ def run_sweep(backend, args, rank, world, dtype, es):
             for size in sizes:
                 if algo == "oneshot" and size > (128 << 10):
                     continue
-                if algo == "twoshot_ll" and size > world * (256 << 10):
+                if algo == "twoshot_ll" and size > world * (512 << 10):
                     continue
                 if algo in ("ring", "rabenseifner") and size > (256 << 20):
                     continue

@@ -202,6 +202,16 @@ int dccl_tuner_choose(const char* coll, int nranks, size_t bytes, int nvls_ok, c
     return 0;
 }
 
+/** As dccl_tuner_choose, for elements of `esize` bytes (rules bound to an element width come first). */
+int dccl_tuner_choose_width(const char* coll, int nranks, size_t bytes, int nvls_ok, int esize, char* algo_out, size_t len, int* ctas) {
+    int c = coll && !strcmp(coll, "allreduce_sym") ? TUNE_ALLREDUCE_SYM : coll && !strcmp(coll, "reducescatter_sym") ? TUNE_REDUCESCATTER_SYM : parse_collective_name(coll);
+    if (c < 0) return -1;
+    TuneChoice ch = test_tuner().choose(c, nranks, bytes, nvls_ok != 0, esize);
+    if (algo_out && len) snprintf(algo_out, len, "%s", algo_name(ch.algo));
+    if (ctas) *ctas = ch.ctas;
+    return 0;
+}
+
 /* index arithmetic, exported so unit tests can check it without a communicator */
 void dccl_slot_range(size_t count, unsigned n, unsigned i, size_t align, size_t* lo, size_t* hi) { slot_range(count, n, i, align, lo, hi); }
 unsigned dccl_reverse_bits(unsigned x, unsigned bits) { return reverse_bits(x, bits); }

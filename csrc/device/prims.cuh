@@ -37,8 +37,8 @@ constexpr size_t kP2pChunk = 1u << 20;
 constexpr int kP2pDepth = 4;
 constexpr size_t kP2pBytesPerSrc = kP2pChunk * kP2pDepth;
 constexpr size_t kLL2Off = 40u << 20;                   // packets of the two-shot packet all-reduce
-constexpr size_t kLL2PhaseBytes = 512u << 10;           // per generation, source rank and phase (half of it is payload)
-constexpr size_t kStageOff = 64u << 20;                 // two staging halves follow
+constexpr size_t kLL2PhaseBytes = 1u << 20;             // per generation, source rank and phase (half of it is payload)
+constexpr size_t kStageOff = 80u << 20;                 // two staging halves follow
 static_assert(kLLOff + kLLBytes <= kP2pOff, "LL region overlaps the p2p FIFOs");
 static_assert(kP2pFlagOff + 2 * kMaxPeers * 4 * kP2pCtas * 8 <= kLLOff, "p2p flag words overlap the packet region");
 static_assert(kP2pOff + kMaxPeers * kP2pBytesPerSrc <= kLL2Off, "p2p FIFOs overlap the second packet region");

@@ -101,7 +101,7 @@ ncclResult_t GpuCommImpl::all_reduce(const void* send, void* recv, size_t count,
     // all ranks must come to the same answer: look at every rank's alignment, not only the local one
     for (int p = 0; peer_addr && p < n_; p++) peer_addr = (uintptr_t)sp[p] % 16 == 0 && (uintptr_t)rp[p] % 16 == 0;
     const bool sym = peer_addr && nvls_ok && bytes % 16 == 0 && smc && rmc && ((uintptr_t)smc % 16 == 0) && ((uintptr_t)rmc % 16 == 0);
-    TuneChoice ch = tuner_.choose(sym ? TUNE_ALLREDUCE_SYM : COLL_ALLREDUCE, n_, bytes, nvls_ok);
+    TuneChoice ch = tuner_.choose(sym ? TUNE_ALLREDUCE_SYM : COLL_ALLREDUCE, n_, bytes, nvls_ok, (int)es);
     if (algo != ALGO_AUTO) ch.algo = algo;
     // a forced variant that cannot serve this call falls back to the closest one that can
     if (ch.algo == ALGO_NVLS && !nvls_ok) ch.algo = ALGO_TWOSHOT;
@@ -214,7 +214,7 @@ ncclResult_t GpuCommImpl::reduce_scatter(const void* send, void* recv, size_t re
     const char* sym_peers[kMaxPeers];
     const char* sym_mc = nullptr;
     const bool sym = nvls_ok && (recvcount * es) % 16 == 0 && sym_view(send, bytes, sym_peers, &sym_mc) && sym_mc && (uintptr_t)sym_mc % 16 == 0;
-    TuneChoice ch = tuner_.choose(sym ? TUNE_REDUCESCATTER_SYM : COLL_REDUCESCATTER, n_, bytes, nvls_ok);
+    TuneChoice ch = tuner_.choose(sym ? TUNE_REDUCESCATTER_SYM : COLL_REDUCESCATTER, n_, bytes, nvls_ok, (int)es);
     if (algo != ALGO_AUTO) ch.algo = algo;
     if (ch.algo == ALGO_NVLS && !nvls_ok) ch.algo = ALGO_TWOSHOT;
     if (ch.algo == ALGO_ONESHOT && recvcount * es > oneshot_ll_capacity_bytes()) ch.algo = ALGO_TWOSHOT;
@@ -315,7 +315,7 @@ ncclResult_t GpuCommImpl::all_gather(const void* send, void* recv, size_t sendco
     CallScope scope(this, stream, COLL_ALLGATHER, "dccl:allgather");
     const size_t bytes = sendcount * es * (size_t)n_;
     const bool nvls_ok = pool_.mc_base != nullptr;
-    TuneChoice ch = tuner_.choose(COLL_ALLGATHER, n_, bytes, nvls_ok);
+    TuneChoice ch = tuner_.choose(COLL_ALLGATHER, n_, bytes, nvls_ok, (int)es);
     if (algo != ALGO_AUTO) ch.algo = algo;
     if (ch.algo == ALGO_NVLS && !nvls_ok) ch.algo = ALGO_TWOSHOT;
     if (ch.algo == ALGO_ONESHOT && sendcount * es > oneshot_ll_capacity_bytes()) ch.algo = ALGO_TWOSHOT;
@@ -384,7 +384,7 @@ ncclResult_t GpuCommImpl::broadcast(const void* send, void* recv, size_t count, 
     if (!count) return ncclSuccess;
     CallScope scope(this, stream, COLL_BROADCAST, "dccl:broadcast");
     const bool nvls_ok = pool_.mc_base != nullptr;
-    TuneChoice ch = tuner_.choose(COLL_BROADCAST, n_, bytes, nvls_ok);
+    TuneChoice ch = tuner_.choose(COLL_BROADCAST, n_, bytes, nvls_ok, (int)es);
     if (algo != ALGO_AUTO) ch.algo = algo;
     if (ch.algo == ALGO_NVLS && !nvls_ok) ch.algo = ALGO_TWOSHOT;
     if (ch.algo != ALGO_NVLS && ch.algo != ALGO_ONESHOT) ch.algo = ALGO_TWOSHOT;
@@ -455,7 +455,7 @@ ncclResult_t GpuCommImpl::reduce(const void* send, void* recv, size_t count, ncc
     if (!count) return ncclSuccess;
     CallScope scope(this, stream, COLL_REDUCE, "dccl:reduce");
     const bool nvls_ok = pool_.mc_base != nullptr && nvls_supports(dt, op);
-    TuneChoice ch = tuner_.choose(COLL_REDUCE, n_, bytes, nvls_ok);
+    TuneChoice ch = tuner_.choose(COLL_REDUCE, n_, bytes, nvls_ok, (int)es);
     if (algo != ALGO_AUTO) ch.algo = algo;
     if (ch.algo == ALGO_NVLS && !nvls_ok) ch.algo = ALGO_TWOSHOT;
     if (ch.algo == ALGO_ONESHOT && bytes > oneshot_ll_capacity_bytes()) ch.algo = ALGO_TWOSHOT;

@@ -20,11 +20,14 @@ static const TuneRule kBuiltin[] = {
     {COLL_ALLREDUCE, 0, 8u << 20, ALGO_NVLS, 64},
     {COLL_ALLREDUCE, 0, kInf, ALGO_NVLS, 128},
     // two ranks (measured on 2 x B200): the switch fetches the local copy over NVLink as well, so the peer-to-peer
-    // two-shot variant wins for large messages, with or without symmetric buffers
-    // (zero-copy on buffers the peers can address: 682 GB/s at 1 GB against 410 through the switch)
-    {COLL_ALLREDUCE, 2, 128u << 10, ALGO_ONESHOT, 8},
+    // variants win for large messages, zero-copy on buffers the peers can address (symmetric, registered, or mapped
+    // lazily inside the call): 670 GB/s at 1 GB against 410 through the switch and 567 for NCCL. Between 64 KB and
+    // 1 MB the two-shot packet form (no barrier) takes 8.5 us where the barrier forms take 19-21 and NCCL 10.7-13.
+    {COLL_ALLREDUCE, 2, 64u << 10, ALGO_ONESHOT, 8},
+    {COLL_ALLREDUCE, 2, 1u << 20, ALGO_TWOSHOT_LL, 32},
     {COLL_ALLREDUCE, 2, kInf, ALGO_TWOSHOT, 128},
-    {TUNE_ALLREDUCE_SYM, 2, 128u << 10, ALGO_ONESHOT, 8},
+    {TUNE_ALLREDUCE_SYM, 2, 64u << 10, ALGO_ONESHOT, 8},
+    {TUNE_ALLREDUCE_SYM, 2, 1u << 20, ALGO_TWOSHOT_LL, 32},
     {TUNE_ALLREDUCE_SYM, 2, kInf, ALGO_TWOSHOT, 128},
     {TUNE_REDUCESCATTER_SYM, 2, 256u << 10, ALGO_ONESHOT, 8},
     {TUNE_REDUCESCATTER_SYM, 2, kInf, ALGO_TWOSHOT, 128},
@@ -61,11 +64,12 @@ Tuner::Tuner() {
 
 void Tuner::add(const TuneRule& r) {
     for (auto& x : rules_)
-        if (x.coll == r.coll && x.nranks == r.nranks && x.max_bytes == r.max_bytes) { x = r; return; }
+        if (x.coll == r.coll && x.nranks == r.nranks && x.max_bytes == r.max_bytes && x.esize == r.esize) { x = r; return; }
     rules_.push_back(r);
     std::stable_sort(rules_.begin(), rules_.end(), [](const TuneRule& a, const TuneRule& b) {
         if (a.coll != b.coll) return a.coll < b.coll;
         if (a.nranks != b.nranks) return a.nranks > b.nranks;   // exact world sizes before the wildcard
+        if (a.esize != b.esize) return a.esize > b.esize;       // exact element widths before the wildcard
         return a.max_bytes < b.max_bytes;
     });
 }
@@ -98,11 +102,14 @@ int Tuner::load_text(const std::string& text, std::string* err) {
         if (!(ls >> coll)) continue;
         if (!(ls >> nr >> mb >> algo >> ctas)) { if (err) *err += "line " + std::to_string(lineno) + ": expected 5 fields; "; continue; }
         TuneRule r;
+        std::string width;
+        r.esize = (ls >> width) && width != "*" ? atoi(width.c_str()) : 0;
         r.coll = coll == "allreduce_sym" ? TUNE_ALLREDUCE_SYM : coll == "reducescatter_sym" ? TUNE_REDUCESCATTER_SYM : parse_collective_name(coll.c_str());
         r.nranks = nr == "*" ? 0 : atoi(nr.c_str());
         r.algo = parse_algo_name(algo.c_str());
         r.ctas = ctas;
-        if (r.coll < 0 || r.algo == ALGO_COUNT || !parse_bytes(mb, &r.max_bytes) || ctas < 1 || ctas > 256) {
+        if (r.coll < 0 || r.algo == ALGO_COUNT || !parse_bytes(mb, &r.max_bytes) || ctas < 1 || ctas > 256 ||
+            (r.esize != 0 && r.esize != 1 && r.esize != 2 && r.esize != 4 && r.esize != 8)) {
             if (err) *err += "line " + std::to_string(lineno) + ": bad value; ";
             continue;
         }
@@ -128,12 +135,15 @@ bool Tuner::load_file(const std::string& path, std::string* err) {
     return n > 0;
 }
 
-TuneChoice Tuner::choose(int coll, int nranks, size_t bytes, bool nvls_ok) const {
+TuneChoice Tuner::choose(int coll, int nranks, size_t bytes, bool nvls_ok, int esize) const {
     TuneChoice fallback = {ALGO_TWOSHOT, 32};
-    for (int pass = 0; pass < 2; pass++) {
+    // (exact world size, exact width), (exact world size, any width), (any world size, exact width), (any, any)
+    for (int pass = 0; pass < 4; pass++) {
+        if ((pass == 0 || pass == 2) && esize == 0) continue;
         for (const auto& r : rules_) {
             if (r.coll != coll) continue;
-            if (pass == 0 ? r.nranks != nranks : r.nranks != 0) continue;
+            if (pass < 2 ? r.nranks != nranks : r.nranks != 0) continue;
+            if ((pass == 0 || pass == 2) ? r.esize != esize : r.esize != 0) continue;
             if (bytes > r.max_bytes) continue;
             if (r.algo == ALGO_NVLS && !nvls_ok) { fallback.ctas = r.ctas; continue; }
             return TuneChoice{r.algo, r.ctas};

@@ -3,12 +3,17 @@
  *
  * The original picks between ring and Rabenseifner from one configuration key
  * (reference src/core/dccl.cpp:412-413,454). Here the choice is made per
- * (collective, world size, message bytes) from a table of measured bus
- * bandwidths: the built-in table below was filled from sweeps on 8xB200, and a
- * file named by DCCL_TUNE_FILE (or DCCL/tune_file) replaces rows of it. File
- * format, one rule per line, '#' comments:
+ * (collective, world size, element width, message bytes) from a table of
+ * measured bus bandwidths: the built-in table was filled from sweeps on 2, 4
+ * and 8 B200s, and a file named by DCCL_TUNE_FILE (or DCCL/tune_file) replaces
+ * rows of it. File format, one rule per line, '#' comments:
  *
- *     <collective> <nranks|*> <max_bytes> <algorithm> <ctas>
+ *     <collective> <nranks|*> <max_bytes> <algorithm> <ctas> [<element bytes|*>]
+ *
+ * The optional last field binds a rule to one element width (1, 2, 4 or 8
+ * bytes); rules without it serve every width. A rule for the exact world size
+ * beats a wildcard one, and among those a rule for the exact width beats one
+ * for every width.
  *
  * <collective> is allreduce, reducescatter, allgather, broadcast, reduce, or
  * allreduce_sym (all-reduce whose buffers live in symmetric memory, where the
@@ -39,6 +44,7 @@ struct TuneRule {
     size_t max_bytes;    // inclusive upper bound
     GpuAlgo algo;
     int ctas;
+    int esize = 0;       // element bytes this rule is for; 0 = any
 };
 
 struct TuneChoice {
@@ -53,7 +59,7 @@ public:
     int load_text(const std::string& text, std::string* err);
     bool load_file(const std::string& path, std::string* err);
     /** nvls_ok: the variant can serve this (dtype, op, buffers) on this communicator. */
-    TuneChoice choose(int coll, int nranks, size_t bytes, bool nvls_ok) const;
+    TuneChoice choose(int coll, int nranks, size_t bytes, bool nvls_ok, int esize = 0) const;
     const std::vector<TuneRule>& rules() const { return rules_; }
 
 private:

@@ -88,6 +88,7 @@ def _declare(lib):
         "dccl_bf16_to_float": (c.c_float, [c.c_ushort]),
         "dccl_float_to_bf16": (c.c_ushort, [c.c_float]),
         "dccl_tuner_choose": (i, [cp, i, sz, i, cp, sz, c.POINTER(i)]),
+        "dccl_tuner_choose_width": (i, [cp, i, sz, i, i, cp, sz, c.POINTER(i)]),
         "dccl_tuner_load_text": (i, [cp]),
     }
     cuda_only = {

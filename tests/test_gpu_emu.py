@@ -298,9 +298,9 @@ def test_ring_kernel_adds_in_ring_order(dccl_lib, n):
 
 @pytest.mark.parametrize("n", [2, 3, 8])
 def test_two_shot_packet_all_reduce(dccl_lib, n):
-    """Shards to their owners and folded shards to everybody, both as polled packets (no barrier); up to 256 KB per shard."""
+    """Shards to their owners and folded shards to everybody, both as polled packets (no barrier); up to 512 KB per shard."""
     for name in ["float32", "bfloat16", "int8", "float64"]:
-        cap = (n * (256 << 10)) // np.dtype(np_dtype(name)).itemsize       # 256 KB per shard
+        cap = (n * (512 << 10)) // np.dtype(np_dtype(name)).itemsize       # 512 KB per shard
         for count in [c for c in [1, 9, 4099, 65536 + 5, cap] if c <= cap]:
             for op in ["sum", "avg", "max"]:
                 ins = inputs_for(name, op, count, n, seed=53)
@@ -341,7 +341,7 @@ def test_guard_words_between_the_pool_regions_stay_intact(dccl_lib):
     ll_cap = (128 << 10) // 4
     cases = [("allreduce", "oneshot", ll_cap), ("reducescatter", "oneshot", ll_cap), ("allgather", "oneshot", ll_cap),
              ("broadcast", "oneshot", ll_cap), ("reduce", "oneshot", ll_cap),
-             ("allreduce", "twoshot_ll", n * (256 << 10) // 4), ("reduce", "twoshot_ll", n * (256 << 10) // 4)]
+             ("allreduce", "twoshot_ll", n * (512 << 10) // 4), ("reduce", "twoshot_ll", n * (512 << 10) // 4)]
     for kind in ["allreduce", "reducescatter", "allgather", "broadcast", "reduce"]:
         for algo in ["twoshot", "ring", "rabenseifner"]:
             if algo == "rabenseifner" and kind != "allreduce" or algo == "ring" and kind in ("broadcast", "reduce"):

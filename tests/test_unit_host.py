@@ -132,7 +132,8 @@ def test_tuner_table_and_file_override(dccl_lib):
     assert choose("allreduce_sym", 8, 1 << 30) == ("nvls", 16)
     # two ranks: rows for an exact world size come before the wildcard rows
     assert choose("allreduce_sym", 2, 1 << 30) == ("twoshot", 128) and choose("allreduce", 2, 1 << 24) == ("twoshot", 128)
-    assert choose("allreduce", 2, 100000)[0] == "oneshot" and choose("allreduce", 4, 1 << 30)[0] == "nvls"
+    assert choose("allreduce", 2, 50000)[0] == "oneshot" and choose("allreduce", 2, 300000)[0] == "twoshot_ll"
+    assert choose("allreduce", 4, 1 << 30)[0] == "nvls"
     assert choose("reducescatter_sym", 8, 1 << 30) == ("nvls", 64) and choose("reducescatter", 8, 1 << 30)[0] == "twoshot"
     assert dccl_lib.dccl_tuner_choose(b"bogus", 8, 1, 1, algo, 32, ctypes.byref(ctas)) == -1
     text = b"# my table\nallreduce 8 4k ring 4\nallreduce * inf rabenseifner 12\nnot a rule\nallreduce 8 1m twoshot 999\n"
@@ -141,6 +142,15 @@ def test_tuner_table_and_file_override(dccl_lib):
     assert choose("allreduce", 8, 100000) == ("rabenseifner", 12)
     assert choose("allreduce", 4, 10) == ("rabenseifner", 12)
     assert choose("reducescatter", 8, 10)[0] == "oneshot"              # untouched collective keeps the built-in rows
+    # rules bound to an element width: they come before the rules for every width, for the same world size only
+    def choose_w(coll, n, nbytes, esize):
+        assert dccl_lib.dccl_tuner_choose_width(coll.encode(), n, nbytes, 1, esize, algo, 32, ctypes.byref(ctas)) == 0
+        return algo.value.decode(), ctas.value
+    text = b"allgather 8 1m ring 8 2\nallgather 8 1m twoshot 16\nallgather * inf nvls 24 4\nallgather * inf oneshot 3 *\nallgather 8 inf ring 5 3\n"
+    assert dccl_lib.dccl_tuner_load_text(text) == 4                     # an element width of 3 bytes is refused
+    assert choose_w("allgather", 8, 1000, 2) == ("ring", 8) and choose_w("allgather", 8, 1000, 4) == ("twoshot", 16)
+    assert choose_w("allgather", 8, 1000, 0) == ("twoshot", 16) and choose_w("allgather", 8, 1 << 22, 4) == ("nvls", 24)
+    assert choose_w("allgather", 4, 1000, 2) == ("oneshot", 3) and choose_w("allgather", 4, 1000, 4) == ("nvls", 24)
 
 
 def test_oracle_integer_semantics():

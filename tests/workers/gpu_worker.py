@@ -172,6 +172,28 @@ def main():
             check(np.array_equal(to_numpy(g, name), np.concatenate([x[:per] for x in ins])), "switch all_gather into symmetric memory, one source unaligned")
             comm.set_algorithm("allgather", "auto")
             comm.free_symmetric(g)
+            # max / min inside the switch follow the same NaN rule as the peer kernels: a number beats a NaN
+            for name in ["bfloat16", "float16"]:
+                count = 70001
+                ins = [oracle.make_input(name, count, seed=7700 + r) for r in range(world)]
+                nan = np.uint16(0x7FC0) if name == "bfloat16" else np.nan
+                for r in range(world):
+                    ins[r][r::9] = nan
+                    ins[r][4::113] = nan
+                comm.set_algorithm("allreduce", "nvls")
+                for op in ["max", "min"]:
+                    want = oracle.fold(ins, op, bf16=name == "bfloat16")
+                    wf = oracle.bf16_to_f32(want) if name == "bfloat16" else want.astype(np.float32)
+                    s = to_torch(ins[rank], name, dev)
+                    out = torch.zeros_like(s)
+                    comm.all_reduce(s, out, op=op)
+                    torch.cuda.synchronize()
+                    got = to_numpy(out, name)
+                    gf = oracle.bf16_to_f32(got) if name == "bfloat16" else got.astype(np.float32)
+                    check(comm.last_algorithm("allreduce") == "nvls", "NaN rule: ran %s" % comm.last_algorithm("allreduce"))
+                    check(np.array_equal(np.isnan(gf), np.isnan(wf)) and np.array_equal(gf[~np.isnan(wf)], wf[~np.isnan(wf)]),
+                          "switch %s of %s with NaN inputs" % (op, name))
+                comm.set_algorithm("allreduce", "auto")
         code, emsg = comm.last_error()
         check(code == 0, "async error: " + emsg)
         launches = comm.launches

@@ -19,6 +19,8 @@
  *   --param NAME=VALUE (a tuning knob of this library's device side, repeatable: pipe_ctas=96, direct_rs=1, ...)
  *   --nccl-register (the NCCL arm runs on ncclMemAlloc memory registered with ncclCommRegister: NCCL's own
  *                    zero-copy path, the like-for-like partner of --symmetric)
+ *   --grid "NAME=V1:V2;NAME2=W1:W2" (the whole sweep once per combination of these parameter values, in one process;
+ *                    the combination is appended to the variant column)
  *   --colls also takes broadcast and reduce (root 0; S = the message)
  *   --out FILE (rank 0 writes the rows as JSON)
  */
@@ -72,7 +74,7 @@ int main(int argc, char** argv) {
         {"factor", required_argument, 0, 'f'}, {"type", required_argument, 0, 't'}, {"colls", required_argument, 0, 'c'},
         {"impls", required_argument, 0, 'i'}, {"algo", required_argument, 0, 'A'}, {"symmetric", no_argument, 0, 's'},
         {"out", required_argument, 0, 'o'}, {"op", required_argument, 0, 'O'}, {"register", no_argument, 0, 'R'},
-        {"param", required_argument, 0, 'p'}, {"nccl-register", no_argument, 0, 'N'}, {0, 0, 0, 0}};
+        {"param", required_argument, 0, 'p'}, {"nccl-register", no_argument, 0, 'N'}, {"grid", required_argument, 0, 'G'}, {0, 0, 0, 0}};
     int gpu = -2;
     size_t minb = 1024, maxb = 1ull << 30, factor = 2;
     dccl::ncclDataType_t dt = dccl::ncclBfloat16;
@@ -80,9 +82,10 @@ int main(int argc, char** argv) {
     std::string colls = "all_reduce,reduce_scatter,all_gather", impls = "dccl,nccl", algo, out;
     bool symmetric = false, registered = false, nccl_registered = false;
     std::vector<std::pair<std::string, int>> params;
+    std::vector<std::pair<std::string, std::vector<int>>> grid;
     while (true) {
         int idx = 0;
-        int c = getopt_long(argc, argv, "g:m:M:f:t:c:i:A:so:O:Rp:N", long_options, &idx);
+        int c = getopt_long(argc, argv, "g:m:M:f:t:c:i:A:so:O:Rp:NG:", long_options, &idx);
         if (c == -1) break;
         switch (c) {
         case 'g': gpu = !strcmp(optarg, "auto") ? -2 : atoi(optarg); break;
@@ -96,6 +99,21 @@ int main(int argc, char** argv) {
         case 's': symmetric = true; break;
         case 'R': registered = true; break;
         case 'N': nccl_registered = true; break;
+        case 'G': {
+            std::stringstream gs(optarg);
+            std::string item;
+            while (std::getline(gs, item, ';')) {
+                const size_t eq = item.find('=');
+                if (eq == std::string::npos) { std::cerr << "--grid wants NAME=V1:V2;..." << std::endl; return 1; }
+                std::vector<int> vals;
+                std::stringstream vs(item.substr(eq + 1));
+                std::string v;
+                while (std::getline(vs, v, ':')) if (!v.empty()) vals.push_back(atoi(v.c_str()));
+                if (vals.empty()) { std::cerr << "--grid: no values for " << item << std::endl; return 1; }
+                grid.emplace_back(item.substr(0, eq), vals);
+            }
+            break;
+        }
         case 'p': {
             const char* eq = strchr(optarg, '=');
             if (!eq) { std::cerr << "--param wants NAME=VALUE" << std::endl; return 1; }
@@ -197,9 +215,23 @@ int main(int argc, char** argv) {
     bool first = true;
     if (rank == 0) printf("%-15s %-5s %12s %10s %10s %10s  %s\n", "collective", "impl", "bytes", "us", "algbw", "busbw", "variant");
 
+    // every combination of the --grid values (one empty combination without --grid)
+    std::vector<std::vector<int>> combos(1);
+    for (const auto& g : grid) {
+        std::vector<std::vector<int>> next;
+        for (const auto& c : combos) for (int v : g.second) { auto d = c; d.push_back(v); next.push_back(d); }
+        combos.swap(next);
+    }
+    for (const auto& combo : combos) {
+    std::string tag;
+    for (size_t k = 0; k < combo.size(); k++) {
+        if (want_dccl && dccl::dcclSetParam(comm, grid[k].first.c_str(), combo[k]) != dccl::ncclSuccess) { std::cerr << "bad --grid parameter " << grid[k].first << std::endl; return 1; }
+        tag += " " + grid[k].first + "=" + std::to_string(combo[k]);
+    }
     for (const std::string& coll : split(colls)) {
         for (const std::string& impl : split(impls)) {
             const bool ours = impl == "dccl";
+            if (!ours && &combo != &combos[0]) continue;      // NCCL does not depend on the grid: once
             if ((ours && !want_dccl) || (!ours && !want_nccl)) continue;
             char* sb = ours ? s_ours : s_nccl;
             char* rb = ours ? r_ours : r_nccl;
@@ -238,6 +270,7 @@ int main(int argc, char** argv) {
                                            : nccl_registered ? "nccl-registered" : "nccl";
                 std::string vname(variant);
                 if (ours && dccl::dcclGetStat(comm, "zero_copy_calls") > zc0) vname += "+zerocopy";   // served out of / into user memory
+                if (ours) vname += tag;
                 if (rank == 0) {
                     printf("%-15s %-5s %12zu %10.2f %10.2f %10.2f  %s\n", coll.c_str(), impl.c_str(), total, us, alg, alg * f, vname.c_str());
                     fflush(stdout);
@@ -247,6 +280,7 @@ int main(int argc, char** argv) {
                 }
             }
         }
+    }
     }
     json << "\n]}\n";
     if (rank == 0 && !out.empty()) {
