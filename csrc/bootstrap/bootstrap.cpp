@@ -188,6 +188,28 @@ bool Bootstrap::fast_allgather(const void* in, size_t bytes, void* out) {
     return true;
 }
 
+bool Bootstrap::bulletin_post(const void* note, size_t bytes) {
+    if (!ctl_ || rank_ < 0 || rank_ >= kMaxGpuRanks || bytes > kBulletinBytes) return false;
+    CtlBulletin& b = ctl_->bulletin[rank_];
+    const uint64_t k = b.count.load(std::memory_order_relaxed);      // this rank is the only writer
+    memcpy(b.note[k % kBulletinDepth], note, bytes);
+    b.count.store(k + 1, std::memory_order_release);
+    return true;
+}
+
+int Bootstrap::bulletin_read(int rank, uint64_t index, void* out, size_t bytes) {
+    if (!ctl_ || rank < 0 || rank >= kMaxGpuRanks || bytes > kBulletinBytes) return -1;
+    CtlBulletin& b = ctl_->bulletin[rank];
+    const uint64_t have = b.count.load(std::memory_order_acquire);
+    if (index >= have) return 0;
+    if (have - index > (uint64_t)kBulletinDepth) return -1;
+    memcpy(out, b.note[index % kBulletinDepth], bytes);
+    // the writer may have lapped the entry while it was being copied: it starts to overwrite entry `index` when it posts
+    // note index + depth, i.e. once the count has reached index + depth
+    std::atomic_thread_fence(std::memory_order_acquire);
+    return b.count.load(std::memory_order_acquire) - index >= (uint64_t)kBulletinDepth ? -1 : 1;
+}
+
 ShmChannel* Bootstrap::channel(int src, int dst) {
     if (!data_) return nullptr;
     return (ShmChannel*)(data_ + chan_stride_ * ((size_t)src * (size_t)world_ + (size_t)dst));

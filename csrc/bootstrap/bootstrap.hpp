@@ -66,6 +66,14 @@ struct CtlBoardSlot {
     char pad[8];
     char data[kBoardBytes];
 };
+/** One rank's bulletin: small notes for whoever reads them later (bulletin_post / bulletin_read), kept in a ring. */
+static const size_t kBulletinBytes = 96;
+static const int kBulletinDepth = 32;
+struct CtlBulletin {
+    std::atomic<uint64_t> count;       // notes posted so far; note k lives in entry k % kBulletinDepth
+    char pad[56];
+    char note[kBulletinDepth][kBulletinBytes];
+};
 struct CtlSegment {
     std::atomic<uint32_t> abort;       // non-zero: somebody failed; value = 1 + failed rank
     std::atomic<uint32_t> abort_code;  // ncclResult_t
@@ -73,6 +81,7 @@ struct CtlSegment {
     CtlRank ranks[kMaxRanks];
     CtlShrink shrink;
     CtlBoardSlot board[kMaxRanks][2];
+    CtlBulletin bulletin[kMaxGpuRanks];
 };
 
 /** One direction of a rank pair: single-producer single-consumer byte FIFO. */
@@ -112,6 +121,14 @@ public:
      * (lazy buffer registration); all ranks must call it in the same order. False on abort or after the time limit.
      */
     bool fast_allgather(const void* in, size_t bytes, void* out);
+    /**
+     * One-sided notes in the shared control segment, for news that peers pick up whenever they next look (which
+     * allocations this rank has exported): bulletin_post appends a note of at most kBulletinBytes to this rank's ring
+     * and never waits; bulletin_read copies note number `index` of `rank`: 1 = copied, 0 = not posted yet, -1 = it has
+     * been overwritten (the ring holds the last kBulletinDepth notes). Ranks 0 .. kMaxGpuRanks-1 only.
+     */
+    bool bulletin_post(const void* note, size_t bytes);
+    int bulletin_read(int rank, uint64_t index, void* out, size_t bytes);
 
     bool send_fd(int peer, int fd, uint32_t tag);
     bool recv_fd(int peer, uint32_t tag, int* fd, int timeout_ms);

@@ -28,6 +28,8 @@ constexpr int kFlagVals = 32;           // flag values reserved per collective c
 constexpr size_t kFlagOff = 0;                          // uint32 flags[kMaxCtas][kMaxPeers]
 constexpr size_t kP2pFlagOff = 16u << 10;               // uint64 head[kMaxPeers][kP2pDepth][kP2pCtas], then tail[...] likewise
 constexpr int kP2pCtas = 32;                            // CTAs that can serve one direction of a pair
+constexpr size_t kP2pRdvOff = 32u << 10;                // rendezvous words of zero-copy send / recv (p2p.cu), 12 KB
+constexpr int kP2pRdvSlots = 16;                        // large messages per pair that one launch can hold
 constexpr size_t kLLOff = 64u << 10;                    // flag-in-data packets
 constexpr size_t kLLSlotBytes = 256u << 10;             // packets per source rank (half of it is payload)
 constexpr size_t kLLBytes = 2 * kMaxPeers * kLLSlotBytes;   // two generations
@@ -40,7 +42,8 @@ constexpr size_t kLL2Off = 40u << 20;                   // packets of the two-sh
 constexpr size_t kLL2PhaseBytes = 1u << 20;             // per generation, source rank and phase (half of it is payload)
 constexpr size_t kStageOff = 80u << 20;                 // two staging halves follow
 static_assert(kLLOff + kLLBytes <= kP2pOff, "LL region overlaps the p2p FIFOs");
-static_assert(kP2pFlagOff + 2 * kMaxPeers * 4 * kP2pCtas * 8 <= kLLOff, "p2p flag words overlap the packet region");
+static_assert(kP2pFlagOff + 2 * kMaxPeers * 4 * kP2pCtas * 8 <= kP2pRdvOff, "p2p flag words overlap the rendezvous words");
+static_assert(kP2pRdvOff + kMaxPeers * kP2pRdvSlots * (64 + 8 + 8 + 8) <= kLLOff, "rendezvous words overlap the packet region");
 static_assert(kP2pOff + kMaxPeers * kP2pBytesPerSrc <= kLL2Off, "p2p FIFOs overlap the second packet region");
 static_assert(kLL2Off + 2 * kMaxPeers * 2 * kLL2PhaseBytes <= kStageOff, "second packet region overlaps the staging area");
 
@@ -95,6 +98,7 @@ struct CollArgs {
     int unroll;            // vectors in flight per thread in the switch pass (2, 4 or 8)
     int pipe_nv;           // pipelined switch kernels: CTAs of the switch group ...
     int pipe_copy;         // ... and of each copy group
+    int pipe_teams;        // ... and how many teams the switch group forms (they take the chunks in turn)
 };
 
 struct Ctx {

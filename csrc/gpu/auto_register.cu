@@ -34,6 +34,7 @@ struct AutoBuf {                  // what a rank tells the others about one of i
     unsigned long long id;        // driver buffer id of the allocation; 0: cannot be exported
     unsigned long long base;      // of the allocation, in the owner's address space
     unsigned long long offset;    // of the buffer inside the allocation
+    unsigned long long size;      // of the allocation
     unsigned int fresh;           // the peers have not opened this allocation yet
     unsigned int pad;
     cudaIpcMemHandle_t handle;
@@ -74,6 +75,7 @@ static void describe(const DriverApi* d, const void* buf, std::map<unsigned long
     out->id = id;
     out->base = (unsigned long long)base;
     out->offset = (unsigned long long)((const char*)buf - (const char*)base);
+    out->size = (unsigned long long)it->second.size;
     out->handle = it->second.handle;
 }
 
@@ -97,29 +99,7 @@ bool GpuCommImpl::auto_view(const void* send, const void* recv, const char** sen
             if (!b.id) { usable = false; continue; }
             if (b.fresh) any_fresh = true;
             if (q == rank_) continue;
-            const std::pair<int, unsigned long long> key(q, b.base);
-            auto it = auto_imports_.find(key);
-            if (it != auto_imports_.end() && it->second.id != b.id) {
-                // the owner freed that allocation and got the address again: drop the stale mapping
-                close_import(it->second);
-                auto_imports_.erase(it);
-                it = auto_imports_.end();
-            }
-            if (it == auto_imports_.end()) {
-                AutoImport im;
-                im.id = b.id;
-                im.hkey.assign((const char*)&b.handle, sizeof(cudaIpcMemHandle_t));
-                im.hkey += (char)q;
-                auto op = ipc_opened_.find(im.hkey);  // one open per allocation and process, shared with explicit registration
-                if (op != ipc_opened_.end()) im.mapped = op->second;
-                else if (cudaIpcOpenMemHandle(&im.mapped, b.handle, cudaIpcMemLazyEnablePeerAccess) == cudaSuccess) ipc_opened_[im.hkey] = im.mapped;
-                else {
-                    cudaGetLastError();
-                    failed[k] |= (unsigned char)(1u << q);
-                    continue;
-                }
-                auto_imports_[key] = im;
-            }
+            if (!import_allocation(q, b.base, b.id, (size_t)b.size, b.handle)) failed[k] |= (unsigned char)(1u << q);
         }
     }
     if (any_fresh) {
@@ -151,6 +131,74 @@ bool GpuCommImpl::auto_view(const void* send, const void* recv, const char** sen
         recv_peers[q] = (const char*)auto_imports_[std::make_pair(q, all[q].b[1].base)].mapped + all[q].b[1].offset;
     }
     return true;
+}
+
+AutoImport* GpuCommImpl::import_allocation(int owner, unsigned long long base, unsigned long long id, size_t size, const cudaIpcMemHandle_t& handle) {
+    const std::pair<int, unsigned long long> key(owner, base);
+    auto it = auto_imports_.find(key);
+    if (it != auto_imports_.end() && it->second.id != id) {
+        // the owner freed that allocation and got the address again: drop the stale mapping
+        close_import(it->second);
+        auto_imports_.erase(it);
+        it = auto_imports_.end();
+    }
+    if (it != auto_imports_.end()) return &it->second;
+    AutoImport im;
+    im.id = id;
+    im.size = size;
+    im.stamp = ++import_stamp_;
+    im.hkey.assign((const char*)&handle, sizeof(cudaIpcMemHandle_t));
+    im.hkey += (char)owner;
+    auto op = ipc_opened_.find(im.hkey);      // one open per allocation and process, shared with explicit registration
+    if (op != ipc_opened_.end()) im.mapped = op->second;
+    else if (cudaIpcOpenMemHandle(&im.mapped, handle, cudaIpcMemLazyEnablePeerAccess) == cudaSuccess) ipc_opened_[im.hkey] = im.mapped;
+    else { cudaGetLastError(); return nullptr; }
+    return &(auto_imports_[key] = im);
+}
+
+/* ---- send / recv: the receiver's exports reach the sender through the bulletin, nobody waits ---- */
+
+namespace {
+struct ExportNote {               // one exported allocation, as posted on the owner's bulletin
+    unsigned long long id, base, size;
+    cudaIpcMemHandle_t handle;
+};
+static_assert(sizeof(ExportNote) <= kBulletinBytes, "an export note must fit a bulletin entry");
+}
+
+void GpuCommImpl::describe_receive_buffer(const void* buf, size_t bytes, P2pOp* op) {
+    op->dst_kind = P2P_DST_NONE;
+    const char* c = (const char*)buf;
+    for (size_t i = 0; i < user_segs_.size(); i++) {      // symmetric memory: allocated collectively, so segment i is segment i everywhere
+        const SymSegment& s = user_segs_[i];
+        if (c < s.base[rank_] || c + bytes > s.base[rank_] + s.size) continue;
+        op->dst_kind = P2P_DST_SYM; op->dst_a = i; op->dst_id = 0; op->dst_off = (unsigned long long)(c - s.base[rank_]);
+        return;
+    }
+    std::string err;
+    AutoBuf d;
+    describe(driver_api(&err), buf, auto_exports_, &d);
+    if (!d.id) return;
+    AutoExport& e = auto_exports_[d.base];
+    if (!e.posted) {
+        ExportNote note;
+        memset(&note, 0, sizeof(note));
+        note.id = d.id; note.base = d.base; note.size = d.size; note.handle = d.handle;
+        if (!bs_->bulletin_post(&note, sizeof(note))) return;
+        e.posted = true;
+    }
+    op->dst_kind = P2P_DST_IPC; op->dst_a = d.base; op->dst_id = d.id; op->dst_off = d.offset;
+}
+
+void GpuCommImpl::poll_exports(int peer) {
+    ExportNote note;
+    for (;;) {
+        const int got = bs_->bulletin_read(peer, bulletin_seen_[peer], &note, sizeof(note));
+        if (got == 0) return;
+        bulletin_seen_[peer]++;
+        if (got < 0) continue;                      // overwritten before this rank looked: that buffer keeps using the FIFO
+        import_allocation(peer, note.base, note.id, (size_t)note.size, note.handle);
+    }
 }
 
 void GpuCommImpl::close_import(const AutoImport& im) {

@@ -13,20 +13,23 @@ namespace {
 
 constexpr size_t kFlagEnd = kFlagOff + (size_t)kMaxCtas * kMaxPeers * sizeof(uint32_t);
 constexpr size_t kP2pFlagEnd = kP2pFlagOff + 2 * (size_t)kMaxPeers * kP2pDepth * kP2pCtas * sizeof(unsigned long long);
+// rendezvous words of large send / recv: a 64-byte post per (rank, slot), then path, done and arrival words
+constexpr size_t kP2pRdvEnd = kP2pRdvOff + (size_t)kMaxPeers * kP2pRdvSlots * (64 + 3 * sizeof(unsigned long long));
 constexpr size_t kLLEnd = kLLOff + kLLBytes;
 constexpr size_t kP2pEnd = kP2pOff + (size_t)kMaxPeers * kP2pBytesPerSrc;
 constexpr size_t kLL2End = kLL2Off + 2 * (size_t)kMaxPeers * 2 * kLL2PhaseBytes;
 
 const PoolGap g_gaps[] = {
     {kFlagEnd, kP2pFlagOff, "the flag rows"},
-    {kP2pFlagEnd, kLLOff, "the send/recv credit words"},
+    {kP2pRdvEnd, kLLOff, "the send/recv credit and rendezvous words"},
     {kLLEnd, kP2pOff, "the packet region"},
     {kLL2End, kStageOff, "the second packet region"},
 };
 constexpr int kGaps = (int)(sizeof(g_gaps) / sizeof(g_gaps[0]));
 
 static_assert(kFlagEnd + 2 * kGuardBytes <= kP2pFlagOff, "no room for guard words after the flag rows");
-static_assert(kP2pFlagEnd + 2 * kGuardBytes <= kLLOff, "no room for guard words after the credit words");
+static_assert(kP2pFlagEnd <= kP2pRdvOff, "the credit words overlap the rendezvous words");
+static_assert(kP2pRdvEnd + 2 * kGuardBytes <= kLLOff, "no room for guard words after the rendezvous words");
 static_assert(kLLEnd + 2 * kGuardBytes <= kP2pOff, "no room for guard words after the packet region");
 static_assert(kP2pEnd == kLL2Off, "the FIFOs are expected to end where the second packet region starts");
 static_assert(kLL2End + 2 * kGuardBytes <= kStageOff, "no room for guard words after the second packet region");

@@ -45,7 +45,40 @@ size_t g_declared_stage = 0;
 // 0 staged (nvls.cu), 1 pipelined all-reduce / reduce-scatter (nvls_pipe.cu), 2 pipelined broadcast / reduce (nvls_rooted.cu)
 int g_switch_form = 0;
 int g_pipe_nv = 0;
+int g_pipe_teams = 2;      // dccl_emu_set_pipe(chunk, 100 * teams + switch CTAs)
+
 #endif
+// set by dccl_emu_set_p2p_rendezvous: how large send / recv messages of the emulated ranks travel.
+// 0 FIFO only; 1 rendezvous, every receive buffer is mapped by its sender (zero-copy); 2 rendezvous, no buffer is
+// mapped (every sender answers "FIFO"); 3 rendezvous, only the buffers of even ranks are mapped (both paths in one launch)
+int g_p2p_rdv = 0;
+
+/** Fill the rendezvous fields of the emulated ranks' operations (per pair and direction: large messages are numbered in
+ *  the order of the operations) and the table of mappings: with all ranks in one address space a buffer is "mapped" at
+ *  its own address. `rdv_base[src][dst]`: large messages of earlier launches. */
+void emu_rendezvous(std::vector<P2pOp>& ops, size_t nranks, const std::vector<int>& nops, std::vector<unsigned long long>& rdv_base, P2pArgs* a) {
+    a->nmaps = 0;
+    if (!g_p2p_rdv) return;
+    std::vector<unsigned long long> sent(rdv_base), recvd(rdv_base);     // [src * n + dst]
+    for (size_t r = 0; r < nranks; r++)
+        for (int k = 0; k < nops[r]; k++) {
+            P2pOp& o = ops[r * kMaxP2pOps + (size_t)k];
+            if (o.bytes < kP2pRdvMinBytes) continue;
+            o.rdv = 1;
+            if (o.is_send) o.rdv_index = sent[r * nranks + (size_t)o.peer]++;
+            else {
+                o.rdv_index = recvd[(size_t)o.peer * nranks + r]++;
+                const bool mapped = g_p2p_rdv == 1 || (g_p2p_rdv == 3 && r % 2 == 0);
+                o.dst_kind = g_p2p_rdv == 2 ? P2P_DST_NONE : P2P_DST_IPC;
+                o.dst_a = (unsigned long long)(uintptr_t)o.buf; o.dst_id = 1; o.dst_off = 0;
+                if (mapped && a->nmaps < kMaxP2pMaps) {
+                    P2pMap& m = a->maps[a->nmaps++];
+                    m.peer = (int)r; m.kind = P2P_DST_IPC; m.a = o.dst_a; m.id = 1; m.size = o.bytes; m.mapped = o.buf;
+                }
+            }
+        }
+    rdv_base = sent;
+}
 
 // Pools of finished emulation runs, kept for the next run of the same size (the tests make thousands of short
 // runs; allocating and clearing 8 x 80 MB for each would dominate them).
@@ -216,9 +249,14 @@ int dccl_emu_declare_stage_bytes(size_t bytes) {
  *  2 pipelined broadcast / reduce. */
 void dccl_emu_set_switch_form(int form) { g_switch_form = form; }
 /** Host simulation only: target chunk size of the pipelined switch kernels and the size of their switch group
- *  (0: the default share of the grid). */
-void dccl_emu_set_pipe(size_t chunk_bytes, int nv_ctas) { nvls_pipe_set_chunk_bytes(chunk_bytes); g_pipe_nv = nv_ctas; }
+ *  (0: the default share of the grid); 100 * teams + size chooses the number of teams of that group as well (default 2). */
+void dccl_emu_set_pipe(size_t chunk_bytes, int nv_ctas) { nvls_pipe_set_chunk_bytes(chunk_bytes); g_pipe_nv = nv_ctas % 100; g_pipe_teams = nv_ctas >= 100 ? nv_ctas / 100 : 2; }
 #endif
+
+/** How large send / recv messages of the emulated ranks travel: 0 FIFO only, 1 rendezvous with every receive buffer
+ *  mapped by its sender (zero-copy), 2 rendezvous with none mapped (FIFO after the rendezvous), 3 only even ranks' buffers
+ *  mapped. */
+void dccl_emu_set_p2p_rendezvous(int mode) { g_p2p_rdv = mode; }
 
 /** 1: all-reduce with the two-shot variant runs its zero-copy form on the emulated ranks' user buffers. */
 void dccl_emu_set_peer_buffers(int on) { g_peer_buffers = on ? 1 : 0; }
@@ -328,12 +366,12 @@ int dccl_emu_collective(const char* kind_s, const char* algo_s, int nranks, int 
                     cap = nvls_pipe_capacity(es, stage_bytes, nranks, false);
                     LaunchCfg pc = cfg;
                     pc.ctas = cfg.ctas < 3 ? 3 : cfg.ctas;
-                    if (count <= cap) e = launch_nvls_pipe(a, dt, pc, false, g_pipe_nv);
+                    if (count <= cap) e = launch_nvls_pipe(a, dt, pc, false, g_pipe_nv, g_pipe_teams);
                 } else if (coll == COLL_REDUCESCATTER && g_switch_form == 1) {
                     cap = nvls_pipe_capacity(es, stage_bytes, nranks, true);
                     LaunchCfg pc = cfg;
                     pc.ctas = cfg.ctas < 2 ? 2 : cfg.ctas;
-                    if (count <= cap) e = launch_nvls_pipe(a, dt, pc, true, g_pipe_nv);
+                    if (count <= cap) e = launch_nvls_pipe(a, dt, pc, true, g_pipe_nv, g_pipe_teams);
                 } else if ((coll == COLL_BROADCAST || coll == COLL_REDUCE) && g_switch_form == 2) {
                     a.mode = coll == COLL_BROADCAST ? ROOTED_BROADCAST : ROOTED_REDUCE;
                     cap = nvls_pipe_capacity(es, stage_bytes, nranks, false);
@@ -443,6 +481,7 @@ int dccl_emu_sendrecv_ring(int nranks, size_t bytes, int window, int ctas_per_op
     cudaMemcpy(d_nops, nops.data(), n * sizeof(int), cudaMemcpyHostToDevice);
     int rc = 0;
     unsigned long long chunk_base = 0;
+    std::vector<unsigned long long> rdv_base(n * n, 0ull);
     for (int it = 0; it < iters && rc == 0; it++) {
         std::vector<P2pOp> ops(n * kMaxP2pOps);
         for (size_t r = 0; r < n; r++)
@@ -453,9 +492,10 @@ int dccl_emu_sendrecv_ring(int nranks, size_t bytes, int window, int ctas_per_op
                 d.is_send = 0; d.peer = (int)((r + n - 1) % n); d.buf = rb[r] + k * bytes; d.bytes = bytes; d.chunk_base = chunk_base + k * p2p_chunks(bytes);
             }
         chunk_base += W * p2p_chunks(bytes);
-        cudaMemcpy(d_ops, ops.data(), ops.size() * sizeof(P2pOp), cudaMemcpyHostToDevice);
         P2pArgs a;
         memset(&a, 0, sizeof(a));
+        emu_rendezvous(ops, n, nops, rdv_base, &a);
+        cudaMemcpy(d_ops, ops.data(), ops.size() * sizeof(P2pOp), cudaMemcpyHostToDevice);
         a.emu = w.d_comms;
         a.emu_ops = d_ops;
         a.emu_nops = d_nops;
@@ -504,6 +544,7 @@ int dccl_emu_all_to_all(int nranks, size_t bytes, int ctas_per_op, int iters, co
     int rc = 0;
     // chunks moved so far per ordered pair (every pair moves one message per iteration)
     unsigned long long chunk_base = 0;
+    std::vector<unsigned long long> rdv_base(n * n, 0ull);
     for (int it = 0; it < iters && rc == 0; it++) {
         std::vector<P2pOp> ops(n * kMaxP2pOps);
         for (size_t r = 0; r < n; r++) {
@@ -520,9 +561,10 @@ int dccl_emu_all_to_all(int nranks, size_t bytes, int ctas_per_op, int iters, co
             }
         }
         chunk_base += p2p_chunks(bytes);
-        cudaMemcpy(d_ops, ops.data(), ops.size() * sizeof(P2pOp), cudaMemcpyHostToDevice);
         P2pArgs a;
         memset(&a, 0, sizeof(a));
+        emu_rendezvous(ops, n, nops_v, rdv_base, &a);
+        cudaMemcpy(d_ops, ops.data(), ops.size() * sizeof(P2pOp), cudaMemcpyHostToDevice);
         a.emu = w.d_comms;
         a.emu_ops = d_ops;
         a.emu_nops = d_nops;

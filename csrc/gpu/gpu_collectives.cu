@@ -35,8 +35,12 @@ bool GpuCommImpl::set_param(const char* name, int value) {
     if (k == "pipe_min_mb" && value >= 0) { pipe_min_bytes_ = (size_t)value << 20; return true; }
     if (k == "pipe_ctas" && value >= 3 && value <= kMaxCtas) { pipe_ctas_ = value; return true; }
     if (k == "pipe_nv_ctas" && value >= 1 && value <= kMaxCtas / 2) { pipe_nv_ctas_ = value; return true; }
+    if (k == "pipe_teams" && value >= 1 && value <= 4) { pipe_teams_ = value; return true; }
+    if (k == "pipe_unroll" && (value == 2 || value == 4 || value == 8)) { pipe_unroll_ = value; return true; }
     if (k == "auto_register_min_kb" && value >= 0) { auto_min_bytes_ = (size_t)value << 10; return true; }
     if (k == "direct_rs" && (value == 0 || value == 1)) { direct_rs_ = value == 1; return true; }
+    if (k == "direct_rs_min_mb" && value >= 0) { direct_rs_min_bytes_ = (size_t)value << 20; return true; }
+    if (k == "p2p_rendezvous" && (value == 0 || value == 1)) { p2p_rdv_ = value == 1; return true; }
     if (k == "device_seq" && (value == 0 || value == 1)) return set_device_seq(value == 1);
     if (k == "rooted_pipe" && (value == 0 || value == 1)) { rooted_pipe_ = value == 1; return true; }
     if (k == "pipe_chunk_kb" && value >= 256) { nvls_pipe_set_chunk_bytes((size_t)value << 10); return true; }
@@ -138,6 +142,13 @@ ncclResult_t GpuCommImpl::all_reduce(const void* send, void* recv, size_t count,
         peer_addr = true;
         for (int p = 0; peer_addr && p < n_; p++) peer_addr = (uintptr_t)sp[p] % 16 == 0 && (uintptr_t)rp[p] % 16 == 0;
     }
+    // The table asked for the peer form because zero-copy beats the switch at this world size, but these buffers cannot
+    // be mapped (pool or virtual-memory allocations): large messages then do better through the switch's pipeline than
+    // through peer staging. (The answer of the exchange is the same on every rank.)
+    if (ch.algo == ALGO_TWOSHOT && !peer_addr && algo == ALGO_AUTO && n_ > 2 && nvls_ok && pipe_min_bytes_ > 0 && bytes >= pipe_min_bytes_) {
+        ch.algo = ALGO_NVLS;
+        last_[COLL_ALLREDUCE] = ch.algo;
+    }
     // two-shot on buffers the peers can address: fold straight out of / into the user buffers, no staging
     if (ch.algo == ALGO_TWOSHOT && peer_addr) {
         zero_copy_calls_++;
@@ -181,7 +192,7 @@ ncclResult_t GpuCommImpl::all_reduce(const void* send, void* recv, size_t count,
         cudaError_t e;
         switch (ch.algo) {
         case ALGO_NVLS:
-            if (pipe) e = launch_nvls_pipe(a, dt, cfg, false, pipe_nv_ctas_);
+            if (pipe) { a.unroll = pipe_unroll_; e = launch_nvls_pipe(a, dt, cfg, false, pipe_nv_ctas_, pipe_teams_); }
             else { a.mode = NV_ALLREDUCE; e = launch_nvls(a, dt, cfg); }
             break;
         case ALGO_RING: a.mode = RING_ALLREDUCE; e = launch_ring(a, dt, cfg); break;
@@ -238,7 +249,7 @@ ncclResult_t GpuCommImpl::reduce_scatter(const void* send, void* recv, size_t re
     // two-shot on buffers the peers can address: every rank folds its slot straight out of the peers' send buffers.
     // Chosen by itself only at world size 2, where this form is measured (all-reduce: 1.5 x the staged form);
     // elsewhere the caller asks for it with dcclSetAlgorithm(twoshot).
-    if (ch.algo == ALGO_TWOSHOT && (n_ == 2 || direct_rs_ || algo == ALGO_TWOSHOT) && (recvcount * es) % 16 == 0) {
+    if (ch.algo == ALGO_TWOSHOT && (n_ == 2 || (direct_rs_ && bytes >= direct_rs_min_bytes_) || algo == ALGO_TWOSHOT) && (recvcount * es) % 16 == 0) {
         // the kernel moves whole 16-byte vectors, so every rank's send and receive pointer must be aligned; the ranks
         // know each other's through the symmetric layout or through the exchange
         const char* rp[kMaxPeers];
@@ -289,7 +300,7 @@ ncclResult_t GpuCommImpl::reduce_scatter(const void* send, void* recv, size_t re
         a.count = c;
         NEXT_SEQ(a);
         cudaError_t e;
-        if (pipe) e = launch_nvls_pipe(a, dt, cfg, true, pipe_nv_ctas_);
+        if (pipe) { a.unroll = pipe_unroll_; e = launch_nvls_pipe(a, dt, cfg, true, pipe_nv_ctas_, pipe_teams_); }
         else if (ch.algo == ALGO_NVLS) { a.mode = NV_REDUCESCATTER; e = launch_nvls(a, dt, cfg); }
         else if (ch.algo == ALGO_RING) { a.mode = RING_REDUCESCATTER; e = launch_ring(a, dt, cfg); }
         else { a.mode = TS_REDUCESCATTER; e = launch_twoshot(a, dt, cfg); }
@@ -519,6 +530,27 @@ ncclResult_t GpuCommImpl::p2p_launch(std::vector<P2pOp>& ops, cudaStream_t strea
         // the ranks record their operations in matching order.
         std::stable_partition(ops.begin() + (long)first, ops.begin() + (long)first + a.nops, [](const P2pOp& o) { return o.is_send == 0; });
         for (int i = 0; i < a.nops; i++) a.ops[i] = ops[first + i];
+        // what this rank has mapped of the peers it sends large messages to in this launch: their symmetric segments and
+        // their exported allocations, newest first; the receiver's kernel says which buffer it is, the sender's kernel looks here
+        a.nmaps = 0;
+        bool listed[kMaxPeers] = {false};
+        for (int i = 0; i < a.nops; i++) {
+            const P2pOp& o = a.ops[i];
+            if (!o.is_send || !o.rdv || listed[o.peer]) continue;
+            listed[o.peer] = true;
+            for (size_t k = 0; k < user_segs_.size() && a.nmaps < kMaxP2pMaps; k++) {
+                P2pMap& m = a.maps[a.nmaps++];
+                m.peer = o.peer; m.kind = P2P_DST_SYM; m.a = k; m.id = 0; m.size = user_segs_[k].size; m.mapped = user_segs_[k].base[o.peer];
+            }
+            std::vector<const std::pair<const std::pair<int, unsigned long long>, AutoImport>*> mine;
+            for (const auto& kv : auto_imports_) if (kv.first.first == o.peer) mine.push_back(&kv);
+            std::sort(mine.begin(), mine.end(), [](auto* x, auto* y) { return x->second.stamp > y->second.stamp; });
+            for (const auto* kv : mine) {
+                if (a.nmaps >= kMaxP2pMaps) break;
+                P2pMap& m = a.maps[a.nmaps++];
+                m.peer = o.peer; m.kind = P2P_DST_IPC; m.a = kv->first.second; m.id = kv->second.id; m.size = kv->second.size; m.mapped = (char*)kv->second.mapped;
+            }
+        }
         LaunchCfg cfg;
         cfg.ctas = a.nops * ctas_per_op;
         cfg.stream = stream;
@@ -538,8 +570,15 @@ ncclResult_t GpuCommImpl::send(const void* buf, size_t bytes, int peer, cudaStre
     last_[COLL_SENDRECV] = ALGO_ONESHOT;
     if (!bytes) return ncclSuccess;
     P2pOp op;
+    memset(&op, 0, sizeof(op));
     op.is_send = 1; op.peer = peer; op.buf = (char*)buf; op.bytes = bytes; op.chunk_base = sent_chunks_[peer];
     sent_chunks_[peer] += p2p_chunks(bytes);
+    if (p2p_rdv_ && bytes >= kP2pRdvMinBytes) {     // a large message: meet the receiver first, zero-copy where its buffer is mapped here
+        DeviceGuard g(dev_);
+        op.rdv = 1;
+        op.rdv_index = sent_rdv_[peer]++;
+        poll_exports(peer);
+    }
     if (in_group_) { if (group_ops_.empty()) group_stream_ = stream; group_ops_.push_back(op); return ncclSuccess; }
     std::vector<P2pOp> ops{op};
     return p2p_launch(ops, stream);
@@ -552,8 +591,15 @@ ncclResult_t GpuCommImpl::recv(void* buf, size_t bytes, int peer, cudaStream_t s
     last_[COLL_SENDRECV] = ALGO_ONESHOT;
     if (!bytes) return ncclSuccess;
     P2pOp op;
+    memset(&op, 0, sizeof(op));
     op.is_send = 0; op.peer = peer; op.buf = (char*)buf; op.bytes = bytes; op.chunk_base = recv_chunks_[peer];
     recv_chunks_[peer] += p2p_chunks(bytes);
+    if (p2p_rdv_ && bytes >= kP2pRdvMinBytes) {
+        DeviceGuard g(dev_);
+        op.rdv = 1;
+        op.rdv_index = recv_rdv_[peer]++;
+        describe_receive_buffer(buf, bytes, &op);
+    }
     if (in_group_) { if (group_ops_.empty()) group_stream_ = stream; group_ops_.push_back(op); return ncclSuccess; }
     std::vector<P2pOp> ops{op};
     return p2p_launch(ops, stream);

@@ -58,12 +58,16 @@ bool GpuCommImpl::init(std::string* err) {
     set_param("unroll", (int)cfg.get_int("DCCL/unroll", 8));
     pipe_min_bytes_ = (size_t)cfg.get_int("DCCL/nvls_pipe_min_bytes", 16ll << 20);
     auto_min_bytes_ = (size_t)cfg.get_int("DCCL/auto_register_min_bytes", 4ll << 20);
-    direct_rs_ = cfg.get_bool("DCCL/direct_reduce_scatter", false);
+    direct_rs_ = cfg.get_bool("DCCL/direct_reduce_scatter", true);
+    direct_rs_min_bytes_ = (size_t)cfg.get_int("DCCL/direct_reduce_scatter_min_bytes", 32ll << 20);
+    p2p_rdv_ = cfg.get_bool("DCCL/p2p_rendezvous", true);
     pipe_ctas_ = (int)cfg.get_int("DCCL/nvls_pipe_ctas", 80);
     pipe_nv_ctas_ = (int)cfg.get_int("DCCL/nvls_pipe_nv_ctas", 16);
+    pipe_teams_ = (int)cfg.get_int("DCCL/nvls_pipe_teams", 2);
+    if (pipe_teams_ < 1 || pipe_teams_ > 4) pipe_teams_ = 2;
     device_stamps_ = cfg.get_bool("DCCL/device_stamps", false);
     rooted_pipe_ = cfg.get_bool("DCCL/nvls_rooted_pipe", false);
-    nvls_pipe_set_chunk_bytes((size_t)cfg.get_int("DCCL/nvls_pipe_chunk_bytes", 8ll << 20));
+    nvls_pipe_set_chunk_bytes((size_t)cfg.get_int("DCCL/nvls_pipe_chunk_bytes", 16ll << 20));
     rooted_pipe_min_bytes_ = (size_t)cfg.get_int("DCCL/nvls_rooted_pipe_min_bytes", 16ll << 20);
     if (p2p_ctas_ < 1) p2p_ctas_ = 1;
     if (p2p_ctas_ > kP2pCtas) p2p_ctas_ = kP2pCtas;

@@ -25,12 +25,15 @@ struct AutoExport {
     size_t size = 0;
     cudaIpcMemHandle_t handle;
     bool announced = false;           // the peers have seen it in an exchange
+    bool posted = false;              // it is on this rank's bulletin (send / recv peers pick it up from there)
     bool refused = false;             // cannot be exported, or a peer could not open it: not offered (again)
 };
 /** ... and a peer's allocation as mapped here. */
 struct AutoImport {
     unsigned long long id = 0;
     void* mapped = nullptr;
+    size_t size = 0;                  // of the allocation
+    unsigned long long stamp = 0;     // when it was mapped (newer mappings are offered to a send first)
     std::string hkey;                 // its entry in the table of opened handles
 };
 
@@ -93,6 +96,12 @@ private:
      *  (on every rank alike) when all ranks can address all buffers; fills the peers' views of both. Collective. */
     bool auto_view(const void* send, const void* recv, const char** send_peers, const char** recv_peers);
     void close_import(const AutoImport& im);
+    /** Map (or find) allocation `id` at `base` of rank `owner`; nullptr when it cannot be opened. */
+    AutoImport* import_allocation(int owner, unsigned long long base, unsigned long long id, size_t size, const cudaIpcMemHandle_t& handle);
+    /** A large receive: where `buf` lies, for the sender (symmetric segment, exported allocation, or neither). */
+    void describe_receive_buffer(const void* buf, size_t bytes, P2pOp* op);
+    /** A large send: pick up what `peer` has exported since the last look. */
+    void poll_exports(int peer);
     int ctas_for(int tuned) const;
     /** Move the sequence number to the device counter (calls become replayable from a CUDA graph) or back to
      *  the host. Every rank must switch at the same point of its call order. Waits for the device to go idle.
@@ -133,6 +142,8 @@ private:
     size_t pipe_min_bytes_ = 16u << 20;   // ordinary-buffer switch all-reduce is pipelined from this size on (0 = never)
     int pipe_ctas_ = 80;                  // grid of the pipelined switch all-reduce: pipe_nv_ctas_ switch CTAs, the rest copy in / out
     int pipe_nv_ctas_ = 16;
+    int pipe_teams_ = 2;                  // the switch CTAs take the chunks in turn, in this many teams
+    int pipe_unroll_ = 4;                 // vectors in flight per thread in the pipeline's switch pass
     int unroll_ = 8;
     bool rooted_pipe_ = false;            // broadcast / reduce of large ordinary buffers: pipelined switch form (nvls_rooted.cu)
     size_t rooted_pipe_min_bytes_ = 16u << 20;
@@ -145,9 +156,14 @@ private:
     std::map<unsigned long long, AutoExport> auto_exports_;                  // by base address of the allocation
     std::map<std::pair<int, unsigned long long>, AutoImport> auto_imports_;  // by (owner, base address at the owner)
     size_t auto_min_bytes_ = 4u << 20;          // lazy registration serves calls from this size on (0: never)
-    bool direct_rs_ = false;                    // reduce-scatter on addressable buffers: zero-copy pull at every world size
+    bool direct_rs_ = true;                     // reduce-scatter on addressable buffers: zero-copy pull, from direct_rs_min_bytes_ on
+    size_t direct_rs_min_bytes_ = 32u << 20;    // (two ranks: from the lazy-registration threshold on)
     uint64_t zero_copy_calls_ = 0;              // calls served straight out of / into user memory by peer kernels
     unsigned long long sent_chunks_[kMaxPeers], recv_chunks_[kMaxPeers];
+    unsigned long long sent_rdv_[kMaxPeers] = {0}, recv_rdv_[kMaxPeers] = {0};   // large (rendezvous) messages per peer and direction
+    uint64_t bulletin_seen_[kMaxPeers] = {0};   // notes of each peer's bulletin read so far
+    unsigned long long import_stamp_ = 0;
+    bool p2p_rdv_ = true;                       // large send / recv meet and go zero-copy where the buffer is mapped
     bool in_group_ = false;
     std::vector<P2pOp> group_ops_;
     cudaStream_t group_stream_ = nullptr;

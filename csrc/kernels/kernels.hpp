@@ -53,8 +53,9 @@ cudaError_t launch_nvls(const CollArgs& a, ncclDataType_t dt, const LaunchCfg& c
  * chunk by chunk (reduce-scatter: count = per-rank elements, stride = slot distance in the send buffer) */
 size_t nvls_pipe_capacity(size_t elem_size, size_t stage_bytes, int nranks, bool reduce_scatter);
 /** cfg.ctas is the whole grid; nv_ctas of it form the switch group (0: a fifth / a third of the grid), the rest is
- *  split evenly between copy-in and copy-out (all-reduce) or is the copy-in group (reduce-scatter). */
-cudaError_t launch_nvls_pipe(const CollArgs& a, ncclDataType_t dt, const LaunchCfg& cfg, bool reduce_scatter, int nv_ctas = 0);
+ *  split evenly between copy-in and copy-out (all-reduce) or is the copy-in group (reduce-scatter). The switch CTAs
+ *  form `teams` teams that take the chunks in turn. */
+cudaError_t launch_nvls_pipe(const CollArgs& a, ncclDataType_t dt, const LaunchCfg& cfg, bool reduce_scatter, int nv_ctas = 0, int teams = 2);
 /** Target chunk size of the pipeline (default 8 MB, at most 24 chunks per launch); a tuning knob, the same on every rank. */
 void nvls_pipe_set_chunk_bytes(size_t bytes);
 
@@ -74,15 +75,33 @@ cudaError_t launch_hd(const CollArgs& a, ncclDataType_t dt, const LaunchCfg& cfg
 cudaError_t launch_local_copy(void* dst, const void* src, size_t bytes, cudaStream_t stream);
 cudaError_t launch_local_reduce(void* acc, const void* in, size_t count, ncclDataType_t dt, ncclRedOp_t op, cudaStream_t stream);
 
-/* p2p.cu: send / recv through the per-pair FIFOs */
+/* p2p.cu: send / recv. Small messages go through the per-pair FIFOs; a large message is written straight into the
+ * receiver's buffer when the sender has that buffer mapped (rendezvous), else through the FIFO as well. */
+enum { P2P_DST_NONE = 0,     // the receive buffer cannot be reached by peers: FIFO
+       P2P_DST_SYM = 1,      // it lies in symmetric memory: (segment number, offset)
+       P2P_DST_IPC = 2 };    // it lies in an exported allocation: (base address at the owner, buffer id, offset)
 struct P2pOp {
     int is_send;
     int peer;
     char* buf;
     size_t bytes;
     unsigned long long chunk_base;   // chunks already moved on this (peer, direction) before this op
+    int rdv;                         // 1: a large message: sender and receiver meet before data moves
+    int dst_kind;                    // receives only: where the buffer lies (P2P_DST_*)
+    unsigned long long rdv_index;    // large messages on this (peer, direction) before this op
+    unsigned long long dst_a, dst_id, dst_off;   // receives only: segment number or base address, buffer id, offset
+};
+/** What a sender knows about a peer's memory: where a segment / allocation of `peer` is mapped in this process. */
+struct P2pMap {
+    int peer;
+    int kind;                        // P2P_DST_SYM or P2P_DST_IPC
+    unsigned long long a, id;        // segment number, or base address at the owner and buffer id
+    unsigned long long size;
+    char* mapped;
 };
 constexpr int kMaxP2pOps = 16;
+constexpr int kMaxP2pMaps = 24;
+constexpr size_t kP2pRdvMinBytes = 512u << 10;   // messages from this size on are rendezvous messages (both ends know the size)
 struct P2pArgs {
     DevComm comm;
     const DevComm* emu;              // emulation: array of per-rank DevComm
@@ -91,7 +110,9 @@ struct P2pArgs {
     int ctas_per_op;
     int ctas_per_rank;
     int nops;
+    int nmaps;
     P2pOp ops[kMaxP2pOps];
+    P2pMap maps[kMaxP2pMaps];        // the mappings of the peers this launch sends to (most recent first)
 };
 cudaError_t launch_p2p(const P2pArgs& a, const LaunchCfg& cfg);
 inline size_t p2p_chunks(size_t bytes) { return (bytes + kP2pChunk - 1) / kP2pChunk; }

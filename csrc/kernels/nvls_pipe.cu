@@ -15,7 +15,13 @@
  *        all-reduce only)
  *
  * so that the copies of chunks k+1 and k-1 run while the switch works on chunk
- * k. The groups have sizes of their own: the switch pass is bound by latency
+ * k. Between two chunks a switch CTA has dead time: its multicast stores must
+ * have landed everywhere before it may signal, and the first reductions of the
+ * next chunk take a round trip through the switch before data flows (about
+ * 10 us, measured as the difference between 16 and 24 chunks per launch). The
+ * NV CTAs therefore form P teams (a.pipe_teams, 2 by default) that take the
+ * chunks in turn, so that one team streams while the other is between chunks;
+ * eight CTAs already saturate the switch pass. The groups have sizes of their own: the switch pass is bound by latency
  * and saturates with about 16 CTAs, the copies are bound by HBM and want long
  * contiguous ranges. Each copy CTA therefore moves ONE contiguous slice of a
  * chunk (a piece of a few tens of KB per source would leave the unrolled copy
@@ -40,13 +46,13 @@ namespace dccl {
 constexpr int kPipeMaxChunks = 24;    // flag values per call are limited (kFlagVals)
 static_assert(kPipeMaxChunks < kFlagVals, "chunk numbers must fit the per-call flag values");
 
-/** wait until point idx was signalled on flag rows [row0, row0 + rows) by EVERY rank */
-__device__ __forceinline__ bool wait_rows_all_ranks(const DevComm& c, int row0, int rows, uint32_t seq, int idx, int site) {
+/** wait until point idx was signalled on the `rows` flag rows row0, row0 + stride, ... by EVERY rank */
+__device__ __forceinline__ bool wait_rows_all_ranks(const DevComm& c, int row0, int rows, int stride, uint32_t seq, int idx, int site) {
     __shared__ int s_fail;
     if (threadIdx.x == 0) s_fail = 0;
     __syncthreads();
     for (int t = (int)threadIdx.x; t < c.nranks * rows; t += (int)blockDim.x)
-        if (!wait_peer(c, t % c.nranks, row0 + t / c.nranks, seq, idx, site)) s_fail = 1;
+        if (!wait_peer(c, t % c.nranks, row0 + (t / c.nranks) * stride, seq, idx, site)) s_fail = 1;
     __syncthreads();
     const bool ok = s_fail == 0;
     __syncthreads();
@@ -76,6 +82,7 @@ __device__ __forceinline__ void nvls_pipe_body(const CollArgs& a, const Ctx& x) 
     const int n = c.nranks, r = c.rank;
     const bool rs = a.root != 0;                   // reduce-scatter (count = per-rank elements) instead of all-reduce
     const int Gn = a.pipe_nv, Gc = a.pipe_copy;    // switch CTAs; copy CTAs on each side
+    const int P = a.pipe_teams < 1 ? 1 : (a.pipe_teams > Gn ? Gn : a.pipe_teams);   // NV CTA g belongs to team g % P, which takes chunks k with k % P == g % P
     // CTA order: [NV (Gn)] [IN (Gc)] [OUT (Gc), all-reduce only]; a CTA's flag row is its index
     enum { ROLE_IN, ROLE_NV, ROLE_OUT };
     int role, g;
@@ -116,13 +123,15 @@ __device__ __forceinline__ void nvls_pipe_body(const CollArgs& a, const Ctx& x) 
             }
             signal_all_ranks(c, x.bid, x.seq, k);
         } else if (role == ROLE_NV) {
-            if (!wait_rows_all_ranks(c, Gn, Gc, x.seq, k, 560)) return;
+            if (k % P != g % P) continue;
+            const int team = (Gn - g % P + P - 1) / P, gi = g / P;      // CTAs of this team, this CTA's place in it
+            if (!wait_rows_all_ranks(c, Gn, Gc, 1, x.seq, k, 560)) return;
             // this rank's shard of the chunk: the whole chunk of its slot (reduce-scatter) or the r-th n-th of it
             const size_t per = rs ? cnt : ((cnt + n - 1) / n + VE - 1) / VE * VE;
             const size_t s_lo = rs ? 0 : (per * (size_t)r < cnt ? per * (size_t)r : cnt);
             const size_t s_len = rs ? cnt : (cnt - s_lo < per ? cnt - s_lo : per);
             size_t lo, hi;
-            split_range(s_len, g, Gn, VE, &lo, &hi);
+            split_range(s_len, gi, team, VE, &lo, &hi);
             if (hi > lo) {
                 if (rs) {
                     const size_t off = ((size_t)r * slot + base + lo) * ES;
@@ -143,7 +152,8 @@ __device__ __forceinline__ void nvls_pipe_body(const CollArgs& a, const Ctx& x) 
             }
             if (!rs) signal_all_ranks(c, x.bid, x.seq, k);
         } else {
-            if (!wait_rows_all_ranks(c, 0, Gn, x.seq, k, 570)) return;
+            // the team that reduced chunk k: rows k % P, k % P + P, ...
+            if (!wait_rows_all_ranks(c, k % P, (Gn - k % P + P - 1) / P, P, x.seq, k, 570)) return;
             size_t lo, hi;
             split_range(cnt, g, Gc, VE, &lo, &hi);
             if (hi > lo) copy_range<T>(recv + base + lo, my_stage + base + lo, hi - lo);
@@ -164,7 +174,7 @@ size_t nvls_pipe_capacity(size_t es, size_t stage_bytes, int nranks, bool reduce
     return reduce_scatter ? (elems / (size_t)nranks / 64) * 64 : elems;
 }
 
-static size_t g_pipe_chunk_bytes = 8u << 20;   // target chunk size; every rank must use the same value
+static size_t g_pipe_chunk_bytes = 16u << 20;  // target chunk size; every rank must use the same value
 
 void nvls_pipe_set_chunk_bytes(size_t bytes) { if (bytes >= 4096) g_pipe_chunk_bytes = bytes; }
 
@@ -187,9 +197,10 @@ void nvls_pipe_split(int ctas, int nv, bool reduce_scatter, int* nv_out, int* co
     *copy_out = copy;
 }
 
-cudaError_t launch_nvls_pipe(const CollArgs& a_in, ncclDataType_t dt, const LaunchCfg& cfg_in, bool reduce_scatter, int nv_ctas) {
+cudaError_t launch_nvls_pipe(const CollArgs& a_in, ncclDataType_t dt, const LaunchCfg& cfg_in, bool reduce_scatter, int nv_ctas, int teams) {
     CollArgs a = a_in;
     LaunchCfg cfg = cfg_in;
+    a.pipe_teams = teams;
     nvls_pipe_split(cfg.ctas, nv_ctas, reduce_scatter, &a.pipe_nv, &a.pipe_copy);
     cfg.ctas = a.pipe_nv + (reduce_scatter ? 1 : 2) * a.pipe_copy;
     const size_t es = dt == ncclFloat64 || dt == ncclInt64 || dt == ncclUint64 ? 8 : dt == ncclFloat16 || dt == ncclBfloat16 ? 2 : 4;

@@ -67,8 +67,8 @@ void check(dccl::ncclResult_t r, const char* what) {
 
 class WorkDccl : public Work {
 public:
-    WorkDccl(c10d::OpType op, std::vector<at::Tensor> outputs, bool cuda)
-        : Work(-1, op), outputs_(std::move(outputs)), cuda_(cuda) {
+    WorkDccl(c10d::OpType op, std::vector<at::Tensor> outputs, bool cuda, dccl::ncclComm_t comm = nullptr)
+        : Work(-1, op), outputs_(std::move(outputs)), cuda_(cuda), comm_(comm) {
         if (cuda_) {
             event_ = std::make_shared<at::cuda::CUDAEvent>(cudaEventDisableTiming);
             std::vector<c10::Device> devs;
@@ -91,9 +91,23 @@ public:
         finish();
     }
     bool isCompleted() override { return !cuda_ || event_->query(); }
-    bool isSuccess() const override { return true; }
+    /** What the communicator knows by now: a bounded wait inside a kernel that gave up, or an abort by the watchdog,
+     *  shows in its status block (the kernels of later calls may not have run yet; they report through later work). */
+    bool isSuccess() const override {
+        if (!comm_) return true;
+        dccl::ncclResult_t async = dccl::ncclSuccess;
+        char msg[160];
+        dccl::dcclGetLastError(comm_, &async, msg, sizeof(msg));
+        return async == dccl::ncclSuccess;
+    }
     bool wait(std::chrono::milliseconds = std::chrono::milliseconds(0)) override {
         synchronize();
+        if (comm_) {
+            dccl::ncclResult_t async = dccl::ncclSuccess;
+            char msg[160] = "";
+            dccl::dcclGetLastError(comm_, &async, msg, sizeof(msg));
+            TORCH_CHECK(async == dccl::ncclSuccess, "dccl backend: the communicator reported ", dccl::dcclGetErrorString(async), ": ", msg);
+        }
         return true;
     }
     void synchronize() override {
@@ -108,6 +122,7 @@ public:
 private:
     std::vector<at::Tensor> outputs_;
     bool cuda_;
+    dccl::ncclComm_t comm_;
     std::shared_ptr<at::cuda::CUDAEvent> event_;
     c10::intrusive_ptr<c10::ivalue::Future> future_;
 };
@@ -356,7 +371,12 @@ public:
         return work;
     }
     c10::intrusive_ptr<Work> barrier(const c10d::BarrierOptions&) override {
-        // a host all-reduce of one word: returns when every rank has arrived
+        // What this rank has queued on the communication stream finishes first; then a host all-reduce of one word,
+        // which returns when every rank has arrived: after the barrier every rank's earlier collectives are complete.
+        {
+            std::lock_guard<std::mutex> g(mu_);
+            if (stream_) stream_->synchronize();
+        }
         int32_t word = 0;
         check(dccl::ncclAllReduce(&word, &word, 1, dccl::ncclInt32, dccl::ncclSum, comm_, nullptr), "barrier");
         auto w = c10::make_intrusive<WorkDccl>(c10d::OpType::BARRIER, std::vector<at::Tensor>{}, false);
@@ -390,7 +410,7 @@ private:
         std::lock_guard<std::mutex> g(mu_);
         TORCH_CHECK(comm_, "dccl backend: the process group was shut down");
         const bool cuda = where.is_cuda();
-        auto work = c10::make_intrusive<WorkDccl>(op, std::move(outputs), cuda);
+        auto work = c10::make_intrusive<WorkDccl>(op, std::move(outputs), cuda, comm_);
         if (!cuda) {
             check(fn(nullptr), "host collective");
             work->launched(nullptr);

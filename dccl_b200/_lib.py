@@ -108,6 +108,7 @@ def _declare(lib):
         "dccl_emu_set_guard": (None, [i]),
         "dccl_emu_set_mix": (i, [cp]),
         "dccl_emu_set_switch_form": (None, [i]),
+        "dccl_emu_set_p2p_rendezvous": (None, [i]),
         "dccl_emu_set_pipe": (None, [sz, i]),
         "dccl_emu_declare_stage_bytes": (i, [sz]),
     }

@@ -15,6 +15,8 @@ extern "C" void dccl_emu_set_device_seq(int);
 extern "C" void dccl_emu_set_switch_form(int);
 extern "C" int dccl_emu_set_mix(const char*);
 extern "C" int dccl_emu_all_to_all(int, size_t, int, int, const void*, void*);
+extern "C" void dccl_emu_set_p2p_rendezvous(int);
+extern "C" void dccl_emu_set_pipe(size_t, int);
 
 static int run_one(const char* kind, const char* algo, int n, size_t count, int in_place, size_t misalign) {
     size_t in_e = !strcmp(kind, "reducescatter") ? count * n : count, out_e = !strcmp(kind, "allgather") ? count * n : count;
@@ -94,5 +96,25 @@ int main(int argc, char** argv) {
         printf("all_to_all rc=%d\n", arc);
         bad += arc != 0;
     }
+    // large messages as rendezvous messages: stored straight into the receiver's buffer, through the FIFO after the
+    // rendezvous, and both in one launch; then small messages again, which need the credit the direct messages returned
+    for (int mode = 1; mode <= 3; mode++) {
+        dccl_emu_set_p2p_rendezvous(mode);
+        const size_t mb = (2u << 20) + 4096;
+        std::vector<unsigned char> rin(n * 2 * mb), rout(n * 2 * mb);
+        for (size_t i = 0; i < rin.size(); i++) rin[i] = (unsigned char)(i * 11);
+        const int r1 = dccl_emu_sendrecv_ring(n, mb, 2, 3, 3, rin.data(), rout.data());
+        const int r2 = dccl_emu_all_to_all(n, (1u << 20) + 64, 2, 2, rin.data(), rout.data());
+        printf("rendezvous mode %d: sendrecv rc=%d all_to_all rc=%d\n", mode, r1, r2);
+        bad += (r1 != 0) + (r2 != 0);
+    }
+    dccl_emu_set_p2p_rendezvous(0);
+    // the pipelined switch forms with many small chunks and a switch group of its own size
+    dccl_emu_set_switch_form(1);
+    dccl_emu_set_pipe(4096, 2);
+    bad += run_one("allreduce", "nvls", 4, 50001, 0, 0);
+    bad += run_one("reducescatter", "nvls", 4, 20001, 0, 4);
+    dccl_emu_set_pipe(8u << 20, 0);
+    dccl_emu_set_switch_form(0);
     return bad + (rc != 0);
 }

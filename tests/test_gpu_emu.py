@@ -427,3 +427,38 @@ def test_all_to_all_as_grouped_send_recv(dccl_lib, n, ctas):
         for r in range(n):
             for p in range(n):
                 assert np.array_equal(got[r, p], src[p, r]), (n, nbytes, r, p)
+
+
+@pytest.mark.parametrize("mode", [1, 2, 3])
+def test_large_send_recv_meet_first_and_go_zero_copy_where_mapped(dccl_lib, mode):
+    """Messages of 512 KB and more are rendezvous messages: the receiver posts where its buffer lies, the sender stores
+    straight into it when it has that memory mapped (mode 1), falls back to the FIFO when it has not (mode 2), and both
+    happen in one launch (mode 3: only even ranks' buffers are mapped). Small messages between them keep using the FIFO,
+    whose chunk numbers and credit must stay consistent across the direct messages; several rounds, windows of messages
+    per peer, sizes that are not whole chunks."""
+    dccl_lib.dccl_emu_set_p2p_rendezvous(mode)
+    try:
+        for n, window, ctas in [(2, 1, 4), (4, 2, 3), (8, 1, 2), (3, 3, 2)]:
+            for nbytes in [(512 << 10), (1 << 20) + 40, (5 << 20) + 8, 1000]:
+                if window > 1 and nbytes > (2 << 20):
+                    continue
+                hin = np.random.default_rng(nbytes + n + mode).integers(0, 256, n * window * nbytes, dtype=np.uint8)
+                hout = np.zeros_like(hin)
+                rc = dccl_lib.dccl_emu_sendrecv_ring(n, nbytes, window, ctas, 4, hin.ctypes.data, hout.ctypes.data)
+                assert rc == 0, (mode, n, window, nbytes, rc)
+                a, b = hin.reshape(n, window * nbytes), hout.reshape(n, window * nbytes)
+                for r in range(n):
+                    assert np.array_equal(b[r], a[(r - 1) % n]), (mode, n, window, nbytes, r)
+        # the launch an all-to-all is made of: 2 (n - 1) operations per rank, more receive buffers than the table of mappings holds
+        for n, ctas in [(4, 3), (8, 1)]:
+            for nbytes in [(1 << 20) + 24, (600 << 10)]:
+                hin = np.random.default_rng(nbytes + n).integers(0, 255, size=n * n * nbytes, dtype=np.uint8)
+                hout = np.zeros_like(hin)
+                rc = dccl_lib.dccl_emu_all_to_all(n, nbytes, ctas, 3, hin.ctypes.data, hout.ctypes.data)
+                assert rc == 0, (mode, n, nbytes, rc)
+                src, got = hin.reshape(n, n, nbytes), hout.reshape(n, n, nbytes)
+                for r in range(n):
+                    for p in range(n):
+                        assert np.array_equal(got[r, p], src[p, r]), (mode, n, nbytes, r, p)
+    finally:
+        dccl_lib.dccl_emu_set_p2p_rendezvous(0)

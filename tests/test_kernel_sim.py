@@ -95,6 +95,6 @@ def test_thread_sanitizer_finds_no_unordered_access_between_ranks(tmp_path):
     assert run.returncode == 0, run.stdout[-2000:] + run.stderr[-3000:]
     assert "sendrecv rc=0" in run.stdout
     locations = [l.strip() for l in run.stderr.splitlines() if l.strip().startswith("Location is")]
-    other = [l for l in locations if not ("::s_ok'" in l or "::s_fail'" in l)]
+    other = [l for l in locations if not ("::s_ok'" in l or "::s_fail'" in l or "::s_fine'" in l)]
     assert not other, "accesses that the protocol does not order:\n" + "\n".join(other[:10]) + "\n" + run.stderr[-4000:]
     assert run.stderr.count("WARNING: ThreadSanitizer") == len(locations), run.stderr[-4000:]

@@ -133,7 +133,8 @@ def test_tuner_table_and_file_override(dccl_lib):
     # two ranks: rows for an exact world size come before the wildcard rows
     assert choose("allreduce_sym", 2, 1 << 30) == ("twoshot", 128) and choose("allreduce", 2, 1 << 24) == ("twoshot", 128)
     assert choose("allreduce", 2, 50000)[0] == "oneshot" and choose("allreduce", 2, 300000)[0] == "twoshot_ll"
-    assert choose("allreduce", 4, 1 << 30)[0] == "nvls"
+    assert choose("allreduce", 4, 1 << 30)[0] == "twoshot" and choose("allreduce_sym", 4, 1 << 30) == ("nvls", 16)
+    assert choose("allreduce", 4, 1 << 20)[0] == "twoshot_ll" and choose("allreduce", 6, 1 << 30)[0] == "nvls"
     assert choose("reducescatter_sym", 8, 1 << 30) == ("nvls", 64) and choose("reducescatter", 8, 1 << 30)[0] == "twoshot"
     assert dccl_lib.dccl_tuner_choose(b"bogus", 8, 1, 1, algo, 32, ctypes.byref(ctas)) == -1
     text = b"# my table\nallreduce 8 4k ring 4\nallreduce * inf rabenseifner 12\nnot a rule\nallreduce 8 1m twoshot 999\n"

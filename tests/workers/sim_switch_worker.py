@@ -52,7 +52,7 @@ def main():
     # the pipelined forms with many chunks (4 KB each: up to 24 per call), other group sizes, in place and unaligned
     L.dccl_emu_set_switch_form(1)
     try:
-        for chunk, nv, ctas in ((4096, 2, 7), (16384, 1, 12), (4096, 3, 5)):
+        for chunk, nv, ctas in ((4096, 2, 7), (16384, 1, 12), (4096, 303, 9), (8192, 104, 11)):     # 303: three teams of one
             L.dccl_emu_set_pipe(chunk, nv)
             for n in (2, 5, 8):
                 for kind in ("allreduce", "reducescatter"):
