@@ -13,6 +13,7 @@ repeat the command that made the capture, so that the summary can be kept next t
 import argparse
 import csv
 import io
+import os
 import subprocess
 import sys
 
@@ -97,7 +98,7 @@ def main(argv=None):
     if args.command:
         print("# Plain run first (exit 0), then:")
         print("#   " + args.command)
-    print("# Read with: ncu -i %s --page raw --csv (this file: python benchmarks/ncu_summary.py)" % args.report)
+    print("# Read with: ncu -i %s --page raw --csv (this file: python benchmarks/ncu_summary.py)" % os.path.basename(args.report))
     for i, (name, rec) in enumerate(launches):
         if args.launch >= 0 and i != args.launch:
             continue

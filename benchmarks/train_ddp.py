@@ -38,6 +38,8 @@ def main():
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--seq", type=int, default=2048)
     ap.add_argument("--bucket-mb", type=int, default=25)
+    ap.add_argument("--plain-buckets", action="store_true",
+                    help="dccl_ddp: leave DDP's gradient buckets in ordinary memory (default: they come from a memory pool of symmetric memory)")
     args = ap.parse_args()
     rank, world, local = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1)), int(os.environ.get("LOCAL_RANK", 0))
     torch.cuda.set_device(local)
@@ -66,7 +68,14 @@ def main():
             comm.bind_device(local)
         else:
             dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
-        ddp = torch.nn.parallel.DistributedDataParallel(model, device_ids=[local], bucket_cap_mb=args.bucket_mb, gradient_as_bucket_view=True)
+        if args.backend == "dccl_ddp" and not args.plain_buckets and world > 1:
+            # DDP allocates its gradient buckets while it is constructed: inside the pool they become symmetric memory,
+            # which the switch reduces in place
+            pool = comm.symmetric_mem_pool()
+            with torch.cuda.use_mem_pool(pool):
+                ddp = torch.nn.parallel.DistributedDataParallel(model, device_ids=[local], bucket_cap_mb=args.bucket_mb, gradient_as_bucket_view=True)
+        else:
+            ddp = torch.nn.parallel.DistributedDataParallel(model, device_ids=[local], bucket_cap_mb=args.bucket_mb, gradient_as_bucket_view=True)
         if args.backend == "dccl_ddp":
             register_ddp_hook(ddp, comm, dev)
         net = ddp

@@ -3,6 +3,7 @@
  * package binds these). Every function returns the ncclResult_t value as int;
  * C++ exceptions (a null communicator) become ncclInvalidArgument.
  */
+#include <atomic>
 #include <vector>
 #include <dccl/dccl.hpp>
 #include "../core/config.hpp"
@@ -117,6 +118,27 @@ int dccl_set_algorithm(void* comm, const char* coll, const char* name) { GUARD(d
 const char* dccl_last_algorithm(void* comm, const char* coll) {
     try { return dcclGetLastAlgorithm((ncclComm_t)comm, coll); } catch (...) { return ""; }
 }
+
+/* ---- allocator hook for framework memory pools ----
+ * torch.cuda.memory.CUDAPluggableAllocator loads two functions by name from a shared library and torch.cuda.MemPool
+ * routes the allocations made inside `use_mem_pool` to them. dccl_pool_alloc serves them with dcclMemAlloc on the
+ * communicator bound with dccl_pool_bind, so tensors created there (DDP's gradient buckets, activations that are reduced
+ * every step) live in symmetric, multicast-bound memory and collectives on them run zero-copy through the switch, with
+ * no change to the code that allocates them. dcclMemAlloc is collective: every rank must make the same allocations in
+ * the same order inside the pool (ranks that build the same model do). dccl_pool_free only retires the segment; the
+ * memory is unmapped when the communicator is finalized, because the framework may free segments in an order that
+ * differs between ranks and a collective free would then hang.
+ */
+static std::atomic<dcclComm*> g_pool_comm{nullptr};
+void dccl_pool_bind(void* comm) { g_pool_comm.store((dcclComm*)comm); }
+void* dccl_pool_alloc(ssize_t size, int device, void* stream) {
+    (void)device; (void)stream;
+    dcclComm* c = g_pool_comm.load();
+    void* p = nullptr;
+    if (!c || size <= 0 || dcclMemAlloc(c, &p, (size_t)size) != ncclSuccess) return nullptr;
+    return p;
+}
+void dccl_pool_free(void* ptr, ssize_t size, int device, void* stream) { (void)ptr; (void)size; (void)device; (void)stream; }
 
 /**
  * Self test of the exchange board (Bootstrap::fast_allgather): `rounds` all-gathers of a message whose bytes depend on

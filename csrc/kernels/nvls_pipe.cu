@@ -169,8 +169,9 @@ __global__ void __launch_bounds__(512) k_nvls_pipe(const __grid_constant__ CollA
 }
 
 size_t nvls_pipe_capacity(size_t es, size_t stage_bytes, int nranks, bool reduce_scatter) {
-    // the whole message (plus rounding of the last vector) sits in one staging half
-    const size_t elems = (stage_bytes / es / 64) * 64 - 64;
+    // the whole message sits in one staging half; chunk and shard boundaries are rounded up to whole vectors, which a
+    // capacity that is itself a multiple of 64 elements always leaves room for
+    const size_t elems = (stage_bytes / es / 64) * 64;
     return reduce_scatter ? (elems / (size_t)nranks / 64) * 64 : elems;
 }
 

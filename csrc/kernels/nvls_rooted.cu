@@ -8,11 +8,16 @@
  * into chunks and the local copies of one chunk run while the switch works on
  * the next, in ONE launch:
  *
- *   broadcast  root CTA g:   multimem.st chunk k (its sub-range) to all ranks, signal row g of every rank
- *              other ranks:  CTA g waits for the root's signal k, copies chunk k from staging to the user buffer
- *   reduce     every rank, CTA g (first half of the grid): copy chunk k into staging, signal row g of the root
- *              root, CTA G+g (second half):                wait for signal k of every rank,
- *                                                          multimem.ld_reduce chunk k into the user buffer
+ *   broadcast  root CTA g:   multimem.st its part of chunk k to all ranks, signal row g of every rank
+ *              other ranks:  CTA g waits for the root CTAs that pushed chunk k, copies its slice of the chunk
+ *                            from staging to the user buffer
+ *   reduce     every rank, CTA g (first half of the grid): copy its slice of chunk k into staging, signal row g of the root
+ *              root, CTA G+g (second half):                wait for the copies of chunk k of every rank,
+ *                                                          multimem.ld_reduce its part of the chunk into the user buffer
+ *
+ * The CTAs that talk to the switch (the root's) form two teams that take the chunks in turn: between two chunks such
+ * a CTA has dead time (its multicast stores must have landed everywhere before it may signal, and the first accesses of
+ * the next chunk take a round trip through the switch), during which the other team keeps the links busy.
  *
  * The whole message sits in one staging half, so no byte of it is reused within
  * a launch and the hand-over needs no back pressure. The side that waits for
@@ -64,17 +69,23 @@ __device__ __forceinline__ void nvls_rooted_body(const CollArgs& a, const Ctx& x
     const bool second = reduce && x.bid >= G;
     const int g = second ? x.bid - G : x.bid;
     if (reduce && (x.bid >= 2 * G || (second && r != root))) return;
+    // the CTAs that use the switch (root of a broadcast, second group of a reduce) work in P teams: CTA g belongs to
+    // team g % P, which takes the chunks k with k % P == g % P
+    const int P = G >= 2 ? 2 : 1;
+    const int team_of_g = g % P, gi = g / P, team_size = (G - team_of_g + P - 1) / P;
     // entry announcement; the root's second group shares rows with its first and leaves it to that one
     if (!second && (int)threadIdx.x < n && (int)threadIdx.x != r) signal_peer(c, (int)threadIdx.x, g, x.seq, 0);
 
     for (int k = 0; k < nchunks; k++) {
         const size_t base = (size_t)k * chunk;
         const size_t cnt = base >= a.count ? 0 : (a.count - base < chunk ? a.count - base : chunk);
-        const Geometry<T> geo(GEO_WHOLE, cnt, 1, g, G);
-        const size_t lo = geo.blo < cnt ? geo.blo : cnt, hi = geo.bhi < cnt ? geo.bhi : cnt;
-        const size_t off = base + lo;
+        // a copy CTA's slice of the chunk (1/G), and a switch CTA's part of it (1/team size)
+        const Geometry<T> whole(GEO_WHOLE, cnt, 1, g, G), part(GEO_WHOLE, cnt, 1, gi, team_size);
+        const bool mine = k % P == team_of_g;
         if (!reduce) {
             if (r == root) {
+                if (!mine) continue;
+                const size_t lo = part.blo < cnt ? part.blo : cnt, hi = part.bhi < cnt ? part.bhi : cnt, off = base + lo;
                 if (hi > lo) {
                     const T* src = send + off;
                     if (aligned16(src)) nvls_push(mc_stage + off * ES, reinterpret_cast<const char*>(src), vecs(hi - lo));
@@ -88,18 +99,32 @@ __device__ __forceinline__ void nvls_rooted_body(const CollArgs& a, const Ctx& x
                 __syncthreads();
                 if ((int)threadIdx.x < n) signal_peer(c, (int)threadIdx.x, g, x.seq, k + 1);
             } else {
-                if (!cta_wait_peer(c, root, g, x.seq, k + 1, 580)) return;
+                // the root CTAs of the team that pushed chunk k: rows k % P, k % P + P, ...
+                const int t0 = k % P, rows = (G - t0 + P - 1) / P;
+                if (threadIdx.x == 0) s_fail = 0;
+                __syncthreads();
+                for (int t = (int)threadIdx.x; t < rows; t += (int)blockDim.x)
+                    if (!wait_peer(c, root, t0 + t * P, x.seq, k + 1, 580)) s_fail = 1;
+                __syncthreads();
+                if (s_fail) return;
+                const size_t lo = whole.blo < cnt ? whole.blo : cnt, hi = whole.bhi < cnt ? whole.bhi : cnt, off = base + lo;
                 if (hi > lo) copy_range<T>(recv + off, my_stage + off, hi - lo);
+                __syncthreads();
             }
         } else if (!second) {
+            const size_t lo = whole.blo < cnt ? whole.blo : cnt, hi = whole.bhi < cnt ? whole.bhi : cnt, off = base + lo;
             if (hi > lo) copy_range<T>(my_stage + off, send + off, hi - lo);
             cta_signal_peer(c, root, g, x.seq, k + 1);
         } else {
+            if (!mine) continue;
             if (threadIdx.x == 0) s_fail = 0;
             __syncthreads();
-            if ((int)threadIdx.x < n && !wait_peer(c, (int)threadIdx.x, g, x.seq, k + 1, 590)) s_fail = 1;
+            // every copy CTA of every rank has brought its slice of chunk k
+            for (int t = (int)threadIdx.x; t < n * G; t += (int)blockDim.x)
+                if (!wait_peer(c, t % n, t / n, x.seq, k + 1, 590)) s_fail = 1;
             __syncthreads();
             if (s_fail) return;
+            const size_t lo = part.blo < cnt ? part.blo : cnt, hi = part.bhi < cnt ? part.bhi : cnt, off = base + lo;
             if (hi > lo) {
                 char* dst = reinterpret_cast<char*>(recv + off);
                 if (aligned16(dst)) nvls_pass<T, OP>(mc_stage + off * ES, nullptr, dst, vecs(hi - lo), (hi - lo) * ES, avg, n, a.unroll);

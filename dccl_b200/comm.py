@@ -240,6 +240,19 @@ class Communicator:
     def free_symmetric(self, t):
         self.mem_free(t._dccl_ptr)
 
+    def symmetric_mem_pool(self):
+        """A ``torch.cuda.MemPool`` whose memory is symmetric (``dcclMemAlloc``): tensors created inside
+        ``with torch.cuda.use_mem_pool(pool):`` (DDP's gradient buckets, activations that are reduced every step) are
+        mapped by every rank and bound to the switch, so collectives on them run zero-copy without the code that
+        allocates them knowing. Every rank must make the same allocations in the same order inside the pool. The memory
+        is returned when the communicator is finalized. One communicator per process can serve pools at a time."""
+        from . import _lib
+        torch = _torch()
+        lib().dccl_pool_bind(self._h)
+        path = os.environ.get("DCCL_LIBRARY") or _lib.LIB_PATH
+        self._pool_allocator = torch.cuda.memory.CUDAPluggableAllocator(path, "dccl_pool_alloc", "dccl_pool_free")
+        return torch.cuda.MemPool(self._pool_allocator.allocator())
+
     # -- collectives --------------------------------------------------
     def all_reduce(self, send, recv=None, op="sum", stream=None):
         recv = send if recv is None else recv

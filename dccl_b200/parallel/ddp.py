@@ -124,18 +124,22 @@ class _HookState:
     def __init__(self, comm, device):
         self.comm = comm
         self.stream = torch.cuda.Stream(device=device, priority=-1)
+        self.events = {}          # one "gradients of this bucket are ready" event per bucket, made once
 
 
 def _ddp_hook(state, bucket):
     buf = bucket.buffer()
     fut = torch.futures.Future(devices=[buf.device])
-    ready = torch.cuda.Event()
+    ready = state.events.get(bucket.index())
+    if ready is None:
+        ready = state.events[bucket.index()] = torch.cuda.Event()
     ready.record()
     state.stream.wait_event(ready)
     with torch.cuda.stream(state.stream):
         state.comm.all_reduce(buf, op="avg", stream=state.stream)
-        buf.record_stream(state.stream)
-        fut.set_result(buf)      # the future records the side stream; DDP waits on it before using the bucket
+        # The future keeps the bucket alive and records the side stream; DDP waits on it before it uses the bucket,
+        # and the bucket is DDP's own long-lived buffer, so the allocator needs no note about the side stream.
+        fut.set_result(buf)
     return fut
 
 
