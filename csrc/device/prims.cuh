@@ -49,7 +49,8 @@ static_assert(kLL2Off + 2 * kMaxPeers * 2 * kLL2PhaseBytes <= kStageOff, "second
 
 /* ---- status block (pinned host memory, or device memory in single-GPU emulation) ---- */
 enum : uint32_t { ST_CODE = 0, ST_PEER = 1, ST_SITE = 2, ST_SEQ = 3, ST_KERNEL = 4, ST_WORDS = 8 };
-enum : uint32_t { DEV_OK = 0, DEV_TIMEOUT = 1, DEV_ABORTED = 2, DEV_BOUNDS = 3 };
+enum : uint32_t { DEV_OK = 0, DEV_TIMEOUT = 1, DEV_ABORTED = 2, DEV_BOUNDS = 3,
+                  DEV_MISMATCH = 4 };   // the two ends of a send / recv were launched with different CTA counts per operation
 
 /** What a kernel needs to know about the communicator; passed by value. */
 struct DevComm {
@@ -265,10 +266,12 @@ __device__ __forceinline__ bool wait_flag_ge(const DevComm& c, const uint32_t* p
     return true;
 }
 
-__device__ __forceinline__ bool wait_flag64_ge(const DevComm& c, const unsigned long long* p, unsigned long long val, int peer, int site, uint32_t seq) {
+/** `mask` selects the bits that count (a word may carry other information above its counter). */
+__device__ __forceinline__ bool wait_flag64_ge(const DevComm& c, const unsigned long long* p, unsigned long long val, int peer, int site, uint32_t seq,
+                                               unsigned long long mask = ~0ull) {
     uint32_t spins = 0;
     unsigned long long t0 = 0;
-    while (ld_acquire_sys64(p) < val) {
+    while ((ld_acquire_sys64(p) & mask) < val) {
         if ((++spins & 0xffu) == 0) {
             unsigned long long now = global_timer_ns();
             if (t0 == 0) t0 = now;

@@ -51,6 +51,7 @@ uint64_t GpuCommImpl::stat(const char* name) const {
     const std::string k(name ? name : "");
     if (k == "launches") return launches_;
     if (k == "zero_copy_calls") return zero_copy_calls_;
+    if (k == "symmetric_calls") return symmetric_calls_;
     return 0;
 }
 
@@ -170,6 +171,7 @@ ncclResult_t GpuCommImpl::all_reduce(const void* send, void* recv, size_t count,
         a.count = count;
         NEXT_SEQ(a);
         launches_++;
+        symmetric_calls_++;
         return cuda_result(launch_nvls(a, dt, cfg), "nvls all-reduce (symmetric)");
     }
 
@@ -277,6 +279,7 @@ ncclResult_t GpuCommImpl::reduce_scatter(const void* send, void* recv, size_t re
             a.count = recvcount;
             NEXT_SEQ(a);
             launches_++;
+        symmetric_calls_++;
             return cuda_result(launch_nvls(a, dt, cfg), "nvls reduce-scatter (symmetric)");
         }
     }
@@ -358,6 +361,7 @@ ncclResult_t GpuCommImpl::all_gather(const void* send, void* recv, size_t sendco
             a.count = sendcount;
             NEXT_SEQ(a);
             launches_++;
+        symmetric_calls_++;
             return cuda_result(launch_nvls(a, dt, cfg), "nvls all-gather (symmetric)");
         }
     }
@@ -427,6 +431,7 @@ ncclResult_t GpuCommImpl::broadcast(const void* send, void* recv, size_t count, 
             a.count = count;
             NEXT_SEQ(a);
             launches_++;
+        symmetric_calls_++;
             return cuda_result(launch_nvls(a, dt, cfg), "nvls broadcast (symmetric)");
         }
     }

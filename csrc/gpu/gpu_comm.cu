@@ -290,11 +290,14 @@ ncclResult_t GpuCommImpl::async_error(char* msg, size_t len) {
     sticky_error_ = true;
     if (msg && len && code == DEV_BOUNDS)
         snprintf(msg, len, "a range check failed in a kernel of rank %u (site %u, value %u)", st[ST_PEER], st[ST_SITE], st[ST_SEQ]);
+    else if (msg && len && code == DEV_MISMATCH)
+        snprintf(msg, len, "send / recv with rank %u: the sender used %u CTAs per operation, this rank another number "
+                           "(p2p_ctas, or the operations of a group, differ between the ranks)", st[ST_PEER], st[ST_SEQ]);
     else if (msg && len) {
         const char* what = code == DEV_TIMEOUT ? "timed out waiting for" : code == DEV_ABORTED ? "gave up (abort) waiting for" : "failed on";
         snprintf(msg, len, "a kernel %s rank %u (site %u, call %u)", what, st[ST_PEER], st[ST_SITE], st[ST_SEQ]);
     }
-    return code == DEV_BOUNDS ? ncclInternalError : ncclRemoteError;
+    return code == DEV_BOUNDS ? ncclInternalError : code == DEV_MISMATCH ? ncclInvalidUsage : ncclRemoteError;
 }
 
 void GpuCommImpl::abort(int failed_rank) {

@@ -84,7 +84,7 @@ public:
     virtual bool set_param(const char* name, int value) = 0;
     /** Kernels launched by this communicator so far. */
     virtual uint64_t launches() const = 0;
-    /** Counters: "launches", "zero_copy_calls" (calls served straight out of / into user memory by the peer kernels). */
+    /** Counters: "launches", "zero_copy_calls", "symmetric_calls" (calls served straight out of / into user memory by the peer kernels). */
     virtual uint64_t stat(const char* name) const = 0;
 };
 

@@ -158,6 +158,7 @@ private:
     size_t auto_min_bytes_ = 4u << 20;          // lazy registration serves calls from this size on (0: never)
     bool direct_rs_ = true;                     // reduce-scatter on addressable buffers: zero-copy pull, from direct_rs_min_bytes_ on
     size_t direct_rs_min_bytes_ = 32u << 20;    // (two ranks: from the lazy-registration threshold on)
+    uint64_t symmetric_calls_ = 0;              // calls that the switch served in place on symmetric (dcclMemAlloc) buffers
     uint64_t zero_copy_calls_ = 0;              // calls served straight out of / into user memory by peer kernels
     unsigned long long sent_chunks_[kMaxPeers], recv_chunks_[kMaxPeers];
     unsigned long long sent_rdv_[kMaxPeers] = {0}, recv_rdv_[kMaxPeers] = {0};   // large (rendezvous) messages per peer and direction

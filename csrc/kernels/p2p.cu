@@ -174,10 +174,21 @@ __global__ void __launch_bounds__(512) k_p2p(const __grid_constant__ P2pArgs a) 
             if (hi > lo) copy_bytes(p2p_fifo(c.pool[peer], r, G) + lo, op.buf + coff + lo, hi - lo);
             __syncthreads();
             if (threadIdx.x == 0) {
-                st_release_sys64(p2p_head(c.pool[peer], r, G, b), G + 1);
+                // the head word carries, above the chunk number, how many CTAs serve this operation here: both ends cut a
+                // chunk by that number, and the receiver checks that they agree
+                st_release_sys64(p2p_head(c.pool[peer], r, G, b), (G + 1) | ((unsigned long long)B << 56));
             }
         } else {
-            if (threadIdx.x == 0) s_ok = wait_flag64_ge(c, p2p_head(c.pool[r], peer, G, b), G + 1, peer, 810, 0) ? 1 : 0;
+            if (threadIdx.x == 0) {
+                const unsigned long long* hp = p2p_head(c.pool[r], peer, G, b);
+                s_ok = wait_flag64_ge(c, hp, G + 1, peer, 810, 0, (1ull << 56) - 1) ? 1 : 0;
+                if (s_ok && (int)(ld_acquire_sys64(hp) >> 56) != B) {
+                    // the sender cut this chunk for another number of CTAs (p2p_ctas or the shape of a group differs
+                    // between the ranks): the bytes of this CTA's part may not be there. Say so instead of copying.
+                    report_failure(c, DEV_MISMATCH, peer, 811, (uint32_t)(ld_acquire_sys64(hp) >> 56));
+                    s_ok = 0;
+                }
+            }
             __syncthreads();
             if (!s_ok) return;
             if (hi > lo) copy_bytes(op.buf + coff + lo, p2p_fifo(c.pool[r], peer, G) + lo, hi - lo);

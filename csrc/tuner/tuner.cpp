@@ -15,8 +15,11 @@ static const size_t kInf = ~(size_t)0;
  * all-gather. */
 static const TuneRule kBuiltin[] = {
     // Measured on 8 x B200 (bf16 sum; sweep of every variant x CTA count, best per size bucket).
-    // all-reduce, ordinary buffers: packets while latency bound, then the switch variant through staging
-    {COLL_ALLREDUCE, 0, 128u << 10, ALGO_ONESHOT, 8},
+    // all-reduce, ordinary buffers: packets while latency bound (8-15 us to 64 KB), the two-shot packet form to 2 MB
+    // (16.5-23 us where the staged switch form and NCCL take 28-32), then the switch through staging, pipelined from
+    // 16 MB on (634 / 765 / 768 GB/s at 64 MB / 256 MB / 1 GB against 428 / 657 / 727 for NCCL)
+    {COLL_ALLREDUCE, 0, 64u << 10, ALGO_ONESHOT, 8},
+    {COLL_ALLREDUCE, 0, 2u << 20, ALGO_TWOSHOT_LL, 32},
     {COLL_ALLREDUCE, 0, 8u << 20, ALGO_NVLS, 64},
     {COLL_ALLREDUCE, 0, kInf, ALGO_NVLS, 128},
     // two ranks (measured on 2 x B200): the switch fetches the local copy over NVLink as well, so the peer-to-peer
@@ -52,14 +55,17 @@ static const TuneRule kBuiltin[] = {
     {COLL_REDUCESCATTER, 0, 256u << 10, ALGO_ONESHOT, 8},
     {COLL_REDUCESCATTER, 0, 1u << 20, ALGO_TWOSHOT, 32},
     {COLL_REDUCESCATTER, 0, kInf, ALGO_TWOSHOT, 128},
+    {COLL_ALLGATHER, 2, 64u << 10, ALGO_ONESHOT, 8},
+    {COLL_ALLGATHER, 2, 8u << 20, ALGO_NVLS, 128},
+    {COLL_ALLGATHER, 2, kInf, ALGO_TWOSHOT, 128},
     {COLL_ALLGATHER, 0, 256u << 10, ALGO_ONESHOT, 8},
     {COLL_ALLGATHER, 0, 1u << 20, ALGO_NVLS, 32},
-    {COLL_ALLGATHER, 0, 8u << 20, ALGO_NVLS, 128},
+    {COLL_ALLGATHER, 0, 16u << 20, ALGO_NVLS, 128},       // 16 MB: 40 us through the switch, 47 by peer loads
     {COLL_ALLGATHER, 0, kInf, ALGO_TWOSHOT, 128},
     {COLL_BROADCAST, 0, 256u << 10, ALGO_ONESHOT, 16},
     {COLL_BROADCAST, 0, kInf, ALGO_NVLS, 64},
     {COLL_REDUCE, 0, 64u << 10, ALGO_ONESHOT, 8},
-    {COLL_REDUCE, 0, 1u << 20, ALGO_TWOSHOT, 32},
+    {COLL_REDUCE, 0, 2u << 20, ALGO_TWOSHOT_LL, 32},       // folded shards to the root as packets: no barrier (the staged form has two)
     {COLL_REDUCE, 0, kInf, ALGO_NVLS, 128},
 };
 

@@ -195,7 +195,7 @@ class Communicator:
         _check(lib().dccl_debug_check(self._h), "dcclDebugCheck")
 
     def stat(self, name):
-        """A counter of the device side: "launches", "zero_copy_calls" (calls that the peer kernels served straight out
+        """A counter of the device side: "launches", "zero_copy_calls", "symmetric_calls" (calls that the peer kernels served straight out
         of / into user memory: symmetric, registered or lazily registered buffers)."""
         return int(lib().dccl_comm_stat(self._h, name.encode()))
 

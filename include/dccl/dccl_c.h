@@ -35,7 +35,7 @@ const char* dccl_error_string(int result);
 int dccl_has_multicast(void* comm);
 unsigned long long dccl_launch_count(void* comm);
 int dccl_comm_set_param(void* comm, const char* name, int value);
-/* counters of a communicator's device side: "launches", "zero_copy_calls" */
+/* counters of a communicator's device side: "launches", "zero_copy_calls", "symmetric_calls" */
 unsigned long long dccl_comm_stat(void* comm, const char* name);
 int dccl_cuda_device_count(void);
 int dccl_barrier(void* comm);                                       /* host-side barrier over the control plane */

@@ -40,6 +40,17 @@ def test_unregistered_buffers_are_mapped_on_first_use_and_alignment_is_a_group_d
 
 
 @pytest.mark.skipif(gpu_count() < 2, reason="needs two GPUs")
+def test_framework_memory_pool_hands_out_symmetric_memory_and_host_buffers_go_through_the_gpus():
+    """torch.cuda.MemPool over the library's allocator hook: tensors made inside the pool are reduced in place by the
+    switch; pinned host buffers are reduced by the chunked host -> device -> switch -> host helper."""
+    world = min(gpu_count(), 4)
+    res = python_ranks(os.path.join(HERE, "workers", "pool_worker.py"), [], world, timeout=600, gpus=True)
+    for r, p in enumerate(res):
+        assert p.returncode == 0, "rank %d:\n%s\n%s" % (r, p.stdout[-3000:], p.stderr[-3000:])
+        assert p.stdout.strip().splitlines()[-1].startswith("OK"), p.stdout
+
+
+@pytest.mark.skipif(gpu_count() < 2, reason="needs two GPUs")
 def test_messages_larger_than_staging_are_chunked():
     world = min(gpu_count(), 8)
     run(world, ["--suite", "chunk"], env={"DCCL_STAGING_BYTES": str(4 << 20)})
