@@ -57,6 +57,7 @@ int dccl_comm_bind_device(void* comm, int device) {
 }
 int dccl_has_multicast(void* comm) { dcclComm* c = (dcclComm*)comm; return c && c->gpu && c->gpu->has_multicast() ? 1 : 0; }
 unsigned long long dccl_launch_count(void* comm) { dcclComm* c = (dcclComm*)comm; return c && c->gpu ? c->gpu->launches() : 0ull; }
+int dccl_is_symmetric(void* comm, const void* p, size_t bytes) { dcclComm* c = (dcclComm*)comm; return c && c->gpu && c->gpu->is_symmetric(p, bytes) ? 1 : 0; }
 unsigned long long dccl_comm_stat(void* comm, const char* name) { dcclComm* c = (dcclComm*)comm; return c && c->gpu ? c->gpu->stat(name) : 0ull; }
 int dccl_comm_set_param(void* comm, const char* name, int value) { dcclComm* c = (dcclComm*)comm; return c && c->gpu && c->gpu->set_param(name, value) ? 0 : (int)ncclInvalidArgument; }
 int dccl_cuda_device_count() { return cuda_device_count(); }

@@ -100,6 +100,8 @@ struct CollArgs {
     int pipe_nv;           // pipelined switch kernels: CTAs of the switch group ...
     int pipe_copy;         // ... and of each copy group
     int pipe_teams;        // ... and how many teams the switch group forms (they take the chunks in turn)
+    int pipe_ring;         // ... chunk slots in a staging half
+    size_t pipe_chunk;     // ... and elements per chunk
 };
 
 struct Ctx {

@@ -352,9 +352,11 @@ int dccl_emu_collective(const char* kind_s, const char* algo_s, int nranks, int 
         a.op = op;
         a.root = root;
         // one launch of (collective, variant) on the buffers of this run; the arguments are a copy, the caller's stay as they are
+        uint32_t extra_seqs = 0;       // call numbers a launch used beyond its own (the pipelined switch forms)
         auto launch_one = [&](int coll, GpuAlgo algo, CollArgs a, size_t* cap_out) -> cudaError_t {
             cudaError_t e = cudaErrorInvalidValue;
             size_t cap = 0;
+            extra_seqs = 0;
 #ifdef DCCL_HOST_SIM
             if (algo == ALGO_NVLS) {
                 // the switch kernels on ordinary buffers (staged through the pool), played by the simulated multicast mapping
@@ -363,15 +365,16 @@ int dccl_emu_collective(const char* kind_s, const char* algo_s, int nranks, int 
                                                      dt != ncclInt8 && dt != ncclUint8);
                 if (!switch_op) e = cudaErrorInvalidValue;
                 else if (coll == COLL_ALLREDUCE && g_switch_form == 1) {
-                    cap = nvls_pipe_capacity(es, stage_bytes, nranks, false);
+                    // with host-counted sequence numbers the staging half is a ring and takes any length
+                    cap = g_device_seq ? nvls_pipe_capacity(es, stage_bytes, nranks, false) : count;
                     LaunchCfg pc = cfg;
                     pc.ctas = cfg.ctas < 3 ? 3 : cfg.ctas;
-                    if (count <= cap) e = launch_nvls_pipe(a, dt, pc, false, g_pipe_nv, g_pipe_teams);
+                    if (count <= cap) { e = launch_nvls_pipe(a, dt, pc, false, stage_bytes, g_pipe_nv, g_pipe_teams, g_device_seq != 0); extra_seqs = nvls_pipe_extra_seqs(count, es, stage_bytes, nranks, false, g_device_seq != 0); }
                 } else if (coll == COLL_REDUCESCATTER && g_switch_form == 1) {
-                    cap = nvls_pipe_capacity(es, stage_bytes, nranks, true);
+                    cap = g_device_seq ? nvls_pipe_capacity(es, stage_bytes, nranks, true) : count;
                     LaunchCfg pc = cfg;
                     pc.ctas = cfg.ctas < 2 ? 2 : cfg.ctas;
-                    if (count <= cap) e = launch_nvls_pipe(a, dt, pc, true, g_pipe_nv, g_pipe_teams);
+                    if (count <= cap) { e = launch_nvls_pipe(a, dt, pc, true, stage_bytes, g_pipe_nv, g_pipe_teams, g_device_seq != 0); extra_seqs = nvls_pipe_extra_seqs(count, es, stage_bytes, nranks, true, g_device_seq != 0); }
                 } else if ((coll == COLL_BROADCAST || coll == COLL_REDUCE) && g_switch_form == 2) {
                     a.mode = coll == COLL_BROADCAST ? ROOTED_BROADCAST : ROOTED_REDUCE;
                     cap = nvls_pipe_capacity(es, stage_bytes, nranks, false);
@@ -428,12 +431,13 @@ int dccl_emu_collective(const char* kind_s, const char* algo_s, int nranks, int 
             a.parity = (int)(a.seq & 1u);
             if (g_device_seq) { a.seq = 0x5eed0000u; a.parity = 0; }
             e = launch_one(g_mix[k].first, g_mix[k].second, a, &cap);
+            next_seq_no += extra_seqs;
             if (e == cudaSuccess && cudaDeviceSynchronize() != cudaSuccess) e = cudaErrorLaunchFailure;
         }
         a.seq = next_seq_no++;
         a.parity = (int)(a.seq & 1u);
         if (g_device_seq) { a.seq = 0x5eed0000u; a.parity = 0; }
-        if (e == cudaSuccess) e = launch_one(coll, algo, a, &cap);
+        if (e == cudaSuccess) { e = launch_one(coll, algo, a, &cap); next_seq_no += extra_seqs; }
         if (e != cudaSuccess) { fprintf(stderr, "dccl emulation: launch failed or count %zu above capacity %zu: %s\n", count, cap, cudaGetErrorString(e)); rc = -3; break; }
         if (cudaDeviceSynchronize() != cudaSuccess) { rc = fail("kernel"); break; }
         uint32_t st[ST_WORDS];

@@ -180,7 +180,7 @@ ncclResult_t GpuCommImpl::all_reduce(const void* send, void* recv, size_t count,
     if (pipe) cfg.ctas = pipe_ctas_ < sm_count_ ? pipe_ctas_ : sm_count_;
     size_t cap;
     switch (ch.algo) {
-    case ALGO_NVLS: cap = pipe ? nvls_pipe_capacity(es, stage_bytes_, n_, false) : nvls_capacity(NV_ALLREDUCE, n_, es, stage_bytes_); break;
+    case ALGO_NVLS: cap = !pipe ? nvls_capacity(NV_ALLREDUCE, n_, es, stage_bytes_) : device_seq_ ? nvls_pipe_capacity(es, stage_bytes_, n_, false) : count; break;
     case ALGO_RING: cap = ring_capacity(RING_ALLREDUCE, n_, es, stage_bytes_); break;
     case ALGO_RABENSEIFNER: cap = hd_capacity(n_, es, stage_bytes_); break;
     default: cap = twoshot_capacity(TS_ALLREDUCE, n_, es, stage_bytes_); break;
@@ -194,7 +194,12 @@ ncclResult_t GpuCommImpl::all_reduce(const void* send, void* recv, size_t count,
         cudaError_t e;
         switch (ch.algo) {
         case ALGO_NVLS:
-            if (pipe) { a.unroll = pipe_unroll_; e = launch_nvls_pipe(a, dt, cfg, false, pipe_nv_ctas_, pipe_teams_); }
+            if (pipe) {
+                a.unroll = pipe_unroll_;
+                e = launch_nvls_pipe(a, dt, cfg, false, stage_bytes_, pipe_nv_ctas_, pipe_teams_, device_seq_);
+                // chunk numbers beyond one call's flag values live in the following call numbers of the same parity
+                for (int k = nvls_pipe_extra_seqs(c, es, stage_bytes_, n_, false, device_seq_); k > 0; k--) seq_ = next_seq(seq_);
+            }
             else { a.mode = NV_ALLREDUCE; e = launch_nvls(a, dt, cfg); }
             break;
         case ALGO_RING: a.mode = RING_ALLREDUCE; e = launch_ring(a, dt, cfg); break;
@@ -292,7 +297,7 @@ ncclResult_t GpuCommImpl::reduce_scatter(const void* send, void* recv, size_t re
         const int nv = pipe_nv_ctas_ < total ? pipe_nv_ctas_ : total / 3;
         cfg.ctas = nv + (total - nv) / 2;
     }
-    size_t cap = pipe ? nvls_pipe_capacity(es, stage_bytes_, n_, true)
+    size_t cap = pipe ? (device_seq_ ? nvls_pipe_capacity(es, stage_bytes_, n_, true) : recvcount)
                  : ch.algo == ALGO_NVLS ? nvls_capacity(NV_REDUCESCATTER, n_, es, stage_bytes_)
                  : ch.algo == ALGO_RING ? ring_capacity(RING_REDUCESCATTER, n_, es, stage_bytes_)
                                         : twoshot_capacity(TS_REDUCESCATTER, n_, es, stage_bytes_);
@@ -303,7 +308,11 @@ ncclResult_t GpuCommImpl::reduce_scatter(const void* send, void* recv, size_t re
         a.count = c;
         NEXT_SEQ(a);
         cudaError_t e;
-        if (pipe) { a.unroll = pipe_unroll_; e = launch_nvls_pipe(a, dt, cfg, true, pipe_nv_ctas_, pipe_teams_); }
+        if (pipe) {
+            a.unroll = pipe_unroll_;
+            e = launch_nvls_pipe(a, dt, cfg, true, stage_bytes_, pipe_nv_ctas_, pipe_teams_, device_seq_);
+            for (int k = nvls_pipe_extra_seqs(c, es, stage_bytes_, n_, true, device_seq_); k > 0; k--) seq_ = next_seq(seq_);
+        }
         else if (ch.algo == ALGO_NVLS) { a.mode = NV_REDUCESCATTER; e = launch_nvls(a, dt, cfg); }
         else if (ch.algo == ALGO_RING) { a.mode = RING_REDUCESCATTER; e = launch_ring(a, dt, cfg); }
         else { a.mode = TS_REDUCESCATTER; e = launch_twoshot(a, dt, cfg); }

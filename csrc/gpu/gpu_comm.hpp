@@ -84,6 +84,8 @@ public:
     virtual bool set_param(const char* name, int value) = 0;
     /** Kernels launched by this communicator so far. */
     virtual uint64_t launches() const = 0;
+    /** True when [p, p + bytes) lies in symmetric memory of this communicator (dcclMemAlloc, or a memory pool served by it). */
+    virtual bool is_symmetric(const void* p, size_t bytes) const = 0;
     /** Counters: "launches", "zero_copy_calls", "symmetric_calls" (calls served straight out of / into user memory by the peer kernels). */
     virtual uint64_t stat(const char* name) const = 0;
 };

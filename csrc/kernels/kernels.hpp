@@ -50,12 +50,19 @@ size_t nvls_capacity(int mode, int nranks, size_t elem_size, size_t stage_bytes)
 cudaError_t launch_nvls(const CollArgs& a, ncclDataType_t dt, const LaunchCfg& cfg);
 
 /* nvls_pipe.cu: all-reduce / reduce-scatter of ordinary buffers with copy-in, switch pass and copy-out overlapped
- * chunk by chunk (reduce-scatter: count = per-rank elements, stride = slot distance in the send buffer) */
+ * chunk by chunk (reduce-scatter: count = per-rank elements, stride = slot distance in the send buffer). The staging
+ * half (stage_bytes) is a ring of chunk slots, so ONE launch takes a message of any length; chunk numbers beyond the flag
+ * values of one call use nvls_pipe_extra_seqs() further call numbers, which the caller must skip after the launch.
+ * nvls_pipe_capacity is the largest message that needs no further call numbers and no slot twice (the limit when
+ * sequence numbers are counted on the device). */
 size_t nvls_pipe_capacity(size_t elem_size, size_t stage_bytes, int nranks, bool reduce_scatter);
+int nvls_pipe_extra_seqs(size_t count, size_t elem_size, size_t stage_bytes, int nranks, bool reduce_scatter, bool single_seq = false);
 /** cfg.ctas is the whole grid; nv_ctas of it form the switch group (0: a fifth / a third of the grid), the rest is
  *  split evenly between copy-in and copy-out (all-reduce) or is the copy-in group (reduce-scatter). The switch CTAs
- *  form `teams` teams that take the chunks in turn. */
-cudaError_t launch_nvls_pipe(const CollArgs& a, ncclDataType_t dt, const LaunchCfg& cfg, bool reduce_scatter, int nv_ctas = 0, int teams = 2);
+ *  form `teams` teams that take the chunks in turn. single_seq: the message is at most nvls_pipe_capacity and must not
+ *  use further call numbers (sequence numbers counted on the device). */
+cudaError_t launch_nvls_pipe(const CollArgs& a, ncclDataType_t dt, const LaunchCfg& cfg, bool reduce_scatter, size_t stage_bytes, int nv_ctas = 0, int teams = 2,
+                             bool single_seq = false);
 /** Target chunk size of the pipeline (default 8 MB, at most 24 chunks per launch); a tuning knob, the same on every rank. */
 void nvls_pipe_set_chunk_bytes(size_t bytes);
 

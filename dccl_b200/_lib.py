@@ -67,6 +67,7 @@ def _declare(lib):
         "dccl_group_end": (i, []),
         "dccl_comm_stat": (c.c_ulonglong, [vp, cp]),
         "dccl_pool_bind": (None, [vp]),
+        "dccl_is_symmetric": (i, [vp, vp, sz]),
         "dccl_selftest_board": (i, [vp, i]),
         "dccl_set_algorithm": (i, [vp, cp, cp]),
         "dccl_last_algorithm": (cp, [vp, cp]),

@@ -240,6 +240,11 @@ class Communicator:
     def free_symmetric(self, t):
         self.mem_free(t._dccl_ptr)
 
+    def is_symmetric(self, t):
+        """True when the tensor lies in symmetric memory of this communicator (``symmetric_empty`` or a pool from
+        ``symmetric_mem_pool``): collectives on it need no staging copy and no registration."""
+        return bool(lib().dccl_is_symmetric(self._h, _addr(t), _numel(t) * t.element_size()))
+
     def symmetric_mem_pool(self):
         """A ``torch.cuda.MemPool`` whose memory is symmetric (``dcclMemAlloc``): tensors created inside
         ``with torch.cuda.use_mem_pool(pool):`` (DDP's gradient buckets, activations that are reduced every step) are

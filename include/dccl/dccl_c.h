@@ -37,6 +37,8 @@ unsigned long long dccl_launch_count(void* comm);
 int dccl_comm_set_param(void* comm, const char* name, int value);
 /* counters of a communicator's device side: "launches", "zero_copy_calls", "symmetric_calls" */
 unsigned long long dccl_comm_stat(void* comm, const char* name);
+/* 1 when [p, p + bytes) lies in symmetric memory of the communicator (dcclMemAlloc or a memory pool it serves) */
+int dccl_is_symmetric(void* comm, const void* p, size_t bytes);
 int dccl_cuda_device_count(void);
 int dccl_barrier(void* comm);                                       /* host-side barrier over the control plane */
 int dccl_debug_check(void* comm);                                   /* guard words of the device pool (DCCL_DEBUG_BOUNDS=1) */

@@ -114,7 +114,17 @@ int main(int argc, char** argv) {
     dccl_emu_set_pipe(4096, 2);
     bad += run_one("allreduce", "nvls", 4, 50001, 0, 0);
     bad += run_one("reducescatter", "nvls", 4, 20001, 0, 4);
-    dccl_emu_set_pipe(8u << 20, 0);
+    {   // a staging half of 64 KB under a 200 KB message: the chunk slots are reused as a ring, chunk numbers pass 24
+        std::vector<float> rin(4 * 50001), rout(4 * 50001);
+        for (size_t i = 0; i < rin.size(); i++) rin[i] = (float)(i % 89) * 0.5f;
+        const int r1 = dccl_emu_collective("allreduce", "nvls", 4, 7, 0, 50001, 0, 7, 0, 0, 2, 64 << 10, rin.data(), rout.data());
+        std::vector<float> sin(4 * 4 * 4099), sout(4 * 4099);
+        for (size_t i = 0; i < sin.size(); i++) sin[i] = (float)(i % 83) * 0.5f;
+        const int r2 = dccl_emu_collective("reducescatter", "nvls", 4, 7, 0, 4099, 0, 7, 0, 0, 2, 64 << 10, sin.data(), sout.data());
+        printf("pipeline ring: allreduce rc=%d reducescatter rc=%d\n", r1, r2);
+        bad += (r1 != 0) + (r2 != 0);
+    }
+    dccl_emu_set_pipe(16u << 20, 0);
     dccl_emu_set_switch_form(0);
     return bad + (rc != 0);
 }

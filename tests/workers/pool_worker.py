@@ -39,21 +39,22 @@ def main():
             ins = [oracle.make_input(name, count, seed=4000 + r) for r in range(world)]
             src = ins[rank].view(np.int16) if name == "bfloat16" else ins[rank]
             t.copy_(torch.from_numpy(src.copy()).view(t.dtype).to(dev))
-            s0 = comm.stat("symmetric_calls")
+            check(comm.is_symmetric(t), "a tensor from the pool lies in symmetric memory (%s)" % name)
+            s0 = comm.stat("symmetric_calls") + comm.stat("zero_copy_calls")
             comm.all_reduce(t, op="avg")
             torch.cuda.synchronize()
-            check(comm.stat("symmetric_calls") == s0 + 1, "a tensor from the pool is reduced in place by the switch (%s)" % name)
+            # in place by the switch, or (two ranks) by the zero-copy peer form: no staging either way
+            check(comm.stat("symmetric_calls") + comm.stat("zero_copy_calls") == s0 + 1, "a tensor from the pool is reduced where it lies (%s)" % name)
             got = t.cpu().view(torch.int16).numpy().view(np.uint16) if name == "bfloat16" else t.cpu().numpy()
             want = oracle.fold(ins, "avg", bf16=name == "bfloat16")
             rtol, atol = oracle.tolerances(name, world)
             g = oracle.bf16_to_f32(got) if name == "bfloat16" else got
             w = oracle.bf16_to_f32(want) if name == "bfloat16" else want
             check(np.allclose(g.astype(np.float64), w.astype(np.float64), rtol=rtol, atol=atol), "all_reduce of a pool tensor (%s)" % name)
-        s0 = comm.stat("symmetric_calls")
         outside.fill_(1.0)
         comm.all_reduce(outside, op="sum")
         torch.cuda.synchronize()
-        check(comm.stat("symmetric_calls") == s0 and bool((outside == float(world)).all()), "a tensor from the ordinary allocator is not")
+        check(not comm.is_symmetric(outside) and bool((outside == float(world)).all()), "a tensor from the ordinary allocator is not symmetric, and reduces all the same")
         del a, b
 
     # ---- host buffers through the GPUs, three chunks in flight ----

@@ -68,8 +68,25 @@ def main():
                                     ok = all(close(out[r], want[r * count:(r + 1) * count], name, n) for r in range(n))
                                 assert ok, ("pipe", chunk, nv, ctas, n, kind, name, op, count, in_place, misalign)
                                 cases += 1
+        # a staging half much smaller than the message: the chunk slots are used as a ring (copy-in waits for the slot's
+        # previous tenant to be gone) and chunk numbers run past one call's flag values into the following call numbers
+        L.dccl_emu_set_pipe(4096, 2)
+        for n in (2, 4, 8):
+            for kind, counts in (("allreduce", (4099, 50001)), ("reducescatter", (4099,))):
+                for name, op in (("float32", "sum"), ("bfloat16", "avg")):
+                    for count in counts:
+                        for in_place, misalign in ((0, 0), (1, 0), (0, 4 if name == "float32" else 2)):
+                            ins = inputs_for(name, op, count * n if kind == "reducescatter" else count, n, seed=83)
+                            out = emu(L, kind, "nvls", n, name, op, count, ins, ctas=7, in_place=in_place, misalign=misalign, iters=3, stage=64 << 10)
+                            want = oracle.fold(ins, op, bf16=name == "bfloat16")
+                            if kind == "allreduce":
+                                ok = all(close(out[r], want, name, n) for r in range(n))
+                            else:
+                                ok = all(close(out[r], want[r * count:(r + 1) * count], name, n) for r in range(n))
+                            assert ok, ("pipe ring", n, kind, name, op, count, in_place, misalign)
+                            cases += 1
     finally:
-        L.dccl_emu_set_pipe(8 << 20, 0)
+        L.dccl_emu_set_pipe(16 << 20, 0)
     # zero-copy forms: the user buffers themselves are multicast-mapped (what dcclMemAlloc memory is)
     L.dccl_emu_set_switch_form(0)
     L.dccl_emu_set_peer_buffers(1)
