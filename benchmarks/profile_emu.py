@@ -69,7 +69,8 @@ def main():
     out_elems = count * n if args.kind == "allgather" else count
     hin = np.ones(in_elems * n, dtype=np.float32)
     hout = np.zeros(out_elems * n, dtype=np.float32)
-    stage = int(max(in_elems, out_elems) * 4 * 2.5) + (1 << 20)
+    # staging per half: the staged variants need up to (n + 1) / n of the message, Rabenseifner log2(n) + 1 areas of it
+    stage = int(max(in_elems, out_elems) * 4 * (4.5 if args.algo == "rabenseifner" else 2.5)) + (1 << 20)
     rc = L.dccl_emu_collective(args.kind.encode(), args.algo.encode(), n, 7, 0, count, 0, args.ctas, 0, 0, args.iters, stage,
                                hin.ctypes.data, hout.ctypes.data)
     print("rc", rc, "sample", hout[:2])

@@ -61,7 +61,7 @@ bool GpuCommImpl::init(std::string* err) {
     direct_rs_ = cfg.get_bool("DCCL/direct_reduce_scatter", true);
     direct_rs_min_bytes_ = (size_t)cfg.get_int("DCCL/direct_reduce_scatter_min_bytes", 32ll << 20);
     p2p_rdv_ = cfg.get_bool("DCCL/p2p_rendezvous", true);
-    pipe_ctas_ = (int)cfg.get_int("DCCL/nvls_pipe_ctas", 80);
+    pipe_ctas_ = (int)cfg.get_int("DCCL/nvls_pipe_ctas", 112);
     pipe_nv_ctas_ = (int)cfg.get_int("DCCL/nvls_pipe_nv_ctas", 16);
     pipe_teams_ = (int)cfg.get_int("DCCL/nvls_pipe_teams", 2);
     if (pipe_teams_ < 1 || pipe_teams_ > 4) pipe_teams_ = 2;

@@ -144,7 +144,7 @@ private:
     int threads_ = 512;
     int sm_count_ = 148;
     size_t pipe_min_bytes_ = 16u << 20;   // ordinary-buffer switch all-reduce is pipelined from this size on (0 = never)
-    int pipe_ctas_ = 80;                  // grid of the pipelined switch all-reduce: pipe_nv_ctas_ switch CTAs, the rest copy in / out
+    int pipe_ctas_ = 112;                 // grid of the pipelined switch all-reduce: pipe_nv_ctas_ switch CTAs, the rest copy in / out
     int pipe_nv_ctas_ = 16;
     int pipe_teams_ = 2;                  // the switch CTAs take the chunks in turn, in this many teams
     int pipe_unroll_ = 4;                 // vectors in flight per thread in the pipeline's switch pass
