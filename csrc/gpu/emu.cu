@@ -392,7 +392,7 @@ int dccl_emu_collective(const char* kind_s, const char* algo_s, int nranks, int 
                 if (algo == ALGO_ONESHOT) { cap = oneshot_ll_capacity_bytes() / es; if (count <= cap) e = launch_oneshot_ll(a, dt, cfg); }
                 else if (algo == ALGO_TWOSHOT_LL) { a.mode = LL2_ALLREDUCE; cap = ll_twoshot_capacity_bytes(nranks) / es; if (count <= cap) e = launch_ll_twoshot(a, dt, cfg); }
                 else if (algo == ALGO_RING) { a.mode = RING_ALLREDUCE; cap = ring_capacity(a.mode, nranks, es, stage_bytes); if (count <= cap) e = launch_ring(a, dt, cfg); }
-                else if (algo == ALGO_RABENSEIFNER) { cap = hd_capacity(nranks, es, stage_bytes); if (count <= cap && is_power_of_two((uint32_t)nranks)) e = launch_hd(a, dt, cfg); }
+                else if (algo == ALGO_RABENSEIFNER) { cap = hd_capacity(nranks, es, stage_bytes); if (count <= cap) e = launch_hd(a, dt, cfg); }
                 else if (direct) { a.symmetric = 1; a.mode = DIRECT_ALLREDUCE; cap = count; e = launch_direct(a, dt, cfg); }
                 else { a.mode = TS_ALLREDUCE; cap = twoshot_capacity(a.mode, nranks, es, stage_bytes); if (count <= cap) e = launch_twoshot(a, dt, cfg); }
             } else if (coll == COLL_REDUCE && algo == ALGO_TWOSHOT_LL) {

@@ -112,7 +112,6 @@ ncclResult_t GpuCommImpl::all_reduce(const void* send, void* recv, size_t count,
     if (ch.algo == ALGO_NVLS && !nvls_ok) ch.algo = ALGO_TWOSHOT;
     if (ch.algo == ALGO_ONESHOT && bytes > oneshot_ll_capacity_bytes()) ch.algo = ALGO_TWOSHOT;
     if (ch.algo == ALGO_TWOSHOT_LL && bytes > ll_twoshot_capacity_bytes(n_)) ch.algo = ALGO_TWOSHOT;
-    if (ch.algo == ALGO_RABENSEIFNER && !is_power_of_two((uint32_t)n_)) ch.algo = ALGO_TWOSHOT;
     if (ch.algo == ALGO_LOCAL || ch.algo == ALGO_AUTO) ch.algo = ALGO_TWOSHOT;
     last_[COLL_ALLREDUCE] = ch.algo;
 

@@ -74,6 +74,24 @@ def test_allreduce_fp32_bf16_sizes(dccl_lib, algo, n):
                     assert np.array_equal(out[r], out[0]), (algo, n, name, op, count, "ranks differ")
 
 
+@pytest.mark.parametrize("n", [3, 5, 6, 7])
+def test_rabenseifner_on_worlds_that_are_not_a_power_of_two(dccl_lib, n):
+    """n = 2^m + r: the first 2r ranks pair up (the odd one hands its vector to the even one and gets the result back),
+    the rest run the halving and doubling steps on 2^m ranks. Every rank must end with the same bits, at the largest
+    count the staging takes too."""
+    stage = 1 << 20
+    cap = _capacity_fp32("rabenseifner", "allreduce", n, stage)
+    for name, op, count, in_place, misalign in [("float32", "sum", 1, 0, 0), ("float32", "avg", 10007, 0, 4), ("bfloat16", "sum", 65536 + 5, 1, 0),
+                                                ("int32", "max", 4099, 0, 0), ("float64", "prod", 257, 1, 8), ("float32", "sum", cap, 0, 0)]:
+        ins = inputs_for(name, op, count, n, seed=71 + n)
+        want = oracle.fold(ins, op, bf16=name == "bfloat16")
+        out = emu(dccl_lib, "allreduce", "rabenseifner", n, name, op, count, ins, in_place=in_place, misalign=misalign, iters=3, stage=stage)
+        for r in range(n):
+            assert close(out[r], want, name, n), (n, name, op, count, r)
+        for r in range(1, n):
+            assert np.array_equal(out[r], out[0]), (n, name, op, count, "ranks differ")
+
+
 @pytest.mark.parametrize("algo", ["oneshot", "twoshot", "ring", "rabenseifner"])
 def test_allreduce_every_dtype_and_operator(dccl_lib, algo):
     n, count = 4, 1031
@@ -326,7 +344,8 @@ def _capacity_fp32(algo, kind, n, stage):
     if algo == "ring":
         return n * fl(elems // (2 * n)) if kind == "allreduce" else fl(elems // (2 * n))
     if algo == "rabenseifner":
-        return fl(elems // (n.bit_length()))                      # log2(n) + 1 areas for a power of two
+        # log2(n) + 1 areas for a power of two, one more for the leader / follower pairs of any other world
+        return fl(elems // (n.bit_length() + (1 if n & (n - 1) else 0)))
     if kind in ("allreduce", "reduce"):
         return n * fl(elems // (n + 1))
     if kind == "reducescatter":

@@ -56,6 +56,12 @@ def test_messages_larger_than_staging_are_chunked():
     run(world, ["--suite", "chunk"], env={"DCCL_STAGING_BYTES": str(4 << 20)})
 
 
+@pytest.mark.skipif(gpu_count() < 3, reason="needs three GPUs")
+def test_every_variant_on_a_world_that_is_not_a_power_of_two():
+    """Three ranks: halving and doubling with one leader / follower pair, and every other variant on an odd world."""
+    run(3, ["--suite", "basic"])
+
+
 @pytest.mark.skipif(gpu_count() < 2, reason="needs two GPUs")
 def test_peer_handles_fallback_without_multicast():
     """cudaIpc handles instead of cuMem descriptors: no multicast, peer loads / stores only."""
