@@ -36,7 +36,7 @@ struct AutoBuf {                  // what a rank tells the others about one of i
     unsigned long long offset;    // of the buffer inside the allocation
     unsigned long long size;      // of the allocation
     unsigned int fresh;           // the peers have not opened this allocation yet
-    unsigned int pad;
+    unsigned int symmetric;       // 1: symmetric memory, mapped everywhere already; `base` is the number of the segment
     cudaIpcMemHandle_t handle;
 };
 struct AutoMsg { AutoBuf b[2]; };
@@ -83,13 +83,25 @@ bool GpuCommImpl::auto_view(const void* send, const void* recv, const char** sen
     std::string err;
     const DriverApi* d = driver_api(&err);
     AutoMsg mine;
-    describe(d, send, auto_exports_, &mine.b[0]);
+    auto describe_any = [&](const void* buf, AutoBuf* out) {
+        // symmetric memory was allocated collectively: segment i is segment i on every rank, and every rank maps all of it
+        const char* c = (const char*)buf;
+        for (size_t i = 0; i < user_segs_.size(); i++) {
+            const SymSegment& s = user_segs_[i];
+            if (c < s.base[rank_] || c >= s.base[rank_] + s.size) continue;
+            memset(out, 0, sizeof(*out));
+            out->id = ~0ull; out->base = i; out->offset = (unsigned long long)(c - s.base[rank_]); out->size = s.size; out->symmetric = 1;
+            return;
+        }
+        describe(d, buf, auto_exports_, out);
+    };
+    describe_any(send, &mine.b[0]);
     if (recv == send) mine.b[1] = mine.b[0];
-    else describe(d, recv, auto_exports_, &mine.b[1]);
+    else describe_any(recv, &mine.b[1]);
     std::vector<AutoMsg> all((size_t)n_);
     if (!bs_->fast_allgather(&mine, sizeof(mine), all.data())) { dccl_warn("lazy registration: %s", bs_->last_error().c_str()); return false; }
     for (int k = 0; k < 2; k++)
-        if (mine.b[k].id) auto_exports_[mine.b[k].base].announced = true;
+        if (mine.b[k].id && !mine.b[k].symmetric) auto_exports_[mine.b[k].base].announced = true;
 
     bool usable = true, any_fresh = false;
     unsigned char failed[2] = {0, 0};     // bit q: this rank could not open rank q's send / receive allocation
@@ -97,6 +109,7 @@ bool GpuCommImpl::auto_view(const void* send, const void* recv, const char** sen
         for (int k = 0; k < 2; k++) {
             const AutoBuf& b = all[q].b[k];
             if (!b.id) { usable = false; continue; }
+            if (b.symmetric) { if (b.base >= user_segs_.size()) usable = false; continue; }
             if (b.fresh) any_fresh = true;
             if (q == rank_) continue;
             if (!import_allocation(q, b.base, b.id, (size_t)b.size, b.handle)) failed[k] |= (unsigned char)(1u << q);
@@ -127,8 +140,12 @@ bool GpuCommImpl::auto_view(const void* send, const void* recv, const char** sen
     if (!usable) return false;
     for (int q = 0; q < n_; q++) {
         if (q == rank_) { send_peers[q] = (const char*)send; recv_peers[q] = (const char*)recv; continue; }
-        send_peers[q] = (const char*)auto_imports_[std::make_pair(q, all[q].b[0].base)].mapped + all[q].b[0].offset;
-        recv_peers[q] = (const char*)auto_imports_[std::make_pair(q, all[q].b[1].base)].mapped + all[q].b[1].offset;
+        const char** out[2] = {&send_peers[q], &recv_peers[q]};
+        for (int k = 0; k < 2; k++) {
+            const AutoBuf& b = all[q].b[k];
+            *out[k] = b.symmetric ? user_segs_[(size_t)b.base].base[q] + b.offset
+                                  : (const char*)auto_imports_[std::make_pair(q, b.base)].mapped + b.offset;
+        }
     }
     return true;
 }

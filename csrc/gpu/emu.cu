@@ -30,6 +30,7 @@ int g_device_seq = 0;
 // set by dccl_emu_set_peer_buffers: the user buffers count as addressable by every rank (symmetric / registered
 // memory), so that the two-shot all-reduce takes its zero-copy form
 int g_peer_buffers = 0;
+int g_bcast_chunks = 0;
 // set by dccl_emu_set_mix: (collective, variant) pairs launched before every call under test
 std::vector<std::pair<int, GpuAlgo>> g_mix;
 // set by dccl_emu_set_guard: guard words in the unused parts of every virtual rank's pool, checked after each run
@@ -258,8 +259,11 @@ void dccl_emu_set_pipe(size_t chunk_bytes, int nv_ctas) { nvls_pipe_set_chunk_by
  *  mapped. */
 void dccl_emu_set_p2p_rendezvous(int mode) { g_p2p_rdv = mode; }
 
-/** 1: all-reduce with the two-shot variant runs its zero-copy form on the emulated ranks' user buffers. */
+/** 1: all-reduce, reduce-scatter, broadcast and reduce with the two-shot variant run their zero-copy forms on the emulated ranks' user buffers. */
 void dccl_emu_set_peer_buffers(int on) { g_peer_buffers = on ? 1 : 0; }
+
+/** Chunks per shard of the zero-copy broadcast (0: by message size, as the library does). */
+void dccl_emu_set_bcast_chunks(int chunks) { g_bcast_chunks = chunks; }
 
 /**
  * Run `iters` back-to-back calls of one collective among `nranks` virtual ranks on the current
@@ -313,7 +317,7 @@ int dccl_emu_collective(const char* kind_s, const char* algo_s, int nranks, int 
             ios[r].recv_peer[p] = (char*)ios[p].recv;
         }
     const bool direct = g_peer_buffers && algo == ALGO_TWOSHOT && misalign % 16 == 0 &&
-                        (coll == COLL_ALLREDUCE || (coll == COLL_REDUCESCATTER && (count * es) % 16 == 0));
+                        (coll == COLL_ALLREDUCE || coll == COLL_REDUCE || coll == COLL_BROADCAST || (coll == COLL_REDUCESCATTER && (count * es) % 16 == 0));
 #ifdef DCCL_HOST_SIM
     // with "peer buffers" on, the user buffers also count as multicast-bound (what dcclMemAlloc memory is): the switch
     // kernels then run their zero-copy forms on them
@@ -410,6 +414,10 @@ int dccl_emu_collective(const char* kind_s, const char* algo_s, int nranks, int 
             } else if (coll == COLL_ALLGATHER) {
                 if (algo == ALGO_RING) { a.mode = RING_ALLGATHER; cap = ring_capacity(a.mode, nranks, es, stage_bytes); if (count <= cap) e = launch_ring(a, dt, cfg); }
                 else { a.mode = TS_ALLGATHER; cap = twoshot_capacity(a.mode, nranks, es, stage_bytes); if (count <= cap) e = launch_twoshot(a, dt, cfg); }
+            } else if (coll == COLL_BROADCAST && direct) {
+                a.symmetric = 1; cap = count; e = launch_direct_bcast(a, count * es, nranks, cfg, g_bcast_chunks);
+            } else if (coll == COLL_REDUCE && direct) {
+                a.symmetric = 1; a.mode = DIRECT_REDUCE; cap = count; e = launch_direct(a, dt, cfg);
             } else if (coll == COLL_BROADCAST) {
                 a.mode = algo == ALGO_ONESHOT ? TS_BROADCAST_DIRECT : TS_BROADCAST;
                 cap = twoshot_capacity(a.mode, nranks, es, stage_bytes);

@@ -43,6 +43,10 @@ bool GpuCommImpl::set_param(const char* name, int value) {
     if (k == "p2p_rendezvous" && (value == 0 || value == 1)) { p2p_rdv_ = value == 1; return true; }
     if (k == "device_seq" && (value == 0 || value == 1)) return set_device_seq(value == 1);
     if (k == "rooted_pipe" && (value == 0 || value == 1)) { rooted_pipe_ = value == 1; return true; }
+    if (k == "direct_rooted" && (value == 0 || value == 1)) { direct_rooted_ = value == 1; return true; }
+    if (k == "direct_rooted_ctas" && value >= 1 && value <= kMaxCtas) { direct_rooted_ctas_ = value; return true; }
+    if (k == "direct_bcast_min_kb" && value >= 0) { direct_bcast_min_bytes_ = (size_t)value << 10; return true; }
+    if (k == "direct_bcast_ctas" && value >= 1 && value <= kMaxCtas) { direct_bcast_ctas_ = value; return true; }
     if (k == "pipe_chunk_kb" && value >= 256) { nvls_pipe_set_chunk_bytes((size_t)value << 10); return true; }
     return false;
 }
@@ -443,6 +447,27 @@ ncclResult_t GpuCommImpl::broadcast(const void* send, void* recv, size_t count, 
             return cuda_result(launch_nvls(a, dt, cfg), "nvls broadcast (symmetric)");
         }
     }
+    // Large messages on buffers the peers can address (symmetric, registered, or ordinary ones mapped on first use): the
+    // receivers load the message out of the root's buffer and out of each other's, no staging. The exchange is collective
+    // and entered on facts every rank shares; the root describes its source, the others only their destination.
+    if (algo == ALGO_AUTO && direct_rooted_ && auto_min_bytes_ > 0 && bytes >= auto_min_bytes_ && bytes >= direct_bcast_min_bytes_ &&
+        (ch.algo == ALGO_NVLS || ch.algo == ALGO_TWOSHOT)) {
+        const char* sp[kMaxPeers];
+        const char* rp[kMaxPeers];
+        bool ok = auto_view(send, recv, sp, rp);
+        ok = ok && (uintptr_t)sp[root] % 16 == 0;
+        for (int p = 0; ok && p < n_; p++) ok = (uintptr_t)rp[p] % 16 == 0;
+        if (ok) {
+            zero_copy_calls_++;
+            a.symmetric = 1;
+            for (int p = 0; p < n_; p++) { a.io.send_peer[p] = sp[p]; a.io.recv_peer[p] = (char*)rp[p]; }
+            if (ctas_override_ == 0) cfg.ctas = ctas_for(direct_bcast_ctas_);
+            NEXT_SEQ(a);
+            launches_++;
+            last_[COLL_BROADCAST] = ALGO_TWOSHOT;
+            return cuda_result(launch_direct_bcast(a, bytes, n_, cfg), "zero-copy broadcast");
+        }
+    }
     const int ts_mode = ch.algo == ALGO_ONESHOT ? TS_BROADCAST_DIRECT : TS_BROADCAST;
     // large messages through the switch: the receivers' copy-out overlaps the root's push chunk by chunk
     const bool rooted = ch.algo == ALGO_NVLS && rooted_pipe_ && bytes >= rooted_pipe_min_bytes_;
@@ -505,6 +530,27 @@ ncclResult_t GpuCommImpl::reduce(const void* send, void* recv, size_t count, ncc
         NEXT_SEQ(a);
         launches_++;
         return cuda_result(launch_ll_twoshot(a, dt, cfg), "two-shot packet reduce");
+    }
+    // Large messages on buffers the peers can address: the ranks other than the root fold one shard each straight out of
+    // every rank's send buffer into the root's receive buffer. Only the root's receive buffer matters.
+    if (algo == ALGO_AUTO && direct_rooted_ && auto_min_bytes_ > 0 && bytes >= auto_min_bytes_ && (ch.algo == ALGO_NVLS || ch.algo == ALGO_TWOSHOT)) {
+        const char* sp[kMaxPeers];
+        const char* rp[kMaxPeers];
+        bool ok = auto_view(send, rank_ == root ? recv : send, sp, rp);
+        ok = ok && (uintptr_t)rp[root] % 16 == 0;
+        for (int p = 0; ok && p < n_; p++) ok = (uintptr_t)sp[p] % 16 == 0;
+        if (ok) {
+            zero_copy_calls_++;
+            a.symmetric = 1;
+            for (int p = 0; p < n_; p++) { a.io.send_peer[p] = sp[p]; a.io.recv_peer[p] = (char*)rp[p]; }
+            a.mode = DIRECT_REDUCE;
+            a.count = count;
+            if (ctas_override_ == 0) cfg.ctas = ctas_for(direct_rooted_ctas_);
+            NEXT_SEQ(a);
+            launches_++;
+            last_[COLL_REDUCE] = ALGO_TWOSHOT;
+            return cuda_result(launch_direct(a, dt, cfg), "zero-copy reduce");
+        }
     }
     // large messages through the switch: every rank's copy-in overlaps the root's switch pass chunk by chunk
     const bool rooted = ch.algo == ALGO_NVLS && rooted_pipe_ && bytes >= rooted_pipe_min_bytes_;

@@ -53,7 +53,7 @@ bool GpuCommImpl::init(std::string* err) {
     if (!ok) { cudaGetLastError(); if (err) *err = "cudaSetDevice(" + std::to_string(dev_) + ") failed"; }
     if (ok) { int sms = 0; if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev_) == cudaSuccess && sms > 0) sm_count_ = sms; }
     ctas_override_ = (int)cfg.get_int("DCCL/ctas", 0);
-    p2p_ctas_ = (int)cfg.get_int("DCCL/p2p_ctas", 16);
+    p2p_ctas_ = (int)cfg.get_int("DCCL/p2p_ctas", 32);
     set_param("threads", (int)cfg.get_int("DCCL/threads", 512));
     set_param("unroll", (int)cfg.get_int("DCCL/unroll", 8));
     pipe_min_bytes_ = (size_t)cfg.get_int("DCCL/nvls_pipe_min_bytes", 16ll << 20);
@@ -67,6 +67,12 @@ bool GpuCommImpl::init(std::string* err) {
     if (pipe_teams_ < 1 || pipe_teams_ > 4) pipe_teams_ = 2;
     device_stamps_ = cfg.get_bool("DCCL/device_stamps", false);
     rooted_pipe_ = cfg.get_bool("DCCL/nvls_rooted_pipe", false);
+    direct_rooted_ = cfg.get_bool("DCCL/direct_rooted", true);
+    direct_rooted_ctas_ = (int)cfg.get_int("DCCL/direct_rooted_ctas", 64);
+    direct_bcast_min_bytes_ = (size_t)cfg.get_int("DCCL/direct_broadcast_min_bytes", 32ll << 20);
+    if (direct_rooted_ctas_ < 1 || direct_rooted_ctas_ > kMaxCtas) direct_rooted_ctas_ = 64;
+    direct_bcast_ctas_ = (int)cfg.get_int("DCCL/direct_broadcast_ctas", 128);
+    if (direct_bcast_ctas_ < 1 || direct_bcast_ctas_ > kMaxCtas) direct_bcast_ctas_ = 128;
     nvls_pipe_set_chunk_bytes((size_t)cfg.get_int("DCCL/nvls_pipe_chunk_bytes", 16ll << 20));
     rooted_pipe_min_bytes_ = (size_t)cfg.get_int("DCCL/nvls_rooted_pipe_min_bytes", 16ll << 20);
     if (p2p_ctas_ < 1) p2p_ctas_ = 1;

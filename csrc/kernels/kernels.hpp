@@ -25,8 +25,12 @@ cudaError_t launch_twoshot(const CollArgs& a, ncclDataType_t dt, const LaunchCfg
 
 /* direct.cu: zero-copy peer all-reduce (io.send_peer / io.recv_peer hold every rank's buffers, 16-byte aligned) and
  * reduce-scatter (io.send_peer, io.recv; count = per-rank elements, stride = slot distance, slots 16-byte aligned) */
-enum { DIRECT_ALLREDUCE = 0, DIRECT_REDUCESCATTER };
+enum { DIRECT_ALLREDUCE = 0, DIRECT_REDUCESCATTER, DIRECT_REDUCE };
 cudaError_t launch_direct(const CollArgs& a, ncclDataType_t dt, const LaunchCfg& cfg);
+/* zero-copy broadcast of `bytes` bytes from a.root (io.send_peer[root], io.recv_peer[*], all 16-byte aligned): scatter and
+ * all-gather by peer loads, pipelined in `chunks` chunks per shard (0: direct_bcast_chunks(), about 1 MB each, at most 24) */
+int direct_bcast_chunks(size_t bytes, int nranks);
+cudaError_t launch_direct_bcast(const CollArgs& a, size_t bytes, int nranks, const LaunchCfg& cfg, int chunks = 0);
 
 /* oneshot_ll.cu: flag-in-data all-reduce for small messages */
 size_t oneshot_ll_capacity_bytes();

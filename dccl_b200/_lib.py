@@ -102,6 +102,7 @@ def _declare(lib):
         "dccl_selftest_symmem": (i, [vp, i]),
         "dccl_emu_set_device_seq": (None, [i]),
         "dccl_emu_set_peer_buffers": (None, [i]),
+        "dccl_emu_set_bcast_chunks": (None, [i]),
         "dccl_emu_switch_single": (i, [i, i, sz, i, i, vp, vp]),
         "dccl_local_reduce": (i, [vp, vp, sz, i, i]),
         "dccl_local_reduce_device": (i, [vp, vp, sz, i, i, vp]),

@@ -201,7 +201,7 @@ class Communicator:
 
     def set_param(self, name, value):
         """Tuning knob for sweeps: ctas (0 = table), threads, unroll, p2p_ctas, pipe_ctas, pipe_nv_ctas, pipe_chunk_kb,
-        auto_register_min_kb (0: no lazy registration), direct_rs."""
+        auto_register_min_kb (0: no lazy registration), direct_rs, direct_rooted, direct_rooted_ctas, direct_bcast_min_kb."""
         _check(lib().dccl_comm_set_param(self._h, name.encode(), int(value)), "set_param")
 
     def set_algorithm(self, collective, name):

@@ -11,6 +11,7 @@
 extern "C" int dccl_emu_collective(const char*, const char*, int, int, int, size_t, int, int, int, size_t, int, size_t, const void*, void*);
 extern "C" int dccl_emu_sendrecv_ring(int, size_t, int, int, int, const void*, void*);
 extern "C" void dccl_emu_set_peer_buffers(int);
+extern "C" void dccl_emu_set_bcast_chunks(int);
 extern "C" void dccl_emu_set_device_seq(int);
 extern "C" void dccl_emu_set_switch_form(int);
 extern "C" int dccl_emu_set_mix(const char*);
@@ -56,6 +57,13 @@ int main(int argc, char** argv) {
     bad += run_one("allreduce", "twoshot", 4, 40000, 0, 0);
     bad += run_one("allreduce", "twoshot", 8, 4099, 1, 0);
     bad += run_one("reducescatter", "twoshot", 4, 4096, 0, 0);
+    // zero-copy broadcast (scatter and all-gather by peer loads, five chunks per shard) and reduce (root n - 1)
+    dccl_emu_set_bcast_chunks(5);
+    for (int n2 : {2, 3, 8}) {
+        bad += run_one("broadcast", "twoshot", n2, 300000, 0, 0);
+        bad += run_one("reduce", "twoshot", n2, 100003, n2 == 3, 0);
+    }
+    dccl_emu_set_bcast_chunks(0);
     dccl_emu_set_peer_buffers(0);
     dccl_emu_set_device_seq(1);
     for (const char* algo : algos) bad += run_one("allreduce", algo, 4, 1031, 0, 0);

@@ -304,6 +304,35 @@ def test_zero_copy_two_shot_on_peer_addressable_buffers(dccl_lib):
         dccl_lib.dccl_emu_set_peer_buffers(0)
 
 
+@pytest.mark.parametrize("n", [2, 3, 5, 8])
+def test_zero_copy_broadcast_and_reduce_on_peer_addressable_buffers(dccl_lib, n):
+    """Broadcast as a pipelined scatter and all-gather by peer loads (every chunk count from one to more chunks than the
+    shard has vectors), reduce with one shard per rank other than the root folded into the root's buffer; every root."""
+    dccl_lib.dccl_emu_set_peer_buffers(1)
+    try:
+        for root in sorted({0, 1, n - 1}):
+            for chunks in [1, 2, 5, 24]:
+                dccl_lib.dccl_emu_set_bcast_chunks(chunks)
+                for name, count in [("uint8", 1), ("uint8", 4099), ("float32", 16), ("bfloat16", 100003), ("float32", (1 << 18) + 4), ("float64", 777)]:
+                    ins = inputs_for(name, "sum", count, n, seed=83 + root)
+                    for in_place in [0, 1]:
+                        out = emu(dccl_lib, "broadcast", "twoshot", n, name, "sum", count, ins, root=root, in_place=in_place, ctas=5, iters=3)
+                        for r in range(n):
+                            assert np.array_equal(out[r], ins[root]), ("bcast", n, root, chunks, name, count, r, in_place)
+            dccl_lib.dccl_emu_set_bcast_chunks(0)
+            for name in ["bfloat16", "float32", "int32", "float64"]:
+                for count in [1, 7, 4096, 100003, (1 << 19) + 24]:
+                    for op in ["sum", "avg", "max"]:
+                        ins = inputs_for(name, op, count, n, seed=89)
+                        want = oracle.fold(ins, op, bf16=name == "bfloat16")
+                        for in_place in [0, 1]:
+                            out = emu(dccl_lib, "reduce", "twoshot", n, name, op, count, ins, root=root, in_place=in_place, ctas=5)
+                            assert close(out[root], want, name, n), ("reduce", n, root, name, count, op, in_place)
+    finally:
+        dccl_lib.dccl_emu_set_bcast_chunks(0)
+        dccl_lib.dccl_emu_set_peer_buffers(0)
+
+
 @pytest.mark.parametrize("n", [2, 4, 8])
 def test_ring_kernel_adds_in_ring_order(dccl_lib, n):
     """fp32 sum through the ring kernel against a fold in the order the ring adds, shard by shard (shards are whole

@@ -145,6 +145,43 @@ def main():
         comm.set_param("direct_rs", 0)
         comm.set_algorithm("allreduce", "auto")
         comm.set_algorithm("reducescatter", "auto")
+        # broadcast and reduce from the same threshold on: the receivers load the message out of the root's buffer and out
+        # of each other's; the owners of a shard fold it into the root's buffer. Ordinary tensors, a root whose source is
+        # symmetric memory, every root position, in place; one unaligned rank sends everybody down the staged path.
+        comm.set_param("direct_bcast_min_kb", 4096)       # by default the broadcast takes this path from 32 MB on
+        for name, count in [("bfloat16", (4 << 20) + 72), ("float32", (3 << 20) + 4), ("uint8", (5 << 20) + 13)]:
+            ins = [oracle.make_input(name, count, seed=7700 + r) for r in range(world)]
+            want = oracle.fold(ins, "sum", bf16=name == "bfloat16")
+            for root in sorted({0, 1 % world, world - 1}):
+                for variant in ["plain", "in place", "symmetric source", "unaligned"]:
+                    shift = 1 if variant == "unaligned" and rank == world - 1 else 0
+                    base_s = comm.symmetric_empty(count + 16, to_torch(ins[rank][:1], name, dev).dtype, local) if variant == "symmetric source" \
+                        else torch.zeros(count + 16, dtype=to_torch(ins[rank][:1], name, dev).dtype, device=dev)
+                    base_o = torch.zeros(count + 16, dtype=base_s.dtype, device=dev)
+                    v = base_s[shift:shift + count]
+                    o = v if variant == "in place" else base_o[shift:shift + count]
+                    v.copy_(to_torch(ins[rank], name, dev))
+                    z0 = comm.stat("zero_copy_calls")
+                    for _ in range(2):
+                        comm.broadcast(v, o, root=root)
+                    torch.cuda.synchronize()
+                    zc = comm.stat("zero_copy_calls") - z0
+                    check(zc == (0 if variant == "unaligned" else 2), "broadcast %s %s root %d: zero-copy calls %d" % (name, variant, root, zc))
+                    check(np.array_equal(to_numpy(o.contiguous(), name), ins[root]), "lazy broadcast %s %s root %d" % (name, variant, root))
+                    if name != "uint8":
+                        v.copy_(to_torch(ins[rank], name, dev))
+                        z0 = comm.stat("zero_copy_calls")
+                        comm.reduce(v, o if rank == root or variant == "in place" else None, op="sum", root=root)
+                        torch.cuda.synchronize()
+                        zc = comm.stat("zero_copy_calls") - z0
+                        check(zc == (0 if variant == "unaligned" else 1), "reduce %s %s root %d: zero-copy calls %d" % (name, variant, root, zc))
+                        check(rank != root or close(to_numpy(o.contiguous(), name), want, name, world), "lazy reduce %s %s root %d" % (name, variant, root))
+                    torch.cuda.synchronize()
+                    comm.barrier()
+                    if variant == "symmetric source":
+                        comm.free_symmetric(base_s)
+                    del base_s, base_o, v, o
+        comm.set_param("direct_bcast_min_kb", 32 << 10)
         # variant choices that only one rank's alignment could have changed: a reduce-scatter into an unaligned receive
         # buffer (pipelined switch form from 256 KB on) and an all-gather from an unaligned source into symmetric memory
         if comm.has_multicast:
