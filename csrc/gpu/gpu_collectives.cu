@@ -450,7 +450,9 @@ ncclResult_t GpuCommImpl::broadcast(const void* send, void* recv, size_t count, 
     // Large messages on buffers the peers can address (symmetric, registered, or ordinary ones mapped on first use): the
     // receivers load the message out of the root's buffer and out of each other's, no staging. The exchange is collective
     // and entered on facts every rank shares; the root describes its source, the others only their destination.
-    if (algo == ALGO_AUTO && direct_rooted_ && auto_min_bytes_ > 0 && bytes >= auto_min_bytes_ && bytes >= direct_bcast_min_bytes_ &&
+    // (two ranks: one hop, nothing to forward; it beats the staged form from 16 MB on)
+    const size_t direct_min = n_ == 2 && direct_bcast_min_bytes_ > (16u << 20) ? (size_t)(16u << 20) : direct_bcast_min_bytes_;
+    if (algo == ALGO_AUTO && direct_rooted_ && auto_min_bytes_ > 0 && bytes >= auto_min_bytes_ && bytes >= direct_min &&
         (ch.algo == ALGO_NVLS || ch.algo == ALGO_TWOSHOT)) {
         const char* sp[kMaxPeers];
         const char* rp[kMaxPeers];
