@@ -9,9 +9,15 @@ from the previous measured size (exclusive) to its own (inclusive); the last one
 on symmetric buffers go to the keys allreduce_sym / reducescatter_sym.
 
     python benchmarks/make_tune_table.py --in results/sweep.json --in results/sym_nvls16.json:16 --out tune.txt
+
+`--builtin` writes the table that is compiled into the library instead (the starting point for a table of one's own; the
+copy kept in cfg/tune_b200_nvswitch.txt is made this way and a unit test holds the two together):
+
+    python benchmarks/make_tune_table.py --builtin --out cfg/tune_b200_nvswitch.txt
 """
 import argparse
 import json
+import os
 import sys
 
 COLL = {"allreduce": "allreduce", "all_reduce": "allreduce", "reducescatter": "reducescatter", "reduce_scatter": "reducescatter",
@@ -68,12 +74,45 @@ def build(rows):
     return rules
 
 
+BUILTIN_HEADER = """# Variant table of dccl-b200 for B200 GPUs on one NVSwitch box: the table compiled into the library, in the format of
+# DCCL_TUNE_FILE / [DCCL] tune_file. Written by: python benchmarks/make_tune_table.py --builtin
+#
+#   <collective> <nranks|*> <max_bytes> <algorithm> <ctas> [<element bytes>]
+#
+# Rules of one (collective, nranks) are tried in ascending max_bytes; an exact world size beats '*'. The rows come from
+# sweeps of every variant and CTA count on 2, 4 and 8 B200s (bf16 and fp32 sum; 1 KB - 1 GB), best per size bucket.
+# allreduce_sym / reducescatter_sym: buffers in symmetric memory (dcclMemAlloc). Where the row says twoshot and the peers
+# can address the buffers (symmetric, registered, or mapped on first use from 4 MB on) the zero-copy peer form runs.
+"""
+
+
+def builtin_table():
+    sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    import ctypes
+    from dccl_b200._lib import lib
+    n = lib().dccl_tuner_dump(None, 0)
+    buf = ctypes.create_string_buffer(n + 1)
+    lib().dccl_tuner_dump(buf, n + 1)
+    return buf.value.decode()
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--in", dest="inputs", action="append", required=True, help="sweep JSON, optionally FILE:CTAS")
+    ap.add_argument("--in", dest="inputs", action="append", default=[], help="sweep JSON, optionally FILE:CTAS")
     ap.add_argument("--ctas", type=int, default=32, help="CTA count for rows that do not say")
+    ap.add_argument("--builtin", action="store_true", help="write the table compiled into the library")
     ap.add_argument("--out", default="-")
     args = ap.parse_args()
+    if args.builtin:
+        text = BUILTIN_HEADER + builtin_table()
+        if args.out == "-":
+            sys.stdout.write(text)
+        else:
+            with open(args.out, "w") as f:
+                f.write(text)
+        return 0
+    if not args.inputs:
+        ap.error("give --in FILE (one or more) or --builtin")
     rows = []
     for spec in args.inputs:
         rows += load(spec, args.ctas)

@@ -225,6 +225,13 @@ int dccl_tuner_choose(const char* coll, int nranks, size_t bytes, int nvls_ok, c
     return 0;
 }
 
+/** The process-wide table in the file format; returns the length of the text (the copy is cut to `len` - 1 characters). */
+size_t dccl_tuner_dump(char* out, size_t len) {
+    const std::string text = test_tuner().dump();
+    if (out && len) snprintf(out, len, "%s", text.c_str());
+    return text.size();
+}
+
 /** As dccl_tuner_choose, for elements of `esize` bytes (rules bound to an element width come first). */
 int dccl_tuner_choose_width(const char* coll, int nranks, size_t bytes, int nvls_ok, int esize, char* algo_out, size_t len, int* ctas) {
     int c = coll && !strcmp(coll, "allreduce_sym") ? TUNE_ALLREDUCE_SYM : coll && !strcmp(coll, "reducescatter_sym") ? TUNE_REDUCESCATTER_SYM : parse_collective_name(coll);

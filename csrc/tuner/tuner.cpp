@@ -17,7 +17,7 @@ static const TuneRule kBuiltin[] = {
     // Measured on 8 x B200 (bf16 sum; sweep of every variant x CTA count, best per size bucket).
     // all-reduce, ordinary buffers: packets while latency bound (8-15 us to 64 KB), the two-shot packet form to 2 MB
     // (16.5-23 us where the staged switch form and NCCL take 28-32), then the switch through staging, pipelined from
-    // 16 MB on (634 / 765 / 768 GB/s at 64 MB / 256 MB / 1 GB against 428 / 657 / 727 for NCCL)
+    // 16 MB on (staging half as a ring of 16 MB chunk slots, grid of 112 CTAs: 812-822 GB/s at 1 GB against 728 for NCCL)
     {COLL_ALLREDUCE, 0, 64u << 10, ALGO_ONESHOT, 8},
     {COLL_ALLREDUCE, 0, 2u << 20, ALGO_TWOSHOT_LL, 32},
     {COLL_ALLREDUCE, 0, 8u << 20, ALGO_NVLS, 64},
@@ -62,6 +62,8 @@ static const TuneRule kBuiltin[] = {
     {COLL_ALLGATHER, 0, 1u << 20, ALGO_NVLS, 32},
     {COLL_ALLGATHER, 0, 16u << 20, ALGO_NVLS, 128},       // 16 MB: 40 us through the switch, 47 by peer loads
     {COLL_ALLGATHER, 0, kInf, ALGO_TWOSHOT, 128},
+    // broadcast / reduce: packets, then the switch through staging; on buffers the peers can address (or can map on first
+    // use) the dispatcher takes the zero-copy peer forms instead: reduce from 4 MB on, broadcast from 32 MB (two ranks: 16 MB)
     {COLL_BROADCAST, 0, 256u << 10, ALGO_ONESHOT, 16},
     {COLL_BROADCAST, 0, kInf, ALGO_NVLS, 64},
     {COLL_REDUCE, 0, 64u << 10, ALGO_ONESHOT, 8},
@@ -88,6 +90,27 @@ void Tuner::add(const TuneRule& r) {
         if (a.esize != b.esize) return a.esize > b.esize;       // exact element widths before the wildcard
         return a.max_bytes < b.max_bytes;
     });
+}
+
+std::string Tuner::dump() const {
+    static const char* const kNames[] = {"allreduce", "reducescatter", "allgather", "broadcast", "reduce"};
+    std::ostringstream out;
+    for (const TuneRule& r : rules_) {
+        const char* coll = r.coll == TUNE_ALLREDUCE_SYM ? "allreduce_sym" : r.coll == TUNE_REDUCESCATTER_SYM ? "reducescatter_sym"
+                           : r.coll >= 0 && r.coll < (int)(sizeof(kNames) / sizeof(kNames[0])) ? kNames[r.coll] : nullptr;
+        if (!coll) continue;
+        out << coll << ' ';
+        if (r.nranks) out << r.nranks; else out << '*';
+        out << ' ';
+        if (r.max_bytes == kInf) out << "inf";
+        else if (r.max_bytes % (1u << 20) == 0) out << (r.max_bytes >> 20) << 'm';
+        else if (r.max_bytes % (1u << 10) == 0) out << (r.max_bytes >> 10) << 'k';
+        else out << r.max_bytes;
+        out << ' ' << algo_name(r.algo) << ' ' << r.ctas;
+        if (r.esize) out << ' ' << r.esize;
+        out << '\n';
+    }
+    return out.str();
 }
 
 static bool parse_bytes(const std::string& s, size_t* out) {

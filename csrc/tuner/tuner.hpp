@@ -61,6 +61,8 @@ public:
     /** nvls_ok: the variant can serve this (dtype, op, buffers) on this communicator. */
     TuneChoice choose(int coll, int nranks, size_t bytes, bool nvls_ok, int esize = 0) const;
     const std::vector<TuneRule>& rules() const { return rules_; }
+    /** The table in the file format (one rule per line), so that it can be written out, edited and loaded again. */
+    std::string dump() const;
 
 private:
     void add(const TuneRule& r);

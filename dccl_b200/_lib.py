@@ -92,6 +92,7 @@ def _declare(lib):
         "dccl_tuner_choose": (i, [cp, i, sz, i, cp, sz, c.POINTER(i)]),
         "dccl_tuner_choose_width": (i, [cp, i, sz, i, i, cp, sz, c.POINTER(i)]),
         "dccl_tuner_load_text": (i, [cp]),
+        "dccl_tuner_dump": (sz, [cp, sz]),
     }
     cuda_only = {
         "dccl_emu_collective": (i, [cp, cp, i, i, i, sz, i, i, i, sz, i, sz, vp, vp]),

@@ -285,3 +285,33 @@ def test_profile_summary_from_a_raw_page():
     assert [l[0] for l in lines[:3]] == ["gpu__time_duration.sum", "dram__bytes_read.sum", "launch__registers_per_thread"]
     assert [l[0] for l in lines[3:]] == [pre + s + post for s in ("long_scoreboard", "membar", "barrier")]
     assert lines[0][1:] == ("12.5", "us")
+
+
+def test_committed_table_file_is_the_built_in_table(tmp_path):
+    """cfg/tune_b200_nvswitch.txt is what `make_tune_table.py --builtin` writes (a fresh process: no test has touched the
+    table), and loading it over the built-in table changes no choice."""
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = {k: v for k, v in os.environ.items() if k != "DCCL_TUNE_FILE"}
+    p = subprocess.run([sys.executable, os.path.join(root, "benchmarks", "make_tune_table.py"), "--builtin"], capture_output=True, text=True,
+                       env=env, check=True)
+    committed = open(os.path.join(root, "cfg", "tune_b200_nvswitch.txt")).read()
+    assert p.stdout == committed
+    rules = [line for line in committed.splitlines() if line and not line.startswith("#")]
+    assert len(rules) >= 30 and all(len(r.split()) in (5, 6) for r in rules)
+    code = ("import ctypes, sys\n"
+            "from dccl_b200._lib import lib\n"
+            "L = lib()\n"
+            "def pick(coll, n, b, w):\n"
+            "    a = ctypes.create_string_buffer(32); c = ctypes.c_int()\n"
+            "    assert L.dccl_tuner_choose_width(coll, n, b, 1, w, a, 32, ctypes.byref(c)) == 0\n"
+            "    return a.value, c.value\n"
+            "grid = [(coll, n, 1 << s, w) for coll in [b'allreduce', b'allreduce_sym', b'reducescatter', b'reducescatter_sym', b'allgather', b'broadcast', b'reduce']\n"
+            "        for n in (2, 3, 4, 8) for s in range(2, 31, 2) for w in (1, 2, 4, 8)]\n"
+            "before = [pick(*g) for g in grid]\n"
+            "assert L.dccl_tuner_load_text(open(sys.argv[1]).read().encode()) >= 30\n"
+            "assert [pick(*g) for g in grid] == before\n"
+            "print('same')\n")
+    q = subprocess.run([sys.executable, "-c", code, os.path.join(root, "cfg", "tune_b200_nvswitch.txt")], capture_output=True, text=True, env=env, cwd=root)
+    assert q.returncode == 0 and "same" in q.stdout, q.stdout + q.stderr
