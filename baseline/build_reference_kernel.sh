@@ -4,10 +4,11 @@
 # the reference's own headers plus a generated dccl/config.h (what its CMake writes from config.h.in when CUDA is
 # found). The rest of the original needs Derecho, libfabric and spdlog and cannot be built offline; this file needs
 # none of them because the source hides them behind NVCC_VISIBLE.
-#   baseline/build_reference_kernel.sh [path to the reference tree, default /root/reference]
+#   baseline/build_reference_kernel.sh <path to the reference tree>      (or DCCL_REFERENCE_DIR=<path>)
 # benchmarks/local_reduce_bench.py times it against this library's dccl_local_reduce on the same buffers.
 set -e
-REF=${1:-/root/reference}
+REF=${1:-$DCCL_REFERENCE_DIR}
+if [ -z "$REF" ] || [ ! -f "$REF/src/core/reduce.cu" ]; then echo "usage: $0 <path to the reference tree>" >&2; exit 2; fi
 HERE=$(cd "$(dirname "$0")" && pwd)
 OUT=$HERE/_ref
 mkdir -p "$OUT/gen/dccl"
