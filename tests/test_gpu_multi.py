@@ -58,8 +58,8 @@ def test_messages_larger_than_staging_are_chunked():
 
 @pytest.mark.skipif(gpu_count() < 3, reason="needs three GPUs")
 def test_every_variant_on_a_world_that_is_not_a_power_of_two():
-    """Three ranks: halving and doubling with one leader / follower pair, and every other variant on an odd world."""
-    run(3, ["--suite", "basic"])
+    """Three ranks: halving and doubling with one leader / follower pair, next to the two-shot and ring forms."""
+    run(3, ["--suite", "odd_world"])
 
 
 @pytest.mark.skipif(gpu_count() < 2, reason="needs two GPUs")

@@ -53,6 +53,34 @@ def main():
         if not ok:
             failures.append(what)
 
+    if args.suite == "odd_world":
+        # all-reduce of every staged peer variant on a world that is not a power of two: halving and doubling folds the
+        # world onto the next lower power of two through leader / follower pairs
+        for algo in ["rabenseifner", "twoshot", "ring"]:
+            comm.set_algorithm("allreduce", algo)
+            for name in ["float32", "bfloat16", "int32"]:
+                for count in [1, 1000, 300001, 4 << 20]:
+                    ins = [oracle.make_input(name, count, seed=37 * r + count % 103) for r in range(world)]
+                    for op in ["sum", "avg", "max"]:
+                        want = oracle.fold(ins, op, bf16=name == "bfloat16")
+                        s = to_torch(ins[rank], name, dev)
+                        r = torch.zeros_like(s)
+                        for _ in range(3):
+                            comm.all_reduce(s, r, op=op)
+                        torch.cuda.synchronize()
+                        check(comm.last_algorithm("allreduce") == algo, "all_reduce %s ran %s" % (algo, comm.last_algorithm("allreduce")))
+                        check(close(to_numpy(r, name), want, name, world), "all_reduce %s %s %s n=%d" % (algo, name, op, count))
+                        comm.all_reduce(s, op=op)   # in place
+                        torch.cuda.synchronize()
+                        check(close(to_numpy(s, name), want, name, world), "all_reduce in place %s %s %s n=%d" % (algo, name, op, count))
+        launches = comm.stat("launches")
+        comm.finalize()
+        if failures:
+            print("FAILED %d of %d on rank %d: %s" % (len(failures), cases, rank, "; ".join(failures[:10])))
+            sys.exit(1)
+        print("OK %d multicast=%d launches=%d" % (cases, 0, launches))
+        return
+
     if args.suite == "rooted":
         # broadcast / reduce of large ordinary buffers with the pipelined switch form switched on
         if not comm.has_multicast:
