@@ -209,10 +209,9 @@ __device__ DCCL_NOINLINE void copy_set(const CopySet& p, int ns, bool dual, ptrd
     }
     // only the end of the message can be ragged
     for (int s = 0; s < ns; s++) {
-        const size_t body = p.len[s] / 16 * 16;
-        if (body + tid < p.len[s]) {
-            p.dst[s][body + tid] = p.src[s][body + tid];
-            if (dual) const_cast<char*>(p.src[s])[local_delta + (ptrdiff_t)(body + tid)] = p.src[s][body + tid];
+        for (size_t j = p.len[s] / 16 * 16 + tid; j < p.len[s]; j += nt) {
+            p.dst[s][j] = p.src[s][j];
+            if (dual) const_cast<char*>(p.src[s])[local_delta + (ptrdiff_t)j] = p.src[s][j];
         }
     }
 }
@@ -241,8 +240,8 @@ __device__ DCCL_NOINLINE void fan_out(const char* src, char* const* dsts, int nd
                 if (d < nd) *reinterpret_cast<uint4*>(dst[d] + i * 16) = v[u];
         }
     }
-    if (nv * 16 + tid < len)
-        for (int d = 0; d < nd; d++) dsts[d][nv * 16 + tid] = src[nv * 16 + tid];
+    for (size_t j = nv * 16 + tid; j < len; j += nt)
+        for (int d = 0; d < nd; d++) dsts[d][j] = src[j];
 }
 
 /**

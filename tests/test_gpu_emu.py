@@ -333,6 +333,40 @@ def test_zero_copy_broadcast_and_reduce_on_peer_addressable_buffers(dccl_lib, n)
         dccl_lib.dccl_emu_set_peer_buffers(0)
 
 
+def test_zero_copy_rooted_forms_and_odd_worlds_on_random_shapes(dccl_lib):
+    """Forty shapes drawn with a fixed seed: world size, root, chunk count, grid, element count, type, in place or not.
+    Every byte of a broadcast must arrive exactly once whatever the cut into shards, chunks, teams and CTA slices;
+    the reduce and the halving-and-doubling all-reduce must match the serial fold."""
+    rng = np.random.RandomState(20240607)
+    dccl_lib.dccl_emu_set_peer_buffers(1)
+    try:
+        for case in range(40):
+            n = int(rng.randint(2, 9))
+            root = int(rng.randint(0, n))
+            chunks = int(rng.choice([1, 2, 3, 7, 24]))
+            ctas = int(rng.choice([1, 2, 3, 6]))
+            name = str(rng.choice(["uint8", "bfloat16", "float32", "float64"]))
+            count = int(rng.choice([1, 15, 16, 17, 1000, 4097, 70001, 300007]))
+            in_place = int(rng.randint(0, 2))
+            ins = inputs_for(name, "sum", count, n, seed=100 + case)
+            dccl_lib.dccl_emu_set_bcast_chunks(chunks)
+            out = emu(dccl_lib, "broadcast", "twoshot", n, name, "sum", count, ins, root=root, in_place=in_place, ctas=ctas, iters=2)
+            for r in range(n):
+                assert np.array_equal(out[r], ins[root]), ("bcast", case, n, root, chunks, ctas, name, count, in_place, r)
+            if name != "uint8":
+                op = str(rng.choice(["sum", "avg", "min"]))
+                ins = inputs_for(name, op, count, n, seed=200 + case)
+                want = oracle.fold(ins, op, bf16=name == "bfloat16")
+                out = emu(dccl_lib, "reduce", "twoshot", n, name, op, count, ins, root=root, in_place=in_place, ctas=ctas, iters=2)
+                assert close(out[root], want, name, n), ("reduce", case, n, root, ctas, name, count, op, in_place)
+                out = emu(dccl_lib, "allreduce", "rabenseifner", n, name, op, count, ins, in_place=in_place, ctas=ctas, iters=2, stage=32 << 20)
+                for r in range(n):
+                    assert close(out[r], want, name, n), ("rabenseifner", case, n, ctas, name, count, op, in_place, r)
+    finally:
+        dccl_lib.dccl_emu_set_bcast_chunks(0)
+        dccl_lib.dccl_emu_set_peer_buffers(0)
+
+
 @pytest.mark.parametrize("n", [2, 4, 8])
 def test_ring_kernel_adds_in_ring_order(dccl_lib, n):
     """fp32 sum through the ring kernel against a fold in the order the ring adds, shard by shard (shards are whole

@@ -35,7 +35,7 @@ def sim_lib():
 
 def test_emulation_tests_on_the_host_simulation(sim_lib):
     select = ("fp32_bf16_sizes or not_a_power_of_two or roots or send_recv_ring or ring_order or (two_shot_packet and 2) or guard_words or sequence_number "
-              "or (all_to_all_as and (4-4 or 8-1)) or (zero_copy_broadcast and 3)")
+              "or (all_to_all_as and (4-4 or 8-1)) or (zero_copy_broadcast and 3) or random_shapes")
     env = dict(os.environ, DCCL_LIBRARY=sim_lib)
     p = subprocess.run([sys.executable, "-m", "pytest", os.path.join(ROOT, "tests", "test_gpu_emu.py"), "-q", "-m", "gpu", "-p", "no:cacheprovider", "-k", select],
                        env=env, capture_output=True, text=True, timeout=1500)
