@@ -269,8 +269,10 @@ const char*   dcclGetLastAlgorithm(ncclComm_t comm, const char* collective);
 
 /**
  * Tuning knob of the communicator's device side, for sweeps and tools: "ctas" (0: the table's value), "threads",
- * "unroll", "p2p_ctas", "pipe_ctas", "pipe_nv_ctas", "pipe_chunk_kb", "pipe_min_mb", "rooted_pipe",
- * "auto_register_min_kb" (0: no lazy registration), "direct_rs", "device_seq". Every rank sets the same value at the
+ * "unroll", "p2p_ctas", "p2p_rendezvous", "pipe_ctas", "pipe_nv_ctas", "pipe_teams", "pipe_unroll", "pipe_chunk_kb",
+ * "pipe_min_mb", "rooted_pipe", "auto_register_min_kb" (0: no lazy registration), "direct_rs", "direct_rs_min_mb",
+ * "direct_rooted" (zero-copy reduce / broadcast), "direct_rooted_ctas", "direct_bcast_ctas", "direct_bcast_min_kb",
+ * "device_seq". Every rank sets the same value at the
  * same point of its call order. ncclInvalidArgument for an unknown name or a value out of range, ncclInvalidUsage
  * before a device was bound.
  */
