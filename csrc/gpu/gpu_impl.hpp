@@ -153,6 +153,7 @@ private:
     size_t rooted_pipe_min_bytes_ = 16u << 20;
     bool direct_rooted_ = true;           // reduce from the lazy-registration threshold on, broadcast from direct_bcast_min_bytes_
     int direct_rooted_ctas_ = 64;         // on: zero-copy peer forms (direct.cu). Grid of the reduce (8 GPUs, 256 MB: 598 us with 64 CTAs, 640 with 128)
+    bool direct_reduce_small_ = false;    // worlds of 2-4 ranks: zero-copy reduce from the lazy-registration threshold on too (default: from 32 MB)
     int direct_bcast_ctas_ = 128;         // and of the broadcast (506 us with 64, 487 with 128)
     size_t direct_bcast_min_bytes_ = 32u << 20;   // below it the two hops of the zero-copy broadcast cost more than the staging copy
     bool sticky_error_ = false;

@@ -63,7 +63,7 @@ static const TuneRule kBuiltin[] = {
     {COLL_ALLGATHER, 0, 16u << 20, ALGO_NVLS, 128},       // 16 MB: 40 us through the switch, 47 by peer loads
     {COLL_ALLGATHER, 0, kInf, ALGO_TWOSHOT, 128},
     // broadcast / reduce: packets, then the switch through staging; on buffers the peers can address (or can map on first
-    // use) the dispatcher takes the zero-copy peer forms instead: reduce from 4 MB on, broadcast from 32 MB (two ranks: 16 MB)
+    // use) the dispatcher takes the zero-copy peer forms instead: reduce from 4 MB on (worlds of up to four ranks: 32 MB), broadcast from 32 MB (two ranks: 16 MB)
     {COLL_BROADCAST, 0, 256u << 10, ALGO_ONESHOT, 16},
     {COLL_BROADCAST, 0, kInf, ALGO_NVLS, 64},
     {COLL_REDUCE, 0, 64u << 10, ALGO_ONESHOT, 8},

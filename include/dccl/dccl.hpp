@@ -272,7 +272,7 @@ const char*   dcclGetLastAlgorithm(ncclComm_t comm, const char* collective);
  * "unroll", "p2p_ctas", "p2p_rendezvous", "pipe_ctas", "pipe_nv_ctas", "pipe_teams", "pipe_unroll", "pipe_chunk_kb",
  * "pipe_min_mb", "rooted_pipe", "auto_register_min_kb" (0: no lazy registration), "direct_rs", "direct_rs_min_mb",
  * "direct_rooted" (zero-copy reduce / broadcast), "direct_rooted_ctas", "direct_bcast_ctas", "direct_bcast_min_kb",
- * "device_seq". Every rank sets the same value at the
+ * "direct_reduce_small_worlds", "device_seq". Every rank sets the same value at the
  * same point of its call order. ncclInvalidArgument for an unknown name or a value out of range, ncclInvalidUsage
  * before a device was bound.
  */

@@ -176,7 +176,8 @@ def main():
         # broadcast and reduce from the same threshold on: the receivers load the message out of the root's buffer and out
         # of each other's; the owners of a shard fold it into the root's buffer. Ordinary tensors, a root whose source is
         # symmetric memory, every root position, in place; one unaligned rank sends everybody down the staged path.
-        comm.set_param("direct_bcast_min_kb", 4096)       # by default the broadcast takes this path from 32 MB on
+        comm.set_param("direct_bcast_min_kb", 4096)       # by default the broadcast takes this path from 32 MB on,
+        comm.set_param("direct_reduce_small_worlds", 1)   # and so does the reduce on worlds of up to four ranks
         for name, count in [("bfloat16", (4 << 20) + 72), ("float32", (3 << 20) + 4), ("uint8", (5 << 20) + 13)]:
             ins = [oracle.make_input(name, count, seed=7700 + r) for r in range(world)]
             want = oracle.fold(ins, "sum", bf16=name == "bfloat16")
@@ -210,6 +211,7 @@ def main():
                         comm.free_symmetric(base_s)
                     del base_s, base_o, v, o
         comm.set_param("direct_bcast_min_kb", 32 << 10)
+        comm.set_param("direct_reduce_small_worlds", 0)
         # variant choices that only one rank's alignment could have changed: a reduce-scatter into an unaligned receive
         # buffer (pipelined switch form from 256 KB on) and an all-gather from an unaligned source into symmetric memory
         if comm.has_multicast:
