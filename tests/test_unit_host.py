@@ -315,3 +315,17 @@ def test_committed_table_file_is_the_built_in_table(tmp_path):
             "print('same')\n")
     q = subprocess.run([sys.executable, "-c", code, os.path.join(root, "cfg", "tune_b200_nvswitch.txt")], capture_output=True, text=True, env=env, cwd=root)
     assert q.returncode == 0 and "same" in q.stdout, q.stdout + q.stderr
+
+
+def test_table_dump_round_trips_rules_with_an_element_width(dccl_lib):
+    """A rule bound to an element width comes back out of the dump in the file format, and the dump loads again."""
+    assert dccl_lib.dccl_tuner_load_text(b"broadcast 8 3m twoshot 24 2\nbroadcast * inf nvls 48\n") == 2
+    n = dccl_lib.dccl_tuner_dump(None, 0)
+    buf = ctypes.create_string_buffer(n + 1)
+    dccl_lib.dccl_tuner_dump(buf, n + 1)
+    lines = buf.value.decode().splitlines()
+    assert "broadcast 8 3m twoshot 24 2" in lines and "broadcast * inf nvls 48" in lines
+    assert dccl_lib.dccl_tuner_load_text(buf.value) == len(lines)
+    buf2 = ctypes.create_string_buffer(n + 1)
+    dccl_lib.dccl_tuner_dump(buf2, n + 1)
+    assert buf2.value == buf.value
